@@ -1,0 +1,109 @@
+/* kquant_b200 - C ABI of the B200 (sm_100a) quantized-weight path.
+ *
+ * A drop-in for the quantized-weight ops of asher/mlx-kquant: the entry points
+ * below are what the reference's op layer (src/kquant_ops.cpp) hands to its
+ * Primitive::eval_* implementations, flattened to plain pointers and sizes. File
+ * and line citations are paths inside the reference repository.
+ *
+ * Conventions
+ *  - Every function returns 0 on success or a KQ_ERR_* code and records a
+ *    message retrievable with kq_last_error() (thread-local). Argument errors
+ *    carry the reference's message text, prefixed "[mlx_kquant.<op>]".
+ *  - All data pointers are DEVICE pointers owned by the caller unless a name
+ *    ends in _host. Nothing is allocated internally; the one kernel family that
+ *    needs scratch (gather) takes a caller-provided workspace whose size is
+ *    given by kq_gather_qmm_workspace_bytes().
+ *  - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).
+ *    Calls are asynchronous; ordering is stream order.
+ *  - dtype codes: KQ_F32 = 0, KQ_F16 = 1, KQ_BF16 = 2.
+ *  - Codecs are named as in the reference registry (src/kquant_codec.cpp:12-37);
+ *    this library implements q2_k q3_k q4_k q5_k q6_k q4_0 q8_0 iq4_nl iq4_xs
+ *    iq2_xxs and reports any other name as unknown.
+ */
+#ifndef KQUANT_B200_H
+#define KQUANT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define KQ_API __attribute__((visibility("default")))
+#else
+#define KQ_API
+#endif
+
+#define KQ_F32 0
+#define KQ_F16 1
+#define KQ_BF16 2
+
+#define KQ_OK 0
+#define KQ_ERR_INVALID_ARGUMENT 1 /* the reference throws std::invalid_argument here */
+#define KQ_ERR_RUNTIME 2          /* the reference throws std::runtime_error here */
+#define KQ_ERR_CUDA 3             /* a CUDA call failed; message holds cudaGetErrorString */
+#define KQ_ERR_UNSUPPORTED 4      /* valid in the reference, not built here yet */
+
+/* Message of the last failing call on this thread ("" if none). */
+KQ_API const char* kq_last_error(void);
+
+/* Library version string. */
+KQ_API const char* kq_version(void);
+
+/* ---- codec registry: replaces codec_by_name / codec_names,
+ * src/kquant_codec.h:10-25, src/kquant_codec.cpp:12-55 ---- */
+KQ_API int kq_codec_count(void);
+/* Fills the geometry of codec `index` (0 <= index < kq_codec_count()); any
+ * out-pointer may be NULL. *name points at a static string. */
+KQ_API int kq_codec_info(int index, const char** name, int* weights_per_block, int* bytes_per_block, int* bits,
+                  int* requires_imatrix);
+/* Index of a codec name, or -1. */
+KQ_API int kq_codec_find(const char* name);
+
+/* ---- dequantize: replaces KQuantDequantize::eval_cpu / eval_gpu,
+ * src/kquant_dequantize.cpp:59-130 (op: src/kquant_ops.cpp:55-110) ----
+ * w: w_bytes of wire data, a whole number of blocks. out: w_bytes /
+ * bytes_per_block * weights_per_block elements of out_dtype. Bit-exact with the
+ * reference's CPU decoders for f32; f16/bf16 are the IEEE round-to-nearest-even
+ * of that f32 value. */
+KQ_API int kq_dequantize(const void* w, size_t w_bytes, const char* kquant_type, int out_dtype, void* out, void* stream);
+
+/* ---- quantized_matmul: replaces KQuantMatmul::eval_cpu / eval_gpu,
+ * src/kquant_matmul.cpp:1104-1164, 1199-1488 (op: src/kquant_ops.cpp:112-183) ----
+ * y[rows, N] = x[rows, K] . dequant(w)^T with fp32 accumulation, w laid out
+ * [N, K / weights_per_block * bytes_per_block] (transpose != 0).
+ *  - x_dtype KQ_F16 / KQ_BF16: y has the same dtype. KQ_F32: x is rounded to
+ *    bf16 and y is bf16, as the reference's op does (src/kquant_ops.cpp:159).
+ *  - x rows: `rows` of them (all leading dims of the reference's x flattened),
+ *    x_row_stride elements apart, each row contiguous and 16-byte aligned.
+ *  - y rows are y_row_stride elements apart.
+ *  - transpose == 0 ([K, N] weights) is not built yet: KQ_ERR_UNSUPPORTED. */
+KQ_API int kq_quantized_matmul(const void* x, int x_dtype, long long rows, int K, long long x_row_stride, const void* w,
+                        size_t w_row_bytes, int N, const char* kquant_type, int transpose, void* y,
+                        long long y_row_stride, void* stream);
+
+/* ---- gather_qmm: replaces KQuantGatherQMM::eval_cpu / eval_gpu,
+ * src/kquant_gather.cpp:470-746, 819-956 (op: src/kquant_ops.cpp:293-420) ----
+ * For every index entry b in [0, n_entries):
+ *     y[b] [M, N] = x[lhs[b]] [M, K] . dequant(w[rhs[b]])^T
+ * x: [x_batch, M, K] dense (x_dtype as above); w: n_experts matrices, matrix e
+ * at w + e * w_expert_stride_bytes (64-bit, so strided views and stacks above
+ * 2 GiB work, cf. src/kquant_gather.cpp:548-563); lhs / rhs: uint32 device
+ * arrays of n_entries, already broadcast together; y: [n_entries, M, N] dense.
+ * rhs_sorted != 0 promises rhs is non-decreasing (the reference's right_sorted
+ * flag); it is a hint only, results do not depend on it.
+ * workspace: at least kq_gather_qmm_workspace_bytes(n_entries, M, n_experts)
+ * bytes of device memory, 256-byte aligned, private to this call until it
+ * completes on the stream. */
+KQ_API size_t kq_gather_qmm_workspace_bytes(long long n_entries, int M, int n_experts);
+KQ_API int kq_gather_qmm(const void* x, int x_dtype, long long x_batch, int M, int K, const void* w, int n_experts,
+                  long long w_expert_stride_bytes, size_t w_row_bytes, int N, const char* kquant_type,
+                  const uint32_t* lhs_indices, const uint32_t* rhs_indices, long long n_entries, int transpose,
+                  int rhs_sorted, void* y, void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KQUANT_B200_H */

@@ -1,0 +1,183 @@
+// The extern "C" surface declared in include/kquant_b200.h: argument validation
+// with the reference op layer's rules and message texts (src/kquant_ops.cpp),
+// regime selection, and kernel launches. No allocation happens here.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include "../../include/kquant_b200.h"
+#include "kq_common.cuh"
+#include "kq_launch.h"
+
+namespace {
+
+thread_local std::string g_err;
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_err = buf;
+  return code;
+}
+
+int cuda_fail(const char* what, cudaError_t e) {
+  return fail(KQ_ERR_CUDA, "[mlx_kquant] %s: CUDA error: %s", what, cudaGetErrorString(e));
+}
+
+int find_codec(const char* name) {
+  if (name == nullptr) return -1;
+  for (int i = 0; i < kq::NUM_CODECS; i++)
+    if (std::strcmp(kq::kCodecs[i].name, name) == 0) return i;
+  return -1;
+}
+
+bool dtype_ok(int d) { return d == KQ_F32 || d == KQ_F16 || d == KQ_BF16; }
+
+}  // namespace
+
+extern "C" {
+
+const char* kq_last_error(void) { return g_err.c_str(); }
+
+const char* kq_version(void) { return "kquant_b200 0.1 (sm_100a)"; }
+
+int kq_codec_count(void) { return kq::NUM_CODECS; }
+
+int kq_codec_info(int index, const char** name, int* wpb, int* bpb, int* bits, int* requires_imatrix) {
+  if (index < 0 || index >= kq::NUM_CODECS) return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant] codec index out of range");
+  const kq::CodecInfo& c = kq::kCodecs[index];
+  if (name) *name = c.name;
+  if (wpb) *wpb = c.wpb;
+  if (bpb) *bpb = c.bpb;
+  if (bits) *bits = c.bits;
+  if (requires_imatrix) *requires_imatrix = c.requires_imatrix;
+  return KQ_OK;
+}
+
+int kq_codec_find(const char* name) { return find_codec(name); }
+
+int kq_dequantize(const void* w, size_t w_bytes, const char* kquant_type, int out_dtype, void* out, void* stream) {
+  const int ci = find_codec(kquant_type);
+  if (ci < 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.dequantize] Unknown kquant_type: '%s'.",
+                kquant_type ? kquant_type : "(null)");
+  const kq::CodecInfo& c = kq::kCodecs[ci];
+  if (w_bytes % (size_t)c.bpb != 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.dequantize] Last dim (%zu) must be a multiple of bytes_per_block (%d) for codec '%s'.",
+                w_bytes, c.bpb, c.name);
+  if (!dtype_ok(out_dtype))
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.dequantize] Only real floating output dtypes are supported.");
+  if (w_bytes == 0) return KQ_OK;
+  if (w == nullptr || out == nullptr) return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.dequantize] null pointer.");
+  cudaError_t e = kq::launch_dequantize(ci, static_cast<const uint8_t*>(w), (long long)(w_bytes / c.bpb), out_dtype,
+                                        out, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("dequantize", e);
+  return KQ_OK;
+}
+
+int kq_quantized_matmul(const void* x, int x_dtype, long long rows, int K, long long x_row_stride, const void* w,
+                        size_t w_row_bytes, int N, const char* kquant_type, int transpose, void* y,
+                        long long y_row_stride, void* stream) {
+  const int ci = find_codec(kquant_type);
+  if (ci < 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.quantized_matmul] Unknown kquant_type: '%s'.",
+                kquant_type ? kquant_type : "(null)");
+  const kq::CodecInfo& c = kq::kCodecs[ci];
+  if (w_row_bytes % (size_t)c.bpb != 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.quantized_matmul] KQuant weight last dim (%zu bytes) is not a whole number of %d-byte %s "
+                "blocks.",
+                w_row_bytes, c.bpb, c.name);
+  if (!dtype_ok(x_dtype))
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.quantized_matmul] Only real floating x dtypes are supported.");
+  if (!transpose)
+    return fail(KQ_ERR_UNSUPPORTED, "[mlx_kquant.quantized_matmul] transpose=false ([K, N] weights) is not built yet.");
+  const long long wpr = (long long)(w_row_bytes / c.bpb) * c.wpb;
+  if (wpr != K)
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.quantized_matmul] x last dim (%d) does not match the expanded quantized matrix inner dim "
+                "(%lld) for codec '%s' with transpose=true.",
+                K, wpr, c.name);
+  if (rows < 0 || N < 0) return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.quantized_matmul] negative size.");
+  if (rows == 0 || N == 0) return KQ_OK;
+  if (!x || !w || !y) return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.quantized_matmul] null pointer.");
+  const size_t xe = x_dtype == KQ_F32 ? 4 : 2;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || ((size_t)x_row_stride * xe) % 16 != 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.quantized_matmul] x rows must be 16-byte aligned.");
+  if (rows > 16LL * 65535)
+    return fail(KQ_ERR_UNSUPPORTED, "[mlx_kquant.quantized_matmul] more than 1048560 rows in one call.");
+
+  kq::GemvArgs a{};
+  a.x = x;
+  a.x_row_stride = x_row_stride;
+  a.y = y;
+  a.y_row_stride = y_row_stride;
+  a.w = static_cast<const uint8_t*>(w);
+  a.w_align16 = (reinterpret_cast<uintptr_t>(w) & 15) == 0 ? 1 : 0;
+  a.row_bytes = (long long)w_row_bytes;
+  a.N = N;
+  a.K = K;
+  a.M = (int)rows;
+  cudaError_t e = kq::launch_gemv(ci, x_dtype, a, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("quantized_matmul", e);
+  return KQ_OK;
+}
+
+size_t kq_gather_qmm_workspace_bytes(long long n_entries, int M, int n_experts) {
+  if (n_entries < 0 || M <= 0 || n_experts <= 0) return 0;
+  return kq::gather_layout(n_entries, M, n_experts).total;
+}
+
+int kq_gather_qmm(const void* x, int x_dtype, long long x_batch, int M, int K, const void* w, int n_experts,
+                  long long w_expert_stride_bytes, size_t w_row_bytes, int N, const char* kquant_type,
+                  const uint32_t* lhs_indices, const uint32_t* rhs_indices, long long n_entries, int transpose,
+                  int rhs_sorted, void* y, void* workspace, size_t workspace_bytes, void* stream) {
+  (void)rhs_sorted;
+  (void)x_batch;
+  const int ci = find_codec(kquant_type);
+  if (ci < 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmm] Unknown kquant_type: '%s'.",
+                kquant_type ? kquant_type : "(null)");
+  const kq::CodecInfo& c = kq::kCodecs[ci];
+  if (w_row_bytes % (size_t)c.bpb != 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.gather_qmm] KQuant weight last dim (%zu bytes) is not a whole number of %d-byte %s blocks.",
+                w_row_bytes, c.bpb, c.name);
+  if (!dtype_ok(x_dtype))
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmm] Only real floating x dtypes are supported.");
+  if (!transpose)
+    return fail(KQ_ERR_UNSUPPORTED, "[mlx_kquant.gather_qmm] transpose=false ([K, N] weights) is not built yet.");
+  const long long wpr = (long long)(w_row_bytes / c.bpb) * c.wpb;
+  if (wpr != K)
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.gather_qmm] x last dim (%d) does not match the expanded quantized matrix inner dim (%lld) "
+                "for codec '%s' with transpose=true.",
+                K, wpr, c.name);
+  if (n_entries < 0 || M < 0 || N < 0 || n_experts < 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmm] negative size.");
+  if (n_entries == 0 || M == 0 || N == 0) return KQ_OK;
+  if (n_experts == 0) return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmm] no expert matrices.");
+  if (!x || !w || !y || !lhs_indices || !rhs_indices)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmm] null pointer.");
+  const size_t xe = x_dtype == KQ_F32 ? 4 : 2;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || ((size_t)K * xe) % 16 != 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmm] x rows must be 16-byte aligned.");
+  const size_t need = kq::gather_layout(n_entries, M, n_experts).total;
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmm] workspace too small: %zu bytes given, %zu needed.",
+                workspace_bytes, need);
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmm] workspace must be 256-byte aligned.");
+  cudaError_t e = kq::launch_gather(ci, x_dtype, x, M, K, static_cast<const uint8_t*>(w), n_experts,
+                                    w_expert_stride_bytes, (long long)w_row_bytes, N, lhs_indices, rhs_indices,
+                                    n_entries, y, workspace, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("gather_qmm", e);
+  return KQ_OK;
+}
+
+}  // extern "C"

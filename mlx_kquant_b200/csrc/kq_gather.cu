@@ -1,0 +1,182 @@
+// gather_qmm (mixture-of-experts matmul): for every index entry b,
+//   y[b] [M, N] = x[lhs[b]] [M, K] . dequant(w[rhs[b]])^T
+// replacing KQuantGatherQMM::eval_cpu (src/kquant_gather.cpp:470-746). Like the
+// reference, entries are grouped by expert so each expert's wire bytes are
+// streamed once per 16 rows instead of once per entry; unlike the reference
+// the grouping happens on the device, inside the caller's stream, with no host
+// round trip:
+//   1. histogram of rhs -> rows per expert
+//   2. one-CTA exclusive scan -> entry offsets and task offsets per expert
+//   3. scatter of entry ids into expert order
+//   4. task build: each expert's c*M rows are cut into GemvTask slices of 16
+//   5. the skinny-M kernel runs over (row tile, task)
+// All of it lives in a caller-provided workspace laid out by gather_layout().
+#include "kq_common.cuh"
+#include "kq_launch.h"
+
+namespace kq {
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+GatherLayout gather_layout(long long n_entries, int M, int n_experts) {
+  GatherLayout L;
+  const long long rows = n_entries * (long long)M;
+  // every task but at most one per expert is full, and no task is empty
+  long long mt = rows / 16 + (n_entries < n_experts ? n_entries : n_experts);
+  if (mt > rows) mt = rows;
+  if (mt < 1) mt = 1;
+  L.max_tasks = mt;
+  size_t off = 0;
+  L.counts = off;    off = align_up(off + sizeof(int) * (size_t)n_experts, 256);
+  L.cursor = off;    off = align_up(off + sizeof(int) * (size_t)n_experts, 256);
+  L.offsets = off;   off = align_up(off + sizeof(int) * ((size_t)n_experts + 1), 256);
+  L.task_base = off; off = align_up(off + sizeof(int) * ((size_t)n_experts + 1), 256);
+  L.n_tasks = off;   off = align_up(off + sizeof(int), 256);
+  L.order = off;     off = align_up(off + sizeof(int) * (size_t)(n_entries > 0 ? n_entries : 1), 256);
+  L.tasks = off;     off = align_up(off + sizeof(GemvTask) * (size_t)mt, 256);
+  L.total = off;
+  return L;
+}
+
+__global__ void gather_hist_kernel(const uint32_t* __restrict__ rhs, long long n, int n_experts, int* counts) {
+  const long long b = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (b < n) {
+    const uint32_t e = rhs[b];
+    if (e < (uint32_t)n_experts) atomicAdd(&counts[e], 1);
+  }
+}
+
+// One CTA: exclusive scans of counts (entry offsets) and of ceil(count*M/16)
+// (task offsets). n_experts is small (hundreds), a serial chunked scan is enough.
+__global__ void gather_scan_kernel(const int* __restrict__ counts, int n_experts, int M, int* offsets, int* task_base,
+                                   int* n_tasks) {
+  __shared__ int s_cnt[1024], s_tsk[1024];
+  __shared__ int carry_c, carry_t;
+  if (threadIdx.x == 0) carry_c = carry_t = 0;
+  __syncthreads();
+  for (int base = 0; base < n_experts; base += 1024) {
+    const int e = base + threadIdx.x;
+    const int c = e < n_experts ? counts[e] : 0;
+    const int tk = (int)(((long long)c * M + 15) / 16);
+    s_cnt[threadIdx.x] = c;
+    s_tsk[threadIdx.x] = tk;
+    __syncthreads();
+    // Hillis-Steele inclusive scan over 1024 slots
+    for (int d = 1; d < 1024; d <<= 1) {
+      int vc = 0, vt = 0;
+      if ((int)threadIdx.x >= d) {
+        vc = s_cnt[threadIdx.x - d];
+        vt = s_tsk[threadIdx.x - d];
+      }
+      __syncthreads();
+      s_cnt[threadIdx.x] += vc;
+      s_tsk[threadIdx.x] += vt;
+      __syncthreads();
+    }
+    if (e < n_experts) {
+      offsets[e] = carry_c + s_cnt[threadIdx.x] - c;
+      task_base[e] = carry_t + s_tsk[threadIdx.x] - tk;
+    }
+    __syncthreads();
+    if (threadIdx.x == 1023) {
+      carry_c += s_cnt[1023];
+      carry_t += s_tsk[1023];
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    offsets[n_experts] = carry_c;
+    task_base[n_experts] = carry_t;
+    *n_tasks = carry_t;
+  }
+}
+
+__global__ void gather_scatter_kernel(const uint32_t* __restrict__ rhs, long long n, int n_experts,
+                                      const int* __restrict__ offsets, int* cursor, int* order) {
+  const long long b = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (b < n) {
+    const uint32_t e = rhs[b];
+    if (e < (uint32_t)n_experts) order[offsets[e] + atomicAdd(&cursor[e], 1)] = (int)b;
+  }
+}
+
+// grid.x = expert. The scatter's atomics leave each expert's entries in an
+// arbitrary order; that is harmless because an output row depends only on its
+// own activation row and the weights, never on which rows share its task.
+__global__ void gather_tasks_kernel(const uint8_t* w, long long expert_stride, int M, const uint32_t* __restrict__ lhs,
+                                    const int* __restrict__ offsets, const int* __restrict__ task_base,
+                                    const int* __restrict__ order, GemvTask* tasks) {
+  const int e = blockIdx.x;
+  const int o0 = offsets[e], c = offsets[e + 1] - o0;
+  if (c == 0) return;
+  const long long rows = (long long)c * M;
+  const int nt = (int)((rows + 15) / 16);
+  const int tb = task_base[e];
+  for (int idx = threadIdx.x; idx < nt * 16; idx += blockDim.x) {
+    const int tk = idx >> 4, slot = idx & 15;
+    GemvTask& t = tasks[tb + tk];
+    const long long r = (long long)tk * 16 + slot;
+    if (slot == 0) {
+      t.w = w + (long long)e * expert_stride;
+      t.m = (int)min(16LL, rows - (long long)tk * 16);
+      t.pad = 0;
+    }
+    if (r < rows) {
+      const int entry = order[o0 + (int)(r / M)];
+      const int i = (int)(r % M);
+      t.xrow[slot] = (int)lhs[entry] * M + i;
+      t.yrow[slot] = entry * M + i;
+    } else {
+      t.xrow[slot] = 0;
+      t.yrow[slot] = 0;
+    }
+  }
+}
+
+cudaError_t launch_gather(int codec, int x_dtype, const void* x, int M, int K, const uint8_t* w, int n_experts,
+                          long long expert_stride, long long row_bytes, int N, const uint32_t* lhs,
+                          const uint32_t* rhs, long long n_entries, void* y, void* workspace, cudaStream_t st) {
+  if (n_entries <= 0 || M <= 0) return cudaSuccess;
+  const GatherLayout L = gather_layout(n_entries, M, n_experts);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  int* counts = reinterpret_cast<int*>(ws + L.counts);
+  int* cursor = reinterpret_cast<int*>(ws + L.cursor);
+  int* offsets = reinterpret_cast<int*>(ws + L.offsets);
+  int* task_base = reinterpret_cast<int*>(ws + L.task_base);
+  int* n_tasks = reinterpret_cast<int*>(ws + L.n_tasks);
+  int* order = reinterpret_cast<int*>(ws + L.order);
+  GemvTask* tasks = reinterpret_cast<GemvTask*>(ws + L.tasks);
+
+  cudaError_t err = cudaMemsetAsync(ws + L.counts, 0, L.offsets - L.counts, st);  // counts + cursor
+  if (err != cudaSuccess) return err;
+  const int th = 256;
+  const unsigned nb = (unsigned)((n_entries + th - 1) / th);
+  gather_hist_kernel<<<nb, th, 0, st>>>(rhs, n_entries, n_experts, counts);
+  gather_scan_kernel<<<1, 1024, 0, st>>>(counts, n_experts, M, offsets, task_base, n_tasks);
+  gather_scatter_kernel<<<nb, th, 0, st>>>(rhs, n_entries, n_experts, offsets, cursor, order);
+  gather_tasks_kernel<<<n_experts, 256, 0, st>>>(w, expert_stride, M, lhs, offsets, task_base, order, tasks);
+  if ((err = cudaGetLastError()) != cudaSuccess) return err;
+
+  GemvArgs a{};
+  a.x = x;
+  a.x_row_stride = K;
+  a.y = y;
+  a.y_row_stride = N;
+  a.w = w;
+  a.w_align16 = ((reinterpret_cast<uintptr_t>(w) & 15) == 0 && (expert_stride & 15) == 0) ? 1 : 0;
+  a.row_bytes = row_bytes;
+  a.N = N;
+  a.K = K;
+  a.M = 0;
+  a.n_tasks_dev = n_tasks;
+  // grid.y is capped at 65535: cover the task list in slices
+  for (long long t0 = 0; t0 < L.max_tasks; t0 += 65535) {
+    a.tasks = tasks + t0;
+    a.n_tasks = (int)((L.max_tasks - t0) < 65535 ? (L.max_tasks - t0) : 65535);
+    a.task_offset = (int)t0;
+    if ((err = launch_gemv(codec, x_dtype, a, st)) != cudaSuccess) return err;
+  }
+  return cudaSuccess;
+}
+
+}  // namespace kq

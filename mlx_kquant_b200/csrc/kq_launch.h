@@ -1,0 +1,55 @@
+// Internal launch interface between the C-ABI layer (kq_abi.cu) and the kernel
+// translation units. Not installed; the public surface is include/kquant_b200.h.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace kq {
+
+// dequantize n_blocks blocks of `codec` wire bytes to `dtype` (0 f32, 1 f16, 2 bf16).
+cudaError_t launch_dequantize(int codec, const uint8_t* w, long long n_blocks, int dtype, void* out,
+                              cudaStream_t st);
+
+// One group of at most 16 activation rows that all multiply the same weight
+// matrix: the unit of work of the skinny-M kernel. Built on the device by the
+// gather path (one per expert and 16-row slice); the dense path needs none.
+struct GemvTask {
+  const uint8_t* w;   // wire bytes of the [N, K] matrix
+  int m;              // valid rows, 1..16
+  int pad;
+  int xrow[16];       // row index into x (units of x_row_stride)
+  int yrow[16];       // row index into y (units of y_row_stride)
+};
+
+struct GemvArgs {
+  const void* x;
+  long long x_row_stride;   // elements between consecutive x rows
+  void* y;
+  long long y_row_stride;   // elements between consecutive y rows
+  const uint8_t* w;         // used when tasks == nullptr
+  int w_align16;            // every weight matrix (w, or each task's w) starts 16-byte aligned
+  long long row_bytes;      // wire bytes per weight row
+  int N, K;
+  int M;                    // total rows when tasks == nullptr (split in 16-row slices)
+  const GemvTask* tasks;    // device array or nullptr
+  const int* n_tasks_dev;   // device count of valid tasks (may be < grid.y), or nullptr
+  int n_tasks;              // grid.y when tasks != nullptr
+  int task_offset;          // index of tasks[0] in the whole task list (for n_tasks_dev)
+};
+
+// y = x . dequant(w)^T for skinny row groups. x_dtype: 0 f32 (rounded to bf16
+// on load, output bf16), 1 f16, 2 bf16.
+cudaError_t launch_gemv(int codec, int x_dtype, const GemvArgs& a, cudaStream_t st);
+
+// gather_qmm: device-side grouping by expert + the skinny-M kernel per group.
+struct GatherLayout {
+  size_t counts, offsets, task_base, cursor, n_tasks, order, tasks, total;
+  long long max_tasks;
+};
+GatherLayout gather_layout(long long n_entries, int M, int n_experts);
+cudaError_t launch_gather(int codec, int x_dtype, const void* x, int M, int K, const uint8_t* w, int n_experts,
+                          long long expert_stride, long long row_bytes, int N, const uint32_t* lhs,
+                          const uint32_t* rhs, long long n_entries, void* y, void* workspace, cudaStream_t st);
+
+}  // namespace kq

@@ -1,0 +1,203 @@
+"""The ``kq.*`` ops over torch tensors, mirroring the reference's Python surface.
+
+Names, argument order, defaults and the keyword-only ``stream`` follow the
+reference's binding (bindings.cpp:94-141, 1349-1381, 1439-1461); shape and dtype
+rules follow its op layer (src/kquant_ops.cpp). Tensors are ``torch`` CUDA
+tensors instead of MLX arrays; CPU tensors are accepted for activations and
+indices and are copied to the weights' device and back (that is the end-to-end
+path the benchmark times). All arithmetic happens in the CUDA library behind
+``include/kquant_b200.h``.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import KQ_BF16, KQ_F16, KQ_F32, check
+
+_DT = {torch.float32: KQ_F32, torch.float16: KQ_F16, torch.bfloat16: KQ_BF16}
+
+
+def codecs() -> list[str]:
+    """Names of the supported codecs (bindings.cpp:40-43)."""
+    import ctypes as C
+
+    L = _lib.lib()
+    out = []
+    name = C.c_char_p()
+    for i in range(L.kq_codec_count()):
+        L.kq_codec_info(i, C.byref(name), None, None, None, None)
+        out.append(name.value.decode())
+    return out
+
+
+def codec_geometry(kquant_type: str) -> tuple[int, int, int, bool]:
+    """(weights_per_block, bytes_per_block, bits, requires_imatrix) or ValueError."""
+    import ctypes as C
+
+    L = _lib.lib()
+    i = L.kq_codec_find(kquant_type.encode())
+    if i < 0:
+        raise ValueError(f"[mlx_kquant] Unknown kquant_type: '{kquant_type}'.")
+    v = [C.c_int() for _ in range(4)]
+    L.kq_codec_info(i, None, *[C.byref(t) for t in v])
+    return v[0].value, v[1].value, v[2].value, bool(v[3].value)
+
+
+def _stream_ptr(stream, device) -> int:
+    if stream is None:
+        return torch.cuda.current_stream(device).cuda_stream
+    return stream.cuda_stream
+
+
+def _require_cuda(w: torch.Tensor, op: str) -> None:
+    if not w.is_cuda:
+        raise RuntimeError(f"[mlx_kquant.{op}] w must live on a CUDA device; there is no CPU path.")
+
+
+def dequantize(w, scales, kquant_type, dtype=None, *, stream=None):
+    """Wire bytes -> float tensor; default dtype float16 (src/kquant_ops.cpp:55-110)."""
+    if w.dtype != torch.uint8:
+        raise ValueError("[mlx_kquant.dequantize] w must be uint8 (raw GGUF wire bytes).")
+    if w.dim() < 1:
+        raise ValueError("[mlx_kquant.dequantize] w must have at least 1 dimension.")
+    out_dtype = dtype or torch.float16
+    if out_dtype not in _DT:
+        raise ValueError("[mlx_kquant.dequantize] Only real floating output dtypes are supported.")
+    wpb, bpb, _, _ = codec_geometry(kquant_type)
+    if w.shape[-1] % bpb != 0:
+        raise ValueError(
+            f"[mlx_kquant.dequantize] Last dim ({w.shape[-1]}) must be a multiple of bytes_per_block ({bpb}) "
+            f"for codec '{kquant_type}'.")
+    _require_cuda(w, "dequantize")
+    w_c = w.contiguous()
+    out = torch.empty(w.shape[:-1] + (w.shape[-1] // bpb * wpb,), dtype=out_dtype, device=w.device)
+    with torch.cuda.device(w.device):
+        check(_lib.lib().kq_dequantize(w_c.data_ptr(), w_c.numel(), kquant_type.encode(), _DT[out_dtype],
+                                       out.data_ptr(), _stream_ptr(stream, w.device)))
+    return out
+
+
+def _prep_x(x: torch.Tensor, device, op: str):
+    """Returns (x on device with a dense last dim, was_on_cpu)."""
+    if x.dtype not in _DT:
+        raise ValueError(f"[mlx_kquant.{op}] Only real floating x dtypes are supported.")
+    on_cpu = not x.is_cuda
+    if on_cpu:
+        x = x.to(device, non_blocking=True)
+    return x, on_cpu
+
+
+def _expanded_inner(w, kquant_type, op):
+    wpb, bpb, _, _ = codec_geometry(kquant_type)
+    if w.shape[-1] % bpb != 0:
+        raise ValueError(
+            f"[mlx_kquant.{op}] KQuant weight last dim ({w.shape[-1]} bytes) is not a whole number of "
+            f"{bpb}-byte {kquant_type} blocks.")
+    return w.shape[-1] // bpb * wpb
+
+
+def quantized_matmul(x, w, scales, kquant_type, transpose=True, *, stream=None):
+    """``x @ dequant(w).T`` (src/kquant_ops.cpp:112-183). Output dtype = x dtype,
+    float32 promoted to bfloat16."""
+    op = "quantized_matmul"
+    if w.dtype != torch.uint8:
+        raise ValueError(f"[mlx_kquant.{op}] w must be uint8 (raw GGUF wire bytes).")
+    codec_geometry(kquant_type)
+    if x.dim() > 2 and w.dim() > 2:
+        raise ValueError(f"[mlx_kquant.{op}] batched (>2D) weights are not supported; use gather_qmm for "
+                         "mixture-of-experts.")
+    wpr = _expanded_inner(w, kquant_type, op)
+    inner = wpr if transpose else w.shape[-2]
+    outer = w.shape[-2] if transpose else wpr
+    if inner != x.shape[-1]:
+        raise ValueError(
+            f"[mlx_kquant.{op}] x last dim ({x.shape[-1]}) does not match the expanded quantized matrix inner dim "
+            f"({inner}) for codec '{kquant_type}' with transpose={'true' if transpose else 'false'}.")
+    _require_cuda(w, op)
+    x, on_cpu = _prep_x(x, w.device, op)
+    out_dtype = torch.bfloat16 if x.dtype == torch.float32 else x.dtype
+    w2 = w if w.dim() == 2 else w.reshape(-1, w.shape[-2], w.shape[-1])[0]
+    w2 = w2.contiguous()
+    K = x.shape[-1]
+    x2 = x.reshape(-1, K) if x.dim() != 1 else x.reshape(1, K)
+    if x2.stride(-1) != 1 or (x2.stride(0) * x2.element_size()) % 16 != 0 or x2.data_ptr() % 16 != 0:
+        x2 = x2.contiguous()
+    rows = x2.shape[0]
+    y = torch.empty((rows, outer), dtype=out_dtype, device=w.device)
+    with torch.cuda.device(w.device):
+        check(_lib.lib().kq_quantized_matmul(x2.data_ptr(), _DT[x.dtype], rows, K, x2.stride(0), w2.data_ptr(),
+                                             w2.shape[-1], outer, kquant_type.encode(), int(bool(transpose)),
+                                             y.data_ptr(), y.stride(0), _stream_ptr(stream, w.device)))
+    y = y.reshape(x.shape[:-1] + (outer,))
+    return y.cpu() if on_cpu else y
+
+
+def gather_qmm(x, w, scales, kquant_type, lhs_indices=None, rhs_indices=None, transpose=True,
+               sorted_indices=False, *, stream=None):
+    """Mixture-of-experts matmul (src/kquant_ops.cpp:293-420): for each index entry,
+    ``x[lhs] @ dequant(w[rhs]).T``; output shape ``lhs_indices.shape + [M, N]``."""
+    op = "gather_qmm"
+    if lhs_indices is None and rhs_indices is None:
+        return quantized_matmul(x, w, scales, kquant_type, transpose, stream=stream)
+    if w.dtype != torch.uint8:
+        raise ValueError(f"[mlx_kquant.{op}] w must be uint8 (raw GGUF wire bytes).")
+    codec_geometry(kquant_type)
+    if x.dim() < 2:
+        raise ValueError(f"[mlx_kquant.{op}] x must have at least two dimensions but got shape {tuple(x.shape)}.")
+    wpr = _expanded_inner(w, kquant_type, op)
+    inner = wpr if transpose else w.shape[-2]
+    outer = w.shape[-2] if transpose else wpr
+    if inner != x.shape[-1]:
+        raise ValueError(
+            f"[mlx_kquant.{op}] x last dim ({x.shape[-1]}) does not match the expanded quantized matrix inner dim "
+            f"({inner}) for codec '{kquant_type}' with transpose={'true' if transpose else 'false'}.")
+    _require_cuda(w, op)
+    x, on_cpu = _prep_x(x, w.device, op)
+    out_dtype = torch.bfloat16 if x.dtype == torch.float32 else x.dtype
+    dev = w.device
+
+    def default_idx(t):
+        shape = t.shape[:-2]
+        total = 1
+        for d in shape:
+            total *= d
+        return torch.arange(total, dtype=torch.int64, device=dev).reshape(shape)
+
+    lhs = default_idx(x) if lhs_indices is None else lhs_indices.to(dev)
+    rhs = default_idx(w) if rhs_indices is None else rhs_indices.to(dev)
+    lhs, rhs = torch.broadcast_tensors(lhs, rhs)
+    idx_shape = tuple(lhs.shape)
+    # uint32 on the wire; int32 storage holds the same bits for indices < 2^31
+    lhs32 = lhs.reshape(-1).to(torch.int32).contiguous()
+    rhs32 = rhs.reshape(-1).to(torch.int32).contiguous()
+    n_entries = lhs32.numel()
+
+    M, K = x.shape[-2], x.shape[-1]
+    x3 = x.reshape(-1, M, K).contiguous()
+    if w.dim() == 2:
+        w3 = w.unsqueeze(0)
+    elif w.dim() == 3:
+        w3 = w
+    else:
+        w3 = w.reshape(-1, w.shape[-2], w.shape[-1])
+    # matrix-contiguity is enough: a strided expert dimension is walked in 64-bit
+    if w3.stride(2) != 1 or w3.stride(1) != w3.shape[2]:
+        w3 = w3.contiguous()
+    E = w3.shape[0]
+    y = torch.empty((n_entries, M, outer), dtype=out_dtype, device=dev)
+    L = _lib.lib()
+    ws_bytes = L.kq_gather_qmm_workspace_bytes(n_entries, M, E)
+    ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+    right_sorted = bool(sorted_indices) and lhs_indices is None
+    if stream is not None:
+        for t in (ws, y, x3, lhs32, rhs32):
+            t.record_stream(stream)
+    with torch.cuda.device(dev):
+        check(L.kq_gather_qmm(x3.data_ptr(), _DT[x.dtype], x3.shape[0], M, K, w3.data_ptr(), E,
+                              w3.stride(0) if E > 1 else w3.shape[1] * w3.shape[2], w3.shape[2], outer,
+                              kquant_type.encode(), lhs32.data_ptr(), rhs32.data_ptr(), n_entries,
+                              int(bool(transpose)), int(right_sorted), y.data_ptr(), ws.data_ptr(), ws.numel(),
+                              _stream_ptr(stream, dev)))
+    y = y.reshape(idx_shape + (M, outer))
+    return y.cpu() if on_cpu else y

@@ -1,0 +1,116 @@
+"""gather_qmm on the GPU against the CPU restatement of the reference's
+KQuantGatherQMM::eval_cpu (src/kquant_gather.cpp:496-731)."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+import mlx_kquant_b200 as kq
+from conftest import max_rel_to_peak, rel_fro
+from gpu_util import mint_wire, x_to_torch, y_to_f32
+from oracle.kq_oracle import to_f32
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+
+
+def make_experts(codec, E, N, K, seed):
+    rng = np.random.default_rng(seed)
+    return np.stack([mint_wire(codec, rng.normal(0, 0.02, (N, K)).astype(np.float32)) for _ in range(E)])
+
+
+def fp64_ref(oracle, store, dt, wire, codec, lhs, rhs):
+    xs = to_f32(store, dt).astype(np.float64)
+    Wd = oracle.dequantize(wire, codec, "f32").astype(np.float64)
+    return np.stack([xs[l] @ Wd[r].T for l, r in zip(lhs.ravel(), rhs.ravel())])
+
+
+@pytest.mark.parametrize("codec", ["q4_k", "q6_k", "q8_0", "iq4_xs", "iq2_xxs", "q2_k", "q3_k", "q5_k", "q4_0", "iq4_nl"])
+@pytest.mark.parametrize("M", [1, 3])
+def test_gather_sweep(oracle, codec, M):
+    # B = 8 entries, lhs = arange and reversed-with-repeat (tests/test_cpu_decode.py:186-224)
+    E, N, K, B = 4, 64, 512, 8
+    wire = make_experts(codec, E, N, K, seed=21)
+    x, store = x_to_torch(np.random.default_rng(22).normal(0, 1, (B, M, K)).astype(np.float32), "f16")
+    wd = torch.from_numpy(wire).cuda()
+    rhs = np.array([0, 3, 1, 1, 2, 0, 3, 3], np.uint32)
+    for lhs in (np.arange(B, dtype=np.uint32), np.array([7, 6, 5, 4, 3, 3, 1, 0], np.uint32)):
+        y = kq.gather_qmm(x, wd, None, codec, lhs_indices=torch.from_numpy(lhs.astype(np.int64)),
+                          rhs_indices=torch.from_numpy(rhs.astype(np.int64)))
+        assert tuple(y.shape) == (B, M, N) and y.dtype == torch.float16
+        ref = fp64_ref(oracle, store, "f16", wire, codec, lhs, rhs)
+        assert rel_fro(y_to_f32(y), ref) <= TOL and max_rel_to_peak(y_to_f32(y), ref) <= TOL
+        cpu = oracle.gather_qmm(store, wire, lhs, rhs, codec, "f16").astype(np.float32)
+        assert rel_fro(y_to_f32(y), cpu) <= TOL
+
+
+def test_gather_defaults_and_index_shapes(oracle):
+    # rhs only (the MoE call): lhs defaults to arange over x's batch dims; 2-D index tensors keep their shape
+    codec, E, N, K = "q4_k", 8, 96, 512
+    wire = make_experts(codec, E, N, K, seed=31)
+    wd = torch.from_numpy(wire).cuda()
+    x, store = x_to_torch(np.random.default_rng(32).normal(0, 1, (6, 1, K)).astype(np.float32), "bf16")
+    rhs = np.array([5, 5, 0, 7, 2, 5], np.uint32)
+    y = kq.gather_qmm(x, wd, None, codec, rhs_indices=torch.from_numpy(rhs.astype(np.int64)).cuda())
+    assert tuple(y.shape) == (6, 1, N) and y.dtype == torch.bfloat16
+    ref = fp64_ref(oracle, store, "bf16", wire, codec, np.arange(6), rhs)
+    assert rel_fro(y_to_f32(y), ref) <= TOL
+    # broadcast: one token against top-k experts, indices shaped [1, 4]
+    rhs2 = torch.tensor([[1, 3, 4, 6]])
+    lhs2 = torch.zeros((1, 1), dtype=torch.int64)
+    y2 = kq.gather_qmm(x, wd, None, codec, lhs_indices=lhs2, rhs_indices=rhs2)
+    assert tuple(y2.shape) == (1, 4, 1, N)
+    ref2 = fp64_ref(oracle, store, "bf16", wire, codec, np.zeros(4, int), np.array([1, 3, 4, 6]))
+    assert rel_fro(y_to_f32(y2).reshape(4, 1, N), ref2) <= TOL
+    # no indices at all is a plain matmul (src/kquant_ops.cpp:303-312)
+    y3 = kq.gather_qmm(x[:, 0], wd[0], None, codec)
+    assert torch.equal(y3, kq.quantized_matmul(x[:, 0], wd[0], None, codec))
+
+
+def test_duplicates_match_singletons_bitwise(oracle):
+    # repeated (lhs, rhs) pairs give bit-identical rows (tests/test_gather.py:253-321)
+    codec, E, N, K = "q4_k", 3, 64, 512
+    wire = make_experts(codec, E, N, K, seed=41)
+    wd = torch.from_numpy(wire).cuda()
+    x, _ = x_to_torch(np.random.default_rng(42).normal(0, 1, (4, 1, K)).astype(np.float32), "f16")
+    lhs = torch.tensor([2, 2, 2, 0, 2])
+    rhs = torch.tensor([1, 1, 1, 1, 1])
+    y = kq.gather_qmm(x, wd, None, codec, lhs_indices=lhs, rhs_indices=rhs)
+    single = kq.gather_qmm(x, wd, None, codec, lhs_indices=torch.tensor([2]), rhs_indices=torch.tensor([1]))
+    for i in (0, 1, 2, 4):
+        assert torch.equal(y[i], single[0])
+
+
+def test_sorted_large_group_and_strided_experts(oracle):
+    # 700 rows sorted by expert (prefill shape, groups far above 16 rows) through a strided expert view:
+    # the gate half of a fused [E, 2N, bytes] gate_up tensor (src/kquant_ops.cpp:24-49)
+    codec, E, N, K, B = "q4_k", 4, 48, 512, 700
+    fused = make_experts(codec, E, 2 * N, K, seed=51)
+    fd = torch.from_numpy(fused).cuda()
+    gate = fd[:, :N, :]
+    assert not gate.is_contiguous()
+    x, store = x_to_torch(np.random.default_rng(52).normal(0, 1, (B, 1, K)).astype(np.float32), "bf16")
+    rhs = np.sort(np.random.default_rng(53).integers(0, E, B)).astype(np.uint32)
+    y = kq.gather_qmm(x, gate, None, codec, rhs_indices=torch.from_numpy(rhs.astype(np.int64)), sorted_indices=True)
+    ref = fp64_ref(oracle, store, "bf16", fused[:, :N, :], codec, np.arange(B), rhs)
+    assert rel_fro(y_to_f32(y), ref) <= TOL and max_rel_to_peak(y_to_f32(y), ref) <= TOL
+    # sorted and shuffled orders agree row for row
+    perm = np.random.default_rng(54).permutation(B)
+    y_sh = kq.gather_qmm(x, gate, None, codec, lhs_indices=torch.from_numpy(perm), rhs_indices=torch.from_numpy(rhs[perm].astype(np.int64)))
+    assert torch.equal(y_sh, y[torch.from_numpy(perm).cuda()])
+
+
+def test_many_rows_regression():
+    # more than 32767 routed rows in one call (tests/test_gather.py:197-250), K = 256
+    codec, E, N, K, B = "q8_0", 2, 16, 256, 33000
+    wire = make_experts(codec, E, N, K, seed=61)
+    wd = torch.from_numpy(wire).cuda()
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(B, 1, K, device="cuda", generator=g).half()
+    rhs = (torch.arange(B, device="cuda") * 2 // B).to(torch.int64)
+    y = kq.gather_qmm(x, wd, None, codec, rhs_indices=rhs, sorted_indices=True)
+    half = B // 2
+    want0 = kq.quantized_matmul(x[:half, 0], wd[0], None, codec)
+    want1 = kq.quantized_matmul(x[half:, 0], wd[1], None, codec)
+    assert torch.equal(y[:half, 0], want0) and torch.equal(y[half:, 0], want1)
