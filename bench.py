@@ -1,0 +1,345 @@
+#!/usr/bin/env python3
+"""Benchmark of the quantized-weight hot path.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+Headline workload (config.workload = "c1_q4k_decode_gemv"): the decode-shape
+Q4_K quantized_matmul of the reference's first benchmark cell - W [4096, 4096]
+in q4_k wire bytes, activations fp16 [M, 4096] (M = 1 unless --m is given). One
+STEP is one pass of that matmul over a stack of `layers` DISTINCT weight
+matrices (64 x 9.4 MB = 604 MB, several times the 126 MB L2), so every launch
+streams its weights cold from HBM - the way the reference measures
+("working set streamed far past the SLC", src/kquant_matmul.cpp:1436-1437).
+metric = weight wire bytes processed per second (GB/s), the reference's own
+definition (benchmarks/bench_qmm_bm128_ab.py:18-19).
+
+value   device-resident: inputs already in HBM, the step is one CUDA-graph
+        replay of the `layers` launches; CUDA events on the launching stream.
+e2e     the same step through the public op with HOST buffers: pinned-host x
+        -> device copy, the launches, device -> pinned-host copy of the outputs,
+        all inside the timed region.
+N > 1   weak scaling: every rank holds its own [4096, 4096] column shard (rows
+        r*4096 .. (r+1)*4096 of a [N*4096, 4096] matrix) per layer and the
+        [layers, M, 4096] output shards are all-gathered over NCCL each step.
+--impl reference   times the reference's own CPU implementation of the path
+        (oracle/_ref/libkqref.so = its kquant_qmm_cpu compiled in place; the
+        oracle's C port if that library is absent) on a bounded sample of the
+        same workload with all host threads.
+
+Weights are synthetic valid wire bytes (mlx_kquant_b200/synth.py); activations
+are seeded N(0, 1).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+N_ROWS = 4096
+K_COLS = 4096
+CODEC = "q4_k"
+ROW_BYTES = K_COLS // 256 * 144
+MATRIX_BYTES = N_ROWS * ROW_BYTES  # 9 437 184
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--layers", type=int, default=64, help="distinct weight matrices per step")
+    ap.add_argument("--m", type=int, default=1, help="activation rows (decode batch), <= 16")
+    ap.add_argument("--cpu-sample", type=int, default=16, help="matrices in the CPU-baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows = []
+        self.proc = None
+        self.index = index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                smax.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def measured_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+def host_wire(layers: int, seed: int = 0):
+    """Synthetic valid q4_k wire bytes on the host (numpy), same recipe as synth.random_wire."""
+    import numpy as np
+
+    rng = np.random.default_rng(seed)
+    w = rng.integers(0, 256, (layers, N_ROWS, K_COLS // 256, 144), dtype=np.uint8)
+    d = rng.uniform(0.001, 0.02, (layers, N_ROWS, K_COLS // 256)).astype(np.float16).view(np.uint16)
+    for off in (0, 2):
+        w[..., off] = (d & 0xFF).astype(np.uint8)
+        w[..., off + 1] = (d >> 8).astype(np.uint8)
+    return w.reshape(layers, N_ROWS, ROW_BYTES)
+
+
+def cpu_arm(m: int, sample: int, repeats: int):
+    """The reference's CPU path on `sample` matrices; returns (GB/s, kind, cores, seconds per pass)."""
+    import numpy as np
+
+    from oracle import kq_oracle
+
+    wire = host_wire(sample, seed=1)
+    x = np.random.default_rng(2001).normal(0, 1, (m, K_COLS)).astype(np.float16)
+    if kq_oracle.Ref.available():
+        impl, kind = kq_oracle.Ref(), "reference"
+    else:
+        impl, kind = kq_oracle.Oracle(), "port"
+    cores = impl.threads()
+    impl.qmm(x, wire[0], CODEC, "f16")  # warm the pool
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        for i in range(sample):
+            impl.qmm(x, wire[i], CODEC, "f16")
+        best = min(best, time.perf_counter() - t0)
+    return sample * MATRIX_BYTES / best / 1e9, kind, cores, best
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample = args.cpu_sample
+    # each "step" is one pass over the bounded sample
+    t_all = []
+    gbs, kind, cores, _ = cpu_arm(args.m, sample, max(1, args.warmup))
+    import numpy as np
+
+    from oracle import kq_oracle
+
+    impl = kq_oracle.Ref() if kq_oracle.Ref.available() else kq_oracle.Oracle()
+    wire = host_wire(sample, seed=1)
+    x = np.random.default_rng(2001).normal(0, 1, (args.m, K_COLS)).astype(np.float16)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        for i in range(sample):
+            impl.qmm(x, wire[i], CODEC, "f16")
+    total = time.perf_counter() - t0
+    value = args.steps * sample * MATRIX_BYTES / total / 1e9
+    line = {
+        "impl": "reference", "metric": "q4k_gemv_weight_GBps", "value": value, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "c1_q4k_decode_gemv", "codec": CODEC, "N": N_ROWS, "K": K_COLS, "M": args.m,
+                   "layers": sample},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": kind,
+                         "sample": f"{sample} of the step's matrices per step, x86_64 scalar/threaded eval_cpu path"},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+
+    import mlx_kquant_b200 as kq
+    from mlx_kquant_b200.synth import random_wire
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    layers, M = args.layers, args.m
+    # this rank's column shard of every layer: rows [rank*4096, (rank+1)*4096) of a [world*4096, 4096] matrix
+    W = random_wire(CODEC, N_ROWS, K_COLS, seed=1000 + rank, device=dev, lead=(layers,))
+    g = torch.Generator(device="cpu").manual_seed(2000 + M)
+    x_host = torch.randn(M, K_COLS, generator=g).to(torch.float16).pin_memory()
+    x_dev = x_host.to(dev)
+    y_dev = torch.empty(layers, M, N_ROWS, dtype=torch.float16, device=dev)
+    y_all = torch.empty(world, layers, M, N_ROWS, dtype=torch.float16, device=dev) if world > 1 else None
+    y_host = torch.empty(layers, M, N_ROWS, dtype=torch.float16).pin_memory()
+
+    from mlx_kquant_b200 import _lib
+    L = _lib.lib()
+    stream = torch.cuda.Stream(dev)
+
+    def launch_all(s):
+        for i in range(layers):
+            rc = L.kq_quantized_matmul(x_dev.data_ptr(), _lib.KQ_F16, M, K_COLS, K_COLS, W[i].data_ptr(), ROW_BYTES,
+                                       N_ROWS, CODEC.encode(), 1, y_dev[i].data_ptr(), N_ROWS, s.cuda_stream)
+            _lib.check(rc)
+
+    # ---- correctness guard: the captured path equals the public op
+    with torch.cuda.stream(stream):
+        launch_all(stream)
+        ref0 = kq.quantized_matmul(x_dev, W[0], None, CODEC)
+    stream.synchronize()
+    assert torch.equal(ref0, y_dev[0]), "C-ABI launch and public op disagree"
+
+    # ---- device-resident arm: one CUDA graph of `layers` launches
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            launch_all(stream)
+    # ---- end-to-end arm: H2D of x, the launches, D2H of y, captured as one graph of the public path
+    graph_e2e = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph_e2e, stream=stream):
+            x_dev.copy_(x_host, non_blocking=True)
+            launch_all(stream)
+            y_host.copy_(y_dev, non_blocking=True)
+
+    def step_device():
+        graph.replay()
+        if world > 1:
+            dist.all_gather_into_tensor(y_all, y_dev)
+
+    def step_e2e():
+        graph_e2e.replay()
+        if world > 1:
+            dist.all_gather_into_tensor(y_all, y_dev)
+
+    def timed(fn, steps, warmup):
+        with torch.cuda.stream(stream):
+            for _ in range(warmup):
+                fn()
+            stream.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(steps):
+                fn()
+            e1.record(stream)
+            stream.synchronize()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms_dev = timed(step_device, args.steps, max(3, args.warmup))
+    ms_e2e = timed(step_e2e, args.steps, max(3, args.warmup))
+    clocks = sampler.stop() if rank == 0 else None
+
+    step_bytes = layers * MATRIX_BYTES * world
+    value = step_bytes / (ms_dev / args.steps * 1e-3) / 1e9
+    e2e = step_bytes / (ms_e2e / args.steps * 1e-3) / 1e9
+    # dominant kernel: average launch duration over the timed region of the device arm (rank-local bytes)
+    launch_s = ms_dev * 1e-3 / (args.steps * layers)
+    peak, peak_kind = measured_peak()
+    achieved = MATRIX_BYTES / launch_s / 1e9
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        try:
+            gbs, kind, cores, secs = cpu_arm(M, args.cpu_sample, 5)
+            cpu = {"value": gbs, "unit": "GB/s", "cores": cores, "kind": kind,
+                   "sample": f"{args.cpu_sample} of the {layers} matrices, best of 5 passes ({secs * 1e3:.1f} ms per pass)"}
+        except Exception as e:  # the checker is optional for timing; say why it is missing
+            cpu = {"value": None, "unit": "GB/s", "cores": 0, "kind": "port", "sample": f"unavailable: {e}"}
+
+    if rank == 0:
+        line = {
+            "metric": "q4k_gemv_weight_GBps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": ms_dev / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "c1_q4k_decode_gemv", "codec": CODEC, "N": N_ROWS, "K": K_COLS, "M": M,
+                       "layers": layers, "x_dtype": "f16", "accumulate": "f32",
+                       "cold_cache": f"{layers} distinct weight matrices per step = {layers * MATRIX_BYTES / 1e6:.0f} MB > 126 MB L2",
+                       "parallelism": "single GPU" if world == 1 else f"column shard x{world} + NCCL all-gather of outputs"},
+            "e2e": {"value": e2e, "unit": "GB/s", "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
+            "gpu_launches": args.steps * layers,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_kind": peak_kind, "traffic": None, "kernel": "gemv_kernel<q4_k, f16, NT=1, FAST>",
+                         "algorithmic_bytes_per_launch": MATRIX_BYTES},
+            "cpu_baseline": cpu,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()

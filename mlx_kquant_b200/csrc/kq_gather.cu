@@ -169,6 +169,7 @@ cudaError_t launch_gather(int codec, int x_dtype, const void* x, int M, int K, c
   a.K = K;
   a.M = 0;
   a.n_tasks_dev = n_tasks;
+  a.max_m = (int)(n_entries * M < 16 ? n_entries * M : 16);
   // grid.y is capped at 65535: cover the task list in slices
   for (long long t0 = 0; t0 < L.max_tasks; t0 += 65535) {
     a.tasks = tasks + t0;

@@ -1,38 +1,57 @@
-// Skinny-M quantized matmul (decode regime, M <= 16 rows per weight matrix):
+// Skinny-M quantized matmul (decode regime, at most 16 activation rows per
+// weight matrix per task):
 //   y[m, n] = sum_k x[m, k] * dequant(w)[n, k]
 // replacing the reference's fused decode-then-dot CPU path
 // (src/kquant_matmul.cpp:1104-1164 -> src/kquant_cpu_decode.cpp:1032-1065,
 // 1254-1297) and, through GemvTask lists, its batched MoE decode
 // (src/kquant_cpu_decode.cpp:1362-1527).
 //
-// The kernel is HBM-bound: every wire byte is read exactly once. Work layout:
-// one CTA of 8 warps owns 16 consecutive weight rows; the warps split K in
-// 256-weight chunks round-robin and their partial sums meet in shared memory.
-// Inside a warp the 16 rows x 16 K-slice products run on mma.sync m16n8k16 with
-// the WEIGHTS as the A operand (lane (g, t) holds rows g and g+8) and up to 8
-// (or 16) activation rows as the B operand, so the cost per weight does not
-// grow with M up to 16 and accumulation is fp32 throughout.
+// The kernel is HBM-bound: every wire byte is read exactly once, with 16-byte
+// loads issued one superblock ahead of their use.
 //
-//  * gemv_q4k_f16_kernel (q4_k, fp16 activations): lane t of each quad owns
-//    sub-block pair (2t, 2t+1) of the superblock, so it issues two 16-byte
-//    loads of quants per row and unpacks only its own two 6-bit scales. The
-//    A operand is the exact integer sc*q (<= 63*15, exact in fp16) built by one
-//    HFMA2 from the 0x6400|q half trick; a second MMA chain with A = mn gives
-//    sum(mn * x); the fp16 block scales d and dmin are applied in fp32 once per
-//    superblock: y += d * sum(sc*q*x) - dmin * sum(mn*x).
-//  * gemv_generic_kernel (every codec, f16 / bf16 / f32-as-bf16 activations):
-//    decode8<> produces bit-exact fp32 weights which are rounded to fp16 (fp16
-//    activations) or split into bf16 hi + lo (bf16 activations, two MMAs), so
-//    the weight error stays below 2^-12 relative either way.
+// Work layout. A thread-block CLUSTER of S <= 8 CTAs owns 128 consecutive
+// weight rows; CTA s of the cluster owns K-slice s, so even a 4096 x 4096
+// matrix spreads over 256 CTAs while each CTA re-reads only its own 1/S of
+// the activations. Inside a CTA the 8 warps own 16 rows each and walk the
+// slice together; the slice's activations sit in shared memory (swizzled so
+// the 16-byte fragment reads are conflict-free) and are shared by all warps.
+// The S partial [128 x M] tiles meet through distributed shared memory:
+// after a cluster barrier CTA s sums every S-th element over all peers and
+// writes y. No scratch in global memory, no atomics, a fixed summation order.
+//
+// Inside a warp the 16 rows x 16 K products run on mma.sync m16n8k16 with the
+// WEIGHTS as the A operand (lane (g, t) holds rows g and g+8) and 8 (or 16)
+// activation rows as the B operand: the cost per weight does not grow with M up
+// to 16, products are exact and accumulation is fp32.
+//
+//  * FAST (q4_k, fp16 activations): lane t of each quad owns sub-block pair
+//    (2t, 2t+1) of the superblock: two 16-byte loads of quants per row, and only
+//    its own two 6-bit scales to unpack. The A operand is the exact integer
+//    sc*q (<= 63*15, exact in fp16), built by one HFMA2 from the 0x6400|q half
+//    trick; a second MMA chain with A = mn gives sum(mn * x); the fp16 block
+//    scales are applied in fp32 once per superblock:
+//        y += d * sum(sc*q*x) - dmin * sum(mn*x).
+//  * generic (every codec; f16 / bf16 / f32-as-bf16 activations): decode8<>
+//    yields bit-exact fp32 weights, rounded to fp16 (fp16 activations) or split
+//    into bf16 hi + lo (two MMAs), so the weight error stays below 2^-12.
+#include <cooperative_groups.h>
+
+#include <cstdlib>
 #include <type_traits>
 
 #include "kq_common.cuh"
 #include "kq_launch.h"
 
+namespace cg = cooperative_groups;
+
 namespace kq {
 
 constexpr int kGemvWarps = 8;
 constexpr int kGemvThreads = kGemvWarps * 32;
+constexpr int kRowsPerCta = kGemvWarps * 16;
+constexpr int kStageK = 1024;              // activations per row staged in shared memory at a time
+constexpr int kStageChunks = kStageK / 8;  // 16-byte chunks per staged row
+constexpr int kMaxSplit = 8;               // portable cluster size limit
 
 __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                         uint32_t b0, uint32_t b1) {
@@ -58,24 +77,68 @@ __device__ __forceinline__ uint32_t pack_bf2(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// Eight consecutive activations as four packed 16-bit pairs. p == nullptr
-// (a padding row of the 8-wide B tile) yields zeros. float input is rounded to
-// bf16 first, as the reference's op does before its matmul
-// (src/kquant_ops.cpp:159-168).
-template <typename XT>
-__device__ __forceinline__ void load_x8(const XT* p, uint32_t (&r)[4]) {
-  if (p == nullptr) {
-    r[0] = r[1] = r[2] = r[3] = 0u;
-    return;
-  }
-  if constexpr (sizeof(XT) == 2) {
-    const uint4 v = __ldg(reinterpret_cast<const uint4*>(p));
-    r[0] = v.x; r[1] = v.y; r[2] = v.z; r[3] = v.w;
-  } else {
-    const float4 a = __ldg(reinterpret_cast<const float4*>(p));
-    const float4 b = __ldg(reinterpret_cast<const float4*>(p) + 1);
-    r[0] = pack_bf2(a.x, a.y); r[1] = pack_bf2(a.z, a.w);
-    r[2] = pack_bf2(b.x, b.y); r[3] = pack_bf2(b.z, b.w);
+// Programmatic dependent launch: a kernel launched with the programmatic-
+// serialization attribute may start while its predecessor in the stream is
+// still running; it must pass pdl_wait() before touching anything the
+// predecessor writes (here: activations). Both are no-ops for plain launches.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+// ---- activations in shared memory -------------------------------------------
+// Row n of the stage holds kStageChunks 16-byte chunks (8 activations each).
+// Chunk c of row n lives at slot c with its low three bits XOR-ed with bits 3-4
+// of c and with the row parity, so the eight lanes that one LDS.128 phase
+// serves (two rows x four quad lanes, whose chunks differ by 1 or by 8) always
+// touch eight different 16-byte bank groups.
+__device__ __forceinline__ int x_slot(int n, int c) {
+  return n * kStageChunks + ((c & ~7) | ((c & 7) ^ ((c >> 3) & 3) ^ ((n & 1) << 2)));
+}
+
+// Stage activations [k0, k0 + kStageK) of the task's rows; rows >= m and
+// columns >= k_end are zero. float input is rounded to bf16, as the reference's
+// op does before its matmul (src/kquant_ops.cpp:159-168).
+//
+// PERM (the q4_k fast path, fp16 only) stores each chunk x0..x7 as
+// x0 x2 x1 x3 x4 x6 x5 x7, the order in which the nibble unpacking yields
+// weights, and also leaves, per row and 32-activation group, the group sum
+// split into an fp16 head and tail (sum = hi + lo to 2^-22) in `xsum`
+// laid out [row][256-chunk][hi0..hi7 lo0..lo7].
+template <typename XT, int NT, bool PERM>
+__device__ __forceinline__ void stage_x(uint4* xs, __half* xsum, const GemvArgs& a, const int* s_xrow, int m, int k0,
+                                        int k_end) {
+  for (int idx = threadIdx.x; idx < NT * 8 * kStageChunks; idx += kGemvThreads) {
+    const int n = idx / kStageChunks, c = idx % kStageChunks;
+    const int k = k0 + 8 * c;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (n < m && k < k_end) {
+      const XT* p = static_cast<const XT*>(a.x) + (long long)s_xrow[n] * a.x_row_stride + k;
+      if constexpr (sizeof(XT) == 2) {
+        v = __ldg(reinterpret_cast<const uint4*>(p));
+      } else {
+        const float4 f0 = __ldg(reinterpret_cast<const float4*>(p));
+        const float4 f1 = __ldg(reinterpret_cast<const float4*>(p) + 1);
+        v = make_uint4(pack_bf2(f0.x, f0.y), pack_bf2(f0.z, f0.w), pack_bf2(f1.x, f1.y), pack_bf2(f1.z, f1.w));
+      }
+    }
+    if constexpr (PERM) {
+      const float2 p0 = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+      const float2 p1 = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+      const float2 p2 = __half22float2(*reinterpret_cast<const __half2*>(&v.z));
+      const float2 p3 = __half22float2(*reinterpret_cast<const __half2*>(&v.w));
+      float sum = ((p0.x + p0.y) + (p1.x + p1.y)) + ((p2.x + p2.y) + (p3.x + p3.y));
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);  // the four chunks of one 32-group sit in one aligned quad
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      if ((c & 3) == 0) {
+        const __half hi = __float2half_rn(sum);
+        const __half lo = __float2half_rn(sum - __half2float(hi));
+        __half* dst = xsum + (n * (kStageK / 256) + (c >> 5)) * 16 + ((c >> 2) & 7);
+        dst[0] = hi;
+        dst[8] = lo;
+      }
+      v = make_uint4(__byte_perm(v.x, v.y, 0x5410), __byte_perm(v.x, v.y, 0x7632), __byte_perm(v.z, v.w, 0x5410),
+                     __byte_perm(v.z, v.w, 0x7632));
+    }
+    xs[x_slot(n, c)] = v;
   }
 }
 
@@ -84,12 +147,12 @@ struct TaskView {
   int m;
 };
 
-// Resolve this CTA's row group into shared memory; returns false when the CTA
-// has nothing to do (a task index at or beyond the device-side task count).
+// Resolve this CTA's row group into shared memory. All CTAs of a cluster share
+// blockIdx.x and blockIdx.z, so they take the same decision.
 __device__ __forceinline__ bool resolve_task(const GemvArgs& a, int* s_xrow, int* s_yrow, TaskView& tv) {
   if (a.tasks != nullptr) {
-    if (a.n_tasks_dev != nullptr && (int)blockIdx.y + a.task_offset >= *a.n_tasks_dev) return false;
-    const GemvTask& t = a.tasks[blockIdx.y];
+    if (a.n_tasks_dev != nullptr && (int)blockIdx.z + a.task_offset >= *a.n_tasks_dev) return false;
+    const GemvTask& t = a.tasks[blockIdx.z];
     tv.w = t.w;
     tv.m = t.m;
     if (threadIdx.x < 16) {
@@ -97,7 +160,7 @@ __device__ __forceinline__ bool resolve_task(const GemvArgs& a, int* s_xrow, int
       s_yrow[threadIdx.x] = t.yrow[threadIdx.x];
     }
   } else {
-    const int r0 = blockIdx.y * 16;
+    const int r0 = blockIdx.z * 16;
     tv.w = a.w;
     tv.m = min(16, a.M - r0);
     if (threadIdx.x < 16) {
@@ -109,67 +172,215 @@ __device__ __forceinline__ bool resolve_task(const GemvArgs& a, int* s_xrow, int
   return tv.m > 0;
 }
 
-// Cross-warp sum of the per-warp D fragments and the store of the finished
-// 16-row x (8*NT)-token tile. OT is the output element type.
-template <int NT, typename OT>
-__device__ __forceinline__ void reduce_store(float (&acc)[NT][4], float* red, const GemvArgs& a, const int* s_yrow,
-                                             int m, int row0) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int g = lane >> 2, t = lane & 3;
-  constexpr int kTile = NT * 8 * 16;
-#pragma unroll
-  for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-      const int tok = nt * 8 + 2 * t + (i & 1);
-      const int row = g + 8 * (i >> 1);
-      red[warp * kTile + tok * 16 + row] = acc[nt][i];
-    }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < kTile; idx += kGemvThreads) {
-    const int tok = idx >> 4, row = idx & 15;
-    if (tok < m && row0 + row < a.N) {
-      float s = 0.f;
-#pragma unroll
-      for (int w = 0; w < kGemvWarps; w++) s += red[w * kTile + idx];
-      OT* y = static_cast<OT*>(a.y) + (long long)s_yrow[tok] * a.y_row_stride + row0 + row;
-      if constexpr (sizeof(OT) == 2 && !std::is_same<OT, __half>::value) {
-        *y = __float2bfloat16_rn(s);
-      } else {
-        *y = __float2half_rn(s);
-      }
-    }
+// ---- q4_k fast path pieces ---------------------------------------------------
+__device__ __forceinline__ uint32_t hfma2_u(uint32_t a, __half2 b, __half2 c) {
+  __half2 r = __hfma2(*reinterpret_cast<__half2*>(&a), b, c);
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+// (a & mask) | magic as ONE three-input logic op. Written as C the two different
+// constants become two instructions (a logic op carries a single immediate); with
+// both constants in registers it is one.
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t magic) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;\n" : "=r"(r) : "r"(a), "r"(mask), "r"(magic));
+  return r;
+}
+
+struct Q4kLoad {  // what one lane consumes per superblock: header + its 32 quant bytes, for both of its rows
+  uint4 hA, hB, qa0, qa1, qb0, qb1;
+};
+
+// Weight prefetch ring (fast path). Every warp owns kRing slots of one
+// superblock x 16 rows (16 x 144 B) in dynamic shared memory and keeps up to
+// kRing superblocks in flight with 16-byte cp.async copies - prefetch depth
+// without register cost, and 16 fully used 144-byte segments per warp request.
+constexpr int kRing = 2;
+constexpr int kSlotBytes = 16 * 144;
+constexpr int kRingBytesPerCta = kGemvWarps * kRing * kSlotBytes;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+// wait until at most n (0..kRing-1) of this thread's copy groups are still pending
+__device__ __forceinline__ void cp_async_wait(int n) {
+  switch (n) {
+    case 0: asm volatile("cp.async.wait_group 0;\n" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;\n" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;\n" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 3;\n" ::: "memory"); break;
   }
 }
 
-// ------------------------------------------------------------------ generic
-template <int C, int A, typename XT, int NT>
-__global__ void __launch_bounds__(kGemvThreads) gemv_generic_kernel(const GemvArgs a) {
+// The 144 16-byte pieces of a slot are spread over the lanes: piece j = lane + 32 i
+// is bytes [16 (j % 9), +16) of row j / 9. src_off / dst_off are fixed per lane.
+struct Q4kRingLane {
+  long long src_off[5];
+  int dst_off[5];
+};
+__device__ __forceinline__ Q4kRingLane q4k_ring_lane(int lane, int row0, int n_rows, long long row_bytes) {
+  Q4kRingLane r;
+#pragma unroll
+  for (int i = 0; i < 5; i++) {
+    const int j = lane + 32 * i;
+    const int row = j / 9, piece = j % 9;
+    r.src_off[i] = (long long)min(row0 + row, n_rows - 1) * row_bytes + piece * 16;
+    r.dst_off[i] = row * 144 + piece * 16;
+  }
+  return r;
+}
+__device__ __forceinline__ void q4k_ring_issue(const Q4kRingLane& r, const uint8_t* w, uint8_t* slot, int sb,
+                                               int lane) {
+#pragma unroll
+  for (int i = 0; i < 5; i++)
+    if (i < 4 || lane < 16) cp_async16(slot + r.dst_off[i], w + r.src_off[i] + (long long)sb * 144);
+  cp_async_commit();
+}
+__device__ __forceinline__ Q4kLoad q4k_ring_read(const uint8_t* slot, int g, int t) {
+  const uint4* bA = reinterpret_cast<const uint4*>(slot + g * 144);
+  const uint4* bB = reinterpret_cast<const uint4*>(slot + (g + 8) * 144);
+  Q4kLoad l;
+  l.hA = bA[0];
+  l.hB = bB[0];
+  l.qa0 = bA[1 + 2 * t];
+  l.qa1 = bA[2 + 2 * t];
+  l.qb0 = bB[1 + 2 * t];
+  l.qb1 = bB[2 + 2 * t];
+  return l;
+}
+
+// Scales of the lane's two sub-blocks (2t, 2t+1) of one row, ready for the
+// unpacking below: lo nibbles become 1024+q and take (sc, -1024 sc); hi nibbles
+// are left in place as 1024+16q and take (sc/16, -64 sc). All four constants and
+// every product are exact in fp16 (sc <= 63, q <= 15).
+struct Q4kRow {
+  __half2 sc_lo, off_lo, sc_hi, off_hi;
+  uint32_t mn;  // half2(mn[2t], mn[2t+1])
+  float d, dmin;
+};
+__device__ __forceinline__ uint32_t bytes_to_h2(uint32_t two_bytes) {
+  // (b0, b1) -> half2(b0, b1) exactly: 0x6400 | b is 1024 + b
+  const uint32_t m = (two_bytes & 0xffu) | ((two_bytes & 0xff00u) << 8) | 0x64006400u;
+  const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&m), __float2half2_rn(1024.f));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+__device__ __forceinline__ Q4kRow q4k_row_prep(const uint4& hdr, int t) {
+  Q4kRow r;
+  r.d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffff)));
+  r.dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+  // 6-bit pairs (src/kquant_cpu_decode.cpp:155-174), two sub-blocks at a time on 16-bit fields
+  const int sh = 16 * (t & 1);
+  const uint32_t u0 = (hdr.y >> sh) & 0xffffu, u1 = (hdr.z >> sh) & 0xffffu, u2 = (hdr.w >> sh) & 0xffffu;
+  uint32_t sc2, mn2;
+  if (t < 2) {
+    sc2 = u0 & 0x3f3fu;
+    mn2 = u1 & 0x3f3fu;
+  } else {
+    sc2 = (u2 & 0x0f0fu) | ((u0 >> 2) & 0x3030u);
+    mn2 = ((u2 >> 4) & 0x0f0fu) | ((u1 >> 2) & 0x3030u);
+  }
+  const uint32_t sch = bytes_to_h2(sc2);
+  const __half2 sc = *reinterpret_cast<const __half2*>(&sch);
+  r.sc_lo = __low2half2(sc);
+  r.off_lo = __hmul2(r.sc_lo, __float2half2_rn(-1024.f));
+  r.sc_hi = __hmul2(__high2half2(sc), __float2half2_rn(0.0625f));
+  r.off_hi = __hmul2(__high2half2(sc), __float2half2_rn(-64.f));
+  r.mn = bytes_to_h2(mn2);
+  return r;
+}
+
+// One superblock of the warp's 16 rows against the staged activations.
+// sbl = index of the superblock inside the shared-memory stage; xoff[] are the
+// lane's eight precomputed chunk slots of superblock 0 (see gemv_kernel).
+template <int NT>
+__device__ __forceinline__ void q4k_compute(const Q4kLoad& l, const uint4* xs, const __half* xsum, int sbl, int g,
+                                            int t, const int (&xoff)[8], float (&fin)[NT][4]) {
+  const Q4kRow ra = q4k_row_prep(l.hA, t), rb = q4k_row_prep(l.hB, t);
+  const uint32_t wa[8] = {l.qa0.x, l.qa0.y, l.qa0.z, l.qa0.w, l.qa1.x, l.qa1.y, l.qa1.z, l.qa1.w};
+  const uint32_t wb[8] = {l.qb0.x, l.qb0.y, l.qb0.z, l.qb0.w, l.qb1.x, l.qb1.y, l.qb1.z, l.qb1.w};
+  float accq[NT][4], accm[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+    for (int i = 0; i < 4; i++) accq[nt][i] = accm[nt][i] = 0.f;
+  const uint4* xsb = xs + sbl * 32;
+  const uint32_t kLo = 0x000f000fu, kHi = 0x00f000f0u, kMagic = 0x64006400u;
+#pragma unroll
+  for (int ip = 0; ip < 4; ip++) {
+    uint4 x0[NT], x1[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+      x0[nt] = xsb[xoff[ip] + nt * 8 * kStageChunks];      // sub-block 2t, activations 8ip..8ip+7
+      x1[nt] = xsb[xoff[4 + ip] + nt * 8 * kStageChunks];  // sub-block 2t+1
+    }
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      const uint32_t Wa = wa[2 * ip + h], Wb = wb[2 * ip + h];
+      const uint32_t Wa8 = Wa >> 8, Wb8 = Wb >> 8;
+      // pairs (byte0, byte2) and (byte1, byte3): the staged activations are in the same order
+      const uint32_t a0 = hfma2_u(and_or(Wa, kLo, kMagic), ra.sc_lo, ra.off_lo);
+      const uint32_t a1 = hfma2_u(and_or(Wb, kLo, kMagic), rb.sc_lo, rb.off_lo);
+      const uint32_t a2 = hfma2_u(and_or(Wa8, kLo, kMagic), ra.sc_lo, ra.off_lo);
+      const uint32_t a3 = hfma2_u(and_or(Wb8, kLo, kMagic), rb.sc_lo, rb.off_lo);
+      const uint32_t c0 = hfma2_u(and_or(Wa, kHi, kMagic), ra.sc_hi, ra.off_hi);
+      const uint32_t c1 = hfma2_u(and_or(Wb, kHi, kMagic), rb.sc_hi, rb.off_hi);
+      const uint32_t c2 = hfma2_u(and_or(Wa8, kHi, kMagic), ra.sc_hi, ra.off_hi);
+      const uint32_t c3 = hfma2_u(and_or(Wb8, kHi, kMagic), rb.sc_hi, rb.off_hi);
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++) {
+        mma_f16(accq[nt], a0, a1, a2, a3, h ? x0[nt].z : x0[nt].x, h ? x0[nt].w : x0[nt].y);
+        mma_f16(accq[nt], c0, c1, c2, c3, h ? x1[nt].z : x1[nt].x, h ? x1[nt].w : x1[nt].y);
+      }
+    }
+  }
+  // sum_s mn_s * xsum_s in one MMA: K slots 0-7 carry the fp16 heads of the eight
+  // group sums, slots 8-15 their tails; the lane supplies mn of its sub-blocks 2t, 2t+1.
+#pragma unroll
+  for (int nt = 0; nt < NT; nt++) {
+    const uint32_t* xq = reinterpret_cast<const uint32_t*>(xsum + ((nt * 8 + g) * (kStageK / 256) + sbl) * 16);
+    mma_f16(accm[nt], ra.mn, rb.mn, ra.mn, rb.mn, xq[t], xq[4 + t]);
+    fin[nt][0] += ra.d * accq[nt][0] - ra.dmin * accm[nt][0];
+    fin[nt][1] += ra.d * accq[nt][1] - ra.dmin * accm[nt][1];
+    fin[nt][2] += rb.d * accq[nt][2] - rb.dmin * accm[nt][2];
+    fin[nt][3] += rb.d * accq[nt][3] - rb.dmin * accm[nt][3];
+  }
+}
+
+// ---- the kernel ---------------------------------------------------------------
+// grid = (row groups of 128, S k-slices, tasks); cluster = (1, S, 1).
+template <int C, int A, typename XT, int NT, bool FAST>
+__global__ void __launch_bounds__(kGemvThreads) gemv_kernel(const GemvArgs a) {
   constexpr bool kHalf = std::is_same<XT, __half>::value;
   using OT = typename std::conditional<kHalf, __half, __nv_bfloat16>::type;
   constexpr int WPB = wpb_of(C), BPB = bpb_of(C);
+  constexpr int kTile = NT * 8 * kRowsPerCta;  // floats in one CTA's partial tile
+  constexpr bool kIq = (C == IQ4_NL || C == IQ4_XS || C == IQ2_XXS);
   __shared__ int s_xrow[16], s_yrow[16];
-  __shared__ float red[kGemvWarps * NT * 8 * 16];
-  __shared__ __align__(16) uint8_t s_tabs[kIqSmemBytes];
+  __shared__ __align__(16) uint4 xs[NT * 8 * kStageChunks];
+  __shared__ float red[kTile];
+  __shared__ __align__(16) uint8_t s_tabs[kIq ? kIqSmemBytes : 16];
+  __shared__ __align__(16) __half xsum[FAST ? NT * 8 * (kStageK / 256) * 16 : 8];
 
+  cg::cluster_group cluster = cg::this_cluster();
   IqTables tabs{};
-  if constexpr (C == IQ4_NL || C == IQ4_XS || C == IQ2_XXS) {
+  if constexpr (kIq) {
     tabs = stage_iq_tables(s_tabs, threadIdx.x, kGemvThreads);
   }
   TaskView tv;
-  if (!resolve_task(a, s_xrow, s_yrow, tv)) return;
+  if (!resolve_task(a, s_xrow, s_yrow, tv)) return;  // uniform over the cluster
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const int row0 = blockIdx.x * 16;
+  const int row0 = blockIdx.x * kRowsPerCta + warp * 16;
   const uint8_t* pA = tv.w + (long long)min(row0 + g, a.N - 1) * a.row_bytes;
   const uint8_t* pB = tv.w + (long long)min(row0 + g + 8, a.N - 1) * a.row_bytes;
-  const XT* xp[NT];
-#pragma unroll
-  for (int nt = 0; nt < NT; nt++) {
-    const int tok = nt * 8 + g;
-    xp[nt] = tok < tv.m ? static_cast<const XT*>(a.x) + (long long)s_xrow[tok] * a.x_row_stride : nullptr;
-  }
+
+  // this CTA's K-slice, in 256-weight chunks
+  const int S = gridDim.y, slice = blockIdx.y;
+  const int nchunks = (a.K + 255) >> 8;
+  const int per = (nchunks + S - 1) / S;
+  const int ch0 = min(slice * per, nchunks), ch1 = min(ch0 + per, nchunks);
 
   float acc[NT][4];
 #pragma unroll
@@ -177,192 +388,175 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_generic_kernel(const GemvAr
 #pragma unroll
     for (int i = 0; i < 4; i++) acc[nt][i] = 0.f;
 
-  const int ngroups = a.K / 32;  // 32-weight groups along K
-  for (int g0 = warp * 8; g0 < ngroups; g0 += kGemvWarps * 8) {
-#pragma unroll 2
-    for (int G = 0; G < 8; G++) {
-      const int gi = g0 + G;
-      if (gi >= ngroups) break;
-      long long boff;
-      int oct;
-      if constexpr (WPB == 256) {
-        boff = (long long)(gi >> 3) * BPB;
-        oct = (gi & 7) * 4 + t;
-      } else {
-        boff = (long long)gi * BPB;
-        oct = t;
+  // fast path: the lane's chunk slots inside superblock 0 of the stage, row g
+  // (sub-block 2t: chunks 8t+ip, sub-block 2t+1: chunks 8t+4+ip)
+  int xoff[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) xoff[i] = x_slot(g, 8 * t + i);
+
+  constexpr int kStageCh = kStageK / 256;  // 256-weight chunks per stage
+  if constexpr (FAST) {
+    extern __shared__ __align__(16) uint8_t dyn_smem[];
+    uint8_t* ring = dyn_smem + warp * (kRing * kSlotBytes);
+    const Q4kRingLane rl = q4k_ring_lane(lane, row0, a.N, a.row_bytes);
+    // Weights never depend on the preceding kernel: start streaming them before
+    // anything else, up to kRing superblocks deep.
+    int issued = ch0;
+    for (int d = 0; d < kRing && issued < ch1; d++, issued++)
+      q4k_ring_issue(rl, tv.w, ring + d * kSlotBytes, issued, lane);
+    // Every CTA of this grid is resident by the time all of them have said so;
+    // the next kernel in the stream may then start streaming ITS weights.
+    pdl_launch_dependents();
+    if (a.tasks == nullptr) pdl_wait();  // activations may come from the kernel before this one
+    for (int sb = ch0; sb < ch1; sb++) {
+      const int rel = sb - ch0;
+      if (rel % kStageCh == 0) {
+        if (rel != 0) __syncthreads();  // everyone is done with the previous stage
+        stage_x<XT, NT, true>(xs, xsum, a, s_xrow, tv.m, sb * 256, a.K);
+        __syncthreads();
       }
-      float va[8], vb[8];
-      decode8<C, A>(pA + boff, oct, va, tabs);
-      decode8<C, A>(pB + boff, oct, vb, tabs);
-      uint32_t xb[NT][4];
-#pragma unroll
-      for (int nt = 0; nt < NT; nt++) load_x8<XT>(xp[nt] ? xp[nt] + gi * 32 + t * 8 : nullptr, xb[nt]);
-      uint32_t ha[4], hb[4];
-      if constexpr (kHalf) {
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-          ha[i] = pack_h2(va[2 * i], va[2 * i + 1]);
-          hb[i] = pack_h2(vb[2 * i], vb[2 * i + 1]);
+      cp_async_wait(issued - sb - 1);
+      __syncwarp();
+      const Q4kLoad cur = q4k_ring_read(ring + (rel % kRing) * kSlotBytes, g, t);
+      __syncwarp();  // the slot is free again
+      if (issued < ch1) {
+        q4k_ring_issue(rl, tv.w, ring + (rel % kRing) * kSlotBytes, issued, lane);
+        issued++;
+      }
+      q4k_compute<NT>(cur, xs, xsum, rel % kStageCh, g, t, xoff, acc);
+    }
+  } else {
+    pdl_launch_dependents();
+    if (a.tasks == nullptr) pdl_wait();
+    for (int cs = ch0; cs < ch1; cs += kStageCh) {
+      const int ce = min(cs + kStageCh, ch1);
+      if (cs != ch0) __syncthreads();  // everyone is done with the previous stage
+      stage_x<XT, NT, false>(xs, xsum, a, s_xrow, tv.m, cs * 256, a.K);
+      __syncthreads();
+      const int ngroups = a.K / 32;
+      const int g_end = min(ce * 8, ngroups);
+#pragma unroll 2
+      for (int gi = cs * 8; gi < g_end; gi++) {
+        long long boff;
+        int oct;
+        if constexpr (WPB == 256) {
+          boff = (long long)(gi >> 3) * BPB;
+          oct = (gi & 7) * 4 + t;
+        } else {
+          boff = (long long)gi * BPB;
+          oct = t;
         }
+        float va[8], vb[8];
+        decode8<C, A>(pA + boff, oct, va, tabs);
+        decode8<C, A>(pB + boff, oct, vb, tabs);
+        const int c = (gi - cs * 8) * 4 + t;
+        uint4 xb[NT];
 #pragma unroll
-        for (int s = 0; s < 2; s++)
+        for (int nt = 0; nt < NT; nt++) xb[nt] = xs[x_slot(nt * 8 + g, c)];
+        uint32_t ha[4], hb[4];
+        if constexpr (kHalf) {
 #pragma unroll
-          for (int nt = 0; nt < NT; nt++)
-            mma_f16(acc[nt], ha[2 * s], hb[2 * s], ha[2 * s + 1], hb[2 * s + 1], xb[nt][2 * s], xb[nt][2 * s + 1]);
-      } else {
-        uint32_t la[4], lb[4];
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-          const __nv_bfloat162 h1 = __floats2bfloat162_rn(va[2 * i], va[2 * i + 1]);
-          const __nv_bfloat162 h2 = __floats2bfloat162_rn(vb[2 * i], vb[2 * i + 1]);
-          ha[i] = *reinterpret_cast<const uint32_t*>(&h1);
-          hb[i] = *reinterpret_cast<const uint32_t*>(&h2);
-          la[i] = pack_bf2(va[2 * i] - __low2float(h1), va[2 * i + 1] - __high2float(h1));
-          lb[i] = pack_bf2(vb[2 * i] - __low2float(h2), vb[2 * i + 1] - __high2float(h2));
-        }
-#pragma unroll
-        for (int s = 0; s < 2; s++)
+          for (int i = 0; i < 4; i++) {
+            ha[i] = pack_h2(va[2 * i], va[2 * i + 1]);
+            hb[i] = pack_h2(vb[2 * i], vb[2 * i + 1]);
+          }
 #pragma unroll
           for (int nt = 0; nt < NT; nt++) {
-            mma_bf16(acc[nt], ha[2 * s], hb[2 * s], ha[2 * s + 1], hb[2 * s + 1], xb[nt][2 * s], xb[nt][2 * s + 1]);
-            mma_bf16(acc[nt], la[2 * s], lb[2 * s], la[2 * s + 1], lb[2 * s + 1], xb[nt][2 * s], xb[nt][2 * s + 1]);
+            mma_f16(acc[nt], ha[0], hb[0], ha[1], hb[1], xb[nt].x, xb[nt].y);
+            mma_f16(acc[nt], ha[2], hb[2], ha[3], hb[3], xb[nt].z, xb[nt].w);
           }
+        } else {
+          uint32_t la[4], lb[4];
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            const __nv_bfloat162 h1 = __floats2bfloat162_rn(va[2 * i], va[2 * i + 1]);
+            const __nv_bfloat162 h2 = __floats2bfloat162_rn(vb[2 * i], vb[2 * i + 1]);
+            ha[i] = *reinterpret_cast<const uint32_t*>(&h1);
+            hb[i] = *reinterpret_cast<const uint32_t*>(&h2);
+            la[i] = pack_bf2(va[2 * i] - __low2float(h1), va[2 * i + 1] - __high2float(h1));
+            lb[i] = pack_bf2(vb[2 * i] - __low2float(h2), vb[2 * i + 1] - __high2float(h2));
+          }
+#pragma unroll
+          for (int nt = 0; nt < NT; nt++) {
+            mma_bf16(acc[nt], ha[0], hb[0], ha[1], hb[1], xb[nt].x, xb[nt].y);
+            mma_bf16(acc[nt], la[0], lb[0], la[1], lb[1], xb[nt].x, xb[nt].y);
+            mma_bf16(acc[nt], ha[2], hb[2], ha[3], hb[3], xb[nt].z, xb[nt].w);
+            mma_bf16(acc[nt], la[2], lb[2], la[3], lb[3], xb[nt].z, xb[nt].w);
+          }
+        }
       }
     }
   }
-  reduce_store<NT, OT>(acc, red, a, s_yrow, tv.m, row0);
-}
-
-// ------------------------------------------------------------------ q4_k, fp16
-// (1024 + q) pairs from one byte pair: bytes {i, i+1} of `nib` (each holding a
-// 4-bit value) become the low bytes of two halves whose high byte is 0x64.
-__device__ __forceinline__ uint32_t h2_magic01(uint32_t nib) { return __byte_perm(nib, 0x64646464u, 0x4140); }
-__device__ __forceinline__ uint32_t h2_magic23(uint32_t nib) { return __byte_perm(nib, 0x64646464u, 0x4342); }
-
-__device__ __forceinline__ uint32_t hfma2_u(uint32_t a, __half2 b, __half2 c) {
-  __half2 r = __hfma2(*reinterpret_cast<__half2*>(&a), b, c);
-  return *reinterpret_cast<uint32_t*>(&r);
-}
-
-struct Q4kRow {
-  __half2 sc0, off0, sc1, off1;  // sub-blocks 2t and 2t+1: scale and -1024*scale, both lanes of a half2
-  uint32_t mn0, mn1;             // the two mins as half2 broadcasts
-  float d, dmin;
-};
-
-__device__ __forceinline__ Q4kRow q4k_row_prep(const uint4& hdr, int t) {
-  Q4kRow r;
-  r.d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffff)));
-  r.dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
-  uint32_t sc0, mn0, sc1, mn1;
-  k4_scale_min(hdr.y, hdr.z, hdr.w, 2 * t, sc0, mn0);
-  k4_scale_min(hdr.y, hdr.z, hdr.w, 2 * t + 1, sc1, mn1);
-  const __half2 m1024 = __float2half2_rn(-1024.f);
-  r.sc0 = __half2half2(__ushort2half_rn((unsigned short)sc0));
-  r.sc1 = __half2half2(__ushort2half_rn((unsigned short)sc1));
-  r.off0 = __hmul2(r.sc0, m1024);
-  r.off1 = __hmul2(r.sc1, m1024);
-  const __half2 m0 = __half2half2(__ushort2half_rn((unsigned short)mn0));
-  const __half2 m1 = __half2half2(__ushort2half_rn((unsigned short)mn1));
-  r.mn0 = *reinterpret_cast<const uint32_t*>(&m0);
-  r.mn1 = *reinterpret_cast<const uint32_t*>(&m1);
-  return r;
-}
-
-template <int NT>
-__global__ void __launch_bounds__(kGemvThreads) gemv_q4k_f16_kernel(const GemvArgs a) {
-  __shared__ int s_xrow[16], s_yrow[16];
-  __shared__ float red[kGemvWarps * NT * 8 * 16];
-  TaskView tv;
-  if (!resolve_task(a, s_xrow, s_yrow, tv)) return;
-
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int g = lane >> 2, t = lane & 3;
-  const int row0 = blockIdx.x * 16;
-  const uint8_t* pA = tv.w + (long long)min(row0 + g, a.N - 1) * a.row_bytes;
-  const uint8_t* pB = tv.w + (long long)min(row0 + g + 8, a.N - 1) * a.row_bytes;
-  const __half* xp[NT];
-#pragma unroll
-  for (int nt = 0; nt < NT; nt++) {
-    const int tok = nt * 8 + g;
-    xp[nt] = tok < tv.m ? static_cast<const __half*>(a.x) + (long long)s_xrow[tok] * a.x_row_stride + 64 * t
-                        : nullptr;
-  }
-
-  float fin[NT][4];
+  // ---- partial tile -> shared memory, [token][row] so that y stores are contiguous
 #pragma unroll
   for (int nt = 0; nt < NT; nt++)
 #pragma unroll
-    for (int i = 0; i < 4; i++) fin[nt][i] = 0.f;
-
-  const int nsb = a.K >> 8;
-#pragma unroll 2
-  for (int sb = warp; sb < nsb; sb += kGemvWarps) {
-    const uint4* bA = reinterpret_cast<const uint4*>(pA + (long long)sb * 144);
-    const uint4* bB = reinterpret_cast<const uint4*>(pB + (long long)sb * 144);
-    // quants of sub-block pair t: bytes [32t, 32t+32) of the 128
-    const uint4 qa0 = __ldg(bA + 1 + 2 * t), qa1 = __ldg(bA + 2 + 2 * t);
-    const uint4 qb0 = __ldg(bB + 1 + 2 * t), qb1 = __ldg(bB + 2 + 2 * t);
-    const uint4 hA = __ldg(bA), hB = __ldg(bB);
-    const Q4kRow ra = q4k_row_prep(hA, t), rb = q4k_row_prep(hB, t);
-    const uint32_t wa[8] = {qa0.x, qa0.y, qa0.z, qa0.w, qa1.x, qa1.y, qa1.z, qa1.w};
-    const uint32_t wb[8] = {qb0.x, qb0.y, qb0.z, qb0.w, qb1.x, qb1.y, qb1.z, qb1.w};
-
-    float accq[NT][4], accm[NT][4];
-#pragma unroll
-    for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-      for (int i = 0; i < 4; i++) accq[nt][i] = accm[nt][i] = 0.f;
-
-#pragma unroll
-    for (int ip = 0; ip < 4; ip++) {  // two words (8 weights per sub-block) per step
-      uint32_t x0[NT][4], x1[NT][4];
-#pragma unroll
-      for (int nt = 0; nt < NT; nt++) {
-        load_x8<__half>(xp[nt] ? xp[nt] + sb * 256 + ip * 8 : nullptr, x0[nt]);        // sub-block 2t
-        load_x8<__half>(xp[nt] ? xp[nt] + sb * 256 + 32 + ip * 8 : nullptr, x1[nt]);   // sub-block 2t+1
-      }
-#pragma unroll
-      for (int h = 0; h < 2; h++) {
-        const uint32_t Wa = wa[2 * ip + h], Wb = wb[2 * ip + h];
-        const uint32_t la = Wa & 0x0f0f0f0fu, ua = (Wa >> 4) & 0x0f0f0f0fu;
-        const uint32_t lb = Wb & 0x0f0f0f0fu, ub = (Wb >> 4) & 0x0f0f0f0fu;
-        // sub-block 2t (low nibbles)
-        const uint32_t a0 = hfma2_u(h2_magic01(la), ra.sc0, ra.off0), a2 = hfma2_u(h2_magic23(la), ra.sc0, ra.off0);
-        const uint32_t a1 = hfma2_u(h2_magic01(lb), rb.sc0, rb.off0), a3 = hfma2_u(h2_magic23(lb), rb.sc0, rb.off0);
-        // sub-block 2t+1 (high nibbles)
-        const uint32_t c0 = hfma2_u(h2_magic01(ua), ra.sc1, ra.off1), c2 = hfma2_u(h2_magic23(ua), ra.sc1, ra.off1);
-        const uint32_t c1 = hfma2_u(h2_magic01(ub), rb.sc1, rb.off1), c3 = hfma2_u(h2_magic23(ub), rb.sc1, rb.off1);
-#pragma unroll
-        for (int nt = 0; nt < NT; nt++) {
-          mma_f16(accq[nt], a0, a1, a2, a3, x0[nt][2 * h], x0[nt][2 * h + 1]);
-          mma_f16(accm[nt], ra.mn0, rb.mn0, ra.mn0, rb.mn0, x0[nt][2 * h], x0[nt][2 * h + 1]);
-          mma_f16(accq[nt], c0, c1, c2, c3, x1[nt][2 * h], x1[nt][2 * h + 1]);
-          mma_f16(accm[nt], ra.mn1, rb.mn1, ra.mn1, rb.mn1, x1[nt][2 * h], x1[nt][2 * h + 1]);
-        }
-      }
+    for (int i = 0; i < 4; i++) {
+      const int tok = nt * 8 + 2 * t + (i & 1);
+      const int row = warp * 16 + g + 8 * (i >> 1);
+      red[tok * kRowsPerCta + row] = acc[nt][i];
     }
+  cluster.sync();
+  // CTA `slice` finishes elements slice, slice + S, ... of the tile: fixed order over the S peers
+  const float* peer[kMaxSplit];
 #pragma unroll
-    for (int nt = 0; nt < NT; nt++) {
-      fin[nt][0] += ra.d * accq[nt][0] - ra.dmin * accm[nt][0];
-      fin[nt][1] += ra.d * accq[nt][1] - ra.dmin * accm[nt][1];
-      fin[nt][2] += rb.d * accq[nt][2] - rb.dmin * accm[nt][2];
-      fin[nt][3] += rb.d * accq[nt][3] - rb.dmin * accm[nt][3];
+  for (int s = 0; s < kMaxSplit; s++) peer[s] = s < S ? cluster.map_shared_rank(red, s) : red;
+  const int cta_row0 = blockIdx.x * kRowsPerCta;
+  for (int idx = slice + S * threadIdx.x; idx < kTile; idx += S * kGemvThreads) {
+    const int tok = idx / kRowsPerCta, row = idx % kRowsPerCta;
+    if (tok < tv.m && cta_row0 + row < a.N) {
+      float sum = 0.f;
+#pragma unroll
+      for (int s = 0; s < kMaxSplit; s++)
+        if (s < S) sum += peer[s][idx];
+      OT* y = static_cast<OT*>(a.y) + (long long)s_yrow[tok] * a.y_row_stride + cta_row0 + row;
+      if constexpr (kHalf) {
+        *y = __float2half_rn(sum);
+      } else {
+        *y = __float2bfloat16_rn(sum);
+      }
     }
   }
-  reduce_store<NT, __half>(fin, red, a, s_yrow, tv.m, row0);
+  cluster.sync();  // peers may still be reading this CTA's tile
 }
 
 // ------------------------------------------------------------------ launch
+template <int C, int A, typename XT, int NT, bool FAST>
+static cudaError_t launch_k(const GemvArgs& a, dim3 grid, cudaStream_t st) {
+  auto kern = gemv_kernel<C, A, XT, NT, FAST>;
+  const size_t dyn = FAST ? (size_t)kRingBytesPerCta : 0;
+  if (dyn > 0) {
+    static bool attr_set[16] = {};  // per device, set once
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 16 && !attr_set[dev]) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn);
+      if (e != cudaSuccess) return e;
+      attr_set[dev] = true;
+    }
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kGemvThreads);
+  cfg.dynamicSmemBytes = dyn;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = grid.y;
+  attr[0].val.clusterDim.z = 1;
+  // dense calls overlap their weight prefetch with the tail of the previous kernel
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = a.tasks == nullptr ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, kern, a);
+}
+
 template <int C, int NAT>
 static cudaError_t launch_generic(int x_dtype, const GemvArgs& a, dim3 grid, bool nt2, bool aligned, cudaStream_t st) {
-#define KQ_GV(AL, XT)                                                             \
-  do {                                                                            \
-    if (nt2) gemv_generic_kernel<C, AL, XT, 2><<<grid, kGemvThreads, 0, st>>>(a); \
-    else gemv_generic_kernel<C, AL, XT, 1><<<grid, kGemvThreads, 0, st>>>(a);     \
-    return cudaGetLastError();                                                    \
-  } while (0)
+#define KQ_GV(AL, XT) \
+  return nt2 ? launch_k<C, AL, XT, 2, false>(a, grid, st) : launch_k<C, AL, XT, 1, false>(a, grid, st)
   if (aligned) {
     if (x_dtype == F16) KQ_GV(NAT, __half);
     if (x_dtype == BF16) KQ_GV(NAT, __nv_bfloat16);
@@ -380,17 +574,29 @@ cudaError_t launch_gemv(int codec, int x_dtype, const GemvArgs& a, cudaStream_t 
   const int groups = a.tasks ? a.n_tasks : (a.M + 15) / 16;
   if (groups <= 0) return cudaSuccess;
   if (groups > 65535) return cudaErrorInvalidConfiguration;
-  const dim3 grid((a.N + 15) / 16, groups);
-  const bool nt2 = a.tasks ? true : (a.M > 8);
-  // Block starts keep their natural alignment when the base pointer is 16-byte
-  // aligned and rows are a whole number of blocks (always true).
+  // K split (= cluster size). Measured on B200: what matters is (a) at least two
+  // CTAs per SM, whatever it costs, and (b) beyond that, slices of at least four
+  // 256-weight chunks so that the per-CTA prologue and cluster reduce amortise.
+  const int row_groups = (a.N + kRowsPerCta - 1) / kRowsPerCta;
+  const int nchunks = (a.K + 255) / 256;
+  int S = 1;
+  while (S < kMaxSplit && S * 2 <= nchunks) {
+    const long long ctas = (long long)row_groups * groups * S;
+    if (ctas >= 4 * 148) break;
+    if (ctas >= 2 * 148 && nchunks / (2 * S) < 4) break;
+    S *= 2;
+  }
+  // A/B lever: KQ_GEMV_SPLIT=1|2|4|8 overrides the K-split heuristic.
+  if (const char* env = std::getenv("KQ_GEMV_SPLIT")) {
+    const int v = std::atoi(env);
+    if ((v == 1 || v == 2 || v == 4 || v == 8) && v <= nchunks) S = v;
+  }
+  const dim3 grid(row_groups, S, groups);
+  const bool nt2 = a.tasks ? (a.max_m > 8) : (a.M > 8);
   const bool aligned = a.w_align16 != 0;
 
-  if (codec == Q4_K && x_dtype == F16 && aligned) {
-    if (nt2) gemv_q4k_f16_kernel<2><<<grid, kGemvThreads, 0, st>>>(a);
-    else gemv_q4k_f16_kernel<1><<<grid, kGemvThreads, 0, st>>>(a);
-    return cudaGetLastError();
-  }
+  if (codec == Q4_K && x_dtype == F16 && aligned)
+    return nt2 ? launch_k<Q4_K, 16, __half, 2, true>(a, grid, st) : launch_k<Q4_K, 16, __half, 1, true>(a, grid, st);
   switch (codec) {
     case Q2_K: return launch_generic<Q2_K, 4>(x_dtype, a, grid, nt2, aligned, st);
     case Q3_K: return launch_generic<Q3_K, 2>(x_dtype, a, grid, nt2, aligned, st);

@@ -36,6 +36,7 @@ struct GemvArgs {
   const int* n_tasks_dev;   // device count of valid tasks (may be < grid.y), or nullptr
   int n_tasks;              // grid.y when tasks != nullptr
   int task_offset;          // index of tasks[0] in the whole task list (for n_tasks_dev)
+  int max_m;                // upper bound on any task's m (picks the 8- or 16-row B tile)
 };
 
 // y = x . dequant(w)^T for skinny row groups. x_dtype: 0 f32 (rounded to bf16

@@ -61,7 +61,24 @@ def rel_fro(got: np.ndarray, want: np.ndarray) -> float:
     return float(np.linalg.norm(got - want) / max(np.linalg.norm(want), 1e-30))
 
 
-def max_rel_to_peak(got: np.ndarray, want: np.ndarray) -> float:
+# Unit roundoff of the output type: the result is rounded ONCE from fp32 to it.
+OUT_ULP = {"f16": 2.0 ** -11, "bf16": 2.0 ** -8, "f32": 2.0 ** -24}
+
+
+def max_rel_to_peak(got: np.ndarray, want: np.ndarray, out_dtype: str = "f32") -> float:
+    """max |got - want| / max |want| after discounting the unavoidable rounding of
+    each element to the output dtype (half an ulp: up to 2^-8 relative for bf16,
+    which alone exceeds 2e-3 of an element near the peak)."""
     got = got.astype(np.float64)
     want = want.astype(np.float64)
-    return float(np.abs(got - want).max() / max(np.abs(want).max(), 1e-30))
+    excess = np.maximum(np.abs(got - want) - OUT_ULP[out_dtype] * np.abs(want), 0.0)
+    return float(excess.max() / max(np.abs(want).max(), 1e-30))
+
+
+def assert_close(got, ref, out_dtype: str, tol: float = 2e-3) -> None:
+    """The matmul parity bar: relative Frobenius error <= tol and peak-normalised
+    max error (beyond the output rounding) <= tol, against an fp64-accumulated
+    reference of the fp32 math."""
+    rf, mx = rel_fro(got, ref), max_rel_to_peak(got, ref, out_dtype)
+    assert rf <= tol, f"rel_fro {rf:.3e} > {tol}"
+    assert mx <= tol, f"max/peak {mx:.3e} > {tol}"

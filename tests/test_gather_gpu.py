@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import mlx_kquant_b200 as kq
-from conftest import max_rel_to_peak, rel_fro
+from conftest import assert_close, rel_fro
 from gpu_util import mint_wire, x_to_torch, y_to_f32
 from oracle.kq_oracle import to_f32
 
@@ -40,7 +40,7 @@ def test_gather_sweep(oracle, codec, M):
                           rhs_indices=torch.from_numpy(rhs.astype(np.int64)))
         assert tuple(y.shape) == (B, M, N) and y.dtype == torch.float16
         ref = fp64_ref(oracle, store, "f16", wire, codec, lhs, rhs)
-        assert rel_fro(y_to_f32(y), ref) <= TOL and max_rel_to_peak(y_to_f32(y), ref) <= TOL
+        assert_close(y_to_f32(y), ref, "f16", TOL)
         cpu = oracle.gather_qmm(store, wire, lhs, rhs, codec, "f16").astype(np.float32)
         assert rel_fro(y_to_f32(y), cpu) <= TOL
 
@@ -94,7 +94,7 @@ def test_sorted_large_group_and_strided_experts(oracle):
     rhs = np.sort(np.random.default_rng(53).integers(0, E, B)).astype(np.uint32)
     y = kq.gather_qmm(x, gate, None, codec, rhs_indices=torch.from_numpy(rhs.astype(np.int64)), sorted_indices=True)
     ref = fp64_ref(oracle, store, "bf16", fused[:, :N, :], codec, np.arange(B), rhs)
-    assert rel_fro(y_to_f32(y), ref) <= TOL and max_rel_to_peak(y_to_f32(y), ref) <= TOL
+    assert_close(y_to_f32(y), ref, "bf16", TOL)
     # sorted and shuffled orders agree row for row
     perm = np.random.default_rng(54).permutation(B)
     y_sh = kq.gather_qmm(x, gate, None, codec, lhs_indices=torch.from_numpy(perm), rhs_indices=torch.from_numpy(rhs[perm].astype(np.int64)))
