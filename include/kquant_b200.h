@@ -103,6 +103,30 @@ KQ_API int kq_gather_qmm(const void* x, int x_dtype, long long x_batch, int M, i
                   const uint32_t* lhs_indices, const uint32_t* rhs_indices, long long n_entries, int transpose,
                   int rhs_sorted, void* y, void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- gather_qmm without a workspace (no counterpart in the reference) ----
+ * Same computation and arguments as kq_gather_qmm, minus the workspace: the
+ * grouping scratch lives in a fixed KQ_GATHER_STATIC_WS_BYTES array that is part
+ * of the library image on every GPU that loads it. Meant for callers that are
+ * not allowed to allocate device memory at all: a plugin inside a host process
+ * that has handed every byte of HBM to its own arena and forbids driver
+ * allocations afterwards, or a serving loop that must never pay cudaMalloc's
+ * device-wide synchronisation. Nothing here calls cudaMalloc, cudaFree or an
+ * allocating library routine.
+ *  - Limit: problems whose kq_gather_qmm_workspace_bytes() exceeds
+ *    KQ_GATHER_STATIC_WS_BYTES are rejected with KQ_ERR_INVALID_ARGUMENT (for
+ *    M = 1 and 128 experts that is about 75 000 index entries per call).
+ *  - The first call on each device looks up the array's device address; make
+ *    that first call outside any stream capture.
+ *  - All calls on a device share the one array (it keeps the previous call's
+ *    contents; what has to start from zero is cleared on the stream first), so
+ *    two calls that can overlap on the GPU - different streams, no dependency -
+ *    race. Serialise them or use kq_gather_qmm with separate workspaces. */
+#define KQ_GATHER_STATIC_WS_BYTES (1u << 20)
+KQ_API int kq_gather_qmm_noalloc(const void* x, int x_dtype, long long x_batch, int M, int K, const void* w,
+                                 int n_experts, long long w_expert_stride_bytes, size_t w_row_bytes, int N,
+                                 const char* kquant_type, const uint32_t* lhs_indices, const uint32_t* rhs_indices,
+                                 long long n_entries, int transpose, int rhs_sorted, void* y, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -32,6 +32,9 @@ SIGNATURES = {
     "kq_gather_qmm": (C.c_int, [C.c_void_p, C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_void_p, C.c_int,
                                 C.c_longlong, C.c_size_t, C.c_int, C.c_char_p, C.c_void_p, C.c_void_p,
                                 C.c_longlong, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "kq_gather_qmm_noalloc": (C.c_int, [C.c_void_p, C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_void_p, C.c_int,
+                                        C.c_longlong, C.c_size_t, C.c_int, C.c_char_p, C.c_void_p, C.c_void_p,
+                                        C.c_longlong, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
 }
 
 _lib = None

@@ -39,6 +39,13 @@ bool dtype_ok(int d) { return d == KQ_F32 || d == KQ_F16 || d == KQ_BF16; }
 
 }  // namespace
 
+namespace kq {
+int set_error(int code, const char* msg) {
+  g_err = msg ? msg : "";
+  return code;
+}
+}  // namespace kq
+
 extern "C" {
 
 const char* kq_last_error(void) { return g_err.c_str(); }

@@ -11,6 +11,10 @@
 //   4. task build: each expert's c*M rows are cut into GemvTask slices of 16
 //   5. the skinny-M kernel runs over (row tile, task)
 // All of it lives in a caller-provided workspace laid out by gather_layout().
+#include <cstdio>
+#include <mutex>
+
+#include "../../include/kquant_b200.h"
 #include "kq_common.cuh"
 #include "kq_launch.h"
 
@@ -181,3 +185,65 @@ cudaError_t launch_gather(int codec, int x_dtype, const void* x, int M, int K, c
 }
 
 }  // namespace kq
+
+// ---- gather_qmm for callers that may not allocate ---------------------------
+// The grouping scratch of launch_gather(), as a fixed array inside the library
+// image: every GPU that loads the library carries these bytes until the
+// process exits, whether or not this entry point is ever called.
+static __device__ __align__(256) unsigned char g_gather_static_ws[KQ_GATHER_STATIC_WS_BYTES];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_ws_mutex;
+void* g_static_ws_addr[kMaxDevices] = {};
+
+// Device address of g_gather_static_ws on the CURRENT device. The symbol name is
+// only a host-side handle: handing it to a kernel would pass a host address, so
+// the real address is asked for once per device and remembered.
+cudaError_t static_ws_address(void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(g_static_ws_mutex);
+  if (g_static_ws_addr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_gather_static_ws);
+    if (e != cudaSuccess) return e;
+    g_static_ws_addr[dev] = p;
+  }
+  *out = g_static_ws_addr[dev];
+  return cudaSuccess;
+}
+
+}  // namespace
+
+extern "C" int kq_gather_qmm_noalloc(const void* x, int x_dtype, long long x_batch, int M, int K, const void* w,
+                                     int n_experts, long long w_expert_stride_bytes, size_t w_row_bytes, int N,
+                                     const char* kquant_type, const uint32_t* lhs_indices,
+                                     const uint32_t* rhs_indices, long long n_entries, int transpose, int rhs_sorted,
+                                     void* y, void* stream) {
+  const size_t need = kq_gather_qmm_workspace_bytes(n_entries, M, n_experts);
+  if (need > KQ_GATHER_STATIC_WS_BYTES) {
+    char msg[256];
+    std::snprintf(msg, sizeof(msg),
+                  "[mlx_kquant.gather_qmm] problem too large for the built-in scratch: needs %zu bytes, the fixed array "
+                  "holds %u; use kq_gather_qmm with a caller-provided workspace.",
+                  need, (unsigned)KQ_GATHER_STATIC_WS_BYTES);
+    return kq::set_error(KQ_ERR_INVALID_ARGUMENT, msg);
+  }
+  void* ws = nullptr;
+  const cudaError_t e = static_ws_address(&ws);
+  if (e != cudaSuccess) {
+    char msg[256];
+    std::snprintf(msg, sizeof(msg), "[mlx_kquant] gather_qmm: cannot resolve the built-in scratch: %s",
+                  cudaGetErrorString(e));
+    return kq::set_error(KQ_ERR_CUDA, msg);
+  }
+  // From here on it is the ordinary path; it clears the counters it needs on the stream.
+  return kq_gather_qmm(x, x_dtype, x_batch, M, K, w, n_experts, w_expert_stride_bytes, w_row_bytes, N, kquant_type,
+                       lhs_indices, rhs_indices, n_entries, transpose, rhs_sorted, y, ws, KQ_GATHER_STATIC_WS_BYTES,
+                       stream);
+}
+

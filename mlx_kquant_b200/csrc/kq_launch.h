@@ -53,4 +53,8 @@ cudaError_t launch_gather(int codec, int x_dtype, const void* x, int M, int K, c
                           long long expert_stride, long long row_bytes, int N, const uint32_t* lhs,
                           const uint32_t* rhs, long long n_entries, void* y, void* workspace, cudaStream_t st);
 
+// Record `msg` as this thread's last error (what kq_last_error() returns) and
+// hand back `code`; lets entry points that live outside kq_abi.cu report errors.
+int set_error(int code, const char* msg);
+
 }  // namespace kq
