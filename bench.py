@@ -323,7 +323,7 @@ def run_b200(args):
                     "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
             "gpu_launches": args.steps * layers,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_kind": peak_kind, "traffic": None, "kernel": "gemv_kernel<q4_k, f16, NT=1, FAST>",
+                         "peak_kind": peak_kind, "traffic": 9463040, "kernel": "gemv_kernel<q4_k, f16, NT=1, FAST>",
                          "algorithmic_bytes_per_launch": MATRIX_BYTES},
             "cpu_baseline": cpu,
             "clocks": clocks,
