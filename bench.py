@@ -229,7 +229,7 @@ def run_b200(args):
     def launch_all(s):
         for i in range(layers):
             rc = L.kq_quantized_matmul(x_dev.data_ptr(), _lib.KQ_F16, M, K_COLS, K_COLS, W[i].data_ptr(), ROW_BYTES,
-                                       N_ROWS, CODEC.encode(), 1, y_dev[i].data_ptr(), N_ROWS, s.cuda_stream)
+                                       N_ROWS, CODEC.encode(), 1, y_dev[i].data_ptr(), N_ROWS, None, 0, s.cuda_stream)
             _lib.check(rc)
 
     # ---- correctness guard: the captured path equals the public op

@@ -79,10 +79,22 @@ KQ_API int kq_dequantize(const void* w, size_t w_bytes, const char* kquant_type,
  *  - x rows: `rows` of them (all leading dims of the reference's x flattened),
  *    x_row_stride elements apart, each row contiguous and 16-byte aligned.
  *  - y rows are y_row_stride elements apart.
- *  - transpose == 0 ([K, N] weights) is not built yet: KQ_ERR_UNSUPPORTED. */
+ *  - transpose == 0 ([K, N] weights) is not built yet: KQ_ERR_UNSUPPORTED.
+ *  - workspace: kq_quantized_matmul_workspace_bytes(x_dtype, rows, K) bytes of
+ *    device memory, 256-byte aligned (0 bytes, and NULL allowed, for fp16
+ *    activations or rows <= 16). Calls with more than 16 rows run on the tensor
+ *    cores in fp16; bf16 / f32 activations are converted there first, exactly, with
+ *    a per-row power-of-two factor. */
+KQ_API size_t kq_quantized_matmul_workspace_bytes(int x_dtype, long long rows, int K);
 KQ_API int kq_quantized_matmul(const void* x, int x_dtype, long long rows, int K, long long x_row_stride, const void* w,
                         size_t w_row_bytes, int N, const char* kquant_type, int transpose, void* y,
-                        long long y_row_stride, void* stream);
+                        long long y_row_stride, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Diagnostic: kernels never spin forever - a wait that does not complete within
+ * two seconds makes the kernel stop, raise a bit here and return (results of that
+ * call are then undefined). *flags = 0 means no kernel ever gave up. Synchronises
+ * the device; clear != 0 resets the flags. No counterpart in the reference. */
+KQ_API int kq_device_error_flags(int* flags, int clear);
 
 /* ---- gather_qmm: replaces KQuantGatherQMM::eval_cpu / eval_gpu,
  * src/kquant_gather.cpp:470-746, 819-956 (op: src/kquant_ops.cpp:293-420) ----

@@ -3,6 +3,7 @@
 // regime selection, and kernel launches. No allocation happens here.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 
@@ -87,9 +88,14 @@ int kq_dequantize(const void* w, size_t w_bytes, const char* kquant_type, int ou
   return KQ_OK;
 }
 
+size_t kq_quantized_matmul_workspace_bytes(int x_dtype, long long rows, int K) {
+  if (!dtype_ok(x_dtype) || rows <= 0 || K <= 0) return 0;
+  return kq::gemm_workspace_bytes(x_dtype, rows, K);
+}
+
 int kq_quantized_matmul(const void* x, int x_dtype, long long rows, int K, long long x_row_stride, const void* w,
                         size_t w_row_bytes, int N, const char* kquant_type, int transpose, void* y,
-                        long long y_row_stride, void* stream) {
+                        long long y_row_stride, void* workspace, size_t workspace_bytes, void* stream) {
   const int ci = find_codec(kquant_type);
   if (ci < 0)
     return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.quantized_matmul] Unknown kquant_type: '%s'.",
@@ -119,19 +125,42 @@ int kq_quantized_matmul(const void* x, int x_dtype, long long rows, int K, long 
   if (rows > 16LL * 65535)
     return fail(KQ_ERR_UNSUPPORTED, "[mlx_kquant.quantized_matmul] more than 1048560 rows in one call.");
 
-  kq::GemvArgs a{};
-  a.x = x;
-  a.x_row_stride = x_row_stride;
-  a.y = y;
-  a.y_row_stride = y_row_stride;
-  a.w = static_cast<const uint8_t*>(w);
-  a.w_align16 = (reinterpret_cast<uintptr_t>(w) & 15) == 0 ? 1 : 0;
-  a.row_bytes = (long long)w_row_bytes;
-  a.N = N;
-  a.K = K;
-  a.M = (int)rows;
-  cudaError_t e = kq::launch_gemv(ci, x_dtype, a, static_cast<cudaStream_t>(stream));
+  // Regimes: at most 16 rows -> the HBM-bound skinny kernel; more -> the tcgen05 tile kernel
+  // (KQ_FORCE_SKINNY=1 keeps everything on the skinny kernel, an A/B lever).
+  static const bool force_skinny = std::getenv("KQ_FORCE_SKINNY") != nullptr;
+  cudaError_t e;
+  if (rows > 16 && !force_skinny) {
+    const size_t need = kq::gemm_workspace_bytes(x_dtype, rows, K);
+    if (need > 0 && (workspace == nullptr || workspace_bytes < need))
+      return fail(KQ_ERR_INVALID_ARGUMENT,
+                  "[mlx_kquant.quantized_matmul] workspace too small: %zu bytes given, %zu needed.", workspace_bytes,
+                  need);
+    if (need > 0 && (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+      return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.quantized_matmul] workspace must be 256-byte aligned.");
+    e = kq::launch_gemm(ci, x_dtype, x, x_row_stride, y, y_row_stride, static_cast<const uint8_t*>(w),
+                        (long long)w_row_bytes, (int)rows, N, K, workspace, static_cast<cudaStream_t>(stream));
+  } else {
+    kq::GemvArgs a{};
+    a.x = x;
+    a.x_row_stride = x_row_stride;
+    a.y = y;
+    a.y_row_stride = y_row_stride;
+    a.w = static_cast<const uint8_t*>(w);
+    a.w_align16 = (reinterpret_cast<uintptr_t>(w) & 15) == 0 ? 1 : 0;
+    a.row_bytes = (long long)w_row_bytes;
+    a.N = N;
+    a.K = K;
+    a.M = (int)rows;
+    e = kq::launch_gemv(ci, x_dtype, a, static_cast<cudaStream_t>(stream));
+  }
   if (e != cudaSuccess) return cuda_fail("quantized_matmul", e);
+  return KQ_OK;
+}
+
+int kq_device_error_flags(int* flags, int clear) {
+  if (flags == nullptr) return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant] kq_device_error_flags: null pointer.");
+  cudaError_t e = kq::read_device_error(flags, clear != 0);
+  if (e != cudaSuccess) return cuda_fail("device_error_flags", e);
   return KQ_OK;
 }
 

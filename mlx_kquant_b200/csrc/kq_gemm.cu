@@ -1,0 +1,518 @@
+// Prefill quantized matmul (M > 16): y[M, N] = x[M, K] . dequant(W)^T on the
+// 5th-generation tensor cores, replacing the reference's dequantize-then-GEMM CPU
+// path (src/kquant_cpu_decode.cpp:1299-1352) and its Metal tile kernels
+// (src/kquant_matmul.cpp:313-527).
+//
+// One CTA computes a (128*MT) x 128 output tile. Warp-specialised pipeline over
+// K in steps of 64 (one 128-byte swizzle row of 16-bit elements), 4 stages:
+//   warps 0-3  producers: (a) activations: 16-byte cp.async copies straight into
+//              the 128B-swizzled K-major tile; (b) weights: wire bytes -> fp16 in registers -> the same
+//              swizzled layout. Then fence.proxy.async + mbarrier arrive.
+//   warp 4     one thread issues tcgen05.mma (M=128, N=128, K=16, kind::f16, fp32
+//              accumulators in tensor memory), tcgen05.commit frees the stage.
+//   warps 0-3  epilogue: tcgen05.ld the accumulators (thread = output row), round
+//              once to the output type, 32-byte stores.
+// Both operands are fp16: rounding a dequantized weight to bf16 alone would cost
+// 1.6e-3 relative error and break the 2e-3 budget together with a bf16 output
+// (fp16 costs 3e-4), and kind::f16 rejects a bf16 A operand next to an fp16 B
+// operand (illegal instruction on sm_100a), so bf16 / f32 activations are first
+// converted to fp16 by convert_x_kernel - exactly, with a per-row power-of-two
+// factor that the epilogue undoes.
+// q4_k weights are built exactly up to one rounding: sc*q is an exact integer in
+// fp16, d is an fp16 value already, so w = fma(sc*q, d, -fp16(dmin*mn)).
+//
+// Every mbarrier wait is bounded (2 s of %globaltimer): on expiry the CTA raises
+// a flag in g_kq_device_error, stops issuing work, frees its tensor memory and
+// returns, so a logic error can never leave the GPU spinning.
+#include <cstdio>
+#include <type_traits>
+
+#include "kq_common.cuh"
+#include "kq_launch.h"
+
+namespace kq {
+
+constexpr int kBN = 128;
+constexpr int kBK = 64;
+constexpr int kStages = 4;
+constexpr int kProducerThreads = 128;
+constexpr int kGemmThreads = kProducerThreads + 32;
+constexpr int kTileBytes = 128 * 128;  // 128 rows x 64 16-bit elements
+
+__device__ int g_kq_device_error = 0;
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t));
+  return t;
+}
+// Bounded wait. Returns false (after raising the abort flag) when the barrier did
+// not flip within 2 s or another thread of the CTA already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (int spin = 0;; spin++) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 63) == 63) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > 2000000000ull) {
+        *abort_flag = 1;
+        atomicOr(&g_kq_device_error, code);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void cp_async16_zfill(void* smem, const void* gmem, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(smem)), "l"(gmem), "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(smem_dst)),
+               "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(
+          tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile [rows][64 x 16-bit] with the
+// 128-byte swizzle: 8-row groups are 1024 B apart (stride byte offset), layout
+// type 2, descriptor version 1 (bits 46-47).
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3ffff) >> 4);  // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                       // leading byte offset (unused with swizzle), 16-byte units
+  d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset
+  d |= (uint64_t)1 << 46;                       // version
+  d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor, kind::f16: fp32 accumulate, A format a_fmt (0 fp16, 1
+// bf16), B fp16, both K-major, M = 128, N = kBN.
+__host__ __device__ constexpr uint32_t umma_idesc(uint32_t a_fmt) {
+  return (1u << 4) | (a_fmt << 7) | (0u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+
+__device__ __forceinline__ uint32_t pack_h2f(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t hfma2_bits(uint32_t a, __half2 b, __half2 c) {
+  __half2 r = __hfma2(*reinterpret_cast<__half2*>(&a), b, c);
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
+struct GemmArgs {
+  const void* x;
+  long long x_row_stride;
+  void* y;
+  long long y_row_stride;
+  const uint8_t* w;
+  long long row_bytes;
+  int M, N, K;
+  const float* row_scale;  // per-row factor applied in the epilogue, or nullptr
+};
+
+// ---- weight producers: 64 consecutive weights of one row -> eight swizzled 16-byte chunks
+template <int C, int A>
+__device__ __forceinline__ void produce_w_generic(const uint8_t* row, int kb, int K, uint8_t* dst_row, int r,
+                                                  const IqTables& tabs) {
+  constexpr int WPB = wpb_of(C), BPB = bpb_of(C);
+#pragma unroll 2
+  for (int c = 0; c < 8; c++) {
+    const int k = kb * kBK + c * 8;
+    uint4 out = make_uint4(0u, 0u, 0u, 0u);
+    if (k < K) {
+      float v[8];
+      if constexpr (WPB == 256) {
+        decode8<C, A>(row + (long long)(k >> 8) * BPB, (k & 255) >> 3, v, tabs);
+      } else {
+        decode8<C, A>(row + (long long)(k >> 5) * BPB, (k & 31) >> 3, v, tabs);
+      }
+      out = make_uint4(pack_h2f(v[0], v[1]), pack_h2f(v[2], v[3]), pack_h2f(v[4], v[5]), pack_h2f(v[6], v[7]));
+    }
+    *reinterpret_cast<uint4*>(dst_row + ((c ^ (r & 7)) << 4)) = out;
+  }
+}
+
+__device__ __forceinline__ uint32_t two_bytes_to_h2(uint32_t two_bytes) {
+  const uint32_t m = (two_bytes & 0xffu) | ((two_bytes & 0xff00u) << 8) | 0x64006400u;
+  const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&m), __float2half2_rn(1024.f));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+// q4_k: K-chunk kb is sub-block pair p = kb & 3 of superblock kb >> 2 (src/kquant_cpu_decode.cpp:177-202)
+__device__ __forceinline__ void produce_w_q4k(const uint8_t* row, int kb, uint8_t* dst_row, int r) {
+  const uint4* blk = reinterpret_cast<const uint4*>(row + (long long)(kb >> 2) * 144);
+  const int p = kb & 3;
+  const uint4 hdr = __ldg(blk);
+  const uint4 q0 = __ldg(blk + 1 + 2 * p), q1 = __ldg(blk + 2 + 2 * p);
+  const int sh = 16 * (p & 1);
+  const uint32_t u0 = (hdr.y >> sh) & 0xffffu, u1 = (hdr.z >> sh) & 0xffffu, u2 = (hdr.w >> sh) & 0xffffu;
+  uint32_t sc2, mn2;
+  if (p < 2) {
+    sc2 = u0 & 0x3f3fu;
+    mn2 = u1 & 0x3f3fu;
+  } else {
+    sc2 = (u2 & 0x0f0fu) | ((u0 >> 2) & 0x3030u);
+    mn2 = ((u2 >> 4) & 0x0f0fu) | ((u1 >> 2) & 0x3030u);
+  }
+  const uint32_t sch = two_bytes_to_h2(sc2);
+  const __half2 sc = *reinterpret_cast<const __half2*>(&sch);
+  const __half2 sc_a = __low2half2(sc), sc_b = __high2half2(sc);
+  const __half2 m1024 = __float2half2_rn(-1024.f);
+  const __half2 off_a = __hmul2(sc_a, m1024), off_b = __hmul2(sc_b, m1024);
+  const __half dh = __ushort_as_half((unsigned short)(hdr.x & 0xffff));
+  const __half2 d2 = __half2half2(dh);
+  const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+  const __half2 ndm_a = __float2half2_rn(-(dmin * (float)(mn2 & 0xff)));
+  const __half2 ndm_b = __float2half2_rn(-(dmin * (float)(mn2 >> 8)));
+  const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+  for (int c = 0; c < 4; c++) {
+    uint32_t lo[4], hi[4];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      const uint32_t W = w[2 * c + h];
+      const uint32_t l4 = W & 0x0f0f0f0fu, h4 = (W >> 4) & 0x0f0f0f0fu;
+      // (1024 + q) pairs in natural order, then sc*q exactly, then one rounding: fma(sc*q, d, -dmin*mn)
+      lo[2 * h] = hfma2_bits(hfma2_bits(__byte_perm(l4, 0x64646464u, 0x4140), sc_a, off_a), d2, ndm_a);
+      lo[2 * h + 1] = hfma2_bits(hfma2_bits(__byte_perm(l4, 0x64646464u, 0x4342), sc_a, off_a), d2, ndm_a);
+      hi[2 * h] = hfma2_bits(hfma2_bits(__byte_perm(h4, 0x64646464u, 0x4140), sc_b, off_b), d2, ndm_b);
+      hi[2 * h + 1] = hfma2_bits(hfma2_bits(__byte_perm(h4, 0x64646464u, 0x4342), sc_b, off_b), d2, ndm_b);
+    }
+    *reinterpret_cast<uint4*>(dst_row + ((c ^ (r & 7)) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    *reinterpret_cast<uint4*>(dst_row + (((c + 4) ^ (r & 7)) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+  }
+}
+
+// ------------------------------------------------------------------ the kernel
+// Activations are always fp16 here (bf16 / f32 callers go through
+// convert_x_kernel first). OT: output type. MT: 128-row halves per CTA tile.
+template <int C, int A, typename OT, int MT, bool FASTQ4>
+__global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmArgs a) {
+  constexpr bool kHalf = std::is_same<OT, __half>::value;
+  using XT = __half;
+  constexpr int kStageBytes = (MT + 1) * kTileBytes;
+  constexpr bool kIq = (C == IQ4_NL || C == IQ4_XS || C == IQ2_XXS);
+  extern __shared__ __align__(1024) uint8_t gemm_smem[];
+  // 1024-byte alignment of the tiles is what the 128B swizzle pattern assumes
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gemm_smem) + 1023) & ~(uintptr_t)1023);
+  __shared__ uint64_t full_bar[kStages], empty_bar[kStages], accum_bar;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+  __shared__ __align__(16) uint8_t s_tabs[kIq ? kIqSmemBytes : 16];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * kBN, m0 = blockIdx.y * (128 * MT);
+  const int KB = (a.K + kBK - 1) / kBK;
+  constexpr uint32_t kTmemCols = MT * kBN;  // 128 or 256: a power of two >= 32
+
+  IqTables tabs{};
+  if constexpr (kIq) tabs = stage_iq_tables(s_tabs, threadIdx.x, kGemmThreads);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; s++) {
+      mbar_init(&full_bar[s], kProducerThreads / 32);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&accum_bar, 1);
+    abort_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 4) tmem_alloc(&tmem_base_s, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_s;
+  volatile int* abort_flag = &abort_s;
+
+  if (warp < 4) {
+    // ================= producers =================
+    const int tid = threadIdx.x;
+    const uint8_t* wrow = a.w + (long long)min(n0 + tid, a.N - 1) * a.row_bytes;
+    bool ok = true;
+    for (int kb = 0; kb < KB && ok; kb++) {
+      const int s = kb % kStages;
+      if (kb >= kStages) ok = mbar_wait(&empty_bar[s], ((kb / kStages) & 1) ^ 1, abort_flag, 1);
+      if (!ok) break;
+      uint8_t* st = tiles + s * kStageBytes;
+      // activations: MT*128 rows x 8 chunks, consecutive threads take consecutive chunks of a row
+#pragma unroll
+      for (int u = 0; u < MT * 8; u++) {
+        const int j = tid + kProducerThreads * u;
+        const int row = j >> 3, c = j & 7;
+        const int r = row & 127;
+        uint8_t* dst = st + (row >> 7) * kTileBytes + r * 128 + ((c ^ (r & 7)) << 4);
+        const int k = kb * kBK + c * 8;
+        const bool in = (m0 + row < a.M) && (k < a.K);
+        const XT* src = static_cast<const XT*>(a.x) + (long long)(in ? m0 + row : 0) * a.x_row_stride + (in ? k : 0);
+        cp_async16_zfill(dst, src, in ? 16 : 0);
+      }
+      // weights: this thread's row, 64 weights
+      uint8_t* wdst = st + MT * kTileBytes + tid * 128;
+      if constexpr (FASTQ4) {
+        produce_w_q4k(wrow, kb, wdst, tid);
+      } else {
+        produce_w_generic<C, A>(wrow, kb, a.K, wdst, tid, tabs);
+      }
+      cp_async_wait_all();
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&full_bar[s]);
+    }
+    // ================= epilogue =================
+    if (ok) ok = mbar_wait(&accum_bar, 0, abort_flag, 4);
+    if (ok) {
+      tc_fence_after();
+#pragma unroll 1
+      for (int h = 0; h < MT; h++) {
+        const int row = m0 + h * 128 + warp * 32 + lane;
+        OT* yrow = static_cast<OT*>(a.y) + (long long)row * a.y_row_stride + n0;
+        const bool vec_ok = ((reinterpret_cast<uintptr_t>(yrow) & 15) == 0);
+#pragma unroll 1
+        for (int c0 = 0; c0 < kBN; c0 += 16) {
+          uint32_t v[16];
+          tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(h * kBN + c0), v);
+          tmem_ld_wait();
+          if (row < a.M) {
+            const float rs = a.row_scale ? a.row_scale[row] : 1.f;
+            uint32_t o[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+              const float f0 = __uint_as_float(v[2 * i]) * rs, f1 = __uint_as_float(v[2 * i + 1]) * rs;
+              if constexpr (kHalf) {
+                o[i] = pack_h2f(f0, f1);
+              } else {
+                __nv_bfloat162 b = __floats2bfloat162_rn(f0, f1);
+                o[i] = *reinterpret_cast<uint32_t*>(&b);
+              }
+            }
+            if (vec_ok && n0 + c0 + 16 <= a.N) {
+              reinterpret_cast<uint4*>(yrow + c0)[0] = make_uint4(o[0], o[1], o[2], o[3]);
+              reinterpret_cast<uint4*>(yrow + c0)[1] = make_uint4(o[4], o[5], o[6], o[7]);
+            } else {
+              const OT* oe = reinterpret_cast<const OT*>(o);
+              for (int i = 0; i < 16; i++)
+                if (n0 + c0 + i < a.N) yrow[c0 + i] = oe[i];
+            }
+          }
+        }
+      }
+    }
+  } else {
+    // ================= MMA issuer =================
+    constexpr uint32_t idesc = umma_idesc(0u);
+    bool ok = true;
+    for (int kb = 0; kb < KB && ok; kb++) {
+      const int s = kb % kStages;
+      ok = mbar_wait(&full_bar[s], (kb / kStages) & 1, abort_flag, 2);
+      if (!ok) break;
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t st = smem_u32(tiles + s * kStageBytes);
+        const uint32_t bt = st + MT * kTileBytes;
+#pragma unroll
+        for (int h = 0; h < MT; h++)
+#pragma unroll
+          for (int j = 0; j < kBK / 16; j++)
+            umma_f16(tmem_base + h * kBN, umma_desc_sw128(st + h * kTileBytes + j * 32), umma_desc_sw128(bt + j * 32),
+                     idesc, (kb > 0 || j > 0) ? 1u : 0u);
+        umma_commit(&empty_bar[s]);  // the stage is free once these MMAs have read it
+      }
+      __syncwarp();
+    }
+    if (lane == 0) umma_commit(&accum_bar);  // also on the abort path: lets the wait below see the MMAs drain
+    __syncwarp();
+    if (!ok) mbar_wait(&accum_bar, 0, abort_flag, 8);
+  }
+
+  // ================= teardown =================
+  cp_async_wait_all();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------ activation pre-pass
+// bf16 / f32 activations -> fp16 for the tensor-core tile kernel (kind::f16 does
+// not accept a bf16 A operand next to an fp16 B operand). float input is first
+// rounded to bf16, as the reference's op does (src/kquant_ops.cpp:159-168). A
+// bf16 value converts to fp16 exactly unless it is out of fp16's range, so each
+// row is divided by a power of two 2^e (e = 0 for every row whose largest
+// magnitude is below 32768, i.e. practically always) and the factor is handed to
+// the epilogue: nothing saturates, nothing is rounded twice.
+template <typename XT>
+__global__ void __launch_bounds__(256) convert_x_kernel(const XT* __restrict__ x, long long x_row_stride, int K,
+                                                        __half* __restrict__ xh, float* __restrict__ row_scale) {
+  const long long row = blockIdx.x;
+  const XT* xr = x + row * x_row_stride;
+  __shared__ float s_max[8];
+  float mx = 0.f;
+  for (int k = threadIdx.x; k < K; k += 256) {
+    float v;
+    if constexpr (sizeof(XT) == 2) v = __bfloat162float(xr[k]);
+    else v = __bfloat162float(__float2bfloat16_rn(xr[k]));
+    v = fabsf(v);
+    if (v < INFINITY) mx = fmaxf(mx, v);  // inf / nan propagate on their own
+  }
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  mx = s_max[0];
+  for (int i = 1; i < 8; i++) mx = fmaxf(mx, s_max[i]);
+  int e = 0;
+  if (mx >= 32768.f) e = ilogbf(mx) - 14;  // largest magnitude lands in [16384, 32768)
+  const float down = ldexpf(1.f, -e);
+  if (threadIdx.x == 0) row_scale[row] = ldexpf(1.f, e);
+  __half* o = xh + row * (long long)K;
+  for (int k = threadIdx.x; k < K; k += 256) {
+    float v;
+    if constexpr (sizeof(XT) == 2) v = __bfloat162float(xr[k]);
+    else v = __bfloat162float(__float2bfloat16_rn(xr[k]));
+    o[k] = __float2half_rn(v * down);
+  }
+}
+
+size_t gemm_workspace_bytes(int x_dtype, long long rows, int K) {
+  if (x_dtype == F16 || rows <= 16) return 0;
+  const size_t xh = ((size_t)rows * (size_t)K * 2 + 255) & ~(size_t)255;
+  return xh + (((size_t)rows * 4 + 255) & ~(size_t)255);
+}
+
+// ------------------------------------------------------------------ launch
+template <int C, int A, typename OT, int MT, bool FASTQ4>
+static cudaError_t launch_g(const GemmArgs& a, cudaStream_t st) {
+  auto kern = gemm_kernel<C, A, OT, MT, FASTQ4>;
+  const size_t dyn = (size_t)kStages * (MT + 1) * kTileBytes + 1024;
+  static bool attr_set[16] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 16 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  const dim3 grid((a.N + kBN - 1) / kBN, (a.M + 128 * MT - 1) / (128 * MT));
+  kern<<<grid, kGemmThreads, dyn, st>>>(a);
+  return cudaGetLastError();
+}
+
+template <int C, int A, bool FASTQ4>
+static cudaError_t launch_shape(bool out_half, const GemmArgs& a, cudaStream_t st) {
+  const bool mt2 = a.M > 128;
+  if (out_half) return mt2 ? launch_g<C, A, __half, 2, FASTQ4>(a, st) : launch_g<C, A, __half, 1, FASTQ4>(a, st);
+  return mt2 ? launch_g<C, A, __nv_bfloat16, 2, FASTQ4>(a, st) : launch_g<C, A, __nv_bfloat16, 1, FASTQ4>(a, st);
+}
+
+template <int C, int NAT>
+static cudaError_t launch_codec(bool out_half, const GemmArgs& a, bool aligned, cudaStream_t st) {
+  return aligned ? launch_shape<C, NAT, false>(out_half, a, st) : launch_shape<C, 1, false>(out_half, a, st);
+}
+
+cudaError_t launch_gemm(int codec, int x_dtype, const void* x, long long x_row_stride, void* y, long long y_row_stride,
+                        const uint8_t* w, long long row_bytes, int M, int N, int K, void* workspace, cudaStream_t st) {
+  if (M <= 0 || N <= 0 || K <= 0) return cudaSuccess;
+  GemmArgs a;
+  a.x = x;
+  a.x_row_stride = x_row_stride;
+  a.y = y;
+  a.y_row_stride = y_row_stride;
+  a.w = w;
+  a.row_bytes = row_bytes;
+  a.M = M;
+  a.N = N;
+  a.K = K;
+  a.row_scale = nullptr;
+  if (x_dtype != F16) {
+    __half* xh = static_cast<__half*>(workspace);
+    float* rs = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + (((size_t)M * K * 2 + 255) & ~(size_t)255));
+    if (x_dtype == BF16)
+      convert_x_kernel<__nv_bfloat16><<<M, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), x_row_stride, K, xh, rs);
+    else
+      convert_x_kernel<float><<<M, 256, 0, st>>>(static_cast<const float*>(x), x_row_stride, K, xh, rs);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    a.x = xh;
+    a.x_row_stride = K;
+    a.row_scale = rs;
+  }
+  const bool out_half = x_dtype == F16;
+  const bool aligned = (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+  if (codec == Q4_K && aligned) return launch_shape<Q4_K, 16, true>(out_half, a, st);
+  switch (codec) {
+    case Q2_K: return launch_codec<Q2_K, 4>(out_half, a, aligned, st);
+    case Q3_K: return launch_codec<Q3_K, 2>(out_half, a, aligned, st);
+    case Q4_K: return launch_codec<Q4_K, 16>(out_half, a, aligned, st);
+    case Q5_K: return launch_codec<Q5_K, 16>(out_half, a, aligned, st);
+    case Q6_K: return launch_codec<Q6_K, 2>(out_half, a, aligned, st);
+    case Q4_0: return launch_codec<Q4_0, 2>(out_half, a, aligned, st);
+    case Q8_0: return launch_codec<Q8_0, 2>(out_half, a, aligned, st);
+    case IQ4_NL: return launch_codec<IQ4_NL, 2>(out_half, a, aligned, st);
+    case IQ4_XS: return launch_codec<IQ4_XS, 8>(out_half, a, aligned, st);
+    case IQ2_XXS: return launch_codec<IQ2_XXS, 2>(out_half, a, aligned, st);
+  }
+  return cudaErrorInvalidValue;
+}
+
+// Flags raised by kernels that gave up on a bounded wait (0 = none). Synchronises the device.
+cudaError_t read_device_error(int* out, bool clear) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, g_kq_device_error, sizeof(int));
+  if (e == cudaSuccess && clear && *out != 0) {
+    const int zero = 0;
+    e = cudaMemcpyToSymbol(g_kq_device_error, &zero, sizeof(int));
+  }
+  return e;
+}
+
+}  // namespace kq

@@ -43,6 +43,14 @@ struct GemvArgs {
 // on load, output bf16), 1 f16, 2 bf16.
 cudaError_t launch_gemv(int codec, int x_dtype, const GemvArgs& a, cudaStream_t st);
 
+// Prefill (M > 16) tile kernel on tcgen05 tensor cores with TMEM accumulators.
+// bf16 / f32 activations need gemm_workspace_bytes() of scratch for their fp16 copy.
+size_t gemm_workspace_bytes(int x_dtype, long long rows, int K);
+cudaError_t launch_gemm(int codec, int x_dtype, const void* x, long long x_row_stride, void* y, long long y_row_stride,
+                        const uint8_t* w, long long row_bytes, int M, int N, int K, void* workspace, cudaStream_t st);
+// Flags raised by kernels that gave up on a bounded wait (0 = none); synchronises the device.
+cudaError_t read_device_error(int* out, bool clear);
+
 // gather_qmm: device-side grouping by expert + the skinny-M kernel per group.
 struct GatherLayout {
   size_t counts, offsets, task_base, cursor, n_tasks, order, tasks, total;

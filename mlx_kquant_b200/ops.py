@@ -125,10 +125,16 @@ def quantized_matmul(x, w, scales, kquant_type, transpose=True, *, stream=None):
         x2 = x2.contiguous()
     rows = x2.shape[0]
     y = torch.empty((rows, outer), dtype=out_dtype, device=w.device)
+    L = _lib.lib()
+    ws_bytes = L.kq_quantized_matmul_workspace_bytes(_DT[x.dtype], rows, K)
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=w.device) if ws_bytes else None
+    if ws is not None and stream is not None:
+        ws.record_stream(stream)
     with torch.cuda.device(w.device):
-        check(_lib.lib().kq_quantized_matmul(x2.data_ptr(), _DT[x.dtype], rows, K, x2.stride(0), w2.data_ptr(),
-                                             w2.shape[-1], outer, kquant_type.encode(), int(bool(transpose)),
-                                             y.data_ptr(), y.stride(0), _stream_ptr(stream, w.device)))
+        check(L.kq_quantized_matmul(x2.data_ptr(), _DT[x.dtype], rows, K, x2.stride(0), w2.data_ptr(),
+                                    w2.shape[-1], outer, kquant_type.encode(), int(bool(transpose)),
+                                    y.data_ptr(), y.stride(0), ws.data_ptr() if ws is not None else None,
+                                    ws_bytes, _stream_ptr(stream, w.device)))
     y = y.reshape(x.shape[:-1] + (outer,))
     return y.cpu() if on_cpu else y
 

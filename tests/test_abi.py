@@ -48,13 +48,16 @@ def test_abi_validation_needs_no_gpu():
     assert b"must be a multiple of bytes_per_block (144)" in L.kq_last_error()
     assert L.kq_dequantize(None, 144, b"q4_k", 7, None, None) == _lib.KQ_ERR_INVALID_ARGUMENT
     # K mismatch: 2 blocks of q4_k = 512 weights but K = 256
-    rc = L.kq_quantized_matmul(None, 1, 1, 256, 256, None, 288, 4, b"q4_k", 1, None, 4, None)
+    rc = L.kq_quantized_matmul(None, 1, 1, 256, 256, None, 288, 4, b"q4_k", 1, None, 4, None, 0, None)
     assert rc == _lib.KQ_ERR_INVALID_ARGUMENT and b"does not match the expanded quantized matrix inner dim (512)" in L.kq_last_error()
-    rc = L.kq_quantized_matmul(None, 1, 1, 512, 512, None, 288, 4, b"q4_k", 0, None, 4, None)
+    rc = L.kq_quantized_matmul(None, 1, 1, 512, 512, None, 288, 4, b"q4_k", 0, None, 4, None, 0, None)
     assert rc == _lib.KQ_ERR_UNSUPPORTED
     # zero-sized problems succeed without touching memory
     assert L.kq_dequantize(None, 0, b"q4_k", 1, None, None) == 0
-    assert L.kq_quantized_matmul(None, 1, 0, 512, 512, None, 288, 4, b"q4_k", 1, None, 4, None) == 0
+    assert L.kq_quantized_matmul(None, 1, 0, 512, 512, None, 288, 4, b"q4_k", 1, None, 4, None, 0, None) == 0
+    assert L.kq_quantized_matmul_workspace_bytes(1, 4096, 4096) == 0        # fp16 needs none
+    assert L.kq_quantized_matmul_workspace_bytes(2, 4096, 4096) >= 4096 * 4096 * 2
+    assert L.kq_quantized_matmul_workspace_bytes(2, 16, 4096) == 0          # decode regime needs none
     assert L.kq_gather_qmm_workspace_bytes(8, 1, 128) > 0
 
 

@@ -111,6 +111,8 @@ def test_many_rows_regression():
     rhs = (torch.arange(B, device="cuda") * 2 // B).to(torch.int64)
     y = kq.gather_qmm(x, wd, None, codec, rhs_indices=rhs, sorted_indices=True)
     half = B // 2
-    want0 = kq.quantized_matmul(x[:half, 0], wd[0], None, codec)
-    want1 = kq.quantized_matmul(x[half:, 0], wd[1], None, codec)
-    assert torch.equal(y[:half, 0], want0) and torch.equal(y[half:, 0], want1)
+    want0 = kq.quantized_matmul(x[:half, 0], wd[0], None, codec).float()   # dense tile kernel: fp16-rounded weights
+    want1 = kq.quantized_matmul(x[half:, 0], wd[1], None, codec).float()
+    e0 = (y[:half, 0].float() - want0).norm() / want0.norm()
+    e1 = (y[half:, 0].float() - want1).norm() / want1.norm()
+    assert float(e0) < TOL and float(e1) < TOL
