@@ -3,15 +3,22 @@
 // path (src/kquant_cpu_decode.cpp:1299-1352) and its Metal tile kernels
 // (src/kquant_matmul.cpp:313-527).
 //
-// One CTA computes a (128*MT) x 128 output tile. Warp-specialised pipeline over
-// K in steps of 64 (one 128-byte swizzle row of 16-bit elements), 4 stages:
-//   warps 0-3  producers: (a) activations: 16-byte cp.async copies straight into
-//              the 128B-swizzled K-major tile; (b) weights: wire bytes -> fp16 in registers -> the same
-//              swizzled layout. Then fence.proxy.async + mbarrier arrive.
-//   warp 4     one thread issues tcgen05.mma (M=128, N=128, K=16, kind::f16, fp32
-//              accumulators in tensor memory), tcgen05.commit frees the stage.
-//   warps 0-3  epilogue: tcgen05.ld the accumulators (thread = output row), round
-//              once to the output type, 32-byte stores.
+// One CTA computes a (128*MT) x 128 output tile, MT in {1, 2, 4}. A weight tile
+// costs CUDA-core work to make, an activation tile costs nothing (TMA), so the
+// dequantized weight tile of each K-step (64 wide: one 128-byte swizzle row of
+// fp16) is multiplied against MT activation tiles: at MT = 4 the tensor pipe has
+// 1024 cycles of work per weight tile and the producers keep up.
+//   warps 0-7  weight producers: wire bytes -> fp16 in registers -> the
+//              128B-swizzled K-major tile of a 3-deep ring; fence.proxy.async +
+//              mbarrier arrive. Two threads per weight row, 32 weights each.
+//   warp 8     one thread issues tcgen05.mma (M=128, N=128, K=16, kind::f16, fp32
+//              accumulators in tensor memory: MT x 128 columns); tcgen05.commit
+//              hands activation slots and weight stages back.
+//   warp 9     one thread streams activation tiles [128 rows x 64] with TMA
+//              (cp.async.bulk.tensor.2d, 128B swizzle, zero fill past M and K)
+//              into an 8-slot ring, two K-steps ahead of the MMAs.
+//   warps 0-7  epilogue: tcgen05.ld the accumulators (thread = output row, warps
+//              4-7 take the upper half of the columns), round once, 32-byte stores.
 // Both operands are fp16: rounding a dequantized weight to bf16 alone would cost
 // 1.6e-3 relative error and break the 2e-3 budget together with a bf16 output
 // (fp16 costs 3e-4), and kind::f16 rejects a bf16 A operand next to an fp16 B
@@ -24,7 +31,10 @@
 // Every mbarrier wait is bounded (2 s of %globaltimer): on expiry the CTA raises
 // a flag in g_kq_device_error, stops issuing work, frees its tensor memory and
 // returns, so a logic error can never leave the GPU spinning.
+#include <cuda.h>
+
 #include <cstdio>
+#include <cstdlib>
 #include <type_traits>
 
 #include "kq_common.cuh"
@@ -34,9 +44,12 @@ namespace kq {
 
 constexpr int kBN = 128;
 constexpr int kBK = 64;
-constexpr int kStages = 4;
-constexpr int kProducerThreads = 128;
-constexpr int kGemmThreads = kProducerThreads + 32;
+constexpr int kBStages = 3;            // weight-tile ring
+constexpr int kProducerThreads = 256;  // 8 warps: two threads per weight row, 32 weights each per K-step
+constexpr int kGemmThreads = kProducerThreads + 64;
+constexpr int kMmaWarp = kProducerThreads / 32;
+constexpr int kTmaWarp = kMmaWarp + 1;
+__host__ __device__ constexpr int a_slots(int MT, int NB) { return NB == 2 ? 6 : (MT == 1 ? 4 : 8); }  // activation-tile ring
 constexpr int kTileBytes = 128 * 128;  // 128 rows x 64 16-bit elements
 
 __device__ int g_kq_device_error = 0;
@@ -82,11 +95,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
-__device__ __forceinline__ void cp_async16_zfill(void* smem, const void* gmem, int src_bytes) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(smem)), "l"(gmem), "r"(src_bytes)
-               : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;\n" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
@@ -112,6 +120,18 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar))
                : "memory");
 }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// One 2-D tile load: box {64 elements along K, 128 rows}; x = element offset along K
+// (a multiple of 64, so the 16-byte start rule holds), y = row. No multicast.
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tmap, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
+          smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
@@ -136,9 +156,9 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
 }
 
 // Instruction descriptor, kind::f16: fp32 accumulate, A format a_fmt (0 fp16, 1
-// bf16), B fp16, both K-major, M = 128, N = kBN.
-__host__ __device__ constexpr uint32_t umma_idesc(uint32_t a_fmt) {
-  return (1u << 4) | (a_fmt << 7) | (0u << 10) | ((uint32_t)(kBN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+// bf16), B fp16, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t umma_idesc(uint32_t a_fmt, int n) {
+  return (1u << 4) | (a_fmt << 7) | (0u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
 }
 
 __device__ __forceinline__ uint32_t pack_h2f(float a, float b) {
@@ -162,12 +182,13 @@ struct GemmArgs {
 };
 
 // ---- weight producers: 64 consecutive weights of one row -> eight swizzled 16-byte chunks
+// hh = 0 / 1: which 32 of the 64 weights this thread makes (chunks 4hh .. 4hh+3)
 template <int C, int A>
-__device__ __forceinline__ void produce_w_generic(const uint8_t* row, int kb, int K, uint8_t* dst_row, int r,
+__device__ __forceinline__ void produce_w_generic(const uint8_t* row, int kb, int K, uint8_t* dst_row, int r, int hh,
                                                   const IqTables& tabs) {
   constexpr int WPB = wpb_of(C), BPB = bpb_of(C);
 #pragma unroll 2
-  for (int c = 0; c < 8; c++) {
+  for (int c = 4 * hh; c < 4 * hh + 4; c++) {
     const int k = kb * kBK + c * 8;
     uint4 out = make_uint4(0u, 0u, 0u, 0u);
     if (k < K) {
@@ -189,12 +210,24 @@ __device__ __forceinline__ uint32_t two_bytes_to_h2(uint32_t two_bytes) {
   return *reinterpret_cast<const uint32_t*>(&r);
 }
 
-// q4_k: K-chunk kb is sub-block pair p = kb & 3 of superblock kb >> 2 (src/kquant_cpu_decode.cpp:177-202)
-__device__ __forceinline__ void produce_w_q4k(const uint8_t* row, int kb, uint8_t* dst_row, int r) {
+// q4_k: K-chunk kb is sub-block pair p = kb & 3 of superblock kb >> 2
+// (src/kquant_cpu_decode.cpp:177-202); thread hh of the row makes sub-block 2p + hh,
+// i.e. the low (hh = 0) or high (hh = 1) nibbles of the pair's 32 quant bytes.
+struct Q4kTileLoad {
+  uint4 hdr, q0, q1;
+};
+__device__ __forceinline__ Q4kTileLoad q4k_tile_load(const uint8_t* row, int kb) {
   const uint4* blk = reinterpret_cast<const uint4*>(row + (long long)(kb >> 2) * 144);
   const int p = kb & 3;
-  const uint4 hdr = __ldg(blk);
-  const uint4 q0 = __ldg(blk + 1 + 2 * p), q1 = __ldg(blk + 2 + 2 * p);
+  Q4kTileLoad l;
+  l.hdr = __ldg(blk);
+  l.q0 = __ldg(blk + 1 + 2 * p);
+  l.q1 = __ldg(blk + 2 + 2 * p);
+  return l;
+}
+__device__ __forceinline__ void produce_w_q4k(const Q4kTileLoad& l, int kb, uint8_t* dst_row, int r, int hh) {
+  const int p = kb & 3;
+  const uint4 hdr = l.hdr;
   const int sh = 16 * (p & 1);
   const uint32_t u0 = (hdr.y >> sh) & 0xffffu, u1 = (hdr.z >> sh) & 0xffffu, u2 = (hdr.w >> sh) & 0xffffu;
   uint32_t sc2, mn2;
@@ -205,125 +238,126 @@ __device__ __forceinline__ void produce_w_q4k(const uint8_t* row, int kb, uint8_
     sc2 = (u2 & 0x0f0fu) | ((u0 >> 2) & 0x3030u);
     mn2 = ((u2 >> 4) & 0x0f0fu) | ((u1 >> 2) & 0x3030u);
   }
-  const uint32_t sch = two_bytes_to_h2(sc2);
-  const __half2 sc = *reinterpret_cast<const __half2*>(&sch);
-  const __half2 sc_a = __low2half2(sc), sc_b = __high2half2(sc);
-  const __half2 m1024 = __float2half2_rn(-1024.f);
-  const __half2 off_a = __hmul2(sc_a, m1024), off_b = __hmul2(sc_b, m1024);
-  const __half dh = __ushort_as_half((unsigned short)(hdr.x & 0xffff));
-  const __half2 d2 = __half2half2(dh);
+  const uint32_t scb = (sc2 >> (8 * hh)) & 0xffu, mnb = (mn2 >> (8 * hh)) & 0xffu;
+  const uint32_t scm = scb | (scb << 16) | 0x64006400u;  // half2(1024 + sc, 1024 + sc)
+  const __half2 sc = __hsub2(*reinterpret_cast<const __half2*>(&scm), __float2half2_rn(1024.f));
+  const __half2 off = __hmul2(sc, __float2half2_rn(-1024.f));
+  const __half2 d2 = __half2half2(__ushort_as_half((unsigned short)(hdr.x & 0xffff)));
   const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
-  const __half2 ndm_a = __float2half2_rn(-(dmin * (float)(mn2 & 0xff)));
-  const __half2 ndm_b = __float2half2_rn(-(dmin * (float)(mn2 >> 8)));
-  const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+  const __half2 ndm = __float2half2_rn(-(dmin * (float)mnb));
+  const uint32_t w[8] = {l.q0.x, l.q0.y, l.q0.z, l.q0.w, l.q1.x, l.q1.y, l.q1.z, l.q1.w};
+  const int shn = 4 * hh;
 #pragma unroll
   for (int c = 0; c < 4; c++) {
-    uint32_t lo[4], hi[4];
+    uint32_t o[4];
 #pragma unroll
     for (int h = 0; h < 2; h++) {
-      const uint32_t W = w[2 * c + h];
-      const uint32_t l4 = W & 0x0f0f0f0fu, h4 = (W >> 4) & 0x0f0f0f0fu;
+      const uint32_t n4 = (w[2 * c + h] >> shn) & 0x0f0f0f0fu;
       // (1024 + q) pairs in natural order, then sc*q exactly, then one rounding: fma(sc*q, d, -dmin*mn)
-      lo[2 * h] = hfma2_bits(hfma2_bits(__byte_perm(l4, 0x64646464u, 0x4140), sc_a, off_a), d2, ndm_a);
-      lo[2 * h + 1] = hfma2_bits(hfma2_bits(__byte_perm(l4, 0x64646464u, 0x4342), sc_a, off_a), d2, ndm_a);
-      hi[2 * h] = hfma2_bits(hfma2_bits(__byte_perm(h4, 0x64646464u, 0x4140), sc_b, off_b), d2, ndm_b);
-      hi[2 * h + 1] = hfma2_bits(hfma2_bits(__byte_perm(h4, 0x64646464u, 0x4342), sc_b, off_b), d2, ndm_b);
+      o[2 * h] = hfma2_bits(hfma2_bits(__byte_perm(n4, 0x64646464u, 0x4140), sc, off), d2, ndm);
+      o[2 * h + 1] = hfma2_bits(hfma2_bits(__byte_perm(n4, 0x64646464u, 0x4342), sc, off), d2, ndm);
     }
-    *reinterpret_cast<uint4*>(dst_row + ((c ^ (r & 7)) << 4)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-    *reinterpret_cast<uint4*>(dst_row + (((c + 4) ^ (r & 7)) << 4)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    *reinterpret_cast<uint4*>(dst_row + (((c + 4 * hh) ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
 
 // ------------------------------------------------------------------ the kernel
 // Activations are always fp16 here (bf16 / f32 callers go through
-// convert_x_kernel first). OT: output type. MT: 128-row halves per CTA tile.
-template <int C, int A, typename OT, int MT, bool FASTQ4>
-__global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmArgs a) {
+// convert_x_kernel first) and arrive through the tensor map. OT: output type.
+// NB: 128-row halves of the weight tile (UMMA N = 128 * NB); MT * NB <= 4 (512 TMEM columns).
+template <int C, int A, typename OT, int MT, int NB, bool FASTQ4>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
   constexpr bool kHalf = std::is_same<OT, __half>::value;
-  using XT = __half;
-  constexpr int kStageBytes = (MT + 1) * kTileBytes;
+  constexpr int NA = a_slots(MT, NB);
+  constexpr int BN = kBN * NB;
+  constexpr int kBTile = NB * kTileBytes;
   constexpr bool kIq = (C == IQ4_NL || C == IQ4_XS || C == IQ2_XXS);
   extern __shared__ __align__(1024) uint8_t gemm_smem[];
   // 1024-byte alignment of the tiles is what the 128B swizzle pattern assumes
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gemm_smem) + 1023) & ~(uintptr_t)1023);
-  __shared__ uint64_t full_bar[kStages], empty_bar[kStages], accum_bar;
+  uint8_t* b_ring = tiles;                          // kBStages weight tiles
+  uint8_t* a_ring = tiles + kBStages * kBTile;      // NA activation tiles
+  __shared__ uint64_t b_full[kBStages], b_empty[kBStages], a_full[NA], a_empty[NA], accum_bar;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
   __shared__ __align__(16) uint8_t s_tabs[kIq ? kIqSmemBytes : 16];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * kBN, m0 = blockIdx.y * (128 * MT);
+  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * (128 * MT);
   const int KB = (a.K + kBK - 1) / kBK;
-  constexpr uint32_t kTmemCols = MT * kBN;  // 128 or 256: a power of two >= 32
+  const int mt_live = min(MT, (a.M - m0 + 127) / 128);  // activation tiles of this CTA that hold rows
+  constexpr uint32_t kTmemCols = MT * BN;               // 128, 256 or 512: a power of two >= 32
 
   IqTables tabs{};
   if constexpr (kIq) tabs = stage_iq_tables(s_tabs, threadIdx.x, kGemmThreads);
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; s++) {
-      mbar_init(&full_bar[s], kProducerThreads / 32);
-      mbar_init(&empty_bar[s], 1);
+    for (int s = 0; s < kBStages; s++) {
+      mbar_init(&b_full[s], kProducerThreads / 32);
+      mbar_init(&b_empty[s], 1);
+    }
+    for (int s = 0; s < NA; s++) {
+      mbar_init(&a_full[s], 1);
+      mbar_init(&a_empty[s], 1);
     }
     mbar_init(&accum_bar, 1);
     abort_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  if (warp == 4) tmem_alloc(&tmem_base_s, kTmemCols);
+  if (warp == kMmaWarp) tmem_alloc(&tmem_base_s, kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_s;
   volatile int* abort_flag = &abort_s;
 
-  if (warp < 4) {
-    // ================= producers =================
+  if (warp < kMmaWarp) {
+    // ================= weight producers =================
     const int tid = threadIdx.x;
-    const uint8_t* wrow = a.w + (long long)min(n0 + tid, a.N - 1) * a.row_bytes;
+    // NB = 1: two threads per weight row (hh = which 32 of its 64 weights); NB = 2: one thread per row
+    const int wr = NB == 1 ? (tid & 127) : tid;
+    const int hh0 = NB == 1 ? (tid >> 7) : 0;
+    const uint8_t* wrow = a.w + (long long)min(n0 + wr, a.N - 1) * a.row_bytes;
     bool ok = true;
+    Q4kTileLoad cur{};
+    if constexpr (FASTQ4) cur = q4k_tile_load(wrow, 0);
     for (int kb = 0; kb < KB && ok; kb++) {
-      const int s = kb % kStages;
-      if (kb >= kStages) ok = mbar_wait(&empty_bar[s], ((kb / kStages) & 1) ^ 1, abort_flag, 1);
+      const int s = kb % kBStages;
+      if (kb >= kBStages) ok = mbar_wait(&b_empty[s], ((kb / kBStages) & 1) ^ 1, abort_flag, 1);
       if (!ok) break;
-      uint8_t* st = tiles + s * kStageBytes;
-      // activations: MT*128 rows x 8 chunks, consecutive threads take consecutive chunks of a row
-#pragma unroll
-      for (int u = 0; u < MT * 8; u++) {
-        const int j = tid + kProducerThreads * u;
-        const int row = j >> 3, c = j & 7;
-        const int r = row & 127;
-        uint8_t* dst = st + (row >> 7) * kTileBytes + r * 128 + ((c ^ (r & 7)) << 4);
-        const int k = kb * kBK + c * 8;
-        const bool in = (m0 + row < a.M) && (k < a.K);
-        const XT* src = static_cast<const XT*>(a.x) + (long long)(in ? m0 + row : 0) * a.x_row_stride + (in ? k : 0);
-        cp_async16_zfill(dst, src, in ? 16 : 0);
-      }
-      // weights: this thread's row, 64 weights
-      uint8_t* wdst = st + MT * kTileBytes + tid * 128;
+      uint8_t* wdst = b_ring + s * kBTile + wr * 128;
       if constexpr (FASTQ4) {
-        produce_w_q4k(wrow, kb, wdst, tid);
+        Q4kTileLoad nxt = cur;
+        if (kb + 1 < KB) nxt = q4k_tile_load(wrow, kb + 1);  // next K-step's bytes are requested first
+#pragma unroll
+        for (int hh = hh0; hh < hh0 + NB; hh++) produce_w_q4k(cur, kb, wdst, wr, hh);
+        cur = nxt;
       } else {
-        produce_w_generic<C, A>(wrow, kb, a.K, wdst, tid, tabs);
+#pragma unroll
+        for (int hh = hh0; hh < hh0 + NB; hh++) produce_w_generic<C, A>(wrow, kb, a.K, wdst, wr, hh, tabs);
       }
-      cp_async_wait_all();
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&full_bar[s]);
+      if (lane == 0) mbar_arrive(&b_full[s]);
     }
     // ================= epilogue =================
     if (ok) ok = mbar_wait(&accum_bar, 0, abort_flag, 4);
     if (ok) {
       tc_fence_after();
+      const int lq = warp & 3;                   // TMEM lane quarter this warp may read
+      const int cbeg = (warp >> 2) * (BN / 2);   // warps 0-3: lower half of the columns, warps 4-7: upper half
 #pragma unroll 1
-      for (int h = 0; h < MT; h++) {
-        const int row = m0 + h * 128 + warp * 32 + lane;
+      for (int h = 0; h < mt_live; h++) {
+        const int row = m0 + h * 128 + lq * 32 + lane;
         OT* yrow = static_cast<OT*>(a.y) + (long long)row * a.y_row_stride + n0;
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(yrow) & 15) == 0);
+        const float rs = (a.row_scale && row < a.M) ? a.row_scale[row] : 1.f;
 #pragma unroll 1
-        for (int c0 = 0; c0 < kBN; c0 += 16) {
+        for (int c0 = cbeg; c0 < cbeg + BN / 2; c0 += 16) {
           uint32_t v[16];
-          tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(h * kBN + c0), v);
+          tmem_ld16(tmem_base + ((uint32_t)(lq * 32) << 16) + (uint32_t)(h * BN + c0), v);
           tmem_ld_wait();
           if (row < a.M) {
-            const float rs = a.row_scale ? a.row_scale[row] : 1.f;
             uint32_t o[8];
 #pragma unroll
             for (int i = 0; i < 8; i++) {
@@ -331,8 +365,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmArgs a)
               if constexpr (kHalf) {
                 o[i] = pack_h2f(f0, f1);
               } else {
-                __nv_bfloat162 b = __floats2bfloat162_rn(f0, f1);
-                o[i] = *reinterpret_cast<uint32_t*>(&b);
+                __nv_bfloat162 bb = __floats2bfloat162_rn(f0, f1);
+                o[i] = *reinterpret_cast<uint32_t*>(&bb);
               }
             }
             if (vec_ok && n0 + c0 + 16 <= a.N) {
@@ -347,38 +381,65 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_kernel(const GemmArgs a)
         }
       }
     }
-  } else {
+  } else if (warp == kMmaWarp) {
     // ================= MMA issuer =================
-    constexpr uint32_t idesc = umma_idesc(0u);
+    constexpr uint32_t idesc = umma_idesc(0u, BN);
     bool ok = true;
+    int t = 0;  // running activation-tile number
     for (int kb = 0; kb < KB && ok; kb++) {
-      const int s = kb % kStages;
-      ok = mbar_wait(&full_bar[s], (kb / kStages) & 1, abort_flag, 2);
+      const int s = kb % kBStages;
+      ok = mbar_wait(&b_full[s], (kb / kBStages) & 1, abort_flag, 2);
       if (!ok) break;
-      tc_fence_after();
-      if (lane == 0) {
-        const uint32_t st = smem_u32(tiles + s * kStageBytes);
-        const uint32_t bt = st + MT * kTileBytes;
-#pragma unroll
-        for (int h = 0; h < MT; h++)
+      const uint32_t bt = smem_u32(b_ring + s * kBTile);
+      for (int h = 0; h < mt_live && ok; h++, t++) {
+        const int slot = t % NA;
+        ok = mbar_wait(&a_full[slot], (t / NA) & 1, abort_flag, 16);
+        if (!ok) break;
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t at = smem_u32(a_ring + slot * kTileBytes);
 #pragma unroll
           for (int j = 0; j < kBK / 16; j++)
-            umma_f16(tmem_base + h * kBN, umma_desc_sw128(st + h * kTileBytes + j * 32), umma_desc_sw128(bt + j * 32),
-                     idesc, (kb > 0 || j > 0) ? 1u : 0u);
-        umma_commit(&empty_bar[s]);  // the stage is free once these MMAs have read it
+            umma_f16(tmem_base + h * BN, umma_desc_sw128(at + j * 32), umma_desc_sw128(bt + j * 32), idesc,
+                     (kb > 0 || j > 0) ? 1u : 0u);
+          umma_commit(&a_empty[slot]);  // the slot is free once these MMAs have read it
+        }
+        __syncwarp();
       }
+      if (ok && lane == 0) umma_commit(&b_empty[s]);
       __syncwarp();
     }
     if (lane == 0) umma_commit(&accum_bar);  // also on the abort path: lets the wait below see the MMAs drain
     __syncwarp();
     if (!ok) mbar_wait(&accum_bar, 0, abort_flag, 8);
+  } else {
+    // ================= activation loader (TMA) =================
+    bool ok = true;
+    int t = 0;
+    for (int kb = 0; kb < KB && ok; kb++) {
+      for (int h = 0; h < mt_live && ok; h++, t++) {
+        const int slot = t % NA;
+        if (t >= NA) ok = mbar_wait(&a_empty[slot], ((t / NA) & 1) ^ 1, abort_flag, 32);
+        if (!ok) break;
+        if (lane == 0) {
+          mbar_expect_tx(&a_full[slot], kTileBytes);
+          tma_load_2d(a_ring + slot * kTileBytes, &tmap_x, kb * kBK, m0 + h * 128, &a_full[slot]);
+        }
+        __syncwarp();
+      }
+    }
+    // In-flight loads must have landed before the CTA may exit: wait (bounded) for the last ones.
+    if (ok && t > 0) {
+      const int first = t > NA ? t - NA : 0;
+      for (int u = first; u < t; u++)
+        if (!mbar_wait(&a_full[u % NA], (u / NA) & 1, abort_flag, 64)) break;
+    }
   }
 
   // ================= teardown =================
-  cp_async_wait_all();
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
@@ -431,10 +492,40 @@ size_t gemm_workspace_bytes(int x_dtype, long long rows, int K) {
 }
 
 // ------------------------------------------------------------------ launch
-template <int C, int A, typename OT, int MT, bool FASTQ4>
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// Tensor map of the fp16 activations [M, K] (row stride in elements): boxes of 64 x 128, 128B swizzle.
+static cudaError_t make_x_map(CUtensorMap* map, const void* x, long long x_row_stride, int M, int K) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return cudaErrorNotSupported;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
+  const cuuint64_t strides[1] = {(cuuint64_t)x_row_stride * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kBK, 128};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+template <int C, int A, typename OT, int MT, int NB, bool FASTQ4>
 static cudaError_t launch_g(const GemmArgs& a, cudaStream_t st) {
-  auto kern = gemm_kernel<C, A, OT, MT, FASTQ4>;
-  const size_t dyn = (size_t)kStages * (MT + 1) * kTileBytes + 1024;
+  auto kern = gemm_kernel<C, A, OT, MT, NB, FASTQ4>;
+  const size_t dyn = (size_t)(kBStages * NB + a_slots(MT, NB)) * kTileBytes + 1024;
   static bool attr_set[16] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -443,16 +534,38 @@ static cudaError_t launch_g(const GemmArgs& a, cudaStream_t st) {
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
-  const dim3 grid((a.N + kBN - 1) / kBN, (a.M + 128 * MT - 1) / (128 * MT));
-  kern<<<grid, kGemmThreads, dyn, st>>>(a);
+  alignas(64) CUtensorMap map;
+  cudaError_t e = make_x_map(&map, a.x, a.x_row_stride, a.M, a.K);
+  if (e != cudaSuccess) return e;
+  const dim3 grid((a.N + kBN * NB - 1) / (kBN * NB), (a.M + 128 * MT - 1) / (128 * MT));
+  kern<<<grid, kGemmThreads, dyn, st>>>(a, map);
   return cudaGetLastError();
 }
 
 template <int C, int A, bool FASTQ4>
 static cudaError_t launch_shape(bool out_half, const GemmArgs& a, cudaStream_t st) {
-  const bool mt2 = a.M > 128;
-  if (out_half) return mt2 ? launch_g<C, A, __half, 2, FASTQ4>(a, st) : launch_g<C, A, __half, 1, FASTQ4>(a, st);
-  return mt2 ? launch_g<C, A, __nv_bfloat16, 2, FASTQ4>(a, st) : launch_g<C, A, __nv_bfloat16, 1, FASTQ4>(a, st);
+  // Tile shapes (rows x columns): 512 x 128 amortises the weight dequantization best,
+  // 256 x 256 halves the activation traffic out of L2; smaller ones fill the GPU at small M.
+  // KQ_GEMM_TILE=1|2|4|22 forces 128x128 / 256x128 / 512x128 / 256x256 (an A/B lever).
+  const long long n_tiles = (a.N + kBN - 1) / kBN;
+  int mt = a.M > 256 ? 4 : (a.M > 128 ? 2 : 1);
+  if (mt == 4 && n_tiles * ((a.M + 511) / 512) < 148) mt = 2;
+  // the q4_k producer is cheap enough to feed a 256-column tile; decode8-based producers are not
+  if (FASTQ4 && a.M > 256) mt = 22;
+  if (const char* env = std::getenv("KQ_GEMM_TILE")) {
+    const int v = std::atoi(env);
+    if (v == 1 || v == 2 || v == 4 || v == 22) mt = v;
+  }
+#define KQ_TILE(OT)                                              \
+  do {                                                           \
+    if (mt == 22) return launch_g<C, A, OT, 2, 2, FASTQ4>(a, st); \
+    if (mt == 4) return launch_g<C, A, OT, 4, 1, FASTQ4>(a, st);  \
+    if (mt == 2) return launch_g<C, A, OT, 2, 1, FASTQ4>(a, st);  \
+    return launch_g<C, A, OT, 1, 1, FASTQ4>(a, st);               \
+  } while (0)
+  if (out_half) KQ_TILE(__half);
+  KQ_TILE(__nv_bfloat16);
+#undef KQ_TILE
 }
 
 template <int C, int NAT>
