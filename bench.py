@@ -61,6 +61,7 @@ def parse():
     ap.add_argument("--m", type=int, default=1, help="activation rows (decode batch), <= 16")
     ap.add_argument("--cpu-sample", type=int, default=16, help="matrices in the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the secondary cells (prefill, dequantize, MoE)")
     return ap.parse_args()
 
 
@@ -197,6 +198,70 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def measured_tflops():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["bf16_tflops"]), "measured"
+        except Exception:
+            pass
+    return 1590.0, "fallback"
+
+
+def extra_cells(dev):
+    """Secondary cells of the metric, single GPU, CUDA events, 5 timed repeats after 2 warm-ups:
+    prefill TFLOP/s (config 3), dequantize GB/s (config 2, q4_k), MoE tokens/s (config 4)."""
+    import torch
+
+    import mlx_kquant_b200 as kq
+    from mlx_kquant_b200.moe import moe_glu, route_topk
+    from mlx_kquant_b200.synth import random_wire
+
+    def timed(fn, reps=5):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e-3
+
+    out = {}
+    peak_tf, kind = measured_tflops()
+    hbm, _ = measured_peak()
+    N, K = 14336, 4096
+    for codec in ("q4_k", "q6_k"):
+        W = random_wire(codec, N, K, seed=3, device=dev)
+        for M in (512, 8192):
+            x = torch.randn(M, K, device=dev).to(torch.bfloat16)
+            t = timed(lambda: kq.quantized_matmul(x, W, None, codec))
+            tf = 2.0 * M * N * K / t / 1e12
+            out[f"prefill_{codec}_m{M}_bf16"] = {"tflops": tf, "ms": t * 1e3, "frac_of_bf16_peak": tf / peak_tf,
+                                                  "peak_kind": kind}
+    W = random_wire("q4_k", N, K, seed=4, device=dev, lead=(4,))       # 4 x 150 MB of traffic > L2
+    def dq():
+        for i in range(4):
+            kq.dequantize(W[i], None, "q4_k", torch.float16)
+    t = timed(dq) / 4
+    gbs = (W[0].numel() + N * K * 2) / t / 1e9
+    out["dequant_q4k_f16"] = {"GBps": gbs, "frac_of_hbm_peak": gbs / hbm}
+    # MoE: 128 experts, hidden 2048, expert FFN 768, top-8
+    E, H, F, k = 128, 2048, 768, 8
+    wg = random_wire("q4_k", F, H, seed=5, device=dev, lead=(E,))
+    wu = random_wire("q4_k", F, H, seed=6, device=dev, lead=(E,))
+    wd = random_wire("q4_k", H, F, seed=7, device=dev, lead=(E,))
+    g = torch.Generator(device="cpu").manual_seed(3000)
+    for T in (1, 64, 4096):
+        x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(dev)
+        ids, probs = route_topk(torch.randn(T, E, generator=g).to(dev), k)
+        t = timed(lambda: moe_glu(x, wg, wu, wd, "q4_k", ids, probs), reps=3)
+        out[f"moe_glu_q4k_T{T}"] = {"tokens_per_s": T / t, "ms": t * 1e3}
+    return out
+
+
 def run_b200(args):
     import torch
     import torch.distributed as dist
@@ -328,6 +393,11 @@ def run_b200(args):
             "cpu_baseline": cpu,
             "clocks": clocks,
         }
+        if world == 1 and not args.no_extra:
+            try:
+                line["extra"] = extra_cells(dev)
+            except Exception as e:
+                line["extra"] = {"error": str(e)[:200]}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
