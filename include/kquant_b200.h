@@ -106,10 +106,13 @@ KQ_API int kq_device_error_flags(int* flags, int clear);
  * arrays of n_entries, already broadcast together; y: [n_entries, M, N] dense.
  * rhs_sorted != 0 promises rhs is non-decreasing (the reference's right_sorted
  * flag); it is a hint only, results do not depend on it.
- * workspace: at least kq_gather_qmm_workspace_bytes(n_entries, M, n_experts)
+ * workspace: at least kq_gather_qmm_workspace_bytes(n_entries, M, n_experts, K)
  * bytes of device memory, 256-byte aligned, private to this call until it
- * completes on the stream. */
-KQ_API size_t kq_gather_qmm_workspace_bytes(long long n_entries, int M, int n_experts);
+ * completes on the stream. Decode-sized calls need a few hundred KB; prefill-sized
+ * ones (32 or more rows per expert on average) also hold an expert-sorted fp16 copy
+ * of the routed activations (n_entries * M * K * 2 bytes) for the tensor-core kernel.
+ * K = 0 returns the decode-regime size, which does not depend on K. */
+KQ_API size_t kq_gather_qmm_workspace_bytes(long long n_entries, int M, int n_experts, int K);
 KQ_API int kq_gather_qmm(const void* x, int x_dtype, long long x_batch, int M, int K, const void* w, int n_experts,
                   long long w_expert_stride_bytes, size_t w_row_bytes, int N, const char* kquant_type,
                   const uint32_t* lhs_indices, const uint32_t* rhs_indices, long long n_entries, int transpose,
@@ -124,8 +127,9 @@ KQ_API int kq_gather_qmm(const void* x, int x_dtype, long long x_batch, int M, i
  * allocations afterwards, or a serving loop that must never pay cudaMalloc's
  * device-wide synchronisation. Nothing here calls cudaMalloc, cudaFree or an
  * allocating library routine.
- *  - Limit: problems whose kq_gather_qmm_workspace_bytes() exceeds
- *    KQ_GATHER_STATIC_WS_BYTES are rejected with KQ_ERR_INVALID_ARGUMENT (for
+ *  - Always runs the decode regime, whatever the size of the call.
+ *  - Limit: problems whose kq_gather_qmm_workspace_bytes(n_entries, M, n_experts, 0)
+ *    exceeds KQ_GATHER_STATIC_WS_BYTES are rejected with KQ_ERR_INVALID_ARGUMENT (for
  *    M = 1 and 128 experts that is about 75 000 index entries per call).
  *  - The first call on each device looks up the array's device address; make
  *    that first call outside any stream capture.

@@ -164,15 +164,28 @@ int kq_device_error_flags(int* flags, int clear) {
   return KQ_OK;
 }
 
-size_t kq_gather_qmm_workspace_bytes(long long n_entries, int M, int n_experts) {
-  if (n_entries < 0 || M <= 0 || n_experts <= 0) return 0;
-  return kq::gather_layout(n_entries, M, n_experts).total;
+size_t kq_gather_qmm_workspace_bytes(long long n_entries, int M, int n_experts, int K) {
+  if (n_entries < 0 || M <= 0 || n_experts <= 0 || K < 0) return 0;
+  return kq::gather_layout(n_entries, M, n_experts, K).total;
 }
 
 int kq_gather_qmm(const void* x, int x_dtype, long long x_batch, int M, int K, const void* w, int n_experts,
                   long long w_expert_stride_bytes, size_t w_row_bytes, int N, const char* kquant_type,
                   const uint32_t* lhs_indices, const uint32_t* rhs_indices, long long n_entries, int transpose,
                   int rhs_sorted, void* y, void* workspace, size_t workspace_bytes, void* stream) {
+  return kq::gather_qmm_entry(x, x_dtype, x_batch, M, K, w, n_experts, w_expert_stride_bytes, w_row_bytes, N,
+                              kquant_type, lhs_indices, rhs_indices, n_entries, transpose, rhs_sorted, y, workspace,
+                              workspace_bytes, stream, /*allow_grouped=*/true);
+}
+
+}  // extern "C"
+
+namespace kq {
+int gather_qmm_entry(const void* x, int x_dtype, long long x_batch, int M, int K, const void* w, int n_experts,
+                     long long w_expert_stride_bytes, size_t w_row_bytes, int N, const char* kquant_type,
+                     const uint32_t* lhs_indices, const uint32_t* rhs_indices, long long n_entries, int transpose,
+                     int rhs_sorted, void* y, void* workspace, size_t workspace_bytes, void* stream,
+                     bool allow_grouped) {
   (void)rhs_sorted;
   (void)x_batch;
   const int ci = find_codec(kquant_type);
@@ -203,7 +216,7 @@ int kq_gather_qmm(const void* x, int x_dtype, long long x_batch, int M, int K, c
   const size_t xe = x_dtype == KQ_F32 ? 4 : 2;
   if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || ((size_t)K * xe) % 16 != 0)
     return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmm] x rows must be 16-byte aligned.");
-  const size_t need = kq::gather_layout(n_entries, M, n_experts).total;
+  const size_t need = kq::gather_layout(n_entries, M, n_experts, allow_grouped ? K : 0).total;
   if (workspace == nullptr || workspace_bytes < need)
     return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmm] workspace too small: %zu bytes given, %zu needed.",
                 workspace_bytes, need);
@@ -211,9 +224,8 @@ int kq_gather_qmm(const void* x, int x_dtype, long long x_batch, int M, int K, c
     return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmm] workspace must be 256-byte aligned.");
   cudaError_t e = kq::launch_gather(ci, x_dtype, x, M, K, static_cast<const uint8_t*>(w), n_experts,
                                     w_expert_stride_bytes, (long long)w_row_bytes, N, lhs_indices, rhs_indices,
-                                    n_entries, y, workspace, static_cast<cudaStream_t>(stream));
+                                    n_entries, y, workspace, allow_grouped, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail("gather_qmm", e);
   return KQ_OK;
 }
-
-}  // extern "C"
+}  // namespace kq

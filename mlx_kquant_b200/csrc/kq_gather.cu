@@ -9,7 +9,11 @@
 //   2. one-CTA exclusive scan -> entry offsets and task offsets per expert
 //   3. scatter of entry ids into expert order
 //   4. task build: each expert's c*M rows are cut into GemvTask slices of 16
-//   5. the skinny-M kernel runs over (row tile, task)
+//   5. the skinny-M kernel runs over (row tile, k-slice, task)
+// Prefill-sized calls (on average 32 or more rows per expert) take the tensor-core
+// route instead: steps 1-3, then a tile list of 256 sorted rows per entry, an
+// expert-sorted fp16 copy of the activations (the tile kernel streams it with TMA),
+// and the tcgen05 tile kernel with a row-index scatter in its epilogue.
 // All of it lives in a caller-provided workspace laid out by gather_layout().
 #include <cstdio>
 #include <mutex>
@@ -22,7 +26,13 @@ namespace kq {
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-GatherLayout gather_layout(long long n_entries, int M, int n_experts) {
+// Which regime a call takes is decided on the host from sizes alone (no device round trip).
+static bool use_grouped(long long n_entries, int M, int n_experts, int K) {
+  const long long rows = n_entries * (long long)M;
+  return K > 0 && (K % 8) == 0 && rows >= 512 && rows >= 32LL * n_experts && rows < (1LL << 31);
+}
+
+GatherLayout gather_layout(long long n_entries, int M, int n_experts, int K) {
   GatherLayout L;
   const long long rows = n_entries * (long long)M;
   // every task but at most one per expert is full, and no task is empty
@@ -30,6 +40,8 @@ GatherLayout gather_layout(long long n_entries, int M, int n_experts) {
   if (mt > rows) mt = rows;
   if (mt < 1) mt = 1;
   L.max_tasks = mt;
+  L.grouped = use_grouped(n_entries, M, n_experts, K);
+  L.max_tiles = rows / kGroupedTileRows + n_experts;
   size_t off = 0;
   L.counts = off;    off = align_up(off + sizeof(int) * (size_t)n_experts, 256);
   L.cursor = off;    off = align_up(off + sizeof(int) * (size_t)n_experts, 256);
@@ -37,7 +49,16 @@ GatherLayout gather_layout(long long n_entries, int M, int n_experts) {
   L.task_base = off; off = align_up(off + sizeof(int) * ((size_t)n_experts + 1), 256);
   L.n_tasks = off;   off = align_up(off + sizeof(int), 256);
   L.order = off;     off = align_up(off + sizeof(int) * (size_t)(n_entries > 0 ? n_entries : 1), 256);
-  L.tasks = off;     off = align_up(off + sizeof(GemvTask) * (size_t)mt, 256);
+  L.xh = L.row_scale = L.yrow = L.tiles = 0;
+  if (L.grouped) {
+    L.tasks = off;  // unused in this regime
+    L.tiles = off;     off = align_up(off + 16 * (size_t)L.max_tiles, 256);
+    L.yrow = off;      off = align_up(off + sizeof(int) * (size_t)rows, 256);
+    L.row_scale = off; off = align_up(off + sizeof(float) * (size_t)rows, 256);
+    L.xh = off;        off = align_up(off + 2 * (size_t)rows * (size_t)K, 256);
+  } else {
+    L.tasks = off;     off = align_up(off + sizeof(GemvTask) * (size_t)mt, 256);
+  }
   L.total = off;
   return L;
 }
@@ -50,10 +71,10 @@ __global__ void gather_hist_kernel(const uint32_t* __restrict__ rhs, long long n
   }
 }
 
-// One CTA: exclusive scans of counts (entry offsets) and of ceil(count*M/16)
-// (task offsets). n_experts is small (hundreds), a serial chunked scan is enough.
-__global__ void gather_scan_kernel(const int* __restrict__ counts, int n_experts, int M, int* offsets, int* task_base,
-                                   int* n_tasks) {
+// One CTA: exclusive scans of counts (entry offsets) and of ceil(count*M/unit)
+// (task or tile offsets; unit = rows per task or tile). n_experts is small (hundreds), a serial chunked scan is enough.
+__global__ void gather_scan_kernel(const int* __restrict__ counts, int n_experts, int M, int unit, int* offsets,
+                                   int* task_base, int* n_tasks) {
   __shared__ int s_cnt[1024], s_tsk[1024];
   __shared__ int carry_c, carry_t;
   if (threadIdx.x == 0) carry_c = carry_t = 0;
@@ -61,7 +82,7 @@ __global__ void gather_scan_kernel(const int* __restrict__ counts, int n_experts
   for (int base = 0; base < n_experts; base += 1024) {
     const int e = base + threadIdx.x;
     const int c = e < n_experts ? counts[e] : 0;
-    const int tk = (int)(((long long)c * M + 15) / 16);
+    const int tk = (int)(((long long)c * M + unit - 1) / unit);
     s_cnt[threadIdx.x] = c;
     s_tsk[threadIdx.x] = tk;
     __syncthreads();
@@ -137,11 +158,31 @@ __global__ void gather_tasks_kernel(const uint8_t* w, long long expert_stride, i
   }
 }
 
+// grid.x = expert: the expert's c*M sorted rows cut into tiles of kGroupedTileRows
+struct GatherTile {
+  int expert, row_start, rows, pad;
+};
+__global__ void gather_tiles_kernel(int M, const int* __restrict__ offsets, const int* __restrict__ tile_base,
+                                    GatherTile* tiles) {
+  const int e = blockIdx.x;
+  const long long start = (long long)offsets[e] * M, rows = (long long)(offsets[e + 1] - offsets[e]) * M;
+  const int nt = (int)((rows + kGroupedTileRows - 1) / kGroupedTileRows);
+  for (int j = threadIdx.x; j < nt; j += blockDim.x) {
+    GatherTile t;
+    t.expert = e;
+    t.row_start = (int)(start + (long long)j * kGroupedTileRows);
+    t.rows = (int)min((long long)kGroupedTileRows, rows - (long long)j * kGroupedTileRows);
+    t.pad = 0;
+    tiles[tile_base[e] + j] = t;
+  }
+}
+
 cudaError_t launch_gather(int codec, int x_dtype, const void* x, int M, int K, const uint8_t* w, int n_experts,
                           long long expert_stride, long long row_bytes, int N, const uint32_t* lhs,
-                          const uint32_t* rhs, long long n_entries, void* y, void* workspace, cudaStream_t st) {
+                          const uint32_t* rhs, long long n_entries, void* y, void* workspace, bool allow_grouped,
+                          cudaStream_t st) {
   if (n_entries <= 0 || M <= 0) return cudaSuccess;
-  const GatherLayout L = gather_layout(n_entries, M, n_experts);
+  const GatherLayout L = gather_layout(n_entries, M, n_experts, allow_grouped ? K : 0);
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   int* counts = reinterpret_cast<int*>(ws + L.counts);
   int* cursor = reinterpret_cast<int*>(ws + L.cursor);
@@ -149,15 +190,28 @@ cudaError_t launch_gather(int codec, int x_dtype, const void* x, int M, int K, c
   int* task_base = reinterpret_cast<int*>(ws + L.task_base);
   int* n_tasks = reinterpret_cast<int*>(ws + L.n_tasks);
   int* order = reinterpret_cast<int*>(ws + L.order);
-  GemvTask* tasks = reinterpret_cast<GemvTask*>(ws + L.tasks);
 
   cudaError_t err = cudaMemsetAsync(ws + L.counts, 0, L.offsets - L.counts, st);  // counts + cursor
   if (err != cudaSuccess) return err;
   const int th = 256;
   const unsigned nb = (unsigned)((n_entries + th - 1) / th);
   gather_hist_kernel<<<nb, th, 0, st>>>(rhs, n_entries, n_experts, counts);
-  gather_scan_kernel<<<1, 1024, 0, st>>>(counts, n_experts, M, offsets, task_base, n_tasks);
+  gather_scan_kernel<<<1, 1024, 0, st>>>(counts, n_experts, M, L.grouped ? kGroupedTileRows : 16, offsets, task_base,
+                                         n_tasks);
   gather_scatter_kernel<<<nb, th, 0, st>>>(rhs, n_entries, n_experts, offsets, cursor, order);
+
+  if (L.grouped) {
+    GatherTile* tiles = reinterpret_cast<GatherTile*>(ws + L.tiles);
+    gather_tiles_kernel<<<n_experts, 64, 0, st>>>(M, offsets, task_base, tiles);
+    if ((err = cudaGetLastError()) != cudaSuccess) return err;
+    if (L.max_tiles > 65535) return cudaErrorInvalidConfiguration;
+    return launch_gemm_grouped(codec, x_dtype, x, M, K, w, expert_stride, row_bytes, N, lhs, order,
+                               n_entries * (long long)M, y, reinterpret_cast<__half*>(ws + L.xh),
+                               reinterpret_cast<float*>(ws + L.row_scale), reinterpret_cast<int*>(ws + L.yrow), tiles,
+                               n_tasks, (int)L.max_tiles, st);
+  }
+
+  GemvTask* tasks = reinterpret_cast<GemvTask*>(ws + L.tasks);
   gather_tasks_kernel<<<n_experts, 256, 0, st>>>(w, expert_stride, M, lhs, offsets, task_base, order, tasks);
   if ((err = cudaGetLastError()) != cudaSuccess) return err;
 
@@ -174,7 +228,7 @@ cudaError_t launch_gather(int codec, int x_dtype, const void* x, int M, int K, c
   a.M = 0;
   a.n_tasks_dev = n_tasks;
   a.max_m = (int)(n_entries * M < 16 ? n_entries * M : 16);
-  // grid.y is capped at 65535: cover the task list in slices
+  // grid.z is capped at 65535: cover the task list in slices
   for (long long t0 = 0; t0 < L.max_tasks; t0 += 65535) {
     a.tasks = tasks + t0;
     a.n_tasks = (int)((L.max_tasks - t0) < 65535 ? (L.max_tasks - t0) : 65535);
@@ -224,7 +278,9 @@ extern "C" int kq_gather_qmm_noalloc(const void* x, int x_dtype, long long x_bat
                                      const char* kquant_type, const uint32_t* lhs_indices,
                                      const uint32_t* rhs_indices, long long n_entries, int transpose, int rhs_sorted,
                                      void* y, void* stream) {
-  const size_t need = kq_gather_qmm_workspace_bytes(n_entries, M, n_experts);
+  // This entry point always takes the decode regime (the skinny kernel over task lists), whose
+  // scratch does not grow with K; K = 0 asks for that layout.
+  const size_t need = kq_gather_qmm_workspace_bytes(n_entries, M, n_experts, 0);
   if (need > KQ_GATHER_STATIC_WS_BYTES) {
     char msg[256];
     std::snprintf(msg, sizeof(msg),
@@ -242,8 +298,8 @@ extern "C" int kq_gather_qmm_noalloc(const void* x, int x_dtype, long long x_bat
     return kq::set_error(KQ_ERR_CUDA, msg);
   }
   // From here on it is the ordinary path; it clears the counters it needs on the stream.
-  return kq_gather_qmm(x, x_dtype, x_batch, M, K, w, n_experts, w_expert_stride_bytes, w_row_bytes, N, kquant_type,
-                       lhs_indices, rhs_indices, n_entries, transpose, rhs_sorted, y, ws, KQ_GATHER_STATIC_WS_BYTES,
-                       stream);
+  return kq::gather_qmm_entry(x, x_dtype, x_batch, M, K, w, n_experts, w_expert_stride_bytes, w_row_bytes, N,
+                              kquant_type, lhs_indices, rhs_indices, n_entries, transpose, rhs_sorted, y, ws,
+                              KQ_GATHER_STATIC_WS_BYTES, stream, /*allow_grouped=*/false);
 }
 

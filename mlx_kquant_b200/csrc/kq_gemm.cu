@@ -170,6 +170,10 @@ __device__ __forceinline__ uint32_t hfma2_bits(uint32_t a, __half2 b, __half2 c)
   return *reinterpret_cast<uint32_t*>(&r);
 }
 
+struct GemmTile {
+  int expert, row_start, rows, pad;
+};
+
 struct GemmArgs {
   const void* x;
   long long x_row_stride;
@@ -179,6 +183,11 @@ struct GemmArgs {
   long long row_bytes;
   int M, N, K;
   const float* row_scale;  // per-row factor applied in the epilogue, or nullptr
+  // grouped (mixture-of-experts) mode: CTA row tiles come from a device-built list
+  const GemmTile* tiles;       // nullptr = dense
+  const int* n_tiles_dev;      // valid entries of `tiles`
+  long long w_expert_stride;   // bytes between expert matrices
+  const int* yrow;             // output row of each (expert-sorted) activation row
 };
 
 // ---- weight producers: 64 consecutive weights of one row -> eight swizzled 16-byte chunks
@@ -284,9 +293,18 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
   __shared__ __align__(16) uint8_t s_tabs[kIq ? kIqSmemBytes : 16];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * (128 * MT);
+  const int n0 = blockIdx.x * BN;
+  int m0 = blockIdx.y * (128 * MT), m_end = a.M;
+  const uint8_t* wbase = a.w;
+  if (a.tiles != nullptr) {
+    if ((int)blockIdx.y >= *a.n_tiles_dev) return;  // whole CTA, before any barrier or allocation
+    const GemmTile t = a.tiles[blockIdx.y];
+    m0 = t.row_start;
+    m_end = t.row_start + t.rows;
+    wbase += (long long)t.expert * a.w_expert_stride;
+  }
   const int KB = (a.K + kBK - 1) / kBK;
-  const int mt_live = min(MT, (a.M - m0 + 127) / 128);  // activation tiles of this CTA that hold rows
+  const int mt_live = min(MT, (m_end - m0 + 127) / 128);  // activation tiles of this CTA that hold rows
   constexpr uint32_t kTmemCols = MT * BN;               // 128, 256 or 512: a power of two >= 32
 
   IqTables tabs{};
@@ -317,7 +335,7 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
     // NB = 1: two threads per weight row (hh = which 32 of its 64 weights); NB = 2: one thread per row
     const int wr = NB == 1 ? (tid & 127) : tid;
     const int hh0 = NB == 1 ? (tid >> 7) : 0;
-    const uint8_t* wrow = a.w + (long long)min(n0 + wr, a.N - 1) * a.row_bytes;
+    const uint8_t* wrow = wbase + (long long)min(n0 + wr, a.N - 1) * a.row_bytes;
     bool ok = true;
     Q4kTileLoad cur{};
     if constexpr (FASTQ4) cur = q4k_tile_load(wrow, 0);
@@ -349,15 +367,17 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
 #pragma unroll 1
       for (int h = 0; h < mt_live; h++) {
         const int row = m0 + h * 128 + lq * 32 + lane;
-        OT* yrow = static_cast<OT*>(a.y) + (long long)row * a.y_row_stride + n0;
+        const bool live = row < m_end;
+        const long long orow = (live && a.yrow) ? a.yrow[row] : row;
+        OT* yrow = static_cast<OT*>(a.y) + orow * a.y_row_stride + n0;
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(yrow) & 15) == 0);
-        const float rs = (a.row_scale && row < a.M) ? a.row_scale[row] : 1.f;
+        const float rs = (a.row_scale && live) ? a.row_scale[row] : 1.f;
 #pragma unroll 1
         for (int c0 = cbeg; c0 < cbeg + BN / 2; c0 += 16) {
           uint32_t v[16];
           tmem_ld16(tmem_base + ((uint32_t)(lq * 32) << 16) + (uint32_t)(h * BN + c0), v);
           tmem_ld_wait();
-          if (row < a.M) {
+          if (live) {
             uint32_t o[8];
 #pragma unroll
             for (int i = 0; i < 8; i++) {
@@ -453,35 +473,53 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
 // row is divided by a power of two 2^e (e = 0 for every row whose largest
 // magnitude is below 32768, i.e. practically always) and the factor is handed to
 // the epilogue: nothing saturates, nothing is rounded twice.
+// Gather mode (order != nullptr): output row r is activation row
+// lhs[order[r / M]] * M + r % M of x, and yrow[r] = order[r / M] * M + r % M says where
+// its result goes; this is the expert-sorted copy the grouped kernel streams with TMA.
 template <typename XT>
-__global__ void __launch_bounds__(256) convert_x_kernel(const XT* __restrict__ x, long long x_row_stride, int K,
-                                                        __half* __restrict__ xh, float* __restrict__ row_scale) {
+__global__ void __launch_bounds__(256)
+convert_x_kernel(const XT* __restrict__ x, long long x_row_stride, int K, __half* __restrict__ xh,
+                 float* __restrict__ row_scale, const int* __restrict__ order, const uint32_t* __restrict__ lhs, int M,
+                 int* __restrict__ yrow) {
   const long long row = blockIdx.x;
-  const XT* xr = x + row * x_row_stride;
-  __shared__ float s_max[8];
-  float mx = 0.f;
-  for (int k = threadIdx.x; k < K; k += 256) {
-    float v;
-    if constexpr (sizeof(XT) == 2) v = __bfloat162float(xr[k]);
-    else v = __bfloat162float(__float2bfloat16_rn(xr[k]));
-    v = fabsf(v);
-    if (v < INFINITY) mx = fmaxf(mx, v);  // inf / nan propagate on their own
+  long long src_row = row;
+  if (order != nullptr) {
+    const int entry = order[row / M], i = (int)(row % M);
+    src_row = (long long)lhs[entry] * M + i;
+    if (threadIdx.x == 0) yrow[row] = entry * M + i;
   }
-  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-  if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = mx;
-  __syncthreads();
-  mx = s_max[0];
-  for (int i = 1; i < 8; i++) mx = fmaxf(mx, s_max[i]);
-  int e = 0;
-  if (mx >= 32768.f) e = ilogbf(mx) - 14;  // largest magnitude lands in [16384, 32768)
-  const float down = ldexpf(1.f, -e);
-  if (threadIdx.x == 0) row_scale[row] = ldexpf(1.f, e);
+  const XT* xr = x + src_row * x_row_stride;
   __half* o = xh + row * (long long)K;
-  for (int k = threadIdx.x; k < K; k += 256) {
-    float v;
-    if constexpr (sizeof(XT) == 2) v = __bfloat162float(xr[k]);
-    else v = __bfloat162float(__float2bfloat16_rn(xr[k]));
-    o[k] = __float2half_rn(v * down);
+  if constexpr (std::is_same<XT, __half>::value) {
+    for (int k = threadIdx.x * 8; k < K; k += 256 * 8)
+      *reinterpret_cast<uint4*>(o + k) = __ldg(reinterpret_cast<const uint4*>(xr + k));
+    if (threadIdx.x == 0) row_scale[row] = 1.f;
+    return;
+  } else {
+    __shared__ float s_max[8];
+    float mx = 0.f;
+    for (int k = threadIdx.x; k < K; k += 256) {
+      float v;
+      if constexpr (sizeof(XT) == 2) v = __bfloat162float(xr[k]);
+      else v = __bfloat162float(__float2bfloat16_rn(xr[k]));
+      v = fabsf(v);
+      if (v < INFINITY) mx = fmaxf(mx, v);  // inf / nan propagate on their own
+    }
+    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = mx;
+    __syncthreads();
+    mx = s_max[0];
+    for (int i = 1; i < 8; i++) mx = fmaxf(mx, s_max[i]);
+    int e = 0;
+    if (mx >= 32768.f) e = ilogbf(mx) - 14;  // largest magnitude lands in [16384, 32768)
+    const float down = ldexpf(1.f, -e);
+    if (threadIdx.x == 0) row_scale[row] = ldexpf(1.f, e);
+    for (int k = threadIdx.x; k < K; k += 256) {
+      float v;
+      if constexpr (sizeof(XT) == 2) v = __bfloat162float(xr[k]);
+      else v = __bfloat162float(__float2bfloat16_rn(xr[k]));
+      o[k] = __float2half_rn(v * down);
+    }
   }
 }
 
@@ -523,7 +561,7 @@ static cudaError_t make_x_map(CUtensorMap* map, const void* x, long long x_row_s
 }
 
 template <int C, int A, typename OT, int MT, int NB, bool FASTQ4>
-static cudaError_t launch_g(const GemmArgs& a, cudaStream_t st) {
+static cudaError_t launch_g(const GemmArgs& a, cudaStream_t st, int grid_y = 0) {
   auto kern = gemm_kernel<C, A, OT, MT, NB, FASTQ4>;
   const size_t dyn = (size_t)(kBStages * NB + a_slots(MT, NB)) * kTileBytes + 1024;
   static bool attr_set[16] = {};
@@ -537,7 +575,7 @@ static cudaError_t launch_g(const GemmArgs& a, cudaStream_t st) {
   alignas(64) CUtensorMap map;
   cudaError_t e = make_x_map(&map, a.x, a.x_row_stride, a.M, a.K);
   if (e != cudaSuccess) return e;
-  const dim3 grid((a.N + kBN * NB - 1) / (kBN * NB), (a.M + 128 * MT - 1) / (128 * MT));
+  const dim3 grid((a.N + kBN * NB - 1) / (kBN * NB), grid_y > 0 ? grid_y : (a.M + 128 * MT - 1) / (128 * MT));
   kern<<<grid, kGemmThreads, dyn, st>>>(a, map);
   return cudaGetLastError();
 }
@@ -587,13 +625,19 @@ cudaError_t launch_gemm(int codec, int x_dtype, const void* x, long long x_row_s
   a.N = N;
   a.K = K;
   a.row_scale = nullptr;
+  a.tiles = nullptr;
+  a.n_tiles_dev = nullptr;
+  a.w_expert_stride = 0;
+  a.yrow = nullptr;
   if (x_dtype != F16) {
     __half* xh = static_cast<__half*>(workspace);
     float* rs = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + (((size_t)M * K * 2 + 255) & ~(size_t)255));
     if (x_dtype == BF16)
-      convert_x_kernel<__nv_bfloat16><<<M, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), x_row_stride, K, xh, rs);
+      convert_x_kernel<__nv_bfloat16><<<M, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), x_row_stride, K, xh, rs,
+                                                         nullptr, nullptr, 1, nullptr);
     else
-      convert_x_kernel<float><<<M, 256, 0, st>>>(static_cast<const float*>(x), x_row_stride, K, xh, rs);
+      convert_x_kernel<float><<<M, 256, 0, st>>>(static_cast<const float*>(x), x_row_stride, K, xh, rs, nullptr,
+                                                 nullptr, 1, nullptr);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     a.x = xh;
@@ -614,6 +658,69 @@ cudaError_t launch_gemm(int codec, int x_dtype, const void* x, long long x_row_s
     case IQ4_NL: return launch_codec<IQ4_NL, 2>(out_half, a, aligned, st);
     case IQ4_XS: return launch_codec<IQ4_XS, 8>(out_half, a, aligned, st);
     case IQ2_XXS: return launch_codec<IQ2_XXS, 2>(out_half, a, aligned, st);
+  }
+  return cudaErrorInvalidValue;
+}
+
+// ------------------------------------------------------------------ grouped (MoE prefill)
+// Row tiles of 256 expert-sorted rows; workspace pieces are laid out by the caller (kq_gather.cu).
+template <int C, int NAT>
+static cudaError_t launch_grouped_codec(bool out_half, const GemmArgs& a, bool aligned, int grid_y, cudaStream_t st) {
+  if (out_half)
+    return aligned ? launch_g<C, NAT, __half, 2, 1, false>(a, st, grid_y) : launch_g<C, 1, __half, 2, 1, false>(a, st, grid_y);
+  return aligned ? launch_g<C, NAT, __nv_bfloat16, 2, 1, false>(a, st, grid_y)
+                 : launch_g<C, 1, __nv_bfloat16, 2, 1, false>(a, st, grid_y);
+}
+
+cudaError_t launch_gemm_grouped(int codec, int x_dtype, const void* x, int M, int K, const uint8_t* w,
+                                long long expert_stride, long long row_bytes, int N, const uint32_t* lhs,
+                                const int* order, long long rows_total, void* y, __half* xh, float* row_scale,
+                                int* yrow, const void* tiles, const int* n_tiles_dev, int max_tiles,
+                                cudaStream_t st) {
+  if (rows_total <= 0 || N <= 0 || K <= 0) return cudaSuccess;
+  if (x_dtype == F16)
+    convert_x_kernel<__half><<<(unsigned)rows_total, 256, 0, st>>>(static_cast<const __half*>(x), K, K, xh, row_scale,
+                                                                    order, lhs, M, yrow);
+  else if (x_dtype == BF16)
+    convert_x_kernel<__nv_bfloat16><<<(unsigned)rows_total, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), K, K,
+                                                                           xh, row_scale, order, lhs, M, yrow);
+  else
+    convert_x_kernel<float><<<(unsigned)rows_total, 256, 0, st>>>(static_cast<const float*>(x), K, K, xh, row_scale,
+                                                                   order, lhs, M, yrow);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  GemmArgs a;
+  a.x = xh;
+  a.x_row_stride = K;
+  a.y = y;
+  a.y_row_stride = N;
+  a.w = w;
+  a.row_bytes = row_bytes;
+  a.M = (int)rows_total;
+  a.N = N;
+  a.K = K;
+  a.row_scale = x_dtype == F16 ? nullptr : row_scale;
+  a.tiles = static_cast<const GemmTile*>(tiles);
+  a.n_tiles_dev = n_tiles_dev;
+  a.w_expert_stride = expert_stride;
+  a.yrow = yrow;
+  const bool out_half = x_dtype == F16;
+  const bool aligned = (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (expert_stride & 15) == 0;
+  if (codec == Q4_K && aligned) {
+    if (out_half) return launch_g<Q4_K, 16, __half, 2, 2, true>(a, st, max_tiles);
+    return launch_g<Q4_K, 16, __nv_bfloat16, 2, 2, true>(a, st, max_tiles);
+  }
+  switch (codec) {
+    case Q2_K: return launch_grouped_codec<Q2_K, 4>(out_half, a, aligned, max_tiles, st);
+    case Q3_K: return launch_grouped_codec<Q3_K, 2>(out_half, a, aligned, max_tiles, st);
+    case Q4_K: return launch_grouped_codec<Q4_K, 16>(out_half, a, aligned, max_tiles, st);
+    case Q5_K: return launch_grouped_codec<Q5_K, 16>(out_half, a, aligned, max_tiles, st);
+    case Q6_K: return launch_grouped_codec<Q6_K, 2>(out_half, a, aligned, max_tiles, st);
+    case Q4_0: return launch_grouped_codec<Q4_0, 2>(out_half, a, aligned, max_tiles, st);
+    case Q8_0: return launch_grouped_codec<Q8_0, 2>(out_half, a, aligned, max_tiles, st);
+    case IQ4_NL: return launch_grouped_codec<IQ4_NL, 2>(out_half, a, aligned, max_tiles, st);
+    case IQ4_XS: return launch_grouped_codec<IQ4_XS, 8>(out_half, a, aligned, max_tiles, st);
+    case IQ2_XXS: return launch_grouped_codec<IQ2_XXS, 2>(out_half, a, aligned, max_tiles, st);
   }
   return cudaErrorInvalidValue;
 }

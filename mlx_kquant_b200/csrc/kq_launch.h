@@ -2,6 +2,7 @@
 // translation units. Not installed; the public surface is include/kquant_b200.h.
 #pragma once
 
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -48,6 +49,12 @@ cudaError_t launch_gemv(int codec, int x_dtype, const GemvArgs& a, cudaStream_t 
 size_t gemm_workspace_bytes(int x_dtype, long long rows, int K);
 cudaError_t launch_gemm(int codec, int x_dtype, const void* x, long long x_row_stride, void* y, long long y_row_stride,
                         const uint8_t* w, long long row_bytes, int M, int N, int K, void* workspace, cudaStream_t st);
+// Grouped (mixture-of-experts) prefill: 256-row tiles of expert-sorted rows, see kq_gather.cu.
+constexpr int kGroupedTileRows = 256;
+cudaError_t launch_gemm_grouped(int codec, int x_dtype, const void* x, int M, int K, const uint8_t* w,
+                                long long expert_stride, long long row_bytes, int N, const uint32_t* lhs,
+                                const int* order, long long rows_total, void* y, __half* xh, float* row_scale,
+                                int* yrow, const void* tiles, const int* n_tiles_dev, int max_tiles, cudaStream_t st);
 // Flags raised by kernels that gave up on a bounded wait (0 = none); synchronises the device.
 cudaError_t read_device_error(int* out, bool clear);
 
@@ -55,11 +62,25 @@ cudaError_t read_device_error(int* out, bool clear);
 struct GatherLayout {
   size_t counts, offsets, task_base, cursor, n_tasks, order, tasks, total;
   long long max_tasks;
+  // grouped tile-kernel regime only (grouped == true): fp16 copy of the sorted rows etc.
+  bool grouped;
+  size_t xh, row_scale, yrow, tiles;
+  long long max_tiles;
 };
-GatherLayout gather_layout(long long n_entries, int M, int n_experts);
+// K > 0 lets the layout include the grouped regime's buffers when that regime would be chosen;
+// K == 0 is the decode-only layout (the skinny kernel over task lists).
+GatherLayout gather_layout(long long n_entries, int M, int n_experts, int K);
 cudaError_t launch_gather(int codec, int x_dtype, const void* x, int M, int K, const uint8_t* w, int n_experts,
                           long long expert_stride, long long row_bytes, int N, const uint32_t* lhs,
-                          const uint32_t* rhs, long long n_entries, void* y, void* workspace, cudaStream_t st);
+                          const uint32_t* rhs, long long n_entries, void* y, void* workspace, bool allow_grouped,
+                          cudaStream_t st);
+
+// The body of kq_gather_qmm; allow_grouped = false pins the decode regime (fixed-size scratch).
+int gather_qmm_entry(const void* x, int x_dtype, long long x_batch, int M, int K, const void* w, int n_experts,
+                     long long w_expert_stride_bytes, size_t w_row_bytes, int N, const char* kquant_type,
+                     const uint32_t* lhs_indices, const uint32_t* rhs_indices, long long n_entries, int transpose,
+                     int rhs_sorted, void* y, void* workspace, size_t workspace_bytes, void* stream,
+                     bool allow_grouped);
 
 // Record `msg` as this thread's last error (what kq_last_error() returns) and
 // hand back `code`; lets entry points that live outside kq_abi.cu report errors.

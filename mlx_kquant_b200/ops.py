@@ -193,7 +193,7 @@ def gather_qmm(x, w, scales, kquant_type, lhs_indices=None, rhs_indices=None, tr
     E = w3.shape[0]
     y = torch.empty((n_entries, M, outer), dtype=out_dtype, device=dev)
     L = _lib.lib()
-    ws_bytes = L.kq_gather_qmm_workspace_bytes(n_entries, M, E)
+    ws_bytes = L.kq_gather_qmm_workspace_bytes(n_entries, M, E, K)
     ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
     right_sorted = bool(sorted_indices) and lhs_indices is None
     if stream is not None:

@@ -58,7 +58,7 @@ def test_abi_validation_needs_no_gpu():
     assert L.kq_quantized_matmul_workspace_bytes(1, 4096, 4096) == 0        # fp16 needs none
     assert L.kq_quantized_matmul_workspace_bytes(2, 4096, 4096) >= 4096 * 4096 * 2
     assert L.kq_quantized_matmul_workspace_bytes(2, 16, 4096) == 0          # decode regime needs none
-    assert L.kq_gather_qmm_workspace_bytes(8, 1, 128) > 0
+    assert L.kq_gather_qmm_workspace_bytes(8, 1, 128, 2048) > 0
 
 
 def test_python_ops_validate_like_the_reference():

@@ -27,7 +27,7 @@ def oracle_moe(oracle, x_bits, wg, wu, wd, ids, probs, codec):
     return (d.reshape(T, k, -1) * probs[:, :, None]).sum(axis=1)
 
 
-@pytest.mark.parametrize("T", [1, 40])
+@pytest.mark.parametrize("T", [1, 40, 256])   # 256 tokens x top-4 = 1024 routed rows: the grouped tile-kernel regime
 def test_moe_glu_matches_oracle_composition(oracle, T):
     codec, E, H, F, k = "q4_k", 16, 512, 256, 4
     rng = np.random.default_rng(4000 + T)

@@ -60,7 +60,7 @@ def test_noalloc_matches_workspace_entry_point_twice():
         rhs = torch.from_numpy(rng.integers(0, E, n_entries).astype(np.int32)).cuda()
         want = torch.full((n_entries, M, N), float("nan"), dtype=torch.float16, device="cuda")
         got = torch.full_like(want, float("nan"))
-        ws = torch.empty(L.kq_gather_qmm_workspace_bytes(n_entries, M, E), dtype=torch.uint8, device="cuda")
+        ws = torch.empty(L.kq_gather_qmm_workspace_bytes(n_entries, M, E, K), dtype=torch.uint8, device="cuda")
         _lib.check(_call(L, L.kq_gather_qmm, x, w, lhs, rhs, want, ws))
         _lib.check(_call(L, L.kq_gather_qmm_noalloc, x, w, lhs, rhs, got))
         torch.cuda.synchronize()
@@ -71,7 +71,7 @@ def test_noalloc_matches_workspace_entry_point_twice():
 def test_noalloc_rejects_problems_beyond_the_fixed_array():
     L = _lib.lib()
     n_entries = 200_000
-    assert L.kq_gather_qmm_workspace_bytes(n_entries, 1, 128) > KQ_GATHER_STATIC_WS_BYTES
+    assert L.kq_gather_qmm_workspace_bytes(n_entries, 1, 128, 0) > KQ_GATHER_STATIC_WS_BYTES
     # validation happens before any pointer is touched, so dummy non-null pointers are enough
     one = torch.zeros(16, dtype=torch.uint8, device="cuda")
     p = one.data_ptr()
