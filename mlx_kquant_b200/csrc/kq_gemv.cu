@@ -347,6 +347,199 @@ __device__ __forceinline__ void q4k_compute(const Q4kLoad& l, const uint4* xs, c
   }
 }
 
+// ---- q4_k, one activation row (the decode case proper) --------------------------
+// With a single token the eight columns of the B operand are free, and they are
+// used to keep the eight sub-blocks of a superblock apart: column n of B holds
+// x[k] for the K slots that belong to sub-block n and zero elsewhere. Lane (g, t)
+// feeds slots of sub-block 2t (low nibbles) or 2t+1 (high nibbles), so it supplies
+// real activations only when its column g is that sub-block and reads a block of
+// zeros otherwise - a choice of base pointer made once per kernel. All sixteen
+// MMAs of a superblock then accumulate into one fragment whose element
+// (row, 2t + j) is sum_k (off_j + q_k) x_k over sub-block 2t + j: exactly the two
+// sub-blocks whose 6-bit scales this lane unpacks. No per-weight arithmetic is
+// left besides the three-input logic op that plants a nibble pair into fp16
+// (0x6400 | q = 1024 + q for low nibbles, 0x5400 | q << 4 = 64 + q for high ones);
+// the offsets leave with the fp32 group sums of x:
+//   y += d * (sc0 (D0 - 1024 xs0) + sc1 (D1 - 64 xs1)) - dmin * (mn0 xs0 + mn1 xs1).
+__device__ __forceinline__ float byte_to_float(uint32_t v, int byte) {
+  // 0x4B0000bb is 2^23 + bb exactly
+  return __uint_as_float(__byte_perm(v, 0x4B000000u, byte == 0 ? 0x7440 : 0x7441)) - 8388608.f;
+}
+
+// qa0/qa1, qb0/qb1: the lane's 32 quant bytes of its two rows; hA/hB: the two block headers.
+__device__ __forceinline__ void q4k_m1_compute(const uint4 hA, const uint4 hB, const uint4 qa0, const uint4 qa1,
+                                               const uint4 qb0, const uint4 qb1, const uint4* xlo, const uint4* xhi,
+                                               const float* xsumf, int sbl, int t, const int (&xoff)[8], float& pA,
+                                               float& pB) {
+  const uint32_t wa[8] = {qa0.x, qa0.y, qa0.z, qa0.w, qa1.x, qa1.y, qa1.z, qa1.w};
+  const uint32_t wb[8] = {qb0.x, qb0.y, qb0.z, qb0.w, qb1.x, qb1.y, qb1.z, qb1.w};
+  const uint32_t kLo = 0x000f000fu, kHi = 0x00f000f0u, kM1024 = 0x64006400u, kM64 = 0x54005400u;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const uint4* plo = xlo + sbl * 32;
+  const uint4* phi = xhi + sbl * 32;
+#pragma unroll
+  for (int ip = 0; ip < 4; ip++) {
+    const uint4 x0 = plo[xoff[ip]];      // sub-block 2t, activations 8ip..8ip+7 (or zeros)
+    const uint4 x1 = phi[xoff[4 + ip]];  // sub-block 2t+1
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      const uint32_t Wa = wa[2 * ip + h], Wb = wb[2 * ip + h];
+      const uint32_t Wa8 = Wa >> 8, Wb8 = Wb >> 8;
+      mma_f16(acc, and_or(Wa, kLo, kM1024), and_or(Wb, kLo, kM1024), and_or(Wa8, kLo, kM1024),
+              and_or(Wb8, kLo, kM1024), h ? x0.z : x0.x, h ? x0.w : x0.y);
+      mma_f16(acc, and_or(Wa, kHi, kM64), and_or(Wb, kHi, kM64), and_or(Wa8, kHi, kM64), and_or(Wb8, kHi, kM64),
+              h ? x1.z : x1.x, h ? x1.w : x1.y);
+    }
+  }
+  // the lane's two sub-blocks: 6-bit pairs (src/kquant_cpu_decode.cpp:155-174) on 16-bit fields
+  const float2 xs = *reinterpret_cast<const float2*>(xsumf + sbl * 8 + 2 * t);
+  const int sh = 16 * (t & 1);
+#pragma unroll
+  for (int r = 0; r < 2; r++) {
+    const uint4 hdr = r ? hB : hA;
+    const uint32_t u0 = (hdr.y >> sh) & 0xffffu, u1 = (hdr.z >> sh) & 0xffffu, u2 = (hdr.w >> sh) & 0xffffu;
+    uint32_t sc2, mn2;
+    if (t < 2) {
+      sc2 = u0 & 0x3f3fu;
+      mn2 = u1 & 0x3f3fu;
+    } else {
+      sc2 = (u2 & 0x0f0fu) | ((u0 >> 2) & 0x3030u);
+      mn2 = ((u2 >> 4) & 0x0f0fu) | ((u1 >> 2) & 0x3030u);
+    }
+    const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(&hdr.x));  // (d, dmin)
+    const float t0 = fmaf(-1024.f, xs.x, acc[2 * r]), t1 = fmaf(-64.f, xs.y, acc[2 * r + 1]);
+    const float u = fmaf(byte_to_float(sc2, 1), t1, byte_to_float(sc2, 0) * t0);
+    const float v = fmaf(byte_to_float(mn2, 1), xs.y, byte_to_float(mn2, 0) * xs.x);
+    float& p = r ? pB : pA;
+    p = fmaf(dd.x, u, p);
+    p = fmaf(-dd.y, v, p);
+  }
+}
+
+// grid = (row groups of 128, S k-slices, 1); cluster = (1, S, 1). One activation row.
+constexpr int kM1StageK = 2048;  // one token: 4 KB of activations cover eight superblocks per staging step
+constexpr int kM1Chunks = kM1StageK / 8;
+__global__ void __launch_bounds__(kGemvThreads, 3) gemv_q4k_m1_kernel(const GemvArgs a) {
+  __shared__ int s_xrow[16], s_yrow[16];
+  __shared__ __align__(16) uint4 xs1[kM1Chunks];  // the staged activations, pair-permuted and swizzled
+  __shared__ __align__(16) uint4 xz[kM1Chunks];   // zeros: what a lane reads when its column is another sub-block
+  __shared__ __align__(16) float xsumf[kM1StageK / 32];
+  __shared__ float red[kRowsPerCta];
+  extern __shared__ __align__(16) uint8_t dyn_smem[];
+
+  cg::cluster_group cluster = cg::this_cluster();
+  TaskView tv;
+  if (!resolve_task(a, s_xrow, s_yrow, tv)) return;  // uniform over the cluster
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int row0 = blockIdx.x * kRowsPerCta + warp * 16;
+  for (int i = threadIdx.x; i < kM1Chunks; i += kGemvThreads) xz[i] = make_uint4(0u, 0u, 0u, 0u);
+
+  const int S = gridDim.y, slice = blockIdx.y;
+  const int nchunks = a.K >> 8;
+  const int per = (nchunks + S - 1) / S;
+  const int ch0 = min(slice * per, nchunks), ch1 = min(ch0 + per, nchunks);
+
+  // Weight ring: two slots per warp. Every loop step commits exactly one copy group (an empty one
+  // once the slice is exhausted), so "all but the newest group" is always the superblock at hand.
+  static_assert(kRing == 2, "the loop below toggles between two slots");
+  uint8_t* ring = dyn_smem + warp * (kRing * kSlotBytes);
+  const uint8_t* src[5];
+  int dst[5];
+#pragma unroll
+  for (int i = 0; i < 5; i++) {
+    const int j = lane + 32 * i;
+    const int row = j / 9, piece = j % 9;
+    src[i] = tv.w + (long long)min(row0 + row, a.N - 1) * a.row_bytes + piece * 16 + (long long)ch0 * 144;
+    dst[i] = row * 144 + piece * 16;
+  }
+  int issued = ch0;
+  auto issue = [&](uint8_t* slot) {
+    if (issued < ch1) {
+#pragma unroll
+      for (int i = 0; i < 5; i++) {
+        if (i < 4 || lane < 16) cp_async16(slot + dst[i], src[i]);
+        src[i] += 144;
+      }
+      issued++;
+    }
+    cp_async_commit();
+  };
+  issue(ring);
+  issue(ring + kSlotBytes);
+  pdl_launch_dependents();
+  if (a.tasks == nullptr) pdl_wait();  // activations may come from the kernel before this one
+
+  const uint4* xlo = (g == 2 * t) ? xs1 : xz;
+  const uint4* xhi = (g == 2 * t + 1) ? xs1 : xz;
+  int xoff[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) xoff[i] = x_slot(0, 8 * t + i);
+  const __half* xrow = static_cast<const __half*>(a.x) + (long long)s_xrow[0] * a.x_row_stride;
+
+  constexpr int kStageCh = kM1StageK / 256;
+  float pA = 0.f, pB = 0.f;
+  int soff = 0;  // byte offset of the current ring slot
+  for (int sb = ch0; sb < ch1; sb++) {
+    const int rel = sb - ch0;
+    if (rel % kStageCh == 0) {
+      if (rel != 0) __syncthreads();  // everyone is done with the previous stage
+      {
+        // one 16-byte chunk per thread: pair-permute it, and leave the fp32 sum of each 32-group
+        static_assert(kM1Chunks == kGemvThreads, "one chunk per thread");
+        const int c = threadIdx.x, k = sb * 256 + 8 * c;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (k < ch1 * 256) v = __ldg(reinterpret_cast<const uint4*>(xrow + k));  // nothing beyond this CTA's slice
+        const float2 p0 = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+        const float2 p1 = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+        const float2 p2 = __half22float2(*reinterpret_cast<const __half2*>(&v.z));
+        const float2 p3 = __half22float2(*reinterpret_cast<const __half2*>(&v.w));
+        float sum = ((p0.x + p0.y) + (p1.x + p1.y)) + ((p2.x + p2.y) + (p3.x + p3.y));
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        if ((c & 3) == 0) xsumf[c >> 2] = sum;
+        xs1[x_slot(0, c)] = make_uint4(__byte_perm(v.x, v.y, 0x5410), __byte_perm(v.x, v.y, 0x7632),
+                                       __byte_perm(v.z, v.w, 0x5410), __byte_perm(v.z, v.w, 0x7632));
+      }
+      __syncthreads();
+    }
+    asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+    __syncwarp();
+    const uint4* bA = reinterpret_cast<const uint4*>(ring + soff + g * 144);
+    const uint4* bB = reinterpret_cast<const uint4*>(ring + soff + (g + 8) * 144);
+    const uint4 hA = bA[0], hB = bB[0];
+    const uint4 qa0 = bA[1 + 2 * t], qa1 = bA[2 + 2 * t], qb0 = bB[1 + 2 * t], qb1 = bB[2 + 2 * t];
+    __syncwarp();  // the slot is free again
+    issue(ring + soff);
+    soff ^= kSlotBytes;
+    q4k_m1_compute(hA, hB, qa0, qa1, qb0, qb1, xlo, xhi, xsumf, rel % kStageCh, t, xoff, pA, pB);
+  }
+  // the four lanes of a quad hold the four sub-block pairs of the same two rows
+  pA += __shfl_xor_sync(0xffffffffu, pA, 1);
+  pB += __shfl_xor_sync(0xffffffffu, pB, 1);
+  pA += __shfl_xor_sync(0xffffffffu, pA, 2);
+  pB += __shfl_xor_sync(0xffffffffu, pB, 2);
+  if (t == 0) {
+    red[warp * 16 + g] = pA;
+    red[warp * 16 + g + 8] = pB;
+  }
+  cluster.sync();
+  const float* peer[kMaxSplit];
+#pragma unroll
+  for (int s = 0; s < kMaxSplit; s++) peer[s] = s < S ? cluster.map_shared_rank(red, s) : red;
+  const int cta_row0 = blockIdx.x * kRowsPerCta;
+  for (int idx = slice + S * threadIdx.x; idx < kRowsPerCta; idx += S * kGemvThreads) {
+    if (cta_row0 + idx < a.N) {
+      float sum = 0.f;
+#pragma unroll
+      for (int s = 0; s < kMaxSplit; s++)
+        if (s < S) sum += peer[s][idx];
+      static_cast<__half*>(a.y)[(long long)s_yrow[0] * a.y_row_stride + cta_row0 + idx] = __float2half_rn(sum);
+    }
+  }
+  cluster.sync();  // peers may still be reading this CTA's partial sums
+}
+
 // ---- the kernel ---------------------------------------------------------------
 // grid = (row groups of 128, S k-slices, tasks); cluster = (1, S, 1).
 template <int C, int A, typename XT, int NT, bool FAST>
@@ -553,6 +746,34 @@ static cudaError_t launch_k(const GemvArgs& a, dim3 grid, cudaStream_t st) {
   return cudaLaunchKernelEx(&cfg, kern, a);
 }
 
+static cudaError_t launch_m1(const GemvArgs& a, dim3 grid, cudaStream_t st) {
+  static bool attr_set[16] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 16 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gemv_q4k_m1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kRingBytesPerCta);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kGemvThreads);
+  cfg.dynamicSmemBytes = kRingBytesPerCta;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = grid.y;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  static const bool no_pdl = std::getenv("KQ_NO_PDL") != nullptr;  // A/B lever
+  cfg.numAttrs = no_pdl ? 1 : 2;
+  return cudaLaunchKernelEx(&cfg, gemv_q4k_m1_kernel, a);
+}
+
 template <int C, int NAT>
 static cudaError_t launch_generic(int x_dtype, const GemvArgs& a, dim3 grid, bool nt2, bool aligned, cudaStream_t st) {
 #define KQ_GV(AL, XT) \
@@ -595,6 +816,8 @@ cudaError_t launch_gemv(int codec, int x_dtype, const GemvArgs& a, cudaStream_t 
   const bool nt2 = a.tasks ? (a.max_m > 8) : (a.M > 8);
   const bool aligned = a.w_align16 != 0;
 
+  static const bool no_m1 = std::getenv("KQ_GEMV_NO_M1") != nullptr;  // A/B lever
+  if (codec == Q4_K && x_dtype == F16 && aligned && a.tasks == nullptr && a.M == 1 && !no_m1) return launch_m1(a, grid, st);
   if (codec == Q4_K && x_dtype == F16 && aligned)
     return nt2 ? launch_k<Q4_K, 16, __half, 2, true>(a, grid, st) : launch_k<Q4_K, 16, __half, 1, true>(a, grid, st);
   switch (codec) {

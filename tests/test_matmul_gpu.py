@@ -84,7 +84,8 @@ def test_ragged_n_and_leading_dims(oracle, codec):
     x1 = x[0, 0]                                    # 1-D activation vector
     y1 = kq.quantized_matmul(x1, torch.from_numpy(wire).cuda(), None, codec)
     assert tuple(y1.shape) == (N,)
-    assert torch.equal(y1, y[0, 0])
+    # a single row may take a kernel of its own: same math, different summation order
+    assert float((y1.float() - y[0, 0].float()).norm() / y[0, 0].float().norm()) < TOL
 
 
 @pytest.mark.parametrize("codec,M", [("q4_k", 40), ("q6_k", 130), ("q8_0", 33)])
