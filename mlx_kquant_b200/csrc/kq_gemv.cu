@@ -84,6 +84,13 @@ __device__ __forceinline__ uint32_t pack_bf2(float a, float b) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 
+// Cluster-wide rendezvous without memory ordering: enough where a CTA only has to
+// outlive its peers' reads of its shared memory (no data is handed over).
+__device__ __forceinline__ void cluster_sync_relaxed() {
+  asm volatile("barrier.cluster.arrive.relaxed.aligned;\n" ::: "memory");
+  asm volatile("barrier.cluster.wait.aligned;\n" ::: "memory");
+}
+
 // ---- activations in shared memory -------------------------------------------
 // Row n of the stage holds kStageChunks 16-byte chunks (8 activations each).
 // Chunk c of row n lives at slot c with its low three bits XOR-ed with bits 3-4
@@ -374,7 +381,9 @@ __device__ __forceinline__ void q4k_m1_compute(const uint4 hA, const uint4 hB, c
   const uint32_t wa[8] = {qa0.x, qa0.y, qa0.z, qa0.w, qa1.x, qa1.y, qa1.z, qa1.w};
   const uint32_t wb[8] = {qb0.x, qb0.y, qb0.z, qb0.w, qb1.x, qb1.y, qb1.z, qb1.w};
   const uint32_t kLo = 0x000f000fu, kHi = 0x00f000f0u, kM1024 = 0x64006400u, kM64 = 0x54005400u;
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  // two independent accumulation chains: low-nibble MMAs only ever reach the even columns,
+  // high-nibble MMAs the odd ones
+  float accl[4] = {0.f, 0.f, 0.f, 0.f}, acch[4] = {0.f, 0.f, 0.f, 0.f};
   const uint4* plo = xlo + sbl * 32;
   const uint4* phi = xhi + sbl * 32;
 #pragma unroll
@@ -385,9 +394,9 @@ __device__ __forceinline__ void q4k_m1_compute(const uint4 hA, const uint4 hB, c
     for (int h = 0; h < 2; h++) {
       const uint32_t Wa = wa[2 * ip + h], Wb = wb[2 * ip + h];
       const uint32_t Wa8 = Wa >> 8, Wb8 = Wb >> 8;
-      mma_f16(acc, and_or(Wa, kLo, kM1024), and_or(Wb, kLo, kM1024), and_or(Wa8, kLo, kM1024),
+      mma_f16(accl, and_or(Wa, kLo, kM1024), and_or(Wb, kLo, kM1024), and_or(Wa8, kLo, kM1024),
               and_or(Wb8, kLo, kM1024), h ? x0.z : x0.x, h ? x0.w : x0.y);
-      mma_f16(acc, and_or(Wa, kHi, kM64), and_or(Wb, kHi, kM64), and_or(Wa8, kHi, kM64), and_or(Wb8, kHi, kM64),
+      mma_f16(acch, and_or(Wa, kHi, kM64), and_or(Wb, kHi, kM64), and_or(Wa8, kHi, kM64), and_or(Wb8, kHi, kM64),
               h ? x1.z : x1.x, h ? x1.w : x1.y);
     }
   }
@@ -407,7 +416,7 @@ __device__ __forceinline__ void q4k_m1_compute(const uint4 hA, const uint4 hB, c
       mn2 = ((u2 >> 4) & 0x0f0fu) | ((u1 >> 2) & 0x3030u);
     }
     const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(&hdr.x));  // (d, dmin)
-    const float t0 = fmaf(-1024.f, xs.x, acc[2 * r]), t1 = fmaf(-64.f, xs.y, acc[2 * r + 1]);
+    const float t0 = fmaf(-1024.f, xs.x, accl[2 * r]), t1 = fmaf(-64.f, xs.y, acch[2 * r + 1]);
     const float u = fmaf(byte_to_float(sc2, 1), t1, byte_to_float(sc2, 0) * t0);
     const float v = fmaf(byte_to_float(mn2, 1), xs.y, byte_to_float(mn2, 0) * xs.x);
     float& p = r ? pB : pA;
@@ -537,7 +546,7 @@ __global__ void __launch_bounds__(kGemvThreads, 3) gemv_q4k_m1_kernel(const Gemv
       static_cast<__half*>(a.y)[(long long)s_yrow[0] * a.y_row_stride + cta_row0 + idx] = __float2half_rn(sum);
     }
   }
-  cluster.sync();  // peers may still be reading this CTA's partial sums
+  cluster_sync_relaxed();  // peers may still be reading this CTA's partial sums
 }
 
 // ---- the kernel ---------------------------------------------------------------
@@ -710,7 +719,7 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_kernel(const GemvArgs a) {
       }
     }
   }
-  cluster.sync();  // peers may still be reading this CTA's tile
+  cluster_sync_relaxed();  // peers may still be reading this CTA's tile
 }
 
 // ------------------------------------------------------------------ launch
