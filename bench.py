@@ -262,6 +262,43 @@ def extra_cells(dev):
     return out
 
 
+def moe_ep_cell(dev, rank, world):
+    """MoE SwiGLU block, 128 experts partitioned over the ranks, all-to-all dispatch and combine over
+    NCCL; weak scaling: T = 4096 tokens per rank. Device time, max over ranks."""
+    import torch
+    import torch.distributed as dist
+
+    from mlx_kquant_b200.dist import shard_bounds
+    from mlx_kquant_b200.moe import moe_glu_expert_parallel, route_topk
+    from mlx_kquant_b200.synth import random_wire
+
+    E, H, F, k, T = 128, 2048, 768, 8, 4096
+    lo, hi = shard_bounds(E, rank, world)
+    wg = random_wire("q4_k", F, H, seed=50 + rank, device=dev, lead=(hi - lo,))
+    wu = random_wire("q4_k", F, H, seed=60 + rank, device=dev, lead=(hi - lo,))
+    wd = random_wire("q4_k", H, F, seed=70 + rank, device=dev, lead=(hi - lo,))
+    g = torch.Generator(device="cpu").manual_seed(3000 + rank)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(dev)
+    ids, probs = route_topk(torch.randn(T, E, generator=g).to(dev), k)
+    fn = lambda: moe_glu_expert_parallel(x, wg, wu, wd, "q4_k", ids, probs, E)
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    reps = 3
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    return {f"moe_glu_q4k_ep{world}_T4096_per_rank": {"tokens_per_s": world * T / (ms * 1e-3), "ms": ms,
+                                                       "experts_per_rank": hi - lo}}
+
+
 def run_b200(args):
     import torch
     import torch.distributed as dist
@@ -375,6 +412,14 @@ def run_b200(args):
         except Exception as e:  # the checker is optional for timing; say why it is missing
             cpu = {"value": None, "unit": "GB/s", "cores": 0, "kind": "port", "sample": f"unavailable: {e}"}
 
+    # expert-parallel MoE (config 4) at N > 1: every rank brings T = 4096 tokens, experts are partitioned
+    ep = None
+    if world > 1 and not args.no_extra:
+        try:
+            ep = moe_ep_cell(dev, rank, world)
+        except Exception as e:
+            ep = {"error": str(e)[:200]}
+
     if rank == 0:
         line = {
             "metric": "q4k_gemv_weight_GBps", "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
@@ -398,6 +443,8 @@ def run_b200(args):
                 line["extra"] = extra_cells(dev)
             except Exception as e:
                 line["extra"] = {"error": str(e)[:200]}
+        if world > 1 and ep is not None:
+            line["extra"] = ep
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
