@@ -722,6 +722,359 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_kernel(const GemvArgs a) {
   cluster_sync_relaxed();  // peers may still be reading this CTA's tile
 }
 
+// ---- table-driven kernel for the IQ codecs (iq4_xs, iq2_xxs) ------------------------
+// Same work layout as gemv_kernel (cluster split-K, 8 warps x 16 rows, weights through
+// a per-warp cp.async ring, activations staged in swizzled shared memory), but the A
+// fragments come from lookup tables in shared memory that already hold the values in
+// the multiplicand type:
+//   iq4_xs   256 entries: byte -> pair (LUT[low nibble], LUT[high nibble])
+//            (src/kquant_cpu_decode.cpp:441-465, kvalues_iq4nl)
+//   iq2_xxs  256 entries: grid index -> its eight lattice values; 128 entries: 7-bit sign
+//            index -> four words of sign-bit masks to XOR in
+//            (src/kquant_cpu_decode.cpp:557-584, iq2xxs_grid / ksigns_iq2xs)
+// The four lanes of a quad work on the same 32-weight group, so two MMAs give the
+// exact integer dot products of that group for the warp's 16 rows, and the group's
+// fp32 scale (d * (ls - 32), resp. d * (0.5 + s) / 4) is applied once per group.
+// Block sizes (136 and 66 bytes) are not multiples of 16: the ring copies the
+// 16-byte-aligned window around each block and readers add the block's phase.
+template <int C>
+struct IqGeom;
+template <>
+struct IqGeom<IQ4_XS> {
+  static constexpr int kBpb = 136, kPieces = 9, kStride = 160;
+};
+template <>
+struct IqGeom<IQ2_XXS> {
+  static constexpr int kBpb = 66, kPieces = 5, kStride = 96;
+};
+
+template <typename MT>
+__device__ __forceinline__ uint32_t pack_mt(float a, float b) {
+  if constexpr (std::is_same<MT, __half>::value) return pack_h2(a, b);
+  else return pack_bf2(a, b);
+}
+
+template <int C, typename XT, int NT>
+__global__ void __launch_bounds__(kGemvThreads, 2) gemv_iq_kernel(const GemvArgs a) {
+  constexpr bool kHalf = std::is_same<XT, __half>::value;
+  using MT = typename std::conditional<kHalf, __half, __nv_bfloat16>::type;
+  using G = IqGeom<C>;
+  constexpr int kSlot = 16 * G::kStride;
+  constexpr int kTile = NT * 8 * kRowsPerCta;
+  __shared__ int s_xrow[16], s_yrow[16];
+  __shared__ __align__(16) uint4 xs[NT * 8 * kStageChunks];
+  __shared__ float red[kTile];
+  __shared__ __align__(16) uint32_t tab[C == IQ4_XS ? 256 : 256 * 2];
+  extern __shared__ __align__(16) uint8_t dyn_smem[];
+
+  cg::cluster_group cluster = cg::this_cluster();
+  // tables, in the multiplicand type
+  if constexpr (C == IQ4_XS) {
+    for (int b = threadIdx.x; b < 256; b += kGemvThreads)
+      tab[b] = pack_mt<MT>((float)kq_tab_iq4nl[b & 15], (float)kq_tab_iq4nl[b >> 4]);
+  } else {
+    // the lattice as it is: 256 x 8 bytes; bytes become multiplicands with the magic-number trick
+    for (int i = threadIdx.x; i < 256; i += kGemvThreads)
+      reinterpret_cast<unsigned long long*>(tab)[i] = kq_tab_iq2xxs_grid[i];
+  }
+  // iq4_xs, fp16: the 16-entry level table in four registers, looked up with byte permutes
+  uint32_t T[4] = {0u, 0u, 0u, 0u};
+  if constexpr (C == IQ4_XS && kHalf) {
+#pragma unroll
+    for (int i = 0; i < 16; i++) T[i >> 2] |= ((uint32_t)(uint8_t)kq_tab_iq4nl[i]) << (8 * (i & 3));
+  }
+  TaskView tv;
+  if (!resolve_task(a, s_xrow, s_yrow, tv)) return;  // uniform over the cluster; also publishes the tables
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int row0 = blockIdx.x * kRowsPerCta + warp * 16;
+  const int S = gridDim.y, slice = blockIdx.y;
+  const int nchunks = a.K >> 8;
+  const int per = (nchunks + S - 1) / S;
+  const int ch0 = min(slice * per, nchunks), ch1 = min(ch0 + per, nchunks);
+
+  // ring: the lane's pieces of a slot (piece j = lane + 32 i is bytes [16 (j % P), +16) of row j / P)
+  constexpr int kPerLane = (16 * G::kPieces + 31) / 32;
+  uint8_t* ring = dyn_smem + warp * (kRing * kSlot);
+  const uint8_t* src[kPerLane];
+  int dst[kPerLane];
+#pragma unroll
+  for (int i = 0; i < kPerLane; i++) {
+    const int j = min(lane + 32 * i, 16 * G::kPieces - 1);
+    const int row = j / G::kPieces, piece = j % G::kPieces;
+    src[i] = tv.w + (long long)min(row0 + row, a.N - 1) * a.row_bytes + piece * 16;
+    dst[i] = row * G::kStride + piece * 16;
+  }
+  int issued = ch0;
+  auto issue = [&](uint8_t* slot) {
+    if (issued < ch1) {
+      const long long base = ((long long)issued * G::kBpb) & ~15LL;
+#pragma unroll
+      for (int i = 0; i < kPerLane; i++)
+        if (lane + 32 * i < 16 * G::kPieces) cp_async16(slot + dst[i], src[i] + base);
+      issued++;
+    }
+    cp_async_commit();
+  };
+  issue(ring);
+  issue(ring + kSlot);
+  pdl_launch_dependents();
+  if (a.tasks == nullptr) pdl_wait();
+
+  float fin[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+    for (int i = 0; i < 4; i++) fin[nt][i] = 0.f;
+  // chunk 4 G + t of row n sits at x_slot(n, 4 G + t) = n * kStageChunks + 8 (G >> 1) +
+  // ((t ^ 4 (n & 1)) ^ (4 (G & 1)) ^ ((G >> 1) & 3)): the lane part is xe, the rest is a constant per G
+  const int xe = t ^ ((g & 1) << 2);
+
+  constexpr int kStageCh = kStageK / 256;
+  int soff = 0;
+  for (int sb = ch0; sb < ch1; sb++) {
+    const int rel = sb - ch0;
+    if (rel % kStageCh == 0) {
+      if (rel != 0) __syncthreads();
+      if constexpr (C == IQ2_XXS) {
+        stage_x<XT, NT, false>(xs, nullptr, a, s_xrow, tv.m, sb * 256, a.K);
+      } else {
+        // iq4_xs: lane t of group G multiplies weights 4t+i (low nibbles) and 4t+i+16 (high nibbles),
+        // so its chunk holds x[4t], x[4t+16], x[4t+1], x[4t+17], ...
+        for (int idx = threadIdx.x; idx < NT * 8 * kStageChunks; idx += kGemvThreads) {
+          const int n = idx / kStageChunks, c = idx % kStageChunks;
+          const int k = sb * 256 + (c >> 2) * 32 + (c & 3) * 4;
+          uint2 lo = make_uint2(0u, 0u), hi = make_uint2(0u, 0u);
+          if (n < tv.m && k < a.K) {
+            const XT* p = static_cast<const XT*>(a.x) + (long long)s_xrow[n] * a.x_row_stride + k;
+            if constexpr (sizeof(XT) == 2) {
+              lo = __ldg(reinterpret_cast<const uint2*>(p));
+              hi = __ldg(reinterpret_cast<const uint2*>(p + 16));
+            } else {
+              const float4 f0 = __ldg(reinterpret_cast<const float4*>(p));
+              const float4 f1 = __ldg(reinterpret_cast<const float4*>(p + 16));
+              lo = make_uint2(pack_bf2(f0.x, f0.y), pack_bf2(f0.z, f0.w));
+              hi = make_uint2(pack_bf2(f1.x, f1.y), pack_bf2(f1.z, f1.w));
+            }
+          }
+          xs[x_slot(n, c)] = make_uint4(__byte_perm(lo.x, hi.x, 0x5410), __byte_perm(lo.x, hi.x, 0x7632),
+                                        __byte_perm(lo.y, hi.y, 0x5410), __byte_perm(lo.y, hi.y, 0x7632));
+        }
+      }
+      __syncthreads();
+    }
+    asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+    __syncwarp();
+    const int ph = (int)(((long long)sb * G::kBpb) & 15);
+    const uint8_t* bA = ring + soff + g * G::kStride + ph;
+    const uint8_t* bB = ring + soff + (g + 8) * G::kStride + ph;
+    const uint4* xsb = xs + (rel % kStageCh) * 32;
+
+    if constexpr (C == IQ4_XS) {
+      // [d f16][scales_h u16][scales_l 4 B][qs 128 B]; lane t prepares the scales of groups 2t, 2t+1
+      const uint2 hA = *reinterpret_cast<const uint2*>(bA), hB = *reinterpret_cast<const uint2*>(bB);
+      float dl[2][2];
+#pragma unroll
+      for (int r = 0; r < 2; r++) {
+        const uint2 h = r ? hB : hA;
+        const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffff)));
+        const uint32_t sh = h.x >> 16, sl = h.y;
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+          const int ib = 2 * t + j;
+          const int ls = (int)(((sl >> (4 * ib)) & 15u) | (((sh >> (2 * ib)) & 3u) << 4));
+          dl[r][j] = d * (float)(ls - 32);
+        }
+      }
+#pragma unroll
+      for (int G8 = 0; G8 < 8; G8++) {
+        const int from = (lane & ~3) | (G8 >> 1);
+        const float dA = __shfl_sync(0xffffffffu, dl[0][G8 & 1], from);
+        const float dB = __shfl_sync(0xffffffffu, dl[1][G8 & 1], from);
+        const uint32_t WA = *reinterpret_cast<const uint32_t*>(bA + 8 + 16 * G8 + 4 * t);
+        const uint32_t WB = *reinterpret_cast<const uint32_t*>(bB + 8 + 16 * G8 + 4 * t);
+        uint32_t pa[4], pb[4];
+        if constexpr (kHalf) {
+          // Two bytes = four nibbles = one permute selector. Entries 0-7 and 8-15 are fetched
+          // separately (a selector nibble has 3 index bits), bit 3 of each nibble, spread over its
+          // byte by a sign-replicating permute, picks between them. The signed levels then become
+          // fp16 exactly: 0x6400 | (v + 128) is 1152 + v.
+          auto lut4 = [&](uint32_t X, uint32_t& p0, uint32_t& p1) {
+            const uint32_t sel = X & 0x7777u;
+            const uint32_t vlo = __byte_perm(T[0], T[1], sel), vhi = __byte_perm(T[2], T[3], sel);
+            uint32_t m;  // selector nibbles with bit 3 set replicate the byte's sign bit
+            asm("prmt.b32 %0, %1, %2, 0xD9C8;\n" : "=r"(m) : "r"(X << 4), "r"(X));
+            uint32_t v;
+            asm("lop3.b32 %0, %1, %2, %3, 0xCA;\n" : "=r"(v) : "r"(m), "r"(vhi), "r"(vlo));
+            v ^= 0x80808080u;
+            const __half2 off = __float2half2_rn(1152.f);
+            const uint32_t h0 = __byte_perm(v, 0x64646464u, 0x4140), h1 = __byte_perm(v, 0x64646464u, 0x4342);
+            const __half2 r0 = __hsub2(*reinterpret_cast<const __half2*>(&h0), off);
+            const __half2 r1 = __hsub2(*reinterpret_cast<const __half2*>(&h1), off);
+            p0 = *reinterpret_cast<const uint32_t*>(&r0);
+            p1 = *reinterpret_cast<const uint32_t*>(&r1);
+          };
+          lut4(WA, pa[0], pa[1]);
+          lut4(WA >> 16, pa[2], pa[3]);
+          lut4(WB, pb[0], pb[1]);
+          lut4(WB >> 16, pb[2], pb[3]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            pa[i] = tab[(WA >> (8 * i)) & 0xff];
+            pb[i] = tab[(WB >> (8 * i)) & 0xff];
+          }
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+          const uint4 xb = xsb[(nt * 8 + g) * kStageChunks + 8 * (G8 >> 1) + (xe ^ ((4 * (G8 & 1)) ^ ((G8 >> 1) & 3)))];
+          float acc[4] = {0.f, 0.f, 0.f, 0.f};
+          if constexpr (kHalf) {
+            mma_f16(acc, pa[0], pb[0], pa[1], pb[1], xb.x, xb.y);
+            mma_f16(acc, pa[2], pb[2], pa[3], pb[3], xb.z, xb.w);
+          } else {
+            mma_bf16(acc, pa[0], pb[0], pa[1], pb[1], xb.x, xb.y);
+            mma_bf16(acc, pa[2], pb[2], pa[3], pb[3], xb.z, xb.w);
+          }
+          fin[nt][0] = fmaf(dA, acc[0], fin[nt][0]);
+          fin[nt][1] = fmaf(dA, acc[1], fin[nt][1]);
+          fin[nt][2] = fmaf(dB, acc[2], fin[nt][2]);
+          fin[nt][3] = fmaf(dB, acc[3], fin[nt][3]);
+        }
+      }
+    } else {
+      // [d f16][8 x (4 grid-index bytes, u32: 4 x 7-bit sign index + 4-bit scale)], 2-byte aligned
+      const float dA0 = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(bA)));
+      const float dB0 = __half2float(__ushort_as_half(*reinterpret_cast<const unsigned short*>(bB)));
+      const uint2* grid = reinterpret_cast<const uint2*>(tab);
+      // eight lattice bytes -> four pairs of multiplicands (0x6400 | b = 1024 + b in fp16, 0x4300 | b =
+      // 128 + b in bf16, minus the offset: exact), signs XOR-ed into the sign bits. The eight sign
+      // bits are the 7-bit field plus its parity (ksigns_iq2xs); r carries bit 2j in its low half
+      // and bit 2j+1 in its high half once shifted left by 15 - 2j.
+      auto make8 = [&](uint2 gb, uint32_t s7, uint4& out) {
+        const uint32_t s8 = s7 | ((__popc(s7) & 1u) << 7);
+        const uint32_t r = s8 | ((s8 >> 1) << 16);
+        const uint32_t magic = kHalf ? 0x64646464u : 0x43434343u;
+        uint32_t v[4] = {__byte_perm(gb.x, magic, 0x4140), __byte_perm(gb.x, magic, 0x4342),
+                         __byte_perm(gb.y, magic, 0x4140), __byte_perm(gb.y, magic, 0x4342)};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          if constexpr (kHalf) {
+            const __half2 q = __hsub2(*reinterpret_cast<const __half2*>(&v[j]), __float2half2_rn(1024.f));
+            v[j] = *reinterpret_cast<const uint32_t*>(&q);
+          } else {
+            const __nv_bfloat162 q =
+                __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&v[j]), __float2bfloat162_rn(128.f));
+            v[j] = *reinterpret_cast<const uint32_t*>(&q);
+          }
+          asm("lop3.b32 %0, %1, %2, %3, 0x78;\n" : "=r"(v[j]) : "r"(v[j]), "r"(r << (15 - 2 * j)), "r"(0x80008000u));
+        }
+        out = make_uint4(v[0], v[1], v[2], v[3]);
+      };
+#pragma unroll
+      for (int G8 = 0; G8 < 8; G8++) {
+        const uint8_t* qa = bA + 2 + 8 * G8;
+        const uint8_t* qb = bB + 2 + 8 * G8;
+        const uint32_t auxA = (uint32_t)*reinterpret_cast<const unsigned short*>(qa + 4) |
+                              ((uint32_t)*reinterpret_cast<const unsigned short*>(qa + 6) << 16);
+        const uint32_t auxB = (uint32_t)*reinterpret_cast<const unsigned short*>(qb + 4) |
+                              ((uint32_t)*reinterpret_cast<const unsigned short*>(qb + 6) << 16);
+        const float dA = dA0 * (0.5f + (float)(auxA >> 28)) * 0.25f;
+        const float dB = dB0 * (0.5f + (float)(auxB >> 28)) * 0.25f;
+        uint4 va, vb;
+        make8(grid[qa[t]], (auxA >> (7 * t)) & 127u, va);
+        make8(grid[qb[t]], (auxB >> (7 * t)) & 127u, vb);
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+          const uint4 xb = xsb[(nt * 8 + g) * kStageChunks + 8 * (G8 >> 1) + (xe ^ ((4 * (G8 & 1)) ^ ((G8 >> 1) & 3)))];
+          float acc[4] = {0.f, 0.f, 0.f, 0.f};
+          if constexpr (kHalf) {
+            mma_f16(acc, va.x, vb.x, va.y, vb.y, xb.x, xb.y);
+            mma_f16(acc, va.z, vb.z, va.w, vb.w, xb.z, xb.w);
+          } else {
+            mma_bf16(acc, va.x, vb.x, va.y, vb.y, xb.x, xb.y);
+            mma_bf16(acc, va.z, vb.z, va.w, vb.w, xb.z, xb.w);
+          }
+          fin[nt][0] = fmaf(dA, acc[0], fin[nt][0]);
+          fin[nt][1] = fmaf(dA, acc[1], fin[nt][1]);
+          fin[nt][2] = fmaf(dB, acc[2], fin[nt][2]);
+          fin[nt][3] = fmaf(dB, acc[3], fin[nt][3]);
+        }
+      }
+    }
+    __syncwarp();  // the slot is free again
+    issue(ring + soff);
+    soff ^= kSlot;
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+
+  // ---- partial tile -> shared memory -> cluster reduce (as in gemv_kernel)
+#pragma unroll
+  for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int tok = nt * 8 + 2 * t + (i & 1);
+      const int row = warp * 16 + g + 8 * (i >> 1);
+      red[tok * kRowsPerCta + row] = fin[nt][i];
+    }
+  cluster.sync();
+  const float* peer[kMaxSplit];
+#pragma unroll
+  for (int s = 0; s < kMaxSplit; s++) peer[s] = s < S ? cluster.map_shared_rank(red, s) : red;
+  const int cta_row0 = blockIdx.x * kRowsPerCta;
+  for (int idx = slice + S * threadIdx.x; idx < kTile; idx += S * kGemvThreads) {
+    const int tok = idx / kRowsPerCta, row = idx % kRowsPerCta;
+    if (tok < tv.m && cta_row0 + row < a.N) {
+      float sum = 0.f;
+#pragma unroll
+      for (int s = 0; s < kMaxSplit; s++)
+        if (s < S) sum += peer[s][idx];
+      MT* y = static_cast<MT*>(a.y) + (long long)s_yrow[tok] * a.y_row_stride + cta_row0 + row;
+      if constexpr (kHalf) *y = __float2half_rn(sum);
+      else *y = __float2bfloat16_rn(sum);
+    }
+  }
+  cluster_sync_relaxed();
+}
+
+template <int C, typename XT, int NT>
+static cudaError_t launch_iq(const GemvArgs& a, dim3 grid, cudaStream_t st) {
+  auto kern = gemv_iq_kernel<C, XT, NT>;
+  constexpr int dyn = kGemvWarps * kRing * 16 * IqGeom<C>::kStride;
+  static bool attr_set[16] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 16 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, dyn);
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kGemvThreads);
+  cfg.dynamicSmemBytes = dyn;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = grid.y;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = a.tasks == nullptr ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, kern, a);
+}
+
+template <int C>
+static cudaError_t launch_iq_any(int x_dtype, const GemvArgs& a, dim3 grid, bool nt2, cudaStream_t st) {
+  if (x_dtype == F16) return nt2 ? launch_iq<C, __half, 2>(a, grid, st) : launch_iq<C, __half, 1>(a, grid, st);
+  if (x_dtype == BF16)
+    return nt2 ? launch_iq<C, __nv_bfloat16, 2>(a, grid, st) : launch_iq<C, __nv_bfloat16, 1>(a, grid, st);
+  return nt2 ? launch_iq<C, float, 2>(a, grid, st) : launch_iq<C, float, 1>(a, grid, st);
+}
+
 // ------------------------------------------------------------------ launch
 template <int C, int A, typename XT, int NT, bool FAST>
 static cudaError_t launch_k(const GemvArgs& a, dim3 grid, cudaStream_t st) {
@@ -827,6 +1180,12 @@ cudaError_t launch_gemv(int codec, int x_dtype, const GemvArgs& a, cudaStream_t 
 
   static const bool no_m1 = std::getenv("KQ_GEMV_NO_M1") != nullptr;  // A/B lever
   if (codec == Q4_K && x_dtype == F16 && aligned && a.tasks == nullptr && a.M == 1 && !no_m1) return launch_m1(a, grid, st);
+  // rows that are whole numbers of 16 bytes let the ring copy aligned windows around each block
+  static const bool no_iq = std::getenv("KQ_GEMV_NO_IQ") != nullptr;  // A/B lever
+  if (aligned && (a.row_bytes & 15) == 0 && !no_iq) {
+    if (codec == IQ4_XS) return launch_iq_any<IQ4_XS>(x_dtype, a, grid, nt2, st);
+    if (codec == IQ2_XXS) return launch_iq_any<IQ2_XXS>(x_dtype, a, grid, nt2, st);
+  }
   if (codec == Q4_K && x_dtype == F16 && aligned)
     return nt2 ? launch_k<Q4_K, 16, __half, 2, true>(a, grid, st) : launch_k<Q4_K, 16, __half, 1, true>(a, grid, st);
   switch (codec) {
