@@ -375,8 +375,8 @@ __device__ __forceinline__ float byte_to_float(uint32_t v, int byte) {
 
 // qa0/qa1, qb0/qb1: the lane's 32 quant bytes of its two rows; hA/hB: the two block headers.
 __device__ __forceinline__ void q4k_m1_compute(const uint4 hA, const uint4 hB, const uint4 qa0, const uint4 qa1,
-                                               const uint4 qb0, const uint4 qb1, const uint4* xlo, const uint4* xhi,
-                                               const float* xsumf, int sbl, int t, const int (&xoff)[8], float& pA,
+                                               const uint4 qb0, const uint4 qb1, const uint4* plo, const uint4* phi,
+                                               const float* xsum8, int t, const int (&xoff)[8], float& pA,
                                                float& pB) {
   const uint32_t wa[8] = {qa0.x, qa0.y, qa0.z, qa0.w, qa1.x, qa1.y, qa1.z, qa1.w};
   const uint32_t wb[8] = {qb0.x, qb0.y, qb0.z, qb0.w, qb1.x, qb1.y, qb1.z, qb1.w};
@@ -384,8 +384,6 @@ __device__ __forceinline__ void q4k_m1_compute(const uint4 hA, const uint4 hB, c
   // two independent accumulation chains: low-nibble MMAs only ever reach the even columns,
   // high-nibble MMAs the odd ones
   float accl[4] = {0.f, 0.f, 0.f, 0.f}, acch[4] = {0.f, 0.f, 0.f, 0.f};
-  const uint4* plo = xlo + sbl * 32;
-  const uint4* phi = xhi + sbl * 32;
 #pragma unroll
   for (int ip = 0; ip < 4; ip++) {
     const uint4 x0 = plo[xoff[ip]];      // sub-block 2t, activations 8ip..8ip+7 (or zeros)
@@ -401,7 +399,7 @@ __device__ __forceinline__ void q4k_m1_compute(const uint4 hA, const uint4 hB, c
     }
   }
   // the lane's two sub-blocks: 6-bit pairs (src/kquant_cpu_decode.cpp:155-174) on 16-bit fields
-  const float2 xs = *reinterpret_cast<const float2*>(xsumf + sbl * 8 + 2 * t);
+  const float2 xs = *reinterpret_cast<const float2*>(xsum8 + 2 * t);
   const int sh = 16 * (t & 1);
 #pragma unroll
   for (int r = 0; r < 2; r++) {
@@ -521,7 +519,8 @@ __global__ void __launch_bounds__(kGemvThreads, 3) gemv_q4k_m1_kernel(const Gemv
     __syncwarp();  // the slot is free again
     issue(ring + soff);
     soff ^= kSlotBytes;
-    q4k_m1_compute(hA, hB, qa0, qa1, qb0, qb1, xlo, xhi, xsumf, rel % kStageCh, t, xoff, pA, pB);
+    const int sbl = rel % kStageCh;
+    q4k_m1_compute(hA, hB, qa0, qa1, qb0, qb1, xlo + sbl * 32, xhi + sbl * 32, xsumf + sbl * 8, t, xoff, pA, pB);
   }
   // the four lanes of a quad hold the four sub-block pairs of the same two rows
   pA += __shfl_xor_sync(0xffffffffu, pA, 1);
@@ -547,6 +546,126 @@ __global__ void __launch_bounds__(kGemvThreads, 3) gemv_q4k_m1_kernel(const Gemv
     }
   }
   cluster_sync_relaxed();  // peers may still be reading this CTA's partial sums
+}
+
+// ---- one activation row, small matrices ------------------------------------------
+// For a matrix of a few MB the launch is a latency chain, not a stream: what counts is how
+// little is left to do once the activations exist. Here a CTA of four warps owns 16 rows and
+// the warps split K between them, so partial sums meet in the CTA's own shared memory (no
+// cluster, no second barrier), ALL of a CTA's weights are in flight before it waits for the
+// preceding kernel, and a CTA is small enough (128 threads, ~46 KB) that the whole grid of the
+// next launch fits beside the running one and has its weights on chip when its turn comes.
+// grid = (ceil(N / 16), 1, 1). K <= kRowsMaxK: the activations are staged whole.
+constexpr int kRowsWarps = 4, kRowsThreads = 32 * kRowsWarps, kRowsDepth = 4, kRowsMaxK = 8192;
+constexpr int kRowsRingBytes = kRowsWarps * kRowsDepth * kSlotBytes;
+static inline int rows_dyn_smem(int K) { return kRowsRingBytes + K * 2 + (K / 32) * 4; }
+
+__global__ void __launch_bounds__(kRowsThreads, 4) gemv_q4k_m1_rows_kernel(const GemvArgs a) {
+  __shared__ int s_xrow[16], s_yrow[16];
+  __shared__ __align__(16) uint4 xz[32];  // zeros: what a lane reads when its column is another sub-block
+  __shared__ float red[kRowsWarps * 16];
+  extern __shared__ __align__(16) uint8_t dyn_smem[];
+  const int nchunks = a.K >> 8;
+  uint4* xs1 = reinterpret_cast<uint4*>(dyn_smem + kRowsRingBytes);  // pair-permuted, swizzled activations
+  float* xsumf = reinterpret_cast<float*>(dyn_smem + kRowsRingBytes + nchunks * 512);
+
+  TaskView tv;
+  if (!resolve_task(a, s_xrow, s_yrow, tv)) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int row0 = blockIdx.x * 16;
+  if (threadIdx.x < 32) xz[threadIdx.x] = make_uint4(0u, 0u, 0u, 0u);
+
+  const int per = (nchunks + kRowsWarps - 1) / kRowsWarps;
+  const int ch0 = min(warp * per, nchunks), ch1 = min(ch0 + per, nchunks);
+
+  // Per-warp ring of kRowsDepth superblocks x 16 rows. Every issue() commits exactly one copy
+  // group (an empty one past the slice), so "all but the newest kRowsDepth - 1" is always the
+  // superblock at hand.
+  uint8_t* ring = dyn_smem + warp * (kRowsDepth * kSlotBytes);
+  const uint8_t* src[5];
+  int dst[5];
+#pragma unroll
+  for (int i = 0; i < 5; i++) {
+    const int j = lane + 32 * i;
+    const int row = j / 9, piece = j % 9;
+    src[i] = tv.w + (long long)min(row0 + row, a.N - 1) * a.row_bytes + piece * 16 + (long long)ch0 * 144;
+    dst[i] = row * 144 + piece * 16;
+  }
+  int issued = ch0;
+  auto issue = [&](uint8_t* slot) {
+    if (issued < ch1) {
+#pragma unroll
+      for (int i = 0; i < 5; i++) {
+        if (i < 4 || lane < 16) cp_async16(slot + dst[i], src[i]);
+        src[i] += 144;
+      }
+      issued++;
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int d = 0; d < kRowsDepth; d++) issue(ring + d * kSlotBytes);
+  pdl_launch_dependents();
+  if (a.tasks == nullptr) pdl_wait();  // activations may come from the kernel before this one
+
+  {
+    // all of K: pair-permute each 16-byte chunk and leave the fp32 sum of each 32-group
+    const __half* xrow = static_cast<const __half*>(a.x) + (long long)s_xrow[0] * a.x_row_stride;
+    for (int c = threadIdx.x; c < nchunks * 32; c += kRowsThreads) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(xrow + 8 * c));
+      const float2 p0 = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+      const float2 p1 = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+      const float2 p2 = __half22float2(*reinterpret_cast<const __half2*>(&v.z));
+      const float2 p3 = __half22float2(*reinterpret_cast<const __half2*>(&v.w));
+      float sum = ((p0.x + p0.y) + (p1.x + p1.y)) + ((p2.x + p2.y) + (p3.x + p3.y));
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      if ((c & 3) == 0) xsumf[c >> 2] = sum;
+      xs1[x_slot(0, c)] = make_uint4(__byte_perm(v.x, v.y, 0x5410), __byte_perm(v.x, v.y, 0x7632),
+                                     __byte_perm(v.z, v.w, 0x5410), __byte_perm(v.z, v.w, 0x7632));
+    }
+  }
+  __syncthreads();
+
+  const uint4* xlo = (g == 2 * t) ? xs1 : xz;
+  const uint4* xhi = (g == 2 * t + 1) ? xs1 : xz;
+  const int lo_step = (g == 2 * t) ? 32 : 0, hi_step = (g == 2 * t + 1) ? 32 : 0;
+  int xoff[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) xoff[i] = x_slot(0, 8 * t + i);
+
+  float pA = 0.f, pB = 0.f;
+  for (int sb = ch0; sb < ch1; sb++) {
+    const int rel = sb - ch0;
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(kRowsDepth - 1) : "memory");
+    __syncwarp();
+    uint8_t* slot = ring + (rel % kRowsDepth) * kSlotBytes;
+    const uint4* bA = reinterpret_cast<const uint4*>(slot + g * 144);
+    const uint4* bB = reinterpret_cast<const uint4*>(slot + (g + 8) * 144);
+    const uint4 hA = bA[0], hB = bB[0];
+    const uint4 qa0 = bA[1 + 2 * t], qa1 = bA[2 + 2 * t], qb0 = bB[1 + 2 * t], qb1 = bB[2 + 2 * t];
+    __syncwarp();  // the slot is free again
+    issue(slot);
+    q4k_m1_compute(hA, hB, qa0, qa1, qb0, qb1, xlo + sb * lo_step, xhi + sb * hi_step, xsumf + sb * 8, t, xoff, pA,
+                   pB);
+  }
+  // the four lanes of a quad hold the four sub-block pairs of the same two rows
+  pA += __shfl_xor_sync(0xffffffffu, pA, 1);
+  pB += __shfl_xor_sync(0xffffffffu, pB, 1);
+  pA += __shfl_xor_sync(0xffffffffu, pA, 2);
+  pB += __shfl_xor_sync(0xffffffffu, pB, 2);
+  if (t == 0) {
+    red[warp * 16 + g] = pA;
+    red[warp * 16 + g + 8] = pB;
+  }
+  __syncthreads();
+  if (threadIdx.x < 16 && row0 + threadIdx.x < a.N) {
+    float sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < kRowsWarps; w++) sum += red[w * 16 + threadIdx.x];
+    static_cast<__half*>(a.y)[(long long)s_yrow[0] * a.y_row_stride + row0 + threadIdx.x] = __float2half_rn(sum);
+  }
 }
 
 // ---- the kernel ---------------------------------------------------------------
@@ -1136,6 +1255,30 @@ static cudaError_t launch_m1(const GemvArgs& a, dim3 grid, cudaStream_t st) {
   return cudaLaunchKernelEx(&cfg, gemv_q4k_m1_kernel, a);
 }
 
+static cudaError_t launch_m1_rows(const GemvArgs& a, cudaStream_t st) {
+  static bool attr_set[16] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 16 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gemv_q4k_m1_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         rows_dyn_smem(kRowsMaxK));
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((a.N + 15) / 16, 1, 1);
+  cfg.blockDim = dim3(kRowsThreads);
+  cfg.dynamicSmemBytes = rows_dyn_smem(a.K);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  static const bool no_pdl = std::getenv("KQ_NO_PDL") != nullptr;  // A/B lever
+  cfg.numAttrs = no_pdl ? 0 : 1;
+  return cudaLaunchKernelEx(&cfg, gemv_q4k_m1_rows_kernel, a);
+}
+
 template <int C, int NAT>
 static cudaError_t launch_generic(int x_dtype, const GemvArgs& a, dim3 grid, bool nt2, bool aligned, cudaStream_t st) {
 #define KQ_GV(AL, XT) \
@@ -1179,7 +1322,17 @@ cudaError_t launch_gemv(int codec, int x_dtype, const GemvArgs& a, cudaStream_t 
   const bool aligned = a.w_align16 != 0;
 
   static const bool no_m1 = std::getenv("KQ_GEMV_NO_M1") != nullptr;  // A/B lever
-  if (codec == Q4_K && x_dtype == F16 && aligned && a.tasks == nullptr && a.M == 1 && !no_m1) return launch_m1(a, grid, st);
+  if (codec == Q4_K && x_dtype == F16 && aligned && a.tasks == nullptr && a.M == 1 && !no_m1) {
+    // The cluster-free kernel wins (measured) unless few row groups leave each warp a long K
+    // chain. A/B lever: KQ_GEMV_ROWS=0|1 forces the choice.
+    static const char* rows_env = std::getenv("KQ_GEMV_ROWS");
+    const int row_ctas = (a.N + 15) / 16;
+    const int sb_per_warp = (nchunks + kRowsWarps - 1) / kRowsWarps;
+    bool rows = a.K <= kRowsMaxK && ((row_ctas >= 148 && sb_per_warp <= 4) || row_ctas >= 3 * 148);
+    if (rows_env) rows = rows_env[0] == '1' && a.K <= kRowsMaxK && row_ctas <= 65535;
+    if (rows) return launch_m1_rows(a, st);
+    return launch_m1(a, grid, st);
+  }
   // rows that are whole numbers of 16 bytes let the ring copy aligned windows around each block
   static const bool no_iq = std::getenv("KQ_GEMV_NO_IQ") != nullptr;  // A/B lever
   if (aligned && (a.row_bytes & 15) == 0 && !no_iq) {
