@@ -1321,6 +1321,8 @@ cudaError_t launch_gemv(int codec, int x_dtype, const GemvArgs& a, cudaStream_t 
   const bool nt2 = a.tasks ? (a.max_m > 8) : (a.M > 8);
   const bool aligned = a.w_align16 != 0;
 
+  static const char* tc_env = std::getenv("KQ_GEMV_TC");  // A/B lever: 1 = tensor-memory decode kernel
+  if (tc_env && tc_env[0] == '1' && gemv_tc_supported(codec, x_dtype, a)) return launch_gemv_tc(a, st);
   static const bool no_m1 = std::getenv("KQ_GEMV_NO_M1") != nullptr;  // A/B lever
   if (codec == Q4_K && x_dtype == F16 && aligned && a.tasks == nullptr && a.M == 1 && !no_m1) {
     // The cluster-free kernel wins (measured) unless few row groups leave each warp a long K

@@ -44,6 +44,12 @@ struct GemvArgs {
 // on load, output bf16), 1 f16, 2 bf16.
 cudaError_t launch_gemv(int codec, int x_dtype, const GemvArgs& a, cudaStream_t st);
 
+// q4_k, fp16, one or two dense activation rows: the decode kernel on tcgen05 tensor cores with
+// the weights as a tensor-memory operand (kq_gemv_tc.cu).
+bool gemv_tc_supported(int codec, int x_dtype, const GemvArgs& a);
+cudaError_t launch_gemv_tc(const GemvArgs& a, cudaStream_t st);
+cudaError_t read_device_error_tc(int* out, bool clear);
+
 // Prefill (M > 16) tile kernel on tcgen05 tensor cores with TMEM accumulators.
 // bf16 / f32 activations need gemm_workspace_bytes() of scratch for their fp16 copy.
 size_t gemm_workspace_bytes(int x_dtype, long long rows, int K);
