@@ -610,20 +610,33 @@ __global__ void __launch_bounds__(kRowsThreads, 4) gemv_q4k_m1_rows_kernel(const
   if (a.tasks == nullptr) pdl_wait();  // activations may come from the kernel before this one
 
   {
-    // all of K: pair-permute each 16-byte chunk and leave the fp32 sum of each 32-group
+    // all of K: pair-permute each 16-byte chunk and leave the fp32 sum of each 32-group.
+    // All loads are issued before the first use: one L2 round trip, not one per iteration.
     const __half* xrow = static_cast<const __half*>(a.x) + (long long)s_xrow[0] * a.x_row_stride;
-    for (int c = threadIdx.x; c < nchunks * 32; c += kRowsThreads) {
-      const uint4 v = __ldg(reinterpret_cast<const uint4*>(xrow + 8 * c));
-      const float2 p0 = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
-      const float2 p1 = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
-      const float2 p2 = __half22float2(*reinterpret_cast<const __half2*>(&v.z));
-      const float2 p3 = __half22float2(*reinterpret_cast<const __half2*>(&v.w));
-      float sum = ((p0.x + p0.y) + (p1.x + p1.y)) + ((p2.x + p2.y) + (p3.x + p3.y));
-      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      if ((c & 3) == 0) xsumf[c >> 2] = sum;
-      xs1[x_slot(0, c)] = make_uint4(__byte_perm(v.x, v.y, 0x5410), __byte_perm(v.x, v.y, 0x7632),
-                                     __byte_perm(v.z, v.w, 0x5410), __byte_perm(v.z, v.w, 0x7632));
+    constexpr int kIt = kRowsMaxK / 8 / kRowsThreads;
+    uint4 xv[kIt];
+#pragma unroll
+    for (int it = 0; it < kIt; it++) {
+      const int c = threadIdx.x + kRowsThreads * it;
+      xv[it] = make_uint4(0u, 0u, 0u, 0u);
+      if (c < nchunks * 32) xv[it] = __ldg(reinterpret_cast<const uint4*>(xrow + 8 * c));
+    }
+#pragma unroll
+    for (int it = 0; it < kIt; it++) {
+      const int c = threadIdx.x + kRowsThreads * it;
+      if (c < nchunks * 32) {  // uniform over a warp: 32 chunks per superblock
+        const uint4 v = xv[it];
+        const float2 p0 = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+        const float2 p1 = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+        const float2 p2 = __half22float2(*reinterpret_cast<const __half2*>(&v.z));
+        const float2 p3 = __half22float2(*reinterpret_cast<const __half2*>(&v.w));
+        float sum = ((p0.x + p0.y) + (p1.x + p1.y)) + ((p2.x + p2.y) + (p3.x + p3.y));
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        if ((c & 3) == 0) xsumf[c >> 2] = sum;
+        xs1[x_slot(0, c)] = make_uint4(__byte_perm(v.x, v.y, 0x5410), __byte_perm(v.x, v.y, 0x7632),
+                                       __byte_perm(v.z, v.w, 0x5410), __byte_perm(v.z, v.w, 0x7632));
+      }
     }
   }
   __syncthreads();
