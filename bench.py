@@ -49,13 +49,17 @@ K_COLS = 4096
 CODEC = "q4_k"
 ROW_BYTES = K_COLS // 256 * 144
 MATRIX_BYTES = N_ROWS * ROW_BYTES  # 9 437 184
+# the kernel that runs this workload, and its DRAM bytes per launch from the ncu capture summarised in
+# profiles/gemv_q4k_f16_decode.md (dram__bytes_read.sum + dram__bytes_write.sum)
+ROOFLINE_KERNEL = "gemv_q4k_m1_rows_kernel"
+ROOFLINE_TRAFFIC = 9469184
 
 
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--layers", type=int, default=64, help="distinct weight matrices per step")
     ap.add_argument("--m", type=int, default=1, help="activation rows (decode batch), <= 16")
@@ -80,7 +84,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -433,7 +437,7 @@ def run_b200(args):
                     "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
             "gpu_launches": args.steps * layers,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_kind": peak_kind, "traffic": 9463040, "kernel": "gemv_kernel<q4_k, f16, NT=1, FAST>",
+                         "peak_kind": peak_kind, "traffic": ROOFLINE_TRAFFIC, "kernel": ROOFLINE_KERNEL,
                          "algorithmic_bytes_per_launch": MATRIX_BYTES},
             "cpu_baseline": cpu,
             "clocks": clocks,
