@@ -31,6 +31,7 @@
 // Every mbarrier wait is bounded (2 s of %globaltimer): on expiry the CTA raises
 // a flag in g_kq_device_error, stops issuing work, frees its tensor memory and
 // returns, so a logic error can never leave the GPU spinning.
+#include <cooperative_groups.h>
 #include <cuda.h>
 
 #include <cstdio>
@@ -41,16 +42,22 @@
 #include "kq_launch.h"
 #include "kq_tcgen05.cuh"
 
+namespace cg = cooperative_groups;
+
 namespace kq {
 
 constexpr int kBN = 128;
 constexpr int kBK = 64;
 constexpr int kBStages = 3;            // weight-tile ring
-constexpr int kProducerThreads = 256;  // 8 warps: two threads per weight row, 32 weights each per K-step
-constexpr int kGemmThreads = kProducerThreads + 64;
-constexpr int kMmaWarp = kProducerThreads / 32;
-constexpr int kTmaWarp = kMmaWarp + 1;
-__host__ __device__ constexpr int a_slots(int MT, int NB) { return NB == 2 ? 6 : (MT == 1 ? 4 : 8); }  // activation-tile ring
+// Eight producer warps, then one MMA warp and one TMA warp. A 128-row weight tile has two producer
+// threads per row (32 weights each per K-step), a 256-row tile one (sixteen warps measured slower:
+// the kernel is bound by the L2 traffic of its activation tiles, not by the producers).
+__host__ __device__ constexpr int producer_threads(int) { return 256; }
+__host__ __device__ constexpr int gemm_threads(int NB) { return producer_threads(NB) + 64; }
+// activation-tile ring; the raw-block ring of the small-M kernels takes the room of four slots
+__host__ __device__ constexpr int a_slots(int MT, int NB, bool RAW = false) {
+  return NB == 2 ? 6 : (MT == 1 || RAW ? 4 : 8);
+}
 constexpr int kTileBytes = 128 * 128;  // 128 rows x 64 16-bit elements
 
 __device__ int g_kq_device_error = 0;
@@ -172,11 +179,19 @@ __device__ __forceinline__ void produce_w_q4k(const Q4kTileLoad& l, int kb, uint
 // Activations are always fp16 here (bf16 / f32 callers go through
 // convert_x_kernel first) and arrive through the tensor map. OT: output type.
 // NB: 128-row halves of the weight tile (UMMA N = 128 * NB); MT * NB <= 4 (512 TMEM columns).
-template <int C, int A, typename OT, int MT, int NB, bool FASTQ4>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+// RAW (q4_k fast producer, NB = 1, K-steps a multiple of 4): the wire blocks of the tile's 128 rows
+// stream through a four-superblock cp.async ring in shared memory instead of per-thread register
+// loads - at small M a CTA is alone on its SM and needs ~70 KB in flight to hide HBM latency.
+constexpr int kRawDepth = 4;
+constexpr int kRawSlot = 128 * 144;
+template <int C, int A, typename OT, int MT, int NB, bool FASTQ4, bool RAW = false>
+__global__ void __launch_bounds__(gemm_threads(NB), 1)
 gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
+  constexpr int kProducerThreads = producer_threads(NB), kGemmThreads = gemm_threads(NB);
+  constexpr int kMmaWarp = kProducerThreads / 32;
+  static_assert(!RAW || (FASTQ4 && NB == 1), "raw ring: q4_k fast producer, 128-row weight tiles");
   constexpr bool kHalf = std::is_same<OT, __half>::value;
-  constexpr int NA = a_slots(MT, NB);
+  constexpr int NA = a_slots(MT, NB, RAW);
   constexpr int BN = kBN * NB;
   constexpr int kBTile = NB * kTileBytes;
   constexpr bool kIq = (C == IQ4_NL || C == IQ4_XS || C == IQ2_XXS);
@@ -201,7 +216,9 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
     m_end = t.row_start + t.rows;
     wbase += (long long)t.expert * a.w_expert_stride;
   }
-  const int KB = (a.K + kBK - 1) / kBK;
+  // K-steps of this CTA: all of them, or slice blockIdx.z of gridDim.z equal slices (split K, below)
+  const int KB = (a.K + kBK - 1) / kBK / (int)gridDim.z;
+  const int kb0 = (int)blockIdx.z * KB;
   const int mt_live = min(MT, (m_end - m0 + 127) / 128);  // activation tiles of this CTA that hold rows
   constexpr uint32_t kTmemCols = MT * BN;               // 128, 256 or 512: a power of two >= 32
 
@@ -231,37 +248,83 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
     // ================= weight producers =================
     const int tid = threadIdx.x;
     // NB = 1: two threads per weight row (hh = which 32 of its 64 weights); NB = 2: one thread per row
-    const int wr = NB == 1 ? (tid & 127) : tid;
-    const int hh0 = NB == 1 ? (tid >> 7) : 0;
+    const int wr = tid % (128 * NB);   // weight row of the tile
+    const int hh0 = tid / (128 * NB);  // first 32-weight half of its 64 weights per K-step this thread makes
+    constexpr int kHalves = 256 * NB / kProducerThreads;  // and how many of them
     const uint8_t* wrow = wbase + (long long)min(n0 + wr, a.N - 1) * a.row_bytes;
     bool ok = true;
-    Q4kTileLoad cur{};
-    if constexpr (FASTQ4) cur = q4k_tile_load(wrow, 0);
-    for (int kb = 0; kb < KB && ok; kb++) {
-      const int s = kb % kBStages;
-      if (kb >= kBStages) ok = mbar_wait(&b_empty[s], ((kb / kBStages) & 1) ^ 1, abort_flag, 1);
-      if (!ok) break;
-      uint8_t* wdst = b_ring + s * kBTile + wr * 128;
-      if constexpr (FASTQ4) {
-        Q4kTileLoad nxt = cur;
-        if (kb + 1 < KB) nxt = q4k_tile_load(wrow, kb + 1);  // next K-step's bytes are requested first
+    uint8_t* raw = a_ring + NA * kTileBytes;
+    const int nsb = KB >> 2;
+    auto issue_sb = [&](int sbl) {  // one copy group per superblock, an empty one past the end
+      if (sbl < nsb) {
+        uint8_t* slot = raw + (sbl % kRawDepth) * kRawSlot;
 #pragma unroll
-        for (int hh = hh0; hh < hh0 + NB; hh++) produce_w_q4k(cur, kb, wdst, wr, hh);
+        for (int i = 0; i < 5; i++) {
+          const int piece = tid + kProducerThreads * i;  // 1152 16-byte pieces, contiguous in the slot
+          if (piece < 1152) {
+            const int row = piece / 9, pc = piece % 9;
+            const uint8_t* src = wbase + (long long)min(n0 + row, a.N - 1) * a.row_bytes +
+                                 (long long)((kb0 >> 2) + sbl) * 144 + pc * 16;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(slot + piece * 16)), "l"(src)
+                         : "memory");
+          }
+        }
+      }
+      asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+    if constexpr (RAW) {
+      for (int d = 0; d < kRawDepth; d++) issue_sb(d);
+    }
+    Q4kTileLoad cur{};
+    if constexpr (FASTQ4 && !RAW) cur = q4k_tile_load(wrow, kb0);
+    {
+    for (int it = 0; it < KB && (ok || RAW); it++) {
+      const int kb = kb0 + it;
+      const int s = it % kBStages;
+      if constexpr (RAW) {
+        // Every producer passes every superblock barrier, also after a failed wait: nobody is left behind.
+        if ((it & 3) == 0) {
+          asm volatile("cp.async.wait_group %0;\n" ::"n"(kRawDepth - 2) : "memory");
+          asm volatile("bar.sync 1, %0;\n" ::"n"(kProducerThreads) : "memory");  // data landed, previous slot read
+          if (it > 0) issue_sb((it >> 2) - 1 + kRawDepth);
+        }
+        if (ok && it >= kBStages) ok = mbar_wait(&b_empty[s], ((it / kBStages) & 1) ^ 1, abort_flag, 1);
+        if (!ok) continue;
+      } else {
+        if (it >= kBStages) ok = mbar_wait(&b_empty[s], ((it / kBStages) & 1) ^ 1, abort_flag, 1);
+        if (!ok) break;
+      }
+      uint8_t* wdst = b_ring + s * kBTile + wr * 128;
+      if constexpr (RAW) {
+        const uint8_t* blk = raw + ((it >> 2) % kRawDepth) * kRawSlot + wr * 144;
+        Q4kTileLoad l;
+        l.hdr = *reinterpret_cast<const uint4*>(blk);
+        l.q0 = *reinterpret_cast<const uint4*>(blk + 16 + 32 * (it & 3));
+        l.q1 = *reinterpret_cast<const uint4*>(blk + 32 + 32 * (it & 3));
+        produce_w_q4k(l, kb, wdst, wr, hh0);
+      } else if constexpr (FASTQ4) {
+        Q4kTileLoad nxt = cur;
+        if (it + 1 < KB) nxt = q4k_tile_load(wrow, kb + 1);  // next K-step's bytes are requested first
+#pragma unroll
+        for (int hh = hh0; hh < hh0 + kHalves; hh++)
+          produce_w_q4k(cur, kb, wdst, wr, hh);
         cur = nxt;
       } else {
 #pragma unroll
-        for (int hh = hh0; hh < hh0 + NB; hh++) produce_w_generic<C, A>(wrow, kb, a.K, wdst, wr, hh, tabs);
+        for (int hh = hh0; hh < hh0 + kHalves; hh++) produce_w_generic<C, A>(wrow, kb, a.K, wdst, wr, hh, tabs);
       }
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(&b_full[s]);
+    }
     }
     // ================= epilogue =================
     if (ok) ok = mbar_wait(&accum_bar, 0, abort_flag, 4);
     if (ok) {
       tc_fence_after();
       const int lq = warp & 3;                   // TMEM lane quarter this warp may read
-      const int cbeg = (warp >> 2) * (BN / 2);   // warps 0-3: lower half of the columns, warps 4-7: upper half
+      constexpr int kColSpan = BN / (kProducerThreads / 128);  // four warps (one per lane quarter) per column span
+      const int cbeg = (warp >> 2) * kColSpan;
 #pragma unroll 1
       for (int h = 0; h < mt_live; h++) {
         const int row = m0 + h * 128 + lq * 32 + lane;
@@ -271,11 +334,23 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
         const bool vec_ok = ((reinterpret_cast<uintptr_t>(yrow) & 15) == 0);
         const float rs = (a.row_scale && live) ? a.row_scale[row] : 1.f;
 #pragma unroll 1
-        for (int c0 = cbeg; c0 < cbeg + BN / 2; c0 += 16) {
+        for (int c0 = cbeg; c0 < cbeg + kColSpan; c0 += 16) {
           uint32_t v[16];
           tmem_ld16(tmem_base + ((uint32_t)(lq * 32) << 16) + (uint32_t)(h * BN + c0), v);
           tmem_ld_wait();
-          if (live) {
+          if (gridDim.z > 1) {
+            // split K: this CTA's partial tile goes to shared memory (the rings are idle now) as fp32
+            // [rows][128], 16-byte chunks XOR-swizzled by the row so that a warp's stores spread over the banks
+            if constexpr (NB == 1) {
+              const int rl = h * 128 + lq * 32 + lane;
+              float* srow = reinterpret_cast<float*>(tiles) + rl * 128;
+#pragma unroll
+              for (int i = 0; i < 4; i++)
+                *reinterpret_cast<float4*>(srow + 4 * (((c0 >> 2) + i) ^ (rl & 31))) =
+                    make_float4(__uint_as_float(v[4 * i]) * rs, __uint_as_float(v[4 * i + 1]) * rs,
+                                __uint_as_float(v[4 * i + 2]) * rs, __uint_as_float(v[4 * i + 3]) * rs);
+            }
+          } else if (live) {
             uint32_t o[8];
 #pragma unroll
             for (int i = 0; i < 8; i++) {
@@ -304,7 +379,7 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
     constexpr uint32_t idesc = umma_idesc(0u, BN);
     bool ok = true;
     int t = 0;  // running activation-tile number
-    for (int kb = 0; kb < KB && ok; kb++) {
+    for (int kb = 0; kb < KB && ok; kb++) {  // kb counts this CTA's own K-steps
       const int s = kb % kBStages;
       ok = mbar_wait(&b_full[s], (kb / kBStages) & 1, abort_flag, 2);
       if (!ok) break;
@@ -341,7 +416,7 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
         if (!ok) break;
         if (lane == 0) {
           mbar_expect_tx(&a_full[slot], kTileBytes);
-          tma_load_2d(a_ring + slot * kTileBytes, &tmap_x, kb * kBK, m0 + h * 128, &a_full[slot]);
+          tma_load_2d(a_ring + slot * kTileBytes, &tmap_x, (kb0 + kb) * kBK, m0 + h * 128, &a_full[slot]);
         }
         __syncwarp();
       }
@@ -351,6 +426,45 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
       const int first = t > NA ? t - NA : 0;
       for (int u = first; u < t; u++)
         if (!mbar_wait(&a_full[u % NA], (u / NA) & 1, abort_flag, 64)) break;
+    }
+  }
+
+  // ================= split K: the slices of a cluster meet through distributed shared memory =================
+  if (gridDim.z > 1) {
+    if constexpr (NB == 1) {
+      cg::cluster_group cluster = cg::this_cluster();
+      tc_fence_before();
+      cluster.sync();  // every slice's partial tile is in its shared memory
+      const int S = (int)gridDim.z, z = (int)blockIdx.z;
+      if (warp < kMmaWarp) {
+        const float* peer[8];
+#pragma unroll
+        for (int q = 0; q < 8; q++)
+          peer[q] = q < S ? cluster.map_shared_rank(reinterpret_cast<float*>(tiles), q) : nullptr;
+        const int c = threadIdx.x & 31;  // 16-byte chunk = four columns
+        for (int rl = z + S * (threadIdx.x >> 5); rl < mt_live * 128; rl += S * (kProducerThreads / 32)) {
+          const int row = m0 + rl;
+          if (row >= m_end) continue;
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int q = 0; q < 8; q++) {
+            if (q < S) {
+              const float4 v = *reinterpret_cast<const float4*>(peer[q] + rl * 128 + 4 * (c ^ (rl & 31)));
+              acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
+            }
+          }
+          OT* yp = static_cast<OT*>(a.y) + (long long)row * a.y_row_stride + n0 + 4 * c;
+          const float f[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            if (n0 + 4 * c + i < a.N) {
+              if constexpr (kHalf) yp[i] = __float2half_rn(f[i]);
+              else yp[i] = __float2bfloat16_rn(f[i]);
+            }
+          }
+        }
+      }
+      cluster.sync();  // peers may still be reading this CTA's partial tile
     }
   }
 
@@ -458,10 +572,10 @@ static cudaError_t make_x_map(CUtensorMap* map, const void* x, long long x_row_s
   return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-template <int C, int A, typename OT, int MT, int NB, bool FASTQ4>
-static cudaError_t launch_g(const GemmArgs& a, cudaStream_t st, int grid_y = 0) {
-  auto kern = gemm_kernel<C, A, OT, MT, NB, FASTQ4>;
-  const size_t dyn = (size_t)(kBStages * NB + a_slots(MT, NB)) * kTileBytes + 1024;
+template <int C, int A, typename OT, int MT, int NB, bool FASTQ4, bool RAW = false>
+static cudaError_t launch_g(const GemmArgs& a, cudaStream_t st, int grid_y = 0, int ksplit = 1) {
+  auto kern = gemm_kernel<C, A, OT, MT, NB, FASTQ4, RAW>;
+  const size_t dyn = (size_t)(kBStages * NB + a_slots(MT, NB, RAW)) * kTileBytes + 1024 + (RAW ? kRawDepth * kRawSlot : 0);
   static bool attr_set[16] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -473,9 +587,26 @@ static cudaError_t launch_g(const GemmArgs& a, cudaStream_t st, int grid_y = 0) 
   alignas(64) CUtensorMap map;
   cudaError_t e = make_x_map(&map, a.x, a.x_row_stride, a.M, a.K);
   if (e != cudaSuccess) return e;
-  const dim3 grid((a.N + kBN * NB - 1) / (kBN * NB), grid_y > 0 ? grid_y : (a.M + 128 * MT - 1) / (128 * MT));
-  kern<<<grid, kGemmThreads, dyn, st>>>(a, map);
-  return cudaGetLastError();
+  if (NB != 1) ksplit = 1;
+  const dim3 grid((a.N + kBN * NB - 1) / (kBN * NB), grid_y > 0 ? grid_y : (a.M + 128 * MT - 1) / (128 * MT), ksplit);
+  if (ksplit == 1) {
+    kern<<<grid, gemm_threads(NB), dyn, st>>>(a, map);
+    return cudaGetLastError();
+  }
+  // split K: the ksplit CTAs of one output tile form a cluster
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(gemm_threads(NB));
+  cfg.dynamicSmemBytes = dyn;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = ksplit;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, a, map);
 }
 
 template <int C, int A, bool FASTQ4>
@@ -492,12 +623,35 @@ static cudaError_t launch_shape(bool out_half, const GemmArgs& a, cudaStream_t s
     const int v = std::atoi(env);
     if (v == 1 || v == 2 || v == 4 || v == 22) mt = v;
   }
-#define KQ_TILE(OT)                                              \
-  do {                                                           \
-    if (mt == 22) return launch_g<C, A, OT, 2, 2, FASTQ4>(a, st); \
-    if (mt == 4) return launch_g<C, A, OT, 4, 1, FASTQ4>(a, st);  \
-    if (mt == 2) return launch_g<C, A, OT, 2, 1, FASTQ4>(a, st);  \
-    return launch_g<C, A, OT, 1, 1, FASTQ4>(a, st);               \
+  // Few output tiles (small M on a matrix with few 128-row groups): split K over a cluster so that
+  // the weights stream through more SMs. The slices must be equal: K-steps % ksplit == 0.
+  int ksplit = 1;
+  if (mt == 1 || mt == 2) {
+    const long long ctas = n_tiles * ((a.M + 128 * mt - 1) / (128 * mt));
+    const int kb_total = (a.K + kBK - 1) / kBK;
+    while (ksplit < 8 && ctas * ksplit * 2 <= 160 && kb_total % (ksplit * 2) == 0 && kb_total / (ksplit * 2) >= 4)
+      ksplit *= 2;
+  }
+  if (FASTQ4)
+    while (ksplit > 1 && ((a.K / 256) % ksplit) != 0) ksplit >>= 1;  // q4_k producers work in whole superblocks
+  if (const char* env = std::getenv("KQ_GEMM_KSPLIT")) {  // A/B lever
+    const int v = std::atoi(env);
+    const int kb_total = (a.K + kBK - 1) / kBK;
+    if ((v == 1 || v == 2 || v == 4 || v == 8) && kb_total % v == 0 && (!FASTQ4 || (a.K / 256) % v == 0)) ksplit = v;
+  }
+  // raw-block ring: whole superblocks per slice and rows that are whole numbers of 16 bytes
+  static const bool no_raw = std::getenv("KQ_GEMM_NO_RAW") != nullptr;  // A/B lever
+  const bool raw_ok = FASTQ4 && !no_raw && (a.K % 256) == 0 && ((a.K / 256) % ksplit) == 0 && (a.row_bytes % 16) == 0;
+#define KQ_TILE(OT)                                                          \
+  do {                                                                       \
+    if (mt == 22) return launch_g<C, A, OT, 2, 2, FASTQ4>(a, st);             \
+    if (mt == 4) return launch_g<C, A, OT, 4, 1, FASTQ4>(a, st);              \
+    if constexpr (FASTQ4) {                                                  \
+      if (raw_ok && mt == 2) return launch_g<C, A, OT, 2, 1, true, true>(a, st, 0, ksplit); \
+      if (raw_ok) return launch_g<C, A, OT, 1, 1, true, true>(a, st, 0, ksplit);            \
+    }                                                                        \
+    if (mt == 2) return launch_g<C, A, OT, 2, 1, FASTQ4>(a, st, 0, ksplit);   \
+    return launch_g<C, A, OT, 1, 1, FASTQ4>(a, st, 0, ksplit);                \
   } while (0)
   if (out_half) KQ_TILE(__half);
   KQ_TILE(__nv_bfloat16);
