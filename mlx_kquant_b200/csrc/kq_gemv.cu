@@ -370,7 +370,7 @@ __device__ __forceinline__ void q4k_compute(const Q4kLoad& l, const uint4* xs, c
 //   y += d * (sc0 (D0 - 1024 xs0) + sc1 (D1 - 64 xs1)) - dmin * (mn0 xs0 + mn1 xs1).
 __device__ __forceinline__ float byte_to_float(uint32_t v, int byte) {
   // 0x4B0000bb is 2^23 + bb exactly
-  return __uint_as_float(__byte_perm(v, 0x4B000000u, byte == 0 ? 0x7440 : 0x7441)) - 8388608.f;
+  return __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7440 + byte)) - 8388608.f;
 }
 
 // qa0/qa1, qb0/qb1: the lane's 32 quant bytes of its two rows; hA/hB: the two block headers.
@@ -678,6 +678,186 @@ __global__ void __launch_bounds__(kRowsThreads, 4) gemv_q4k_m1_rows_kernel(const
 #pragma unroll
     for (int w = 0; w < kRowsWarps; w++) sum += red[w * 16 + threadIdx.x];
     static_cast<__half*>(a.y)[(long long)s_yrow[0] * a.y_row_stride + row0 + threadIdx.x] = __float2half_rn(sum);
+  }
+}
+
+// ---- one activation row on the integer dot-product pipe ------------------------------
+// With a single activation row the tensor-core formulations above waste seven of eight MMA
+// columns, and the legacy tensor pipe, not HBM, bounds them. Here the products run on dp4a
+// instead: the activations of each 32-group are quantized once per CTA to 16-bit integers with
+// the group's own scale (xi = rint(x * 32767 / max|x|), |error| <= 2^-16 of the group maximum -
+// far below the fp16 / bf16 rounding the activations already carry) and stored as two int8 planes
+// (xi = 256 xh + xl). One three-input logic op then yields FOUR weights (W & 0x0f0f0f0f), one
+// dp4a per plane multiplies them; the integer sums are exact, and scale, 6-bit sub-block scales,
+// d and dmin are applied in fp32 per sub-block (src/kquant_cpu_decode.cpp:155-174, 177-202).
+// Thread = weight row (a warp owns 32 rows), the eight warps of a CTA split K and meet in shared
+// memory. Works for fp16, bf16 and float activations alike (float is rounded to bf16 first, as
+// the op does, src/kquant_ops.cpp:159-168).
+constexpr int kDpWarps = 8, kDpThreads = 32 * kDpWarps, kDpRows = 32, kDpSlot = kDpRows * 144;
+constexpr int kDpMaxK = 16384;
+static inline int dp_dyn_smem(int K, int D) { return kDpWarps * D * kDpSlot + 2 * K + 2 * (K / 32) * 4; }
+
+template <typename XT>
+__global__ void __launch_bounds__(kDpThreads, 2) gemv_q4k_m1_dp4a_kernel(const GemvArgs a, const int D) {
+  using OT = typename std::conditional<std::is_same<XT, __half>::value, __half, __nv_bfloat16>::type;
+  __shared__ float red[kDpWarps][kDpRows];
+  extern __shared__ __align__(16) uint8_t dyn_smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nchunks = a.K >> 8;
+  uint32_t* XH = reinterpret_cast<uint32_t*>(dyn_smem + kDpWarps * D * kDpSlot);  // high bytes, four per word
+  uint32_t* XL = XH + a.K / 4;                                                    // low bytes
+  float* SG = reinterpret_cast<float*>(XL + a.K / 4);                             // scale of each 32-group
+  float* XS = SG + a.K / 32;                                                      // sum of each 32-group
+  const int row0 = blockIdx.x * kDpRows;
+  const int per = (nchunks + kDpWarps - 1) / kDpWarps;
+  const int ch0 = min(warp * per, nchunks), ch1 = min(ch0 + per, nchunks);
+
+  // Per-warp ring of D superblocks x 32 rows; every issue() commits exactly one copy group.
+  uint8_t* ring = dyn_smem + warp * D * kDpSlot;
+  const uint8_t* src[9];
+#pragma unroll
+  for (int i = 0; i < 9; i++) {
+    const int j = lane + 32 * i;  // 288 16-byte pieces per superblock, contiguous in the slot
+    src[i] = a.w + (long long)min(row0 + j / 9, a.N - 1) * a.row_bytes + (long long)ch0 * 144 + (j % 9) * 16;
+  }
+  int issued = ch0;
+  auto issue = [&](uint8_t* slot) {
+    if (issued < ch1) {
+#pragma unroll
+      for (int i = 0; i < 9; i++) {
+        cp_async16(slot + 16 * (lane + 32 * i), src[i]);
+        src[i] += 144;
+      }
+      issued++;
+    }
+    cp_async_commit();
+  };
+  for (int d = 0; d < D; d++) issue(ring + d * kDpSlot);
+  pdl_launch_dependents();
+  pdl_wait();  // activations may come from the kernel before this one
+
+  {
+    // quantize all of K: eight activations per thread and step, four threads per 32-group
+    const XT* xrow = static_cast<const XT*>(a.x);
+    for (int c = threadIdx.x; c < a.K / 8; c += kDpThreads) {
+      float v[8];
+      if constexpr (std::is_same<XT, float>::value) {
+        const float4 f0 = __ldg(reinterpret_cast<const float4*>(xrow + 8 * c));
+        const float4 f1 = __ldg(reinterpret_cast<const float4*>(xrow + 8 * c) + 1);
+        const float f[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = __bfloat162float(__float2bfloat16_rn(f[i]));
+      } else {
+        const uint4 u = __ldg(reinterpret_cast<const uint4*>(xrow + 8 * c));
+        const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+          float2 f;
+          if constexpr (std::is_same<XT, __half>::value) f = __half22float2(*reinterpret_cast<const __half2*>(&w4[i]));
+          else f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w4[i]));
+          v[2 * i] = f.x;
+          v[2 * i + 1] = f.y;
+        }
+      }
+      float amax = 0.f, sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        amax = fmaxf(amax, fabsf(v[i]));
+        sum += v[i];
+      }
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      const bool finite = amax > 0.f && amax < INFINITY;
+      // the reciprocal need not be exact: xi * scale reproduces v to ~1e-7 either way
+      const float inv = finite ? 32767.f * __frcp_rn(amax) : 0.f;
+      uint32_t h[2] = {0u, 0u}, l[2] = {0u, 0u};
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const int xi = __float2int_rn(v[i] * inv);
+        h[i >> 2] |= ((uint32_t)(xi >> 8) & 0xffu) << (8 * (i & 3));
+        l[i >> 2] |= ((uint32_t)xi & 0xffu) << (8 * (i & 3));
+      }
+      *reinterpret_cast<uint2*>(XH + 2 * c) = make_uint2(h[0], h[1]);
+      *reinterpret_cast<uint2*>(XL + 2 * c) = make_uint2(l[0], l[1]);
+      if ((c & 3) == 0) {
+        // a group holding inf / nan keeps them: the scale carries the non-finite value into the sum
+        SG[c >> 2] = finite ? amax * (1.f / 32767.f) : (amax > 0.f ? amax : 0.f);
+        XS[c >> 2] = sum;
+      }
+    }
+  }
+  __syncthreads();
+
+  float y = 0.f;
+  for (int sb = ch0; sb < ch1; sb++) {
+    const int rel = sb - ch0;
+    cp_async_wait(D - 1);
+    __syncwarp();
+    uint8_t* slot = ring + (rel % D) * kDpSlot;
+    const uint4* blk = reinterpret_cast<const uint4*>(slot + lane * 144);
+    const uint4 hdr = blk[0];
+    uint4 q[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) q[i] = blk[1 + i];
+    __syncwarp();  // the slot is free again
+    issue(slot);
+    // eight 6-bit (scale, min) pairs from twelve bytes, four at a time
+    const uint32_t u0 = hdr.y, u1 = hdr.z, u2 = hdr.w;
+    const uint32_t scl = u0 & 0x3f3f3f3fu, mnl = u1 & 0x3f3f3f3fu;
+    const uint32_t sch = (u2 & 0x0f0f0f0fu) | ((u0 >> 2) & 0x30303030u);
+    const uint32_t mnh = ((u2 >> 4) & 0x0f0f0f0fu) | ((u1 >> 2) & 0x30303030u);
+    const uint4* xh4 = reinterpret_cast<const uint4*>(XH + sb * 64);
+    const uint4* xl4 = reinterpret_cast<const uint4*>(XL + sb * 64);
+    const float4* sg4 = reinterpret_cast<const float4*>(SG + sb * 8);
+    const float4* xs4 = reinterpret_cast<const float4*>(XS + sb * 8);
+    const float4 sga = sg4[0], sgb = sg4[1], xsa = xs4[0], xsb = xs4[1];
+    const float sg[8] = {sga.x, sga.y, sga.z, sga.w, sgb.x, sgb.y, sgb.z, sgb.w};
+    const float xs[8] = {xsa.x, xsa.y, xsa.z, xsa.w, xsb.x, xsb.y, xsb.z, xsb.w};
+    float t1 = 0.f, t2 = 0.f;
+#pragma unroll
+    for (int p = 0; p < 4; p++) {
+      // 32 bytes: low nibbles are sub-block 2p, high nibbles sub-block 2p + 1, weights in natural order
+      const uint32_t w[8] = {q[2 * p].x, q[2 * p].y, q[2 * p].z, q[2 * p].w,
+                             q[2 * p + 1].x, q[2 * p + 1].y, q[2 * p + 1].z, q[2 * p + 1].w};
+      const uint4 ha0 = xh4[4 * p], ha1 = xh4[4 * p + 1], hb0 = xh4[4 * p + 2], hb1 = xh4[4 * p + 3];
+      const uint4 la0 = xl4[4 * p], la1 = xl4[4 * p + 1], lb0 = xl4[4 * p + 2], lb1 = xl4[4 * p + 3];
+      const uint32_t xha[8] = {ha0.x, ha0.y, ha0.z, ha0.w, ha1.x, ha1.y, ha1.z, ha1.w};
+      const uint32_t xhb[8] = {hb0.x, hb0.y, hb0.z, hb0.w, hb1.x, hb1.y, hb1.z, hb1.w};
+      const uint32_t xla[8] = {la0.x, la0.y, la0.z, la0.w, la1.x, la1.y, la1.z, la1.w};
+      const uint32_t xlb[8] = {lb0.x, lb0.y, lb0.z, lb0.w, lb1.x, lb1.y, lb1.z, lb1.w};
+      int ah_lo = 0, ah_hi = 0;
+      unsigned al_lo = 0u, al_hi = 0u;
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const uint32_t lo = w[j] & 0x0f0f0f0fu, hi = (w[j] >> 4) & 0x0f0f0f0fu;
+        ah_lo = __dp4a((int)lo, (int)xha[j], ah_lo);
+        al_lo = __dp4a(lo, xla[j], al_lo);
+        ah_hi = __dp4a((int)hi, (int)xhb[j], ah_hi);
+        al_hi = __dp4a(hi, xlb[j], al_hi);
+      }
+      const float f_lo = (float)(ah_lo * 256 + (int)al_lo), f_hi = (float)(ah_hi * 256 + (int)al_hi);
+      const float sc_lo = byte_to_float(p < 2 ? scl : sch, 2 * (p & 1)), sc_hi = byte_to_float(p < 2 ? scl : sch, 2 * (p & 1) + 1);
+      const float mn_lo = byte_to_float(p < 2 ? mnl : mnh, 2 * (p & 1)), mn_hi = byte_to_float(p < 2 ? mnl : mnh, 2 * (p & 1) + 1);
+      t1 = fmaf(sc_lo * sg[2 * p], f_lo, t1);
+      t1 = fmaf(sc_hi * sg[2 * p + 1], f_hi, t1);
+      t2 = fmaf(mn_lo, xs[2 * p], t2);
+      t2 = fmaf(mn_hi, xs[2 * p + 1], t2);
+    }
+    const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(&hdr.x));  // (d, dmin)
+    y = fmaf(dd.x, t1, y);
+    y = fmaf(-dd.y, t2, y);
+  }
+  red[warp][lane] = y;
+  __syncthreads();
+  if (warp == 0 && row0 + lane < a.N) {
+    float sum = 0.f;
+#pragma unroll
+    for (int w = 0; w < kDpWarps; w++) sum += red[w][lane];
+    OT* out = static_cast<OT*>(a.y) + row0 + lane;
+    if constexpr (std::is_same<OT, __half>::value) *out = __float2half_rn(sum);
+    else *out = __float2bfloat16_rn(sum);
   }
 }
 
@@ -1292,6 +1472,34 @@ static cudaError_t launch_m1_rows(const GemvArgs& a, cudaStream_t st) {
   return cudaLaunchKernelEx(&cfg, gemv_q4k_m1_rows_kernel, a);
 }
 
+template <typename XT>
+static cudaError_t launch_m1_dp4a(const GemvArgs& a, cudaStream_t st) {
+  const int nchunks = a.K >> 8;
+  const int per = (nchunks + kDpWarps - 1) / kDpWarps;
+  const int D = per < 2 ? 1 : 2;  // 74 KB of ring: two CTAs per SM
+  static bool attr_set[16] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 16 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(gemv_q4k_m1_dp4a_kernel<XT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         dp_dyn_smem(kDpMaxK, 2));
+    if (e != cudaSuccess) return e;
+    attr_set[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((a.N + kDpRows - 1) / kDpRows, 1, 1);
+  cfg.blockDim = dim3(kDpThreads);
+  cfg.dynamicSmemBytes = dp_dyn_smem(a.K, D);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  static const bool no_pdl = std::getenv("KQ_NO_PDL") != nullptr;  // A/B lever
+  cfg.numAttrs = no_pdl ? 0 : 1;
+  return cudaLaunchKernelEx(&cfg, gemv_q4k_m1_dp4a_kernel<XT>, a, D);
+}
+
 template <int C, int NAT>
 static cudaError_t launch_generic(int x_dtype, const GemvArgs& a, dim3 grid, bool nt2, bool aligned, cudaStream_t st) {
 #define KQ_GV(AL, XT) \
@@ -1334,6 +1542,17 @@ cudaError_t launch_gemv(int codec, int x_dtype, const GemvArgs& a, cudaStream_t 
   const bool nt2 = a.tasks ? (a.max_m > 8) : (a.M > 8);
   const bool aligned = a.w_align16 != 0;
 
+  // one dense activation row of q4_k: the integer dot-product kernel. A/B lever: KQ_GEMV_DP4A=0|1.
+  // Measured: it wins up to ~60 M weights against the fp16 tensor-core kernels below (which win
+  // beyond), and always against the generic path that bf16 / float activations would take.
+  static const char* dp_env = std::getenv("KQ_GEMV_DP4A");
+  const bool dp_on = dp_env ? dp_env[0] == '1' : (x_dtype != F16 || (long long)a.N * a.K <= (60ll << 20));
+  if (dp_on && codec == Q4_K && aligned && a.tasks == nullptr && a.M == 1 && (a.K & 255) == 0 && a.K <= kDpMaxK &&
+      (a.row_bytes & 15) == 0) {
+    if (x_dtype == F16) return launch_m1_dp4a<__half>(a, st);
+    if (x_dtype == BF16) return launch_m1_dp4a<__nv_bfloat16>(a, st);
+    return launch_m1_dp4a<float>(a, st);
+  }
   static const char* tc_env = std::getenv("KQ_GEMV_TC");  // A/B lever: 1 = tensor-memory decode kernel
   if (tc_env && tc_env[0] == '1' && gemv_tc_supported(codec, x_dtype, a)) return launch_gemv_tc(a, st);
   static const bool no_m1 = std::getenv("KQ_GEMV_NO_M1") != nullptr;  // A/B lever
