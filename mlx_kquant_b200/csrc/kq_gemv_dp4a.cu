@@ -1,8 +1,9 @@
-// Single-row decode products on the integer dot-product pipe, for the codecs that have no
-// tensor-core fast path: q2_k q3_k q5_k q6_k q4_0 q8_0 iq4_nl iq4_xs.
+// Decode products for one to four activation rows on the integer dot-product pipe, for the codecs
+// that have no tensor-core fast path: q2_k q3_k q5_k q6_k q4_0 q8_0 iq4_nl iq4_xs iq2_xxs.
 //
 // Every one of these formats stores small integers times a per-group scale (minus a per-group
-// minimum for q2_k / q5_k), src/kquant_cpu_decode.cpp:50-82, 205-377, 383-465. So
+// minimum for q2_k / q5_k; iq2_xxs: signed 8-weight lattice points), src/kquant_cpu_decode.cpp:50-82,
+// 205-377, 383-465, 557-584. So
 //   y[n] = sum_groups  scale_g * sum_k (q_k - off) x_k  -  min_g * sum_k x_k
 // and the inner sums run on dp4a once the activations are integers too: each 32-group of x is
 // quantized once per CTA to 16 bits with the group's own scale (xi = rint(x * 32767 / max|x|),
@@ -65,14 +66,17 @@ template <> struct Geom<Q4_0> { static constexpr int kCB = 144, kP = 9; };
 template <> struct Geom<Q8_0> { static constexpr int kCB = 272, kP = 17; };
 template <> struct Geom<IQ4_NL> { static constexpr int kCB = 144, kP = 9; };
 template <> struct Geom<IQ4_XS> { static constexpr int kCB = 136, kP = 9; };
+template <> struct Geom<IQ2_XXS> { static constexpr int kCB = 66, kP = 5; };
 
-// The activations of one chunk, as the products need them.
+// The activations of one chunk for MT rows of x, as the products need them. Row t is t * stride further.
 struct XChunk {
-  const uint4* xh;   // 64 words: high bytes, four weights per word
-  const uint4* xl;   // 64 words: low bytes
-  const float* sg;   // 8: scale of each 32-group
-  const int* xi16;   // 16: integer sum of each 16-group
-  const float* xs16; // 16: float sum of each 16-group
+  const uint4* xh;    // 16 uint4: high bytes, four weights per word, a 16-group per uint4
+  const uint4* xl;    // 16 uint4: low bytes
+  const float* sg;    // 8: scale of each 32-group
+  const int* xi16;    // 16: integer sum of each 16-group
+  const float* xs16;  // 16: float sum of each 16-group
+  int plane_stride;   // uint4 between rows of x in xh / xl
+  int sg_stride, s16_stride;
 };
 
 // Reader of a chunk whose first byte sits PH2 (0 or 2) bytes after the 4-byte-aligned `base`.
@@ -108,24 +112,41 @@ __device__ __forceinline__ int dot16(const uint32_t (&q)[4], const uint4 xh, con
   return hi * 256 + lo;
 }
 
-// ---- per-codec chunk products: returns this chunk's contribution to y ----------------------
-template <int C, int PH2>
-__device__ __forceinline__ float chunk_dot(const Bytes<PH2> B, const XChunk& X, const uint32_t (&T)[4]) {
-  float acc = 0.f;
+// acc[t] += scale * sum_k (q_k - off) x_k over 16-group g16, for every row t of x
+template <bool SIGNED, int MT>
+__device__ __forceinline__ void accum16(const uint32_t (&q)[4], int g16, float scale, int off, const XChunk& X,
+                                        float (&acc)[MT]) {
+#pragma unroll
+  for (int t = 0; t < MT; t++) {
+    int s = dot16<SIGNED>(q, X.xh[t * X.plane_stride + g16], X.xl[t * X.plane_stride + g16]);
+    if (off != 0) s -= off * X.xi16[t * X.s16_stride + g16];
+    acc[t] = fmaf(scale * X.sg[t * X.sg_stride + (g16 >> 1)], (float)s, acc[t]);
+  }
+}
+// acc[t] -= mn * sum_k x_k over 16-group g16
+template <int MT>
+__device__ __forceinline__ void accum_min(int g16, float mn, const XChunk& X, float (&acc)[MT]) {
+#pragma unroll
+  for (int t = 0; t < MT; t++) acc[t] = fmaf(-mn, X.xs16[t * X.s16_stride + g16], acc[t]);
+}
+
+// ---- per-codec chunk products: adds this chunk's contribution to acc[t] ---------------------
+// T: the 16-level table of the iq4 codecs in four registers; grid: the iq2_xxs lattice in shared memory.
+template <int C, int PH2, int MT>
+__device__ __forceinline__ void chunk_dot(const Bytes<PH2> B, const XChunk& X, const uint32_t (&T)[4],
+                                          const uint2* grid, float (&acc)[MT]) {
   if constexpr (C == Q8_0) {
     // eight blocks [f16 d][32 x int8]
 #pragma unroll
     for (int b = 0; b < 8; b++) {
       const float d = f16_bits(B.h(34 * b));
-      int s = 0;
 #pragma unroll
       for (int hlf = 0; hlf < 2; hlf++) {
         uint32_t q[4];
 #pragma unroll
         for (int i = 0; i < 4; i++) q[i] = B.w(34 * b + 2 + 16 * hlf + 4 * i);
-        s += dot16<true>(q, X.xh[2 * b + hlf], X.xl[2 * b + hlf]);  // a 16-group's plane = four words = one uint4
+        accum16<true, MT>(q, 2 * b + hlf, d, 0, X, acc);
       }
-      acc = fmaf(d * X.sg[b], (float)s, acc);
     }
   } else if constexpr (C == Q4_0) {
     // eight blocks [f16 d][16 B]: low nibble -> weight i, high nibble -> weight i + 16, minus 8
@@ -139,9 +160,8 @@ __device__ __forceinline__ float chunk_dot(const Bytes<PH2> B, const XChunk& X, 
         lo[i] = W & 0x0f0f0f0fu;
         hi[i] = (W >> 4) & 0x0f0f0f0fu;
       }
-      const int s = dot16<false>(lo, X.xh[2 * b], X.xl[2 * b]) + dot16<false>(hi, X.xh[2 * b + 1], X.xl[2 * b + 1]) -
-                    8 * (X.xi16[2 * b] + X.xi16[2 * b + 1]);
-      acc = fmaf(d * X.sg[b], (float)s, acc);
+      accum16<false, MT>(lo, 2 * b, d, 8, X, acc);
+      accum16<false, MT>(hi, 2 * b + 1, d, 8, X, acc);
     }
   } else if constexpr (C == IQ4_NL || C == IQ4_XS) {
     // 16 bytes per 32-group: low nibble -> weight i, high nibble -> weight i + 16, through the 16-level
@@ -155,7 +175,7 @@ __device__ __forceinline__ float chunk_dot(const Bytes<PH2> B, const XChunk& X, 
       asm("lop3.b32 %0, %1, %2, %3, 0xCA;\n" : "=r"(v) : "r"(m), "r"(vhi), "r"(vlo));
       return v;
     };
-    float d;
+    float d = 0.f;
     uint32_t sh = 0, sl = 0;
     if constexpr (C == IQ4_XS) {
       d = f16_bits(B.h(0));
@@ -184,8 +204,31 @@ __device__ __forceinline__ float chunk_dot(const Bytes<PH2> B, const XChunk& X, 
           q1[2 * (i - 2) + 1] = lut4(W >> 16);
         }
       }
-      const int s = dot16<true>(q0, X.xh[2 * g], X.xl[2 * g]) + dot16<true>(q1, X.xh[2 * g + 1], X.xl[2 * g + 1]);
-      acc = fmaf(dl * X.sg[g], (float)s, acc);
+      accum16<true, MT>(q0, 2 * g, dl, 0, X, acc);
+      accum16<true, MT>(q1, 2 * g + 1, dl, 0, X, acc);
+    }
+  } else if constexpr (C == IQ2_XXS) {
+    // [f16 d][8 x (4 lattice-index bytes, u32: 4 x 7-bit sign field + 4-bit scale @28)]. A lattice entry is
+    // eight bytes out of {8, 25, 43}; the eighth sign is the parity of the seven stored ones.
+    const float d = f16_bits(B.h(0));
+#pragma unroll
+    for (int g = 0; g < 8; g++) {
+      const uint32_t aux0 = B.w(2 + 8 * g), aux1 = B.w(6 + 8 * g);
+      const float db = d * (0.5f + (float)(aux1 >> 28)) * 0.25f;
+      uint32_t q[8];
+#pragma unroll
+      for (int l = 0; l < 4; l++) {
+        const uint2 gv = grid[(aux0 >> (8 * l)) & 0xffu];
+        const uint32_t s7 = (aux1 >> (7 * l)) & 127u;
+        const uint32_t s8 = s7 | ((__popc(s7) & 1u) << 7);
+        // sign bit -> 0x01 in its byte -> negate that byte: (v ^ 0xff) + 1 (bytes are 8..43: no carry out)
+        const uint32_t b0 = ((s8 & 15u) * 0x00204081u) & 0x01010101u, b1 = ((s8 >> 4) * 0x00204081u) & 0x01010101u;
+        q[2 * l] = (gv.x ^ (b0 * 255u)) + b0;
+        q[2 * l + 1] = (gv.y ^ (b1 * 255u)) + b1;
+      }
+      const uint32_t qa[4] = {q[0], q[1], q[2], q[3]}, qb[4] = {q[4], q[5], q[6], q[7]};
+      accum16<true, MT>(qa, 2 * g, db, 0, X, acc);
+      accum16<true, MT>(qb, 2 * g + 1, db, 0, X, acc);
     }
   } else if constexpr (C == Q5_K) {
     // [d][dmin][12 B scales][qh 32][qs 128]: as q4_k plus bit s of qh[i] as the fifth bit of sub-block s
@@ -195,7 +238,6 @@ __device__ __forceinline__ float chunk_dot(const Bytes<PH2> B, const XChunk& X, 
     const uint32_t scl = u0 & 0x3f3f3f3fu, mnl = u1 & 0x3f3f3f3fu;
     const uint32_t sch = (u2 & 0x0f0f0f0fu) | ((u0 >> 2) & 0x30303030u);
     const uint32_t mnh = ((u2 >> 4) & 0x0f0f0f0fu) | ((u1 >> 2) & 0x30303030u);
-    float t1 = 0.f, t2 = 0.f;
 #pragma unroll
     for (int p = 0; p < 4; p++) {
       uint32_t lo[8], hi[8];
@@ -203,26 +245,28 @@ __device__ __forceinline__ float chunk_dot(const Bytes<PH2> B, const XChunk& X, 
       for (int i = 0; i < 8; i++) {
         const uint32_t W = B.w(48 + 32 * p + 4 * i), H = B.w(16 + 4 * i);
         // bit 2p of H -> bit 4 of the low-nibble weights, bit 2p+1 -> bit 4 of the high-nibble ones
-        lo[i] = (W & 0x0f0f0f0fu) | (((2 * p <= 4) ? (H << (4 - 2 * p)) : (H >> (2 * p - 4))) & 0x10101010u);
-        hi[i] = ((W >> 4) & 0x0f0f0f0fu) | (((2 * p + 1 <= 4) ? (H << (3 - 2 * p)) : (H >> (2 * p - 3))) & 0x10101010u);
+        const uint32_t hl = (p <= 2) ? (H << ((p <= 2) ? 4 - 2 * p : 0)) : (H >> ((p > 2) ? 2 * p - 4 : 0));
+        const uint32_t hh = (p <= 1) ? (H << ((p <= 1) ? 3 - 2 * p : 0)) : (H >> ((p > 1) ? 2 * p - 3 : 0));
+        lo[i] = (W & 0x0f0f0f0fu) | (hl & 0x10101010u);
+        hi[i] = ((W >> 4) & 0x0f0f0f0fu) | (hh & 0x10101010u);
       }
       const uint32_t la[4] = {lo[0], lo[1], lo[2], lo[3]}, lb[4] = {lo[4], lo[5], lo[6], lo[7]};
       const uint32_t ha[4] = {hi[0], hi[1], hi[2], hi[3]}, hb[4] = {hi[4], hi[5], hi[6], hi[7]};
-      const int s_lo = dot16<false>(la, X.xh[4 * p], X.xl[4 * p]) + dot16<false>(lb, X.xh[4 * p + 1], X.xl[4 * p + 1]);
-      const int s_hi = dot16<false>(ha, X.xh[4 * p + 2], X.xl[4 * p + 2]) + dot16<false>(hb, X.xh[4 * p + 3], X.xl[4 * p + 3]);
       const uint32_t scw = p < 2 ? scl : sch, mnw = p < 2 ? mnl : mnh;
-      const float sc_lo = (float)((scw >> (16 * (p & 1))) & 0xffu), sc_hi = (float)((scw >> (16 * (p & 1) + 8)) & 0xffu);
-      const float mn_lo = (float)((mnw >> (16 * (p & 1))) & 0xffu), mn_hi = (float)((mnw >> (16 * (p & 1) + 8)) & 0xffu);
-      t1 = fmaf(sc_lo * X.sg[2 * p], (float)s_lo, t1);
-      t1 = fmaf(sc_hi * X.sg[2 * p + 1], (float)s_hi, t1);
-      t2 = fmaf(mn_lo, X.xs16[4 * p] + X.xs16[4 * p + 1], t2);
-      t2 = fmaf(mn_hi, X.xs16[4 * p + 2] + X.xs16[4 * p + 3], t2);
+      const float sc_lo = d * (float)((scw >> (16 * (p & 1))) & 0xffu), sc_hi = d * (float)((scw >> (16 * (p & 1) + 8)) & 0xffu);
+      const float mn_lo = dmin * (float)((mnw >> (16 * (p & 1))) & 0xffu), mn_hi = dmin * (float)((mnw >> (16 * (p & 1) + 8)) & 0xffu);
+      accum16<false, MT>(la, 4 * p, sc_lo, 0, X, acc);
+      accum16<false, MT>(lb, 4 * p + 1, sc_lo, 0, X, acc);
+      accum16<false, MT>(ha, 4 * p + 2, sc_hi, 0, X, acc);
+      accum16<false, MT>(hb, 4 * p + 3, sc_hi, 0, X, acc);
+      accum_min<MT>(4 * p, mn_lo, X, acc);
+      accum_min<MT>(4 * p + 1, mn_lo, X, acc);
+      accum_min<MT>(4 * p + 2, mn_hi, X, acc);
+      accum_min<MT>(4 * p + 3, mn_hi, X, acc);
     }
-    acc = fmaf(d, t1, -dmin * t2);
   } else if constexpr (C == Q6_K) {
     // [ql 128][qh 64][int8 sc 16][f16 d @208]: 16-weight scales, q - 32
     const float d = f16_bits(B.h(208));
-    float t = 0.f;
 #pragma unroll
     for (int hf = 0; hf < 2; hf++) {
 #pragma unroll
@@ -236,22 +280,18 @@ __device__ __forceinline__ float chunk_dot(const Bytes<PH2> B, const XChunk& X, 
             const uint32_t L = B.w(64 * hf + 32 * (qd & 1) + 16 * sub + 4 * i);
             const uint32_t H = B.w(128 + 32 * hf + 16 * sub + 4 * i);
             const uint32_t nib = (qd & 2) ? (L >> 4) : L;
-            const uint32_t hb = (qd < 2) ? (H << (4 - 2 * qd)) : (H >> (2 * qd - 4));
+            const uint32_t hb = (qd < 2) ? (H << ((qd < 2) ? 4 - 2 * qd : 0)) : (H >> ((qd >= 2) ? 2 * qd - 4 : 0));
             q[i] = (nib & 0x0f0f0f0fu) | (hb & 0x30303030u);
           }
           const int g16 = 8 * hf + 2 * qd + sub;  // 16-group of the chunk = index of its scale
-          const int s = dot16<false>(q, X.xh[g16], X.xl[g16]) - 32 * X.xi16[g16];
-          const int sc = (int)(int8_t)B.b(192 + g16);
-          t = fmaf((float)sc * X.sg[g16 >> 1], (float)s, t);
+          accum16<false, MT>(q, g16, d * (float)(int)(int8_t)B.b(192 + g16), 32, X, acc);
         }
       }
     }
-    acc = d * t;
   } else if constexpr (C == Q2_K) {
     // [scales 16: 4-bit scale | 4-bit min << 4][qs 64][d @80][dmin @82]: 16-weight groups
     const uint32_t dd = B.w(80);
     const float d = f16_bits(dd & 0xffffu), dmin = f16_bits(dd >> 16);
-    float t1 = 0.f, t2 = 0.f;
 #pragma unroll
     for (int hf = 0; hf < 2; hf++) {
 #pragma unroll
@@ -262,23 +302,19 @@ __device__ __forceinline__ float chunk_dot(const Bytes<PH2> B, const XChunk& X, 
 #pragma unroll
           for (int i = 0; i < 4; i++) q[i] = (B.w(16 + 32 * hf + 16 * sub + 4 * i) >> (2 * si)) & 0x03030303u;
           const int g16 = 8 * hf + 2 * si + sub;
-          const int s = dot16<false>(q, X.xh[g16], X.xl[g16]);
           const uint32_t scb = B.b(g16);
-          t1 = fmaf((float)(scb & 15u) * X.sg[g16 >> 1], (float)s, t1);
-          t2 = fmaf((float)(scb >> 4), X.xs16[g16], t2);
+          accum16<false, MT>(q, g16, d * (float)(scb & 15u), 0, X, acc);
+          accum_min<MT>(g16, dmin * (float)(scb >> 4), X, acc);
         }
       }
     }
-    acc = fmaf(d, t1, -dmin * t2);
   } else {
     static_assert(C == Q3_K, "codec without an integer dot-product path");
     // [hmask 32][qs 64][scales 12][d @108]: two bits of qs, bit 4 hf + si of hmask as the third, minus 4;
-    // sixteen 6-bit scales minus 32
+    // sixteen 6-bit scales minus 32: scale k takes its low four bits from byte k % 8 (low nibble for k < 8,
+    // high nibble otherwise) and its high two bits from byte 8 + k % 4, shifted by 2 (k / 4)
     const float d = f16_bits(B.h(108));
     const uint32_t s0 = B.w(96), s1 = B.w(100), s2 = B.w(104);
-    // scale k = 0..15: low four bits from bytes 0..7 (k < 8: low nibble of byte k, else high nibble of byte k - 8),
-    // high two bits from byte 8 + k % 4, shift 2 (k / 4)
-    float t = 0.f;
 #pragma unroll
     for (int hf = 0; hf < 2; hf++) {
 #pragma unroll
@@ -291,54 +327,57 @@ __device__ __forceinline__ float chunk_dot(const Bytes<PH2> B, const XChunk& X, 
             const uint32_t Q = (B.w(32 + 32 * hf + 16 * sub + 4 * i) >> (2 * si)) & 0x03030303u;
             const uint32_t M = B.w(16 * sub + 4 * i);
             const int sh = 4 * hf + si;  // mask bit -> bit 2
-            const uint32_t mb = (sh <= 2) ? (M << (2 - sh)) : (M >> (sh - 2));
+            const uint32_t mb = (sh <= 2) ? (M << ((sh <= 2) ? 2 - sh : 0)) : (M >> ((sh > 2) ? sh - 2 : 0));
             q[i] = Q | (mb & 0x04040404u);
           }
           const int k = 8 * hf + 2 * si + sub;
           const uint32_t lw = (k & 4) ? s1 : s0;
           const uint32_t lo4 = ((lw >> (8 * (k & 3))) >> ((k & 8) ? 4 : 0)) & 15u;
           const uint32_t hi2 = ((s2 >> (8 * (k & 3))) >> (2 * (k >> 2))) & 3u;
-          const int sc = (int)(lo4 | (hi2 << 4)) - 32;
-          const int s = dot16<false>(q, X.xh[k], X.xl[k]) - 4 * X.xi16[k];
-          t = fmaf((float)sc * X.sg[k >> 1], (float)s, t);
+          accum16<false, MT>(q, k, d * (float)((int)(lo4 | (hi2 << 4)) - 32), 4, X, acc);
         }
       }
     }
-    acc = d * t;
   }
-  return acc;
 }
 
-// dyn smem: ring [8 warps][D][32 rows x 16 P] | XH [K] | XL [K] | SG [K/32] | XI16 [K/16] | XS16 [K/16]
+// dyn smem: ring [8 warps][D][32 rows x 16 P] | per row of x: XH [K] | XL [K] | SG [K/32] | XI16 [K/16] | XS16 [K/16]
 template <int C>
 constexpr int slot_bytes() { return kRows * 16 * Geom<C>::kP; }
+__host__ __device__ static inline int x_bytes(int K) { return 2 * K + (K / 32) * 4 + 2 * (K / 16) * 4; }
 template <int C>
-int dyn_smem(int K, int D) { return kWarps * D * slot_bytes<C>() + 2 * K + (K / 32) * 4 + 2 * (K / 16) * 4; }
+int dyn_smem(int K, int D, int MT) { return kWarps * D * slot_bytes<C>() + MT * x_bytes(K); }
 
-template <int C, typename XT>
+template <int C, typename XT, int MT>
 __global__ void __launch_bounds__(kThreads, 2) gemv_dp4a_kernel(const GemvArgs a, const int D) {
   using OT = typename std::conditional<std::is_same<XT, __half>::value, __half, __nv_bfloat16>::type;
   using G = Geom<C>;
   constexpr int kSlot = slot_bytes<C>(), kStride = 16 * G::kP;
   constexpr bool kPerm = (C == IQ4_NL || C == IQ4_XS);  // planes of x in the (i, i+16, i+1, i+17) order
-  __shared__ float red[kWarps][kRows];
+  __shared__ float red[kWarps][MT][kRows];
+  __shared__ __align__(16) uint2 s_grid[C == IQ2_XXS ? 256 : 1];
   extern __shared__ __align__(16) uint8_t dyn[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nchunks = a.K >> 8;
-  uint32_t* XH = reinterpret_cast<uint32_t*>(dyn + kWarps * D * kSlot);
-  uint32_t* XL = XH + a.K / 4;
-  float* SG = reinterpret_cast<float*>(XL + a.K / 4);
-  int* XI16 = reinterpret_cast<int*>(SG + a.K / 32);
-  float* XS16 = reinterpret_cast<float*>(XI16 + a.K / 16);
+  const int K = a.K;
+  uint8_t* xbase = dyn + kWarps * D * kSlot;
+  const int xb = x_bytes(K);
   const int row0 = blockIdx.x * kRows;
   const int per = (nchunks + kWarps - 1) / kWarps;
   const int ch0 = min(warp * per, nchunks), ch1 = min(ch0 + per, nchunks);
+  const int m = min(a.M, MT);
 
-  // the 16-level table of the iq4 codecs in four registers
+  // the 16-level table of the iq4 codecs in four registers; the iq2_xxs lattice in shared memory
   uint32_t T[4] = {0u, 0u, 0u, 0u};
   if constexpr (kPerm) {
 #pragma unroll
     for (int i = 0; i < 16; i++) T[i >> 2] |= ((uint32_t)(uint8_t)kq_tab_iq4nl[i]) << (8 * (i & 3));
+  }
+  if constexpr (C == IQ2_XXS) {
+    for (int i = threadIdx.x; i < 256; i += kThreads) {
+      const unsigned long long gv = kq_tab_iq2xxs_grid[i];
+      s_grid[i] = make_uint2((uint32_t)gv, (uint32_t)(gv >> 32));
+    }
   }
 
   // ring: window of chunk sb starts at the 16-byte boundary below it, pulled back for the last chunk
@@ -370,12 +409,21 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_dp4a_kernel(const GemvArgs a
   pdl_launch_dependents();
   pdl_wait();  // activations may come from the kernel before this one
 
-  {
-    // quantize all of K: eight activations per thread and step, four threads per 32-group
-    const XT* xrow = static_cast<const XT*>(a.x);
-    for (int c = threadIdx.x; c < a.K / 8; c += kThreads) {
+  for (int t = 0; t < MT; t++) {
+    // quantize all of K: eight activations per thread and step, four threads per 32-group.
+    // Rows past M are zeros.
+    uint32_t* XH = reinterpret_cast<uint32_t*>(xbase + t * xb);
+    uint32_t* XL = XH + K / 4;
+    float* SG = reinterpret_cast<float*>(XL + K / 4);
+    int* XI16 = reinterpret_cast<int*>(SG + K / 32);
+    float* XS16 = reinterpret_cast<float*>(XI16 + K / 16);
+    const XT* xrow = static_cast<const XT*>(a.x) + (long long)t * a.x_row_stride;
+    for (int c = threadIdx.x; c < K / 8; c += kThreads) {
       float v[8];
-      if constexpr (std::is_same<XT, float>::value) {
+      if (t >= m) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = 0.f;
+      } else if constexpr (std::is_same<XT, float>::value) {
         const float4 f0 = __ldg(reinterpret_cast<const float4*>(xrow + 8 * c));
         const float4 f1 = __ldg(reinterpret_cast<const float4*>(xrow + 8 * c) + 1);
         const float f[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
@@ -452,7 +500,9 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_dp4a_kernel(const GemvArgs a
   }
   __syncthreads();
 
-  float y = 0.f;
+  float y[MT];
+#pragma unroll
+  for (int t = 0; t < MT; t++) y[t] = 0.f;
   for (int sb = ch0; sb < ch1; sb++) {
     const int rel = sb - ch0;
     cp_wait(D - 1);
@@ -461,41 +511,50 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_dp4a_kernel(const GemvArgs a
     const int phase = sb * G::kCB - window_start(sb);  // same for every row; even
     const uint8_t* blk = slot + lane * kStride + (phase & ~3);
     XChunk X;
+    uint32_t* XH = reinterpret_cast<uint32_t*>(xbase);
     X.xh = reinterpret_cast<const uint4*>(XH + sb * 64);
-    X.xl = reinterpret_cast<const uint4*>(XL + sb * 64);
-    X.sg = SG + sb * 8;
-    X.xi16 = XI16 + sb * 16;
-    X.xs16 = XS16 + sb * 16;
-    if (phase & 2) y += chunk_dot<C, 2>(Bytes<2>{reinterpret_cast<const uint32_t*>(blk)}, X, T);
-    else y += chunk_dot<C, 0>(Bytes<0>{reinterpret_cast<const uint32_t*>(blk)}, X, T);
+    X.xl = reinterpret_cast<const uint4*>(XH + K / 4 + sb * 64);
+    X.sg = reinterpret_cast<const float*>(XH + K / 2) + sb * 8;
+    X.xi16 = reinterpret_cast<const int*>(XH + K / 2 + K / 32) + sb * 16;
+    X.xs16 = reinterpret_cast<const float*>(XH + K / 2 + K / 32 + K / 16) + sb * 16;
+    X.plane_stride = xb / 16;
+    X.sg_stride = xb / 4;
+    X.s16_stride = xb / 4;
+    if (phase & 2) chunk_dot<C, 2, MT>(Bytes<2>{reinterpret_cast<const uint32_t*>(blk)}, X, T, s_grid, y);
+    else chunk_dot<C, 0, MT>(Bytes<0>{reinterpret_cast<const uint32_t*>(blk)}, X, T, s_grid, y);
     __syncwarp();  // the slot is free again
     issue(slot);
   }
-  red[warp][lane] = y;
-  __syncthreads();
-  if (warp == 0 && row0 + lane < a.N) {
-    float sum = 0.f;
 #pragma unroll
-    for (int w = 0; w < kWarps; w++) sum += red[w][lane];
-    OT* out = static_cast<OT*>(a.y) + row0 + lane;
-    if constexpr (std::is_same<OT, __half>::value) *out = __float2half_rn(sum);
-    else *out = __float2bfloat16_rn(sum);
+  for (int t = 0; t < MT; t++) red[warp][t][lane] = y[t];
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < MT * kRows; idx += kThreads) {
+    const int t = idx / kRows, r = idx % kRows;
+    if (t < m && row0 + r < a.N) {
+      float sum = 0.f;
+#pragma unroll
+      for (int w = 0; w < kWarps; w++) sum += red[w][t][r];
+      OT* out = static_cast<OT*>(a.y) + (long long)t * a.y_row_stride + row0 + r;
+      if constexpr (std::is_same<OT, __half>::value) *out = __float2half_rn(sum);
+      else *out = __float2bfloat16_rn(sum);
+    }
   }
 }
 
-template <int C, typename XT>
-cudaError_t launch_one(const GemvArgs& a, cudaStream_t st) {
+template <int C, typename XT, int MT>
+cudaError_t launch_mt(const GemvArgs& a, cudaStream_t st) {
   const int nchunks = a.K >> 8;
   const int per = (nchunks + kWarps - 1) / kWarps;
   int D = per < 2 ? 1 : 2;
-  if (dyn_smem<C>(a.K, D) > 110 * 1024) D = 1;  // two CTAs per SM where the ring allows it
-  const int dyn = dyn_smem<C>(a.K, D);
+  if (dyn_smem<C>(a.K, D, MT) > 110 * 1024) D = 1;  // two CTAs per SM where the ring allows it
+  const int dyn = dyn_smem<C>(a.K, D, MT);
   if (dyn > 200 * 1024) return cudaErrorInvalidConfiguration;
   static bool attr_set[16] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 16 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemv_dp4a_kernel<C, XT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaError_t e =
+        cudaFuncSetAttribute(gemv_dp4a_kernel<C, XT, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return e;
     attr_set[dev] = true;
   }
@@ -510,7 +569,14 @@ cudaError_t launch_one(const GemvArgs& a, cudaStream_t st) {
   cfg.attrs = attr;
   static const bool no_pdl = std::getenv("KQ_NO_PDL") != nullptr;  // A/B lever
   cfg.numAttrs = no_pdl ? 0 : 1;
-  return cudaLaunchKernelEx(&cfg, gemv_dp4a_kernel<C, XT>, a, D);
+  return cudaLaunchKernelEx(&cfg, gemv_dp4a_kernel<C, XT, MT>, a, D);
+}
+
+template <int C, typename XT>
+cudaError_t launch_one(const GemvArgs& a, cudaStream_t st) {
+  if (a.M == 1) return launch_mt<C, XT, 1>(a, st);
+  if (a.M == 2) return launch_mt<C, XT, 2>(a, st);
+  return launch_mt<C, XT, 4>(a, st);
 }
 
 template <int C>
@@ -523,10 +589,16 @@ cudaError_t launch_codec(int x_dtype, const GemvArgs& a, cudaStream_t st) {
 }  // namespace
 
 bool gemv_dp4a_supported(int codec, const GemvArgs& a) {
-  if (codec == Q4_K || codec == IQ2_XXS) return false;  // q4_k has its own kernel (kq_gemv.cu)
-  if (a.tasks != nullptr || a.M != 1 || !a.w_align16) return false;
+  if (codec == Q4_K) return false;  // q4_k has its own kernels (kq_gemv.cu)
+  if (a.tasks != nullptr || a.M < 1 || a.M > 4 || !a.w_align16) return false;
+  // measured: with more than one row the table-driven tensor-core kernels of kq_gemv.cu win for these two,
+  // and so they do for iq2_xxs matrices too small to hide the lattice lookups
+  if ((codec == IQ4_XS || codec == IQ2_XXS) && a.M > 1) return false;
+  if (codec == IQ2_XXS && (long long)a.N * a.K < (48ll << 20)) return false;
   if ((a.K & 255) != 0 || a.K > kMaxK || (a.row_bytes & 15) != 0 || a.row_bytes < 16 * 17) return false;
-  return true;
+  // the activations of all rows are staged whole: 2.6 bytes per activation
+  const int mt = a.M == 3 ? 4 : a.M;
+  return mt * x_bytes(a.K) <= 96 * 1024;
 }
 
 cudaError_t launch_gemv_dp4a(int codec, int x_dtype, const GemvArgs& a, cudaStream_t st) {
@@ -539,6 +611,7 @@ cudaError_t launch_gemv_dp4a(int codec, int x_dtype, const GemvArgs& a, cudaStre
     case Q8_0: return launch_codec<Q8_0>(x_dtype, a, st);
     case IQ4_NL: return launch_codec<IQ4_NL>(x_dtype, a, st);
     case IQ4_XS: return launch_codec<IQ4_XS>(x_dtype, a, st);
+    case IQ2_XXS: return launch_codec<IQ2_XXS>(x_dtype, a, st);
   }
   return cudaErrorInvalidValue;
 }
