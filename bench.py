@@ -263,6 +263,25 @@ def extra_cells(dev):
         ids, probs = route_topk(torch.randn(T, E, generator=g).to(dev), k)
         t = timed(lambda: moe_glu(x, wg, wu, wd, "q4_k", ids, probs), reps=3)
         out[f"moe_glu_q4k_T{T}"] = {"tokens_per_s": T / t, "ms": t * 1e3}
+        # the same block replayed from a CUDA graph (no host sync inside it): what a serving loop pays
+        try:
+            side = torch.cuda.Stream(dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    moe_glu(x, wg, wu, wd, "q4_k", ids, probs)
+                side.synchronize()
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr, stream=side):
+                    y_cap = moe_glu(x, wg, wu, wd, "q4_k", ids, probs)
+            torch.cuda.current_stream(dev).wait_stream(side)
+            tg = timed(gr.replay, reps=5)
+            out[f"moe_glu_q4k_T{T}"]["graph_tokens_per_s"] = T / tg
+            out[f"moe_glu_q4k_T{T}"]["graph_ms"] = tg * 1e3
+            del gr, y_cap
+        except Exception as e:  # capture is an optimisation of the caller, not part of the op
+            out[f"moe_glu_q4k_T{T}"]["graph_error"] = str(e)[:120]
+            torch.cuda.synchronize()
     return out
 
 

@@ -1554,7 +1554,7 @@ cudaError_t launch_gemv(int codec, int x_dtype, const GemvArgs& a, cudaStream_t 
     return launch_m1_dp4a<float>(a, st);
   }
   // KQ_GEMV_DP4A=0 also switches the other codecs' integer kernels off
-  if (!(dp_env && dp_env[0] == '0') && gemv_dp4a_supported(codec, a)) return launch_gemv_dp4a(codec, x_dtype, a, st);
+  if (!(dp_env && dp_env[0] == '0') && gemv_dp4a_supported(codec, x_dtype, a)) return launch_gemv_dp4a(codec, x_dtype, a, st);
   static const char* tc_env = std::getenv("KQ_GEMV_TC");  // A/B lever: 1 = tensor-memory decode kernel
   if (tc_env && tc_env[0] == '1' && gemv_tc_supported(codec, x_dtype, a)) return launch_gemv_tc(a, st);
   static const bool no_m1 = std::getenv("KQ_GEMV_NO_M1") != nullptr;  // A/B lever

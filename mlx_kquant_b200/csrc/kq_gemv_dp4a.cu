@@ -60,6 +60,7 @@ template <int C>
 struct Geom;
 template <> struct Geom<Q2_K> { static constexpr int kCB = 84, kP = 7; };
 template <> struct Geom<Q3_K> { static constexpr int kCB = 110, kP = 9; };
+template <> struct Geom<Q4_K> { static constexpr int kCB = 144, kP = 9; };
 template <> struct Geom<Q5_K> { static constexpr int kCB = 176, kP = 11; };
 template <> struct Geom<Q6_K> { static constexpr int kCB = 210, kP = 15; };
 template <> struct Geom<Q4_0> { static constexpr int kCB = 144, kP = 9; };
@@ -230,8 +231,9 @@ __device__ __forceinline__ void chunk_dot(const Bytes<PH2> B, const XChunk& X, c
       accum16<true, MT>(qa, 2 * g, db, 0, X, acc);
       accum16<true, MT>(qb, 2 * g + 1, db, 0, X, acc);
     }
-  } else if constexpr (C == Q5_K) {
-    // [d][dmin][12 B scales][qh 32][qs 128]: as q4_k plus bit s of qh[i] as the fifth bit of sub-block s
+  } else if constexpr (C == Q5_K || C == Q4_K) {
+    // q4_k: [d][dmin][12 B scales][qs 128], low nibbles sub-block 2p, high nibbles 2p + 1;
+    // q5_k: [d][dmin][12 B scales][qh 32][qs 128], plus bit s of qh[i] as the fifth bit of sub-block s
     const uint32_t hd = B.w(0);
     const float d = f16_bits(hd & 0xffffu), dmin = f16_bits(hd >> 16);
     const uint32_t u0 = B.w(4), u1 = B.w(8), u2 = B.w(12);
@@ -243,7 +245,7 @@ __device__ __forceinline__ void chunk_dot(const Bytes<PH2> B, const XChunk& X, c
       uint32_t lo[8], hi[8];
 #pragma unroll
       for (int i = 0; i < 8; i++) {
-        const uint32_t W = B.w(48 + 32 * p + 4 * i), H = B.w(16 + 4 * i);
+        const uint32_t W = B.w((C == Q5_K ? 48 : 16) + 32 * p + 4 * i), H = (C == Q5_K) ? B.w(16 + 4 * i) : 0u;
         // bit 2p of H -> bit 4 of the low-nibble weights, bit 2p+1 -> bit 4 of the high-nibble ones
         const uint32_t hl = (p <= 2) ? (H << ((p <= 2) ? 4 - 2 * p : 0)) : (H >> ((p > 2) ? 2 * p - 4 : 0));
         const uint32_t hh = (p <= 1) ? (H << ((p <= 1) ? 3 - 2 * p : 0)) : (H >> ((p > 1) ? 2 * p - 3 : 0));
@@ -365,7 +367,25 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_dp4a_kernel(const GemvArgs a
   const int row0 = blockIdx.x * kRows;
   const int per = (nchunks + kWarps - 1) / kWarps;
   const int ch0 = min(warp * per, nchunks), ch1 = min(ch0 + per, nchunks);
-  const int m = min(a.M, MT);
+  // dense: rows 0 .. M-1 of x against a.w; task list: task blockIdx.y, its rows MT blockIdx.z .. +MT-1
+  int m = min(a.M, MT);
+  const uint8_t* wmat = a.w;
+  int xr[MT], yr[MT];
+#pragma unroll
+  for (int t = 0; t < MT; t++) xr[t] = yr[t] = t;
+  if (a.tasks != nullptr) {
+    if (a.n_tasks_dev != nullptr && (int)blockIdx.y + a.task_offset >= *a.n_tasks_dev) return;  // whole CTA
+    const GemvTask& tk = a.tasks[blockIdx.y];
+    const int t0 = MT * (int)blockIdx.z;
+    m = min(MT, tk.m - t0);
+    if (m <= 0) return;
+    wmat = tk.w;
+#pragma unroll
+    for (int t = 0; t < MT; t++) {
+      xr[t] = tk.xrow[min(t0 + t, 15)];
+      yr[t] = tk.yrow[min(t0 + t, 15)];
+    }
+  }
 
   // the 16-level table of the iq4 codecs in four registers; the iq2_xxs lattice in shared memory
   uint32_t T[4] = {0u, 0u, 0u, 0u};
@@ -391,7 +411,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_dp4a_kernel(const GemvArgs a
     roff[i] = min(row0 + j / G::kP, a.N - 1) - row0;  // row of the piece, clamped at the matrix end
     roff[i] = roff[i] * 64 + (j % G::kP);             // packed: row * 64 + piece
   }
-  const uint8_t* wbase = a.w + (long long)row0 * a.row_bytes;
+  const uint8_t* wbase = wmat + (long long)row0 * a.row_bytes;
   const int last_ws = (int)a.row_bytes - kStride;
   auto window_start = [&](int sb) { return min((sb * G::kCB) & ~15, last_ws); };
   int issued = ch0;
@@ -407,8 +427,9 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_dp4a_kernel(const GemvArgs a
   };
   for (int d = 0; d < D; d++) issue(ring + d * kSlot);
   pdl_launch_dependents();
-  pdl_wait();  // activations may come from the kernel before this one
+  if (a.tasks == nullptr) pdl_wait();  // activations may come from the kernel before this one
 
+#pragma unroll
   for (int t = 0; t < MT; t++) {
     // quantize all of K: eight activations per thread and step, four threads per 32-group.
     // Rows past M are zeros.
@@ -417,7 +438,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_dp4a_kernel(const GemvArgs a
     float* SG = reinterpret_cast<float*>(XL + K / 4);
     int* XI16 = reinterpret_cast<int*>(SG + K / 32);
     float* XS16 = reinterpret_cast<float*>(XI16 + K / 16);
-    const XT* xrow = static_cast<const XT*>(a.x) + (long long)t * a.x_row_stride;
+    const XT* xrow = static_cast<const XT*>(a.x) + (long long)xr[t] * a.x_row_stride;
     for (int c = threadIdx.x; c < K / 8; c += kThreads) {
       float v[8];
       if (t >= m) {
@@ -534,7 +555,11 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_dp4a_kernel(const GemvArgs a
       float sum = 0.f;
 #pragma unroll
       for (int w = 0; w < kWarps; w++) sum += red[w][t][r];
-      OT* out = static_cast<OT*>(a.y) + (long long)t * a.y_row_stride + row0 + r;
+      int yrow = yr[0];
+#pragma unroll
+      for (int u = 1; u < MT; u++)
+        if (t == u) yrow = yr[u];
+      OT* out = static_cast<OT*>(a.y) + (long long)yrow * a.y_row_stride + row0 + r;
       if constexpr (std::is_same<OT, __half>::value) *out = __float2half_rn(sum);
       else *out = __float2bfloat16_rn(sum);
     }
@@ -559,7 +584,8 @@ cudaError_t launch_mt(const GemvArgs& a, cudaStream_t st) {
     attr_set[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((a.N + kRows - 1) / kRows, 1, 1);
+  cfg.gridDim = a.tasks ? dim3((a.N + kRows - 1) / kRows, a.n_tasks, (a.max_m + MT - 1) / MT)
+                        : dim3((a.N + kRows - 1) / kRows, 1, 1);
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = dyn;
   cfg.stream = st;
@@ -568,14 +594,15 @@ cudaError_t launch_mt(const GemvArgs& a, cudaStream_t st) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   static const bool no_pdl = std::getenv("KQ_NO_PDL") != nullptr;  // A/B lever
-  cfg.numAttrs = no_pdl ? 0 : 1;
+  cfg.numAttrs = (no_pdl || a.tasks != nullptr) ? 0 : 1;  // a task list comes from the kernel before: plain stream order
   return cudaLaunchKernelEx(&cfg, gemv_dp4a_kernel<C, XT, MT>, a, D);
 }
 
 template <int C, typename XT>
 cudaError_t launch_one(const GemvArgs& a, cudaStream_t st) {
-  if (a.M == 1) return launch_mt<C, XT, 1>(a, st);
-  if (a.M == 2) return launch_mt<C, XT, 2>(a, st);
+  const int rows = a.tasks ? a.max_m : a.M;
+  if (rows == 1) return launch_mt<C, XT, 1>(a, st);
+  if (rows == 2) return launch_mt<C, XT, 2>(a, st);
   return launch_mt<C, XT, 4>(a, st);
 }
 
@@ -588,14 +615,21 @@ cudaError_t launch_codec(int x_dtype, const GemvArgs& a, cudaStream_t st) {
 
 }  // namespace
 
-bool gemv_dp4a_supported(int codec, const GemvArgs& a) {
-  if (codec == Q4_K) return false;  // q4_k has its own kernels (kq_gemv.cu)
-  if (a.tasks != nullptr || a.M < 1 || a.M > 4 || !a.w_align16) return false;
+bool gemv_dp4a_supported(int codec, int x_dtype, const GemvArgs& a) {
+  if (!a.w_align16 || (a.K & 255) != 0 || a.K > kMaxK || (a.row_bytes & 15) != 0 || a.row_bytes < 16 * 17) return false;
+  if (a.tasks != nullptr) {
+    // task lists (gather_qmm): rows in slices of four. q4_k with fp16 rows and the two table codecs keep
+    // their tensor-core kernels, which take sixteen rows per pass over the weights.
+    if ((codec == Q4_K && x_dtype == F16) || codec == IQ4_XS || codec == IQ2_XXS) return false;
+    if (a.n_tasks > 65535) return false;
+    return 4 * x_bytes(a.K) <= 96 * 1024;
+  }
+  if (codec == Q4_K) return false;  // dense q4_k has its own kernels (kq_gemv.cu)
+  if (a.M < 1 || a.M > 4) return false;
   // measured: with more than one row the table-driven tensor-core kernels of kq_gemv.cu win for these two,
   // and so they do for iq2_xxs matrices too small to hide the lattice lookups
   if ((codec == IQ4_XS || codec == IQ2_XXS) && a.M > 1) return false;
   if (codec == IQ2_XXS && (long long)a.N * a.K < (48ll << 20)) return false;
-  if ((a.K & 255) != 0 || a.K > kMaxK || (a.row_bytes & 15) != 0 || a.row_bytes < 16 * 17) return false;
   // the activations of all rows are staged whole: 2.6 bytes per activation
   const int mt = a.M == 3 ? 4 : a.M;
   return mt * x_bytes(a.K) <= 96 * 1024;
@@ -605,6 +639,7 @@ cudaError_t launch_gemv_dp4a(int codec, int x_dtype, const GemvArgs& a, cudaStre
   switch (codec) {
     case Q2_K: return launch_codec<Q2_K>(x_dtype, a, st);
     case Q3_K: return launch_codec<Q3_K>(x_dtype, a, st);
+    case Q4_K: return launch_codec<Q4_K>(x_dtype, a, st);
     case Q5_K: return launch_codec<Q5_K>(x_dtype, a, st);
     case Q6_K: return launch_codec<Q6_K>(x_dtype, a, st);
     case Q4_0: return launch_codec<Q4_0>(x_dtype, a, st);

@@ -50,9 +50,9 @@ bool gemv_tc_supported(int codec, int x_dtype, const GemvArgs& a);
 cudaError_t launch_gemv_tc(const GemvArgs& a, cudaStream_t st);
 cudaError_t read_device_error_tc(int* out, bool clear);
 
-// One dense activation row, codecs without a tensor-core fast path: products on the integer
-// dot-product pipe over 16-bit quantized activations (kq_gemv_dp4a.cu).
-bool gemv_dp4a_supported(int codec, const GemvArgs& a);
+// Up to four activation rows per pass (dense, or task lists in slices of four): products on the
+// integer dot-product pipe over 16-bit quantized activations (kq_gemv_dp4a.cu).
+bool gemv_dp4a_supported(int codec, int x_dtype, const GemvArgs& a);
 cudaError_t launch_gemv_dp4a(int codec, int x_dtype, const GemvArgs& a, cudaStream_t st);
 
 // Prefill (M > 16) tile kernel on tcgen05 tensor cores with TMEM accumulators.
