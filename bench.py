@@ -50,9 +50,9 @@ CODEC = "q4_k"
 ROW_BYTES = K_COLS // 256 * 144
 MATRIX_BYTES = N_ROWS * ROW_BYTES  # 9 437 184
 # the kernel that runs this workload, and its DRAM bytes per launch from the ncu capture summarised in
-# profiles/gemv_q4k_f16_decode.md (dram__bytes_read.sum + dram__bytes_write.sum)
+# profiles/gemv_q4k_dp4a_decode.md (dram__bytes_read.sum + dram__bytes_write.sum)
 ROOFLINE_KERNEL = "gemv_q4k_m1_dp4a_kernel<__half>"
-ROOFLINE_TRAFFIC = 9469184
+ROOFLINE_TRAFFIC = 9469696
 
 
 def parse():
@@ -193,7 +193,9 @@ def run_reference(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "c1_q4k_decode_gemv", "codec": CODEC, "N": N_ROWS, "K": K_COLS, "M": args.m,
-                   "layers": sample},
+                   "layers": args.layers, "x_dtype": "f16", "accumulate": "f32",
+                   "cold_cache": f"a step is a bounded sample: {sample} of the {args.layers} distinct matrices",
+                   "parallelism": "host threads"},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": kind,
                          "sample": f"{sample} of the step's matrices per step, x86_64 scalar/threaded eval_cpu path"},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
