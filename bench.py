@@ -337,6 +337,7 @@ def run_b200(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        os.environ.pop("NCCL_DEBUG", None)  # NCCL's version banner would share stdout with the one JSON line
         dist.init_process_group("nccl", device_id=dev)
 
     layers, M = args.layers, args.m

@@ -24,7 +24,7 @@ def route_topk(router_logits: torch.Tensor, top_k: int) -> tuple[torch.Tensor, t
     return idx, p / p.sum(dim=-1, keepdim=True)
 
 
-def moe_glu(x, w_gate, w_up, w_down, kquant_type, expert_ids, expert_probs, *, sort_rows: bool = True):
+def moe_glu(x, w_gate, w_up, w_down, kquant_type, expert_ids, expert_probs, *, sort_rows: bool = False):
     """x [T, H] (f16 / bf16), expert stacks [E, F, bytes(H)] x2 and [E, H, bytes(F)],
     expert_ids / expert_probs [T, k]. Returns y [T, H] in x's dtype."""
     T, H = x.shape
@@ -32,8 +32,10 @@ def moe_glu(x, w_gate, w_up, w_down, kquant_type, expert_ids, expert_probs, *, s
     rows = T * k
     flat_e = expert_ids.reshape(rows)
     tok = torch.arange(T, device=x.device).repeat_interleave(k)
+    # Rows go in routing order: gather_qmm groups them by expert on the device itself, so the explicit
+    # argsort / unsort that the reference's callers do from 64 routed rows up (src/kquant_gather.cpp:8-16)
+    # would only add passes over the activations. sort_rows=True keeps that composition for comparison.
     if sort_rows and rows >= 64:
-        # expert-sorted rows, as the reference's callers do from 64 routed rows up (src/kquant_gather.cpp:8-16)
         order = torch.argsort(flat_e, stable=True)
         flat_e, tok = flat_e[order], tok[order]
     else:
@@ -64,7 +66,7 @@ def moe_glu_expert_parallel(x, w_gate, w_up, w_down, kquant_type, expert_ids, ex
     """
     import torch.distributed as dist
 
-    from .dist import expert_owner, shard_bounds, split_by_owner
+    from .dist import expert_owner, shard_bounds
 
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
@@ -74,10 +76,15 @@ def moe_glu_expert_parallel(x, w_gate, w_up, w_down, kquant_type, expert_ids, ex
     flat_e = expert_ids.reshape(rows)
     tok = torch.arange(T, device=x.device).repeat_interleave(k)
     owner = expert_owner(flat_e, n_experts, world)
-    order, send_counts = split_by_owner(owner, world)
-    recv_counts_t = torch.empty(world, dtype=torch.int64, device=x.device)
-    dist.all_to_all_single(recv_counts_t, torch.tensor(send_counts, dtype=torch.int64, device=x.device), group=group)
-    recv_counts = recv_counts_t.tolist()
+    # rows grouped by destination rank; every rank's per-destination counts are gathered so that one
+    # host read gives both the send and the receive splits of the all-to-alls
+    order = torch.argsort(owner, stable=True)
+    counts = torch.bincount(owner, minlength=world)
+    all_counts = torch.empty(world * world, dtype=counts.dtype, device=x.device)
+    dist.all_gather_into_tensor(all_counts, counts, group=group)
+    table = all_counts.view(world, world).tolist()
+    send_counts = table[rank]
+    recv_counts = [table[r][rank] for r in range(world)]
     n_recv = sum(recv_counts)
     # dispatch: activations and expert ids of the routed rows, grouped by destination
     send_x = x[tok[order]].contiguous()
@@ -86,26 +93,22 @@ def moe_glu_expert_parallel(x, w_gate, w_up, w_down, kquant_type, expert_ids, ex
     recv_e = torch.empty(n_recv, dtype=torch.int32, device=x.device)
     dist.all_to_all_single(recv_x, send_x, output_split_sizes=recv_counts, input_split_sizes=send_counts, group=group)
     dist.all_to_all_single(recv_e, send_e, output_split_sizes=recv_counts, input_split_sizes=send_counts, group=group)
-    # local experts
+    # local experts: rows stay in arrival order, gather_qmm groups them by expert on the device
     lo, _ = shard_bounds(n_experts, rank, world)
-    local_e = (recv_e.to(torch.int64) - lo)
     if n_recv > 0:
-        sort = torch.argsort(local_e, stable=True)
-        xs = recv_x[sort].reshape(n_recv, 1, H)
-        es = local_e[sort]
-        g = gather_qmm(xs, w_gate, None, kquant_type, rhs_indices=es, sorted_indices=True)
-        u = gather_qmm(xs, w_up, None, kquant_type, rhs_indices=es, sorted_indices=True)
+        es = recv_e.to(torch.int64) - lo
+        xs = recv_x.reshape(n_recv, 1, H)
+        g = gather_qmm(xs, w_gate, None, kquant_type, rhs_indices=es)
+        u = gather_qmm(xs, w_up, None, kquant_type, rhs_indices=es)
         h = (torch.nn.functional.silu(g.float()) * u.float()).to(x.dtype)
-        d = gather_qmm(h, w_down, None, kquant_type, rhs_indices=es, sorted_indices=True).reshape(n_recv, H)
-        out_rows = torch.empty_like(d)
-        out_rows[sort] = d
+        out_rows = gather_qmm(h, w_down, None, kquant_type, rhs_indices=es).reshape(n_recv, H)
     else:
         out_rows = torch.empty((0, H), dtype=x.dtype, device=x.device)
-    # combine: results return to the rank of their token
+    # combine: results return to the rank of their token and are summed there with the routing weights
     back = torch.empty((rows, H), dtype=x.dtype, device=x.device)
     dist.all_to_all_single(back, out_rows.contiguous(), output_split_sizes=send_counts, input_split_sizes=recv_counts,
                            group=group)
-    d_all = torch.empty((rows, H), dtype=torch.float32, device=x.device)
-    d_all[order] = back.float()
-    y = (d_all.reshape(T, k, H) * expert_probs.reshape(T, k, 1).float()).sum(dim=1)
+    w_sorted = expert_probs.reshape(rows)[order].float()
+    y = torch.zeros((T, H), dtype=torch.float32, device=x.device)
+    y.index_add_(0, tok[order], back.float() * w_sorted[:, None])
     return y.to(x.dtype)
