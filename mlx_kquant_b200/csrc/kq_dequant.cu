@@ -112,6 +112,44 @@ dequant_kernel(const uint8_t* __restrict__ w, T* __restrict__ out, long long n_b
   const uint8_t* tile_s = stage + phase;
   T* out_t = out + b0 * WPB;
   const int n_oct = nb * OPB;
+  if constexpr ((C == Q4_K || C == Q5_K) && A >= 4) {
+    // The 6-bit scale / min pair of a sub-block serves 32 weights: unpack each pair once per tile
+    // (one per thread: TB * 8 = 256 of them) instead of once per eight weights. Same arithmetic as
+    // decode8<>: sc = d * scale, mn = dmin * min in fp32, v = sc * q - mn (sc * q is exact).
+    float2* scmn = reinterpret_cast<float2*>(smem + ((kStage + 15) & ~15));
+    for (int i = threadIdx.x; i < nb * 8; i += kDqThreads) {
+      const uint8_t* blk = tile_s + (i >> 3) * BPB;
+      const uint32_t h = ld32<A>(blk);
+      const float d = __half2float(__ushort_as_half((unsigned short)(h & 0xffff)));
+      const float dmin = __half2float(__ushort_as_half((unsigned short)(h >> 16)));
+      uint32_t rsc, rmn;
+      k4_scale_min(ld32<A>(blk + 4), ld32<A>(blk + 8), ld32<A>(blk + 12), i & 7, rsc, rmn);
+      scmn[i] = make_float2(d * u2f(rsc), dmin * u2f(rmn));
+    }
+    __syncthreads();
+    for (int o = threadIdx.x; o < n_oct; o += kDqThreads) {
+      const int blk = o / OPB, j = o % OPB;
+      const int sb = j >> 2, i0 = (j & 3) * 8;
+      const float2 sm = scmn[blk * 8 + sb];
+      const uint8_t* bp = tile_s + blk * BPB;
+      const uint8_t* qs = bp + (C == Q4_K ? 16 : 48) + (sb >> 1) * 32 + i0;
+      const int sh = (sb & 1) * 4;
+      // four nibbles per word in the low halves of its bytes, then one conversion per byte
+      uint32_t n0 = (ld32<A>(qs) >> sh) & 0x0f0f0f0fu, n1 = (ld32<A>(qs + 4) >> sh) & 0x0f0f0f0fu;
+      if constexpr (C == Q5_K) {
+        n0 |= ((ld32<A>(bp + 16 + i0) >> sb) & 0x01010101u) << 4;
+        n1 |= ((ld32<A>(bp + 20 + i0) >> sb) & 0x01010101u) << 4;
+      }
+      float v[8];
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        v[c] = sm.x * u2f((n0 >> (8 * c)) & 0xffu) - sm.y;
+        v[c + 4] = sm.x * u2f((n1 >> (8 * c)) & 0xffu) - sm.y;
+      }
+      Pack8<T>::store(out_t + (size_t)o * 8, v, out_vec != 0);
+    }
+    return;
+  }
   for (int o = threadIdx.x; o < n_oct; o += kDqThreads) {
     const int blk = o / OPB, j = o % OPB;
     float v[8];
@@ -125,6 +163,7 @@ static cudaError_t launch_one(const uint8_t* w, void* out, long long n_blocks, c
   constexpr int WPB = wpb_of(C), BPB = bpb_of(C), TB = kTileW / WPB;
   const long long tiles = (n_blocks + TB - 1) / TB;
   if (tiles == 0) return cudaSuccess;
+  static_assert(kIqSmemBytes >= (kTileW / 256) * 8 * 8, "the k-quant scale table shares the IQ table area");
   const int smem = ((TB * BPB + 32 + 15) & ~15) + kIqSmemBytes;
   const int out_vec = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
   dequant_kernel<C, A, T><<<(unsigned)tiles, kDqThreads, smem, st>>>(w, static_cast<T*>(out), n_blocks, out_vec);
