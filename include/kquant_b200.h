@@ -70,6 +70,16 @@ KQ_API int kq_codec_find(const char* name);
  * of that f32 value. */
 KQ_API int kq_dequantize(const void* w, size_t w_bytes, const char* kquant_type, int out_dtype, void* out, void* stream);
 
+/* ---- quantize: replaces KQuantQuantize::eval_cpu, src/kquant_encode.cpp:48-98 ->
+ * kquant_quantize_dispatch, src/kquant_cpu_encode.cpp:824-859 (op: src/kquant_ops.cpp:550-631) ----
+ * HOST pointers: the reference's encoder is a CPU-only op as well. w: n_weights values of w_dtype
+ * (rows of K), out: n_weights / weights_per_block * bytes_per_block bytes, imatrix: K floats or NULL.
+ * Byte-identical with the reference for q8_0 q4_0 q2_k q3_k q4_k q5_k q6_k; the IQ encoders
+ * (iq4_nl, iq4_xs, iq2_xxs; src/kquant_iq_encode.cpp) are not built: KQ_ERR_UNSUPPORTED.
+ * threads: 0 = all host threads (blocks are independent: the bytes do not depend on it). */
+KQ_API int kq_quantize_cpu(const void* w, int w_dtype, long long n_weights, long long K, const char* kquant_type,
+                           const float* imatrix, void* out, int threads);
+
 /* ---- quantized_matmul: replaces KQuantMatmul::eval_cpu / eval_gpu,
  * src/kquant_matmul.cpp:1104-1164, 1199-1488 (op: src/kquant_ops.cpp:112-183) ----
  * y[rows, N] = x[rows, K] . dequant(w)^T with fp32 accumulation, w laid out

@@ -25,6 +25,8 @@ SIGNATURES = {
                                 C.POINTER(C.c_int), C.POINTER(C.c_int)]),
     "kq_codec_find": (C.c_int, [C.c_char_p]),
     "kq_dequantize": (C.c_int, [C.c_void_p, C.c_size_t, C.c_char_p, C.c_int, C.c_void_p, C.c_void_p]),
+    "kq_quantize_cpu": (C.c_int, [C.c_void_p, C.c_int, C.c_longlong, C.c_longlong, C.c_char_p, C.c_void_p,
+                                  C.c_void_p, C.c_int]),
     "kq_quantized_matmul_workspace_bytes": (C.c_size_t, [C.c_int, C.c_longlong, C.c_int]),
     "kq_quantized_matmul": (C.c_int, [C.c_void_p, C.c_int, C.c_longlong, C.c_int, C.c_longlong, C.c_void_p,
                                       C.c_size_t, C.c_int, C.c_char_p, C.c_int, C.c_void_p, C.c_longlong,

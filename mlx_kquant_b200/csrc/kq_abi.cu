@@ -88,6 +88,36 @@ int kq_dequantize(const void* w, size_t w_bytes, const char* kquant_type, int ou
   return KQ_OK;
 }
 
+int kq_quantize_cpu(const void* w, int w_dtype, long long n_weights, long long K, const char* kquant_type,
+                    const float* imatrix, void* out, int threads) {
+  const int ci = find_codec(kquant_type);
+  if (ci < 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.quantize] Unknown kquant_type: '%s'.",
+                kquant_type ? kquant_type : "(null)");
+  const kq::CodecInfo& c = kq::kCodecs[ci];
+  if (!dtype_ok(w_dtype))
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.quantize] w must be a real floating tensor (float32, float16, or bfloat16).");
+  if (K <= 0 || n_weights < 0 || n_weights % K != 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.quantize] w must have at least 1 dimension.");
+  if (K % c.wpb != 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.quantize] Last dim (%lld) must be a multiple of weights_per_block (%d) for codec '%s'.", K,
+                c.wpb, c.name);
+  if (c.requires_imatrix && imatrix == nullptr)
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.quantize] codec '%s' requires an importance matrix (imatrix); ggml rejects encoding it "
+                "without one.",
+                c.name);
+  if (!kq::quantize_supported(ci))
+    return fail(KQ_ERR_UNSUPPORTED, "[mlx_kquant.quantize] the host encoder of codec '%s' is not built in this library.",
+                c.name);
+  if (n_weights == 0) return KQ_OK;
+  if (w == nullptr || out == nullptr) return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.quantize] null pointer.");
+  kq::quantize_host(ci, w, w_dtype, n_weights, K, imatrix, static_cast<uint8_t*>(out), threads);
+  return KQ_OK;
+}
+
 size_t kq_quantized_matmul_workspace_bytes(int x_dtype, long long rows, int K) {
   if (!dtype_ok(x_dtype) || rows <= 0 || K <= 0) return 0;
   return kq::gemm_workspace_bytes(x_dtype, rows, K);

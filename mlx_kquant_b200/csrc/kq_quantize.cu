@@ -1,0 +1,464 @@
+// kq_quantize_cpu: float weights -> GGUF wire bytes on the HOST, the producer of everything the GPU
+// kernels read. The reference's `quantize` is a CPU-only op too (src/kquant_ops.cpp:550-631 ->
+// src/kquant_encode.cpp:48-98 -> src/kquant_cpu_encode.cpp:824-859); this file restates the ggml
+// block-fitting searches it uses, in the same operation order, so that the bytes are identical:
+//   q8_0, q4_0     absmax scale, round-half-away (src/kquant_cpu_encode.cpp:38-91)
+//   q4_k, q5_k     per-32 (scale, min) by the 37-step grid search, 6-bit super-scales (:445-540)
+//   q6_k, q3_k     per-16 signed scale by the 19-step search, 8- / 6-bit super-scales (:542-734)
+//   q2_k           per-16 (scale, min), 4-bit super-scales (:736-822)
+// The IQ encoders (iq4_nl, iq4_xs, iq2_xxs; src/kquant_iq_encode.cpp) are not restated: the call
+// reports KQ_ERR_UNSUPPORTED for them.
+// Everything is plain float arithmetic without contraction (no FMA on the host build), one thread
+// per group of rows; blocks are independent, so threading does not change a byte.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <thread>
+#include <vector>
+
+#include "kq_common.cuh"
+#include "kq_launch.h"
+
+namespace kq {
+
+namespace {
+
+inline void put_f16(uint8_t* p, float v) {
+  const __half h = __float2half_rn(v);
+  std::memcpy(p, &h, 2);
+}
+inline float get_f16(const uint8_t* p) {
+  __half h;
+  std::memcpy(&h, p, 2);
+  return __half2float(h);
+}
+inline int rne(float v) { return (int)std::rint(v); }
+inline int clampi(int v, int lo, int hi) { return v < lo ? lo : (v > hi ? hi : v); }
+
+// ---- the three fitting searches ------------------------------------------------------------
+// All follow ggml's routines of the same purpose; comments name the reference's copy.
+
+// (scale, min) of n values with levels 0..nmax, weights wt: start from the min / max line, then try
+// 37 inverse scales around it and keep the weighted-least-squares (scale, min) with the smallest
+// weighted squared error. Returns the scale, *neg_min = -min. (kq_make_qkx3_quants, :250-336)
+float fit_scale_min(const float* x, const float* wt, int n, int nmax, float* neg_min) {
+  float lo = x[0], hi = x[0], sw = wt[0], sx = sw * x[0];
+  for (int i = 1; i < n; i++) {
+    if (x[i] < lo) lo = x[i];
+    if (x[i] > hi) hi = x[i];
+    sw += wt[i];
+    sx += wt[i] * x[i];
+  }
+  if (lo > 0.f) lo = 0.f;
+  if (hi <= lo) {
+    *neg_min = -lo;
+    return 0.f;
+  }
+  float inv = (float)nmax / (hi - lo);
+  float scale = 1.f / inv;
+  float best_err = 0.f;
+  for (int i = 0; i < n; i++) {
+    const int l = clampi(rne(inv * (x[i] - lo)), 0, nmax);
+    const float e = scale * (float)l + lo - x[i];
+    best_err += wt[i] * e * e;
+  }
+  float best_min = lo;
+  uint8_t lv[32];
+  for (int step = 0; step <= 36; step++) {
+    const float inv_s = (-0.9f + 0.05f * (float)step + (float)nmax) / (hi - lo);
+    float sl = 0.f, sl2 = 0.f, sxl = 0.f;
+    for (int i = 0; i < n; i++) {
+      const int l = clampi(rne(inv_s * (x[i] - lo)), 0, nmax);
+      lv[i] = (uint8_t)l;
+      sl += wt[i] * (float)l;
+      sl2 += wt[i] * (float)l * (float)l;
+      sxl += wt[i] * (float)l * x[i];
+    }
+    const float det = sw * sl2 - sl * sl;
+    if (det > 0.f) {
+      float s = (sw * sxl - sx * sl) / det;
+      float m = (sl2 * sx - sl * sxl) / det;
+      if (m > 0.f) {
+        m = 0.f;
+        s = sxl / sl2;
+      }
+      float err = 0.f;
+      for (int i = 0; i < n; i++) {
+        const float e = s * (float)lv[i] + m - x[i];
+        err += wt[i] * e * e;
+      }
+      if (err < best_err) {
+        best_err = err;
+        scale = s;
+        best_min = m;
+      }
+    }
+  }
+  *neg_min = -best_min;
+  return scale;
+}
+
+// Signed scale of 16 values with levels -nmax..nmax-1 (weights wt, or x^2 when wt is null): the
+// scale that maps the largest magnitude to -nmax, then 18 neighbours, keeping the one that
+// maximises (sum w x l)^2 / (sum w l^2). (kq_make_qx_quants_16, :338-397)
+float fit_signed16(const float* x, const float* wt, int nmax) {
+  float big = 0.f, amax = 0.f;
+  for (int i = 0; i < 16; i++) {
+    const float a = std::fabs(x[i]);
+    if (a > amax) {
+      amax = a;
+      big = x[i];
+    }
+  }
+  if (amax < 1e-30f) return 0.f;
+  auto sums = [&](float inv, float& slx, float& sl2) {
+    slx = 0.f;
+    sl2 = 0.f;
+    for (int i = 0; i < 16; i++) {
+      const int l = clampi(rne(inv * x[i]), -nmax, nmax - 1);
+      const float w = wt ? wt[i] : x[i] * x[i];
+      slx += w * x[i] * (float)l;
+      sl2 += w * (float)l * (float)l;
+    }
+  };
+  float slx, sl2;
+  sums(-(float)nmax / big, slx, sl2);
+  float scale = sl2 > 0.f ? slx / sl2 : 0.f;
+  float best = scale * slx;
+  for (int step = -9; step <= 9; step++) {
+    if (step == 0) continue;
+    sums(-((float)nmax + 0.1f * (float)step) / big, slx, sl2);
+    if (sl2 > 0.f && slx * slx > best * sl2) {
+      scale = slx / sl2;
+      best = scale * slx;
+    }
+  }
+  return scale;
+}
+
+// One non-negative scale for n non-negative values with levels 0..nmax: eight neighbours of
+// nmax / max, then up to five rounds of single-level refinement. Writes the levels, returns the
+// scale. (kq_make_qp_quants, src/kquant_cpu_encode_util.h:57-144)
+float fit_positive(const float* x, const float* wt, int n, int nmax, uint8_t* levels) {
+  float top = 0.f;
+  for (int i = 0; i < n; i++)
+    if (x[i] > top) top = x[i];
+  if (top < 1e-30f) {
+    for (int i = 0; i < n; i++) levels[i] = 0;
+    return 0.f;
+  }
+  float inv = (float)nmax / top;
+  uint8_t lv[16];
+  for (int i = 0; i < n; i++) lv[i] = (uint8_t)clampi(rne(inv * x[i]), 0, nmax);
+  const float s0 = 1.f / inv;
+  float best = 0.f;
+  for (int i = 0; i < n; i++) {
+    const float e = x[i] - s0 * (float)lv[i];
+    best += wt[i] * e * e;
+  }
+  for (int step = -4; step <= 4; step++) {
+    if (step == 0) continue;
+    const float inv_s = (0.1f * (float)step + (float)nmax) / top;
+    const float s = 1.f / inv_s;
+    float err = 0.f;
+    for (int i = 0; i < n; i++) {
+      const int l = std::min(nmax, rne(inv_s * x[i]));
+      const float e = x[i] - s * (float)l;
+      err += wt[i] * e * e;
+    }
+    if (err < best) {
+      best = err;
+      inv = inv_s;
+    }
+  }
+  float slx = 0.f, sl2 = 0.f;
+  for (int i = 0; i < n; i++) {
+    const int l = std::min(nmax, rne(inv * x[i]));
+    lv[i] = (uint8_t)l;
+    slx += wt[i] * x[i] * (float)l;
+    sl2 += wt[i] * (float)l * (float)l;
+  }
+  for (int round = 0; round < 5; round++) {
+    int changed = 0;
+    for (int i = 0; i < n; i++) {
+      const float w = wt[i];
+      float a = slx - w * x[i] * (float)lv[i];
+      float b = sl2 - w * (float)lv[i] * (float)lv[i];
+      if (a > 0.f && b > 0.f) {
+        const int nl = std::min(nmax, rne(x[i] * b / a));
+        if (nl != (int)lv[i]) {
+          a += w * x[i] * (float)nl;
+          b += w * (float)nl * (float)nl;
+          if (a * a * sl2 > slx * slx * b) {
+            lv[i] = (uint8_t)nl;
+            slx = a;
+            sl2 = b;
+            changed++;
+          }
+        }
+      }
+    }
+    if (changed == 0) break;
+  }
+  for (int i = 0; i < n; i++) levels[i] = lv[i];
+  return sl2 > 0.f ? slx / sl2 : 0.f;
+}
+
+// importance weights of a superblock: imatrix[k] * sqrt(sigma2 + x^2), or av_x + |x| without one;
+// sigma2 = factor * sum(x^2) / 256 (compute_sigma2_av_x, :237-248)
+void importance(const float* x, const float* im, float factor, bool need_default, float* wt) {
+  float total = 0.f;
+  for (int i = 0; i < 256; i++) total += x[i] * x[i];
+  const float sigma2 = factor * total / 256.0f;
+  if (im) {
+    for (int i = 0; i < 256; i++) wt[i] = im[i] * std::sqrt(sigma2 + x[i] * x[i]);
+  } else if (need_default) {
+    const float av = std::sqrt(sigma2);
+    for (int i = 0; i < 256; i++) wt[i] = av + std::fabs(x[i]);
+  }
+}
+
+// ---- block encoders (x: 32 or 256 floats, im: the matching slice of the imatrix or null) ----
+void enc_q8_0(const float* x, const float*, uint8_t* b) {
+  float amax = 0.f;
+  for (int j = 0; j < 32; j++) amax = std::max(amax, std::fabs(x[j]));
+  const float d = amax / 127.0f, id = d != 0.f ? 1.0f / d : 0.f;
+  put_f16(b, d);
+  for (int j = 0; j < 32; j++)
+    b[2 + j] = (uint8_t)(int8_t)std::min(127.0f, std::max(-127.0f, std::round(x[j] * id)));
+}
+
+void enc_q4_0(const float* x, const float*, uint8_t* b) {
+  float amax = 0.f;
+  for (int j = 0; j < 32; j++) amax = std::max(amax, std::fabs(x[j]));
+  const float d = amax / 7.0f, id = d != 0.f ? 1.0f / d : 0.f;
+  put_f16(b, d);
+  for (int j = 0; j < 16; j++) {
+    const uint8_t q0 = (uint8_t)std::min(15.0f, std::max(0.0f, std::round(x[j] * id) + 8.0f));
+    const uint8_t q1 = (uint8_t)std::min(15.0f, std::max(0.0f, std::round(x[j + 16] * id) + 8.0f));
+    b[2 + j] = (uint8_t)(q0 | (q1 << 4));
+  }
+}
+
+// q4_k (bits = 4) and q5_k (bits = 5)
+template <int BITS>
+void enc_q45_k(const float* x, const float* im, uint8_t* b) {
+  constexpr int nmax = BITS == 4 ? 15 : 31;
+  constexpr int kQs = BITS == 4 ? 16 : 48;
+  float wt[256];
+  importance(x, im, 2.0f, true, wt);
+  float sc[8], mn[8], sw[8];
+  for (int s = 0; s < 8; s++) {
+    float t = 0.f;
+    for (int l = 0; l < 32; l++) t += wt[32 * s + l];
+    sw[s] = t;
+    sc[s] = fit_scale_min(x + 32 * s, wt + 32 * s, 32, nmax, &mn[s]);
+  }
+  uint8_t ls[8], lm[8];
+  put_f16(b, fit_positive(sc, sw, 8, 63, ls));
+  put_f16(b + 2, fit_positive(mn, sw, 8, 63, lm));
+  // twelve bytes of 6-bit pairs (inverse of the decoder's unpacking, src/kquant_cpu_decode.cpp:155-174)
+  uint8_t* p = b + 4;
+  std::memset(p, 0, 12);
+  for (int j = 0; j < 8; j++) {
+    if (j < 4) {
+      p[j] = ls[j];
+      p[j + 4] = lm[j];
+    } else {
+      p[j + 4] = (uint8_t)((ls[j] & 15) | ((lm[j] & 15) << 4));
+      p[j - 4] |= (uint8_t)((ls[j] >> 4) << 6);
+      p[j] |= (uint8_t)((lm[j] >> 4) << 6);
+    }
+  }
+  // levels against the scales as the decoder will see them (fp16 d / dmin, 6-bit integers)
+  const float d = get_f16(b), dmin = get_f16(b + 2);
+  uint8_t L[256];
+  for (int s = 0; s < 8; s++) {
+    const float ds = d * (float)ls[s], ms = dmin * (float)lm[s];
+    for (int l = 0; l < 32; l++) {
+      const int i = 32 * s + l;
+      L[i] = ds == 0.f ? 0 : (uint8_t)clampi(rne((x[i] + ms) / ds), 0, nmax);
+    }
+  }
+  for (int g = 0; g < 4; g++)
+    for (int l = 0; l < 32; l++) b[kQs + 32 * g + l] = (uint8_t)((L[64 * g + l] & 15) | ((L[64 * g + 32 + l] & 15) << 4));
+  if (BITS == 5) {
+    for (int j = 0; j < 32; j++) {
+      uint8_t bits = 0;
+      for (int s = 0; s < 8; s++)
+        if (L[32 * s + j] > 15) bits |= (uint8_t)(1u << s);
+      b[16 + j] = bits;
+    }
+  }
+}
+
+void enc_q6_k(const float* x, const float* im, uint8_t* b) {
+  float sc[16];
+  for (int s = 0; s < 16; s++) sc[s] = fit_signed16(x + 16 * s, im ? im + 16 * s : nullptr, 32);
+  float top = 0.f, atop = 0.f;
+  for (int s = 0; s < 16; s++) {
+    const float a = std::fabs(sc[s]);
+    if (a > atop) {
+      atop = a;
+      top = sc[s];
+    }
+  }
+  if (atop < 1e-30f) {
+    std::memset(b, 0, 210);
+    return;
+  }
+  const float inv = -128.0f / top;
+  put_f16(b + 208, 1.0f / inv);
+  int8_t* so = reinterpret_cast<int8_t*>(b + 192);
+  for (int s = 0; s < 16; s++) so[s] = (int8_t)std::min(127, rne(inv * sc[s]));
+  const float d = get_f16(b + 208);
+  uint8_t L[256];
+  for (int i = 0; i < 256; i++) {
+    const float de = d * (float)so[i / 16];
+    L[i] = de == 0.f ? 32 : (uint8_t)(clampi(rne(x[i] / de), -32, 31) + 32);
+  }
+  for (int h = 0; h < 2; h++) {
+    for (int l = 0; l < 32; l++) {
+      const uint8_t a = L[128 * h + l], bb = L[128 * h + 32 + l], c = L[128 * h + 64 + l], e = L[128 * h + 96 + l];
+      b[64 * h + l] = (uint8_t)((a & 15) | ((c & 15) << 4));
+      b[64 * h + 32 + l] = (uint8_t)((bb & 15) | ((e & 15) << 4));
+      b[128 + 32 * h + l] = (uint8_t)((a >> 4) | ((bb >> 4) << 2) | ((c >> 4) << 4) | ((e >> 4) << 6));
+    }
+  }
+}
+
+void enc_q3_k(const float* x, const float* im, uint8_t* b) {
+  float wt[256];
+  if (im) importance(x, im, 2.0f, false, wt);
+  float sc[16];
+  for (int s = 0; s < 16; s++) sc[s] = fit_signed16(x + 16 * s, im ? wt + 16 * s : nullptr, 4);
+  float top = 0.f, atop = 0.f;
+  for (int s = 0; s < 16; s++) {
+    const float a = std::fabs(sc[s]);
+    if (a > atop) {
+      atop = a;
+      top = sc[s];
+    }
+  }
+  uint8_t* p = b + 96;
+  std::memset(p, 0, 12);
+  float dblk = 0.f;
+  int lsc[16];
+  for (int s = 0; s < 16; s++) lsc[s] = 0;
+  if (top != 0.f) {
+    const float inv = -32.0f / top;
+    for (int s = 0; s < 16; s++) {
+      const int l = clampi(rne(inv * sc[s]), -32, 31) + 32;  // biased, 0..63
+      lsc[s] = l;
+      if (s < 8) p[s] = (uint8_t)(l & 15);
+      else p[s - 8] |= (uint8_t)((l & 15) << 4);
+      p[8 + (s & 3)] |= (uint8_t)(((l >> 4) & 3) << (2 * (s >> 2)));
+    }
+    dblk = 1.0f / inv;
+  }
+  put_f16(b + 108, dblk);
+  const float d = get_f16(b + 108);
+  uint8_t L[256];
+  for (int i = 0; i < 256; i++) {
+    const float de = d * (float)(lsc[i / 16] - 32);
+    L[i] = de == 0.f ? 4 : (uint8_t)(clampi(rne(x[i] / de), -4, 3) + 4);
+  }
+  for (int h = 0; h < 2; h++)
+    for (int l = 0; l < 32; l++) {
+      uint8_t v = 0;
+      for (int k = 0; k < 4; k++) v |= (uint8_t)((L[128 * h + 32 * k + l] & 3) << (2 * k));
+      b[32 + 32 * h + l] = v;
+    }
+  for (int l = 0; l < 32; l++) {
+    uint8_t v = 0;
+    for (int bit = 0; bit < 8; bit++) v |= (uint8_t)(((L[128 * (bit >> 2) + 32 * (bit & 3) + l] >> 2) & 1) << bit);
+    b[l] = v;
+  }
+}
+
+void enc_q2_k(const float* x, const float* im, uint8_t* b) {
+  float wt[256];
+  importance(x, im, 1.0f, true, wt);
+  float sc[16], mn[16], sw[16];
+  for (int s = 0; s < 16; s++) {
+    float t = 0.f;
+    for (int l = 0; l < 16; l++) t += wt[16 * s + l];
+    sw[s] = t;
+    sc[s] = fit_scale_min(x + 16 * s, wt + 16 * s, 16, 3, &mn[s]);
+  }
+  uint8_t ls[16], lm[16];
+  put_f16(b + 80, fit_positive(sc, sw, 16, 15, ls));
+  put_f16(b + 82, fit_positive(mn, sw, 16, 15, lm));
+  for (int s = 0; s < 16; s++) b[s] = (uint8_t)((ls[s] & 15) | ((lm[s] & 15) << 4));
+  const float d = get_f16(b + 80), dmin = get_f16(b + 82);
+  uint8_t L[256];
+  for (int i = 0; i < 256; i++) {
+    const float de = d * (float)(b[i / 16] & 15), me = dmin * (float)(b[i / 16] >> 4);
+    L[i] = de == 0.f ? 0 : (uint8_t)clampi(rne((x[i] + me) / de), 0, 3);
+  }
+  for (int h = 0; h < 2; h++)
+    for (int l = 0; l < 32; l++) {
+      uint8_t v = 0;
+      for (int k = 0; k < 4; k++) v |= (uint8_t)((L[128 * h + 32 * k + l] & 3) << (2 * k));
+      b[16 + 32 * h + l] = v;
+    }
+}
+
+using BlockFn = void (*)(const float*, const float*, uint8_t*);
+BlockFn block_encoder(int codec) {
+  switch (codec) {
+    case Q8_0: return enc_q8_0;
+    case Q4_0: return enc_q4_0;
+    case Q4_K: return enc_q45_k<4>;
+    case Q5_K: return enc_q45_k<5>;
+    case Q6_K: return enc_q6_k;
+    case Q3_K: return enc_q3_k;
+    case Q2_K: return enc_q2_k;
+  }
+  return nullptr;
+}
+
+inline float load_as_float(const void* w, int dtype, long long i) {
+  if (dtype == F32) return static_cast<const float*>(w)[i];
+  if (dtype == F16) return __half2float(static_cast<const __half*>(w)[i]);
+  return __bfloat162float(static_cast<const __nv_bfloat16*>(w)[i]);
+}
+
+}  // namespace
+
+bool quantize_supported(int codec) { return block_encoder(codec) != nullptr; }
+
+// w: n_weights values of dtype (0 f32, 1 f16, 2 bf16) in host memory, rows of K; imatrix: K floats
+// or null; out: n_weights / wpb * bpb bytes. Block b of the flat array uses imatrix[(b * wpb) % K ...]
+// (src/kquant_cpu_encode.cpp:471).
+void quantize_host(int codec, const void* w, int dtype, long long n_weights, long long K, const float* imatrix,
+                   uint8_t* out, int threads) {
+  const BlockFn fn = block_encoder(codec);
+  const int wpb = kCodecs[codec].wpb, bpb = kCodecs[codec].bpb;
+  const long long n_blocks = n_weights / wpb;
+  if (fn == nullptr || n_blocks <= 0) return;
+  const bool uses_imatrix = wpb == 256;  // the flat codecs ignore it (src/kquant_cpu_encode.cpp:832-834)
+  auto run = [&](long long b0, long long b1) {
+    float x[256];
+    for (long long b = b0; b < b1; b++) {
+      for (int i = 0; i < wpb; i++) x[i] = load_as_float(w, dtype, b * wpb + i);
+      const float* im = (imatrix && uses_imatrix) ? imatrix + (b * wpb) % K : nullptr;
+      fn(x, im, out + b * bpb);
+    }
+  };
+  int nt = threads > 0 ? threads : (int)std::thread::hardware_concurrency();
+  nt = (int)std::max(1LL, std::min<long long>(nt > 0 ? nt : 1, n_blocks / 64));
+  if (nt == 1) {
+    run(0, n_blocks);
+    return;
+  }
+  std::vector<std::thread> pool;
+  for (int t = 0; t < nt; t++) pool.emplace_back(run, n_blocks * t / nt, n_blocks * (t + 1) / nt);
+  for (auto& th : pool) th.join();
+}
+
+}  // namespace kq

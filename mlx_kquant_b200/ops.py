@@ -78,6 +78,35 @@ def dequantize(w, scales, kquant_type, dtype=None, *, stream=None):
     return out
 
 
+def quantize(w, kquant_type, imatrix=None, *, stream=None):
+    """Float weights [..., K] -> (wire bytes uint8 [..., K / wpb * bpb], scales placeholder uint8 [1]) on the
+    HOST, like the reference's CPU-only encoder op (src/kquant_ops.cpp:550-631, bindings.cpp:1439-1446).
+    Byte-identical with the reference for q8_0 q4_0 q2_k q3_k q4_k q5_k q6_k; the IQ encoders are not built."""
+    del stream  # host work: there is no stream to order it on
+    if w.dtype not in _DT:
+        raise ValueError("[mlx_kquant.quantize] w must be a real floating tensor (float32, float16, or bfloat16).")
+    if w.dim() < 1:
+        raise ValueError("[mlx_kquant.quantize] w must have at least 1 dimension.")
+    wpb, bpb, _, _ = codec_geometry(kquant_type)  # raises for an unknown codec
+    K = w.shape[-1]
+    if K % wpb != 0:
+        raise ValueError(f"[mlx_kquant.quantize] Last dim ({K}) must be a multiple of weights_per_block ({wpb}) "
+                         f"for codec '{kquant_type}'.")
+    im_ptr = None
+    if imatrix is not None:
+        if imatrix.dtype != torch.float32:
+            raise ValueError("[mlx_kquant.quantize] imatrix must be float32.")
+        if imatrix.dim() != 1 or imatrix.shape[-1] != K:
+            raise ValueError(f"[mlx_kquant.quantize] imatrix shape must be [K]=({K},) but got {tuple(imatrix.shape)}.")
+        imatrix = imatrix.detach().cpu().contiguous()
+        im_ptr = imatrix.data_ptr()
+    w_c = w.detach().cpu().contiguous()
+    out = torch.empty(w.shape[:-1] + (K // wpb * bpb,), dtype=torch.uint8)
+    check(_lib.lib().kq_quantize_cpu(w_c.data_ptr(), _DT[w.dtype], w_c.numel(), K, kquant_type.encode(), im_ptr,
+                                     out.data_ptr(), 0))
+    return out, torch.zeros(1, dtype=torch.uint8)
+
+
 def _prep_x(x: torch.Tensor, device, op: str):
     """Returns (x on device with a dense last dim, was_on_cpu)."""
     if x.dtype not in _DT:
