@@ -831,13 +831,14 @@ __global__ void __launch_bounds__(kDpThreads, 2) gemv_q4k_m1_dp4a_kernel(const G
       unsigned al_lo = 0u, al_hi = 0u;
 #pragma unroll
       for (int j = 0; j < 8; j++) {
-        const uint32_t lo = w[j] & 0x0f0f0f0fu, hi = (w[j] >> 4) & 0x0f0f0f0fu;
+        // high nibbles stay where they are: 16 q as an unsigned byte, the 1/16 goes into the scale
+        const uint32_t lo = w[j] & 0x0f0f0f0fu, hi = w[j] & 0xf0f0f0f0u;
         ah_lo = __dp4a((int)lo, (int)xha[j], ah_lo);
         al_lo = __dp4a(lo, xla[j], al_lo);
-        ah_hi = __dp4a((int)hi, (int)xhb[j], ah_hi);
+        asm("dp4a.u32.s32 %0, %1, %2, %3;\n" : "=r"(ah_hi) : "r"(hi), "r"(xhb[j]), "r"(ah_hi));
         al_hi = __dp4a(hi, xlb[j], al_hi);
       }
-      const float f_lo = (float)(ah_lo * 256 + (int)al_lo), f_hi = (float)(ah_hi * 256 + (int)al_hi);
+      const float f_lo = (float)(ah_lo * 256 + (int)al_lo), f_hi = (float)(ah_hi * 256 + (int)al_hi) * 0.0625f;
       const float sc_lo = byte_to_float(p < 2 ? scl : sch, 2 * (p & 1)), sc_hi = byte_to_float(p < 2 ? scl : sch, 2 * (p & 1) + 1);
       const float mn_lo = byte_to_float(p < 2 ? mnl : mnh, 2 * (p & 1)), mn_hi = byte_to_float(p < 2 ? mnl : mnh, 2 * (p & 1) + 1);
       t1 = fmaf(sc_lo * sg[2 * p], f_lo, t1);
