@@ -540,6 +540,8 @@ convert_x_kernel(const XT* __restrict__ x, long long x_row_stride, int K, __half
     const int entry = order[row / M], i = (int)(row % M);
     src_row = (long long)lhs[entry] * M + i;
     if (threadIdx.x == 0) yrow[row] = entry * M + i;
+  } else if (lhs != nullptr) {
+    src_row = (long long)lhs[row / M] * M + row % M;  // entry order, no sort
   }
   const XT* xr = x + src_row * x_row_stride;
   __half* o = xh + row * (long long)K;
@@ -574,6 +576,22 @@ convert_x_kernel(const XT* __restrict__ x, long long x_row_stride, int K, __half
       o[k] = __float2half_rn(v * down);
     }
   }
+}
+
+cudaError_t launch_convert_rows(int x_dtype, const void* x, long long x_row_stride, int K, long long rows,
+                                const uint32_t* lhs, int M, void* xh, float* row_scale, cudaStream_t st) {
+  if (rows <= 0) return cudaSuccess;
+  __half* o = static_cast<__half*>(xh);
+  if (x_dtype == F16)
+    convert_x_kernel<__half><<<(unsigned)rows, 256, 0, st>>>(static_cast<const __half*>(x), x_row_stride, K, o,
+                                                             row_scale, nullptr, lhs, M, nullptr);
+  else if (x_dtype == BF16)
+    convert_x_kernel<__nv_bfloat16><<<(unsigned)rows, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), x_row_stride,
+                                                                    K, o, row_scale, nullptr, lhs, M, nullptr);
+  else
+    convert_x_kernel<float><<<(unsigned)rows, 256, 0, st>>>(static_cast<const float*>(x), x_row_stride, K, o, row_scale,
+                                                            nullptr, lhs, M, nullptr);
+  return cudaGetLastError();
 }
 
 size_t gemm_workspace_bytes(int x_dtype, long long rows, int K) {

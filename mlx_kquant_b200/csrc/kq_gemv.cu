@@ -1026,7 +1026,12 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_kernel(const GemvArgs a) {
         if (s < S) sum += peer[s][idx];
       OT* y = static_cast<OT*>(a.y) + (long long)s_yrow[tok] * a.y_row_stride + cta_row0 + row;
       if constexpr (kHalf) {
-        *y = __float2half_rn(sum);
+        if (a.out_bf16) {  // rows that were bf16 / f32 before their exact conversion to fp16
+          const float rs = a.row_scale ? a.row_scale[s_xrow[tok]] : 1.f;
+          *reinterpret_cast<__nv_bfloat16*>(y) = __float2bfloat16_rn(sum * rs);
+        } else {
+          *y = __float2half_rn(sum);
+        }
       } else {
         *y = __float2bfloat16_rn(sum);
       }

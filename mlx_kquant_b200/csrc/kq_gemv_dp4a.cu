@@ -622,6 +622,9 @@ bool gemv_dp4a_supported(int codec, int x_dtype, const GemvArgs& a) {
     // their tensor-core kernels, which take sixteen rows per pass over the weights.
     if ((codec == Q4_K && x_dtype == F16) || codec == IQ4_XS || codec == IQ2_XXS) return false;
     if (a.n_tasks > 65535) return false;
+    // measured on a 128-expert block: a win at ~4 rows per expert, a loss at 16 (every four-row slice
+    // streams the expert's weights again)
+    if (a.avg_rows > 4) return false;
     return 4 * x_bytes(a.K) <= 96 * 1024;
   }
   if (codec == Q4_K) return false;  // dense q4_k has its own kernels (kq_gemv.cu)

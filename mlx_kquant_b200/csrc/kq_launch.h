@@ -38,6 +38,11 @@ struct GemvArgs {
   int n_tasks;              // grid.y when tasks != nullptr
   int task_offset;          // index of tasks[0] in the whole task list (for n_tasks_dev)
   int max_m;                // upper bound on any task's m (picks the 8- or 16-row B tile)
+  int avg_rows;             // task lists: average rows per weight matrix (0 = unknown), a dispatch hint
+  // fp16 kernels only: write bfloat16 instead (y = bf16(sum * row_scale[x row])), for callers that
+  // converted bf16 / f32 activations to fp16 with a per-row power-of-two factor
+  int out_bf16;
+  const float* row_scale;   // indexed like the rows of x, or nullptr
 };
 
 // y = x . dequant(w)^T for skinny row groups. x_dtype: 0 f32 (rounded to bf16
@@ -68,6 +73,10 @@ cudaError_t launch_gemm_grouped(int codec, int x_dtype, const void* x, int M, in
                                 int* yrow, const void* tiles, const int* n_tiles_dev, int max_tiles, cudaStream_t st);
 // Flags raised by kernels that gave up on a bounded wait (0 = none); synchronises the device.
 cudaError_t read_device_error(int* out, bool clear);
+// Exact fp16 copy of `rows` activation rows (x_dtype 0 f32 / 1 f16 / 2 bf16) with a per-row power-of-two
+// factor in row_scale (kq_gemm.cu). lhs != nullptr: output row r is x row lhs[r / M] * M + r % M.
+cudaError_t launch_convert_rows(int x_dtype, const void* x, long long x_row_stride, int K, long long rows,
+                                const uint32_t* lhs, int M, void* xh, float* row_scale, cudaStream_t st);
 
 // gather_qmm: device-side grouping by expert + the skinny-M kernel per group.
 struct GatherLayout {
