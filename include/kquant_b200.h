@@ -92,9 +92,11 @@ KQ_API int kq_quantize_cpu(const void* w, int w_dtype, long long n_weights, long
  *  - transpose == 0 ([K, N] weights) is not built yet: KQ_ERR_UNSUPPORTED.
  *  - workspace: kq_quantized_matmul_workspace_bytes(x_dtype, rows, K) bytes of
  *    device memory, 256-byte aligned (0 bytes, and NULL allowed, for fp16
- *    activations or rows <= 16). Calls with more than 16 rows run on the tensor
+ *    activations or a single row). Calls with more than 16 rows run on the tensor
  *    cores in fp16; bf16 / f32 activations are converted there first, exactly, with
- *    a per-row power-of-two factor. */
+ *    a per-row power-of-two factor. With 2-16 rows the workspace is optional: q4_k
+ *    uses it for the same conversion (several times faster), and a call without it
+ *    still works. */
 KQ_API size_t kq_quantized_matmul_workspace_bytes(int x_dtype, long long rows, int K);
 KQ_API int kq_quantized_matmul(const void* x, int x_dtype, long long rows, int K, long long x_row_stride, const void* w,
                         size_t w_row_bytes, int N, const char* kquant_type, int transpose, void* y,

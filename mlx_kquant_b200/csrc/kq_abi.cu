@@ -181,7 +181,26 @@ int kq_quantized_matmul(const void* x, int x_dtype, long long rows, int K, long 
     a.N = N;
     a.K = K;
     a.M = (int)rows;
-    e = kq::launch_gemv(ci, x_dtype, a, static_cast<cudaStream_t>(stream));
+    // q4_k, 2-16 rows of bf16 / f32 activations, scratch at hand: exact fp16 copy of the rows (per-row
+    // power-of-two factor), then the fp16 tensor-core decode kernel writing bf16(sum * factor) - several
+    // times faster than the path that takes bf16 rows directly. Without scratch that path still serves.
+    const size_t need = kq::gemm_workspace_bytes(x_dtype, rows, K);
+    int eff_dtype = x_dtype;
+    if (ci == kq::Q4_K && x_dtype != KQ_F16 && rows >= 2 && a.w_align16 && (w_row_bytes & 15) == 0 &&
+        workspace != nullptr && workspace_bytes >= need && need > 0 &&
+        (reinterpret_cast<uintptr_t>(workspace) & 255) == 0) {
+      float* rs = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) +
+                                           (((size_t)rows * (size_t)K * 2 + 255) & ~(size_t)255));
+      e = kq::launch_convert_rows(x_dtype, x, x_row_stride, K, rows, nullptr, 1, workspace, rs,
+                                  static_cast<cudaStream_t>(stream));
+      if (e != cudaSuccess) return cuda_fail("quantized_matmul", e);
+      a.x = workspace;
+      a.x_row_stride = K;
+      a.out_bf16 = 1;
+      a.row_scale = rs;
+      eff_dtype = KQ_F16;
+    }
+    e = kq::launch_gemv(ci, eff_dtype, a, static_cast<cudaStream_t>(stream));
   }
   if (e != cudaSuccess) return cuda_fail("quantized_matmul", e);
   return KQ_OK;

@@ -595,7 +595,8 @@ cudaError_t launch_convert_rows(int x_dtype, const void* x, long long x_row_stri
 }
 
 size_t gemm_workspace_bytes(int x_dtype, long long rows, int K) {
-  if (x_dtype == F16 || rows <= 16) return 0;
+  // rows 2..16 of bf16 / f32 activations use the same fp16 copy (q4_k decode kernel); one row never does
+  if (x_dtype == F16 || rows <= 1) return 0;
   const size_t xh = ((size_t)rows * (size_t)K * 2 + 255) & ~(size_t)255;
   return xh + (((size_t)rows * 4 + 255) & ~(size_t)255);
 }
