@@ -6,8 +6,9 @@
 //   q4_k, q5_k     per-32 (scale, min) by the 37-step grid search, 6-bit super-scales (:445-540)
 //   q6_k, q3_k     per-16 signed scale by the 19-step search, 8- / 6-bit super-scales (:542-734)
 //   q2_k           per-16 (scale, min), 4-bit super-scales (:736-822)
-// The IQ encoders (iq4_nl, iq4_xs, iq2_xxs; src/kquant_iq_encode.cpp) are not restated: the call
-// reports KQ_ERR_UNSUPPORTED for them.
+//   iq4_nl, iq4_xs 16-level table, per-32 scale by a 15-step search (src/kquant_iq_encode.cpp:49-223)
+// The lattice encoder of iq2_xxs (src/kquant_iq_encode.cpp:228-598) is not restated: the call reports
+// KQ_ERR_UNSUPPORTED for it.
 // Everything is plain float arithmetic without contraction (no FMA on the host build), one thread
 // per group of rows; blocks are independent, so threading does not change a byte.
 #include <cuda_bf16.h>
@@ -408,6 +409,106 @@ void enc_q2_k(const float* x, const float* im, uint8_t* b) {
     }
 }
 
+// ---- iq4_nl / iq4_xs: the 16 non-uniform levels of ggml's kvalues_iq4nl ------------------------
+const int8_t kLevels[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+
+// index of the level nearest to v; ties go to the lower index (best_index_int8, :49-68)
+inline int nearest_level(float v) {
+  if (v <= (float)kLevels[0]) return 0;
+  if (v >= (float)kLevels[15]) return 15;
+  int lo = 0, hi = 15;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) / 2;
+    if (v < (float)kLevels[mid]) hi = mid;
+    else lo = mid;
+  }
+  return v - (float)kLevels[hi - 1] < (float)kLevels[hi] - v ? hi - 1 : hi;
+}
+
+// n = 32 (iq4_nl: [f16 d][16 B]) or 256 (iq4_xs: [f16 d][u16 high scale bits][4 B low nibbles][128 B]).
+// Per 32 weights: the scale that maps the largest magnitude to level -127, then 15 neighbours, keeping
+// the one with the largest (sum w q x)^2 / (sum w q^2). (quantize_iq4_block, :73-223, ntry = 7)
+template <int N>
+void enc_iq4(const float* x, const float* im, uint8_t* b) {
+  constexpr int nsb = N / 32;
+  float sigma2 = 0.f;
+  for (int j = 0; j < N; j++) sigma2 += x[j] * x[j];
+  sigma2 *= 2.f / (float)N;
+  float scales[8];
+  float top = 0.f, atop = 0.f;
+  for (int ib = 0; ib < nsb; ib++) {
+    const float* xb = x + 32 * ib;
+    float wt[32];
+    for (int j = 0; j < 32; j++) wt[j] = im ? im[32 * ib + j] * std::sqrt(sigma2 + xb[j] * xb[j]) : xb[j] * xb[j];
+    float amax = 0.f, big = 0.f;
+    for (int j = 0; j < 32; j++) {
+      const float a = std::fabs(xb[j]);
+      if (a > amax) {
+        amax = a;
+        big = xb[j];
+      }
+    }
+    if (amax < 1e-15f) {
+      scales[ib] = 0.f;
+      continue;
+    }
+    auto sums = [&](float inv, float& sqx, float& sq2) {
+      sqx = 0.f;
+      sq2 = 0.f;
+      for (int j = 0; j < 32; j++) {
+        const float q = (float)kLevels[nearest_level(inv * xb[j])];
+        sqx += wt[j] * q * xb[j];
+        sq2 += wt[j] * q * q;
+      }
+    };
+    float d = -big / (float)kLevels[0];
+    float sqx, sq2;
+    sums(1.f / d, sqx, sq2);
+    d = sq2 > 0.f ? sqx / sq2 : 0.f;
+    float best = d * sqx;
+    for (int step = -7; step <= 7; step++) {
+      sums(((float)step + (float)kLevels[0]) / big, sqx, sq2);
+      if (sq2 > 0.f && sqx * sqx > best * sq2) {
+        d = sqx / sq2;
+        best = d * sqx;
+      }
+    }
+    scales[ib] = d;
+    if (std::fabs(d) > atop) {
+      atop = std::fabs(d);
+      top = d;
+    }
+  }
+  uint8_t L[256];
+  uint8_t* q4;
+  if (nsb > 1) {
+    q4 = b + 8;
+    std::memset(b + 4, 0, 4);
+    uint32_t high = 0;
+    const float d = -top / 32.f;
+    put_f16(b, d);
+    const float id = d != 0.f ? 1.f / d : 0.f;
+    for (int ib = 0; ib < nsb; ib++) {
+      int l = clampi(rne(id * scales[ib]), -32, 31);
+      const float dl = d * (float)l;
+      const float idl = dl != 0.f ? 1.f / dl : 0.f;
+      for (int j = 0; j < 32; j++) L[32 * ib + j] = (uint8_t)nearest_level(idl * x[32 * ib + j]);
+      l += 32;
+      b[4 + ib / 2] |= (uint8_t)((l & 15) << (4 * (ib & 1)));
+      high |= (uint32_t)(l >> 4) << (2 * ib);
+    }
+    b[2] = (uint8_t)(high & 0xff);
+    b[3] = (uint8_t)(high >> 8);
+  } else {
+    q4 = b + 2;
+    put_f16(b, scales[0]);
+    const float id = scales[0] != 0.f ? 1.f / scales[0] : 0.f;
+    for (int j = 0; j < 32; j++) L[j] = (uint8_t)nearest_level(id * x[j]);
+  }
+  for (int i = 0; i < nsb; i++)
+    for (int j = 0; j < 16; j++) q4[16 * i + j] = (uint8_t)(L[32 * i + j] | (L[32 * i + 16 + j] << 4));
+}
+
 using BlockFn = void (*)(const float*, const float*, uint8_t*);
 BlockFn block_encoder(int codec) {
   switch (codec) {
@@ -418,6 +519,8 @@ BlockFn block_encoder(int codec) {
     case Q6_K: return enc_q6_k;
     case Q3_K: return enc_q3_k;
     case Q2_K: return enc_q2_k;
+    case IQ4_NL: return enc_iq4<32>;
+    case IQ4_XS: return enc_iq4<256>;
   }
   return nullptr;
 }
@@ -441,7 +544,7 @@ void quantize_host(int codec, const void* w, int dtype, long long n_weights, lon
   const int wpb = kCodecs[codec].wpb, bpb = kCodecs[codec].bpb;
   const long long n_blocks = n_weights / wpb;
   if (fn == nullptr || n_blocks <= 0) return;
-  const bool uses_imatrix = wpb == 256;  // the flat codecs ignore it (src/kquant_cpu_encode.cpp:832-834)
+  const bool uses_imatrix = !(codec == Q8_0 || codec == Q4_0);  // the flat codecs ignore it (src/kquant_cpu_encode.cpp:832-834)
   auto run = [&](long long b0, long long b1) {
     float x[256];
     for (long long b = b0; b < b1; b++) {

@@ -9,8 +9,8 @@ import torch
 import mlx_kquant_b200 as kq
 from oracle import kq_oracle
 
-BUILT = ("q8_0", "q4_0", "q2_k", "q3_k", "q4_k", "q5_k", "q6_k")
-NOT_BUILT = ("iq4_nl", "iq4_xs", "iq2_xxs")
+BUILT = ("q8_0", "q4_0", "q2_k", "q3_k", "q4_k", "q5_k", "q6_k", "iq4_nl", "iq4_xs")
+NOT_BUILT = ("iq2_xxs",)
 
 
 @pytest.fixture(scope="module")
@@ -79,7 +79,7 @@ def test_argument_errors():
 
 
 @pytest.mark.parametrize("codec", NOT_BUILT)
-def test_iq_encoders_report_unsupported(codec):
+def test_lattice_encoder_reports_unsupported(codec):
     W = torch.zeros(2, 256)
     with pytest.raises(Exception, match="not built"):
         kq.quantize(W, codec, torch.ones(256))
