@@ -74,8 +74,8 @@ KQ_API int kq_dequantize(const void* w, size_t w_bytes, const char* kquant_type,
  * kquant_quantize_dispatch, src/kquant_cpu_encode.cpp:824-859 (op: src/kquant_ops.cpp:550-631) ----
  * HOST pointers: the reference's encoder is a CPU-only op as well. w: n_weights values of w_dtype
  * (rows of K), out: n_weights / weights_per_block * bytes_per_block bytes, imatrix: K floats or NULL.
- * Byte-identical with the reference for q8_0 q4_0 q2_k q3_k q4_k q5_k q6_k iq4_nl iq4_xs; the lattice
- * encoder of iq2_xxs (src/kquant_iq_encode.cpp:228-598) is not built: KQ_ERR_UNSUPPORTED.
+ * Byte-identical with the reference for all ten codecs (the IQ ones: src/kquant_iq_encode.cpp:2099-2176);
+ * iq2_xxs requires an imatrix, as in the reference.
  * threads: 0 = all host threads (blocks are independent: the bytes do not depend on it). */
 KQ_API int kq_quantize_cpu(const void* w, int w_dtype, long long n_weights, long long K, const char* kquant_type,
                            const float* imatrix, void* out, int threads);

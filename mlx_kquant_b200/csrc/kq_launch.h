@@ -107,7 +107,7 @@ int gather_qmm_entry(const void* x, int x_dtype, long long x_batch, int M, int K
 int set_error(int code, const char* msg);
 
 // Host-side encoder (kq_quantize.cu): float weights -> wire bytes, byte-identical with the
-// reference's CPU encoder for q8_0 q4_0 q2_k q3_k q4_k q5_k q6_k iq4_nl iq4_xs.
+// reference's CPU encoder for all ten codecs.
 bool quantize_supported(int codec);
 void quantize_host(int codec, const void* w, int dtype, long long n_weights, long long K, const float* imatrix,
                    uint8_t* out, int threads);

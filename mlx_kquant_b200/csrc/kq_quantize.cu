@@ -7,8 +7,8 @@
 //   q6_k, q3_k     per-16 signed scale by the 19-step search, 8- / 6-bit super-scales (:542-734)
 //   q2_k           per-16 (scale, min), 4-bit super-scales (:736-822)
 //   iq4_nl, iq4_xs 16-level table, per-32 scale by a 15-step search (src/kquant_iq_encode.cpp:49-223)
-// The lattice encoder of iq2_xxs (src/kquant_iq_encode.cpp:228-598) is not restated: the call reports
-// KQ_ERR_UNSUPPORTED for it.
+//   iq2_xxs        8-weight lattice points with parity-constrained signs; nearest-neighbour lists of
+//                  off-lattice points built once from the decode lattice (:228-598)
 // Everything is plain float arithmetic without contraction (no FMA on the host build), one thread
 // per group of rows; blocks are independent, so threading does not change a byte.
 #include <cuda_bf16.h>
@@ -23,6 +23,14 @@
 
 #include "kq_common.cuh"
 #include "kq_launch.h"
+
+// a host copy of the generated tables (kq_common.cuh holds the device copy)
+#undef KQ_IQ_TABLES_INC
+#undef KQ_TAB_QUAL
+#define KQ_TAB_QUAL static
+namespace kq_host_tabs {
+#include "kq_iq_tables.inc"
+}
 
 namespace kq {
 
@@ -144,16 +152,16 @@ float fit_signed16(const float* x, const float* wt, int nmax) {
 // One non-negative scale for n non-negative values with levels 0..nmax: eight neighbours of
 // nmax / max, then up to five rounds of single-level refinement. Writes the levels, returns the
 // scale. (kq_make_qp_quants, src/kquant_cpu_encode_util.h:57-144)
-float fit_positive(const float* x, const float* wt, int n, int nmax, uint8_t* levels) {
+float fit_positive(const float* x, const float* wt, int n, int nmax, uint8_t* levels, float eps = 1e-30f) {
   float top = 0.f;
   for (int i = 0; i < n; i++)
     if (x[i] > top) top = x[i];
-  if (top < 1e-30f) {
+  if (top < eps) {
     for (int i = 0; i < n; i++) levels[i] = 0;
     return 0.f;
   }
   float inv = (float)nmax / top;
-  uint8_t lv[16];
+  uint8_t lv[32];
   for (int i = 0; i < n; i++) lv[i] = (uint8_t)clampi(rne(inv * x[i]), 0, nmax);
   const float s0 = 1.f / inv;
   float best = 0.f;
@@ -509,6 +517,208 @@ void enc_iq4(const float* x, const float* im, uint8_t* b) {
     for (int j = 0; j < 16; j++) q4[16 * i + j] = (uint8_t)(L[32 * i + j] | (L[32 * i + 16 + j] << 4));
 }
 
+// ---- iq2_xxs --------------------------------------------------------------------------------------
+// Search space: eight levels l in {0, 1, 2} (decoded as 8, 25, 43), searched as 2 l + 1, packed two bits
+// each into an index < 43692. `slot[index]` is the lattice entry, or -(offset + 1) into `near`, where a
+// count and that many entries list the lattice points at the two smallest distances (ties by entry
+// number). Built once from the decode lattice. (build_iq_grid_index, :235-330, nwant = 2)
+struct Lattice {
+  int8_t point[256][8];
+  std::vector<int> slot;
+  std::vector<uint16_t> near;
+  Lattice() : slot(43692, -1) {
+    for (int e = 0; e < 256; e++) {
+      int index = 0;
+      for (int i = 0; i < 8; i++) {
+        const int byte = (int)((kq_host_tabs::kq_tab_iq2xxs_grid[e] >> (8 * i)) & 0xff);
+        const int l = byte == 8 ? 0 : (byte == 25 ? 1 : 2);
+        point[e][i] = (int8_t)(2 * l + 1);
+        index |= l << (2 * i);
+      }
+      slot[index] = e;
+    }
+    std::vector<std::pair<int, int>> dist(256);
+    for (int idx = 0; idx < (int)slot.size(); idx++) {
+      if (slot[idx] >= 0) continue;
+      for (int e = 0; e < 256; e++) {
+        int d2 = 0;
+        for (int i = 0; i < 8; i++) {
+          const int diff = point[e][i] - (2 * ((idx >> (2 * i)) & 3) + 1);
+          d2 += diff * diff;
+        }
+        dist[e] = {d2, e};
+      }
+      std::sort(dist.begin(), dist.end());
+      const int at = (int)near.size();
+      near.push_back(0);
+      int d2 = dist[0].first, have = 1;
+      for (int e = 0; e < 256; e++) {
+        if (dist[e].first > d2) {
+          if (have == 2) break;
+          d2 = dist[e].first;
+          have++;
+        }
+        near.push_back((uint16_t)dist[e].second);
+      }
+      near[at] = (uint16_t)(near.size() - at - 1);
+      slot[idx] = -(at + 1);
+    }
+  }
+};
+const Lattice& lattice() {
+  static const Lattice l;  // thread-safe one-time construction
+  return l;
+}
+
+// lattice entry for the packed levels u; off-lattice: the listed neighbour with the smallest weighted
+// squared error to the scaled point (iq2_find_best_neighbour, :359-389)
+inline int lattice_entry(const Lattice& G, int u, const float* xv, const float* w, float scale) {
+  int e = G.slot[u];
+  if (e >= 0) return e;
+  const uint16_t* nb = G.near.data() + (-e - 1);
+  float best = 3.402823466e+38f;
+  e = -1;
+  for (int j = 1; j <= (int)nb[0]; j++) {
+    const int8_t* pg = G.point[nb[j]];
+    float d2 = 0.f;
+    for (int i = 0; i < 8; i++) {
+      const float diff = scale * (float)pg[i] - xv[i];
+      d2 += w[i] * diff * diff;
+    }
+    if (d2 < best) {
+      best = d2;
+      e = nb[j];
+    }
+  }
+  return e;
+}
+
+// (quantize_iq2_xxs_block, :392-598)
+void enc_iq2_xxs(const float* x, const float* im, uint8_t* b) {
+  const Lattice& G = lattice();
+  uint32_t q2[16];
+  std::memset(q2, 0, sizeof(q2));
+  float total = 0.f;
+  for (int i = 0; i < 256; i++) total += x[i] * x[i];
+  const float sigma2 = total / 256.0f;
+  float scales[8], top = 0.f;
+  for (int ib = 0; ib < 8; ib++) {
+    const float* xb = x + 32 * ib;
+    float wt[32], wsq[32], xv[32];
+    for (int i = 0; i < 32; i++) wt[i] = im[32 * ib + i] * std::sqrt(sigma2 + xb[i] * xb[i]);
+    for (int i = 0; i < 32; i++) wsq[i] = std::sqrt(wt[i]);
+    // magnitudes and sign bits; an odd number of negatives flips the least important weight so that the
+    // eighth sign is the parity of the other seven
+    uint8_t signs[4];
+    for (int k = 0; k < 4; k++) {
+      int flips = 0;
+      uint8_t sb = 0;
+      for (int i = 0; i < 8; i++) {
+        const float v = xb[8 * k + i];
+        if (v >= 0.f) {
+          xv[8 * k + i] = v;
+        } else {
+          xv[8 * k + i] = -v;
+          flips++;
+          sb |= (uint8_t)(1 << i);
+        }
+      }
+      if (flips & 1) {
+        int imin = 0;
+        float least = wt[8 * k] * xb[8 * k] * xb[8 * k];
+        for (int i = 1; i < 8; i++) {
+          const float a = wt[8 * k + i] * xb[8 * k + i] * xb[8 * k + i];
+          if (a < least) {
+            least = a;
+            imin = i;
+          }
+        }
+        xv[8 * k + imin] = -xv[8 * k + imin];
+        sb ^= (uint8_t)(1 << imin);
+      }
+      signs[k] = sb & 127;
+    }
+    float mx = xv[0];
+    for (int i = 1; i < 32; i++) mx = std::max(mx, xv[i]);
+    scales[ib] = 0.f;
+    if (mx < 1e-15f) continue;
+    int8_t L[32], La[32];
+    float scale = fit_positive(xv, wt, 32, 4, reinterpret_cast<uint8_t*>(L), 1e-15f);
+    const float eff_max = scale * 3;
+    if (eff_max <= 0.f) continue;
+    auto levels_of = [&](float id, int k, int8_t* out) {
+      int u = 0;
+      for (int i = 0; i < 8; i++) {
+        const int l = clampi(rne(0.5f * (id * xv[8 * k + i] - 1)), 0, 2);
+        out[i] = (int8_t)l;
+        u |= l << (2 * i);
+      }
+      return u;
+    };
+    auto score = [&](const int8_t* lv, float& sqx, float& sq2) {
+      sqx = 0.f;
+      sq2 = 0.f;
+      for (int i = 0; i < 32; i++) {
+        const float q = (float)(2 * lv[i] + 1);
+        sqx += wt[i] * xv[i] * q;
+        sq2 += wt[i] * q * q;
+      }
+    };
+    float best = 0.f, sqx, sq2;
+    for (int step = -6; step <= 6; step++) {
+      const float id = (5 + step * 0.1f) / eff_max;
+      const float this_scale = 1 / id;
+      for (int k = 0; k < 4; k++) {
+        const int u = levels_of(id, k, La + 8 * k);
+        if (G.slot[u] < 0) {
+          const int8_t* pg = G.point[lattice_entry(G, u, xv + 8 * k, wsq + 8 * k, this_scale)];
+          for (int i = 0; i < 8; i++) La[8 * k + i] = (int8_t)((pg[i] - 1) / 2);
+        }
+      }
+      score(La, sqx, sq2);
+      if (sq2 > 0.f && sqx * sqx > best * sq2) {
+        scale = sqx / sq2;
+        best = scale * sqx;
+        std::memcpy(L, La, 32);
+      }
+    }
+    if (scale > 0.f) {
+      const float id = 1 / scale;
+      for (int k = 0; k < 4; k++) {
+        int8_t tmp[8];
+        const int u = levels_of(id, k, tmp);
+        const int8_t* pg = G.point[lattice_entry(G, u, xv + 8 * k, wsq + 8 * k, scale)];
+        for (int i = 0; i < 8; i++) L[8 * k + i] = (int8_t)((pg[i] - 1) / 2);
+      }
+      score(L, sqx, sq2);
+      if (sq2 > 0.f) scale = sqx / sq2;
+    }
+    if (scale < 0.f) {  // the wire holds an unsigned scale: move the sign into the sign bits
+      scale = -scale;
+      for (int k = 0; k < 4; k++) signs[k] = (uint8_t)((~signs[k]) & 127);
+    }
+    for (int k = 0; k < 4; k++) {
+      int u = 0;
+      for (int i = 0; i < 8; i++) u |= L[8 * k + i] << (2 * i);
+      const int e = G.slot[u] >= 0 ? G.slot[u] : 0;  // always on the lattice after the step above
+      q2[2 * ib] |= (uint32_t)e << (8 * k);
+      q2[2 * ib + 1] |= (uint32_t)signs[k] << (7 * k);
+    }
+    scales[ib] = scale;
+    top = std::max(top, scale);
+  }
+  if (!(top != 0.f)) {
+    put_f16(b, 0.f);
+    std::memset(b + 2, 0, 64);
+    return;
+  }
+  const float d = top / 31;
+  put_f16(b, d);
+  const float id = 1 / d;
+  for (int ib = 0; ib < 8; ib++) q2[2 * ib + 1] |= (uint32_t)clampi(rne(0.5f * (id * scales[ib] - 1)), 0, 15) << 28;
+  std::memcpy(b + 2, q2, 64);
+}
+
 using BlockFn = void (*)(const float*, const float*, uint8_t*);
 BlockFn block_encoder(int codec) {
   switch (codec) {
@@ -521,6 +731,7 @@ BlockFn block_encoder(int codec) {
     case Q2_K: return enc_q2_k;
     case IQ4_NL: return enc_iq4<32>;
     case IQ4_XS: return enc_iq4<256>;
+    case IQ2_XXS: return enc_iq2_xxs;
   }
   return nullptr;
 }
