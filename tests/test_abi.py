@@ -57,7 +57,8 @@ def test_abi_validation_needs_no_gpu():
     assert L.kq_quantized_matmul(None, 1, 0, 512, 512, None, 288, 4, b"q4_k", 1, None, 4, None, 0, None) == 0
     assert L.kq_quantized_matmul_workspace_bytes(1, 4096, 4096) == 0        # fp16 needs none
     assert L.kq_quantized_matmul_workspace_bytes(2, 4096, 4096) >= 4096 * 4096 * 2
-    assert L.kq_quantized_matmul_workspace_bytes(2, 16, 4096) == 0          # decode regime needs none
+    assert L.kq_quantized_matmul_workspace_bytes(2, 16, 4096) >= 16 * 4096 * 2  # optional fp16 copy of 2-16 rows
+    assert L.kq_quantized_matmul_workspace_bytes(2, 1, 4096) == 0           # a single row never needs one
     assert L.kq_gather_qmm_workspace_bytes(8, 1, 128, 2048) > 0
 
 
