@@ -220,7 +220,7 @@ def extra_cells(dev):
     import torch
 
     import mlx_kquant_b200 as kq
-    from mlx_kquant_b200.moe import moe_glu, route_topk
+    from mlx_kquant_b200.moe import fuse_gate_up, moe_glu, route_topk
     from mlx_kquant_b200.synth import random_wire
 
     def timed(fn, reps=5):
@@ -259,11 +259,12 @@ def extra_cells(dev):
     wg = random_wire("q4_k", F, H, seed=5, device=dev, lead=(E,))
     wu = random_wire("q4_k", F, H, seed=6, device=dev, lead=(E,))
     wd = random_wire("q4_k", H, F, seed=7, device=dev, lead=(E,))
+    wgu = fuse_gate_up(wg, wu)  # gate | up of every expert as one [E, 2F, bytes] stack: a load-time layout choice
     g = torch.Generator(device="cpu").manual_seed(3000)
     for T in (1, 64, 4096):
         x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(dev)
         ids, probs = route_topk(torch.randn(T, E, generator=g).to(dev), k)
-        t = timed(lambda: moe_glu(x, wg, wu, wd, "q4_k", ids, probs), reps=3)
+        t = timed(lambda: moe_glu(x, None, None, wd, "q4_k", ids, probs, w_gate_up=wgu), reps=3)
         out[f"moe_glu_q4k_T{T}"] = {"tokens_per_s": T / t, "ms": t * 1e3}
         # the same block replayed from a CUDA graph (no host sync inside it): what a serving loop pays
         try:
@@ -271,11 +272,11 @@ def extra_cells(dev):
             side.wait_stream(torch.cuda.current_stream(dev))
             with torch.cuda.stream(side):
                 for _ in range(2):
-                    moe_glu(x, wg, wu, wd, "q4_k", ids, probs)
+                    moe_glu(x, None, None, wd, "q4_k", ids, probs, w_gate_up=wgu)
                 side.synchronize()
                 gr = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(gr, stream=side):
-                    y_cap = moe_glu(x, wg, wu, wd, "q4_k", ids, probs)
+                    y_cap = moe_glu(x, None, None, wd, "q4_k", ids, probs, w_gate_up=wgu)
             torch.cuda.current_stream(dev).wait_stream(side)
             tg = timed(gr.replay, reps=5)
             out[f"moe_glu_q4k_T{T}"]["graph_tokens_per_s"] = T / tg

@@ -89,7 +89,9 @@ KQ_API int kq_quantize_cpu(const void* w, int w_dtype, long long n_weights, long
  *  - x rows: `rows` of them (all leading dims of the reference's x flattened),
  *    x_row_stride elements apart, each row contiguous and 16-byte aligned.
  *  - y rows are y_row_stride elements apart.
- *  - transpose == 0 ([K, N] weights) is not built yet: KQ_ERR_UNSUPPORTED.
+ *  - transpose == 0: w is [K, N / weights_per_block * bytes_per_block] (every row a quantized vector of N
+ *    weights), y = x . dequant(w); served by a plain streaming kernel (any M, tuned for small M); x needs
+ *    element alignment only.
  *  - workspace: kq_quantized_matmul_workspace_bytes(x_dtype, rows, K) bytes of
  *    device memory, 256-byte aligned (0 bytes, and NULL allowed, for fp16
  *    activations or a single row). Calls with more than 16 rows run on the tensor
@@ -129,6 +131,19 @@ KQ_API int kq_gather_qmm(const void* x, int x_dtype, long long x_batch, int M, i
                   long long w_expert_stride_bytes, size_t w_row_bytes, int N, const char* kquant_type,
                   const uint32_t* lhs_indices, const uint32_t* rhs_indices, long long n_entries, int transpose,
                   int rhs_sorted, void* y, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- the elementwise stages of a mixture-of-experts SwiGLU block ----
+ * Not among the reference's three ops: they are the stages its fused Metal MoE op (moe_glu_gather_kq,
+ * src/kquant.h:335-357; no CPU evaluation) performs between the three gathered products, offered here so that
+ * a block composed of kq_gather_qmm calls needs no generic elementwise passes. Device pointers, dtype KQ_F16
+ * or KQ_BF16, fp32 arithmetic, one rounding.
+ *  kq_swiglu:      out[r, c] = silu(gate[r * in_row_stride + c]) * up[r * in_row_stride + c], c < F; out is
+ *                  [rows, F] dense. A fused [rows, 2F] gate|up product passes up = gate + F, stride 2F.
+ *  kq_moe_combine: y[t, :] = sum_j probs[t * k + j] * d[(t * k + j), :], d [tokens * k, H], probs float32. */
+KQ_API int kq_swiglu(const void* gate, const void* up, long long in_row_stride, long long rows, int F, int dtype,
+                     void* out, void* stream);
+KQ_API int kq_moe_combine(const void* d, const float* probs, long long tokens, int k, int H, int dtype, void* y,
+                          void* stream);
 
 /* ---- gather_qmm without a workspace (no counterpart in the reference) ----
  * Same computation and arguments as kq_gather_qmm, minus the workspace: the

@@ -138,19 +138,19 @@ int kq_quantized_matmul(const void* x, int x_dtype, long long rows, int K, long 
                 w_row_bytes, c.bpb, c.name);
   if (!dtype_ok(x_dtype))
     return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.quantized_matmul] Only real floating x dtypes are supported.");
-  if (!transpose)
-    return fail(KQ_ERR_UNSUPPORTED, "[mlx_kquant.quantized_matmul] transpose=false ([K, N] weights) is not built yet.");
   const long long wpr = (long long)(w_row_bytes / c.bpb) * c.wpb;
-  if (wpr != K)
+  // transpose: w is [N, bytes(K)]; otherwise w is [K, bytes(N)] and its row count is x's last dim by construction
+  if (transpose ? wpr != K : wpr != N)
     return fail(KQ_ERR_INVALID_ARGUMENT,
                 "[mlx_kquant.quantized_matmul] x last dim (%d) does not match the expanded quantized matrix inner dim "
-                "(%lld) for codec '%s' with transpose=true.",
-                K, wpr, c.name);
+                "(%lld) for codec '%s' with transpose=%s.",
+                K, transpose ? wpr : (long long)K, c.name, transpose ? "true" : "false");
   if (rows < 0 || N < 0) return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.quantized_matmul] negative size.");
   if (rows == 0 || N == 0) return KQ_OK;
   if (!x || !w || !y) return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.quantized_matmul] null pointer.");
   const size_t xe = x_dtype == KQ_F32 ? 4 : 2;
-  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || ((size_t)x_row_stride * xe) % 16 != 0)
+  // the [N, K] kernels read activations sixteen bytes at a time; the [K, N] one reads them one by one
+  if (transpose && ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || ((size_t)x_row_stride * xe) % 16 != 0))
     return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.quantized_matmul] x rows must be 16-byte aligned.");
   if (rows > 16LL * 65535)
     return fail(KQ_ERR_UNSUPPORTED, "[mlx_kquant.quantized_matmul] more than 1048560 rows in one call.");
@@ -159,7 +159,11 @@ int kq_quantized_matmul(const void* x, int x_dtype, long long rows, int K, long 
   // (KQ_FORCE_SKINNY=1 keeps everything on the skinny kernel, an A/B lever).
   static const bool force_skinny = std::getenv("KQ_FORCE_SKINNY") != nullptr;
   cudaError_t e;
-  if (rows > 16 && !force_skinny) {
+  if (!transpose) {
+    if (rows > 0x7fffffffLL) return fail(KQ_ERR_UNSUPPORTED, "[mlx_kquant.quantized_matmul] too many rows.");
+    e = kq::launch_qvm(ci, x_dtype, x, x_row_stride, y, y_row_stride, static_cast<const uint8_t*>(w),
+                       (long long)w_row_bytes, (int)rows, N, K, static_cast<cudaStream_t>(stream));
+  } else if (rows > 16 && !force_skinny) {
     const size_t need = kq::gemm_workspace_bytes(x_dtype, rows, K);
     if (need > 0 && (workspace == nullptr || workspace_bytes < need))
       return fail(KQ_ERR_INVALID_ARGUMENT,
@@ -203,6 +207,35 @@ int kq_quantized_matmul(const void* x, int x_dtype, long long rows, int K, long 
     e = kq::launch_gemv(ci, eff_dtype, a, static_cast<cudaStream_t>(stream));
   }
   if (e != cudaSuccess) return cuda_fail("quantized_matmul", e);
+  return KQ_OK;
+}
+
+int kq_swiglu(const void* gate, const void* up, long long in_row_stride, long long rows, int F, int dtype, void* out,
+              void* stream) {
+  if (dtype != KQ_F16 && dtype != KQ_BF16)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.swiglu] activations must be float16 or bfloat16.");
+  if (rows < 0 || F < 0 || F % 8 != 0 || in_row_stride % 8 != 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.swiglu] F and the row stride must be multiples of 8.");
+  if (rows == 0 || F == 0) return KQ_OK;
+  if (!gate || !up || !out || ((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up) |
+                                reinterpret_cast<uintptr_t>(out)) & 15) != 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.swiglu] pointers must be non-null and 16-byte aligned.");
+  cudaError_t e = kq::launch_swiglu(dtype, gate, up, in_row_stride, rows, F, out, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("swiglu", e);
+  return KQ_OK;
+}
+
+int kq_moe_combine(const void* d, const float* probs, long long tokens, int k, int H, int dtype, void* y,
+                   void* stream) {
+  if (dtype != KQ_F16 && dtype != KQ_BF16)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_combine] activations must be float16 or bfloat16.");
+  if (tokens < 0 || k <= 0 || H < 0 || H % 8 != 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_combine] H must be a multiple of 8 and k positive.");
+  if (tokens == 0 || H == 0) return KQ_OK;
+  if (!d || !probs || !y || ((reinterpret_cast<uintptr_t>(d) | reinterpret_cast<uintptr_t>(y)) & 15) != 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_combine] pointers must be non-null and 16-byte aligned.");
+  cudaError_t e = kq::launch_moe_combine(dtype, d, probs, tokens, k, H, y, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("moe_combine", e);
   return KQ_OK;
 }
 

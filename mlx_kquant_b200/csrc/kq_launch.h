@@ -112,4 +112,14 @@ bool quantize_supported(int codec);
 void quantize_host(int codec, const void* w, int dtype, long long n_weights, long long K, const float* imatrix,
                    uint8_t* out, int threads);
 
+// Elementwise stages of a mixture-of-experts SwiGLU block (kq_moe.cu). dtype 1 f16 / 2 bf16.
+cudaError_t launch_swiglu(int dtype, const void* gate, const void* up, long long in_row_stride, long long rows, int F,
+                          void* out, cudaStream_t st);
+cudaError_t launch_moe_combine(int dtype, const void* d, const float* probs, long long tokens, int k, int H, void* y,
+                               cudaStream_t st);
+
+// transpose == 0 ([K, N] weights, rows quantized along N): streaming CUDA-core kernel (kq_qvm.cu).
+cudaError_t launch_qvm(int codec, int x_dtype, const void* x, long long x_row_stride, void* y, long long y_row_stride,
+                       const uint8_t* w, long long row_bytes, int M, int N, int K, cudaStream_t st);
+
 }  // namespace kq

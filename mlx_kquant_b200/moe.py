@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import torch
 
+from . import _lib
 from .ops import gather_qmm
 
 
@@ -24,9 +25,48 @@ def route_topk(router_logits: torch.Tensor, top_k: int) -> tuple[torch.Tensor, t
     return idx, p / p.sum(dim=-1, keepdim=True)
 
 
-def moe_glu(x, w_gate, w_up, w_down, kquant_type, expert_ids, expert_probs, *, sort_rows: bool = False):
+def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """silu(gate) * up in float32, rounded once to the inputs' dtype. gate / up: [rows, F] views that may be
+    the two halves of one [rows, 2F] product (same row stride)."""
+    rows, F = gate.shape
+    if (gate.is_cuda and gate.dtype in (torch.float16, torch.bfloat16) and F % 8 == 0 and gate.stride(1) == 1
+            and up.stride(1) == 1 and gate.stride(0) == up.stride(0) and gate.stride(0) % 8 == 0
+            and gate.data_ptr() % 16 == 0 and up.data_ptr() % 16 == 0):
+        out = torch.empty((rows, F), dtype=gate.dtype, device=gate.device)
+        with torch.cuda.device(gate.device):
+            _lib.check(_lib.lib().kq_swiglu(gate.data_ptr(), up.data_ptr(), gate.stride(0), rows, F,
+                                            _lib.KQ_F16 if gate.dtype == torch.float16 else _lib.KQ_BF16,
+                                            out.data_ptr(), torch.cuda.current_stream(gate.device).cuda_stream))
+        return out
+    return (torch.nn.functional.silu(gate.float()) * up.float()).to(gate.dtype)
+
+
+def combine(d: torch.Tensor, probs: torch.Tensor, k: int) -> torch.Tensor:
+    """y[t] = sum_j probs[t, j] * d[t k + j] in float32, rounded once. d [T k, H], probs [T, k] float32."""
+    rows, H = d.shape
+    T = rows // k
+    if d.is_cuda and d.dtype in (torch.float16, torch.bfloat16) and H % 8 == 0 and d.is_contiguous():
+        p = probs.reshape(T * k).float().contiguous()
+        y = torch.empty((T, H), dtype=d.dtype, device=d.device)
+        with torch.cuda.device(d.device):
+            _lib.check(_lib.lib().kq_moe_combine(d.data_ptr(), p.data_ptr(), T, k, H,
+                                                 _lib.KQ_F16 if d.dtype == torch.float16 else _lib.KQ_BF16,
+                                                 y.data_ptr(), torch.cuda.current_stream(d.device).cuda_stream))
+        return y
+    return (d.reshape(T, k, H).float() * probs.reshape(T, k, 1).float()).sum(dim=1).to(d.dtype)
+
+
+def fuse_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """[E, F, bytes] x2 -> [E, 2F, bytes]: rows are independent codec streams, so stacking the two matrices of
+    every expert along N is a valid weight matrix whose product is gate | up side by side. Done once, at load."""
+    return torch.cat([w_gate, w_up], dim=1).contiguous()
+
+
+def moe_glu(x, w_gate, w_up, w_down, kquant_type, expert_ids, expert_probs, *, sort_rows: bool = False,
+            w_gate_up=None):
     """x [T, H] (f16 / bf16), expert stacks [E, F, bytes(H)] x2 and [E, H, bytes(F)],
-    expert_ids / expert_probs [T, k]. Returns y [T, H] in x's dtype."""
+    expert_ids / expert_probs [T, k]. Returns y [T, H] in x's dtype. With w_gate_up = fuse_gate_up(w_gate,
+    w_up) the gate and up products are one gather_qmm call (w_gate / w_up may then be None)."""
     T, H = x.shape
     k = expert_ids.shape[1]
     rows = T * k
@@ -41,17 +81,24 @@ def moe_glu(x, w_gate, w_up, w_down, kquant_type, expert_ids, expert_probs, *, s
     else:
         order = None
     x3 = x.reshape(T, 1, H)
-    g = gather_qmm(x3, w_gate, None, kquant_type, lhs_indices=tok, rhs_indices=flat_e)
-    u = gather_qmm(x3, w_up, None, kquant_type, lhs_indices=tok, rhs_indices=flat_e)
-    h = (torch.nn.functional.silu(g.float()) * u.float()).to(x.dtype)          # [rows, 1, F]
-    d = gather_qmm(h, w_down, None, kquant_type, rhs_indices=flat_e, sorted_indices=order is not None)
-    d = d.reshape(rows, H).float()
+    if w_gate_up is not None:
+        F = w_gate_up.shape[1] // 2
+        gu = gather_qmm(x3, w_gate_up, None, kquant_type, lhs_indices=tok, rhs_indices=flat_e).reshape(rows, 2 * F)
+        h = swiglu(gu[:, :F], gu[:, F:])
+    else:
+        g = gather_qmm(x3, w_gate, None, kquant_type, lhs_indices=tok, rhs_indices=flat_e)
+        u = gather_qmm(x3, w_up, None, kquant_type, lhs_indices=tok, rhs_indices=flat_e)
+        F = g.shape[-1]
+        h = swiglu(g.reshape(rows, F), u.reshape(rows, F))
+    d = gather_qmm(h.reshape(rows, 1, F), w_down, None, kquant_type, rhs_indices=flat_e,
+                   sorted_indices=order is not None)
+    d = d.reshape(rows, H)
+    probs = expert_probs.reshape(rows)
     if order is not None:
         unsort = torch.empty_like(order)
         unsort[order] = torch.arange(rows, device=x.device)
         d = d[unsort]
-    y = (d.reshape(T, k, H) * expert_probs.reshape(T, k, 1).float()).sum(dim=1)
-    return y.to(x.dtype)
+    return combine(d, probs.reshape(T, k), k)
 
 
 def moe_glu_expert_parallel(x, w_gate, w_up, w_down, kquant_type, expert_ids, expert_probs, n_experts, group=None):
@@ -100,7 +147,8 @@ def moe_glu_expert_parallel(x, w_gate, w_up, w_down, kquant_type, expert_ids, ex
         xs = recv_x.reshape(n_recv, 1, H)
         g = gather_qmm(xs, w_gate, None, kquant_type, rhs_indices=es)
         u = gather_qmm(xs, w_up, None, kquant_type, rhs_indices=es)
-        h = (torch.nn.functional.silu(g.float()) * u.float()).to(x.dtype)
+        Fh = g.shape[-1]
+        h = swiglu(g.reshape(n_recv, Fh), u.reshape(n_recv, Fh)).reshape(n_recv, 1, Fh)
         out_rows = gather_qmm(h, w_down, None, kquant_type, rhs_indices=es).reshape(n_recv, H)
     else:
         out_rows = torch.empty((0, H), dtype=x.dtype, device=x.device)

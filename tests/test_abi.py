@@ -50,8 +50,10 @@ def test_abi_validation_needs_no_gpu():
     # K mismatch: 2 blocks of q4_k = 512 weights but K = 256
     rc = L.kq_quantized_matmul(None, 1, 1, 256, 256, None, 288, 4, b"q4_k", 1, None, 4, None, 0, None)
     assert rc == _lib.KQ_ERR_INVALID_ARGUMENT and b"does not match the expanded quantized matrix inner dim (512)" in L.kq_last_error()
+    # transpose = 0: w is [K, bytes(N)], so the row's expanded width (512) must equal N
     rc = L.kq_quantized_matmul(None, 1, 1, 512, 512, None, 288, 4, b"q4_k", 0, None, 4, None, 0, None)
-    assert rc == _lib.KQ_ERR_UNSUPPORTED
+    assert rc == _lib.KQ_ERR_INVALID_ARGUMENT and b"transpose=false" in L.kq_last_error()
+    assert L.kq_quantized_matmul(None, 1, 0, 300, 300, None, 288, 512, b"q4_k", 0, None, 512, None, 0, None) == 0
     # zero-sized problems succeed without touching memory
     assert L.kq_dequantize(None, 0, b"q4_k", 1, None, None) == 0
     assert L.kq_quantized_matmul(None, 1, 0, 512, 512, None, 288, 4, b"q4_k", 1, None, 4, None, 0, None) == 0

@@ -124,3 +124,32 @@ def test_linearity_property_full_size():
     err = (yc - (ya + yb)).norm() / (ya + yb).norm()
     assert err < 3e-3, float(err)
     assert torch.count_nonzero(kq.quantized_matmul(torch.zeros_like(x1), wd, None, "iq4_xs")) == 0
+
+
+@pytest.mark.parametrize("codec", CODECS)
+@pytest.mark.parametrize("M", [1, 3, 9])
+def test_transpose_false_all_codecs(oracle, codec, M):
+    """w [K, bytes(N)]: every row of w is a quantized vector of N weights (src/kquant_ops.cpp:140-155)."""
+    rng = np.random.default_rng(300 + M)
+    K, N = 300, 512   # K rows of w: any number; N = 2 superblocks or 16 blocks per row
+    wire = mint_wire(codec, rng.normal(0, 0.02, (K, N)).astype(np.float32))
+    for dt in ("f16", "bf16"):
+        x, store = x_to_torch(rng.normal(0, 1, (M, K)).astype(np.float32), dt)
+        y = kq.quantized_matmul(x, torch.from_numpy(wire).cuda(), None, codec, transpose=False)
+        assert tuple(y.shape) == (M, N)
+        Wd = oracle.dequantize(wire, codec, "f32").astype(np.float64)          # [K, N]
+        ref = to_f32(store, dt).astype(np.float64) @ Wd
+        check(y_to_f32(y), ref, dt)
+        # and the reference-order CPU result
+        assert rel_fro(y_to_f32(y), to_f32(oracle.qmm(store, wire, codec, dt, transpose=False), dt)) <= 2 * TOL
+
+
+def test_transpose_false_ragged_columns_and_f32(oracle):
+    rng = np.random.default_rng(310)
+    K, N = 64, 96     # q8_0: three 32-blocks per row, a partly filled 256-column chunk
+    wire = mint_wire("q8_0", rng.normal(0, 0.02, (K, N)).astype(np.float32))
+    x, store = x_to_torch(rng.normal(0, 1, (2, K)).astype(np.float32), "f32")
+    y = kq.quantized_matmul(x, torch.from_numpy(wire).cuda(), None, "q8_0", transpose=False)
+    assert y.dtype == torch.bfloat16 and tuple(y.shape) == (2, N)
+    xs = torch.from_numpy(store).to(torch.bfloat16).float().numpy().astype(np.float64)
+    check(y_to_f32(y), xs @ oracle.dequantize(wire, "q8_0", "f32").astype(np.float64), "bf16")

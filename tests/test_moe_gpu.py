@@ -45,6 +45,26 @@ def test_moe_glu_matches_oracle_composition(oracle, T):
     want = oracle_moe(oracle, x_bits, wg, wu, wd, ids.cpu().numpy(), probs.cpu().numpy(), codec)
     err = rel_fro(y.float().cpu().numpy(), want)
     assert err < 6e-3, err      # three chained bf16 roundings (gate/up, h, down) + the bf16 output
+    # gate | up as one stacked weight matrix: one gather_qmm instead of two, same numbers up to summation order
+    from mlx_kquant_b200.moe import fuse_gate_up
+    wgu = fuse_gate_up(torch.from_numpy(wg).cuda(), torch.from_numpy(wu).cuda())
+    y2 = moe_glu(x.cuda(), None, None, torch.from_numpy(wd).cuda(), codec, ids, probs, w_gate_up=wgu)
+    assert rel_fro(y2.float().cpu().numpy(), want) < 6e-3
+
+
+def test_swiglu_and_combine_kernels_match_torch():
+    from mlx_kquant_b200.moe import combine, swiglu
+    g = torch.Generator(device="cpu").manual_seed(5)
+    for dt in (torch.bfloat16, torch.float16):
+        gu = (torch.randn(37, 2 * 264, generator=g) * 3).to(dt).cuda()
+        got = swiglu(gu[:, :264], gu[:, 264:])
+        want = (torch.nn.functional.silu(gu[:, :264].float()) * gu[:, 264:].float()).to(dt)
+        assert torch.allclose(got.float(), want.float(), rtol=2 ** -7 if dt == torch.bfloat16 else 2 ** -10, atol=1e-6)
+        d = torch.randn(5 * 4, 520, generator=g).to(dt).cuda()
+        p = torch.rand(5, 4, generator=g).cuda()
+        got = combine(d, p, 4)
+        want = (d.reshape(5, 4, 520).float() * p.reshape(5, 4, 1)).sum(1).to(dt)
+        assert torch.allclose(got.float(), want.float(), rtol=2 ** -7 if dt == torch.bfloat16 else 2 ** -10, atol=1e-5)
 
 
 def test_topk_ties_go_to_the_lowest_index():
