@@ -295,7 +295,7 @@ def moe_ep_cell(dev, rank, world):
     import torch.distributed as dist
 
     from mlx_kquant_b200.dist import shard_bounds
-    from mlx_kquant_b200.moe import moe_glu_expert_parallel, route_topk
+    from mlx_kquant_b200.moe import fuse_gate_up, moe_glu_expert_parallel, route_topk
     from mlx_kquant_b200.synth import random_wire
 
     E, H, F, k, T = 128, 2048, 768, 8, 4096
@@ -306,7 +306,8 @@ def moe_ep_cell(dev, rank, world):
     g = torch.Generator(device="cpu").manual_seed(3000 + rank)
     x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(dev)
     ids, probs = route_topk(torch.randn(T, E, generator=g).to(dev), k)
-    fn = lambda: moe_glu_expert_parallel(x, wg, wu, wd, "q4_k", ids, probs, E)
+    wgu = fuse_gate_up(wg, wu)
+    fn = lambda: moe_glu_expert_parallel(x, None, None, wd, "q4_k", ids, probs, E, w_gate_up=wgu)
     for _ in range(2):
         fn()
     torch.cuda.synchronize()

@@ -108,7 +108,7 @@ __device__ __forceinline__ int x_slot(int n, int c) {
 // PERM (the q4_k fast path, fp16 only) stores each chunk x0..x7 as
 // x0 x2 x1 x3 x4 x6 x5 x7, the order in which the nibble unpacking yields
 // weights, and also leaves, per row and 32-activation group, the group sum
-// split into an fp16 head and tail (sum = hi + lo to 2^-22) in `xsum`
+// divided by 64 and split into an fp16 head and tail (sum / 64 = hi + lo to 2^-22) in `xsum`
 // laid out [row][256-chunk][hi0..hi7 lo0..lo7].
 template <typename XT, int NT, bool PERM>
 __device__ __forceinline__ void stage_x(uint4* xs, __half* xsum, const GemvArgs& a, const int* s_xrow, int m, int k0,
@@ -136,6 +136,9 @@ __device__ __forceinline__ void stage_x(uint4* xs, __half* xsum, const GemvArgs&
       sum += __shfl_xor_sync(0xffffffffu, sum, 1);  // the four chunks of one 32-group sit in one aligned quad
       sum += __shfl_xor_sync(0xffffffffu, sum, 2);
       if ((c & 3) == 0) {
+        // kept as sum / 64: thirty-two fp16 values can add up to 2^21, beyond fp16's range, and the
+        // consumer multiplies the factor back in fp32
+        sum *= 0.015625f;
         const __half hi = __float2half_rn(sum);
         const __half lo = __float2half_rn(sum - __half2float(hi));
         __half* dst = xsum + (n * (kStageK / 256) + (c >> 5)) * 16 + ((c >> 2) & 7);
@@ -347,10 +350,11 @@ __device__ __forceinline__ void q4k_compute(const Q4kLoad& l, const uint4* xs, c
   for (int nt = 0; nt < NT; nt++) {
     const uint32_t* xq = reinterpret_cast<const uint32_t*>(xsum + ((nt * 8 + g) * (kStageK / 256) + sbl) * 16);
     mma_f16(accm[nt], ra.mn, rb.mn, ra.mn, rb.mn, xq[t], xq[4 + t]);
-    fin[nt][0] += ra.d * accq[nt][0] - ra.dmin * accm[nt][0];
-    fin[nt][1] += ra.d * accq[nt][1] - ra.dmin * accm[nt][1];
-    fin[nt][2] += rb.d * accq[nt][2] - rb.dmin * accm[nt][2];
-    fin[nt][3] += rb.d * accq[nt][3] - rb.dmin * accm[nt][3];
+    // accm holds sum_s mn_s * xsum_s / 64 (the group sums are staged divided by 64)
+    fin[nt][0] += ra.d * accq[nt][0] - ra.dmin * 64.f * accm[nt][0];
+    fin[nt][1] += ra.d * accq[nt][1] - ra.dmin * 64.f * accm[nt][1];
+    fin[nt][2] += rb.d * accq[nt][2] - rb.dmin * 64.f * accm[nt][2];
+    fin[nt][3] += rb.d * accq[nt][3] - rb.dmin * 64.f * accm[nt][3];
   }
 }
 

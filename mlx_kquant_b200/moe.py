@@ -101,7 +101,8 @@ def moe_glu(x, w_gate, w_up, w_down, kquant_type, expert_ids, expert_probs, *, s
     return combine(d, probs.reshape(T, k), k)
 
 
-def moe_glu_expert_parallel(x, w_gate, w_up, w_down, kquant_type, expert_ids, expert_probs, n_experts, group=None):
+def moe_glu_expert_parallel(x, w_gate, w_up, w_down, kquant_type, expert_ids, expert_probs, n_experts, group=None,
+                            *, w_gate_up=None):
     """The same block with the experts partitioned over the ranks of `group`.
 
     Every rank holds its own tokens x [T, H] and routing, and only the expert
@@ -145,10 +146,15 @@ def moe_glu_expert_parallel(x, w_gate, w_up, w_down, kquant_type, expert_ids, ex
     if n_recv > 0:
         es = recv_e.to(torch.int64) - lo
         xs = recv_x.reshape(n_recv, 1, H)
-        g = gather_qmm(xs, w_gate, None, kquant_type, rhs_indices=es)
-        u = gather_qmm(xs, w_up, None, kquant_type, rhs_indices=es)
-        Fh = g.shape[-1]
-        h = swiglu(g.reshape(n_recv, Fh), u.reshape(n_recv, Fh)).reshape(n_recv, 1, Fh)
+        if w_gate_up is not None:  # the local experts' gate | up stacked along N (fuse_gate_up)
+            Fh = w_gate_up.shape[1] // 2
+            gu = gather_qmm(xs, w_gate_up, None, kquant_type, rhs_indices=es).reshape(n_recv, 2 * Fh)
+            h = swiglu(gu[:, :Fh], gu[:, Fh:]).reshape(n_recv, 1, Fh)
+        else:
+            g = gather_qmm(xs, w_gate, None, kquant_type, rhs_indices=es)
+            u = gather_qmm(xs, w_up, None, kquant_type, rhs_indices=es)
+            Fh = g.shape[-1]
+            h = swiglu(g.reshape(n_recv, Fh), u.reshape(n_recv, Fh)).reshape(n_recv, 1, Fh)
         out_rows = gather_qmm(h, w_down, None, kquant_type, rhs_indices=es).reshape(n_recv, H)
     else:
         out_rows = torch.empty((0, H), dtype=x.dtype, device=x.device)

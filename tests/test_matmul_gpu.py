@@ -153,3 +153,19 @@ def test_transpose_false_ragged_columns_and_f32(oracle):
     assert y.dtype == torch.bfloat16 and tuple(y.shape) == (2, N)
     xs = torch.from_numpy(store).to(torch.bfloat16).float().numpy().astype(np.float64)
     check(y_to_f32(y), xs @ oracle.dequantize(wire, "q8_0", "f32").astype(np.float64), "bf16")
+
+
+def test_large_activations_do_not_overflow_group_sums(oracle):
+    """fp16 rows whose 32-group sums exceed fp16's range (2-16 rows take the kernel that stages group sums
+    in fp16): the result must stay finite and accurate."""
+    rng = np.random.default_rng(400)
+    N, K, M = 64, 1024, 4
+    wire = mint_wire("q4_k", rng.normal(0, 0.02, (N, K)).astype(np.float32))
+    xf = np.abs(rng.normal(0, 1, (M, K))).astype(np.float32) * 6000.0 + 3000.0   # all positive: sums ~ 2.5e5
+    x, store = x_to_torch(xf, "f16")
+    y = kq.quantized_matmul(x, torch.from_numpy(wire).cuda(), None, "q4_k")
+    ref = fp64_ref(oracle, store, "f16", wire, "q4_k")
+    got = y_to_f32(y)
+    finite = np.abs(ref) < 60000          # outputs beyond fp16's range saturate to inf by definition
+    assert np.isfinite(got[finite]).all()
+    assert np.abs(got[finite] - ref[finite]).max() <= 2e-3 * np.abs(ref[finite]).max()
