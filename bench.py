@@ -348,54 +348,75 @@ def run_b200(args):
     g = torch.Generator(device="cpu").manual_seed(2000 + M)
     x_host = torch.randn(M, K_COLS, generator=g).to(torch.float16).pin_memory()
     x_dev = x_host.to(dev)
-    y_dev = torch.empty(layers, M, N_ROWS, dtype=torch.float16, device=dev)
-    y_all = torch.empty(world, layers, M, N_ROWS, dtype=torch.float16, device=dev) if world > 1 else None
+    # two output buffers: at N > 1 the all-gather of step i overlaps the matmuls of step i + 1
+    y_devs = [torch.empty(layers, M, N_ROWS, dtype=torch.float16, device=dev) for _ in range(2)]
+    y_alls = [torch.empty(world, layers, M, N_ROWS, dtype=torch.float16, device=dev) for _ in range(2)] if world > 1 else None
+    y_dev = y_devs[0]
     y_host = torch.empty(layers, M, N_ROWS, dtype=torch.float16).pin_memory()
 
     from mlx_kquant_b200 import _lib
     L = _lib.lib()
     stream = torch.cuda.Stream(dev)
 
-    def launch_all(s):
+    def launch_all(s, yb):
         for i in range(layers):
             rc = L.kq_quantized_matmul(x_dev.data_ptr(), _lib.KQ_F16, M, K_COLS, K_COLS, W[i].data_ptr(), ROW_BYTES,
-                                       N_ROWS, CODEC.encode(), 1, y_dev[i].data_ptr(), N_ROWS, None, 0, s.cuda_stream)
+                                       N_ROWS, CODEC.encode(), 1, yb[i].data_ptr(), N_ROWS, None, 0, s.cuda_stream)
             _lib.check(rc)
 
     # ---- correctness guard: the captured path equals the public op
     with torch.cuda.stream(stream):
-        launch_all(stream)
+        launch_all(stream, y_dev)
         ref0 = kq.quantized_matmul(x_dev, W[0], None, CODEC)
     stream.synchronize()
     assert torch.equal(ref0, y_dev[0]), "C-ABI launch and public op disagree"
 
-    # ---- device-resident arm: one CUDA graph of `layers` launches
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.stream(stream):
-        with torch.cuda.graph(graph, stream=stream):
-            launch_all(stream)
+    # ---- device-resident arm: one CUDA graph of `layers` launches (one graph per output buffer)
+    def capture(yb, with_copies):
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(gr, stream=stream):
+                if with_copies:
+                    x_dev.copy_(x_host, non_blocking=True)
+                launch_all(stream, yb)
+                if with_copies:
+                    y_host.copy_(yb, non_blocking=True)
+        return gr
+
+    graphs = [capture(yb, False) for yb in y_devs]
     # ---- end-to-end arm: H2D of x, the launches, D2H of y, captured as one graph of the public path
-    graph_e2e = torch.cuda.CUDAGraph()
-    with torch.cuda.stream(stream):
-        with torch.cuda.graph(graph_e2e, stream=stream):
-            x_dev.copy_(x_host, non_blocking=True)
-            launch_all(stream)
-            y_host.copy_(y_dev, non_blocking=True)
+    graphs_e2e = [capture(yb, True) for yb in y_devs]
+
+    # At N > 1 every step ends with the all-gather of its output shards. It is issued asynchronously and
+    # the buffer it reads is not written again before it has finished, so it overlaps the next step.
+    state = {"i": 0, "works": [None, None]}
+
+    def run_step(gs):
+        b = state["i"] & 1
+        state["i"] += 1
+        if world > 1 and state["works"][b] is not None:
+            state["works"][b].wait()      # stream-side wait: buffer b is free again
+        gs[b].replay()
+        if world > 1:
+            state["works"][b] = dist.all_gather_into_tensor(y_alls[b], y_devs[b], async_op=True)
+
+    def drain():
+        for b in range(2):
+            if state["works"][b] is not None:
+                state["works"][b].wait()
+                state["works"][b] = None
 
     def step_device():
-        graph.replay()
-        if world > 1:
-            dist.all_gather_into_tensor(y_all, y_dev)
+        run_step(graphs)
 
     def step_e2e():
-        graph_e2e.replay()
-        if world > 1:
-            dist.all_gather_into_tensor(y_all, y_dev)
+        run_step(graphs_e2e)
 
     def timed(fn, steps, warmup):
         with torch.cuda.stream(stream):
             for _ in range(warmup):
                 fn()
+            drain()
             stream.synchronize()
             if world > 1:
                 dist.barrier()
@@ -404,6 +425,7 @@ def run_b200(args):
             e0.record(stream)
             for _ in range(steps):
                 fn()
+            drain()                      # the timed region ends when the last all-gather has landed
             e1.record(stream)
             stream.synchronize()
             torch.cuda.synchronize()
@@ -456,7 +478,7 @@ def run_b200(args):
             "config": {"workload": "c1_q4k_decode_gemv", "codec": CODEC, "N": N_ROWS, "K": K_COLS, "M": M,
                        "layers": layers, "x_dtype": "f16", "accumulate": "f32",
                        "cold_cache": f"{layers} distinct weight matrices per step = {layers * MATRIX_BYTES / 1e6:.0f} MB > 126 MB L2",
-                       "parallelism": "single GPU" if world == 1 else f"column shard x{world} + NCCL all-gather of outputs"},
+                       "parallelism": "single GPU" if world == 1 else f"column shard x{world} + NCCL all-gather of outputs, overlapped with the next step"},
             "e2e": {"value": e2e, "unit": "GB/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
             "gpu_launches": args.steps * layers,
