@@ -215,7 +215,7 @@ cudaError_t launch_gather(int codec, int x_dtype, const void* x, int M, int K, c
     return launch_gemm_grouped(codec, x_dtype, x, M, K, w, expert_stride, row_bytes, N, lhs, order,
                                n_entries * (long long)M, y, reinterpret_cast<__half*>(ws + L.xh),
                                reinterpret_cast<float*>(ws + L.row_scale), reinterpret_cast<int*>(ws + L.yrow), tiles,
-                               n_tasks, (int)L.max_tiles, st);
+                               n_tasks, (int)L.max_tiles, offsets + n_experts, st);
   }
 
   GemvTask* tasks = reinterpret_cast<GemvTask*>(ws + L.tasks);

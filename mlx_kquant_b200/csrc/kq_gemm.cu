@@ -533,9 +533,11 @@ template <typename XT>
 __global__ void __launch_bounds__(256)
 convert_x_kernel(const XT* __restrict__ x, long long x_row_stride, int K, __half* __restrict__ xh,
                  float* __restrict__ row_scale, const int* __restrict__ order, const uint32_t* __restrict__ lhs, int M,
-                 int* __restrict__ yrow) {
+                 int* __restrict__ yrow, const int* __restrict__ n_valid) {
   const long long row = blockIdx.x;
   long long src_row = row;
+  // gather mode: entries whose expert index is out of range were never placed in `order`; its tail is unset
+  if (n_valid != nullptr && row >= (long long)(*n_valid) * M) return;
   if (order != nullptr) {
     const int entry = order[row / M], i = (int)(row % M);
     src_row = (long long)lhs[entry] * M + i;
@@ -584,13 +586,13 @@ cudaError_t launch_convert_rows(int x_dtype, const void* x, long long x_row_stri
   __half* o = static_cast<__half*>(xh);
   if (x_dtype == F16)
     convert_x_kernel<__half><<<(unsigned)rows, 256, 0, st>>>(static_cast<const __half*>(x), x_row_stride, K, o,
-                                                             row_scale, nullptr, lhs, M, nullptr);
+                                                             row_scale, nullptr, lhs, M, nullptr, nullptr);
   else if (x_dtype == BF16)
     convert_x_kernel<__nv_bfloat16><<<(unsigned)rows, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), x_row_stride,
-                                                                    K, o, row_scale, nullptr, lhs, M, nullptr);
+                                                                    K, o, row_scale, nullptr, lhs, M, nullptr, nullptr);
   else
     convert_x_kernel<float><<<(unsigned)rows, 256, 0, st>>>(static_cast<const float*>(x), x_row_stride, K, o, row_scale,
-                                                            nullptr, lhs, M, nullptr);
+                                                            nullptr, lhs, M, nullptr, nullptr);
   return cudaGetLastError();
 }
 
@@ -746,10 +748,10 @@ cudaError_t launch_gemm(int codec, int x_dtype, const void* x, long long x_row_s
     float* rs = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + (((size_t)M * K * 2 + 255) & ~(size_t)255));
     if (x_dtype == BF16)
       convert_x_kernel<__nv_bfloat16><<<M, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), x_row_stride, K, xh, rs,
-                                                         nullptr, nullptr, 1, nullptr);
+                                                         nullptr, nullptr, 1, nullptr, nullptr);
     else
       convert_x_kernel<float><<<M, 256, 0, st>>>(static_cast<const float*>(x), x_row_stride, K, xh, rs, nullptr,
-                                                 nullptr, 1, nullptr);
+                                                 nullptr, 1, nullptr, nullptr);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     a.x = xh;
@@ -788,17 +790,17 @@ cudaError_t launch_gemm_grouped(int codec, int x_dtype, const void* x, int M, in
                                 long long expert_stride, long long row_bytes, int N, const uint32_t* lhs,
                                 const int* order, long long rows_total, void* y, __half* xh, float* row_scale,
                                 int* yrow, const void* tiles, const int* n_tiles_dev, int max_tiles,
-                                cudaStream_t st) {
+                                const int* n_valid_dev, cudaStream_t st) {
   if (rows_total <= 0 || N <= 0 || K <= 0) return cudaSuccess;
   if (x_dtype == F16)
     convert_x_kernel<__half><<<(unsigned)rows_total, 256, 0, st>>>(static_cast<const __half*>(x), K, K, xh, row_scale,
-                                                                    order, lhs, M, yrow);
+                                                                    order, lhs, M, yrow, n_valid_dev);
   else if (x_dtype == BF16)
     convert_x_kernel<__nv_bfloat16><<<(unsigned)rows_total, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), K, K,
-                                                                           xh, row_scale, order, lhs, M, yrow);
+                                                                           xh, row_scale, order, lhs, M, yrow, n_valid_dev);
   else
     convert_x_kernel<float><<<(unsigned)rows_total, 256, 0, st>>>(static_cast<const float*>(x), K, K, xh, row_scale,
-                                                                   order, lhs, M, yrow);
+                                                                   order, lhs, M, yrow, n_valid_dev);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   GemmArgs a;

@@ -702,7 +702,7 @@ constexpr int kDpMaxK = 16384;
 static inline int dp_dyn_smem(int K, int D) { return kDpWarps * D * kDpSlot + 2 * K + 2 * (K / 32) * 4; }
 
 template <typename XT>
-__global__ void __launch_bounds__(kDpThreads, 2) gemv_q4k_m1_dp4a_kernel(const GemvArgs a, const int D) {
+__global__ void __launch_bounds__(kDpThreads, 2) gemv_q4k_m1_dp4a_kernel(const GemvArgs a, const int D, const int rpc) {
   using OT = typename std::conditional<std::is_same<XT, __half>::value, __half, __nv_bfloat16>::type;
   __shared__ float red[kDpWarps][kDpRows];
   extern __shared__ __align__(16) uint8_t dyn_smem[];
@@ -712,7 +712,9 @@ __global__ void __launch_bounds__(kDpThreads, 2) gemv_q4k_m1_dp4a_kernel(const G
   uint32_t* XL = XH + a.K / 4;                                                    // low bytes
   float* SG = reinterpret_cast<float*>(XL + a.K / 4);                             // scale of each 32-group
   float* XS = SG + a.K / 32;                                                      // sum of each 32-group
-  const int row0 = blockIdx.x * kDpRows;
+  // rpc <= 32 rows per CTA: a grid that covers all SMs when N / 32 would leave some idle
+  const int row0 = blockIdx.x * rpc;
+  const int row_end = min(row0 + rpc, a.N);
   const int per = (nchunks + kDpWarps - 1) / kDpWarps;
   const int ch0 = min(warp * per, nchunks), ch1 = min(ch0 + per, nchunks);
 
@@ -722,7 +724,7 @@ __global__ void __launch_bounds__(kDpThreads, 2) gemv_q4k_m1_dp4a_kernel(const G
 #pragma unroll
   for (int i = 0; i < 9; i++) {
     const int j = lane + 32 * i;  // 288 16-byte pieces per superblock, contiguous in the slot
-    src[i] = a.w + (long long)min(row0 + j / 9, a.N - 1) * a.row_bytes + (long long)ch0 * 144 + (j % 9) * 16;
+    src[i] = a.w + (long long)min(row0 + j / 9, row_end - 1) * a.row_bytes + (long long)ch0 * 144 + (j % 9) * 16;
   }
   int issued = ch0;
   auto issue = [&](uint8_t* slot) {
@@ -856,7 +858,7 @@ __global__ void __launch_bounds__(kDpThreads, 2) gemv_q4k_m1_dp4a_kernel(const G
   }
   red[warp][lane] = y;
   __syncthreads();
-  if (warp == 0 && row0 + lane < a.N) {
+  if (warp == 0 && row0 + lane < row_end) {
     float sum = 0.f;
 #pragma unroll
     for (int w = 0; w < kDpWarps; w++) sum += red[w][lane];
@@ -1497,7 +1499,10 @@ static cudaError_t launch_m1_dp4a(const GemvArgs& a, cudaStream_t st) {
     attr_set[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((a.N + kDpRows - 1) / kDpRows, 1, 1);
+  // fewer than one 32-row CTA per SM: spread the rows over all 148 SMs instead (28 rows each for N = 4096)
+  int rpc = kDpRows;
+  if ((a.N + kDpRows - 1) / kDpRows < 148 && a.N >= 148 * 16) rpc = (a.N + 147) / 148;
+  cfg.gridDim = dim3((a.N + rpc - 1) / rpc, 1, 1);
   cfg.blockDim = dim3(kDpThreads);
   cfg.dynamicSmemBytes = dp_dyn_smem(a.K, D);
   cfg.stream = st;
@@ -1507,7 +1512,7 @@ static cudaError_t launch_m1_dp4a(const GemvArgs& a, cudaStream_t st) {
   cfg.attrs = attr;
   static const bool no_pdl = std::getenv("KQ_NO_PDL") != nullptr;  // A/B lever
   cfg.numAttrs = no_pdl ? 0 : 1;
-  return cudaLaunchKernelEx(&cfg, gemv_q4k_m1_dp4a_kernel<XT>, a, D);
+  return cudaLaunchKernelEx(&cfg, gemv_q4k_m1_dp4a_kernel<XT>, a, D, rpc);
 }
 
 template <int C, int NAT>

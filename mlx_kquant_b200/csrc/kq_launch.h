@@ -70,7 +70,8 @@ constexpr int kGroupedTileRows = 256;
 cudaError_t launch_gemm_grouped(int codec, int x_dtype, const void* x, int M, int K, const uint8_t* w,
                                 long long expert_stride, long long row_bytes, int N, const uint32_t* lhs,
                                 const int* order, long long rows_total, void* y, __half* xh, float* row_scale,
-                                int* yrow, const void* tiles, const int* n_tiles_dev, int max_tiles, cudaStream_t st);
+                                int* yrow, const void* tiles, const int* n_tiles_dev, int max_tiles,
+                                const int* n_valid_dev, cudaStream_t st);
 // Flags raised by kernels that gave up on a bounded wait (0 = none); synchronises the device.
 cudaError_t read_device_error(int* out, bool clear);
 // Exact fp16 copy of `rows` activation rows (x_dtype 0 f32 / 1 f16 / 2 bf16) with a per-row power-of-two

@@ -116,3 +116,24 @@ def test_many_rows_regression():
     e0 = (y[:half, 0].float() - want0).norm() / want0.norm()
     e1 = (y[half:, 0].float() - want1).norm() / want1.norm()
     assert float(e0) < TOL and float(e1) < TOL
+
+
+@pytest.mark.parametrize("B", [12, 640])
+def test_out_of_range_expert_ids_are_skipped(oracle, B):
+    # Entries whose expert index is >= the expert count belong to no group: the other entries' rows are
+    # computed as usual (both regimes: task lists at B = 12, the grouped tile kernel at B = 640).
+    codec, E, N, K = "q4_k", 4, 64, 512
+    wire = make_experts(codec, E, N, K, seed=71)
+    wd = torch.from_numpy(wire).cuda()
+    x, store = x_to_torch(np.random.default_rng(72).normal(0, 1, (B, 1, K)).astype(np.float32), "bf16")
+    rhs = np.random.default_rng(73).integers(0, E, B).astype(np.int64)
+    bad = np.arange(B) % 5 == 2
+    rhs_bad = rhs.copy()
+    rhs_bad[bad] = E + 3
+    y = kq.gather_qmm(x, wd, None, codec, rhs_indices=torch.from_numpy(rhs_bad))
+    good = kq.gather_qmm(x, wd, None, codec, rhs_indices=torch.from_numpy(rhs))
+    torch.cuda.synchronize()
+    keep = torch.from_numpy(~bad).cuda()
+    ref = fp64_ref(oracle, store, "bf16", wire, codec, np.arange(B), rhs)
+    assert rel_fro(y_to_f32(good), ref) <= TOL
+    assert rel_fro(y_to_f32(y[keep]), ref[~bad]) <= TOL
