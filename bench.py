@@ -322,8 +322,31 @@ def moe_ep_cell(dev, rank, world):
     t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
-    return {f"moe_glu_q4k_ep{world}_T4096_per_rank": {"tokens_per_s": world * T / (ms * 1e-3), "ms": ms,
-                                                       "experts_per_rank": hi - lo}}
+    out = {f"moe_glu_q4k_ep{world}_T4096_per_rank": {"tokens_per_s": world * T / (ms * 1e-3), "ms": ms,
+                                                      "experts_per_rank": hi - lo}}
+    # fixed-shape form (all-gather, local experts as a CUDA graph, reduce-scatter): no host read inside a step
+    from mlx_kquant_b200.moe import GatheredExpertParallel
+
+    for Tg in (64, 4096):
+        ep = GatheredExpertParallel(Tg, H, k, E, wgu, wd, "q4_k")
+        xg, idg, prg = x[:Tg].contiguous(), ids[:Tg].contiguous(), probs[:Tg].contiguous()
+        ep.capture()
+        for _ in range(3):
+            ep(xg, idg, prg)
+        torch.cuda.synchronize()
+        dist.barrier()
+        reps = 20 if Tg <= 64 else 5
+        e0.record()
+        for _ in range(reps):
+            ep(xg, idg, prg)
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        out[f"moe_glu_q4k_ep{world}_gathered_T{Tg}_per_rank"] = {"tokens_per_s": world * Tg / (ms * 1e-3), "ms": ms}
+        del ep
+    return out
 
 
 def run_b200(args):

@@ -139,11 +139,20 @@ KQ_API int kq_gather_qmm(const void* x, int x_dtype, long long x_batch, int M, i
  * or KQ_BF16, fp32 arithmetic, one rounding.
  *  kq_swiglu:      out[r, c] = silu(gate[r * in_row_stride + c]) * up[r * in_row_stride + c], c < F; out is
  *                  [rows, F] dense. A fused [rows, 2F] gate|up product passes up = gate + F, stride 2F.
- *  kq_moe_combine: y[t, :] = sum_j probs[t * k + j] * d[(t * k + j), :], d [tokens * k, H], probs float32. */
+ *  kq_moe_combine: y[t, :] = sum_j probs[t * k + j] * d[(t * k + j), :], d [tokens * k, H], probs float32.
+ *                  A row whose weight is exactly 0 is not read.
+ * The two variants below serve a rank that holds only some of the experts (every rank sees every routed row,
+ * and rows of other ranks' experts carry an out-of-range index, which kq_gather_qmm leaves unwritten):
+ *  kq_swiglu_routed:   kq_swiglu that skips rows with row_expert[r] >= n_experts (uint32 compare).
+ *  kq_moe_combine_f32: kq_moe_combine with a float32 y, the partial sum a reduce-scatter then completes. */
 KQ_API int kq_swiglu(const void* gate, const void* up, long long in_row_stride, long long rows, int F, int dtype,
                      void* out, void* stream);
 KQ_API int kq_moe_combine(const void* d, const float* probs, long long tokens, int k, int H, int dtype, void* y,
                           void* stream);
+KQ_API int kq_swiglu_routed(const void* gate, const void* up, long long in_row_stride, long long rows, int F, int dtype,
+                            void* out, const uint32_t* row_expert, int n_experts, void* stream);
+KQ_API int kq_moe_combine_f32(const void* d, const float* probs, long long tokens, int k, int H, int dtype, float* y,
+                              void* stream);
 
 /* ---- gather_qmm without a workspace (no counterpart in the reference) ----
  * Same computation and arguments as kq_gather_qmm, minus the workspace: the

@@ -210,8 +210,8 @@ int kq_quantized_matmul(const void* x, int x_dtype, long long rows, int K, long 
   return KQ_OK;
 }
 
-int kq_swiglu(const void* gate, const void* up, long long in_row_stride, long long rows, int F, int dtype, void* out,
-              void* stream) {
+static int swiglu_impl(const void* gate, const void* up, long long in_row_stride, long long rows, int F, int dtype,
+                       void* out, const uint32_t* row_expert, int n_experts, void* stream) {
   if (dtype != KQ_F16 && dtype != KQ_BF16)
     return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.swiglu] activations must be float16 or bfloat16.");
   if (rows < 0 || F < 0 || F % 8 != 0 || in_row_stride % 8 != 0)
@@ -220,13 +220,26 @@ int kq_swiglu(const void* gate, const void* up, long long in_row_stride, long lo
   if (!gate || !up || !out || ((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up) |
                                 reinterpret_cast<uintptr_t>(out)) & 15) != 0)
     return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.swiglu] pointers must be non-null and 16-byte aligned.");
-  cudaError_t e = kq::launch_swiglu(dtype, gate, up, in_row_stride, rows, F, out, static_cast<cudaStream_t>(stream));
+  cudaError_t e = kq::launch_swiglu(dtype, gate, up, in_row_stride, rows, F, out, row_expert,
+                                    (uint32_t)(n_experts < 0 ? 0 : n_experts), static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail("swiglu", e);
   return KQ_OK;
 }
 
-int kq_moe_combine(const void* d, const float* probs, long long tokens, int k, int H, int dtype, void* y,
-                   void* stream) {
+int kq_swiglu(const void* gate, const void* up, long long in_row_stride, long long rows, int F, int dtype, void* out,
+              void* stream) {
+  return swiglu_impl(gate, up, in_row_stride, rows, F, dtype, out, nullptr, 0, stream);
+}
+
+int kq_swiglu_routed(const void* gate, const void* up, long long in_row_stride, long long rows, int F, int dtype,
+                     void* out, const uint32_t* row_expert, int n_experts, void* stream) {
+  if (!row_expert && rows > 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.swiglu] row_expert must be non-null.");
+  return swiglu_impl(gate, up, in_row_stride, rows, F, dtype, out, row_expert, n_experts, stream);
+}
+
+static int combine_impl(const void* d, const float* probs, long long tokens, int k, int H, int dtype, void* y,
+                        bool y_f32, void* stream) {
   if (dtype != KQ_F16 && dtype != KQ_BF16)
     return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_combine] activations must be float16 or bfloat16.");
   if (tokens < 0 || k <= 0 || H < 0 || H % 8 != 0)
@@ -234,9 +247,19 @@ int kq_moe_combine(const void* d, const float* probs, long long tokens, int k, i
   if (tokens == 0 || H == 0) return KQ_OK;
   if (!d || !probs || !y || ((reinterpret_cast<uintptr_t>(d) | reinterpret_cast<uintptr_t>(y)) & 15) != 0)
     return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_combine] pointers must be non-null and 16-byte aligned.");
-  cudaError_t e = kq::launch_moe_combine(dtype, d, probs, tokens, k, H, y, static_cast<cudaStream_t>(stream));
+  cudaError_t e = kq::launch_moe_combine(dtype, d, probs, tokens, k, H, y, y_f32, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail("moe_combine", e);
   return KQ_OK;
+}
+
+int kq_moe_combine(const void* d, const float* probs, long long tokens, int k, int H, int dtype, void* y,
+                   void* stream) {
+  return combine_impl(d, probs, tokens, k, H, dtype, y, false, stream);
+}
+
+int kq_moe_combine_f32(const void* d, const float* probs, long long tokens, int k, int H, int dtype, float* y,
+                       void* stream) {
+  return combine_impl(d, probs, tokens, k, H, dtype, y, true, stream);
 }
 
 int kq_device_error_flags(int* flags, int clear) {

@@ -114,10 +114,11 @@ void quantize_host(int codec, const void* w, int dtype, long long n_weights, lon
                    uint8_t* out, int threads);
 
 // Elementwise stages of a mixture-of-experts SwiGLU block (kq_moe.cu). dtype 1 f16 / 2 bf16.
+// row_expert != nullptr: rows with row_expert[r] >= n_experts are skipped. y_f32: y is float32.
 cudaError_t launch_swiglu(int dtype, const void* gate, const void* up, long long in_row_stride, long long rows, int F,
-                          void* out, cudaStream_t st);
+                          void* out, const uint32_t* row_expert, uint32_t n_experts, cudaStream_t st);
 cudaError_t launch_moe_combine(int dtype, const void* d, const float* probs, long long tokens, int k, int H, void* y,
-                               cudaStream_t st);
+                               bool y_f32, cudaStream_t st);
 
 // transpose == 0 ([K, N] weights, rows quantized along N): streaming CUDA-core kernel (kq_qvm.cu).
 cudaError_t launch_qvm(int codec, int x_dtype, const void* x, long long x_row_stride, void* y, long long y_row_stride,

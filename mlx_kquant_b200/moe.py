@@ -25,10 +25,23 @@ def route_topk(router_logits: torch.Tensor, top_k: int) -> tuple[torch.Tensor, t
     return idx, p / p.sum(dim=-1, keepdim=True)
 
 
-def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+def swiglu(gate: torch.Tensor, up: torch.Tensor, row_expert: torch.Tensor | None = None,
+           n_experts: int = 0) -> torch.Tensor:
     """silu(gate) * up in float32, rounded once to the inputs' dtype. gate / up: [rows, F] views that may be
-    the two halves of one [rows, 2F] product (same row stride)."""
+    the two halves of one [rows, 2F] product (same row stride). With `row_expert` (int32 [rows]), rows whose
+    expert index is outside [0, n_experts) are skipped and their output rows stay unwritten."""
     rows, F = gate.shape
+    if row_expert is not None:
+        if not (gate.is_cuda and gate.dtype in (torch.float16, torch.bfloat16) and F % 8 == 0):
+            raise ValueError("[mlx_kquant.swiglu] the routed form needs float16 / bfloat16 CUDA rows with F % 8 == 0.")
+        re32 = row_expert.reshape(rows).to(torch.int32).contiguous()
+        out = torch.empty((rows, F), dtype=gate.dtype, device=gate.device)
+        with torch.cuda.device(gate.device):
+            _lib.check(_lib.lib().kq_swiglu_routed(gate.data_ptr(), up.data_ptr(), gate.stride(0), rows, F,
+                                                   _lib.KQ_F16 if gate.dtype == torch.float16 else _lib.KQ_BF16,
+                                                   out.data_ptr(), re32.data_ptr(), n_experts,
+                                                   torch.cuda.current_stream(gate.device).cuda_stream))
+        return out
     if (gate.is_cuda and gate.dtype in (torch.float16, torch.bfloat16) and F % 8 == 0 and gate.stride(1) == 1
             and up.stride(1) == 1 and gate.stride(0) == up.stride(0) and gate.stride(0) % 8 == 0
             and gate.data_ptr() % 16 == 0 and up.data_ptr() % 16 == 0):
@@ -39,6 +52,22 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
                                             out.data_ptr(), torch.cuda.current_stream(gate.device).cuda_stream))
         return out
     return (torch.nn.functional.silu(gate.float()) * up.float()).to(gate.dtype)
+
+
+def combine_partial(d: torch.Tensor, probs: torch.Tensor, k: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """float32 y[t] = sum_j probs[t, j] * d[t k + j]; rows of d whose weight is exactly 0 are not read. The
+    partial sum of a rank that computed only the rows of its own experts."""
+    rows, H = d.shape
+    T = rows // k
+    if not (d.is_cuda and d.dtype in (torch.float16, torch.bfloat16) and H % 8 == 0 and d.is_contiguous()):
+        raise ValueError("[mlx_kquant.moe_combine] needs contiguous float16 / bfloat16 CUDA rows with H % 8 == 0.")
+    p = probs.reshape(T * k).float().contiguous()
+    y = torch.empty((T, H), dtype=torch.float32, device=d.device) if out is None else out
+    with torch.cuda.device(d.device):
+        _lib.check(_lib.lib().kq_moe_combine_f32(d.data_ptr(), p.data_ptr(), T, k, H,
+                                                 _lib.KQ_F16 if d.dtype == torch.float16 else _lib.KQ_BF16,
+                                                 y.data_ptr(), torch.cuda.current_stream(d.device).cuda_stream))
+    return y
 
 
 def combine(d: torch.Tensor, probs: torch.Tensor, k: int) -> torch.Tensor:
@@ -166,3 +195,100 @@ def moe_glu_expert_parallel(x, w_gate, w_up, w_down, kquant_type, expert_ids, ex
     y = torch.zeros((T, H), dtype=torch.float32, device=x.device)
     y.index_add_(0, tok[order], back.float() * w_sorted[:, None])
     return y.to(x.dtype)
+
+
+class GatheredExpertParallel:
+    """Expert-parallel MoE SwiGLU block with fixed shapes and no host read inside a step.
+
+    Where `moe_glu_expert_parallel` sends each routed row to the rank of its expert (two all-to-alls whose
+    split sizes the host must read first), this form moves the same bytes when top-k equals the rank count
+    but needs no sizes: one all-gather gives every rank all tokens with their routing; each rank multiplies
+    the rows routed to ITS experts (the other rows carry an out-of-range expert index, which `gather_qmm`,
+    the routed `swiglu` and the zero-weight rule of `combine_partial` all skip), forms the float32 partial
+    sum per token, and one reduce-scatter adds the partial sums and leaves every rank its own tokens. The
+    local stage touches no communicator, so `capture()` can record it into a CUDA graph.
+
+    x [T, H] float16 / bfloat16 with the same T on every rank; w_gate_up [E_local, 2F, bytes] and
+    w_down [E_local, H, bytes] are the local experts' stacks (`fuse_gate_up`, `dist.shard_bounds`).
+    """
+
+    def __init__(self, T, H, k, n_experts, w_gate_up, w_down, kquant_type, dtype=torch.bfloat16, group=None,
+                 *, rank=None, world=None):
+        from .dist import shard_bounds
+
+        if world is None:  # rank / world given explicitly: no communicator (pack() and local_stage() only)
+            import torch.distributed as dist
+
+            world, rank = dist.get_world_size(group), dist.get_rank(group)
+        self.group, self.world, self.rank = group, world, rank
+        self.T, self.H, self.k, self.kquant_type = T, H, k, kquant_type
+        self.w_gate_up, self.w_down = w_gate_up, w_down
+        self.lo, hi = shard_bounds(n_experts, self.rank, self.world)
+        self.e_local = hi - self.lo
+        dev = w_down.device
+        row_bytes = H * torch.empty((), dtype=dtype).element_size()
+        # routing (ids int32 + weights float32 per routed row) rides in extra rows behind the T activation rows,
+        # so that one all-gather moves everything and all ranks' activations form one [W * rows, H] matrix
+        self.pad_rows = -(-(T * k * 8) // row_bytes)
+        R = T + self.pad_rows
+        self.send = torch.zeros((R, H), dtype=dtype, device=dev)
+        self.recv = torch.empty((self.world * R, H), dtype=dtype, device=dev)
+        self.partial = torch.empty((self.world * T, H), dtype=torch.float32, device=dev)
+        self.y32 = torch.empty((T, H), dtype=torch.float32, device=dev)
+        tok = torch.arange(T, device=dev).repeat_interleave(k)
+        self.lhs = (torch.arange(self.world, device=dev)[:, None] * R + tok[None, :]).reshape(-1)
+        self._graph = None
+
+    def _meta(self, buf, R):
+        return buf.view(-1, R, self.H)[:, self.T:, :].reshape(buf.shape[0] // R, -1).view(torch.int32)
+
+    def local_stage(self):
+        """recv (all ranks' tokens and routing) -> partial (this rank's float32 partial sums for all tokens)."""
+        T, k, W = self.T, self.k, self.world
+        R = T + self.pad_rows
+        meta = self._meta(self.recv, R)
+        ids = meta[:, :T * k].reshape(W * T * k) - self.lo
+        probs = meta[:, T * k:2 * T * k].reshape(W * T * k).view(torch.float32)
+        mine = (ids >= 0) & (ids < self.e_local)
+        probs = torch.where(mine, probs, torch.zeros_like(probs))
+        rows = W * T * k
+        Fh = self.w_gate_up.shape[1] // 2
+        gu = gather_qmm(self.recv.view(W * R, 1, self.H), self.w_gate_up, None, self.kquant_type,
+                        lhs_indices=self.lhs, rhs_indices=ids).reshape(rows, 2 * Fh)
+        h = swiglu(gu[:, :Fh], gu[:, Fh:], row_expert=ids, n_experts=self.e_local)
+        d = gather_qmm(h.reshape(rows, 1, Fh), self.w_down, None, self.kquant_type, rhs_indices=ids)
+        combine_partial(d.reshape(rows, self.H), probs, k, out=self.partial)
+
+    def capture(self):
+        """Record the local stage into a CUDA graph (three warm-up runs on a side stream first)."""
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(3):
+                self.local_stage()
+        torch.cuda.current_stream().wait_stream(s)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.local_stage()
+        self._graph = g
+
+    def pack(self, x, expert_ids, expert_probs):
+        """Fill `send`: this rank's T activation rows, then ids and weights of its routed rows."""
+        T, k = self.T, self.k
+        self.send[:T].copy_(x)
+        tail = self.send[T:].view(torch.int32).reshape(-1)
+        tail[:T * k].copy_(expert_ids.reshape(T * k))
+        tail[T * k:2 * T * k].copy_(expert_probs.reshape(T * k).float().view(torch.int32))
+        return self.send
+
+    def __call__(self, x, expert_ids, expert_probs):
+        import torch.distributed as dist
+
+        self.pack(x, expert_ids, expert_probs)
+        dist.all_gather_into_tensor(self.recv, self.send, group=self.group)
+        if self._graph is not None:
+            self._graph.replay()
+        else:
+            self.local_stage()
+        dist.reduce_scatter_tensor(self.y32, self.partial, group=self.group)
+        return self.y32.to(x.dtype)

@@ -40,6 +40,13 @@ def _worker(rank, world, port, q):
         lo, hi = shard_bounds(E, rank, world)
         got = moe_glu_expert_parallel(x, wg[lo:hi], wu[lo:hi], wd[lo:hi], "q4_k", ids, probs, E).float()
         err = float((got - want).norm() / want.norm())
+        # the fixed-shape form: all-gather, local experts, reduce-scatter; eager and with the local stage as a graph
+        from mlx_kquant_b200.moe import GatheredExpertParallel, fuse_gate_up
+        ep = GatheredExpertParallel(T, H, k, E, fuse_gate_up(wg[lo:hi], wu[lo:hi]), wd[lo:hi].contiguous(), "q4_k")
+        err = max(err, float((ep(x, ids, probs).float() - want).norm() / want.norm()))
+        ep.capture()
+        err = max(err, float((ep(x, ids, probs).float() - want).norm() / want.norm()))
+        torch.cuda.synchronize()
         q.put((rank, err))
     finally:
         dist.destroy_process_group()
@@ -61,4 +68,4 @@ def test_expert_parallel_matches_single_gpu():
         p.join(timeout=60)
         assert p.exitcode == 0
     # same kernels on both sides; rows only meet different partners inside a tile
-    assert all(err < 1e-3 for _, err in results), results
+    assert all(err < 2e-3 for _, err in results), results

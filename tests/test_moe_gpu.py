@@ -72,3 +72,58 @@ def test_topk_ties_go_to_the_lowest_index():
     ids, probs = route_topk(logits, 3)
     assert ids.tolist() == [[0, 1, 2], [0, 1, 2]]
     assert torch.allclose(probs, torch.full((2, 3), 1 / 3))
+
+
+def test_routed_swiglu_and_partial_combine_skip_foreign_rows():
+    # rows of experts another rank owns hold NaN here: the routed forms must neither read nor write them
+    from mlx_kquant_b200.moe import combine_partial, swiglu
+    g = torch.Generator(device="cpu").manual_seed(6)
+    rows, F, H, k = 48, 128, 256, 4
+    gu = torch.randn(rows, 2 * F, generator=g).to(torch.bfloat16).cuda()
+    ids = torch.randint(-3, 9, (rows,), generator=g).to(torch.int32).cuda()     # 6 local experts: 0..5
+    mine = (ids >= 0) & (ids < 6)
+    gu[~mine] = float("nan")
+    out = swiglu(gu[:, :F], gu[:, F:], row_expert=ids, n_experts=6)
+    want = (torch.nn.functional.silu(gu[:, :F].float()) * gu[:, F:].float()).to(torch.bfloat16)
+    assert torch.equal(out[mine], want[mine])
+    d = torch.randn(rows, H, generator=g).to(torch.bfloat16).cuda()
+    d[~mine] = float("nan")
+    p = torch.rand(rows // k, k, generator=g).cuda()
+    p = torch.where(mine.reshape(-1, k), p, torch.zeros_like(p))
+    y = combine_partial(d, p, k)
+    ref = (torch.nan_to_num(d.float()).reshape(-1, k, H) * p[:, :, None]).sum(1)
+    assert y.dtype == torch.float32 and torch.isfinite(y).all()
+    assert torch.allclose(y, ref, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("T,E", [(24, 16), (320, 8)])   # task lists; grouped tile kernel (2560 routed rows, 4 local experts)
+def test_gathered_expert_parallel_two_virtual_ranks(T, E):
+    # Two ranks emulated on one GPU without a communicator: the all-gather is a concatenation of the two
+    # packed send buffers and the reduce-scatter a sum of the two partial buffers.
+    from mlx_kquant_b200.dist import shard_bounds
+    from mlx_kquant_b200.moe import GatheredExpertParallel, fuse_gate_up
+    from mlx_kquant_b200.synth import random_wire
+    dev = torch.device("cuda")
+    H, F, k, W = 512, 256, 4, 2
+    wg = random_wire("q4_k", F, H, seed=1, device=dev, lead=(E,))
+    wu = random_wire("q4_k", F, H, seed=2, device=dev, lead=(E,))
+    wd = random_wire("q4_k", H, F, seed=3, device=dev, lead=(E,))
+    ranks, xs, routes = [], [], []
+    for r in range(W):
+        g = torch.Generator(device="cpu").manual_seed(200 + r)
+        xs.append(torch.randn(T, H, generator=g).to(torch.bfloat16).to(dev))
+        routes.append(route_topk(torch.randn(T, E, generator=g).to(dev), k))
+        lo, hi = shard_bounds(E, r, W)
+        ranks.append(GatheredExpertParallel(T, H, k, E, fuse_gate_up(wg[lo:hi], wu[lo:hi]), wd[lo:hi].contiguous(),
+                                            "q4_k", rank=r, world=W))
+    gathered = torch.cat([ranks[r].pack(xs[r], *routes[r]) for r in range(W)])
+    total = torch.zeros((W * T, H), dtype=torch.float32, device=dev)
+    for r in range(W):
+        ranks[r].recv.copy_(gathered)
+        ranks[r].local_stage()
+        assert torch.isfinite(ranks[r].partial).all()
+        total += ranks[r].partial
+    for r in range(W):
+        want = moe_glu(xs[r], wg, wu, wd, "q4_k", *routes[r]).float()
+        got = total[r * T:(r + 1) * T].to(torch.bfloat16).float()
+        assert float((got - want).norm() / want.norm()) < 2e-3
