@@ -114,6 +114,10 @@ void quantize_host(int codec, const void* w, int dtype, long long n_weights, lon
                    uint8_t* out, int threads);
 
 // Elementwise stages of a mixture-of-experts SwiGLU block (kq_moe.cu). dtype 1 f16 / 2 bf16.
+// q4_k, one or two dense activation rows, on the integer tensor pipe (kq_gemv_imma.cu).
+bool gemv_imma_supported(int codec, int x_dtype, const GemvArgs& a);
+cudaError_t launch_gemv_imma(int x_dtype, const GemvArgs& a, cudaStream_t st);
+
 // row_expert != nullptr: rows with row_expert[r] >= n_experts are skipped. y_f32: y is float32.
 cudaError_t launch_swiglu(int dtype, const void* gate, const void* up, long long in_row_stride, long long rows, int F,
                           void* out, const uint32_t* row_expert, uint32_t n_experts, cudaStream_t st);
