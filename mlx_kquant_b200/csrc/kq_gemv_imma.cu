@@ -12,8 +12,9 @@
 // sums of the activations of sub-block j (src/kquant_cpu_decode.cpp:177-202 is the decode this
 // reproduces; the op rounds float32 activations to bfloat16 first, src/kquant_ops.cpp:159-168).
 //
-// Against the dp4a kernel: a third of the instructions per weight (the products of 512 weights in one
-// instruction instead of 128 in two), which is what bounds a decode launch on this GPU.
+// Against the dp4a kernel: 590 instead of 726 warp instructions per 32 rows x 256 weights (the products of
+// 512 weights in one instruction instead of 128 in two), and the same measured time within noise, so
+// this kernel runs only when KQ_GEMV_IMMA=1 asks for it.
 //
 // CTA = 8 warps x up to 32 weight rows; the warps split K in superblock columns; every warp streams
 // its columns through a cp.async ring of D slots (32 rows x 160 bytes: the 144 wire bytes of a block
