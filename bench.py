@@ -50,9 +50,9 @@ CODEC = "q4_k"
 ROW_BYTES = K_COLS // 256 * 144
 MATRIX_BYTES = N_ROWS * ROW_BYTES  # 9 437 184
 # the kernel that runs this workload, and its DRAM bytes per launch from the ncu capture summarised in
-# profiles/gemv_q4k_dp4a_decode.md (dram__bytes_read.sum + dram__bytes_write.sum)
-ROOFLINE_KERNEL = "gemv_q4k_m1_dp4a_kernel<__half>"
-ROOFLINE_TRAFFIC = 9469696
+# profiles/gemv_q4k_imma_decode.md (dram__bytes_read.sum + dram__bytes_write.sum)
+ROOFLINE_KERNEL = "gemv_q4k_imma_kernel<__half, 1>"
+ROOFLINE_TRAFFIC = 9470208
 
 
 def parse():

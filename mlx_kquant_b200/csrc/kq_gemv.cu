@@ -1558,8 +1558,12 @@ cudaError_t launch_gemv(int codec, int x_dtype, const GemvArgs& a, cudaStream_t 
   const bool aligned = a.w_align16 != 0;
 
   // A/B lever: KQ_GEMV_IMMA=0|1, the integer tensor-pipe kernel for one or two dense rows of q4_k
+  // (measured against the kernels below: 3-7 % faster up to ~60 M weights, slower beyond)
   static const char* imma_env = std::getenv("KQ_GEMV_IMMA");
-  if (imma_env && imma_env[0] == '1' && gemv_imma_supported(codec, x_dtype, a)) return launch_gemv_imma(x_dtype, a, st);
+  static const char* int_env = std::getenv("KQ_GEMV_DP4A");  // = 0 switches every integer kernel off
+  const bool imma_on = imma_env ? imma_env[0] == '1'
+                                : (!(int_env && int_env[0] == '0') && (long long)a.N * a.K <= (60ll << 20));
+  if (imma_on && gemv_imma_supported(codec, x_dtype, a)) return launch_gemv_imma(x_dtype, a, st);
   // one dense activation row of q4_k: the integer dot-product kernel. A/B lever: KQ_GEMV_DP4A=0|1.
   // Measured: it wins up to ~60 M weights against the fp16 tensor-core kernels below (which win
   // beyond), and always against the generic path that bf16 / float activations would take.

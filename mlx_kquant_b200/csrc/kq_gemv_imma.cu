@@ -13,8 +13,8 @@
 // reproduces; the op rounds float32 activations to bfloat16 first, src/kquant_ops.cpp:159-168).
 //
 // Against the dp4a kernel: 590 instead of 726 warp instructions per 32 rows x 256 weights (the products of
-// 512 weights in one instruction instead of 128 in two), and the same measured time within noise, so
-// this kernel runs only when KQ_GEMV_IMMA=1 asks for it.
+// 512 weights in one instruction instead of 128 in two). Measured on one GPU, same run: 3-7 % faster up
+// to ~60 M weights, slower beyond; the dispatcher uses it in that range (KQ_GEMV_IMMA=0|1 forces the choice).
 //
 // CTA = 8 warps x up to 32 weight rows; the warps split K in superblock columns; every warp streams
 // its columns through a cp.async ring of D slots (32 rows x 160 bytes: the 144 wire bytes of a block
@@ -320,11 +320,12 @@ cudaError_t launch_imma(const GemvArgs& a, cudaStream_t st) {
     attr_set[dev] = true;
   }
   // Up to one 32-row block per SM: one CTA per block, rows spread over all 148 SMs (28 each for N = 4096), which
-  // leaves the second CTA slot of every SM to the next launch's prefetch. Larger matrices: 296 persistent CTAs
-  // (two per SM) that share the blocks evenly: `waves` blocks each, of as many rows as that takes.
+  // leaves the second CTA slot of every SM to the next launch's prefetch. Up to two blocks per SM: one CTA per
+  // block. Larger matrices: 296 persistent CTAs (two per SM) that share the blocks evenly: `waves` blocks each,
+  // of as many rows as that takes (measured: [14336, 4096] 11.8 -> 10.5 us).
   int rpc = kImRows, grid;
   const int blocks32 = (a.N + kImRows - 1) / kImRows;
-  if (blocks32 <= 148) {
+  if (blocks32 <= 296) {
     if (blocks32 < 148 && a.N >= 148 * 16) rpc = (a.N + 147) / 148;
     grid = (a.N + rpc - 1) / rpc;
   } else {
