@@ -179,6 +179,31 @@ KQ_API int kq_gather_qmm_noalloc(const void* x, int x_dtype, long long x_batch, 
                                  const char* kquant_type, const uint32_t* lhs_indices, const uint32_t* rhs_indices,
                                  long long n_entries, int transpose, int rhs_sorted, void* y, void* stream);
 
+/* ---- expert tile map + segment product (the MoE prefill pair of the reference) ----
+ * Replaces: mlx_kquant::expert_tile_map (src/kquant_ops.cpp:422-447) and mlx_kquant::gather_qmm_seg
+ * (src/kquant_ops.cpp:466-548; Metal-only in the reference, "no CPU implementation",
+ * src/kquant_gather.cpp:983-1006).
+ *  kq_expert_tile_map: indices uint32 [rows], the expert of every row, rows sorted by expert. Writes
+ *    map uint32 [capacity, 3] = (expert, row_start, num_rows <= 64) for the first *count entries (entry order
+ *    unspecified beyond that, as in the reference) and count uint32 [1]. capacity =
+ *    kq_expert_tile_map_capacity(rows, n_experts) = max(rows / 64 + min(n_experts, rows), 1). Entries whose
+ *    expert is >= n_experts belong to no tile. Device pointers; no host read.
+ *  kq_gather_qmm_seg: x [rows, K] dense (rows grouped by expert), w [n_experts, N, w_row_bytes] with
+ *    w_expert_stride_bytes between matrices, y [rows, N] dense in x's dtype (bfloat16 for float32 x):
+ *    y[r] = x[r] @ dequant(w[expert of the map entry that covers r]).T for the first *count entries of
+ *    map [map_tiles, 3]; rows no entry covers are left unwritten. The pieces of one expert should form
+ *    one run of consecutive rows (both builders above do that); then they are re-cut into 256-row tiles.
+ *    Any other map is taken piece by piece. Pieces must not overlap. */
+KQ_API long long kq_expert_tile_map_capacity(long long rows, int n_experts);
+KQ_API size_t kq_expert_tile_map_workspace_bytes(int n_experts);
+KQ_API int kq_expert_tile_map(const uint32_t* indices, long long rows, int n_experts, uint32_t* map, uint32_t* count,
+                              void* workspace, size_t workspace_bytes, void* stream);
+KQ_API size_t kq_gather_qmm_seg_workspace_bytes(int x_dtype, long long rows, int K, int n_experts, long long map_tiles);
+KQ_API int kq_gather_qmm_seg(const void* x, int x_dtype, long long rows, int K, const void* w, int n_experts,
+                             long long w_expert_stride_bytes, size_t w_row_bytes, int N, const char* kquant_type,
+                             const uint32_t* map, const uint32_t* count, long long map_tiles, void* y, void* workspace,
+                             size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -9,6 +9,8 @@ reference's names, argument order and defaults (bindings.cpp:40-43, 94-141,
 ``include/kquant_b200.h``; importing this package without the built library
 raises at the first op call.
 """
-from .ops import codec_geometry, codecs, dequantize, gather_qmm, quantize, quantized_matmul
+from .ops import (codec_geometry, codecs, dequantize, expert_tile_map, gather_qmm, gather_qmm_seg, quantize,
+                  quantized_matmul)
 
-__all__ = ["codecs", "codec_geometry", "dequantize", "quantized_matmul", "gather_qmm", "quantize"]
+__all__ = ["codecs", "codec_geometry", "dequantize", "quantized_matmul", "gather_qmm", "quantize", "expert_tile_map",
+           "gather_qmm_seg"]

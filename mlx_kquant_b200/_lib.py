@@ -39,6 +39,14 @@ SIGNATURES = {
                                    C.c_void_p, C.c_int, C.c_void_p]),
     "kq_moe_combine_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                      C.c_void_p]),
+    "kq_expert_tile_map_capacity": (C.c_longlong, [C.c_longlong, C.c_int]),
+    "kq_expert_tile_map_workspace_bytes": (C.c_size_t, [C.c_int]),
+    "kq_expert_tile_map": (C.c_int, [C.c_void_p, C.c_longlong, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
+                                     C.c_size_t, C.c_void_p]),
+    "kq_gather_qmm_seg_workspace_bytes": (C.c_size_t, [C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_longlong]),
+    "kq_gather_qmm_seg": (C.c_int, [C.c_void_p, C.c_int, C.c_longlong, C.c_int, C.c_void_p, C.c_int, C.c_longlong,
+                                    C.c_size_t, C.c_int, C.c_char_p, C.c_void_p, C.c_void_p, C.c_longlong,
+                                    C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "kq_device_error_flags": (C.c_int, [C.POINTER(C.c_int), C.c_int]),
     "kq_gather_qmm_workspace_bytes": (C.c_size_t, [C.c_longlong, C.c_int, C.c_int, C.c_int]),
     "kq_gather_qmm": (C.c_int, [C.c_void_p, C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_void_p, C.c_int,

@@ -262,6 +262,81 @@ int kq_moe_combine_f32(const void* d, const float* probs, long long tokens, int 
   return combine_impl(d, probs, tokens, k, H, dtype, y, true, stream);
 }
 
+long long kq_expert_tile_map_capacity(long long rows, int n_experts) {
+  if (rows < 1 || n_experts < 1) return 0;
+  const long long present = rows < n_experts ? rows : n_experts;
+  const long long cap = rows / 64 + present;
+  return cap < 1 ? 1 : cap;
+}
+
+size_t kq_expert_tile_map_workspace_bytes(int n_experts) {
+  return n_experts < 1 ? 0 : kq::tile_map_workspace_bytes(n_experts);
+}
+
+int kq_expert_tile_map(const uint32_t* indices, long long rows, int n_experts, uint32_t* map, uint32_t* count,
+                       void* workspace, size_t workspace_bytes, void* stream) {
+  if (rows < 1 || n_experts < 1)
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.expert_tile_map] indices must be non-empty and n_experts positive.");
+  if (rows >= (1LL << 31)) return fail(KQ_ERR_UNSUPPORTED, "[mlx_kquant.expert_tile_map] too many rows.");
+  if (!indices || !map || !count) return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.expert_tile_map] null pointer.");
+  const size_t need = kq::tile_map_workspace_bytes(n_experts);
+  if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 3) != 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.expert_tile_map] workspace too small: %zu bytes given, %zu needed.",
+                workspace_bytes, need);
+  cudaError_t e = kq::launch_tile_map(indices, rows, n_experts, map, count, workspace, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("expert_tile_map", e);
+  return KQ_OK;
+}
+
+size_t kq_gather_qmm_seg_workspace_bytes(int x_dtype, long long rows, int K, int n_experts, long long map_tiles) {
+  if (!dtype_ok(x_dtype) || rows <= 0 || K <= 0 || n_experts <= 0 || map_tiles <= 0) return 0;
+  return kq::gather_seg_workspace_bytes(x_dtype, rows, K, n_experts, map_tiles);
+}
+
+int kq_gather_qmm_seg(const void* x, int x_dtype, long long rows, int K, const void* w, int n_experts,
+                      long long w_expert_stride_bytes, size_t w_row_bytes, int N, const char* kquant_type,
+                      const uint32_t* map, const uint32_t* count, long long map_tiles, void* y, void* workspace,
+                      size_t workspace_bytes, void* stream) {
+  const int ci = find_codec(kquant_type);
+  if (ci < 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmm_seg] Unknown kquant_type: '%s'.",
+                kquant_type ? kquant_type : "(null)");
+  const kq::CodecInfo& c = kq::kCodecs[ci];
+  if (w_row_bytes % (size_t)c.bpb != 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.gather_qmm_seg] KQuant weight last dim (%zu bytes) is not a whole number of %d-byte %s "
+                "blocks.",
+                w_row_bytes, c.bpb, c.name);
+  const long long wpr = (long long)(w_row_bytes / c.bpb) * c.wpb;
+  if (wpr != K)
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.gather_qmm_seg] x last dim (%d) does not match the expanded quantized row width (%lld) for "
+                "codec '%s'.",
+                K, wpr, c.name);
+  if (!dtype_ok(x_dtype))
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmm_seg] Only real floating x dtypes are supported.");
+  if (rows < 0 || N < 0 || n_experts < 1 || map_tiles < 1)
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.gather_qmm_seg] map must be uint32 [n_tiles >= 1, 3] (expert, row_start, num_rows).");
+  if (rows == 0 || N == 0) return KQ_OK;
+  if (!x || !w || !y || !map || !count) return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmm_seg] null pointer.");
+  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || ((size_t)K * (x_dtype == KQ_F32 ? 4 : 2)) % 16 != 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmm_seg] x rows must be 16-byte aligned.");
+  if (rows >= (1LL << 31) || map_tiles + rows / 256 + 1 > 65535)
+    return fail(KQ_ERR_UNSUPPORTED, "[mlx_kquant.gather_qmm_seg] too many rows or map entries for one call.");
+  const size_t need = kq::gather_seg_workspace_bytes(x_dtype, rows, K, n_experts, map_tiles);
+  if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.gather_qmm_seg] workspace too small or not 256-byte aligned: %zu bytes given, %zu needed.",
+                workspace_bytes, need);
+  cudaError_t e = kq::launch_gather_seg(ci, x_dtype, x, rows, K, static_cast<const uint8_t*>(w), n_experts,
+                                        w_expert_stride_bytes, (long long)w_row_bytes, N, map, count, map_tiles, y,
+                                        workspace, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("gather_qmm_seg", e);
+  return KQ_OK;
+}
+
 int kq_device_error_flags(int* flags, int clear) {
   if (flags == nullptr) return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant] kq_device_error_flags: null pointer.");
   cudaError_t e = kq::read_device_error(flags, clear != 0);

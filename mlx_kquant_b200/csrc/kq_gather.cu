@@ -184,6 +184,160 @@ __global__ void gather_tiles_kernel(int M, const int* __restrict__ offsets, cons
   }
 }
 
+// ---------------------------------------------------------------- tile map + segment product
+// expert_tile_map (src/kquant_ops.cpp:422-447): rows sorted by expert -> (expert, row_start, num_rows) triples of
+// at most 64 rows each and their count. grid.x = expert.
+__global__ void tile_map_kernel(const int* __restrict__ offsets, const int* __restrict__ tile_base, uint32_t* map) {
+  const int e = blockIdx.x;
+  const int start = offsets[e], rows = offsets[e + 1] - offsets[e];
+  const int nt = (rows + kSegMapTileRows - 1) / kSegMapTileRows;
+  for (int j = threadIdx.x; j < nt; j += blockDim.x) {
+    uint32_t* t = map + 3 * (size_t)(tile_base[e] + j);
+    t[0] = (uint32_t)e;
+    t[1] = (uint32_t)(start + j * kSegMapTileRows);
+    t[2] = (uint32_t)min(kSegMapTileRows, rows - j * kSegMapTileRows);
+  }
+}
+
+size_t tile_map_workspace_bytes(int n_experts) { return ((size_t)(3 * (n_experts + 1) + 1) * 4 + 255) & ~(size_t)255; }
+
+cudaError_t launch_tile_map(const uint32_t* indices, long long rows, int n_experts, uint32_t* map, uint32_t* count,
+                            void* workspace, cudaStream_t st) {
+  int* counts = static_cast<int*>(workspace);
+  int* offsets = counts + n_experts + 1;
+  int* tile_base = offsets + n_experts + 1;
+  cudaError_t err = cudaMemsetAsync(counts, 0, (size_t)(n_experts + 1) * 4, st);
+  if (err != cudaSuccess) return err;
+  const int th = 256;
+  gather_hist_kernel<<<(unsigned)((rows + th - 1) / th), th, 0, st>>>(indices, rows, n_experts, counts);
+  gather_scan_kernel<<<1, 1024, 0, st>>>(counts, n_experts, 1, kSegMapTileRows, offsets, tile_base,
+                                         reinterpret_cast<int*>(count));
+  tile_map_kernel<<<n_experts, 64, 0, st>>>(offsets, tile_base, map);
+  return cudaGetLastError();
+}
+
+// gather_qmm_seg (src/kquant_ops.cpp:466-548): the caller's map becomes the tile kernel's list. Maps built by
+// expert_tile_map or by the host recipe (mlx_kquant/nn.py:33-47) give every expert ONE run of consecutive rows cut in
+// 64-row pieces; such a run is re-cut into tiles of kGroupedTileRows rows, so that a weight tile is dequantized once
+// per 256 rows instead of once per 64. A map whose pieces of an expert do not add up to one run is taken piece by
+// piece (pieces longer than a tile are split). One CTA; seg = 3 n_experts ints of scratch.
+__global__ void __launch_bounds__(1024)
+seg_tiles_kernel(const uint32_t* __restrict__ map, const uint32_t* __restrict__ count, int cap, int n_experts,
+                 long long rows_total, int* seg, GatherTile* tiles, int max_tiles, int* n_tiles) {
+  __shared__ int s_scan[1024];
+  __shared__ int irregular, carry, appended;
+  int* seg_start = seg;
+  int* seg_end = seg + n_experts;
+  int* seg_len = seg + 2 * n_experts;
+  const int n = (int)min((unsigned)cap, *count);
+  if (threadIdx.x == 0) irregular = carry = appended = 0;
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+    seg_start[e] = 0x7fffffff;
+    seg_end[e] = 0;
+    seg_len[e] = 0;
+  }
+  __syncthreads();
+  for (int t = threadIdx.x; t < n; t += blockDim.x) {
+    const uint32_t e = map[3 * t], r0 = map[3 * t + 1], nr = map[3 * t + 2];
+    if (nr == 0 || e >= (uint32_t)n_experts || (long long)r0 + nr > rows_total) continue;  // dead or invalid piece
+    atomicMin(&seg_start[e], (int)r0);
+    atomicMax(&seg_end[e], (int)(r0 + nr));
+    atomicAdd(&seg_len[e], (int)nr);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x)
+    if (seg_len[e] > 0 && seg_end[e] - seg_start[e] != seg_len[e]) irregular = 1;
+  __syncthreads();
+  if (!irregular) {
+    for (int base = 0; base < n_experts; base += 1024) {
+      const int e = base + threadIdx.x;
+      const int len = e < n_experts ? seg_len[e] : 0;
+      const int nt = (len + kGroupedTileRows - 1) / kGroupedTileRows;
+      s_scan[threadIdx.x] = nt;
+      __syncthreads();
+      for (int d = 1; d < 1024; d <<= 1) {
+        const int v = (int)threadIdx.x >= d ? s_scan[threadIdx.x - d] : 0;
+        __syncthreads();
+        s_scan[threadIdx.x] += v;
+        __syncthreads();
+      }
+      const int first = carry + s_scan[threadIdx.x] - nt;
+      for (int j = 0; j < nt; j++) {
+        if (first + j >= max_tiles) break;
+        GatherTile t;
+        t.expert = e;
+        t.row_start = seg_start[e] + j * kGroupedTileRows;
+        t.rows = min(kGroupedTileRows, len - j * kGroupedTileRows);
+        t.pad = 0;
+        tiles[first + j] = t;
+      }
+      __syncthreads();
+      if (threadIdx.x == 1023) carry += s_scan[1023];
+      __syncthreads();
+    }
+    if (threadIdx.x == 0) *n_tiles = min(carry, max_tiles);
+  } else {
+    for (int t = threadIdx.x; t < n; t += blockDim.x) {
+      const uint32_t e = map[3 * t], r0 = map[3 * t + 1], nr = map[3 * t + 2];
+      if (nr == 0 || e >= (uint32_t)n_experts || (long long)r0 + nr > rows_total) continue;
+      for (uint32_t off = 0; off < nr; off += kGroupedTileRows) {
+        const int slot = atomicAdd(&appended, 1);
+        if (slot >= max_tiles) break;
+        GatherTile g;
+        g.expert = (int)e;
+        g.row_start = (int)(r0 + off);
+        g.rows = (int)min((uint32_t)kGroupedTileRows, nr - off);
+        g.pad = 0;
+        tiles[slot] = g;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) *n_tiles = min(appended, max_tiles);
+  }
+}
+
+static long long seg_max_tiles(long long rows, long long cap) { return cap + rows / kGroupedTileRows + 1; }
+
+size_t gather_seg_workspace_bytes(int x_dtype, long long rows, int K, int n_experts, long long cap) {
+  size_t b = ((size_t)(3 * n_experts + 1) * 4 + 255) & ~(size_t)255;                        // seg + n_tiles
+  b += ((size_t)seg_max_tiles(rows, cap) * sizeof(GatherTile) + 255) & ~(size_t)255;        // tiles
+  if (x_dtype != F16) {
+    b += ((size_t)rows * (size_t)K * 2 + 255) & ~(size_t)255;                               // fp16 copy of x
+    b += ((size_t)rows * 4 + 255) & ~(size_t)255;                                           // row factors
+  }
+  return b;
+}
+
+cudaError_t launch_gather_seg(int codec, int x_dtype, const void* x, long long rows, int K, const uint8_t* w,
+                              int n_experts, long long expert_stride, long long row_bytes, int N, const uint32_t* map,
+                              const uint32_t* count, long long cap, void* y, void* workspace, cudaStream_t st) {
+  if (rows <= 0 || N <= 0) return cudaSuccess;
+  if (rows >= (1LL << 31)) return cudaErrorInvalidValue;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  int* seg = reinterpret_cast<int*>(ws);
+  int* n_tiles = seg + 3 * n_experts;
+  size_t off = ((size_t)(3 * n_experts + 1) * 4 + 255) & ~(size_t)255;
+  GatherTile* tiles = reinterpret_cast<GatherTile*>(ws + off);
+  const long long max_tiles = seg_max_tiles(rows, cap);
+  if (max_tiles > 65535) return cudaErrorInvalidConfiguration;
+  off += ((size_t)max_tiles * sizeof(GatherTile) + 255) & ~(size_t)255;
+  seg_tiles_kernel<<<1, 1024, 0, st>>>(map, count, (int)cap, n_experts, rows, seg, tiles, (int)max_tiles, n_tiles);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return err;
+  const void* xh = x;
+  const float* rs = nullptr;
+  if (x_dtype != F16) {
+    void* xc = ws + off;
+    off += ((size_t)rows * (size_t)K * 2 + 255) & ~(size_t)255;
+    float* rsw = reinterpret_cast<float*>(ws + off);
+    if ((err = launch_convert_rows(x_dtype, x, K, K, rows, nullptr, 1, xc, rsw, st)) != cudaSuccess) return err;
+    xh = xc;
+    rs = rsw;
+  }
+  return launch_gemm_tiles(codec, x_dtype == F16, xh, rows, K, w, expert_stride, row_bytes, N, y, rs, nullptr, tiles,
+                           n_tiles, (int)max_tiles, st);
+}
+
 cudaError_t launch_gather(int codec, int x_dtype, const void* x, int M, int K, const uint8_t* w, int n_experts,
                           long long expert_stride, long long row_bytes, int N, const uint32_t* lhs,
                           const uint32_t* rhs, long long n_entries, void* y, void* workspace, bool allow_grouped,

@@ -803,6 +803,18 @@ cudaError_t launch_gemm_grouped(int codec, int x_dtype, const void* x, int M, in
                                                                    order, lhs, M, yrow, n_valid_dev);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
+  return launch_gemm_tiles(codec, x_dtype == F16, xh, rows_total, K, w, expert_stride, row_bytes, N, y,
+                           x_dtype == F16 ? nullptr : row_scale, yrow, tiles, n_tiles_dev, max_tiles, st);
+}
+
+// The tile kernel over a device-built list of (expert, row_start, rows <= 256) tiles: fp16 activations xh
+// [rows_total, K] (dense), output row yrow[r] (or r when yrow == nullptr), y = out_half ? fp16 : bf16.
+cudaError_t launch_gemm_tiles(int codec, bool out_half, const void* xh, long long rows_total, int K, const uint8_t* w,
+                              long long expert_stride, long long row_bytes, int N, void* y, const float* row_scale,
+                              const int* yrow, const void* tiles, const int* n_tiles_dev, int max_tiles,
+                              cudaStream_t st) {
+  if (rows_total <= 0 || N <= 0 || K <= 0 || max_tiles <= 0) return cudaSuccess;
+  if (max_tiles > 65535) return cudaErrorInvalidConfiguration;
   GemmArgs a;
   a.x = xh;
   a.x_row_stride = K;
@@ -813,12 +825,11 @@ cudaError_t launch_gemm_grouped(int codec, int x_dtype, const void* x, int M, in
   a.M = (int)rows_total;
   a.N = N;
   a.K = K;
-  a.row_scale = x_dtype == F16 ? nullptr : row_scale;
+  a.row_scale = row_scale;
   a.tiles = static_cast<const GemmTile*>(tiles);
   a.n_tiles_dev = n_tiles_dev;
   a.w_expert_stride = expert_stride;
   a.yrow = yrow;
-  const bool out_half = x_dtype == F16;
   const bool aligned = (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (expert_stride & 15) == 0;
   if (codec == Q4_K && aligned) {
     if (out_half) return launch_g<Q4_K, 16, __half, 2, 2, true>(a, st, max_tiles);

@@ -67,11 +67,24 @@ cudaError_t launch_gemm(int codec, int x_dtype, const void* x, long long x_row_s
                         const uint8_t* w, long long row_bytes, int M, int N, int K, void* workspace, cudaStream_t st);
 // Grouped (mixture-of-experts) prefill: 256-row tiles of expert-sorted rows, see kq_gather.cu.
 constexpr int kGroupedTileRows = 256;
+constexpr int kSegMapTileRows = 64;  // rows per entry of an expert tile map (the reference kernel's tile height)
+// expert_tile_map / gather_qmm_seg (kq_gather.cu)
+size_t tile_map_workspace_bytes(int n_experts);
+cudaError_t launch_tile_map(const uint32_t* indices, long long rows, int n_experts, uint32_t* map, uint32_t* count,
+                            void* workspace, cudaStream_t st);
+size_t gather_seg_workspace_bytes(int x_dtype, long long rows, int K, int n_experts, long long cap);
+cudaError_t launch_gather_seg(int codec, int x_dtype, const void* x, long long rows, int K, const uint8_t* w,
+                              int n_experts, long long expert_stride, long long row_bytes, int N, const uint32_t* map,
+                              const uint32_t* count, long long cap, void* y, void* workspace, cudaStream_t st);
 cudaError_t launch_gemm_grouped(int codec, int x_dtype, const void* x, int M, int K, const uint8_t* w,
                                 long long expert_stride, long long row_bytes, int N, const uint32_t* lhs,
                                 const int* order, long long rows_total, void* y, __half* xh, float* row_scale,
                                 int* yrow, const void* tiles, const int* n_tiles_dev, int max_tiles,
                                 const int* n_valid_dev, cudaStream_t st);
+cudaError_t launch_gemm_tiles(int codec, bool out_half, const void* xh, long long rows_total, int K, const uint8_t* w,
+                              long long expert_stride, long long row_bytes, int N, void* y, const float* row_scale,
+                              const int* yrow, const void* tiles, const int* n_tiles_dev, int max_tiles,
+                              cudaStream_t st);
 // Flags raised by kernels that gave up on a bounded wait (0 = none); synchronises the device.
 cudaError_t read_device_error(int* out, bool clear);
 // Exact fp16 copy of `rows` activation rows (x_dtype 0 f32 / 1 f16 / 2 bf16) with a per-row power-of-two

@@ -292,3 +292,15 @@ class GatheredExpertParallel:
             self.local_stage()
         dist.reduce_scatter_tensor(self.y32, self.partial, group=self.group)
         return self.y32.to(x.dtype)
+
+
+def host_tile_maps(counts, device=None):
+    """Host-built equivalent of `expert_tile_map` from per-expert row counts (mlx_kquant/nn.py:33-47): segments
+    cut into 64-row pieces, only the last piece of a segment partial. Returns (map int32 [n, 3], count int32 [1])."""
+    tiles, row = [], 0
+    for e, c in enumerate(int(v) for v in counts):
+        for off in range(0, c, 64):
+            tiles.append((e, row + off, min(64, c - off)))
+        row += c
+    m = torch.tensor(tiles or [(0, 0, 0)], dtype=torch.int32, device=device)
+    return m, torch.tensor([len(tiles)], dtype=torch.int32, device=device)

@@ -236,3 +236,85 @@ def gather_qmm(x, w, scales, kquant_type, lhs_indices=None, rhs_indices=None, tr
                               _stream_ptr(stream, dev)))
     y = y.reshape(idx_shape + (M, outer))
     return y.cpu() if on_cpu else y
+
+
+def expert_tile_map(indices, n_experts, *, stream=None):
+    """(map uint32-as-int32 [capacity, 3], count [1]) for rows sorted by expert (src/kquant_ops.cpp:422-447):
+    map rows are (expert, row_start, num_rows <= 64), the first ``count[0]`` of them valid, in unspecified order.
+    Built on the device without a host read. torch has no uint32 arithmetic, so both tensors are int32 holding
+    the same bits."""
+    op = "expert_tile_map"
+    if indices.dim() != 1 or indices.dtype not in (torch.int32, torch.int64, torch.uint32):
+        raise ValueError(f"[mlx_kquant.{op}] indices must be 1-D uint32 but got shape {tuple(indices.shape)} "
+                         f"dtype {indices.dtype}.")
+    rows = indices.shape[0]
+    if rows < 1 or n_experts < 1:
+        raise ValueError(f"[mlx_kquant.{op}] indices must be non-empty and n_experts positive.")
+    if not indices.is_cuda:
+        raise RuntimeError(f"[mlx_kquant.{op}] indices must live on a CUDA device; there is no CPU path.")
+    dev = indices.device
+    idx = indices.to(torch.int32).contiguous()
+    L = _lib.lib()
+    cap = L.kq_expert_tile_map_capacity(rows, n_experts)
+    tile_map = torch.zeros((cap, 3), dtype=torch.int32, device=dev)
+    count = torch.zeros(1, dtype=torch.int32, device=dev)
+    ws = torch.empty(max(L.kq_expert_tile_map_workspace_bytes(n_experts), 256), dtype=torch.uint8, device=dev)
+    if stream is not None:
+        for t in (idx, tile_map, count, ws):
+            t.record_stream(stream)
+    with torch.cuda.device(dev):
+        check(L.kq_expert_tile_map(idx.data_ptr(), rows, n_experts, tile_map.data_ptr(), count.data_ptr(),
+                                   ws.data_ptr(), ws.numel(), _stream_ptr(stream, dev)))
+    return tile_map, count
+
+
+def gather_qmm_seg(x, w, scales, kquant_type, map, counts, *, stream=None):  # noqa: A002 - the reference's name
+    """Segment product (src/kquant_ops.cpp:466-548): x [rows, K] grouped by expert, w [n_experts, N, bytes],
+    ``map`` [n_tiles, 3] = (expert, row_start, num_rows), ``counts`` [1] = valid map rows; returns [rows, N] with
+    y[r] = x[r] @ dequant(w[expert covering r]).T. Rows no map entry covers are unspecified."""
+    op = "gather_qmm_seg"
+    if w.dtype != torch.uint8:
+        raise ValueError(f"[mlx_kquant.{op}] w must be uint8 (raw GGUF wire bytes).")
+    wpb, bpb, _, _ = codec_geometry(kquant_type)
+    if x.dim() != 2:
+        raise ValueError(f"[mlx_kquant.{op}] x must be [rows, K] but got shape {tuple(x.shape)}.")
+    if w.dim() != 3:
+        raise ValueError(f"[mlx_kquant.{op}] w must be (n_experts, N, bytes_per_row) but got shape {tuple(w.shape)}.")
+    if map.dim() != 2 or map.shape[1] != 3 or map.shape[0] < 1 or map.dtype not in (torch.int32, torch.uint32):
+        raise ValueError(f"[mlx_kquant.{op}] map must be uint32 [n_tiles >= 1, 3] (expert, row_start, num_rows) "
+                         f"but got shape {tuple(map.shape)} dtype {map.dtype}.")
+    if counts.dim() != 1 or counts.shape[0] != 1 or counts.dtype not in (torch.int32, torch.uint32):
+        raise ValueError(f"[mlx_kquant.{op}] counts must be uint32 [1] but got shape {tuple(counts.shape)} "
+                         f"dtype {counts.dtype}.")
+    if w.shape[-1] % bpb != 0:
+        raise ValueError(f"[mlx_kquant.{op}] KQuant weight last dim ({w.shape[-1]} bytes) is not a whole number of "
+                         f"{bpb}-byte {kquant_type} blocks.")
+    wpr = w.shape[-1] // bpb * wpb
+    if wpr != x.shape[-1]:
+        raise ValueError(f"[mlx_kquant.{op}] x last dim ({x.shape[-1]}) does not match the expanded quantized row "
+                         f"width ({wpr}) for codec '{kquant_type}'.")
+    if x.dtype not in _DT:
+        raise ValueError(f"[mlx_kquant.{op}] Only real floating x dtypes are supported.")
+    _require_cuda(w, op)
+    dev = w.device
+    xc = x.to(dev).contiguous()
+    wc = w if (w.stride(2) == 1 and w.stride(1) == w.shape[2]) else w.contiguous()
+    mc = map.to(dev).contiguous()
+    cc = counts.to(dev).contiguous()
+    rows, K = xc.shape
+    E, N = wc.shape[0], wc.shape[1]
+    out_dtype = torch.bfloat16 if x.dtype == torch.float32 else x.dtype
+    y = torch.empty((rows, N), dtype=out_dtype, device=dev)
+    if rows == 0 or N == 0:
+        return y
+    L = _lib.lib()
+    ws = torch.empty(max(L.kq_gather_qmm_seg_workspace_bytes(_DT[x.dtype], rows, K, E, mc.shape[0]), 256),
+                     dtype=torch.uint8, device=dev)
+    if stream is not None:
+        for t in (xc, mc, cc, ws, y):
+            t.record_stream(stream)
+    with torch.cuda.device(dev):
+        check(L.kq_gather_qmm_seg(xc.data_ptr(), _DT[x.dtype], rows, K, wc.data_ptr(), E, wc.stride(0), wc.shape[2], N,
+                                  kquant_type.encode(), mc.data_ptr(), cc.data_ptr(), mc.shape[0], y.data_ptr(),
+                                  ws.data_ptr(), ws.numel(), _stream_ptr(stream, dev)))
+    return y
