@@ -1,0 +1,71 @@
+"""The torch module layer (mlx_kquant_b200/nn.py) against the ops it wraps; mirrors what the reference's
+tests/test_nn.py and tests/test_switch_gemm.py check of mlx_kquant/nn.py."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+import mlx_kquant_b200 as kq
+from mlx_kquant_b200.nn import KQuantEmbedding, KQuantLinear, KQuantSwitchLinear, bytes_per_row
+from mlx_kquant_b200.synth import random_wire
+
+
+def test_shapes_and_state_dict_keys():
+    lin = KQuantLinear(512, 96, bias=True, codec="q4_k")
+    assert tuple(lin.weight.shape) == (96, bytes_per_row("q4_k", 512)) and lin.weight.dtype == torch.uint8
+    assert set(lin.state_dict()) == {"weight", "scales", "bias"} and lin.mode == "kquant" and lin.bits == 4
+    sw = KQuantSwitchLinear(4, 64, 256, bias=False, codec="q6_k")
+    assert tuple(sw.weight.shape) == (4, 64, 210) and set(sw.state_dict()) == {"weight", "scales"}
+    emb = KQuantEmbedding(100, 256, "q8_0")
+    assert tuple(emb.weight.shape) == (100, 8 * 34)
+    with pytest.raises(ValueError):
+        KQuantLinear(100, 8, bias=False, codec="q4_k")        # 100 is not a whole number of 256-weight blocks
+    with pytest.raises(ValueError):
+        KQuantLinear(256, 8, bias=False, codec="q9_k")
+
+
+@pytest.mark.gpu
+def test_linear_and_embedding():
+    dev = torch.device("cuda")
+    lin = KQuantLinear(512, 96, bias=True, codec="q4_k").to(dev)
+    lin.weight.copy_(random_wire("q4_k", 96, 512, seed=1, device=dev))
+    lin.bias.copy_(torch.linspace(-1, 1, 96))
+    x = torch.randn(3, 5, 512, device=dev).to(torch.bfloat16)
+    y = lin(x)
+    want = kq.quantized_matmul(x, lin.weight, None, "q4_k") + lin.bias.to(torch.bfloat16)
+    assert tuple(y.shape) == (3, 5, 96) and torch.equal(y, want)
+
+    emb = KQuantEmbedding(50, 512, "q6_k").to(dev)
+    emb.weight.copy_(random_wire("q6_k", 50, 512, seed=2, device=dev))
+    tok = torch.tensor([[3, 49, 0], [7, 7, 12]], device=dev)
+    table = kq.dequantize(emb.weight, None, "q6_k", torch.bfloat16)
+    got = emb(tok)
+    assert tuple(got.shape) == (2, 3, 512) and got.dtype == torch.bfloat16 and torch.equal(got, table[tok])
+    h = torch.randn(2, 512, device=dev).to(torch.bfloat16)
+    assert torch.equal(emb.as_linear(h), kq.quantized_matmul(h, emb.weight, None, "q6_k"))
+
+
+@pytest.mark.gpu
+def test_switch_linear_gather_and_sorted_segment_paths():
+    dev = torch.device("cuda")
+    E, N, K = 6, 128, 512
+    sw = KQuantSwitchLinear(E, N, K, bias=True, codec="q4_k").to(dev)
+    sw.weight.copy_(random_wire("q4_k", N, K, seed=3, device=dev, lead=(E,)))
+    sw.bias.copy_(torch.randn(E, N))
+    g = torch.Generator(device="cpu").manual_seed(4)
+    # decode-shaped, unsorted
+    x = torch.randn(7, 1, K, generator=g).to(torch.float16).to(dev)
+    idx = torch.tensor([5, 0, 3, 3, 1, 5, 2], device=dev)
+    y = sw(x, idx)
+    want = kq.gather_qmm(x, sw.weight, None, "q4_k", rhs_indices=idx) + sw.bias[idx].unsqueeze(-2).half()
+    assert tuple(y.shape) == (7, 1, N) and torch.equal(y, want)
+    # prefill-shaped, sorted: the segment product with a device-built tile map (experts 2 absent)
+    counts = torch.tensor([130, 70, 0, 257, 64, 100])
+    B = int(counts.sum())
+    idx = torch.repeat_interleave(torch.arange(E), counts).to(dev)
+    xb = (torch.randn(B, 1, K, generator=g) * 0.5).to(torch.float16).to(dev)
+    y = sw(xb, idx, sorted_indices=True)
+    want = kq.gather_qmm(xb, sw.weight, None, "q4_k", rhs_indices=idx, sorted_indices=True).float() + \
+        sw.bias[idx].unsqueeze(-2)
+    assert tuple(y.shape) == (B, 1, N)
+    assert float((y.float() - want).norm() / want.norm()) < 2e-3
