@@ -200,6 +200,9 @@ cudaError_t launch_dequantize(int codec, const uint8_t* w, long long n_blocks, i
     case IQ4_NL: return launch_codec<IQ4_NL, 2>(w, out, n_blocks, dtype, st);
     case IQ4_XS: return launch_codec<IQ4_XS, 8>(w, out, n_blocks, dtype, st);
     case IQ2_XXS: return launch_codec<IQ2_XXS, 2>(w, out, n_blocks, dtype, st);
+    case Q4_1: return launch_codec<Q4_1, 4>(w, out, n_blocks, dtype, st);
+    case Q5_0: return launch_codec<Q5_0, 2>(w, out, n_blocks, dtype, st);
+    case Q5_1: return launch_codec<Q5_1, 8>(w, out, n_blocks, dtype, st);
   }
   return cudaErrorInvalidValue;
 }

@@ -772,6 +772,9 @@ cudaError_t launch_gemm(int codec, int x_dtype, const void* x, long long x_row_s
     case IQ4_NL: return launch_codec<IQ4_NL, 2>(out_half, a, aligned, st);
     case IQ4_XS: return launch_codec<IQ4_XS, 8>(out_half, a, aligned, st);
     case IQ2_XXS: return launch_codec<IQ2_XXS, 2>(out_half, a, aligned, st);
+    case Q4_1: return launch_codec<Q4_1, 4>(out_half, a, aligned, st);
+    case Q5_0: return launch_codec<Q5_0, 2>(out_half, a, aligned, st);
+    case Q5_1: return launch_codec<Q5_1, 8>(out_half, a, aligned, st);
   }
   return cudaErrorInvalidValue;
 }
@@ -846,6 +849,9 @@ cudaError_t launch_gemm_tiles(int codec, bool out_half, const void* xh, long lon
     case IQ4_NL: return launch_grouped_codec<IQ4_NL, 2>(out_half, a, aligned, max_tiles, st);
     case IQ4_XS: return launch_grouped_codec<IQ4_XS, 8>(out_half, a, aligned, max_tiles, st);
     case IQ2_XXS: return launch_grouped_codec<IQ2_XXS, 2>(out_half, a, aligned, max_tiles, st);
+    case Q4_1: return launch_grouped_codec<Q4_1, 4>(out_half, a, aligned, max_tiles, st);
+    case Q5_0: return launch_grouped_codec<Q5_0, 2>(out_half, a, aligned, max_tiles, st);
+    case Q5_1: return launch_grouped_codec<Q5_1, 8>(out_half, a, aligned, max_tiles, st);
   }
   return cudaErrorInvalidValue;
 }

@@ -1610,6 +1610,9 @@ cudaError_t launch_gemv(int codec, int x_dtype, const GemvArgs& a, cudaStream_t 
     case IQ4_NL: return launch_generic<IQ4_NL, 2>(x_dtype, a, grid, nt2, aligned, st);
     case IQ4_XS: return launch_generic<IQ4_XS, 8>(x_dtype, a, grid, nt2, aligned, st);
     case IQ2_XXS: return launch_generic<IQ2_XXS, 2>(x_dtype, a, grid, nt2, aligned, st);
+    case Q4_1: return launch_generic<Q4_1, 4>(x_dtype, a, grid, nt2, aligned, st);
+    case Q5_0: return launch_generic<Q5_0, 2>(x_dtype, a, grid, nt2, aligned, st);
+    case Q5_1: return launch_generic<Q5_1, 8>(x_dtype, a, grid, nt2, aligned, st);
   }
   return cudaErrorInvalidValue;
 }

@@ -616,6 +616,7 @@ cudaError_t launch_codec(int x_dtype, const GemvArgs& a, cudaStream_t st) {
 }  // namespace
 
 bool gemv_dp4a_supported(int codec, int x_dtype, const GemvArgs& a) {
+  if (codec == Q4_1 || codec == Q5_0 || codec == Q5_1) return false;  // generic decode kernel only
   if (!a.w_align16 || (a.K & 255) != 0 || a.K > kMaxK || (a.row_bytes & 15) != 0 || a.row_bytes < 16 * 17) return false;
   if (a.tasks != nullptr) {
     // task lists (gather_qmm): rows in slices of four. q4_k with fp16 rows and the two table codecs keep

@@ -253,6 +253,64 @@ void enc_q4_0(const float* x, const float*, uint8_t* b) {
   }
 }
 
+// q4_1, q5_0, q5_1 (src/kquant_cpu_encode.cpp:93-205): round-half-away like the other flat codecs
+void enc_q4_1(const float* x, const float*, uint8_t* b) {
+  float vmin = x[0], vmax = x[0];
+  for (int j = 1; j < 32; j++) {
+    vmin = std::min(vmin, x[j]);
+    vmax = std::max(vmax, x[j]);
+  }
+  const float d = (vmax - vmin) / 15.0f, id = d != 0.f ? 1.0f / d : 0.f;
+  put_f16(b, d);
+  put_f16(b + 2, vmin);
+  for (int j = 0; j < 16; j++) {
+    const uint8_t q0 = (uint8_t)std::min(15.0f, std::max(0.0f, std::round((x[j] - vmin) * id)));
+    const uint8_t q1 = (uint8_t)std::min(15.0f, std::max(0.0f, std::round((x[j + 16] - vmin) * id)));
+    b[4 + j] = (uint8_t)(q0 | (q1 << 4));
+  }
+}
+
+template <bool WITH_MIN>
+void enc_q5_01(const float* x, const float*, uint8_t* b) {
+  float d, off;
+  if constexpr (WITH_MIN) {
+    float vmin = x[0], vmax = x[0];
+    for (int j = 1; j < 32; j++) {
+      vmin = std::min(vmin, x[j]);
+      vmax = std::max(vmax, x[j]);
+    }
+    d = (vmax - vmin) / 31.0f;
+    off = vmin;
+    put_f16(b + 2, vmin);
+  } else {
+    float amax = 0.f;
+    for (int j = 0; j < 32; j++) amax = std::max(amax, std::fabs(x[j]));
+    d = amax / 15.0f;
+    off = 0.f;
+  }
+  const float id = d != 0.f ? 1.0f / d : 0.f;
+  put_f16(b, d);
+  uint8_t* qhp = b + (WITH_MIN ? 4 : 2);
+  uint8_t* qs = b + (WITH_MIN ? 8 : 6);
+  uint32_t qh = 0;
+  for (int j = 0; j < 16; j++) {
+    float v0, v1;
+    if constexpr (WITH_MIN) {
+      v0 = std::round((x[j] - off) * id);
+      v1 = std::round((x[j + 16] - off) * id);
+    } else {
+      v0 = std::round(x[j] * id) + 16.0f;
+      v1 = std::round(x[j + 16] * id) + 16.0f;
+    }
+    const uint8_t q0 = (uint8_t)std::min(31.0f, std::max(0.0f, v0));
+    const uint8_t q1 = (uint8_t)std::min(31.0f, std::max(0.0f, v1));
+    qs[j] = (uint8_t)((q0 & 0x0F) | ((q1 & 0x0F) << 4));
+    qh |= (uint32_t)(q0 >> 4) << j;
+    qh |= (uint32_t)(q1 >> 4) << (j + 16);
+  }
+  for (int i = 0; i < 4; i++) qhp[i] = (uint8_t)(qh >> (8 * i));
+}
+
 // q4_k (bits = 4) and q5_k (bits = 5)
 template <int BITS>
 void enc_q45_k(const float* x, const float* im, uint8_t* b) {
@@ -732,6 +790,9 @@ BlockFn block_encoder(int codec) {
     case IQ4_NL: return enc_iq4<32>;
     case IQ4_XS: return enc_iq4<256>;
     case IQ2_XXS: return enc_iq2_xxs;
+    case Q4_1: return enc_q4_1;
+    case Q5_0: return enc_q5_01<false>;
+    case Q5_1: return enc_q5_01<true>;
   }
   return nullptr;
 }
@@ -755,7 +816,7 @@ void quantize_host(int codec, const void* w, int dtype, long long n_weights, lon
   const int wpb = kCodecs[codec].wpb, bpb = kCodecs[codec].bpb;
   const long long n_blocks = n_weights / wpb;
   if (fn == nullptr || n_blocks <= 0) return;
-  const bool uses_imatrix = !(codec == Q8_0 || codec == Q4_0);  // the flat codecs ignore it (src/kquant_cpu_encode.cpp:832-834)
+  const bool uses_imatrix = !(codec == Q8_0 || codec == Q4_0 || codec == Q4_1 || codec == Q5_0 || codec == Q5_1);  // the flat codecs ignore it (src/kquant_cpu_encode.cpp:832-834)
   auto run = [&](long long b0, long long b1) {
     float x[256];
     for (long long b = b0; b < b1; b++) {

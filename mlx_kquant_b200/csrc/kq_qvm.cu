@@ -158,6 +158,9 @@ cudaError_t launch_qvm(int codec, int x_dtype, const void* x, long long x_row_st
     KQ_CASE(IQ4_NL, 2);
     KQ_CASE(IQ4_XS, 8);
     KQ_CASE(IQ2_XXS, 2);
+    KQ_CASE(Q4_1, 4);
+    KQ_CASE(Q5_0, 2);
+    KQ_CASE(Q5_1, 8);
   }
 #undef KQ_CASE
   return cudaErrorInvalidValue;

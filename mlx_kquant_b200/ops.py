@@ -81,7 +81,7 @@ def dequantize(w, scales, kquant_type, dtype=None, *, stream=None):
 def quantize(w, kquant_type, imatrix=None, *, stream=None):
     """Float weights [..., K] -> (wire bytes uint8 [..., K / wpb * bpb], scales placeholder uint8 [1]) on the
     HOST, like the reference's CPU-only encoder op (src/kquant_ops.cpp:550-631, bindings.cpp:1439-1446).
-    Byte-identical with the reference for all ten codecs; iq2_xxs requires an imatrix."""
+    Byte-identical with the reference for all thirteen codecs; iq2_xxs requires an imatrix."""
     del stream  # host work: there is no stream to order it on
     if w.dtype not in _DT:
         raise ValueError("[mlx_kquant.quantize] w must be a real floating tensor (float32, float16, or bfloat16).")

@@ -16,7 +16,8 @@ from .ops import codec_geometry
 
 # byte offsets of the fp16 fields inside one block
 _F16_FIELDS = {"q2_k": (80, 82), "q3_k": (108,), "q4_k": (0, 2), "q5_k": (0, 2), "q6_k": (208,), "q4_0": (0,),
-               "q8_0": (0,), "iq4_nl": (0,), "iq4_xs": (0,), "iq2_xxs": (0,)}
+               "q8_0": (0,), "iq4_nl": (0,), "iq4_xs": (0,), "iq2_xxs": (0,), "q4_1": (0, 2), "q5_0": (0,),
+               "q5_1": (0, 2)}
 
 
 def random_wire(kquant_type: str, rows: int, K: int, *, seed: int = 0, device="cuda", lead: tuple = ()) -> torch.Tensor:

@@ -91,6 +91,8 @@ static const kqo_codec KQO_CODECS[] = {
     {"q6_k", 256, 210, 6, 0},  {"q4_0", 32, 18, 4, 0},
     {"q8_0", 32, 34, 8, 0},    {"iq4_nl", 32, 18, 4, 0},
     {"iq4_xs", 256, 136, 4, 0}, {"iq2_xxs", 256, 66, 2, 1},
+    {"q4_1", 32, 20, 4, 0},    {"q5_0", 32, 22, 5, 0},
+    {"q5_1", 32, 24, 5, 0},
 };
 #define KQO_NCODECS ((int)(sizeof(KQO_CODECS) / sizeof(KQO_CODECS[0])))
 
@@ -137,6 +139,37 @@ static void blk_q4_0(const uint8_t* b, float* o) {
     o[j + 16] = d * (float)((int)(qs[j] >> 4) - 8);
   }
 }
+
+/* src/kquant_cpu_decode.cpp:84-103 */
+static void blk_q4_1(const uint8_t* b, float* o) {
+  float d = rd_f16(b), m = rd_f16(b + 2);
+  const uint8_t* qs = b + 4;
+  for (int j = 0; j < 16; j++) {
+    o[j] = d * (float)(qs[j] & 15) + m;
+    o[j + 16] = d * (float)(qs[j] >> 4) + m;
+  }
+}
+
+/* src/kquant_cpu_decode.cpp:105-128 (with_min = 0) and 130-153 (with_min = 1) */
+static void blk_q5(const uint8_t* b, float* o, int with_min) {
+  float d = rd_f16(b), m = with_min ? rd_f16(b + 2) : 0.f;
+  const uint8_t* qhp = b + (with_min ? 4 : 2);
+  const uint8_t* qs = b + (with_min ? 8 : 6);
+  uint32_t qh = (uint32_t)qhp[0] | ((uint32_t)qhp[1] << 8) | ((uint32_t)qhp[2] << 16) | ((uint32_t)qhp[3] << 24);
+  for (int j = 0; j < 16; j++) {
+    int x0 = (qs[j] & 15) | (int)(((qh >> j) << 4) & 0x10);
+    int x1 = (qs[j] >> 4) | (int)((qh >> (j + 12)) & 0x10);
+    if (with_min) {
+      o[j] = d * (float)x0 + m;
+      o[j + 16] = d * (float)x1 + m;
+    } else {
+      o[j] = d * (float)(x0 - 16);
+      o[j + 16] = d * (float)(x1 - 16);
+    }
+  }
+}
+static void blk_q5_0(const uint8_t* b, float* o) { blk_q5(b, o, 0); }
+static void blk_q5_1(const uint8_t* b, float* o) { blk_q5(b, o, 1); }
 
 /* src/kquant_cpu_decode.cpp:383-397 */
 static void blk_iq4_nl(const uint8_t* b, float* o) {
@@ -311,7 +344,8 @@ static void blk_iq2_xxs(const uint8_t* b, float* o) {
 
 typedef void (*blk_fn)(const uint8_t*, float*);
 static const blk_fn BLK_FNS[] = {blk_q2_k, blk_q3_k, blk_q4_k, blk_q5_k,   blk_q6_k,
-                                 blk_q4_0, blk_q8_0, blk_iq4_nl, blk_iq4_xs, blk_iq2_xxs};
+                                 blk_q4_0, blk_q8_0, blk_iq4_nl, blk_iq4_xs, blk_iq2_xxs,
+                                 blk_q4_1, blk_q5_0, blk_q5_1};
 
 /* ---- output rounding: one IEEE RNE rounding of the exact f32 value ---- */
 static uint16_t f32_to_bf16(float f) {

@@ -28,12 +28,13 @@ DT = {"f32": 0, "f16": 1, "bf16": 2}
 NP_OF = {"f32": np.float32, "f16": np.float16, "bf16": np.uint16}
 
 # (weights_per_block, bytes_per_block, bits, requires_imatrix): the ten in-scope
-# rows of the reference registry, src/kquant_codec.cpp:12-37.
+# rows of the reference registry, src/kquant_codec.cpp:12-37, and three further flat codecs.
 GEOMETRY = {
     "q2_k": (256, 84, 2, False), "q3_k": (256, 110, 3, False), "q4_k": (256, 144, 4, False),
     "q5_k": (256, 176, 5, False), "q6_k": (256, 210, 6, False), "q4_0": (32, 18, 4, False),
     "q8_0": (32, 34, 8, False), "iq4_nl": (32, 18, 4, False), "iq4_xs": (256, 136, 4, False),
-    "iq2_xxs": (256, 66, 2, True),
+    "iq2_xxs": (256, 66, 2, True), "q4_1": (32, 20, 4, False), "q5_0": (32, 22, 5, False),
+    "q5_1": (32, 24, 5, False),
 }
 CODECS = list(GEOMETRY)
 

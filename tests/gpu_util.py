@@ -48,7 +48,8 @@ def synthetic_wire(codec: str, rows: int, K: int, seed: int) -> np.ndarray:
     w = rng.integers(0, 256, (rows, nb, bpb), dtype=np.uint8)
     d = rng.uniform(0.001, 0.02, (rows, nb)).astype(np.float16).view(np.uint16)
     f16_at = {"q2_k": (80, 82), "q3_k": (108,), "q4_k": (0, 2), "q5_k": (0, 2), "q6_k": (208,), "q4_0": (0,),
-              "q8_0": (0,), "iq4_nl": (0,), "iq4_xs": (0,), "iq2_xxs": (0,)}[codec]
+              "q8_0": (0,), "iq4_nl": (0,), "iq4_xs": (0,), "iq2_xxs": (0,), "q4_1": (0, 2), "q5_0": (0,),
+              "q5_1": (0, 2)}[codec]
     for off in f16_at:
         w[:, :, off] = (d & 0xFF).astype(np.uint8)
         w[:, :, off + 1] = (d >> 8).astype(np.uint8)

@@ -32,7 +32,7 @@ def test_header_symbols_all_exported():
 
 
 def test_registry_matches_reference_geometry():
-    # src/kquant_codec.cpp:12-37, ten in-scope rows
+    # src/kquant_codec.cpp:12-37: the ten in-scope rows, then q4_1, q5_0, q5_1
     assert kq.codecs() == CODECS
     for c in CODECS:
         assert kq.codec_geometry(c) == GEOMETRY[c]

@@ -18,7 +18,8 @@ from oracle.kq_oracle import CODECS, GEOMETRY, bf16_bits_to_f32, from_f32, to_f3
 
 KQUANTS = ["q2_k", "q3_k", "q4_k", "q5_k", "q6_k"]
 GGUF_NAME = {"q2_k": "Q2_K", "q3_k": "Q3_K", "q4_k": "Q4_K", "q5_k": "Q5_K", "q6_k": "Q6_K", "q4_0": "Q4_0",
-             "q8_0": "Q8_0", "iq4_nl": "IQ4_NL", "iq4_xs": "IQ4_XS", "iq2_xxs": "IQ2_XXS"}
+             "q8_0": "Q8_0", "iq4_nl": "IQ4_NL", "iq4_xs": "IQ4_XS", "iq2_xxs": "IQ2_XXS", "q4_1": "Q4_1", "q5_0": "Q5_0",
+             "q5_1": "Q5_1"}
 
 
 def bits(a):

@@ -9,7 +9,7 @@ import torch
 import mlx_kquant_b200 as kq
 from oracle import kq_oracle
 
-BUILT = ("q8_0", "q4_0", "q2_k", "q3_k", "q4_k", "q5_k", "q6_k", "iq4_nl", "iq4_xs", "iq2_xxs")
+BUILT = ("q8_0", "q4_0", "q2_k", "q3_k", "q4_k", "q5_k", "q6_k", "iq4_nl", "iq4_xs", "iq2_xxs", "q4_1", "q5_0", "q5_1")
 
 
 @pytest.fixture(scope="module")
