@@ -126,7 +126,11 @@ def read_gguf(path: str | Path, device: torch.device | str | None = None):
 def _pack_value(v) -> bytes:
     if isinstance(v, bool):
         return struct.pack("<I?", 7, v)
-    if isinstance(v, int):
+    if isinstance(v, int):  # the narrowest of u32 / i32 / u64 / i64: readers expect u32 for the common keys
+        if 0 <= v < 2**32:
+            return struct.pack("<II", 4, v)
+        if -2**31 <= v < 0:
+            return struct.pack("<Ii", 5, v)
         return struct.pack("<Iq", 11, v) if v < 0 else struct.pack("<IQ", 10, v)
     if isinstance(v, float):
         return struct.pack("<Id", 12, v)

@@ -74,3 +74,33 @@ def test_tensor_from_file_drives_a_linear(tmp_path):
     assert float((lin(x).float() - want).norm() / want.norm()) < 2e-3
     # and the dequantized weights are the encoder's view of w
     assert float((kq.dequantize(t.data, None, "q4_k", torch.float32).cpu() - w).norm() / w.norm()) < 0.1
+
+
+def test_interoperates_with_gguf_py(tmp_path):
+    # files written by the gguf package are read here, and files written here are read by it
+    ggpy = pytest.importorskip("gguf")
+    import numpy as np
+    w = torch.randn(8, 512, generator=torch.Generator().manual_seed(3)) * 0.05
+    wire, _ = kq.quantize(w, "q4_k")
+    theirs = tmp_path / "theirs.gguf"
+    wr = ggpy.GGUFWriter(str(theirs), "llama")
+    wr.add_uint32("llama.block_count", 2)
+    wr.add_string("general.name", "tiny")
+    wr.add_array("tokenizer.ggml.tokens", ["a", "b"])
+    wr.add_tensor("blk.0.ffn_up.weight", wire.numpy(), raw_dtype=ggpy.GGMLQuantizationType.Q4_K)
+    wr.add_tensor("norm.weight", np.ones(512, np.float32))
+    wr.write_header_to_file()
+    wr.write_kv_data_to_file()
+    wr.write_tensors_to_file()
+    wr.close()
+    meta, tensors = gguf.read_gguf(theirs)
+    assert meta["general.architecture"] == "llama" and meta["llama.block_count"] == 2
+    assert meta["tokenizer.ggml.tokens"] == ["a", "b"]
+    t = tensors["blk.0.ffn_up.weight"]
+    assert t.codec == "q4_k" and t.shape == (8, 512) and torch.equal(t.data, wire)
+    assert tensors["norm.weight"].codec is None and float(tensors["norm.weight"].data.sum()) == 512.0
+    ours = tmp_path / "ours.gguf"
+    gguf.write_gguf(ours, {"general.architecture": "llama", "llama.block_count": 2}, {"a.weight": ("q4_k", (8, 512), wire)})
+    r = ggpy.GGUFReader(str(ours))
+    assert r.tensors[0].name == "a.weight" and r.tensors[0].tensor_type.name == "Q4_K"
+    assert np.array_equal(np.asarray(r.tensors[0].data).reshape(-1), wire.numpy().reshape(-1))
