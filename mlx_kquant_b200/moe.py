@@ -304,3 +304,43 @@ def host_tile_maps(counts, device=None):
         row += c
     m = torch.tensor(tiles or [(0, 0, 0)], dtype=torch.int32, device=device)
     return m, torch.tensor([len(tiles)], dtype=torch.int32, device=device)
+
+
+def moe_router_topk(logits, top_k, norm_topk_prob, shared_gate=True, per_expert_scale=None, bias=None,
+                    scoring="softmax", scale=1.0):
+    """Router top-k with the reference op's semantics (src/kquant.h:560-585): score the E expert columns in
+    float32 ("softmax", or "sqrtsoftplus" = sqrt(softplus(x))), pick the `top_k` largest of score (+ `bias` [E],
+    which ranks the selection only), lowest index first among equals, optionally renormalise the picked scores
+    (the sqrtsoftplus renormalisation carries a 1e-20 guard), multiply by `per_expert_scale` [E] of the picked
+    experts and by the uniform `scale`. With `shared_gate`, logits are [T, E + 1] and the sigmoid of column E
+    lands in an extra last scores slot. Returns (indices [T, top_k] int32, scores float32 [T, top_k (+ 1)]).
+    Composed of torch ops on the logits' device; E <= 1024 and top_k <= 16 as in the reference."""
+    if scoring not in ("softmax", "sqrtsoftplus"):
+        raise ValueError(f"[mlx_kquant.moe_router_topk] unknown scoring '{scoring}'.")
+    if logits.dim() != 2:
+        raise ValueError(f"[mlx_kquant.moe_router_topk] logits must be [T, E] but got shape {tuple(logits.shape)}.")
+    E = logits.shape[1] - (1 if shared_gate else 0)
+    if E < 1 or E > 1024 or top_k < 1 or top_k > 16 or top_k > E:
+        raise ValueError("[mlx_kquant.moe_router_topk] needs 1 <= top_k <= min(E, 16) and E <= 1024.")
+    if scoring == "sqrtsoftplus" and not norm_topk_prob:
+        raise ValueError("[mlx_kquant.moe_router_topk] sqrtsoftplus has no global normaliser: norm_topk_prob is required.")
+    lf = logits.float()
+    x = lf[:, :E]
+    if scoring == "softmax":
+        p = torch.softmax(x, dim=-1)
+    else:
+        p = torch.sqrt(torch.nn.functional.softplus(x, threshold=88.0))
+    rank = p if bias is None else p + bias.to(p.device).float()
+    # a stable descending sort puts the lowest index first among equal scores
+    idx = torch.sort(rank, dim=-1, descending=True, stable=True).indices[:, :top_k]
+    picked = torch.gather(p, 1, idx)
+    if norm_topk_prob:
+        s = picked.sum(dim=-1, keepdim=True)
+        picked = picked / (s + 1e-20 if scoring == "sqrtsoftplus" else s)
+    if per_expert_scale is not None:
+        picked = picked * per_expert_scale.to(p.device).float()[idx]
+    if scale != 1.0:
+        picked = picked * float(scale)
+    if shared_gate:
+        picked = torch.cat([picked, torch.sigmoid(lf[:, E:E + 1])], dim=1)
+    return idx.to(torch.int32), picked
