@@ -180,6 +180,13 @@ KQ_API int kq_gather_qmm_noalloc(const void* x, int x_dtype, long long x_batch, 
                                  const char* kquant_type, const uint32_t* lhs_indices, const uint32_t* rhs_indices,
                                  long long n_entries, int transpose, int rhs_sorted, void* y, void* stream);
 
+/* Decode product with the bias add fused: y = round(x @ dequant(w).T + bias), one row of x, the sum and the add
+ * in float32 and ONE rounding to the output dtype (x's dtype, bfloat16 for float32 x). bias: N values in that
+ * output dtype. Replaces mlx_kquant::quantized_matmul_qmv_bias (src/kquant_ops.cpp:185-283): q8_0 only, any other
+ * codec is KQ_ERR_INVALID_ARGUMENT, as there. */
+KQ_API int kq_quantized_matmul_qmv_bias(const void* x, int x_dtype, int K, const void* w, size_t w_row_bytes, int N,
+                                        const char* kquant_type, const void* bias, void* y, void* stream);
+
 /* ---- expert tile map + segment product (the MoE prefill pair of the reference) ----
  * Replaces: mlx_kquant::expert_tile_map (src/kquant_ops.cpp:422-447) and mlx_kquant::gather_qmm_seg
  * (src/kquant_ops.cpp:466-548; Metal-only in the reference, "no CPU implementation",

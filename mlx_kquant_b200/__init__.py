@@ -10,7 +10,7 @@ reference's names, argument order and defaults (bindings.cpp:40-43, 94-141,
 raises at the first op call.
 """
 from .ops import (codec_geometry, codecs, dequantize, expert_tile_map, gather_qmm, gather_qmm_seg, quantize,
-                  quantized_matmul)
+                  quantized_matmul, quantized_matmul_qmv_bias)
 
 __all__ = ["codecs", "codec_geometry", "dequantize", "quantized_matmul", "gather_qmm", "quantize", "expert_tile_map",
-           "gather_qmm_seg"]
+           "gather_qmm_seg", "quantized_matmul_qmv_bias"]

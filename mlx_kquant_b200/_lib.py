@@ -39,6 +39,8 @@ SIGNATURES = {
                                    C.c_void_p, C.c_int, C.c_void_p]),
     "kq_moe_combine_f32": (C.c_int, [C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                      C.c_void_p]),
+    "kq_quantized_matmul_qmv_bias": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.c_int,
+                                               C.c_char_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "kq_expert_tile_map_capacity": (C.c_longlong, [C.c_longlong, C.c_int]),
     "kq_expert_tile_map_workspace_bytes": (C.c_size_t, [C.c_int]),
     "kq_expert_tile_map": (C.c_int, [C.c_void_p, C.c_longlong, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,

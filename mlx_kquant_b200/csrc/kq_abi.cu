@@ -262,6 +262,49 @@ int kq_moe_combine_f32(const void* d, const float* probs, long long tokens, int 
   return combine_impl(d, probs, tokens, k, H, dtype, y, true, stream);
 }
 
+int kq_quantized_matmul_qmv_bias(const void* x, int x_dtype, int K, const void* w, size_t w_row_bytes, int N,
+                                 const char* kquant_type, const void* bias, void* y, void* stream) {
+  const int ci = find_codec(kquant_type);
+  if (ci != kq::Q8_0)
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.quantized_matmul_qmv_bias] only kquant_type 'q8_0' is wired so far, got '%s'.",
+                kquant_type ? kquant_type : "(null)");
+  const kq::CodecInfo& c = kq::kCodecs[ci];
+  if (w_row_bytes % (size_t)c.bpb != 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.quantized_matmul_qmv_bias] KQuant weight last dim (%zu bytes) is not a whole number of "
+                "%d-byte %s blocks.",
+                w_row_bytes, c.bpb, c.name);
+  if ((long long)(w_row_bytes / c.bpb) * c.wpb != K)
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.quantized_matmul_qmv_bias] x last dim (%d) does not match the expanded quantized matrix "
+                "inner dim (%lld) for codec '%s'.",
+                K, (long long)(w_row_bytes / c.bpb) * c.wpb, c.name);
+  if (!dtype_ok(x_dtype))
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.quantized_matmul_qmv_bias] Only real floating x dtypes are supported.");
+  if (N < 0) return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.quantized_matmul_qmv_bias] negative size.");
+  if (N == 0) return KQ_OK;
+  if (!x || !w || !y || !bias) return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.quantized_matmul_qmv_bias] null pointer.");
+  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.quantized_matmul_qmv_bias] x must be 16-byte aligned.");
+  kq::GemvArgs a{};
+  a.x = x;
+  a.x_row_stride = K;
+  a.y = y;
+  a.y_row_stride = N;
+  a.w = static_cast<const uint8_t*>(w);
+  a.w_align16 = (reinterpret_cast<uintptr_t>(w) & 15) == 0 ? 1 : 0;
+  a.row_bytes = (long long)w_row_bytes;
+  a.N = N;
+  a.K = K;
+  a.M = 1;
+  a.bias = bias;
+  cudaError_t e = kq::launch_gemv(ci, x_dtype, a, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("quantized_matmul_qmv_bias", e);
+  return KQ_OK;
+}
+
 long long kq_expert_tile_map_capacity(long long rows, int n_experts) {
   if (rows < 1 || n_experts < 1) return 0;
   const long long present = rows < n_experts ? rows : n_experts;

@@ -1031,6 +1031,7 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_kernel(const GemvArgs a) {
       for (int s = 0; s < kMaxSplit; s++)
         if (s < S) sum += peer[s][idx];
       OT* y = static_cast<OT*>(a.y) + (long long)s_yrow[tok] * a.y_row_stride + cta_row0 + row;
+      if (a.bias != nullptr) sum += (float)static_cast<const OT*>(a.bias)[cta_row0 + row];
       if constexpr (kHalf) {
         if (a.out_bf16) {  // rows that were bf16 / f32 before their exact conversion to fp16
           const float rs = a.row_scale ? a.row_scale[s_xrow[tok]] : 1.f;

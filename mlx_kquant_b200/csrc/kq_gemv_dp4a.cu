@@ -560,6 +560,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_dp4a_kernel(const GemvArgs a
       for (int u = 1; u < MT; u++)
         if (t == u) yrow = yr[u];
       OT* out = static_cast<OT*>(a.y) + (long long)yrow * a.y_row_stride + row0 + r;
+      if (a.bias != nullptr) sum += (float)static_cast<const OT*>(a.bias)[row0 + r];
       if constexpr (std::is_same<OT, __half>::value) *out = __float2half_rn(sum);
       else *out = __float2bfloat16_rn(sum);
     }

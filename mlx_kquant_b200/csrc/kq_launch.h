@@ -43,6 +43,9 @@ struct GemvArgs {
   // converted bf16 / f32 activations to fp16 with a per-row power-of-two factor
   int out_bf16;
   const float* row_scale;   // indexed like the rows of x, or nullptr
+  // one dense row only: N values in the output dtype added to the float sum before its single rounding
+  // (quantized_matmul_qmv_bias), or nullptr. Honoured by gemv_kernel<> and gemv_dp4a_kernel<>.
+  const void* bias;
 };
 
 // y = x . dequant(w)^T for skinny row groups. x_dtype: 0 f32 (rounded to bf16

@@ -66,6 +66,11 @@ class KQuantLinear(_KQuantBase):
             self.bias = None
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        # decode (one row) with a bias: the add is fused into the q8_0 decode kernel, as the reference does
+        # (mlx_kquant/nn.py:129-146); KQ_DISABLE_QMV_BIAS=1 forces the unfused path, read live
+        if (self.bias is not None and self.kquant_type == "q8_0" and x.numel() // x.shape[-1] == 1
+                and os.environ.get("KQ_DISABLE_QMV_BIAS") != "1"):
+            return kq.quantized_matmul_qmv_bias(x, self.weight, self.scales, self.bias, self.kquant_type)
         y = kq.quantized_matmul(x, self.weight, self.scales, self.kquant_type, transpose=True)
         if self.bias is not None:
             y = y + self.bias.to(y.dtype)

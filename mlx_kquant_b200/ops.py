@@ -318,3 +318,49 @@ def gather_qmm_seg(x, w, scales, kquant_type, map, counts, *, stream=None):  # n
                                   kquant_type.encode(), mc.data_ptr(), cc.data_ptr(), mc.shape[0], y.data_ptr(),
                                   ws.data_ptr(), ws.numel(), _stream_ptr(stream, dev)))
     return y
+
+
+def quantized_matmul_qmv_bias(x, w, scales, bias, kquant_type, *, stream=None):
+    """Decode-only product with the bias add fused into the kernel's epilogue (src/kquant_ops.cpp:185-283):
+    x carries exactly one row, w is 2-D [N, bytes], bias [N]; q8_0 only, like the reference op."""
+    op = "quantized_matmul_qmv_bias"
+    if kquant_type != "q8_0":
+        raise ValueError(f"[mlx_kquant.{op}] only kquant_type 'q8_0' is wired so far, got '{kquant_type}'.")
+    if w.dtype != torch.uint8:
+        raise ValueError(f"[mlx_kquant.{op}] w must be uint8 (raw GGUF wire bytes).")
+    if w.dim() != 2:
+        raise ValueError(f"[mlx_kquant.{op}] w must be 2D (this op is not batched); use gather_qmm for "
+                         "mixture-of-experts.")
+    wpb, bpb, _, _ = codec_geometry(kquant_type)
+    if w.shape[-1] % bpb != 0:
+        raise ValueError(f"[mlx_kquant.{op}] KQuant weight last dim ({w.shape[-1]} bytes) is not a whole number of "
+                         f"{bpb}-byte {kquant_type} blocks.")
+    K, N = w.shape[-1] // bpb * wpb, w.shape[0]
+    if K != x.shape[-1]:
+        raise ValueError(f"[mlx_kquant.{op}] x last dim ({x.shape[-1]}) does not match the expanded quantized matrix "
+                         f"inner dim ({K}) for codec '{kquant_type}'.")
+    if bias.dim() != 1 or bias.shape[0] != N:
+        raise ValueError(f"[mlx_kquant.{op}] bias must be 1D with length {N} (the output dim), got shape "
+                         f"{tuple(bias.shape)}.")
+    if x.numel() // x.shape[-1] != 1:
+        raise ValueError(f"[mlx_kquant.{op}] decode-only: x must carry exactly one row (got "
+                         f"{x.numel() // x.shape[-1]}). Use quantized_matmul() + a separate add for prefill/verify "
+                         "shapes.")
+    if x.dtype not in _DT:
+        raise ValueError(f"[mlx_kquant.{op}] Only real floating x dtypes are supported.")
+    _require_cuda(w, op)
+    dev = w.device
+    x, on_cpu = _prep_x(x, dev, op)
+    out_dtype = torch.bfloat16 if x.dtype == torch.float32 else x.dtype
+    xc = x.reshape(1, K).contiguous()
+    wc = w.contiguous()
+    bc = bias.to(dev).to(out_dtype).contiguous()
+    y = torch.empty(x.shape[:-1] + (N,), dtype=out_dtype, device=dev)
+    if stream is not None:
+        for t in (xc, bc, y):
+            t.record_stream(stream)
+    with torch.cuda.device(dev):
+        check(_lib.lib().kq_quantized_matmul_qmv_bias(xc.data_ptr(), _DT[x.dtype], K, wc.data_ptr(), wc.shape[1], N,
+                                                      kquant_type.encode(), bc.data_ptr(), y.data_ptr(),
+                                                      _stream_ptr(stream, dev)))
+    return y.cpu() if on_cpu else y

@@ -69,3 +69,33 @@ def test_switch_linear_gather_and_sorted_segment_paths():
         sw.bias[idx].unsqueeze(-2)
     assert tuple(y.shape) == (B, 1, N)
     assert float((y.float() - want).norm() / want.norm()) < 2e-3
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("K", [1024, 288])      # integer-kernel shape; generic-kernel shape (K not a multiple of 256)
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_qmv_bias_is_fused_with_one_rounding(K, dtype):
+    dev = torch.device("cuda")
+    N = 200
+    w = random_wire("q8_0", N, K, seed=9, device=dev)
+    x = torch.randn(1, 1, K, device=dev).to(dtype)
+    out_dt = torch.bfloat16 if dtype == torch.float32 else dtype
+    bias = (torch.randn(N, device=dev) * 3).to(out_dt)
+    y = kq.quantized_matmul_qmv_bias(x, w, None, bias, "q8_0")
+    assert tuple(y.shape) == (1, 1, N) and y.dtype == out_dt
+    xr = x.to(torch.bfloat16) if dtype == torch.float32 else x
+    exact = xr.double().reshape(1, K) @ kq.dequantize(w, None, "q8_0", torch.float32).double().T + bias.double()
+    # one rounding of sum + bias: half an ulp of the output dtype plus the kernels' 2e-3 budget on the product
+    ulp = 2.0 ** (-10 if out_dt == torch.float16 else -7)
+    err = (y.double().reshape(1, N) - exact).abs()
+    assert bool((err <= 0.5 * ulp * exact.abs() + 2e-3 * (exact - bias.double()).abs().max() + 1e-6).all())
+    lin = KQuantLinear(K, N, bias=True, codec="q8_0").to(dev)
+    lin.weight.copy_(w)
+    lin.bias.copy_(bias.float())
+    assert torch.equal(lin(x), y)
+    with pytest.raises(ValueError):
+        kq.quantized_matmul_qmv_bias(torch.cat([x, x]), w, None, bias, "q8_0")      # two rows
+    with pytest.raises(ValueError):
+        kq.quantized_matmul_qmv_bias(x, w, None, bias[:-1], "q8_0")
+    with pytest.raises(ValueError):
+        kq.quantized_matmul_qmv_bias(x, w, None, bias, "q4_k")
