@@ -414,7 +414,6 @@ int gather_qmm_entry(const void* x, int x_dtype, long long x_batch, int M, int K
                      int rhs_sorted, void* y, void* workspace, size_t workspace_bytes, void* stream,
                      bool allow_grouped) {
   (void)rhs_sorted;
-  (void)x_batch;
   const int ci = find_codec(kquant_type);
   if (ci < 0)
     return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmm] Unknown kquant_type: '%s'.",
@@ -426,9 +425,26 @@ int gather_qmm_entry(const void* x, int x_dtype, long long x_batch, int M, int K
                 w_row_bytes, c.bpb, c.name);
   if (!dtype_ok(x_dtype))
     return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmm] Only real floating x dtypes are supported.");
-  if (!transpose)
-    return fail(KQ_ERR_UNSUPPORTED, "[mlx_kquant.gather_qmm] transpose=false ([K, N] weights) is not built yet.");
   const long long wpr = (long long)(w_row_bytes / c.bpb) * c.wpb;
+  if (!transpose) {
+    // [K, N] expert matrices (rows quantized along N): the streaming kernel of kq_qvm.cu over the entries
+    if (wpr != N)
+      return fail(KQ_ERR_INVALID_ARGUMENT,
+                  "[mlx_kquant.gather_qmm] x last dim (%d) does not match the expanded quantized matrix inner dim (%d) "
+                  "for codec '%s' with transpose=false.",
+                  K, K, c.name);
+    if (n_entries < 0 || M < 0 || N < 0 || K < 0 || n_experts < 0)
+      return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmm] negative size.");
+    if (n_entries == 0 || M == 0 || N == 0) return KQ_OK;
+    if (n_experts == 0) return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmm] no expert matrices.");
+    if (!x || !w || !y || !lhs_indices || !rhs_indices)
+      return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmm] null pointer.");
+    cudaError_t et = kq::launch_qvm_gather(ci, x_dtype, x, x_batch, y, static_cast<const uint8_t*>(w), n_experts,
+                                           w_expert_stride_bytes, (long long)w_row_bytes, M, N, K, lhs_indices,
+                                           rhs_indices, n_entries, static_cast<cudaStream_t>(stream));
+    if (et != cudaSuccess) return cuda_fail("gather_qmm", et);
+    return KQ_OK;
+  }
   if (wpr != K)
     return fail(KQ_ERR_INVALID_ARGUMENT,
                 "[mlx_kquant.gather_qmm] x last dim (%d) does not match the expanded quantized matrix inner dim (%lld) "

@@ -140,6 +140,9 @@ cudaError_t launch_swiglu(int dtype, const void* gate, const void* up, long long
 cudaError_t launch_moe_combine(int dtype, const void* d, const float* probs, long long tokens, int k, int H, void* y,
                                bool y_f32, cudaStream_t st);
 
+cudaError_t launch_qvm_gather(int codec, int x_dtype, const void* x, long long x_batch, void* y, const uint8_t* w,
+                              int n_experts, long long expert_stride, long long row_bytes, int M, int N, int K,
+                              const uint32_t* lhs, const uint32_t* rhs, long long n_entries, cudaStream_t st);
 // transpose == 0 ([K, N] weights, rows quantized along N): streaming CUDA-core kernel (kq_qvm.cu).
 cudaError_t launch_qvm(int codec, int x_dtype, const void* x, long long x_row_stride, void* y, long long y_row_stride,
                        const uint8_t* w, long long row_bytes, int M, int N, int K, cudaStream_t st);

@@ -23,6 +23,13 @@ namespace {
 
 constexpr int kWarps = 8, kThreads = 256, kMT = 4, kMaxSplit = 8, kCols = 256;
 
+struct QvmGather {
+  const uint32_t* lhs;
+  const uint32_t* rhs;   // nullptr = dense call
+  long long entry0, x_batch, expert_stride;
+  int n_experts, m_tiles;
+};
+
 template <typename XT>
 __device__ __forceinline__ float load_x(const XT* p) {
   if constexpr (std::is_same<XT, __half>::value) return __half2float(*p);
@@ -33,7 +40,7 @@ __device__ __forceinline__ float load_x(const XT* p) {
 template <int C, int A, typename XT>
 __global__ void __launch_bounds__(kThreads)
 qvm_kernel(const XT* __restrict__ x, long long x_row_stride, void* __restrict__ y, long long y_row_stride,
-           const uint8_t* __restrict__ w, long long row_bytes, int M, int N, int K) {
+           const uint8_t* __restrict__ w, long long row_bytes, int M, int N, int K, QvmGather gq) {
   using OT = typename std::conditional<std::is_same<XT, __half>::value, __half, __nv_bfloat16>::type;
   constexpr int WPB = wpb_of(C), BPB = bpb_of(C);
   __shared__ float red[kWarps][kMT][kCols];
@@ -48,7 +55,19 @@ qvm_kernel(const XT* __restrict__ x, long long x_row_stride, void* __restrict__ 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int S = gridDim.y, slice = blockIdx.y;
   const int c0 = blockIdx.x * kCols + 8 * lane;  // this lane's eight output columns
-  const int m0 = blockIdx.z * kMT, m = min(kMT, M - m0);
+  int mtile = blockIdx.z;
+  if (gq.rhs != nullptr) {
+    // gather form: grid.z = entries x row tiles; entry e multiplies x[lhs[e]] ([M, K]) by matrix rhs[e] into y[e].
+    // An index out of range leaves the entry's rows unwritten (uniform over the cluster, which spans grid.y only).
+    const long long e = gq.entry0 + blockIdx.z / gq.m_tiles;
+    mtile = blockIdx.z % gq.m_tiles;
+    const uint32_t l = gq.lhs[e], r = gq.rhs[e];
+    if (r >= (uint32_t)gq.n_experts || (long long)l >= gq.x_batch) return;
+    x += (long long)l * M * x_row_stride;
+    w += (long long)r * gq.expert_stride;
+    y = static_cast<OT*>(y) + e * M * y_row_stride;
+  }
+  const int m0 = mtile * kMT, m = min(kMT, M - m0);
   const int per = (K + S - 1) / S;
   const int k0 = min(slice * per, K), k1 = min(k0 + per, K);
 
@@ -106,12 +125,14 @@ qvm_kernel(const XT* __restrict__ x, long long x_row_stride, void* __restrict__ 
 
 template <int C, int A, typename XT>
 cudaError_t launch_one(const void* x, long long x_row_stride, void* y, long long y_row_stride, const uint8_t* w,
-                       long long row_bytes, int M, int N, int K, cudaStream_t st) {
+                       long long row_bytes, int M, int N, int K, cudaStream_t st, QvmGather gq = QvmGather{},
+                       long long entries = 1) {
   const int col_ctas = (N + kCols - 1) / kCols, m_tiles = (M + kMT - 1) / kMT;
   int S = 1;
-  while (S < kMaxSplit && (long long)col_ctas * m_tiles * S < 2 * 148 && K / (S * 2) >= 4 * kWarps) S *= 2;
+  while (S < kMaxSplit && (long long)col_ctas * m_tiles * entries * S < 2 * 148 && K / (S * 2) >= 4 * kWarps) S *= 2;
+  gq.m_tiles = m_tiles;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(col_ctas, S, m_tiles);
+  cfg.gridDim = dim3(col_ctas, S, (unsigned)(m_tiles * entries));
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = 0;
   cfg.stream = st;
@@ -123,16 +144,17 @@ cudaError_t launch_one(const void* x, long long x_row_stride, void* y, long long
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, qvm_kernel<C, A, XT>, static_cast<const XT*>(x), x_row_stride, y, y_row_stride, w,
-                            row_bytes, M, N, K);
+                            row_bytes, M, N, K, gq);
 }
 
 template <int C, int NAT>
 cudaError_t launch_codec(int x_dtype, const void* x, long long x_row_stride, void* y, long long y_row_stride,
-                         const uint8_t* w, long long row_bytes, int M, int N, int K, cudaStream_t st) {
-  const bool aligned = (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (row_bytes & 15) == 0;
-#define KQ_QVM(XT)                                                                                        \
-  return aligned ? launch_one<C, NAT, XT>(x, x_row_stride, y, y_row_stride, w, row_bytes, M, N, K, st)   \
-                 : launch_one<C, 1, XT>(x, x_row_stride, y, y_row_stride, w, row_bytes, M, N, K, st)
+                         const uint8_t* w, long long row_bytes, int M, int N, int K, cudaStream_t st,
+                         QvmGather gq = QvmGather{}, long long entries = 1) {
+  const bool aligned = (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (row_bytes & 15) == 0 && (gq.expert_stride & 15) == 0;
+#define KQ_QVM(XT)                                                                                                    \
+  return aligned ? launch_one<C, NAT, XT>(x, x_row_stride, y, y_row_stride, w, row_bytes, M, N, K, st, gq, entries)  \
+                 : launch_one<C, 1, XT>(x, x_row_stride, y, y_row_stride, w, row_bytes, M, N, K, st, gq, entries)
   if (x_dtype == F16) KQ_QVM(__half);
   if (x_dtype == BF16) KQ_QVM(__nv_bfloat16);
   KQ_QVM(float);
@@ -164,6 +186,41 @@ cudaError_t launch_qvm(int codec, int x_dtype, const void* x, long long x_row_st
   }
 #undef KQ_CASE
   return cudaErrorInvalidValue;
+}
+
+// gather form of the same kernel: entry e is x[lhs[e]] ([M, K]) @ dequant(w[rhs[e]]) ([K, N]) -> y[e] ([M, N])
+cudaError_t launch_qvm_gather(int codec, int x_dtype, const void* x, long long x_batch, void* y, const uint8_t* w,
+                              int n_experts, long long expert_stride, long long row_bytes, int M, int N, int K,
+                              const uint32_t* lhs, const uint32_t* rhs, long long n_entries, cudaStream_t st) {
+  if (M <= 0 || N <= 0 || K <= 0 || n_entries <= 0) return cudaSuccess;
+  const int m_tiles = (M + kMT - 1) / kMT;
+  if (m_tiles > 65535) return cudaErrorInvalidConfiguration;
+  const long long per_launch = 65535 / m_tiles;
+  for (long long e0 = 0; e0 < n_entries; e0 += per_launch) {
+    const long long cnt = n_entries - e0 < per_launch ? n_entries - e0 : per_launch;
+    QvmGather gq{lhs, rhs, e0, x_batch, expert_stride, n_experts, m_tiles};
+    cudaError_t err = cudaErrorInvalidValue;
+#define KQ_CASE(CODEC, NAT) \
+  case CODEC: err = launch_codec<CODEC, NAT>(x_dtype, x, K, y, N, w, row_bytes, M, N, K, st, gq, cnt); break
+    switch (codec) {
+      KQ_CASE(Q2_K, 4);
+      KQ_CASE(Q3_K, 2);
+      KQ_CASE(Q4_K, 16);
+      KQ_CASE(Q5_K, 16);
+      KQ_CASE(Q6_K, 2);
+      KQ_CASE(Q4_0, 2);
+      KQ_CASE(Q8_0, 2);
+      KQ_CASE(IQ4_NL, 2);
+      KQ_CASE(IQ4_XS, 8);
+      KQ_CASE(IQ2_XXS, 2);
+      KQ_CASE(Q4_1, 4);
+      KQ_CASE(Q5_0, 2);
+      KQ_CASE(Q5_1, 8);
+    }
+#undef KQ_CASE
+    if (err != cudaSuccess) return err;
+  }
+  return cudaSuccess;
 }
 
 }  // namespace kq

@@ -122,3 +122,43 @@ class KQuantSwitchLinear(_KQuantBase):
     def extra_repr(self) -> str:
         n, m, b = self.weight.shape
         return f"num_experts={n}, output_dims={m}, bytes_per_row={b}, kquant_type={self.kquant_type}"
+
+
+class KQuantMultiLinear(_KQuantBase):
+    """Per-head batched linear in wire bytes (mlx_kquant/nn.py:271-352), the absorbed-attention up-projections of
+    the deepseek_v3 family: weight [num_heads, out_dims, bytes_per_row], dispatched through `gather_qmm` with the
+    head as the expert index. `forward(x, transpose)`: x is [B, Hx, L, D] with Hx = num_heads (per-head
+    activations) or 1 (one activation shared by all heads); `transpose=True` computes x[..., h, :, :] @ W[h].T,
+    `transpose=False` computes x @ W[h] (contraction over the axis that is not quantized)."""
+
+    def __init__(self, input_dims: int, output_dims: int, num_heads: int, codec: str):
+        super().__init__()
+        self._init_codec(codec)
+        self.num_heads = num_heads
+        self.register_buffer("weight", torch.zeros((num_heads, output_dims, bytes_per_row(codec, input_dims)),
+                                                   dtype=torch.uint8))
+        self._gather_idx = None
+
+    def forward(self, x: torch.Tensor, transpose: bool = True) -> torch.Tensor:
+        nh = self.num_heads
+        B, Hx = x.shape[0], x.shape[1]
+        dev = self.weight.device
+        cached = self._gather_idx
+        if cached is not None and cached[0] == (B, Hx, dev):
+            lhs, rhs = cached[1], cached[2]
+        else:
+            rhs = torch.arange(nh, device=dev).reshape(1, nh).expand(B, nh).contiguous()
+            if Hx == nh:
+                lhs = torch.arange(B * nh, device=dev).reshape(B, nh)
+            elif Hx == 1:
+                lhs = torch.arange(B, device=dev).reshape(B, 1).expand(B, nh).contiguous()
+            else:
+                raise ValueError(f"KQuantMultiLinear: head axis {Hx} is neither 1 nor num_heads={nh} "
+                                 f"(x.shape={tuple(x.shape)})")
+            self._gather_idx = ((B, Hx, dev), lhs, rhs)
+        return kq.gather_qmm(x, self.weight, self.scales, self.kquant_type, lhs_indices=lhs, rhs_indices=rhs,
+                             transpose=transpose)
+
+    def extra_repr(self) -> str:
+        nh, out_dims, bpr = self.weight.shape
+        return f"num_heads={nh}, output_dims={out_dims}, bytes_per_row={bpr}, kquant_type={self.kquant_type}"

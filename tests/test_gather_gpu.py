@@ -137,3 +137,28 @@ def test_out_of_range_expert_ids_are_skipped(oracle, B):
     ref = fp64_ref(oracle, store, "bf16", wire, codec, np.arange(B), rhs)
     assert rel_fro(y_to_f32(good), ref) <= TOL
     assert rel_fro(y_to_f32(y[keep]), ref[~bad]) <= TOL
+
+
+@pytest.mark.parametrize("codec", ["q4_k", "q8_0", "iq4_xs", "q5_1"])
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+def test_gather_transpose_false(oracle, codec, dt):
+    # [K, N] expert matrices: entry e is x[lhs[e]] @ dequant(w[rhs[e]]); an out-of-range expert index is skipped
+    E, K, N, B, M = 3, 40, 512, 5, 2
+    wire = make_experts(codec, E, K, N, seed=81)        # E matrices of K rows, N weights per row
+    wd = torch.from_numpy(wire).cuda()
+    x, store = x_to_torch(np.random.default_rng(82).normal(0, 1, (B, M, K)).astype(np.float32), dt)
+    lhs = np.array([4, 0, 0, 2, 3, 1], np.int64)
+    rhs = np.array([2, 0, 1, 1, 2, 0], np.int64)
+    y = kq.gather_qmm(x, wd, None, codec, lhs_indices=torch.from_numpy(lhs), rhs_indices=torch.from_numpy(rhs),
+                      transpose=False)
+    assert tuple(y.shape) == (6, M, N)
+    xs = to_f32(store, dt).astype(np.float64)
+    Wd = oracle.dequantize(wire, codec, "f32").astype(np.float64)
+    ref = np.stack([xs[l] @ Wd[r] for l, r in zip(lhs, rhs)])
+    assert_close(y_to_f32(y), ref, dt, TOL)
+    rhs_bad = rhs.copy()
+    rhs_bad[1] = E + 1
+    y2 = kq.gather_qmm(x, wd, None, codec, lhs_indices=torch.from_numpy(lhs), rhs_indices=torch.from_numpy(rhs_bad),
+                       transpose=False)
+    keep = [0, 2, 3, 4, 5]
+    assert torch.equal(y2[keep], y[keep])

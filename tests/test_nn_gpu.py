@@ -99,3 +99,27 @@ def test_qmv_bias_is_fused_with_one_rounding(K, dtype):
         kq.quantized_matmul_qmv_bias(x, w, None, bias[:-1], "q8_0")
     with pytest.raises(ValueError):
         kq.quantized_matmul_qmv_bias(x, w, None, bias, "q4_k")
+
+
+@pytest.mark.gpu
+def test_multi_linear_both_orientations():
+    from mlx_kquant_b200.nn import KQuantMultiLinear
+    dev = torch.device("cuda")
+    nh, out_dims, in_dims, B, L = 4, 64, 256, 2, 3
+    ml = KQuantMultiLinear(in_dims, out_dims, nh, "q6_k").to(dev)
+    ml.weight.copy_(random_wire("q6_k", out_dims, in_dims, seed=5, device=dev, lead=(nh,)))
+    W = kq.dequantize(ml.weight.reshape(nh * out_dims, -1), None, "q6_k", torch.float32).reshape(nh, out_dims, in_dims).double()
+    # transpose=True, per-head activations: [B, nh, L, in] @ W[h].T -> [B, nh, L, out]
+    x = torch.randn(B, nh, L, in_dims, device=dev).to(torch.bfloat16)
+    y = ml(x)
+    want = torch.einsum("bhld,hod->bhlo", x.double(), W)
+    assert tuple(y.shape) == (B, nh, L, out_dims)
+    assert float((y.double() - want).norm() / want.norm()) < 4e-3
+    # transpose=False, one activation shared by the heads: [B, 1, L, out] @ W[h] -> [B, nh, L, in]
+    z = torch.randn(B, 1, L, out_dims, device=dev).to(torch.bfloat16)
+    y2 = ml(z, transpose=False)
+    want2 = torch.einsum("blo,hod->bhld", z[:, 0].double(), W)
+    assert tuple(y2.shape) == (B, nh, L, in_dims)
+    assert float((y2.double() - want2).norm() / want2.norm()) < 4e-3
+    with pytest.raises(ValueError):
+        ml(torch.zeros(B, 3, L, in_dims, device=dev, dtype=torch.bfloat16))
