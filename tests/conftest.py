@@ -80,5 +80,14 @@ def assert_close(got, ref, out_dtype: str, tol: float = 2e-3) -> None:
     max error (beyond the output rounding) <= tol, against an fp64-accumulated
     reference of the fp32 math."""
     rf, mx = rel_fro(got, ref), max_rel_to_peak(got, ref, out_dtype)
+    if rf > tol and out_dtype in ("f16", "bf16"):
+        # On ~100 outputs the rounding of an exact result to bfloat16 alone can reach 2.1e-3 (2^-9 / sqrt(3) is
+        # its expectation): measure against the reference rounded the same way before calling it a failure.
+        r32 = np.asarray(ref, dtype=np.float64).astype(np.float32)
+        if out_dtype == "f16":
+            rounded = r32.astype(np.float16).astype(np.float64)
+        else:
+            rounded = kq_oracle.bf16_bits_to_f32(kq_oracle.f32_to_bf16_bits(r32)).astype(np.float64)
+        rf = min(rf, rel_fro(got, rounded))
     assert rf <= tol, f"rel_fro {rf:.3e} > {tol}"
     assert mx <= tol, f"max/peak {mx:.3e} > {tol}"
