@@ -68,6 +68,9 @@ template <> struct Geom<Q8_0> { static constexpr int kCB = 272, kP = 17; };
 template <> struct Geom<IQ4_NL> { static constexpr int kCB = 144, kP = 9; };
 template <> struct Geom<IQ4_XS> { static constexpr int kCB = 136, kP = 9; };
 template <> struct Geom<IQ2_XXS> { static constexpr int kCB = 66, kP = 5; };
+template <> struct Geom<Q4_1> { static constexpr int kCB = 160, kP = 11; };
+template <> struct Geom<Q5_0> { static constexpr int kCB = 176, kP = 11; };
+template <> struct Geom<Q5_1> { static constexpr int kCB = 192, kP = 13; };
 
 // The activations of one chunk for MT rows of x, as the products need them. Row t is t * stride further.
 struct XChunk {
@@ -163,6 +166,38 @@ __device__ __forceinline__ void chunk_dot(const Bytes<PH2> B, const XChunk& X, c
       }
       accum16<false, MT>(lo, 2 * b, d, 8, X, acc);
       accum16<false, MT>(hi, 2 * b + 1, d, 8, X, acc);
+    }
+  } else if constexpr (C == Q4_1 || C == Q5_0 || C == Q5_1) {
+    // eight blocks [f16 d]([f16 m])([u32 qh])[16 B]: nibbles as q4_0; bit i of qh is the fifth bit of weight i
+    // (src/kquant_cpu_decode.cpp:84-153). q5_0 subtracts 16 through the integer sums of x, the codecs with a
+    // minimum add m * sum x through the float sums.
+    constexpr int kBlk = C == Q4_1 ? 20 : (C == Q5_0 ? 22 : 24);
+    constexpr int kQs = C == Q4_1 ? 4 : (C == Q5_0 ? 6 : 8);
+#pragma unroll
+    for (int b = 0; b < 8; b++) {
+      const float d = f16_bits(B.h(kBlk * b));
+      uint32_t qh = 0;
+      if constexpr (C == Q5_0) qh = B.w(kBlk * b + 2);
+      if constexpr (C == Q5_1) qh = B.w(kBlk * b + 4);
+      uint32_t lo[4], hi[4];
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const uint32_t W = B.w(kBlk * b + kQs + 4 * i);
+        lo[i] = W & 0x0f0f0f0fu;
+        hi[i] = (W >> 4) & 0x0f0f0f0fu;
+        if constexpr (C != Q4_1) {
+          // four consecutive bits of qh -> bit 4 of the four bytes
+          lo[i] |= ((((qh >> (4 * i)) & 0xfu) * 0x00204081u) & 0x01010101u) << 4;
+          hi[i] |= ((((qh >> (16 + 4 * i)) & 0xfu) * 0x00204081u) & 0x01010101u) << 4;
+        }
+      }
+      accum16<false, MT>(lo, 2 * b, d, C == Q5_0 ? 16 : 0, X, acc);
+      accum16<false, MT>(hi, 2 * b + 1, d, C == Q5_0 ? 16 : 0, X, acc);
+      if constexpr (C != Q5_0) {
+        const float m = f16_bits(B.h(kBlk * b + 2));
+        accum_min<MT>(2 * b, -m, X, acc);
+        accum_min<MT>(2 * b + 1, -m, X, acc);
+      }
     }
   } else if constexpr (C == IQ4_NL || C == IQ4_XS) {
     // 16 bytes per 32-group: low nibble -> weight i, high nibble -> weight i + 16, through the 16-level
@@ -617,7 +652,6 @@ cudaError_t launch_codec(int x_dtype, const GemvArgs& a, cudaStream_t st) {
 }  // namespace
 
 bool gemv_dp4a_supported(int codec, int x_dtype, const GemvArgs& a) {
-  if (codec == Q4_1 || codec == Q5_0 || codec == Q5_1) return false;  // generic decode kernel only
   if (!a.w_align16 || (a.K & 255) != 0 || a.K > kMaxK || (a.row_bytes & 15) != 0 || a.row_bytes < 16 * 17) return false;
   if (a.tasks != nullptr) {
     // task lists (gather_qmm): rows in slices of four. q4_k with fp16 rows and the two table codecs keep
@@ -652,6 +686,9 @@ cudaError_t launch_gemv_dp4a(int codec, int x_dtype, const GemvArgs& a, cudaStre
     case IQ4_NL: return launch_codec<IQ4_NL>(x_dtype, a, st);
     case IQ4_XS: return launch_codec<IQ4_XS>(x_dtype, a, st);
     case IQ2_XXS: return launch_codec<IQ2_XXS>(x_dtype, a, st);
+    case Q4_1: return launch_codec<Q4_1>(x_dtype, a, st);
+    case Q5_0: return launch_codec<Q5_0>(x_dtype, a, st);
+    case Q5_1: return launch_codec<Q5_1>(x_dtype, a, st);
   }
   return cudaErrorInvalidValue;
 }
