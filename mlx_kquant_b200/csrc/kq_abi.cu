@@ -384,10 +384,6 @@ int kq_device_error_flags(int* flags, int clear) {
   if (flags == nullptr) return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant] kq_device_error_flags: null pointer.");
   cudaError_t e = kq::read_device_error(flags, clear != 0);
   if (e != cudaSuccess) return cuda_fail("device_error_flags", e);
-  int tc = 0;
-  e = kq::read_device_error_tc(&tc, clear != 0);
-  if (e != cudaSuccess) return cuda_fail("device_error_flags", e);
-  *flags |= tc << 8;  // flags of the tensor-memory decode kernel sit one byte up
   return KQ_OK;
 }
 

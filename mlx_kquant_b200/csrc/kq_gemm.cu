@@ -567,15 +567,19 @@ convert_x_kernel(const XT* __restrict__ x, long long x_row_stride, int K, __half
     __syncthreads();
     mx = s_max[0];
     for (int i = 1; i < 8; i++) mx = fmaxf(mx, s_max[i]);
+    // Every row is normalised: its largest magnitude lands in [16384, 32768), so small rows keep their
+    // mantissas instead of turning into fp16 subnormals. The factor 2^-e is applied in two exact halves
+    // (2^-e alone overflows float32 for the smallest bf16 magnitudes).
     int e = 0;
-    if (mx >= 32768.f) e = ilogbf(mx) - 14;  // largest magnitude lands in [16384, 32768)
-    const float down = ldexpf(1.f, -e);
+    if (mx > 0.f) e = ilogbf(mx) - 14;
+    const int eh = (-e) / 2;
+    const float down1 = ldexpf(1.f, eh), down2 = ldexpf(1.f, -e - eh);
     if (threadIdx.x == 0) row_scale[row] = ldexpf(1.f, e);
     for (int k = threadIdx.x; k < K; k += 256) {
       float v;
       if constexpr (sizeof(XT) == 2) v = __bfloat162float(xr[k]);
       else v = __bfloat162float(__float2bfloat16_rn(xr[k]));
-      o[k] = __float2half_rn(v * down);
+      o[k] = __float2half_rn(v * down1 * down2);
     }
   }
 }
@@ -854,6 +858,19 @@ cudaError_t launch_gemm_tiles(int codec, bool out_half, const void* xh, long lon
     case Q5_1: return launch_grouped_codec<Q5_1, 8>(out_half, a, aligned, max_tiles, st);
   }
   return cudaErrorInvalidValue;
+}
+
+// Device address of the error word of the current device, for kernels of other translation units.
+int* device_error_word() {
+  static int* addr[16] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return nullptr;
+  if (addr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_kq_device_error) != cudaSuccess) return nullptr;
+    addr[dev] = static_cast<int*>(p);
+  }
+  return addr[dev];
 }
 
 // Flags raised by kernels that gave up on a bounded wait (0 = none). Synchronises the device.

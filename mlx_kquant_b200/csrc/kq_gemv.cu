@@ -1564,6 +1564,13 @@ cudaError_t launch_gemv(int codec, int x_dtype, const GemvArgs& a, cudaStream_t 
   static const char* int_env = std::getenv("KQ_GEMV_DP4A");  // = 0 switches every integer kernel off
   const bool imma_on = imma_env ? imma_env[0] == '1'
                                 : (!(int_env && int_env[0] == '0') && (long long)a.N * a.K <= (60ll << 20));
+  // A/B lever: KQ_GEMV_STREAM=0 keeps one-wave matrices on the kernels below
+  static const bool stream_on = [] {
+    const char* e = std::getenv("KQ_GEMV_STREAM");
+    return !(e && e[0] == '0');
+  }();
+  if (stream_on && !(int_env && int_env[0] == '0') && gemv_stream_supported(codec, x_dtype, a))
+    return launch_gemv_stream(x_dtype, a, st);
   if (imma_on && gemv_imma_supported(codec, x_dtype, a)) return launch_gemv_imma(x_dtype, a, st);
   // one dense activation row of q4_k: the integer dot-product kernel. A/B lever: KQ_GEMV_DP4A=0|1.
   // Measured: it wins up to ~60 M weights against the fp16 tensor-core kernels below (which win
@@ -1578,8 +1585,6 @@ cudaError_t launch_gemv(int codec, int x_dtype, const GemvArgs& a, cudaStream_t 
   }
   // KQ_GEMV_DP4A=0 also switches the other codecs' integer kernels off
   if (!(dp_env && dp_env[0] == '0') && gemv_dp4a_supported(codec, x_dtype, a)) return launch_gemv_dp4a(codec, x_dtype, a, st);
-  static const char* tc_env = std::getenv("KQ_GEMV_TC");  // A/B lever: 1 = tensor-memory decode kernel
-  if (tc_env && tc_env[0] == '1' && gemv_tc_supported(codec, x_dtype, a)) return launch_gemv_tc(a, st);
   static const bool no_m1 = std::getenv("KQ_GEMV_NO_M1") != nullptr;  // A/B lever
   if (codec == Q4_K && x_dtype == F16 && aligned && a.tasks == nullptr && a.M == 1 && !no_m1) {
     // The cluster-free kernel wins (measured) unless few row groups leave each warp a long K

@@ -52,12 +52,6 @@ struct GemvArgs {
 // on load, output bf16), 1 f16, 2 bf16.
 cudaError_t launch_gemv(int codec, int x_dtype, const GemvArgs& a, cudaStream_t st);
 
-// q4_k, fp16, one or two dense activation rows: the decode kernel on tcgen05 tensor cores with
-// the weights as a tensor-memory operand (kq_gemv_tc.cu).
-bool gemv_tc_supported(int codec, int x_dtype, const GemvArgs& a);
-cudaError_t launch_gemv_tc(const GemvArgs& a, cudaStream_t st);
-cudaError_t read_device_error_tc(int* out, bool clear);
-
 // Up to four activation rows per pass (dense, or task lists in slices of four): products on the
 // integer dot-product pipe over 16-bit quantized activations (kq_gemv_dp4a.cu).
 bool gemv_dp4a_supported(int codec, int x_dtype, const GemvArgs& a);
@@ -90,6 +84,11 @@ cudaError_t launch_gemm_tiles(int codec, bool out_half, const void* xh, long lon
                               cudaStream_t st);
 // Flags raised by kernels that gave up on a bounded wait (0 = none); synchronises the device.
 cudaError_t read_device_error(int* out, bool clear);
+int* device_error_word();  // device address of that flag word on the current device (nullptr on failure)
+
+// q4_k, one dense fp16 / bf16 activation row, matrices of about one wave of CTAs (kq_gemv_stream.cu)
+bool gemv_stream_supported(int codec, int x_dtype, const GemvArgs& a);
+cudaError_t launch_gemv_stream(int x_dtype, const GemvArgs& a, cudaStream_t st);
 // Exact fp16 copy of `rows` activation rows (x_dtype 0 f32 / 1 f16 / 2 bf16) with a per-row power-of-two
 // factor in row_scale (kq_gemm.cu). lhs != nullptr: output row r is x row lhs[r / M] * M + r % M.
 cudaError_t launch_convert_rows(int x_dtype, const void* x, long long x_row_stride, int K, long long rows,

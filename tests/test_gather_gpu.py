@@ -162,3 +162,19 @@ def test_gather_transpose_false(oracle, codec, dt):
                        transpose=False)
     keep = [0, 2, 3, 4, 5]
     assert torch.equal(y2[keep], y[keep])
+
+
+@pytest.mark.parametrize("scale", [1e-6, 1e-9])
+def test_gather_small_magnitude_rows(oracle, scale):
+    """Rows of bfloat16 activations far below fp16's normal range keep their accuracy through the fp16 copy
+    that the q4_k task kernel and the grouped tile kernel read (both regimes: 8 and 600 entries)."""
+    codec, E, N, K = "q4_k", 4, 64, 512
+    wire = make_experts(codec, E, N, K, seed=61)
+    wd = torch.from_numpy(wire).cuda()
+    for B in (8, 600):
+        rng = np.random.default_rng(62 + B)
+        x, store = x_to_torch((rng.normal(0, 1, (B, 1, K)) * scale).astype(np.float32), "bf16")
+        rhs = rng.integers(0, E, B).astype(np.uint32)
+        y = kq.gather_qmm(x, wd, None, codec, rhs_indices=torch.from_numpy(rhs.astype(np.int64)).cuda())
+        ref = fp64_ref(oracle, store.reshape(B, K), "bf16", wire, codec, np.arange(B), rhs)
+        assert_close(y_to_f32(y).reshape(B, N), ref, "bf16", TOL)

@@ -169,3 +169,22 @@ def test_large_activations_do_not_overflow_group_sums(oracle):
     finite = np.abs(ref) < 60000          # outputs beyond fp16's range saturate to inf by definition
     assert np.isfinite(got[finite]).all()
     assert np.abs(got[finite] - ref[finite]).max() <= 2e-3 * np.abs(ref[finite]).max()
+
+
+@pytest.mark.parametrize("dt", ["bf16", "f32"])
+@pytest.mark.parametrize("M", [8, 64])
+@pytest.mark.parametrize("scale", [1e-6, 1e-9, 3e4])
+def test_small_and_large_magnitude_rows(oracle, dt, M, scale):
+    """bfloat16 / float32 rows go through an fp16 copy with a per-row power-of-two factor: rows far below
+    fp16's normal range (and far above it) must come out as accurately as rows of order one. One row of the
+    batch is kept at order one so that the factor is seen to be per row."""
+    rng = np.random.default_rng(500 + M)
+    N, K = 192, 1024
+    wire = mint_wire("q4_k", rng.normal(0, 0.02, (N, K)).astype(np.float32))
+    xf = rng.normal(0, 1, (M, K)).astype(np.float32) * np.float32(scale)
+    xf[M // 2] = rng.normal(0, 1, K).astype(np.float32)
+    x, store = x_to_torch(xf, dt)
+    y = y_to_f32(kq.quantized_matmul(x, torch.from_numpy(wire).cuda(), None, "q4_k"))
+    ref = fp64_ref(oracle, store, dt, wire, "q4_k")
+    for m in range(M):   # row by row: the rows differ by many orders of magnitude
+        check(y[m:m + 1], ref[m:m + 1], "bf16")
