@@ -2,6 +2,7 @@
 """Benchmark of the quantized-weight hot path.
 
     python bench.py --gpus N --steps K --warmup W [--impl reference]
+    python bench.py --case matmul q4_k 4096 4096 1 40        (one op a few times: the driver of profiler captures)
 
 Headline workload (config.workload = "c1_q4k_decode_gemv"): the decode-shape
 Q4_K quantized_matmul of the reference's first benchmark cell - W [4096, 4096]
@@ -18,9 +19,21 @@ value   device-resident: inputs already in HBM, the step is one CUDA-graph
 e2e     the same step through the public op with HOST buffers: pinned-host x
         -> device copy, the launches, device -> pinned-host copy of the outputs,
         all inside the timed region.
-N > 1   weak scaling: every rank holds its own [4096, 4096] column shard (rows
-        r*4096 .. (r+1)*4096 of a [N*4096, 4096] matrix) per layer and the
-        [layers, M, 4096] output shards are all-gathered over NCCL each step.
+extra   (N = 1) the other cells of the metric, each with its roofline fraction
+        and a bounded CPU sample of the reference's own code: the headline
+        shape at M = 8 and as a dependent chain (every launch consumes the
+        output of the one before), dequantize of all ten codecs [14336, 4096]
+        to f16 and f32, prefill of q4_k / q6_k at M = 128 .. 8192, the
+        [28672, 8192] iq4_xs / iq2_xxs decode at M = 1, 4, 16, and the
+        128-expert MoE block at T = 1, 64, 4096.
+N > 1   weak scaling of the headline: every rank holds its own [4096, 4096]
+        column shard (rows r*4096 .. (r+1)*4096 of a [N*4096, 4096] matrix) per
+        layer and the [layers, M, 4096] output shards are all-gathered over
+        NCCL each step. Before timing, the shards' outputs are compared with
+        single-GPU products (`parity_n`). `extra` then carries the sharded
+        cells: [28672, 8192] iq4_xs decode and [14336, 4096] q4_k prefill
+        column-sharded over the FIXED N (strong scaling, with and without the
+        all-gather), and the expert-parallel MoE block.
 --impl reference   times the reference's own CPU implementation of the path
         (oracle/_ref/libkqref.so = its kquant_qmm_cpu compiled in place; the
         oracle's C port if that library is absent) on a bounded sample of the
@@ -50,9 +63,10 @@ CODEC = "q4_k"
 ROW_BYTES = K_COLS // 256 * 144
 MATRIX_BYTES = N_ROWS * ROW_BYTES  # 9 437 184
 # the kernel that runs this workload, and its DRAM bytes per launch from the ncu capture summarised in
-# profiles/gemv_q4k_imma_decode.md (dram__bytes_read.sum + dram__bytes_write.sum)
-ROOFLINE_KERNEL = "gemv_q4k_imma_kernel<__half, 1>"
-ROOFLINE_TRAFFIC = 9470208
+# profiles/gemv_q4k_stream_decode.md (dram__bytes_read.sum + dram__bytes_write.sum)
+ROOFLINE_KERNEL = "gemv_q4k_stream_kernel<__half>"
+ROOFLINE_TRAFFIC = 9486848
+TEN_CODECS = ("q2_k", "q3_k", "q4_k", "q5_k", "q6_k", "q4_0", "q8_0", "iq4_nl", "iq4_xs", "iq2_xxs")
 
 
 def parse():
@@ -65,7 +79,11 @@ def parse():
     ap.add_argument("--m", type=int, default=1, help="activation rows (decode batch), <= 16")
     ap.add_argument("--cpu-sample", type=int, default=16, help="matrices in the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-extra", action="store_true", help="skip the secondary cells (prefill, dequantize, MoE)")
+    ap.add_argument("--no-extra", action="store_true", help="skip the secondary cells")
+    ap.add_argument("--case", nargs="+", default=None,
+                    help="run one op a few times and exit: matmul <codec> N K M launches [f16|bf16] | "
+                         "dequant <codec> rows K dtype launches | gather <codec> N K tokens top_k | "
+                         "moe T (the 128-expert block)")
     return ap.parse_args()
 
 
@@ -121,14 +139,28 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def measured_peak():
+def _peaks() -> dict:
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         try:
-            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+            return json.loads(p.read_text())
         except Exception:
             pass
-    return 6650.0, "fallback"
+    return {}
+
+
+def measured_peak():
+    try:
+        return float(_peaks()["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def measured_tflops():
+    try:
+        return float(_peaks()["bf16_tflops"]), "measured"
+    except Exception:
+        return 1590.0, "fallback"
 
 
 def host_wire(layers: int, seed: int = 0):
@@ -144,18 +176,22 @@ def host_wire(layers: int, seed: int = 0):
     return w.reshape(layers, N_ROWS, ROW_BYTES)
 
 
+def cpu_impl():
+    """The reference's compiled CPU library when present, else the C restatement: (object, kind)."""
+    from oracle import kq_oracle
+
+    if kq_oracle.Ref.available():
+        return kq_oracle.Ref(), "reference"
+    return kq_oracle.Oracle(), "port"
+
+
 def cpu_arm(m: int, sample: int, repeats: int):
     """The reference's CPU path on `sample` matrices; returns (GB/s, kind, cores, seconds per pass)."""
     import numpy as np
 
-    from oracle import kq_oracle
-
     wire = host_wire(sample, seed=1)
     x = np.random.default_rng(2001).normal(0, 1, (m, K_COLS)).astype(np.float16)
-    if kq_oracle.Ref.available():
-        impl, kind = kq_oracle.Ref(), "reference"
-    else:
-        impl, kind = kq_oracle.Oracle(), "port"
+    impl, kind = cpu_impl()
     cores = impl.threads()
     impl.qmm(x, wire[0], CODEC, "f16")  # warm the pool
     best = float("inf")
@@ -173,13 +209,10 @@ def run_reference(args):
         return
     sample = args.cpu_sample
     # each "step" is one pass over the bounded sample
-    t_all = []
     gbs, kind, cores, _ = cpu_arm(args.m, sample, max(1, args.warmup))
     import numpy as np
 
-    from oracle import kq_oracle
-
-    impl = kq_oracle.Ref() if kq_oracle.Ref.available() else kq_oracle.Oracle()
+    impl, _ = cpu_impl()
     wire = host_wire(sample, seed=1)
     x = np.random.default_rng(2001).normal(0, 1, (args.m, K_COLS)).astype(np.float16)
     t0 = time.perf_counter()
@@ -204,98 +237,415 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def measured_tflops():
-    p = ROOT / "MEASURED_PEAKS.json"
-    if p.exists():
-        try:
-            return float(json.loads(p.read_text())["bf16_tflops"]), "measured"
-        except Exception:
-            pass
-    return 1590.0, "fallback"
+# ------------------------------------------------------------------------------------------ timing helpers
+def _events(torch):
+    return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
 
-def extra_cells(dev):
-    """Secondary cells of the metric, single GPU, CUDA events, 5 timed repeats after 2 warm-ups:
-    prefill TFLOP/s (config 3), dequantize GB/s (config 2, q4_k), MoE tokens/s (config 4)."""
+def timed_eager(torch, fn, reps=5, warm=2):
+    """Seconds per call of fn(), CUDA events on the current stream."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = _events(torch)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps * 1e-3
+
+
+def timed_graph(torch, dev, fn, reps=10, warm=3):
+    """Seconds per replay of a CUDA graph that holds one call of fn() (captured on a side stream)."""
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            fn()
+        side.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr, stream=side):
+            keep = fn()
+    torch.cuda.current_stream(dev).wait_stream(side)
+    t = timed_eager(torch, gr.replay, reps=reps, warm=warm)
+    del gr, keep
+    return t
+
+
+def best_of(fn, repeats=3):
+    fn()
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        fn()
+        best = min(best, time.perf_counter() - t0)
+    return best
+
+
+# ------------------------------------------------------------------------------------------ secondary cells
+def extra_cells(dev, with_cpu: bool):
+    """Secondary cells of the metric on one GPU. GPU numbers: CUDA events, warm-ups first, inputs larger than L2
+    or distinct per launch. `cpu`: the reference's CPU code on a bounded sample of the same cell (host threads)."""
+    import numpy as np
     import torch
 
     import mlx_kquant_b200 as kq
+    from mlx_kquant_b200 import _lib
     from mlx_kquant_b200.moe import fuse_gate_up, moe_glu, route_topk
     from mlx_kquant_b200.synth import random_wire
 
-    def timed(fn, reps=5):
-        for _ in range(2):
-            fn()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(reps):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / reps * 1e-3
-
     out = {}
-    peak_tf, kind = measured_tflops()
-    hbm, _ = measured_peak()
+    peak_tf, tf_kind = measured_tflops()
+    hbm, hbm_kind = measured_peak()
+    impl = kind = None
+    cores = 0
+    if with_cpu:
+        try:
+            impl, kind = cpu_impl()
+            cores = impl.threads()
+        except Exception:
+            impl = None
+    L = _lib.lib()
+
+    def cpu_cell(seconds, units, unit, sample):
+        return {"value": units / seconds, "unit": unit, "cores": cores, "kind": kind, "sample": sample}
+
+    # ---- config 1 at M = 8, and as a dependent chain (launch i reads what launch i - 1 wrote)
+    layers = 64
+    W = random_wire(CODEC, N_ROWS, K_COLS, seed=1000, device=dev, lead=(layers,))
+    g = torch.Generator(device="cpu").manual_seed(2008)
+    x8 = torch.randn(8, K_COLS, generator=g).to(torch.float16).to(dev)
+    y8 = torch.empty(layers, 8, N_ROWS, dtype=torch.float16, device=dev)
+
+    def launch(xp, M, wp, yp, s):
+        _lib.check(L.kq_quantized_matmul(xp, _lib.KQ_F16, M, K_COLS, K_COLS, wp, ROW_BYTES, N_ROWS, CODEC.encode(), 1,
+                                         yp, N_ROWS, None, 0, s))
+
+    def c1_m8():
+        s = torch.cuda.current_stream(dev).cuda_stream
+        for i in range(layers):
+            launch(x8.data_ptr(), 8, W[i].data_ptr(), y8[i].data_ptr(), s)
+
+    t = timed_graph(torch, dev, c1_m8) / layers
+    gbs = MATRIX_BYTES / t / 1e9
+    out["c1_q4k_m8"] = {"GBps": gbs, "us_per_launch": t * 1e6, "frac_of_hbm_peak": gbs / hbm, "peak_kind": hbm_kind}
+    if impl is not None:
+        wh = W[:4].cpu().numpy()
+        xh = x8.cpu().numpy()
+        secs = best_of(lambda: [impl.qmm(xh, wh[i], CODEC, "f16") for i in range(4)])
+        out["c1_q4k_m8"]["cpu"] = cpu_cell(secs, 4 * MATRIX_BYTES / 1e9, "GB/s", "4 of the 64 matrices, M = 8")
+    # chain: super-scale d = 6.1e-5 and dmin = 7.5 d give zero-mean weights of gain ~1 per product, so that 64
+    # products in a row stay inside fp16; the buffers between the launches are cleared at the start of every
+    # replay, so a launch that reads ahead of its producer does not find last replay's values
+    Wc = W.clone().view(layers, N_ROWS, K_COLS // 256, 144)
+    for off, val in ((0, 6.1e-5), (2, 4.575e-4)):
+        b = torch.tensor([val], dtype=torch.float16).view(torch.uint8).to(dev)
+        Wc[..., off] = b[0]
+        Wc[..., off + 1] = b[1]
+    Wc = Wc.view(layers, N_ROWS, ROW_BYTES)
+    ych = torch.empty(layers + 1, 1, N_ROWS, dtype=torch.float16, device=dev)
+    ych[0] = torch.randn(1, K_COLS, generator=g).to(torch.float16).to(dev)
+
+    def c1_chain():
+        s = torch.cuda.current_stream(dev).cuda_stream
+        ych[1:].zero_()
+        for i in range(layers):
+            launch(ych[i].data_ptr(), 1, Wc[i].data_ptr(), ych[i + 1].data_ptr(), s)
+
+    t = timed_graph(torch, dev, c1_chain) / layers
+    gbs = MATRIX_BYTES / t / 1e9
+    out["c1_q4k_m1_dependent_chain"] = {
+        "GBps": gbs, "us_per_launch": t * 1e6, "frac_of_hbm_peak": gbs / hbm, "peak_kind": hbm_kind,
+        "note": "every launch consumes the preceding launch's output: its products cannot start before that "
+                "launch has finished, only its weight stream overlaps",
+        "finite": bool(torch.isfinite(ych[-1]).all().item()), "last_rms": float(ych[-1].float().pow(2).mean().sqrt())}
+    del W, Wc, y8, ych
+
+    # ---- config 2: dequantize [14336, 4096], all ten codecs, to f16 and f32 (wire + output > L2 per call)
     N, K = 14336, 4096
+    for codec in TEN_CODECS:
+        Wq = random_wire(codec, N, K, seed=4, device=dev, lead=(2,))
+        wire_bytes = Wq[0].numel()
+        cell = {}
+        for dt, tdt, nbytes in (("f16", torch.float16, 2), ("f32", torch.float32, 4)):
+            def dq():
+                kq.dequantize(Wq[0], None, codec, tdt)
+                kq.dequantize(Wq[1], None, codec, tdt)
+            t = timed_eager(torch, dq) / 2
+            gbs = (wire_bytes + N * K * nbytes) / t / 1e9
+            cell[dt] = {"GBps": gbs, "frac_of_hbm_peak": gbs / hbm}
+        if impl is not None:
+            wh = Wq[0, :2048].cpu().numpy()
+            secs = best_of(lambda: impl.dequantize(wh, codec, "f16"))
+            cell["cpu"] = cpu_cell(secs, (wh.size + 2048 * K * 2) / 1e9, "GB/s", "2048 of the 14336 rows, to f16")
+        cell["peak_kind"] = hbm_kind
+        out[f"c2_dequant_{codec}"] = cell
+        del Wq
+    out["dequant_q4k_f16"] = {"GBps": out["c2_dequant_q4_k"]["f16"]["GBps"],
+                              "frac_of_hbm_peak": out["c2_dequant_q4_k"]["f16"]["frac_of_hbm_peak"]}
+
+    # ---- config 3: prefill [14336, 4096], bf16 rows
     for codec in ("q4_k", "q6_k"):
-        W = random_wire(codec, N, K, seed=3, device=dev)
-        for M in (512, 8192):
+        Wq = random_wire(codec, N, K, seed=3, device=dev)
+        for M in (128, 512, 2048, 8192):
             x = torch.randn(M, K, device=dev).to(torch.bfloat16)
-            t = timed(lambda: kq.quantized_matmul(x, W, None, codec))
+            t = timed_eager(torch, lambda: kq.quantized_matmul(x, Wq, None, codec), reps=8 if M <= 512 else 5)
             tf = 2.0 * M * N * K / t / 1e12
             out[f"prefill_{codec}_m{M}_bf16"] = {"tflops": tf, "ms": t * 1e3, "frac_of_bf16_peak": tf / peak_tf,
-                                                  "peak_kind": kind}
-    W = random_wire("q4_k", N, K, seed=4, device=dev, lead=(4,))       # 4 x 150 MB of traffic > L2
-    def dq():
-        for i in range(4):
-            kq.dequantize(W[i], None, "q4_k", torch.float16)
-    t = timed(dq) / 4
-    gbs = (W[0].numel() + N * K * 2) / t / 1e9
-    out["dequant_q4k_f16"] = {"GBps": gbs, "frac_of_hbm_peak": gbs / hbm}
-    # MoE: 128 experts, hidden 2048, expert FFN 768, top-8
+                                                  "peak_kind": tf_kind}
+        if impl is not None:
+            wh = Wq[:1024].cpu().numpy()
+            xh = torch.randn(128, K).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+            secs = best_of(lambda: impl.qmm(xh, wh, codec, "bf16"), repeats=2)
+            out[f"prefill_{codec}_m128_bf16"]["cpu"] = cpu_cell(
+                secs, 2.0 * 128 * 1024 * K / 1e12, "TFLOP/s", "1024 of the 14336 weight rows, M = 128")
+        del Wq
+
+    # ---- config 5: 70B-class decode [28672, 8192], fp16 rows; distinct matrices in turn (> L2 between reuses)
+    N5, K5 = 28672, 8192
+    for codec, copies in (("iq4_xs", 2), ("iq2_xxs", 3)):
+        Wq = random_wire(codec, N5, K5, seed=5, device=dev, lead=(copies,))
+        wire_bytes = Wq[0].numel()
+        for M in (1, 4, 16):
+            x = torch.randn(M, K5, device=dev).to(torch.float16)
+
+            def c5():
+                return [kq.quantized_matmul(x, Wq[i % copies], None, codec) for i in range(2 * copies)]
+            t = timed_graph(torch, dev, c5) / (2 * copies)
+            gbs = wire_bytes / t / 1e9
+            out[f"c5_{codec}_m{M}"] = {"GBps": gbs, "us_per_launch": t * 1e6, "frac_of_hbm_peak": gbs / hbm,
+                                       "peak_kind": hbm_kind}
+        if impl is not None:
+            wh = Wq[0, :4096].cpu().numpy()
+            xh = torch.randn(1, K5).to(torch.float16).numpy()
+            secs = best_of(lambda: impl.qmm(xh, wh, codec, "f16"))
+            out[f"c5_{codec}_m1"]["cpu"] = cpu_cell(secs, wh.size / 1e9, "GB/s", "4096 of the 28672 rows, M = 1")
+        del Wq
+
+    # ---- config 4: MoE block, 128 experts, hidden 2048, expert FFN 768, top-8
     E, H, F, k = 128, 2048, 768, 8
     wg = random_wire("q4_k", F, H, seed=5, device=dev, lead=(E,))
     wu = random_wire("q4_k", F, H, seed=6, device=dev, lead=(E,))
     wd = random_wire("q4_k", H, F, seed=7, device=dev, lead=(E,))
     wgu = fuse_gate_up(wg, wu)  # gate | up of every expert as one [E, 2F, bytes] stack: a load-time layout choice
+    del wg, wu
     g = torch.Generator(device="cpu").manual_seed(3000)
-    for T in (1, 64, 4096):
+    for T in (1, 64, 512, 4096):
         x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(dev)
         ids, probs = route_topk(torch.randn(T, E, generator=g).to(dev), k)
-        t = timed(lambda: moe_glu(x, None, None, wd, "q4_k", ids, probs, w_gate_up=wgu), reps=3)
-        out[f"moe_glu_q4k_T{T}"] = {"tokens_per_s": T / t, "ms": t * 1e3}
+        fn = lambda: moe_glu(x, None, None, wd, "q4_k", ids, probs, w_gate_up=wgu)
+        t = timed_eager(torch, fn, reps=3)
+        cell = {"tokens_per_s": T / t, "ms": t * 1e3}
         # the same block replayed from a CUDA graph (no host sync inside it): what a serving loop pays
         try:
-            side = torch.cuda.Stream(dev)
-            side.wait_stream(torch.cuda.current_stream(dev))
-            with torch.cuda.stream(side):
-                for _ in range(2):
-                    moe_glu(x, None, None, wd, "q4_k", ids, probs, w_gate_up=wgu)
+            tg = timed_graph(torch, dev, fn, reps=5)
+            cell["graph_tokens_per_s"] = T / tg
+            cell["graph_ms"] = tg * 1e3
+            experts = int(torch.unique(ids).numel())
+            if T <= 64:   # weight-streaming regime
+                cell["frac_of_hbm_peak"] = experts * 2654208 / tg / 1e9 / hbm
+            else:
+                cell["frac_of_bf16_peak"] = T * 75497472 / tg / 1e12 / peak_tf
+        except Exception as e:  # capture is an optimisation of the caller, not part of the op
+            cell["graph_error"] = str(e)[:120]
+            torch.cuda.synchronize()
+        out[f"moe_glu_q4k_T{T}"] = cell
+    return out
+
+
+# ------------------------------------------------------------------------------------------ N > 1
+def parity_n(dev, rank, world, W0, x_dev, y0):
+    """Correctness at N > 1, before anything is timed. Dense: every rank's output shard of layer 0 equals,
+    bit for bit, the product of that shard computed alone on rank 0 (same kernel, K is not split), and agrees
+    with the matching slice of the product with the whole [world * 4096, 4096] matrix. MoE: both
+    expert-parallel forms against the single-GPU block on the same tokens."""
+    import torch
+    import torch.distributed as dist
+
+    import mlx_kquant_b200 as kq
+    from mlx_kquant_b200.dist import shard_bounds
+    from mlx_kquant_b200.moe import GatheredExpertParallel, fuse_gate_up, moe_glu, moe_glu_expert_parallel, route_topk
+    from mlx_kquant_b200.synth import random_wire
+
+    problems = []
+    shards = [torch.empty_like(W0) for _ in range(world)]
+    dist.all_gather(shards, W0.contiguous())
+    ys = [torch.empty_like(y0) for _ in range(world)]
+    dist.all_gather(ys, y0.contiguous())
+    if rank == 0:
+        full = kq.quantized_matmul(x_dev, torch.cat(shards, dim=0), None, CODEC).float()
+        for r in range(world):
+            alone = kq.quantized_matmul(x_dev, shards[r], None, CODEC)
+            if not torch.equal(alone, ys[r]):
+                problems.append(f"dense shard {r}: not bit-identical to the single-GPU product of that shard")
+            sl = full[:, r * N_ROWS:(r + 1) * N_ROWS]
+            err = float((ys[r].float() - sl).norm() / sl.norm())
+            if not err <= 2e-3:
+                problems.append(f"dense shard {r}: rel error {err:.2e} against the full-matrix product")
+    del shards
+
+    # MoE: T = 64 tokens per rank
+    E, H, F, k, T = 128, 2048, 768, 8, 64
+    lo, hi = shard_bounds(E, rank, world)
+    wg = random_wire("q4_k", F, H, seed=50 + rank, device=dev, lead=(hi - lo,))
+    wu = random_wire("q4_k", F, H, seed=60 + rank, device=dev, lead=(hi - lo,))
+    wd = random_wire("q4_k", H, F, seed=70 + rank, device=dev, lead=(hi - lo,))
+    wgu = fuse_gate_up(wg, wu)
+    g = torch.Generator(device="cpu").manual_seed(3100 + rank)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(dev)
+    ids, probs = route_topk(torch.randn(T, E, generator=g).to(dev), k)
+    y_a2a = moe_glu_expert_parallel(x, None, None, wd, "q4_k", ids, probs, E, w_gate_up=wgu)
+    ep = GatheredExpertParallel(T, H, k, E, wgu, wd, "q4_k")
+    y_gat = ep(x, ids, probs).clone()
+    del ep
+
+    def gather(t):
+        parts = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(parts, t.contiguous())
+        return parts
+
+    same = (hi - lo) * world == E   # equal shards: the stacks can be all-gathered as they are
+    if same:
+        all_wgu, all_wd = torch.cat(gather(wgu), 0), torch.cat(gather(wd), 0)
+        all_x, all_ids, all_p = gather(x), gather(ids), gather(probs)
+        all_a, all_g = gather(y_a2a), gather(y_gat.to(y_a2a.dtype))
+        if rank == 0:
+            for r in range(world):
+                ref = moe_glu(all_x[r], None, None, all_wd, "q4_k", all_ids[r], all_p[r], w_gate_up=all_wgu).float()
+                for name, got in (("all-to-all", all_a[r]), ("gathered", all_g[r])):
+                    err = float((got.float() - ref).norm() / ref.norm())
+                    if not err <= 6e-3:
+                        problems.append(f"MoE {name} form, rank {r}: rel error {err:.2e} against the single-GPU block")
+    flag = torch.tensor([len(problems)], device=dev)
+    dist.broadcast(flag, 0)
+    if rank == 0 and problems:
+        raise AssertionError("; ".join(problems))
+    if int(flag.item()):
+        raise AssertionError("parity at N > 1 failed on rank 0")
+    return "ok"
+
+
+def sharded_cells(dev, rank, world):
+    """Strong scaling of the sharded configurations: the FIXED matrix is column-sharded over the ranks.
+    Device time, max over ranks; `gather` adds the NCCL all-gather of the output shards."""
+    import torch
+    import torch.distributed as dist
+
+    import mlx_kquant_b200 as kq
+    from mlx_kquant_b200.dist import shard_bounds
+    from mlx_kquant_b200.synth import random_wire
+
+    out = {}
+    hbm, _ = measured_peak()
+    peak_tf, _ = measured_tflops()
+
+    def max_ms(ms):
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def run(fn, reps):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = _events(torch)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return max_ms(e0.elapsed_time(e1) / reps)
+
+    from mlx_kquant_b200 import _lib
+    L = _lib.lib()
+
+    def abi_matmul(x, Wm, codec, ybuf, ws):
+        """The C-ABI call writing straight into the (wider) gather buffer: no copy between product and collective."""
+        code = _lib.KQ_F16 if x.dtype == torch.float16 else _lib.KQ_BF16
+        _lib.check(L.kq_quantized_matmul(x.data_ptr(), code, x.shape[0], x.shape[1], x.stride(0), Wm.data_ptr(),
+                                         Wm.shape[1], Wm.shape[0], codec.encode(), 1, ybuf.data_ptr(), ybuf.stride(0),
+                                         ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+                                         torch.cuda.current_stream(dev).cuda_stream))
+
+    def graphs_of(fns):
+        """One CUDA graph per callable (captured on a side stream)."""
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        out_g = []
+        with torch.cuda.stream(side):
+            for fn in fns:
+                fn()
                 side.synchronize()
                 gr = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(gr, stream=side):
-                    y_cap = moe_glu(x, None, None, wd, "q4_k", ids, probs, w_gate_up=wgu)
-            torch.cuda.current_stream(dev).wait_stream(side)
-            tg = timed(gr.replay, reps=5)
-            out[f"moe_glu_q4k_T{T}"]["graph_tokens_per_s"] = T / tg
-            out[f"moe_glu_q4k_T{T}"]["graph_ms"] = tg * 1e3
-            del gr, y_cap
-        except Exception as e:  # capture is an optimisation of the caller, not part of the op
-            out[f"moe_glu_q4k_T{T}"]["graph_error"] = str(e)[:120]
-            torch.cuda.synchronize()
+                    fn()
+                out_g.append(gr)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        return out_g
+
+    # config 5: iq4_xs [28672, 8192], M = 1, fp16; four copies of the shard in turn (together larger than L2)
+    N5, K5 = 28672, 8192
+    lo, hi = shard_bounds(N5, rank, world)
+    copies = 4
+    Wq = random_wire("iq4_xs", hi - lo, K5, seed=500 + rank, device=dev, lead=(copies,))
+    shard_bytes = Wq[0].numel()
+    x = torch.randn(1, K5, device=dev, generator=torch.Generator(device=dev).manual_seed(5)).to(torch.float16)
+    widest = (N5 + world - 1) // world
+    ybuf = torch.zeros(1, widest, dtype=torch.float16, device=dev)
+    yall = torch.empty(world, widest, dtype=torch.float16, device=dev)
+    gs = graphs_of([(lambda i=i: abi_matmul(x, Wq[i], "iq4_xs", ybuf, None)) for i in range(copies)])
+    state = {"i": 0}
+
+    def c5(gather):
+        i = state["i"] = (state["i"] + 1) % copies
+        gs[i].replay()
+        if gather:
+            dist.all_gather_into_tensor(yall, ybuf)
+
+    for gather in (False, True):
+        ms = run(lambda: c5(gather), 40)
+        gbs = shard_bytes / (ms * 1e-3) / 1e9
+        out[f"c5_iq4_xs_m1_shard{world}" + ("_gather" if gather else "")] = {
+            "per_gpu_GBps": gbs, "aggregate_GBps": gbs * world, "us": ms * 1e3, "frac_of_hbm_peak": gbs / hbm,
+            "rows_per_rank": hi - lo}
+    del gs, Wq
+
+    # config 3: q4_k [14336, 4096], M = 512, bf16
+    N3, K3, M = 14336, 4096, 512
+    lo, hi = shard_bounds(N3, rank, world)
+    Wq = random_wire("q4_k", hi - lo, K3, seed=300 + rank, device=dev)
+    x = torch.randn(M, K3, device=dev, generator=torch.Generator(device=dev).manual_seed(3)).to(torch.bfloat16)
+    widest = (N3 + world - 1) // world
+    ybuf = torch.zeros(M, widest, dtype=torch.bfloat16, device=dev)
+    yall = torch.empty(world * M, widest, dtype=torch.bfloat16, device=dev)
+    ws = torch.empty(max(1, L.kq_quantized_matmul_workspace_bytes(_lib.KQ_BF16, M, K3)), dtype=torch.uint8, device=dev)
+    g3 = graphs_of([lambda: abi_matmul(x, Wq, "q4_k", ybuf, ws)])[0]
+
+    def c3(gather):
+        g3.replay()
+        if gather:
+            dist.all_gather_into_tensor(yall, ybuf)
+
+    for gather in (False, True):
+        ms = run(lambda: c3(gather), 20)
+        tf = 2.0 * M * (hi - lo) * K3 / (ms * 1e-3) / 1e12
+        out[f"prefill_q4_k_m512_shard{world}" + ("_gather" if gather else "")] = {
+            "per_gpu_tflops": tf, "aggregate_tflops": 2.0 * M * N3 * K3 / (ms * 1e-3) / 1e12, "us": ms * 1e3,
+            "frac_of_bf16_peak": tf / peak_tf, "rows_per_rank": hi - lo}
+    del g3
     return out
 
 
 def moe_ep_cell(dev, rank, world):
-    """MoE SwiGLU block, 128 experts partitioned over the ranks, all-to-all dispatch and combine over
-    NCCL; weak scaling: T = 4096 tokens per rank. Device time, max over ranks."""
+    """MoE SwiGLU block, 128 experts partitioned over the ranks; weak scaling: T tokens per rank. Device time,
+    max over ranks. Two forms: all-to-all dispatch and combine, and the fixed-shape gathered form."""
     import torch
     import torch.distributed as dist
 
     from mlx_kquant_b200.dist import shard_bounds
-    from mlx_kquant_b200.moe import fuse_gate_up, moe_glu_expert_parallel, route_topk
+    from mlx_kquant_b200.moe import GatheredExpertParallel, fuse_gate_up, moe_glu_expert_parallel, route_topk
     from mlx_kquant_b200.synth import random_wire
 
     E, H, F, k, T = 128, 2048, 768, 8, 4096
@@ -307,12 +657,13 @@ def moe_ep_cell(dev, rank, world):
     x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(dev)
     ids, probs = route_topk(torch.randn(T, E, generator=g).to(dev), k)
     wgu = fuse_gate_up(wg, wu)
+    del wg, wu
     fn = lambda: moe_glu_expert_parallel(x, None, None, wd, "q4_k", ids, probs, E, w_gate_up=wgu)
     for _ in range(2):
         fn()
     torch.cuda.synchronize()
     dist.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0, e1 = _events(torch)
     e0.record()
     reps = 3
     for _ in range(reps):
@@ -325,8 +676,6 @@ def moe_ep_cell(dev, rank, world):
     out = {f"moe_glu_q4k_ep{world}_T4096_per_rank": {"tokens_per_s": world * T / (ms * 1e-3), "ms": ms,
                                                       "experts_per_rank": hi - lo}}
     # fixed-shape form (all-gather, local experts as a CUDA graph, reduce-scatter): no host read inside a step
-    from mlx_kquant_b200.moe import GatheredExpertParallel
-
     for Tg in (64, 4096):
         ep = GatheredExpertParallel(Tg, H, k, E, wgu, wd, "q4_k")
         xg, idg, prg = x[:Tg].contiguous(), ids[:Tg].contiguous(), probs[:Tg].contiguous()
@@ -349,6 +698,59 @@ def moe_ep_cell(dev, rank, world):
     return out
 
 
+# ------------------------------------------------------------------------------------------ single cases
+def run_case(argv):
+    """One op a few times on synthetic inputs: what profiler captures are taken from."""
+    import torch
+
+    import mlx_kquant_b200 as kq
+    from mlx_kquant_b200.synth import random_wire
+
+    DT = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}
+    what = argv[0]
+    if what == "matmul":
+        codec = argv[1]
+        N, K, M, launches = (int(v) for v in argv[2:6])
+        dt = DT[argv[6]] if len(argv) > 6 else torch.float16
+        W = random_wire(codec, N, K, seed=1, lead=(launches,))
+        x = torch.randn(M, K, device="cuda").to(dt)
+        for i in range(launches):
+            y = kq.quantized_matmul(x, W[i], None, codec)
+    elif what == "dequant":
+        codec = argv[1]
+        rows, K = int(argv[2]), int(argv[3])
+        dt, launches = DT[argv[4]], int(argv[5])
+        W = random_wire(codec, rows, K, seed=2, lead=(launches,))
+        for i in range(launches):
+            y = kq.dequantize(W[i], None, codec, dt)
+    elif what == "gather":
+        codec = argv[1]
+        N, K, T, top_k = (int(v) for v in argv[2:6])
+        W = random_wire(codec, N, K, seed=3, lead=(128,))
+        x = torch.randn(T, 1, K, device="cuda").to(torch.bfloat16)
+        idx = torch.randint(0, 128, (T, top_k), device="cuda")
+        y = kq.gather_qmm(x, W, None, codec, lhs_indices=torch.arange(T, device="cuda")[:, None].expand(T, top_k),
+                          rhs_indices=idx)
+    elif what == "moe":
+        from mlx_kquant_b200.moe import fuse_gate_up, moe_glu, route_topk
+
+        T = int(argv[1])
+        E, H, F, k = 128, 2048, 768, 8
+        wgu = fuse_gate_up(random_wire("q4_k", F, H, seed=5, lead=(E,)), random_wire("q4_k", F, H, seed=6, lead=(E,)))
+        wd = random_wire("q4_k", H, F, seed=7, lead=(E,))
+        x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+        ids, probs = route_topk(torch.randn(T, E, device="cuda"), k)
+        for _ in range(3):
+            y = moe_glu(x, None, None, wd, "q4_k", ids, probs, w_gate_up=wgu)
+    else:
+        print(__doc__)
+        return 2
+    torch.cuda.synchronize()
+    print("ok", tuple(y.shape), float(y.float().abs().mean()))
+    return 0
+
+
+# ------------------------------------------------------------------------------------------ headline
 def run_b200(args):
     import torch
     import torch.distributed as dist
@@ -362,7 +764,9 @@ def run_b200(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        os.environ.pop("NCCL_DEBUG", None)  # NCCL's version banner would share stdout with the one JSON line
+        # NCCL's own log (when NCCL_DEBUG asks for one) goes to stderr: stdout carries the one JSON line
+        if os.environ.get("NCCL_DEBUG") and not os.environ.get("NCCL_DEBUG_FILE"):
+            os.environ["NCCL_DEBUG_FILE"] = "/dev/stderr"
         dist.init_process_group("nccl", device_id=dev)
 
     layers, M = args.layers, args.m
@@ -393,6 +797,9 @@ def run_b200(args):
         ref0 = kq.quantized_matmul(x_dev, W[0], None, CODEC)
     stream.synchronize()
     assert torch.equal(ref0, y_dev[0]), "C-ABI launch and public op disagree"
+    parity = None
+    if world > 1:
+        parity = parity_n(dev, rank, world, W[0], x_dev, y_dev[0])
 
     # ---- device-resident arm: one CUDA graph of `layers` launches (one graph per output buffer)
     def capture(yb, with_copies):
@@ -485,13 +892,18 @@ def run_b200(args):
         except Exception as e:  # the checker is optional for timing; say why it is missing
             cpu = {"value": None, "unit": "GB/s", "cores": 0, "kind": "port", "sample": f"unavailable: {e}"}
 
-    # expert-parallel MoE (config 4) at N > 1: every rank brings T = 4096 tokens, experts are partitioned
-    ep = None
-    if world > 1 and not args.no_extra:
+    del graphs, graphs_e2e, W, y_devs, y_alls
+    torch.cuda.empty_cache()
+    extra = None
+    if not args.no_extra:
         try:
-            ep = moe_ep_cell(dev, rank, world)
+            if world > 1:
+                extra = sharded_cells(dev, rank, world)
+                extra.update(moe_ep_cell(dev, rank, world))
+            elif rank == 0:
+                extra = extra_cells(dev, with_cpu=not args.no_cpu_baseline)
         except Exception as e:
-            ep = {"error": str(e)[:200]}
+            extra = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
 
     if rank == 0:
         line = {
@@ -507,17 +919,17 @@ def run_b200(args):
             "gpu_launches": args.steps * layers,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_kind": peak_kind, "traffic": ROOFLINE_TRAFFIC, "kernel": ROOFLINE_KERNEL,
-                         "algorithmic_bytes_per_launch": MATRIX_BYTES},
+                         "algorithmic_bytes_per_launch": MATRIX_BYTES,
+                         "note": "all launches of a step read the same activations, so each launch multiplies while "
+                                 "the launch before it still runs; extra.c1_q4k_m1_dependent_chain is the same "
+                                 "kernel when every launch has to wait for the output of the one before"},
             "cpu_baseline": cpu,
             "clocks": clocks,
         }
-        if world == 1 and not args.no_extra:
-            try:
-                line["extra"] = extra_cells(dev)
-            except Exception as e:
-                line["extra"] = {"error": str(e)[:200]}
-        if world > 1 and ep is not None:
-            line["extra"] = ep
+        if parity is not None:
+            line["parity_n"] = parity
+        if extra is not None:
+            line["extra"] = extra
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -525,6 +937,8 @@ def run_b200(args):
 
 def main():
     args = parse()
+    if args.case:
+        sys.exit(run_case(args.case))
     if args.impl == "reference":
         run_reference(args)
     else:
