@@ -126,7 +126,10 @@ KQ_API int kq_device_error_flags(int* flags, int clear);
  * completes on the stream. Decode-sized calls need a few hundred KB; prefill-sized
  * ones (32 or more rows per expert on average) also hold an expert-sorted fp16 copy
  * of the routed activations (n_entries * M * K * 2 bytes) for the tensor-core kernel.
- * K = 0 returns the decode-regime size, which does not depend on K. */
+ * The size depends on K (the fp16 copy): pass the call's own K. K = 0 returns the size of the grouping
+ * scratch alone, which is what kq_gather_qmm_noalloc needs; kq_gather_qmm rejects a workspace of that size.
+ * Entries whose rhs index is >= n_experts or whose lhs index is >= x_batch are skipped: their rows of y stay
+ * unwritten (the reference checks neither). n_entries * M must stay below 2^31. */
 KQ_API size_t kq_gather_qmm_workspace_bytes(long long n_entries, int M, int n_experts, int K);
 KQ_API int kq_gather_qmm(const void* x, int x_dtype, long long x_batch, int M, int K, const void* w, int n_experts,
                   long long w_expert_stride_bytes, size_t w_row_bytes, int N, const char* kquant_type,
@@ -164,10 +167,15 @@ KQ_API int kq_moe_combine_f32(const void* d, const float* probs, long long token
  * allocations afterwards, or a serving loop that must never pay cudaMalloc's
  * device-wide synchronisation. Nothing here calls cudaMalloc, cudaFree or an
  * allocating library routine.
- *  - Always runs the decode regime, whatever the size of the call.
- *  - Limit: problems whose kq_gather_qmm_workspace_bytes(n_entries, M, n_experts, 0)
- *    exceeds KQ_GATHER_STATIC_WS_BYTES are rejected with KQ_ERR_INVALID_ARGUMENT (for
- *    M = 1 and 128 experts that is about 75 000 index entries per call).
+ *  - Always runs the decode regime, whatever the size of the call, and without the fp16 copy of the rows
+ *    that kq_gather_qmm makes for q4_k with bfloat16 / float32 activations: those calls take the slower
+ *    kernels that read such rows directly.
+ *  - Limit (transpose != 0 only; the [K, N] orientation needs no scratch): the grouping scratch of the call -
+ *    counters per expert, an index per entry and a 144-byte task per 16 rows of every expert, about
+ *    14 bytes per entry plus 0.4 KB per expert at M = 1 - must fit KQ_GATHER_STATIC_WS_BYTES, else the call is
+ *    rejected with KQ_ERR_INVALID_ARGUMENT after the ordinary argument checks (for M = 1 and 128 experts that
+ *    is about 75 000 index entries per call). kq_gather_qmm_workspace_bytes(n_entries, M, n_experts, 0) is the
+ *    number compared with the limit.
  *  - The first call on each device looks up the array's device address; make
  *    that first call outside any stream capture.
  *  - All calls on a device share the one array (it keeps the previous call's

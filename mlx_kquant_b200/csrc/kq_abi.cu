@@ -2,6 +2,7 @@
 // with the reference op layer's rules and message texts (src/kquant_ops.cpp),
 // regime selection, and kernel launches. No allocation happens here.
 #include <cstdarg>
+#include <climits>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -398,7 +399,7 @@ int kq_gather_qmm(const void* x, int x_dtype, long long x_batch, int M, int K, c
                   int rhs_sorted, void* y, void* workspace, size_t workspace_bytes, void* stream) {
   return kq::gather_qmm_entry(x, x_dtype, x_batch, M, K, w, n_experts, w_expert_stride_bytes, w_row_bytes, N,
                               kquant_type, lhs_indices, rhs_indices, n_entries, transpose, rhs_sorted, y, workspace,
-                              workspace_bytes, stream, /*allow_grouped=*/true);
+                              workspace_bytes, stream, /*allow_grouped=*/true, /*builtin_scratch=*/false);
 }
 
 }  // extern "C"
@@ -408,7 +409,7 @@ int gather_qmm_entry(const void* x, int x_dtype, long long x_batch, int M, int K
                      long long w_expert_stride_bytes, size_t w_row_bytes, int N, const char* kquant_type,
                      const uint32_t* lhs_indices, const uint32_t* rhs_indices, long long n_entries, int transpose,
                      int rhs_sorted, void* y, void* workspace, size_t workspace_bytes, void* stream,
-                     bool allow_grouped) {
+                     bool allow_grouped, bool builtin_scratch) {
   (void)rhs_sorted;
   const int ci = find_codec(kquant_type);
   if (ci < 0)
@@ -455,13 +456,22 @@ int gather_qmm_entry(const void* x, int x_dtype, long long x_batch, int M, int K
   const size_t xe = x_dtype == KQ_F32 ? 4 : 2;
   if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || ((size_t)K * xe) % 16 != 0)
     return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmm] x rows must be 16-byte aligned.");
+  // rows are numbered with 32-bit integers on the device
+  if (n_entries > (long long)INT_MAX / (M > 0 ? M : 1))
+    return fail(KQ_ERR_UNSUPPORTED, "[mlx_kquant.gather_qmm] n_entries * M = %lld rows exceed 2^31 - 1; split the call.",
+                n_entries * (long long)M);
   const size_t need = kq::gather_layout(n_entries, M, n_experts, allow_grouped ? K : 0).total;
+  if (builtin_scratch && need > workspace_bytes)
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.gather_qmm] problem too large for the built-in scratch: needs %zu bytes, the fixed array "
+                "holds %zu; use kq_gather_qmm with a caller-provided workspace.",
+                need, workspace_bytes);
   if (workspace == nullptr || workspace_bytes < need)
     return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmm] workspace too small: %zu bytes given, %zu needed.",
                 workspace_bytes, need);
   if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
     return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmm] workspace must be 256-byte aligned.");
-  cudaError_t e = kq::launch_gather(ci, x_dtype, x, M, K, static_cast<const uint8_t*>(w), n_experts,
+  cudaError_t e = kq::launch_gather(ci, x_dtype, x, x_batch, M, K, static_cast<const uint8_t*>(w), n_experts,
                                     w_expert_stride_bytes, (long long)w_row_bytes, N, lhs_indices, rhs_indices,
                                     n_entries, y, workspace, allow_grouped, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return cuda_fail("gather_qmm", e);

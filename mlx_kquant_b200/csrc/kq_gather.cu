@@ -69,11 +69,13 @@ GatherLayout gather_layout(long long n_entries, int M, int n_experts, int K) {
   return L;
 }
 
-__global__ void gather_hist_kernel(const uint32_t* __restrict__ rhs, long long n, int n_experts, int* counts) {
+// Entries whose expert index or activation index is out of range take no part (their output rows stay unwritten).
+__global__ void gather_hist_kernel(const uint32_t* __restrict__ rhs, const uint32_t* __restrict__ lhs,
+                                   long long x_batch, long long n, int n_experts, int* counts) {
   const long long b = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (b < n) {
     const uint32_t e = rhs[b];
-    if (e < (uint32_t)n_experts) atomicAdd(&counts[e], 1);
+    if (e < (uint32_t)n_experts && (lhs == nullptr || (long long)lhs[b] < x_batch)) atomicAdd(&counts[e], 1);
   }
 }
 
@@ -122,12 +124,14 @@ __global__ void gather_scan_kernel(const int* __restrict__ counts, int n_experts
   }
 }
 
-__global__ void gather_scatter_kernel(const uint32_t* __restrict__ rhs, long long n, int n_experts,
-                                      const int* __restrict__ offsets, int* cursor, int* order) {
+__global__ void gather_scatter_kernel(const uint32_t* __restrict__ rhs, const uint32_t* __restrict__ lhs,
+                                      long long x_batch, long long n, int n_experts, const int* __restrict__ offsets,
+                                      int* cursor, int* order) {
   const long long b = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (b < n) {
     const uint32_t e = rhs[b];
-    if (e < (uint32_t)n_experts) order[offsets[e] + atomicAdd(&cursor[e], 1)] = (int)b;
+    if (e < (uint32_t)n_experts && (long long)lhs[b] < x_batch)
+      order[offsets[e] + atomicAdd(&cursor[e], 1)] = (int)b;
   }
 }
 
@@ -209,7 +213,7 @@ cudaError_t launch_tile_map(const uint32_t* indices, long long rows, int n_exper
   cudaError_t err = cudaMemsetAsync(counts, 0, (size_t)(n_experts + 1) * 4, st);
   if (err != cudaSuccess) return err;
   const int th = 256;
-  gather_hist_kernel<<<(unsigned)((rows + th - 1) / th), th, 0, st>>>(indices, rows, n_experts, counts);
+  gather_hist_kernel<<<(unsigned)((rows + th - 1) / th), th, 0, st>>>(indices, nullptr, 0, rows, n_experts, counts);
   gather_scan_kernel<<<1, 1024, 0, st>>>(counts, n_experts, 1, kSegMapTileRows, offsets, tile_base,
                                          reinterpret_cast<int*>(count));
   tile_map_kernel<<<n_experts, 64, 0, st>>>(offsets, tile_base, map);
@@ -338,7 +342,8 @@ cudaError_t launch_gather_seg(int codec, int x_dtype, const void* x, long long r
                            n_tiles, (int)max_tiles, st);
 }
 
-cudaError_t launch_gather(int codec, int x_dtype, const void* x, int M, int K, const uint8_t* w, int n_experts,
+cudaError_t launch_gather(int codec, int x_dtype, const void* x, long long x_batch, int M, int K, const uint8_t* w,
+                          int n_experts,
                           long long expert_stride, long long row_bytes, int N, const uint32_t* lhs,
                           const uint32_t* rhs, long long n_entries, void* y, void* workspace, bool allow_grouped,
                           cudaStream_t st) {
@@ -356,10 +361,10 @@ cudaError_t launch_gather(int codec, int x_dtype, const void* x, int M, int K, c
   if (err != cudaSuccess) return err;
   const int th = 256;
   const unsigned nb = (unsigned)((n_entries + th - 1) / th);
-  gather_hist_kernel<<<nb, th, 0, st>>>(rhs, n_entries, n_experts, counts);
+  gather_hist_kernel<<<nb, th, 0, st>>>(rhs, lhs, x_batch, n_entries, n_experts, counts);
   gather_scan_kernel<<<1, 1024, 0, st>>>(counts, n_experts, M, L.grouped ? kGroupedTileRows : 16, offsets, task_base,
                                          n_tasks);
-  gather_scatter_kernel<<<nb, th, 0, st>>>(rhs, n_entries, n_experts, offsets, cursor, order);
+  gather_scatter_kernel<<<nb, th, 0, st>>>(rhs, lhs, x_batch, n_entries, n_experts, offsets, cursor, order);
 
   if (L.grouped) {
     GatherTile* tiles = reinterpret_cast<GatherTile*>(ws + L.tiles);
@@ -456,17 +461,6 @@ extern "C" int kq_gather_qmm_noalloc(const void* x, int x_dtype, long long x_bat
                                      const char* kquant_type, const uint32_t* lhs_indices,
                                      const uint32_t* rhs_indices, long long n_entries, int transpose, int rhs_sorted,
                                      void* y, void* stream) {
-  // This entry point always takes the decode regime (the skinny kernel over task lists), whose
-  // scratch does not grow with K; K = 0 asks for that layout.
-  const size_t need = kq_gather_qmm_workspace_bytes(n_entries, M, n_experts, 0);
-  if (need > KQ_GATHER_STATIC_WS_BYTES) {
-    char msg[256];
-    std::snprintf(msg, sizeof(msg),
-                  "[mlx_kquant.gather_qmm] problem too large for the built-in scratch: needs %zu bytes, the fixed array "
-                  "holds %u; use kq_gather_qmm with a caller-provided workspace.",
-                  need, (unsigned)KQ_GATHER_STATIC_WS_BYTES);
-    return kq::set_error(KQ_ERR_INVALID_ARGUMENT, msg);
-  }
   void* ws = nullptr;
   const cudaError_t e = static_ws_address(&ws);
   if (e != cudaSuccess) {
@@ -475,9 +469,11 @@ extern "C" int kq_gather_qmm_noalloc(const void* x, int x_dtype, long long x_bat
                   cudaGetErrorString(e));
     return kq::set_error(KQ_ERR_CUDA, msg);
   }
-  // From here on it is the ordinary path; it clears the counters it needs on the stream.
+  // From here on it is the ordinary path (argument checks first, then the size limit of the fixed array for
+  // the orientation that needs scratch; it clears the counters it needs on the stream). This entry point
+  // always takes the decode regime (the skinny kernel over task lists).
   return kq::gather_qmm_entry(x, x_dtype, x_batch, M, K, w, n_experts, w_expert_stride_bytes, w_row_bytes, N,
                               kquant_type, lhs_indices, rhs_indices, n_entries, transpose, rhs_sorted, y, ws,
-                              KQ_GATHER_STATIC_WS_BYTES, stream, /*allow_grouped=*/false);
+                              KQ_GATHER_STATIC_WS_BYTES, stream, /*allow_grouped=*/false, /*builtin_scratch=*/true);
 }
 

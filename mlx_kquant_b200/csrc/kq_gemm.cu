@@ -685,7 +685,8 @@ static cudaError_t launch_shape(bool out_half, const GemmArgs& a, cudaStream_t s
   if (mt == 4 && n_tiles * ((a.M + 511) / 512) < 148) mt = 2;
   // the q4_k producer is cheap enough to feed a 256-column tile; decode8-based producers are not
   if (FASTQ4 && a.M > 256) mt = 22;
-  if (const char* env = std::getenv("KQ_GEMM_TILE")) {
+  static const char* const tile_env = std::getenv("KQ_GEMM_TILE");  // A/B lever, read once per process
+  if (const char* env = tile_env) {
     const int v = std::atoi(env);
     if (v == 1 || v == 2 || v == 4 || v == 22) mt = v;
   }
@@ -700,7 +701,8 @@ static cudaError_t launch_shape(bool out_half, const GemmArgs& a, cudaStream_t s
   }
   if (FASTQ4)
     while (ksplit > 1 && ((a.K / 256) % ksplit) != 0) ksplit >>= 1;  // q4_k producers work in whole superblocks
-  if (const char* env = std::getenv("KQ_GEMM_KSPLIT")) {  // A/B lever
+  static const char* const ksplit_env = std::getenv("KQ_GEMM_KSPLIT");  // A/B lever, read once per process
+  if (const char* env = ksplit_env) {
     const int v = std::atoi(env);
     const int kb_total = (a.K + kBK - 1) / kBK;
     if ((v == 1 || v == 2 || v == 4 || v == 8) && kb_total % v == 0 && (!FASTQ4 || (a.K / 256) % v == 0)) ksplit = v;

@@ -1550,7 +1550,8 @@ cudaError_t launch_gemv(int codec, int x_dtype, const GemvArgs& a, cudaStream_t 
     S *= 2;
   }
   // A/B lever: KQ_GEMV_SPLIT=1|2|4|8 overrides the K-split heuristic.
-  if (const char* env = std::getenv("KQ_GEMV_SPLIT")) {
+  static const char* const split_env = std::getenv("KQ_GEMV_SPLIT");  // read once per process
+  if (const char* env = split_env) {
     const int v = std::atoi(env);
     if ((v == 1 || v == 2 || v == 4 || v == 8) && v <= nchunks) S = v;
   }

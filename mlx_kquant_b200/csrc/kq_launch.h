@@ -106,24 +106,26 @@ struct GatherLayout {
 // K > 0 lets the layout include the grouped regime's buffers when that regime would be chosen;
 // K == 0 is the decode-only layout (the skinny kernel over task lists).
 GatherLayout gather_layout(long long n_entries, int M, int n_experts, int K);
-cudaError_t launch_gather(int codec, int x_dtype, const void* x, int M, int K, const uint8_t* w, int n_experts,
-                          long long expert_stride, long long row_bytes, int N, const uint32_t* lhs,
+// Entries with rhs >= n_experts or lhs >= x_batch are skipped: their output rows stay unwritten.
+cudaError_t launch_gather(int codec, int x_dtype, const void* x, long long x_batch, int M, int K, const uint8_t* w,
+                          int n_experts, long long expert_stride, long long row_bytes, int N, const uint32_t* lhs,
                           const uint32_t* rhs, long long n_entries, void* y, void* workspace, bool allow_grouped,
                           cudaStream_t st);
 
-// The body of kq_gather_qmm; allow_grouped = false pins the decode regime (fixed-size scratch).
+// The body of kq_gather_qmm; allow_grouped = false pins the decode regime (fixed-size scratch);
+// builtin_scratch = true words a too-small workspace as the limit of the library's fixed array.
 int gather_qmm_entry(const void* x, int x_dtype, long long x_batch, int M, int K, const void* w, int n_experts,
                      long long w_expert_stride_bytes, size_t w_row_bytes, int N, const char* kquant_type,
                      const uint32_t* lhs_indices, const uint32_t* rhs_indices, long long n_entries, int transpose,
                      int rhs_sorted, void* y, void* workspace, size_t workspace_bytes, void* stream,
-                     bool allow_grouped);
+                     bool allow_grouped, bool builtin_scratch);
 
 // Record `msg` as this thread's last error (what kq_last_error() returns) and
 // hand back `code`; lets entry points that live outside kq_abi.cu report errors.
 int set_error(int code, const char* msg);
 
 // Host-side encoder (kq_quantize.cu): float weights -> wire bytes, byte-identical with the
-// reference's CPU encoder for all ten codecs.
+// reference's CPU encoder for all thirteen codecs of the registry.
 bool quantize_supported(int codec);
 void quantize_host(int codec, const void* w, int dtype, long long n_weights, long long K, const float* imatrix,
                    uint8_t* out, int threads);

@@ -65,8 +65,8 @@ def from_f32(a: np.ndarray, dtype: str) -> np.ndarray:
 def build(ref_dir: str | None = None) -> None:
     """Compile both checkers with the Makefile beside this file."""
     cmd = ["make", "-s", "-C", str(HERE), "all"]
-    if ref_dir:
-        cmd.append(f"REF={ref_dir}")
+    ref_dir = ref_dir or os.environ.get("KQ_REFERENCE_DIR") or str(HERE.parent.parent / "reference")
+    cmd.append(f"REF={ref_dir}")
     subprocess.run(cmd, check=True)
 
 

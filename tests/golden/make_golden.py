@@ -34,7 +34,7 @@ sys.path.insert(0, str(ROOT))
 from oracle.kq_oracle import CODECS, GEOMETRY, Ref, from_f32  # noqa: E402
 
 
-def main(ref_dir: str = "/root/reference") -> None:
+def main(ref_dir: str) -> None:
     ref = Ref()
     fx = Path(ref_dir) / "tests" / "fixtures"
     out: dict[str, np.ndarray] = {}
@@ -65,4 +65,9 @@ def main(ref_dir: str = "/root/reference") -> None:
 
 
 if __name__ == "__main__":
-    main(*sys.argv[1:])
+    import os
+
+    where = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("KQ_REFERENCE_DIR")
+    if not where:
+        sys.exit("usage: make_golden.py <reference checkout>   (or set KQ_REFERENCE_DIR)")
+    main(where)

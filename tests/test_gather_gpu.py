@@ -178,3 +178,33 @@ def test_gather_small_magnitude_rows(oracle, scale):
         y = kq.gather_qmm(x, wd, None, codec, rhs_indices=torch.from_numpy(rhs.astype(np.int64)).cuda())
         ref = fp64_ref(oracle, store.reshape(B, K), "bf16", wire, codec, np.arange(B), rhs)
         assert_close(y_to_f32(y).reshape(B, N), ref, "bf16", TOL)
+
+
+@pytest.mark.parametrize("B", [12, 640])
+def test_out_of_range_activation_indices_are_skipped(oracle, B):
+    """Entries whose lhs index is >= the number of activation slots read nothing and leave their output rows
+    unwritten, like entries with an out-of-range expert (both regimes). Called through the C-ABI: the Python
+    op would reject such indices earlier."""
+    from mlx_kquant_b200 import _lib
+    L = _lib.lib()
+    codec, E, N, K, XB = "q4_k", 4, 64, 512, 9
+    wire = make_experts(codec, E, N, K, seed=91)
+    wd = torch.from_numpy(wire).cuda()
+    x, store = x_to_torch(np.random.default_rng(92).normal(0, 1, (XB, 1, K)).astype(np.float32), "bf16")
+    rng = np.random.default_rng(93)
+    rhs = rng.integers(0, E, B).astype(np.int32)
+    lhs = rng.integers(0, XB, B).astype(np.int32)
+    bad = np.arange(B) % 7 == 3
+    lhs_bad = lhs.copy()
+    lhs_bad[bad] = XB + 100
+    y = torch.full((B, 1, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    ws = torch.empty(L.kq_gather_qmm_workspace_bytes(B, 1, E, K), dtype=torch.uint8, device="cuda")
+    lt, rt = torch.from_numpy(lhs_bad).cuda(), torch.from_numpy(rhs).cuda()
+    _lib.check(L.kq_gather_qmm(x.data_ptr(), _lib.KQ_BF16, XB, 1, K, wd.data_ptr(), E, wd.stride(0), wd.shape[2], N,
+                               codec.encode(), lt.data_ptr(), rt.data_ptr(), B, 1, 0, y.data_ptr(), ws.data_ptr(),
+                               ws.numel(), torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    ref = fp64_ref(oracle, store.reshape(XB, K), "bf16", wire, codec, lhs, rhs)
+    got = y_to_f32(y).reshape(B, N)
+    assert rel_fro(got[~bad], ref[~bad]) <= TOL
+    assert (got[bad] == 7.0).all()

@@ -78,3 +78,31 @@ def test_noalloc_rejects_problems_beyond_the_fixed_array():
     rc = L.kq_gather_qmm_noalloc(p, _lib.KQ_F16, 1, 1, 256, p, 128, 144, 144, 1, b"q4_k", p, p, n_entries, 1, 0, p, None)
     assert rc == _lib.KQ_ERR_INVALID_ARGUMENT
     assert b"too large for the built-in scratch" in L.kq_last_error()
+
+
+def test_noalloc_checks_arguments_before_the_size_limit_and_only_where_scratch_is_used():
+    """An unknown codec on an oversized call is reported as such, and the [K, N] orientation (transpose = 0),
+    which uses no scratch, is not subject to the limit of the fixed array."""
+    L = _lib.lib()
+    one = torch.zeros(16, dtype=torch.uint8, device="cuda")
+    p = one.data_ptr()
+    rc = L.kq_gather_qmm_noalloc(p, _lib.KQ_F16, 1, 1, 256, p, 128, 144, 144, 1, b"q9_z", p, p, 200_000, 1, 0, p, None)
+    assert rc == _lib.KQ_ERR_INVALID_ARGUMENT and b"Unknown kquant_type" in L.kq_last_error()
+    # transpose = 0: w [E, K, bytes(N)], 100 000 entries (far beyond the limit of the other orientation)
+    E, K, N, B = 2, 32, 256, 100_000
+    w = _wire(E, K, N, seed=5)                       # [E, K rows, bytes of N weights]
+    x = torch.randn(4, 1, K, device="cuda").half()
+    rng = np.random.default_rng(6)
+    lhs = torch.from_numpy(rng.integers(0, 4, B).astype(np.int32)).cuda()
+    rhs = torch.from_numpy(rng.integers(0, E, B).astype(np.int32)).cuda()
+    got = torch.empty(B, 1, N, dtype=torch.float16, device="cuda")
+    want = torch.empty_like(got)
+    s = torch.cuda.current_stream().cuda_stream
+    args = (x.data_ptr(), _lib.KQ_F16, 4, 1, K, w.data_ptr(), E, w.stride(0), w.shape[2], N, b"q4_k", lhs.data_ptr(),
+            rhs.data_ptr(), B, 0, 0)
+    assert L.kq_gather_qmm_workspace_bytes(B, 1, E, 0) > KQ_GATHER_STATIC_WS_BYTES
+    _lib.check(L.kq_gather_qmm_noalloc(*args, got.data_ptr(), s))
+    ws = torch.empty(L.kq_gather_qmm_workspace_bytes(B, 1, E, K), dtype=torch.uint8, device="cuda")
+    _lib.check(L.kq_gather_qmm(*args, want.data_ptr(), ws.data_ptr(), ws.numel(), s))
+    torch.cuda.synchronize()
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
