@@ -158,6 +158,39 @@ KQ_API int kq_swiglu_routed(const void* gate, const void* up, long long in_row_s
 KQ_API int kq_moe_combine_f32(const void* d, const float* probs, long long tokens, int k, int H, int dtype, float* y,
                               void* stream);
 
+/* ---- fused mixture-of-experts decode ops: replace the reference's Metal-only moe_glu_gather_kq,
+ * gather_qmv_mix_ns_kq and moe_router_topk (src/kquant.h:335-357, 549-558, 560-585; no CPU eval exists there,
+ * src/kquant_moe_glu.cpp:1-8, so their oracle is the composition of gather_qmm calls) ----
+ * kq_codec_has_moe_glu: 1 when the codec has these kernels (q4_k), else 0 (codec_has_moe_glu, src/kquant.h:359).
+ * kq_moe_glu_gather: x [T, K]; gate_w / up_w: n_experts matrices [N, w_row_bytes] each, matrix e at
+ *   base + e * expert_stride_bytes; indices uint32 [T, R]; y [T, R, N] in x's dtype:
+ *   y[t, r] = act(x[t] . Wg[e]^T) * (x[t] . Wu[e]^T), e = indices[t, r], float32 sums, the activation in float32,
+ *   ONE rounding. act: "silu", "gelu" (tanh form), "silu_limit" (gate clamped from above and up to +-limit first;
+ *   limit > 0). Entries with e >= n_experts are skipped (their rows of y stay unwritten).
+ * kq_gather_qmv_mix: x [T, S, K] (one row per routed slot); w as above; indices uint32 [T, S]; scores float32
+ *   [T, S]; y [T, N] in x's dtype: y[t] = sum_s scores[t, s] * (x[t, s] . W[e_s]^T), accumulated in float32 in slot
+ *   order, ONE rounding.
+ * Both: q4_k, float16 / bfloat16 rows, K % 256 == 0, dense 16-byte aligned rows; anything else returns
+ *   KQ_ERR_UNSUPPORTED and the caller composes the op from kq_gather_qmm. They are decode kernels: every (token,
+ *   slot) entry streams its expert's rows, so weight traffic grows with T * R.
+ * kq_moe_router_topk: logits [T, E (+ 1 with shared_gate)] of `dtype`; scores the E columns in float32
+ *   ("softmax", or "sqrtsoftplus" = sqrt(softplus(x)), which requires norm_topk_prob), picks the top_k largest of
+ *   score (+ bias [E] if given: it ranks only), lowest index first among equals, optionally renormalises the picked
+ *   scores (sqrtsoftplus with a 1e-20 guard), multiplies by per_expert_scale [E] (if given) and by `scale`; with
+ *   shared_gate the sigmoid of column E lands in scores[:, top_k]. indices uint32 [T, top_k], scores float32
+ *   [T, top_k (+ 1)]. E <= 1024, top_k <= 16. */
+KQ_API int kq_codec_has_moe_glu(const char* kquant_type);
+KQ_API int kq_moe_glu_gather(const void* x, int x_dtype, long long T, int K, const void* gate_w,
+                             long long gate_expert_stride_bytes, const void* up_w, long long up_expert_stride_bytes,
+                             size_t w_row_bytes, int N, int n_experts, const char* kquant_type, const uint32_t* indices,
+                             int R, const char* act, float limit, void* y, void* stream);
+KQ_API int kq_gather_qmv_mix(const void* x, int x_dtype, long long T, int S, int K, const void* w,
+                             long long w_expert_stride_bytes, size_t w_row_bytes, int N, int n_experts,
+                             const char* kquant_type, const uint32_t* indices, const float* scores, void* y, void* stream);
+KQ_API int kq_moe_router_topk(const void* logits, int dtype, long long T, int E, int top_k, int norm_topk_prob,
+                              int shared_gate, const float* per_expert_scale, const float* bias, const char* scoring,
+                              float scale, uint32_t* indices, float* scores, void* stream);
+
 /* ---- gather_qmm without a workspace (no counterpart in the reference) ----
  * Same computation and arguments as kq_gather_qmm, minus the workspace: the
  * grouping scratch lives in a fixed KQ_GATHER_STATIC_WS_BYTES array that is part

@@ -381,6 +381,108 @@ int kq_gather_qmm_seg(const void* x, int x_dtype, long long rows, int K, const v
   return KQ_OK;
 }
 
+int kq_codec_has_moe_glu(const char* kquant_type) {
+  const int ci = find_codec(kquant_type);
+  return ci == kq::Q4_K ? 1 : 0;
+}
+
+static int moe_act_code(const char* act) {
+  if (act == nullptr || std::strcmp(act, "silu") == 0) return 0;
+  if (std::strcmp(act, "gelu") == 0) return 1;
+  if (std::strcmp(act, "silu_limit") == 0) return 2;
+  return -1;
+}
+
+int kq_moe_glu_gather(const void* x, int x_dtype, long long T, int K, const void* gate_w,
+                      long long gate_expert_stride_bytes, const void* up_w, long long up_expert_stride_bytes,
+                      size_t w_row_bytes, int N, int n_experts, const char* kquant_type, const uint32_t* indices, int R,
+                      const char* act, float limit, void* y, void* stream) {
+  const int ci = find_codec(kquant_type);
+  if (ci < 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_glu_gather_kq] Unknown kquant_type: '%s'.",
+                kquant_type ? kquant_type : "(null)");
+  const kq::CodecInfo& c = kq::kCodecs[ci];
+  const int a = moe_act_code(act);
+  if (a < 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.moe_glu_gather_kq] act must be 'silu', 'gelu' or 'silu_limit' but got '%s'.", act);
+  if (a == 2 && !(limit > 0.f))
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_glu_gather_kq] act 'silu_limit' requires limit > 0.");
+  if (w_row_bytes % (size_t)c.bpb != 0 || (long long)(w_row_bytes / c.bpb) * c.wpb != K)
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.moe_glu_gather_kq] x last dim (%d) does not match the expanded expert row (%lld weights).", K,
+                (long long)(w_row_bytes / c.bpb) * c.wpb);
+  if (K % 256 != 0) return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_glu_gather_kq] requires K %% 256 == 0.");
+  if (T < 0 || R < 0 || N < 0 || n_experts < 0) return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_glu_gather_kq] negative size.");
+  if (T == 0 || R == 0 || N == 0) return KQ_OK;
+  if (!x || !gate_w || !up_w || !indices || !y)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_glu_gather_kq] null pointer.");
+  if (T * (long long)R > 65535 ||
+      !kq::moe_decode_supported(ci, x_dtype, K, (long long)w_row_bytes, x, gate_w, gate_expert_stride_bytes, up_w,
+                                up_expert_stride_bytes))
+    return fail(KQ_ERR_UNSUPPORTED,
+                "[mlx_kquant.moe_glu_gather_kq] no fused kernel for this call (q4_k, float16 / bfloat16 rows, 16-byte "
+                "aligned operands, at most 65535 entries): compose it from gather_qmm.");
+  cudaError_t e = kq::launch_moe_glu(x_dtype, x, K, static_cast<const uint8_t*>(gate_w), gate_expert_stride_bytes,
+                                     static_cast<const uint8_t*>(up_w), up_expert_stride_bytes, (long long)w_row_bytes, N,
+                                     n_experts, indices, T * (long long)R, R, a, limit, y,
+                                     static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("moe_glu_gather_kq", e);
+  return KQ_OK;
+}
+
+int kq_gather_qmv_mix(const void* x, int x_dtype, long long T, int S, int K, const void* w,
+                      long long w_expert_stride_bytes, size_t w_row_bytes, int N, int n_experts, const char* kquant_type,
+                      const uint32_t* indices, const float* scores, void* y, void* stream) {
+  const int ci = find_codec(kquant_type);
+  if (ci < 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmv_mix_ns_kq] Unknown kquant_type: '%s'.",
+                kquant_type ? kquant_type : "(null)");
+  const kq::CodecInfo& c = kq::kCodecs[ci];
+  if (w_row_bytes % (size_t)c.bpb != 0 || (long long)(w_row_bytes / c.bpb) * c.wpb != K)
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.gather_qmv_mix_ns_kq] x last dim (%d) does not match the expanded expert row (%lld weights).",
+                K, (long long)(w_row_bytes / c.bpb) * c.wpb);
+  if (T < 0 || S < 0 || N < 0 || n_experts < 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmv_mix_ns_kq] negative size.");
+  if (T == 0 || N == 0) return KQ_OK;
+  if (!x || !w || !indices || !scores || !y)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmv_mix_ns_kq] null pointer.");
+  if (T > 65535 || S == 0 || K % 256 != 0 ||
+      !kq::moe_decode_supported(ci, x_dtype, K, (long long)w_row_bytes, x, w, w_expert_stride_bytes, nullptr, 0))
+    return fail(KQ_ERR_UNSUPPORTED,
+                "[mlx_kquant.gather_qmv_mix_ns_kq] no fused kernel for this call (q4_k, float16 / bfloat16 rows, "
+                "K %% 256 == 0, 16-byte aligned operands, at most 65535 tokens): compose it from gather_qmm.");
+  cudaError_t e = kq::launch_moe_mix(x_dtype, x, K, static_cast<const uint8_t*>(w), w_expert_stride_bytes,
+                                     (long long)w_row_bytes, N, n_experts, indices, scores, T, S, y,
+                                     static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("gather_qmv_mix_ns_kq", e);
+  return KQ_OK;
+}
+
+int kq_moe_router_topk(const void* logits, int dtype, long long T, int E, int top_k, int norm_topk_prob, int shared_gate,
+                       const float* per_expert_scale, const float* bias, const char* scoring, float scale,
+                       uint32_t* indices, float* scores, void* stream) {
+  int sc = -1;
+  if (scoring == nullptr || std::strcmp(scoring, "softmax") == 0) sc = 0;
+  else if (std::strcmp(scoring, "sqrtsoftplus") == 0) sc = 1;
+  if (sc < 0) return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_router_topk] unknown scoring '%s'.", scoring);
+  if (!dtype_ok(dtype)) return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_router_topk] logits must be floating.");
+  if (E < 1 || E > 1024 || top_k < 1 || top_k > 16 || top_k > E)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_router_topk] needs 1 <= top_k <= min(E, 16) and E <= 1024.");
+  if (sc == 1 && !norm_topk_prob)
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.moe_router_topk] sqrtsoftplus has no global normaliser: norm_topk_prob is required.");
+  if (T < 0 || T > 0x7fffffff) return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_router_topk] bad token count.");
+  if (T == 0) return KQ_OK;
+  if (!logits || !indices || !scores) return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_router_topk] null pointer.");
+  cudaError_t e = kq::launch_router_topk(logits, dtype, (int)T, E, top_k, norm_topk_prob ? 1 : 0, shared_gate ? 1 : 0, sc,
+                                         per_expert_scale, bias, scale, indices, scores,
+                                         static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("moe_router_topk", e);
+  return KQ_OK;
+}
+
 int kq_device_error_flags(int* flags, int clear) {
   if (flags == nullptr) return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant] kq_device_error_flags: null pointer.");
   cudaError_t e = kq::read_device_error(flags, clear != 0);

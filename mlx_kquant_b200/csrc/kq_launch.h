@@ -86,6 +86,20 @@ cudaError_t launch_gemm_tiles(int codec, bool out_half, const void* xh, long lon
 cudaError_t read_device_error(int* out, bool clear);
 int* device_error_word();  // device address of that flag word on the current device (nullptr on failure)
 
+// Fused mixture-of-experts decode kernels (kq_moe_decode.cu): q4_k expert stacks, fp16 / bf16 rows.
+// act: 0 silu, 1 gelu (tanh form), 2 silu with limit. scoring: 0 softmax, 1 sqrt(softplus).
+bool moe_decode_supported(int codec, int x_dtype, int K, long long row_bytes, const void* x, const void* w0,
+                          long long stride0, const void* w1, long long stride1);
+cudaError_t launch_moe_glu(int x_dtype, const void* x, int K, const uint8_t* wg, long long stride_g, const uint8_t* wu,
+                           long long stride_u, long long row_bytes, int F, int n_experts, const uint32_t* idx,
+                           long long n_entries, int R, int act, float limit, void* y, cudaStream_t st);
+cudaError_t launch_moe_mix(int x_dtype, const void* x, int K, const uint8_t* w, long long stride_w, long long row_bytes,
+                           int N, int n_experts, const uint32_t* idx, const float* scores, long long T, int S, void* y,
+                           cudaStream_t st);
+cudaError_t launch_router_topk(const void* logits, int dtype, int T, int E, int top_k, int norm, int shared, int scoring,
+                               const float* pes, const float* bias, float scale, uint32_t* indices, float* scores,
+                               cudaStream_t st);
+
 // q4_k, one dense fp16 / bf16 activation row, matrices of about one wave of CTAs (kq_gemv_stream.cu)
 bool gemv_stream_supported(int codec, int x_dtype, const GemvArgs& a);
 cudaError_t launch_gemv_stream(int x_dtype, const GemvArgs& a, cudaStream_t st);

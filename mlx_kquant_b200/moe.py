@@ -18,6 +18,9 @@ from .ops import gather_qmm
 
 def route_topk(router_logits: torch.Tensor, top_k: int) -> tuple[torch.Tensor, torch.Tensor]:
     """(expert ids [T, k] int64, renormalised probabilities [T, k] float32)."""
+    if router_logits.is_cuda and router_logits.shape[1] <= 1024 and top_k <= 16:
+        idx, p = moe_router_topk(router_logits, top_k, True, shared_gate=False)
+        return idx.to(torch.int64), p
     probs = torch.softmax(router_logits.float(), dim=-1)
     # a stable descending sort puts the lowest index first among equal probabilities
     order = torch.sort(probs, dim=-1, descending=True, stable=True)
@@ -91,14 +94,111 @@ def fuse_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
     return torch.cat([w_gate, w_up], dim=1).contiguous()
 
 
+_DT = {torch.float32: _lib.KQ_F32, torch.float16: _lib.KQ_F16, torch.bfloat16: _lib.KQ_BF16}
+FUSED_DECODE_MAX_ENTRIES = 256   # routed (token, expert) entries up to which the per-entry decode kernels are used
+
+
+def codec_has_moe_glu(kquant_type: str) -> bool:
+    """True when the codec has the fused MoE decode kernels (the reference's codec_has_moe_glu, src/kquant.h:359)."""
+    return bool(_lib.lib().kq_codec_has_moe_glu(kquant_type.encode()))
+
+
+def _u32(idx: torch.Tensor, device) -> torch.Tensor:
+    return idx.to(device=device, dtype=torch.int32).contiguous()
+
+
+def moe_glu_gather_kq(x, gate_w, up_w, kquant_type, indices, act="silu", limit=0.0):
+    """The reference's moe_glu_gather_kq (src/kquant.h:335-357): x [T, K], gate_w / up_w [E, N, bytes] (views of
+    one stacked tensor are fine: only the last two dims must be dense), indices [T, R] ->
+    [T, R, N] = act(x . Wg[e]^T) * (x . Wu[e]^T) in x's dtype, one rounding. Raises NotImplementedError when the
+    call has no fused kernel (see kq_moe_glu_gather in include/kquant_b200.h)."""
+    if x.dim() != 2 or indices.dim() != 2 or indices.shape[0] != x.shape[0]:
+        raise ValueError("[mlx_kquant.moe_glu_gather_kq] x must be [T, K] and indices [T, R].")
+    if gate_w.dim() != 3 or up_w.shape != gate_w.shape or gate_w.dtype != torch.uint8 or up_w.dtype != torch.uint8:
+        raise ValueError("[mlx_kquant.moe_glu_gather_kq] gate_w / up_w must be uint8 [E, N, bytes] of one shape.")
+    for w in (gate_w, up_w):
+        if w.stride(2) != 1 or w.stride(1) != w.shape[2]:
+            raise ValueError("[mlx_kquant.moe_glu_gather_kq] the expert matrices must be dense in their last two dims.")
+    if x.dtype not in (torch.float16, torch.bfloat16):
+        raise NotImplementedError("[mlx_kquant.moe_glu_gather_kq] float16 / bfloat16 activations only.")
+    T, K = x.shape
+    E, N, rb = gate_w.shape
+    R = indices.shape[1]
+    xc = x.contiguous()
+    idx = _u32(indices, x.device)
+    y = torch.empty((T, R, N), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().kq_moe_glu_gather(xc.data_ptr(), _DT[x.dtype], T, K, gate_w.data_ptr(), gate_w.stride(0),
+                                                up_w.data_ptr(), up_w.stride(0), rb, N, E, kquant_type.encode(),
+                                                idx.data_ptr(), R, act.encode(), float(limit), y.data_ptr(),
+                                                torch.cuda.current_stream(x.device).cuda_stream))
+    return y
+
+
+def gather_qmv_kq(x, w, kquant_type, indices):
+    """The reference's gather_qmv_kq without bias (src/kquant.h:505-515): x [T, R, K] (one row per expert slot),
+    indices [T, R] -> [T, R, N]. This is gather_qmm over the flattened slots."""
+    T, R, K = x.shape
+    y = gather_qmm(x.reshape(T * R, 1, K), w, None, kquant_type, rhs_indices=indices.reshape(T * R))
+    return y.reshape(T, R, -1)
+
+
+def gather_qmv_mix_ns_kq(x, w, kquant_type, indices, scores):
+    """The reference's gather_qmv_mix_ns_kq (src/kquant.h:549-558): x [T, S, K], w [E, N, bytes], indices [T, S],
+    scores [T, S] -> [T, N] = sum_s scores[t, s] * (x[t, s] . W[e_s]^T), accumulated in float32, one rounding."""
+    if x.dim() != 3 or indices.shape != x.shape[:2] or scores.shape != x.shape[:2]:
+        raise ValueError("[mlx_kquant.gather_qmv_mix_ns_kq] x must be [T, S, K], indices and scores [T, S].")
+    if w.dim() != 3 or w.dtype != torch.uint8 or w.stride(2) != 1 or w.stride(1) != w.shape[2]:
+        raise ValueError("[mlx_kquant.gather_qmv_mix_ns_kq] w must be uint8 [E, N, bytes], dense in its last two dims.")
+    if x.dtype not in (torch.float16, torch.bfloat16):
+        raise NotImplementedError("[mlx_kquant.gather_qmv_mix_ns_kq] float16 / bfloat16 activations only.")
+    T, S, K = x.shape
+    E, N, rb = w.shape
+    xc = x.contiguous()
+    idx = _u32(indices, x.device)
+    sc = scores.to(device=x.device, dtype=torch.float32).contiguous()
+    y = torch.empty((T, N), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().kq_gather_qmv_mix(xc.data_ptr(), _DT[x.dtype], T, S, K, w.data_ptr(), w.stride(0), rb, N, E,
+                                                kquant_type.encode(), idx.data_ptr(), sc.data_ptr(), y.data_ptr(),
+                                                torch.cuda.current_stream(x.device).cuda_stream))
+    return y
+
+
+def _fused_decode_ok(x, kquant_type, rows, *stacks) -> bool:
+    if not (x.is_cuda and x.dtype in (torch.float16, torch.bfloat16) and rows <= FUSED_DECODE_MAX_ENTRIES):
+        return False
+    if not codec_has_moe_glu(kquant_type):
+        return False
+    for w in stacks:
+        if w.stride(2) != 1 or w.stride(1) != w.shape[2] or w.data_ptr() % 16 or (w.stride(0) % 16):
+            return False
+        if (w.shape[2] // 144 * 256) % 256 or w.shape[2] % 144:
+            return False
+    return True
+
+
 def moe_glu(x, w_gate, w_up, w_down, kquant_type, expert_ids, expert_probs, *, sort_rows: bool = False,
-            w_gate_up=None):
+            w_gate_up=None, fused: bool | None = None):
     """x [T, H] (f16 / bf16), expert stacks [E, F, bytes(H)] x2 and [E, H, bytes(F)],
     expert_ids / expert_probs [T, k]. Returns y [T, H] in x's dtype. With w_gate_up = fuse_gate_up(w_gate,
-    w_up) the gate and up products are one gather_qmm call (w_gate / w_up may then be None)."""
+    w_up) the gate and up products are one gather_qmm call (w_gate / w_up may then be None).
+    fused: None = the two fused decode launches when the call is small enough and has them, False = always the
+    three-gather composition (the reference callers' form, with its bf16 intermediates)."""
     T, H = x.shape
     k = expert_ids.shape[1]
     rows = T * k
+    # A few tokens: two launches - gate | up with the activation fused, then down with the weighted sum fused.
+    # One rounding (h) where the composition below has three (gate / up, h, down): not bit-identical to it.
+    if not sort_rows and fused is not False:
+        if w_gate_up is not None:
+            F = w_gate_up.shape[1] // 2
+            wg_v, wu_v = w_gate_up[:, :F], w_gate_up[:, F:]
+        else:
+            wg_v, wu_v = w_gate, w_up
+        if _fused_decode_ok(x, kquant_type, rows, wg_v, wu_v, w_down):
+            h = moe_glu_gather_kq(x, wg_v, wu_v, kquant_type, expert_ids)
+            return gather_qmv_mix_ns_kq(h, w_down, kquant_type, expert_ids, expert_probs)
     flat_e = expert_ids.reshape(rows)
     tok = torch.arange(T, device=x.device).repeat_interleave(k)
     # Rows go in routing order: gather_qmm groups them by expert on the device itself, so the explicit
@@ -150,6 +250,17 @@ def moe_glu_expert_parallel(x, w_gate, w_up, w_down, kquant_type, expert_ids, ex
     T, H = x.shape
     k = expert_ids.shape[1]
     rows = T * k
+    # A few tokens: two launches - gate | up with the activation fused, then down with the weighted sum fused.
+    # One rounding (h) where the composition below has three (gate / up, h, down): not bit-identical to it.
+    if not sort_rows and fused is not False:
+        if w_gate_up is not None:
+            F = w_gate_up.shape[1] // 2
+            wg_v, wu_v = w_gate_up[:, :F], w_gate_up[:, F:]
+        else:
+            wg_v, wu_v = w_gate, w_up
+        if _fused_decode_ok(x, kquant_type, rows, wg_v, wu_v, w_down):
+            h = moe_glu_gather_kq(x, wg_v, wu_v, kquant_type, expert_ids)
+            return gather_qmv_mix_ns_kq(h, w_down, kquant_type, expert_ids, expert_probs)
     flat_e = expert_ids.reshape(rows)
     tok = torch.arange(T, device=x.device).repeat_interleave(k)
     owner = expert_owner(flat_e, n_experts, world)
@@ -314,7 +425,8 @@ def moe_router_topk(logits, top_k, norm_topk_prob, shared_gate=True, per_expert_
     (the sqrtsoftplus renormalisation carries a 1e-20 guard), multiply by `per_expert_scale` [E] of the picked
     experts and by the uniform `scale`. With `shared_gate`, logits are [T, E + 1] and the sigmoid of column E
     lands in an extra last scores slot. Returns (indices [T, top_k] int32, scores float32 [T, top_k (+ 1)]).
-    Composed of torch ops on the logits' device; E <= 1024 and top_k <= 16 as in the reference."""
+    One kernel launch for CUDA logits (kq_moe_router_topk); torch ops for host tensors. E <= 1024 and
+    top_k <= 16 as in the reference."""
     if scoring not in ("softmax", "sqrtsoftplus"):
         raise ValueError(f"[mlx_kquant.moe_router_topk] unknown scoring '{scoring}'.")
     if logits.dim() != 2:
@@ -324,6 +436,22 @@ def moe_router_topk(logits, top_k, norm_topk_prob, shared_gate=True, per_expert_
         raise ValueError("[mlx_kquant.moe_router_topk] needs 1 <= top_k <= min(E, 16) and E <= 1024.")
     if scoring == "sqrtsoftplus" and not norm_topk_prob:
         raise ValueError("[mlx_kquant.moe_router_topk] sqrtsoftplus has no global normaliser: norm_topk_prob is required.")
+    if logits.is_cuda and logits.dtype in _DT:
+        T = logits.shape[0]
+        lc = logits.contiguous()
+        idx = torch.empty((T, top_k), dtype=torch.int32, device=logits.device)
+        sc = torch.empty((T, top_k + (1 if shared_gate else 0)), dtype=torch.float32, device=logits.device)
+        pes = per_expert_scale.to(device=logits.device, dtype=torch.float32).contiguous() if per_expert_scale is not None else None
+        bs = bias.to(device=logits.device, dtype=torch.float32).contiguous() if bias is not None else None
+        with torch.cuda.device(logits.device):
+            _lib.check(_lib.lib().kq_moe_router_topk(lc.data_ptr(), _DT[logits.dtype], T, E, top_k,
+                                                     1 if norm_topk_prob else 0, 1 if shared_gate else 0,
+                                                     pes.data_ptr() if pes is not None else None,
+                                                     bs.data_ptr() if bs is not None else None, scoring.encode(),
+                                                     float(scale), idx.data_ptr(), sc.data_ptr(),
+                                                     torch.cuda.current_stream(logits.device).cuda_stream))
+        return idx, sc
+    # host tensors: the same computation in torch ops
     lf = logits.float()
     x = lf[:, :E]
     if scoring == "softmax":

@@ -1,0 +1,203 @@
+"""The fused mixture-of-experts decode ops (csrc/kq_moe_decode.cu) against the oracle.
+
+The reference has no CPU evaluation of moe_glu_gather_kq / gather_qmv_mix_ns_kq / moe_router_topk
+(src/kquant_moe_glu.cpp:1-8), so the expected values are the float64 statement of each op on the oracle's
+bit-exact dequantized weights, and, for the router, the numpy statement the reference tests its op with
+(tests/test_moe_glu.py:453-549) as restated in test_router.py for host tensors."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_close
+from gpu_util import mint_wire, x_to_torch, y_to_f32
+from mlx_kquant_b200 import _lib
+from mlx_kquant_b200.moe import (codec_has_moe_glu, gather_qmv_kq, gather_qmv_mix_ns_kq, moe_glu, moe_glu_gather_kq,
+                                 moe_router_topk, route_topk)
+from oracle.kq_oracle import to_f32
+
+pytestmark = pytest.mark.gpu
+
+
+def experts(E, N, K, seed):
+    rng = np.random.default_rng(seed)
+    return np.stack([mint_wire("q4_k", rng.normal(0, 0.02, (N, K)).astype(np.float32)) for _ in range(E)])
+
+
+def act_ref(g, u, act, limit):
+    if act == "gelu":
+        return 0.5 * g * (1.0 + np.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3))) * u
+    if act == "silu_limit":
+        g = np.minimum(g, limit)
+        u = np.clip(u, -limit, limit)
+    return g / (1.0 + np.exp(-g)) * u
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("act,limit", [("silu", 0.0), ("gelu", 0.0), ("silu_limit", 0.5)])
+def test_moe_glu_gather_kq(oracle, dt, act, limit):
+    E, N, K, T, R = 6, 100, 512, 3, 4            # N = 100: the last 16-row tile holds 4 rows
+    wg, wu = experts(E, N, K, 11), experts(E, N, K, 12)
+    rng = np.random.default_rng(13)
+    x, store = x_to_torch(rng.normal(0, 1, (T, K)).astype(np.float32), dt)
+    ids = rng.integers(0, E, (T, R))
+    y = moe_glu_gather_kq(x, torch.from_numpy(wg).cuda(), torch.from_numpy(wu).cuda(), "q4_k",
+                          torch.from_numpy(ids).cuda(), act=act, limit=limit)
+    assert tuple(y.shape) == (T, R, N) and y.dtype == x.dtype
+    xs = to_f32(store, dt).astype(np.float64)
+    Wg = oracle.dequantize(wg, "q4_k", "f32").astype(np.float64)
+    Wu = oracle.dequantize(wu, "q4_k", "f32").astype(np.float64)
+    ref = np.stack([np.stack([act_ref(xs[t] @ Wg[e].T, xs[t] @ Wu[e].T, act, limit) for e in ids[t]]) for t in range(T)])
+    assert_close(y_to_f32(y).reshape(T * R, N), ref.reshape(T * R, N), dt, 2e-3)
+
+
+def test_moe_glu_gather_kq_stacked_views_and_skipped_entries(oracle):
+    """gate | up as the two halves of one stacked tensor (strided expert dimension), and an out-of-range expert
+    index whose output row stays untouched."""
+    E, F, K, T, R = 4, 48, 256, 2, 3
+    wg, wu = experts(E, F, K, 21), experts(E, F, K, 22)
+    wgu = torch.from_numpy(np.concatenate([wg, wu], axis=1)).cuda()
+    x, store = x_to_torch(np.random.default_rng(23).normal(0, 1, (T, K)).astype(np.float32), "bf16")
+    ids = torch.tensor([[0, 3, 9], [2, 2, 1]]).cuda()      # 9 >= E
+    L = _lib.lib()
+    y = torch.full((T, R, F), 5.0, dtype=torch.bfloat16, device="cuda")
+    idx = ids.to(torch.int32).contiguous()
+    g_v, u_v = wgu[:, :F], wgu[:, F:]
+    _lib.check(L.kq_moe_glu_gather(x.data_ptr(), _lib.KQ_BF16, T, K, g_v.data_ptr(), g_v.stride(0), u_v.data_ptr(),
+                                   u_v.stride(0), g_v.shape[2], F, E, b"q4_k", idx.data_ptr(), R, b"silu", 0.0,
+                                   y.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    xs = to_f32(store, "bf16").astype(np.float64)
+    Wg = oracle.dequantize(wg, "q4_k", "f32").astype(np.float64)
+    Wu = oracle.dequantize(wu, "q4_k", "f32").astype(np.float64)
+    got = y_to_f32(y)
+    assert (got[0, 2] == 5.0).all()
+    for t in range(T):
+        for r in range(R):
+            e = int(ids[t, r])
+            if e < E:
+                assert_close(got[t, r][None], act_ref(xs[t] @ Wg[e].T, xs[t] @ Wu[e].T, "silu", 0)[None], "bf16", 2e-3)
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("S", [3, 8, 11])
+def test_gather_qmv_mix_ns_kq(oracle, dt, S):
+    E, N, K, T = 5, 84, 768, 3                  # K = 768: three superblocks per row, rows of 432 bytes
+    w = experts(E, N, K, 31)
+    rng = np.random.default_rng(32 + S)
+    x, store = x_to_torch(rng.normal(0, 1, (T, S, K)).astype(np.float32), dt)
+    ids = rng.integers(0, E, (T, S))
+    sc = rng.uniform(0.05, 0.4, (T, S)).astype(np.float32)
+    wd = torch.from_numpy(w).cuda()
+    y = gather_qmv_mix_ns_kq(x, wd, "q4_k", torch.from_numpy(ids).cuda(), torch.from_numpy(sc).cuda())
+    assert tuple(y.shape) == (T, N) and y.dtype == x.dtype
+    xs = to_f32(store, dt).astype(np.float64)
+    W = oracle.dequantize(w, "q4_k", "f32").astype(np.float64)
+    ref = np.stack([sum(sc[t, s] * (xs[t, s] @ W[ids[t, s]].T) for s in range(S)) for t in range(T)])
+    assert_close(y_to_f32(y), ref, dt, 2e-3)
+    # the unfused form of the same op: per-slot products (rounded), then the weighted sum
+    d = gather_qmv_kq(x, wd, "q4_k", torch.from_numpy(ids).cuda()).float()
+    unfused = (d * torch.from_numpy(sc).cuda()[:, :, None]).sum(1)
+    assert float((y.float() - unfused).norm() / unfused.norm()) < 6e-3
+
+
+def test_fused_block_equals_composition(oracle):
+    """moe_glu takes the two fused launches for a few tokens; sort_rows=True forces the three-gather composition."""
+    E, H, F, k, T = 16, 512, 256, 4, 5
+    wg, wu, wd = experts(E, F, H, 41), experts(E, F, H, 42), experts(E, H, F, 43)
+    rng = np.random.default_rng(44)
+    x = torch.from_numpy(rng.normal(0, 1, (T, H)).astype(np.float32)).to(torch.bfloat16).cuda()
+    ids, probs = route_topk(torch.from_numpy(rng.normal(0, 1, (T, E)).astype(np.float32)).cuda(), k)
+    args = (x, torch.from_numpy(wg).cuda(), torch.from_numpy(wu).cuda(), torch.from_numpy(wd).cuda(), "q4_k", ids, probs)
+    assert codec_has_moe_glu("q4_k") and not codec_has_moe_glu("q6_k")
+    y = moe_glu(*args)
+    # float64 statement of the block
+    xs = x.float().cpu().numpy().astype(np.float64)
+    Wg, Wu, Wd = (oracle.dequantize(w, "q4_k", "f32").astype(np.float64) for w in (wg, wu, wd))
+    idn, pn = ids.cpu().numpy(), probs.cpu().numpy().astype(np.float64)
+    ref = np.zeros((T, H))
+    for t in range(T):
+        for j in range(k):
+            e = idn[t, j]
+            g, u = xs[t] @ Wg[e].T, xs[t] @ Wu[e].T
+            ref[t] += pn[t, j] * ((g / (1 + np.exp(-g)) * u) @ Wd[e].T)
+    err = np.linalg.norm(y_to_f32(y) - ref) / np.linalg.norm(ref)
+    assert err < 4e-3, err                       # the rounding of h to bfloat16, then of y
+
+
+def test_indices_written_by_the_preceding_launch(oracle):
+    """router -> fused gate/up -> fused down replayed from a CUDA graph whose first node overwrites the index
+    buffer: the product kernels start their weight copies from the stale indices and must copy again."""
+    E, H, F, k, T = 16, 512, 256, 4, 2
+    wg, wu, wd = (torch.from_numpy(experts(E, n, kk, s)).cuda() for n, kk, s in ((F, H, 51), (F, H, 52), (H, F, 53)))
+    rng = np.random.default_rng(54)
+    x = torch.from_numpy(rng.normal(0, 1, (T, H)).astype(np.float32)).to(torch.float16).cuda()
+    logits = torch.from_numpy(rng.normal(0, 1, (T, E)).astype(np.float32)).cuda()
+    L = _lib.lib()
+    idx = torch.zeros(T, k, dtype=torch.int32, device="cuda")
+    sc = torch.zeros(T, k, dtype=torch.float32, device="cuda")
+    h = torch.empty(T, k, F, dtype=torch.float16, device="cuda")
+    y = torch.empty(T, H, dtype=torch.float16, device="cuda")
+    stream = torch.cuda.Stream()
+
+    def block(s):
+        idx.fill_(E - 1)          # stale: every slot points at the last expert
+        _lib.check(L.kq_moe_router_topk(logits.data_ptr(), _lib.KQ_F32, T, E, k, 1, 0, None, None, b"softmax", 1.0,
+                                        idx.data_ptr(), sc.data_ptr(), s.cuda_stream))
+        _lib.check(L.kq_moe_glu_gather(x.data_ptr(), _lib.KQ_F16, T, H, wg.data_ptr(), wg.stride(0), wu.data_ptr(),
+                                       wu.stride(0), wg.shape[2], F, E, b"q4_k", idx.data_ptr(), k, b"silu", 0.0,
+                                       h.data_ptr(), s.cuda_stream))
+        _lib.check(L.kq_gather_qmv_mix(h.data_ptr(), _lib.KQ_F16, T, k, F, wd.data_ptr(), wd.stride(0), wd.shape[2], H, E,
+                                       b"q4_k", idx.data_ptr(), sc.data_ptr(), y.data_ptr(), s.cuda_stream))
+
+    with torch.cuda.stream(stream):
+        block(stream)
+        stream.synchronize()
+        y_eager = y.clone()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            block(stream)
+        for _ in range(5):
+            g.replay()
+        stream.synchronize()
+    ids, probs = route_topk(logits, k)
+    assert torch.equal(idx.long(), ids)
+    want = moe_glu(x, wg, wu, wd, "q4_k", ids, probs)
+    assert torch.equal(y, y_eager)
+    assert torch.equal(y, want)
+
+
+@pytest.mark.parametrize("case", ["softmax_shared", "pes", "sqrtsoftplus_bias", "wide"])
+def test_router_kernel_matches_host_statement(case):
+    rng = np.random.default_rng(61)
+    if case == "softmax_shared":
+        cfgs = [dict(E=256, k=8, norm=True, shared=True), dict(E=256, k=8, norm=False, shared=True),
+                dict(E=16, k=2, norm=True, shared=True)]
+    elif case == "pes":
+        cfgs = [dict(E=128, k=8, norm=True, shared=False, pes=True), dict(E=100, k=5, norm=True, shared=False, pes=True)]
+    elif case == "sqrtsoftplus_bias":
+        cfgs = [dict(E=256, k=6, norm=True, shared=False, bias=True, scoring="sqrtsoftplus", scale=1.5)]
+    else:
+        cfgs = [dict(E=1024, k=16, norm=True, shared=False), dict(E=33, k=16, norm=False, shared=False)]
+    for c in cfgs:
+        E, k = c["E"], c["k"]
+        T = 37
+        logits = rng.standard_normal((T, E + (1 if c["shared"] else 0))).astype(np.float32)
+        logits[3, 4:9] = logits[3, 4]              # exact ties: the lowest index wins
+        pes = torch.from_numpy(rng.uniform(0.5, 1.5, E).astype(np.float32)) if c.get("pes") else None
+        bias = torch.from_numpy(rng.standard_normal(E).astype(np.float32)) if c.get("bias") else None
+        for dt in (torch.float32, torch.bfloat16, torch.float16):
+            lt = torch.from_numpy(logits).to(dt)
+            kw = dict(shared_gate=c["shared"], per_expert_scale=pes, bias=bias, scoring=c.get("scoring", "softmax"),
+                      scale=c.get("scale", 1.0))
+            i_h, s_h = moe_router_topk(lt, k, c["norm"], **kw)                  # host tensors: torch statement
+            i_d, s_d = moe_router_topk(lt.cuda(), k, c["norm"], **kw)           # the kernel
+            assert i_d.dtype == torch.int32 and tuple(s_d.shape) == tuple(s_h.shape)
+            same = (i_d.cpu() == i_h).all(dim=1)
+            # rows that differ may only differ by float32 rounding noise between equal-within-an-ulp scores
+            for t in torch.nonzero(~same).flatten().tolist():
+                assert set(i_d[t].tolist()) == set(i_h[t].tolist()) or c.get("scoring") == "sqrtsoftplus"
+            ok = same
+            np.testing.assert_allclose(s_d.cpu().numpy()[ok.numpy()], s_h.numpy()[ok.numpy()], rtol=2e-5, atol=1e-6)
+            assert int(ok.sum()) >= T - 2
