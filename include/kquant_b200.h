@@ -171,22 +171,34 @@ KQ_API int kq_moe_combine_f32(const void* d, const float* probs, long long token
  *   [T, S]; y [T, N] in x's dtype: y[t] = sum_s scores[t, s] * (x[t, s] . W[e_s]^T), accumulated in float32 in slot
  *   order, ONE rounding.
  * Both: q4_k, float16 / bfloat16 rows, K % 256 == 0, dense 16-byte aligned rows; anything else returns
- *   KQ_ERR_UNSUPPORTED and the caller composes the op from kq_gather_qmm. They are decode kernels: every (token,
- *   slot) entry streams its expert's rows, so weight traffic grows with T * R.
+ *   KQ_ERR_UNSUPPORTED and the caller composes the op from kq_gather_qmm. Up to KQ_MOE_DIRECT_MAX_ENTRIES (token,
+ *   slot) entries every entry streams its expert's rows by itself and no scratch is needed (workspace may be
+ *   NULL). Beyond that, with a workspace of kq_moe_decode_workspace_bytes(T * R, n_experts, N_mix) bytes (N_mix =
+ *   N for kq_gather_qmv_mix, 0 for kq_moe_glu_gather; 256-byte aligned, private to the call until it completes),
+ *   the entries are grouped by expert on the device and one read of an expert's rows serves up to sixteen entries; the
+ *   mix then rounds each slot's product once before the weighted sum, as the unfused ops do. reuse_grouping != 0
+ *   tells kq_gather_qmv_mix that `workspace` still holds the grouping kq_moe_glu_gather made from the SAME indices
+ *   (same T * S, same n_experts; a workspace of the mix size was given to both calls): it is not rebuilt. Without a workspace
+ *   the per-entry form runs at any size. These are decode kernels: for prefill-sized calls (dozens of rows per
+ *   expert) compose the block from kq_gather_qmm, which uses the tensor-core tile kernel.
  * kq_moe_router_topk: logits [T, E (+ 1 with shared_gate)] of `dtype`; scores the E columns in float32
  *   ("softmax", or "sqrtsoftplus" = sqrt(softplus(x)), which requires norm_topk_prob), picks the top_k largest of
  *   score (+ bias [E] if given: it ranks only), lowest index first among equals, optionally renormalises the picked
  *   scores (sqrtsoftplus with a 1e-20 guard), multiplies by per_expert_scale [E] (if given) and by `scale`; with
  *   shared_gate the sigmoid of column E lands in scores[:, top_k]. indices uint32 [T, top_k], scores float32
  *   [T, top_k (+ 1)]. E <= 1024, top_k <= 16. */
+#define KQ_MOE_DIRECT_MAX_ENTRIES 192
 KQ_API int kq_codec_has_moe_glu(const char* kquant_type);
+KQ_API size_t kq_moe_decode_workspace_bytes(long long n_entries, int n_experts, int N_mix);
 KQ_API int kq_moe_glu_gather(const void* x, int x_dtype, long long T, int K, const void* gate_w,
                              long long gate_expert_stride_bytes, const void* up_w, long long up_expert_stride_bytes,
                              size_t w_row_bytes, int N, int n_experts, const char* kquant_type, const uint32_t* indices,
-                             int R, const char* act, float limit, void* y, void* stream);
+                             int R, const char* act, float limit, void* y, void* workspace, size_t workspace_bytes,
+                             void* stream);
 KQ_API int kq_gather_qmv_mix(const void* x, int x_dtype, long long T, int S, int K, const void* w,
                              long long w_expert_stride_bytes, size_t w_row_bytes, int N, int n_experts,
-                             const char* kquant_type, const uint32_t* indices, const float* scores, void* y, void* stream);
+                             const char* kquant_type, const uint32_t* indices, const float* scores, void* y,
+                             void* workspace, size_t workspace_bytes, int reuse_grouping, void* stream);
 KQ_API int kq_moe_router_topk(const void* logits, int dtype, long long T, int E, int top_k, int norm_topk_prob,
                               int shared_gate, const float* per_expert_scale, const float* bias, const char* scoring,
                               float scale, uint32_t* indices, float* scores, void* stream);

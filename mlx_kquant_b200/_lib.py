@@ -51,12 +51,13 @@ SIGNATURES = {
                                     C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "kq_device_error_flags": (C.c_int, [C.POINTER(C.c_int), C.c_int]),
     "kq_codec_has_moe_glu": (C.c_int, [C.c_char_p]),
+    "kq_moe_decode_workspace_bytes": (C.c_size_t, [C.c_longlong, C.c_int, C.c_int]),
     "kq_moe_glu_gather": (C.c_int, [C.c_void_p, C.c_int, C.c_longlong, C.c_int, C.c_void_p, C.c_longlong, C.c_void_p,
                                     C.c_longlong, C.c_size_t, C.c_int, C.c_int, C.c_char_p, C.c_void_p, C.c_int,
-                                    C.c_char_p, C.c_float, C.c_void_p, C.c_void_p]),
+                                    C.c_char_p, C.c_float, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "kq_gather_qmv_mix": (C.c_int, [C.c_void_p, C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_void_p, C.c_longlong,
                                     C.c_size_t, C.c_int, C.c_int, C.c_char_p, C.c_void_p, C.c_void_p, C.c_void_p,
-                                    C.c_void_p]),
+                                    C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]),
     "kq_moe_router_topk": (C.c_int, [C.c_void_p, C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                      C.c_void_p, C.c_char_p, C.c_float, C.c_void_p, C.c_void_p, C.c_void_p]),
     "kq_gather_qmm_workspace_bytes": (C.c_size_t, [C.c_longlong, C.c_int, C.c_int, C.c_int]),

@@ -381,6 +381,11 @@ int kq_gather_qmm_seg(const void* x, int x_dtype, long long rows, int K, const v
   return KQ_OK;
 }
 
+size_t kq_moe_decode_workspace_bytes(long long n_entries, int n_experts, int N_mix) {
+  if (n_entries <= KQ_MOE_DIRECT_MAX_ENTRIES || n_experts <= 0) return 0;
+  return kq::moe_grouped_workspace_bytes(n_entries, n_experts, N_mix > 0 ? n_entries * (long long)N_mix * 2 : 0);
+}
+
 int kq_codec_has_moe_glu(const char* kquant_type) {
   const int ci = find_codec(kquant_type);
   return ci == kq::Q4_K ? 1 : 0;
@@ -396,7 +401,7 @@ static int moe_act_code(const char* act) {
 int kq_moe_glu_gather(const void* x, int x_dtype, long long T, int K, const void* gate_w,
                       long long gate_expert_stride_bytes, const void* up_w, long long up_expert_stride_bytes,
                       size_t w_row_bytes, int N, int n_experts, const char* kquant_type, const uint32_t* indices, int R,
-                      const char* act, float limit, void* y, void* stream) {
+                      const char* act, float limit, void* y, void* workspace, size_t workspace_bytes, void* stream) {
   const int ci = find_codec(kquant_type);
   if (ci < 0)
     return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_glu_gather_kq] Unknown kquant_type: '%s'.",
@@ -423,17 +428,41 @@ int kq_moe_glu_gather(const void* x, int x_dtype, long long T, int K, const void
     return fail(KQ_ERR_UNSUPPORTED,
                 "[mlx_kquant.moe_glu_gather_kq] no fused kernel for this call (q4_k, float16 / bfloat16 rows, 16-byte "
                 "aligned operands, at most 65535 entries): compose it from gather_qmm.");
-  cudaError_t e = kq::launch_moe_glu(x_dtype, x, K, static_cast<const uint8_t*>(gate_w), gate_expert_stride_bytes,
+  cudaError_t e;
+  const long long n_entries = T * (long long)R;
+  if (n_entries > KQ_MOE_DIRECT_MAX_ENTRIES && workspace != nullptr) {
+    const size_t need = kq::moe_grouped_workspace_bytes(n_entries, n_experts, 0);
+    if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+      return fail(KQ_ERR_INVALID_ARGUMENT,
+                  "[mlx_kquant.moe_glu_gather_kq] workspace too small or not 256-byte aligned: %zu bytes given, %zu needed.",
+                  workspace_bytes, need);
+    if (kq::moe_grouped_supported(K, (long long)w_row_bytes, false)) {
+      e = kq::launch_moe_glu_grouped(x_dtype, x, K, static_cast<const uint8_t*>(gate_w), gate_expert_stride_bytes,
                                      static_cast<const uint8_t*>(up_w), up_expert_stride_bytes, (long long)w_row_bytes, N,
-                                     n_experts, indices, T * (long long)R, R, a, limit, y,
+                                     n_experts, indices, n_entries, R, a, limit, y, workspace,
                                      static_cast<cudaStream_t>(stream));
+    } else {
+      // rows too long for the grouped kernel's shared memory: per-entry kernel; the grouping is still left in
+      // the workspace for a kq_gather_qmv_mix call that was told to reuse it
+      e = kq::launch_moe_grouping_only(indices, n_entries, n_experts, workspace, static_cast<cudaStream_t>(stream));
+      if (e == cudaSuccess)
+        e = kq::launch_moe_glu(x_dtype, x, K, static_cast<const uint8_t*>(gate_w), gate_expert_stride_bytes,
+                               static_cast<const uint8_t*>(up_w), up_expert_stride_bytes, (long long)w_row_bytes, N,
+                               n_experts, indices, n_entries, R, a, limit, y, static_cast<cudaStream_t>(stream));
+    }
+  } else {
+    e = kq::launch_moe_glu(x_dtype, x, K, static_cast<const uint8_t*>(gate_w), gate_expert_stride_bytes,
+                           static_cast<const uint8_t*>(up_w), up_expert_stride_bytes, (long long)w_row_bytes, N,
+                           n_experts, indices, n_entries, R, a, limit, y, static_cast<cudaStream_t>(stream));
+  }
   if (e != cudaSuccess) return cuda_fail("moe_glu_gather_kq", e);
   return KQ_OK;
 }
 
 int kq_gather_qmv_mix(const void* x, int x_dtype, long long T, int S, int K, const void* w,
                       long long w_expert_stride_bytes, size_t w_row_bytes, int N, int n_experts, const char* kquant_type,
-                      const uint32_t* indices, const float* scores, void* y, void* stream) {
+                      const uint32_t* indices, const float* scores, void* y, void* workspace, size_t workspace_bytes,
+                      int reuse_grouping, void* stream) {
   const int ci = find_codec(kquant_type);
   if (ci < 0)
     return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.gather_qmv_mix_ns_kq] Unknown kquant_type: '%s'.",
@@ -453,9 +482,22 @@ int kq_gather_qmv_mix(const void* x, int x_dtype, long long T, int S, int K, con
     return fail(KQ_ERR_UNSUPPORTED,
                 "[mlx_kquant.gather_qmv_mix_ns_kq] no fused kernel for this call (q4_k, float16 / bfloat16 rows, "
                 "K %% 256 == 0, 16-byte aligned operands, at most 65535 tokens): compose it from gather_qmm.");
-  cudaError_t e = kq::launch_moe_mix(x_dtype, x, K, static_cast<const uint8_t*>(w), w_expert_stride_bytes,
-                                     (long long)w_row_bytes, N, n_experts, indices, scores, T, S, y,
-                                     static_cast<cudaStream_t>(stream));
+  cudaError_t e;
+  const long long n_entries = T * (long long)S;
+  if (n_entries > KQ_MOE_DIRECT_MAX_ENTRIES && workspace != nullptr && N % 8 == 0 &&
+      kq::moe_grouped_supported(K, (long long)w_row_bytes, true)) {
+    const size_t need = kq::moe_grouped_workspace_bytes(n_entries, n_experts, n_entries * (long long)N * 2);
+    if (workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+      return fail(KQ_ERR_INVALID_ARGUMENT,
+                  "[mlx_kquant.gather_qmv_mix_ns_kq] workspace too small or not 256-byte aligned: %zu bytes given, %zu needed.",
+                  workspace_bytes, need);
+    e = kq::launch_moe_mix_grouped(x_dtype, x, K, static_cast<const uint8_t*>(w), w_expert_stride_bytes,
+                                   (long long)w_row_bytes, N, n_experts, indices, scores, T, S, y, workspace,
+                                   reuse_grouping != 0, static_cast<cudaStream_t>(stream));
+  } else {
+    e = kq::launch_moe_mix(x_dtype, x, K, static_cast<const uint8_t*>(w), w_expert_stride_bytes, (long long)w_row_bytes,
+                           N, n_experts, indices, scores, T, S, y, static_cast<cudaStream_t>(stream));
+  }
   if (e != cudaSuccess) return cuda_fail("gather_qmv_mix_ns_kq", e);
   return KQ_OK;
 }

@@ -130,7 +130,7 @@ __global__ void gather_scatter_kernel(const uint32_t* __restrict__ rhs, const ui
   const long long b = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   if (b < n) {
     const uint32_t e = rhs[b];
-    if (e < (uint32_t)n_experts && (long long)lhs[b] < x_batch)
+    if (e < (uint32_t)n_experts && (lhs == nullptr || (long long)lhs[b] < x_batch))
       order[offsets[e] + atomicAdd(&cursor[e], 1)] = (int)b;
   }
 }
@@ -201,6 +201,22 @@ __global__ void tile_map_kernel(const int* __restrict__ offsets, const int* __re
     t[1] = (uint32_t)(start + j * kSegMapTileRows);
     t[2] = (uint32_t)min(kSegMapTileRows, rows - j * kSegMapTileRows);
   }
+}
+
+// Group n entries by expert on the stream: counts / cursor / offsets / unit_base are n_experts + 1 ints each
+// (counts and cursor adjacent, cleared here), order n ints, n_units one int. unit_base[e] = first unit of expert e
+// when every expert's entries are cut into units of `unit` entries; *n_units = their total.
+cudaError_t launch_group_by_expert(const uint32_t* rhs, long long n, int n_experts, int unit, int* counts, int* cursor,
+                                   int* offsets, int* unit_base, int* n_units, int* order, cudaStream_t st) {
+  cudaError_t err = cudaMemsetAsync(counts, 0, (size_t)(reinterpret_cast<char*>(cursor) - reinterpret_cast<char*>(counts)) +
+                                                   (size_t)(n_experts + 1) * 4, st);
+  if (err != cudaSuccess) return err;
+  const int th = 256;
+  const unsigned nb = (unsigned)((n + th - 1) / th);
+  gather_hist_kernel<<<nb, th, 0, st>>>(rhs, nullptr, 0, n, n_experts, counts);
+  gather_scan_kernel<<<1, 1024, 0, st>>>(counts, n_experts, 1, unit, offsets, unit_base, n_units);
+  gather_scatter_kernel<<<nb, th, 0, st>>>(rhs, nullptr, 0, n, n_experts, offsets, cursor, order);
+  return cudaGetLastError();
 }
 
 size_t tile_map_workspace_bytes(int n_experts) { return ((size_t)(3 * (n_experts + 1) + 1) * 4 + 255) & ~(size_t)255; }

@@ -194,4 +194,70 @@ __device__ __forceinline__ void st_unit(const uint8_t* const (&blk)[2 * NT], con
 }
 
 
+// The same product for MX <= 4 activation rows at once: B columns 2 m and 2 m + 1 carry the planes of row m, so
+// the instructions are those of one row. bsb: this lane's column (planes of row min(g / 2, MX - 1), high plane for
+// even g) at the superblock + 8 t; xs: sub-block sums of row 0 at this superblock, row m at xs + m * xs_stride;
+// sx: superblock scale of row 0, row m at sx[m * sx_stride].
+// ydot[r]: dot part of fragment row r for activation row m = t (lanes t >= MX hold nothing useful);
+// ymin[r][m]: this lane's share (sub-blocks 2 t, 2 t + 1) of the min part of fragment row r, activation row m -
+// sum it over the quad at the end.
+template <int NT, int MX>
+__device__ __forceinline__ void st_unit_mx(const uint8_t* const (&blk)[2 * NT], const uint8_t* bsb, const float* xs,
+                                           int xs_stride, const float* sx, int sx_stride, int t, float (&ydot)[2 * NT],
+                                           float (&ymin)[2 * NT][MX]) {
+  uint4 hdr[2 * NT];
+  StScales sw[2 * NT];
+#pragma unroll
+  for (int r = 0; r < 2 * NT; r++) {
+    hdr[r] = *reinterpret_cast<const uint4*>(blk[r]);
+    sw[r] = st_unpack(hdr[r]);
+  }
+  int acc[2 * NT][4];
+#pragma unroll
+  for (int r = 0; r < 2 * NT; r++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[r][j] = 0;
+#pragma unroll
+  for (int p = 0; p < 4; p++) {
+    const uint2 bl = *reinterpret_cast<const uint2*>(bsb + 64 * p);
+    const uint2 bh = *reinterpret_cast<const uint2*>(bsb + 64 * p + 32);
+#pragma unroll
+    for (int T = 0; T < NT; T++) {
+      const uint2 wa = *reinterpret_cast<const uint2*>(blk[2 * T] + 16 + 32 * p + 8 * t);
+      const uint2 wb = *reinterpret_cast<const uint2*>(blk[2 * T + 1] + 16 + 32 * p + 8 * t);
+      const uint32_t scwA = p < 2 ? sw[2 * T].scl : sw[2 * T].sch, scwB = p < 2 ? sw[2 * T + 1].scl : sw[2 * T + 1].sch;
+      int c[4], d[4];
+      st_imma(c, wa.x & 0x0f0f0f0fu, wb.x & 0x0f0f0f0fu, wa.y & 0x0f0f0f0fu, wb.y & 0x0f0f0f0fu, bl.x, bl.y);
+      st_imma(d, wa.x & 0xf0f0f0f0u, wb.x & 0xf0f0f0f0u, wa.y & 0xf0f0f0f0u, wb.y & 0xf0f0f0f0u, bh.x, bh.y);
+      int scA = st_byte(scwA, 2 * (p & 1)), scB = st_byte(scwB, 2 * (p & 1));
+      acc[2 * T][0] += c[0] * scA;
+      acc[2 * T][1] += c[1] * scA;
+      acc[2 * T + 1][0] += c[2] * scB;
+      acc[2 * T + 1][1] += c[3] * scB;
+      scA = st_byte(scwA, 2 * (p & 1) + 1);
+      scB = st_byte(scwB, 2 * (p & 1) + 1);
+      acc[2 * T][2] += d[0] * scA;
+      acc[2 * T][3] += d[1] * scA;
+      acc[2 * T + 1][2] += d[2] * scB;
+      acc[2 * T + 1][3] += d[3] * scB;
+    }
+  }
+  const int sh = 16 * (t & 1);
+  const float sxt = sx[min(t, MX - 1) * sx_stride];
+  float2 xv[MX];
+#pragma unroll
+  for (int m = 0; m < MX; m++) xv[m] = *reinterpret_cast<const float2*>(xs + m * xs_stride + 2 * t);
+#pragma unroll
+  for (int r = 0; r < 2 * NT; r++) {
+    const float2 dd = __half22float2(*reinterpret_cast<const __half2*>(&hdr[r].x));  // (d, dmin)
+    const float f =
+        fmaf((float)acc[r][0], 256.f, (float)acc[r][1]) + fmaf((float)acc[r][2], 256.f, (float)acc[r][3]) * 0.0625f;
+    ydot[r] = fmaf(dd.x * sxt, f, ydot[r]);
+    const uint32_t mw = (t & 2) ? sw[r].mnh : sw[r].mnl;
+    const float m0 = dd.y * (float)((mw >> sh) & 0xffu), m1 = dd.y * (float)((mw >> (sh + 8)) & 0xffu);
+#pragma unroll
+    for (int m = 0; m < MX; m++) ymin[r][m] = fmaf(m1, xv[m].y, fmaf(m0, xv[m].x, ymin[r][m]));
+  }
+}
+
 }  // namespace kq

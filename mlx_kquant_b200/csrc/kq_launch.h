@@ -96,6 +96,18 @@ cudaError_t launch_moe_glu(int x_dtype, const void* x, int K, const uint8_t* wg,
 cudaError_t launch_moe_mix(int x_dtype, const void* x, int K, const uint8_t* w, long long stride_w, long long row_bytes,
                            int N, int n_experts, const uint32_t* idx, const float* scores, long long T, int S, void* y,
                            cudaStream_t st);
+// grouped forms for more entries (tasks of up to four entries per expert); scratch from moe_grouped_workspace_bytes
+size_t moe_grouped_workspace_bytes(long long n_entries, int n_experts, long long d_bytes);
+bool moe_grouped_supported(int K, long long row_bytes, bool rows_kernel);
+cudaError_t launch_moe_grouping_only(const uint32_t* idx, long long n_entries, int n_experts, void* workspace,
+                                     cudaStream_t st);
+cudaError_t launch_moe_glu_grouped(int x_dtype, const void* x, int K, const uint8_t* wg, long long stride_g,
+                                   const uint8_t* wu, long long stride_u, long long row_bytes, int F, int n_experts,
+                                   const uint32_t* idx, long long n_entries, int R, int act, float limit, void* y,
+                                   void* workspace, cudaStream_t st);
+cudaError_t launch_moe_mix_grouped(int x_dtype, const void* x, int K, const uint8_t* w, long long stride_w,
+                                   long long row_bytes, int N, int n_experts, const uint32_t* idx, const float* scores,
+                                   long long T, int S, void* y, void* workspace, bool reuse_grouping, cudaStream_t st);
 cudaError_t launch_router_topk(const void* logits, int dtype, int T, int E, int top_k, int norm, int shared, int scoring,
                                const float* pes, const float* bias, float scale, uint32_t* indices, float* scores,
                                cudaStream_t st);
@@ -125,6 +137,10 @@ cudaError_t launch_gather(int codec, int x_dtype, const void* x, long long x_bat
                           int n_experts, long long expert_stride, long long row_bytes, int N, const uint32_t* lhs,
                           const uint32_t* rhs, long long n_entries, void* y, void* workspace, bool allow_grouped,
                           cudaStream_t st);
+
+// memset + histogram + scan + scatter of kq_gather.cu for other callers: see the definition.
+cudaError_t launch_group_by_expert(const uint32_t* rhs, long long n, int n_experts, int unit, int* counts, int* cursor,
+                                   int* offsets, int* unit_base, int* n_units, int* order, cudaStream_t st);
 
 // The body of kq_gather_qmm; allow_grouped = false pins the decode regime (fixed-size scratch);
 // builtin_scratch = true words a too-small workspace as the limit of the library's fixed array.

@@ -306,6 +306,201 @@ __global__ void __launch_bounds__(kMdThreads, 2) moe_mix_kernel(const MixArgs a,
   }
 }
 
+// ---------------------------------------------------------------------------------- grouped by expert
+// From a few dozen routed entries on, entries that share an expert share its weight stream: the entries are
+// grouped by expert on the device (kq_gather.cu) and cut into tasks of at most kTaskEntries entries. A CTA brings
+// its rows of the task's expert into shared memory once and multiplies them by the task's activation rows four
+// at a time (the B operand has room for four rows' byte planes).
+constexpr int kTaskEntries = 16;
+struct Task4 {
+  int expert, m;
+  int ent[kTaskEntries];   // entry indices; slots past m repeat the last one
+};
+
+__global__ void moe_tasks4_kernel(const int* __restrict__ offsets, const int* __restrict__ task_base,
+                                  const int* __restrict__ order, Task4* tasks) {
+  const int e = blockIdx.x;
+  const int o0 = offsets[e], c = offsets[e + 1] - o0;
+  const int nt = (c + kTaskEntries - 1) / kTaskEntries, tb = task_base[e];
+  for (int k = threadIdx.x; k < nt; k += blockDim.x) {
+    Task4 t;
+    t.expert = e;
+    t.m = min(kTaskEntries, c - kTaskEntries * k);
+#pragma unroll
+    for (int j = 0; j < kTaskEntries; j++) t.ent[j] = order[o0 + kTaskEntries * k + min(j, t.m - 1)];
+    tasks[tb + k] = t;
+  }
+}
+
+__device__ __forceinline__ float md_pick4(const float (&v)[4], int t) {
+  return t == 0 ? v[0] : (t == 1 ? v[1] : (t == 2 ? v[2] : v[3]));
+}
+
+// shared memory: gate tile | up tile | planes 4 x 2 K | XS 4 x K / 32 | SX 4 x padded K / 256 | red 8 x 32 x 4 | mbar
+inline int glu4_smem_bytes(int K, int row_bytes) {
+  return 8 * md_group_stride(row_bytes) + 8 * K + (K / 32) * 16 + (((K / 256) + 3) & ~3) * 16 + kMdWarps * 32 * 16 + 16;
+}
+
+template <typename XT>
+__global__ void __launch_bounds__(kMdThreads, 3)
+moe_glu_tasks_kernel(const GluArgs a, const Task4* __restrict__ tasks, const int* __restrict__ n_tasks,
+                     int* __restrict__ error_word) {
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  if ((int)blockIdx.y >= *n_tasks) return;
+  extern __shared__ __align__(128) uint8_t md_dyn[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int K = a.K, nchunks = K >> 8, ncp = (nchunks + 3) & ~3, RB = a.row_bytes;
+  const int gb = 4 * RB, GS = gb + ((32 - (gb & 127)) & 127);
+  uint8_t* wbuf = md_dyn;
+  uint8_t* planes = wbuf + 8 * GS;
+  float* XS = reinterpret_cast<float*>(planes + 8 * K);
+  float* SX = XS + 4 * (K / 32);
+  float* red = SX + 4 * ncp;
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(red + kMdWarps * 32 * 4);
+  const Task4 tk = tasks[blockIdx.y];
+  const int f0 = blockIdx.x * 16, rows = min(16, a.F - f0);
+  if (threadIdx.x == 0) {
+    st_mbar_init(mbar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    st_mbar_expect_tx(mbar, (uint32_t)(2 * rows * RB));
+    md_copy_tile(wbuf, a.wg + (long long)tk.expert * a.stride_g + (long long)f0 * RB, rows, RB, GS, mbar);
+    md_copy_tile(wbuf + 4 * GS, a.wu + (long long)tk.expert * a.stride_u + (long long)f0 * RB, rows, RB, GS, mbar);
+  }
+  const uint8_t* bcol = planes + min(g >> 1, 3) * 2 * K + (g & 1) * K + 8 * t;
+  const int lrA = min(4 * (g & 3) + (g >> 2), rows - 1), lrB = min(4 * (g & 3) + (g >> 2) + 2, rows - 1);
+  const uint8_t* base[4] = {wbuf + (lrA >> 2) * GS + (lrA & 3) * RB, wbuf + (lrB >> 2) * GS + (lrB & 3) * RB,
+                            wbuf + (4 + (lrA >> 2)) * GS + (lrA & 3) * RB, wbuf + (4 + (lrB >> 2)) * GS + (lrB & 3) * RB};
+  const int rA = 4 * (g & 3) + (g >> 2);
+  const int rrow[4] = {rA, rA + 2, 16 + rA, 16 + rA + 2};
+  for (int m0 = 0; m0 < tk.m; m0 += 4) {   // four activation rows per pass over the tile in shared memory
+    for (int sb = warp; sb < nchunks; sb += kMdWarps) {
+#pragma unroll
+      for (int m = 0; m < 4; m++) {
+        const XT* x = static_cast<const XT*>(a.x) + (long long)(tk.ent[min(m0 + m, kTaskEntries - 1)] / a.R) * K;
+        st_quantize<XT>(st_ld_cg16(x + sb * 256 + lane * 8), sb, lane, K, planes + m * 2 * K, XS + m * (K / 32),
+                        SX + m * ncp);
+      }
+    }
+    __syncthreads();  // first pass: the barrier is initialised
+    if (m0 == 0 && !md_wait(mbar, 0, error_word)) return;
+    float ydot[4] = {0.f, 0.f, 0.f, 0.f}, ymin[4][4] = {};
+    for (int sb = warp; sb < nchunks; sb += kMdWarps) {
+      const uint8_t* const blk[4] = {base[0] + sb * 144, base[1] + sb * 144, base[2] + sb * 144, base[3] + sb * 144};
+      st_unit_mx<2, 4>(blk, bcol + sb * 256, XS + sb * 8, K / 32, SX + sb, ncp, t, ydot, ymin);
+    }
+#pragma unroll
+    for (int r = 0; r < 4; r++) {
+#pragma unroll
+      for (int m = 0; m < 4; m++) {
+        ymin[r][m] += __shfl_xor_sync(0xffffffffu, ymin[r][m], 1);
+        ymin[r][m] += __shfl_xor_sync(0xffffffffu, ymin[r][m], 2);
+      }
+      red[(warp * 32 + rrow[r]) * 4 + t] = ydot[r] - md_pick4(ymin[r], t);   // activation row m0 + t of this lane
+    }
+    __syncthreads();
+    if (threadIdx.x < 64) {
+      const int r = threadIdx.x & 15, m = threadIdx.x >> 4;
+      if (r < rows && m0 + m < tk.m) {
+        float gs = 0.f, us = 0.f;
+#pragma unroll
+        for (int w = 0; w < kMdWarps; w++) {
+          gs += red[(w * 32 + r) * 4 + m];
+          us += red[(w * 32 + 16 + r) * 4 + m];
+        }
+        md_store(static_cast<XT*>(a.y) + (long long)tk.ent[m0 + m] * a.F + f0 + r, md_act(gs, us, a.act, a.limit));
+      }
+    }
+    __syncthreads();   // red and the planes are free for the next pass
+  }
+}
+
+struct RowsArgs {
+  const void* x;            // [entries, K]: row of entry b = x + b * K
+  const uint8_t* w;
+  long long stride_w;
+  int row_bytes, K, N;
+  void* y;                  // [entries, N]
+};
+
+// 128 rows per CTA, one 16-row tile per warp (for short rows: few superblocks, nothing to split over the warps)
+// shared memory: 32 groups | planes 4 x 2 K | XS 4 x K / 32 | SX 4 x padded K / 256 | mbar
+inline int rows4_smem_bytes(int K, int row_bytes) {
+  return 32 * md_group_stride(row_bytes) + 8 * K + (K / 32) * 16 + (((K / 256) + 3) & ~3) * 16 + 16;
+}
+
+template <typename XT>
+__global__ void __launch_bounds__(kMdThreads, 3)
+moe_rows_tasks_kernel(const RowsArgs a, const Task4* __restrict__ tasks, const int* __restrict__ n_tasks,
+                      int* __restrict__ error_word) {
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  if ((int)blockIdx.y >= *n_tasks) return;
+  extern __shared__ __align__(128) uint8_t md_dyn[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int K = a.K, nchunks = K >> 8, ncp = (nchunks + 3) & ~3, RB = a.row_bytes;
+  const int gb = 4 * RB, GS = gb + ((32 - (gb & 127)) & 127);
+  uint8_t* wbuf = md_dyn;
+  uint8_t* planes = wbuf + 32 * GS;
+  float* XS = reinterpret_cast<float*>(planes + 8 * K);
+  float* SX = XS + 4 * (K / 32);
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(SX + 4 * ncp);
+  const Task4 tk = tasks[blockIdx.y];
+  const int n0 = blockIdx.x * 128, rows = min(128, a.N - n0);
+  if (warp == 0) {
+    if (lane == 0) {
+      st_mbar_init(mbar, 1);
+      asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+      st_mbar_expect_tx(mbar, (uint32_t)(rows * RB));
+    }
+    __syncwarp();
+    const int r = 4 * lane;   // one group of four rows per lane
+    if (r < rows)
+      st_bulk_g2s(wbuf + lane * GS, a.w + (long long)tk.expert * a.stride_w + (long long)(n0 + r) * RB,
+                  (uint32_t)(min(4, rows - r) * RB), mbar);
+  }
+  const int rowsT = rows - 16 * warp;   // rows of this warp's tile (<= 0: the warp only helps quantizing)
+  const uint8_t* bcol = planes + min(g >> 1, 3) * 2 * K + (g & 1) * K + 8 * t;
+  const int rA = 4 * (g & 3) + (g >> 2);
+  const int hi = max(min(rowsT, 16) - 1, 0);
+  const int lrA = 16 * warp + min(rA, hi), lrB = 16 * warp + min(rA + 2, hi);
+  const uint8_t* pA = wbuf + (lrA >> 2) * GS + (lrA & 3) * RB;
+  const uint8_t* pB = wbuf + (lrB >> 2) * GS + (lrB & 3) * RB;
+  for (int m0 = 0; m0 < tk.m; m0 += 4) {
+    for (int u = warp; u < 4 * nchunks; u += kMdWarps) {
+      const int m = u / nchunks, sb = u - m * nchunks;
+      const XT* x = static_cast<const XT*>(a.x) + (long long)tk.ent[min(m0 + m, kTaskEntries - 1)] * K;
+      st_quantize<XT>(st_ld_cg16(x + sb * 256 + lane * 8), sb, lane, K, planes + m * 2 * K, XS + m * (K / 32),
+                      SX + m * ncp);
+    }
+    __syncthreads();
+    if (m0 == 0 && !md_wait(mbar, 0, error_word)) return;
+    if (rowsT > 0) {
+      float ydot[2] = {0.f, 0.f}, ymin[2][4] = {};
+      for (int sb = 0; sb < nchunks; sb++) {
+        const uint8_t* const blk[2] = {pA + sb * 144, pB + sb * 144};
+        st_unit_mx<1, 4>(blk, bcol + sb * 256, XS + sb * 8, K / 32, SX + sb, ncp, t, ydot, ymin);
+      }
+#pragma unroll
+      for (int r = 0; r < 2; r++) {
+#pragma unroll
+        for (int m = 0; m < 4; m++) {
+          ymin[r][m] += __shfl_xor_sync(0xffffffffu, ymin[r][m], 1);
+          ymin[r][m] += __shfl_xor_sync(0xffffffffu, ymin[r][m], 2);
+        }
+      }
+      if (m0 + t < tk.m) {
+        XT* out = static_cast<XT*>(a.y) + (long long)tk.ent[m0 + t] * a.N + n0 + 16 * warp;
+        if (rA < rowsT) md_store(out + rA, ydot[0] - md_pick4(ymin[0], t));
+        if (rA + 2 < rowsT) md_store(out + rA + 2, ydot[1] - md_pick4(ymin[1], t));
+      }
+    }
+    __syncthreads();   // the planes are free for the next pass
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ router
 struct RouterArgs {
   const void* logits;       // [T, E + shared]
@@ -454,6 +649,126 @@ cudaError_t md_launch(KernelT kern, dim3 grid, int smem, const ArgsT& a, cudaStr
 }
 
 }  // namespace
+
+// ---- grouped forms: scratch = grouping arrays + task list (+ the per-entry products of the down stage)
+struct MoeWs {
+  size_t counts, cursor, offsets, task_base, n_tasks, order, tasks, d, total;
+  long long max_tasks;
+};
+static MoeWs moe_ws_layout(long long n_entries, int n_experts, long long d_bytes) {
+  auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+  MoeWs L{};
+  const size_t e1 = (size_t)(n_experts + 1) * 4;
+  L.counts = 0;
+  L.cursor = e1;
+  L.offsets = 2 * e1;
+  L.task_base = 3 * e1;
+  L.n_tasks = 4 * e1;
+  L.order = up(4 * e1 + 4);
+  L.max_tasks = n_entries / kTaskEntries + n_experts + 1;
+  L.tasks = up(L.order + (size_t)n_entries * 4);
+  L.d = up(L.tasks + (size_t)L.max_tasks * sizeof(Task4));
+  L.total = up(L.d + (size_t)d_bytes);
+  return L;
+}
+
+size_t moe_grouped_workspace_bytes(long long n_entries, int n_experts, long long d_bytes) {
+  return moe_ws_layout(n_entries, n_experts, d_bytes).total;
+}
+
+static cudaError_t moe_build_tasks(const uint32_t* idx, long long n_entries, int n_experts, uint8_t* ws, const MoeWs& L,
+                                   cudaStream_t st) {
+  int* offsets = reinterpret_cast<int*>(ws + L.offsets);
+  int* task_base = reinterpret_cast<int*>(ws + L.task_base);
+  int* order = reinterpret_cast<int*>(ws + L.order);
+  cudaError_t e = launch_group_by_expert(idx, n_entries, n_experts, kTaskEntries, reinterpret_cast<int*>(ws + L.counts),
+                                         reinterpret_cast<int*>(ws + L.cursor), offsets, task_base,
+                                         reinterpret_cast<int*>(ws + L.n_tasks), order, st);
+  if (e != cudaSuccess) return e;
+  moe_tasks4_kernel<<<n_experts, 64, 0, st>>>(offsets, task_base, order, reinterpret_cast<Task4*>(ws + L.tasks));
+  return cudaGetLastError();
+}
+
+template <typename KernelT, typename ArgsT>
+static cudaError_t md_launch_tasks(KernelT kern, dim3 grid, int smem, const ArgsT& a, const Task4* tasks,
+                                   const int* n_tasks, cudaStream_t st) {
+  int* err = device_error_word();
+  if (err == nullptr) return cudaErrorUnknown;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kMdThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  return cudaLaunchKernelEx(&cfg, kern, a, tasks, n_tasks, err);
+}
+
+// the grouping alone (for a caller whose own grouped kernel does not apply but whose workspace is handed on)
+cudaError_t launch_moe_grouping_only(const uint32_t* idx, long long n_entries, int n_experts, void* workspace,
+                                     cudaStream_t st) {
+  const MoeWs L = moe_ws_layout(n_entries, n_experts, 0);
+  return moe_build_tasks(idx, n_entries, n_experts, static_cast<uint8_t*>(workspace), L, st);
+}
+
+bool moe_grouped_supported(int K, long long row_bytes, bool rows_kernel) {
+  const int smem = rows_kernel ? rows4_smem_bytes(K, (int)row_bytes) : glu4_smem_bytes(K, (int)row_bytes);
+  return smem <= 110 * 1024;   // two CTAs per SM
+}
+
+cudaError_t launch_moe_glu_grouped(int x_dtype, const void* x, int K, const uint8_t* wg, long long stride_g,
+                                   const uint8_t* wu, long long stride_u, long long row_bytes, int F, int n_experts,
+                                   const uint32_t* idx, long long n_entries, int R, int act, float limit, void* y,
+                                   void* workspace, cudaStream_t st) {
+  if (n_entries <= 0 || F <= 0) return cudaSuccess;
+  const MoeWs L = moe_ws_layout(n_entries, n_experts, 0);
+  if (L.max_tasks > 65535) return cudaErrorInvalidConfiguration;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  cudaError_t e = moe_build_tasks(idx, n_entries, n_experts, ws, L, st);
+  if (e != cudaSuccess) return e;
+  GluArgs a{x, wg, wu, stride_g, stride_u, (int)row_bytes, K, F, R, (int)n_entries, n_experts, idx, y, act, limit};
+  const int smem = glu4_smem_bytes(K, (int)row_bytes);
+  const dim3 grid((F + 15) / 16, (unsigned)L.max_tasks, 1);
+  const Task4* tasks = reinterpret_cast<const Task4*>(ws + L.tasks);
+  const int* nt = reinterpret_cast<const int*>(ws + L.n_tasks);
+  static bool done_h[16] = {}, done_b[16] = {};
+  if (x_dtype == F16) {
+    if ((e = md_set_smem(moe_glu_tasks_kernel<__half>, kMdMaxSmem, done_h)) != cudaSuccess) return e;
+    return md_launch_tasks(moe_glu_tasks_kernel<__half>, grid, smem, a, tasks, nt, st);
+  }
+  if ((e = md_set_smem(moe_glu_tasks_kernel<__nv_bfloat16>, kMdMaxSmem, done_b)) != cudaSuccess) return e;
+  return md_launch_tasks(moe_glu_tasks_kernel<__nv_bfloat16>, grid, smem, a, tasks, nt, st);
+}
+
+// d[b] = x[b] . W[idx[b]]^T for every entry b (entries grouped by expert), then y[t] = sum_s scores[t, s] d[t S + s]
+cudaError_t launch_moe_mix_grouped(int x_dtype, const void* x, int K, const uint8_t* w, long long stride_w,
+                                   long long row_bytes, int N, int n_experts, const uint32_t* idx, const float* scores,
+                                   long long T, int S, void* y, void* workspace, bool reuse_grouping,
+                                   cudaStream_t st) {
+  const long long n_entries = T * S;
+  if (n_entries <= 0 || N <= 0) return cudaSuccess;
+  const MoeWs L = moe_ws_layout(n_entries, n_experts, n_entries * (long long)N * 2);
+  if (L.max_tasks > 65535) return cudaErrorInvalidConfiguration;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  cudaError_t e = cudaSuccess;
+  // reuse_grouping: the workspace still holds the task list that launch_moe_glu_grouped built from these indices
+  if (!reuse_grouping && (e = moe_build_tasks(idx, n_entries, n_experts, ws, L, st)) != cudaSuccess) return e;
+  // entries of experts out of range get no task: their d rows must not carry old bytes into the weighted sum
+  if ((e = cudaMemsetAsync(ws + L.d, 0, (size_t)n_entries * N * 2, st)) != cudaSuccess) return e;
+  RowsArgs a{x, w, stride_w, (int)row_bytes, K, N, ws + L.d};
+  const int smem = rows4_smem_bytes(K, (int)row_bytes);
+  const dim3 grid((N + 127) / 128, (unsigned)L.max_tasks, 1);
+  const Task4* tasks = reinterpret_cast<const Task4*>(ws + L.tasks);
+  const int* nt = reinterpret_cast<const int*>(ws + L.n_tasks);
+  static bool done_h[16] = {}, done_b[16] = {};
+  if (x_dtype == F16) {
+    if ((e = md_set_smem(moe_rows_tasks_kernel<__half>, kMdMaxSmem, done_h)) != cudaSuccess) return e;
+    e = md_launch_tasks(moe_rows_tasks_kernel<__half>, grid, smem, a, tasks, nt, st);
+  } else {
+    if ((e = md_set_smem(moe_rows_tasks_kernel<__nv_bfloat16>, kMdMaxSmem, done_b)) != cudaSuccess) return e;
+    e = md_launch_tasks(moe_rows_tasks_kernel<__nv_bfloat16>, grid, smem, a, tasks, nt, st);
+  }
+  if (e != cudaSuccess) return e;
+  return launch_moe_combine(x_dtype, ws + L.d, scores, T, S, N, y, false, st);
+}
 
 bool moe_decode_supported(int codec, int x_dtype, int K, long long row_bytes, const void* x, const void* w0,
                           long long stride0, const void* w1, long long stride1) {

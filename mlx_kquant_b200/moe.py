@@ -95,7 +95,20 @@ def fuse_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
 
 
 _DT = {torch.float32: _lib.KQ_F32, torch.float16: _lib.KQ_F16, torch.bfloat16: _lib.KQ_BF16}
-FUSED_DECODE_MAX_ENTRIES = 256   # routed (token, expert) entries up to which the per-entry decode kernels are used
+FUSED_MAX_ENTRIES = 512   # beyond (measured on the 128-expert block): the three-gather composition is faster
+
+
+def _fused_regime(rows: int, n_experts: int) -> bool:
+    """The fused decode kernels serve calls below the prefill regime of gather_qmm (512 or more routed entries
+    with 32 or more per expert on average go to the tensor-core tile kernel)."""
+    return not (rows >= 512 and rows >= 32 * n_experts) and rows <= FUSED_MAX_ENTRIES
+
+
+def _decode_ws(n_entries: int, n_experts: int, n_mix: int, device):
+    need = _lib.lib().kq_moe_decode_workspace_bytes(n_entries, n_experts, n_mix)
+    if need == 0:
+        return None
+    return torch.empty(need, dtype=torch.uint8, device=device)
 
 
 def codec_has_moe_glu(kquant_type: str) -> bool:
@@ -107,7 +120,7 @@ def _u32(idx: torch.Tensor, device) -> torch.Tensor:
     return idx.to(device=device, dtype=torch.int32).contiguous()
 
 
-def moe_glu_gather_kq(x, gate_w, up_w, kquant_type, indices, act="silu", limit=0.0):
+def moe_glu_gather_kq(x, gate_w, up_w, kquant_type, indices, act="silu", limit=0.0, *, workspace=None):
     """The reference's moe_glu_gather_kq (src/kquant.h:335-357): x [T, K], gate_w / up_w [E, N, bytes] (views of
     one stacked tensor are fine: only the last two dims must be dense), indices [T, R] ->
     [T, R, N] = act(x . Wg[e]^T) * (x . Wu[e]^T) in x's dtype, one rounding. Raises NotImplementedError when the
@@ -128,9 +141,12 @@ def moe_glu_gather_kq(x, gate_w, up_w, kquant_type, indices, act="silu", limit=0
     idx = _u32(indices, x.device)
     y = torch.empty((T, R, N), dtype=x.dtype, device=x.device)
     with torch.cuda.device(x.device):
+        ws = workspace if workspace is not None else _decode_ws(T * R, E, 0, x.device)
         _lib.check(_lib.lib().kq_moe_glu_gather(xc.data_ptr(), _DT[x.dtype], T, K, gate_w.data_ptr(), gate_w.stride(0),
                                                 up_w.data_ptr(), up_w.stride(0), rb, N, E, kquant_type.encode(),
                                                 idx.data_ptr(), R, act.encode(), float(limit), y.data_ptr(),
+                                                ws.data_ptr() if ws is not None else None,
+                                                ws.numel() if ws is not None else 0,
                                                 torch.cuda.current_stream(x.device).cuda_stream))
     return y
 
@@ -143,7 +159,7 @@ def gather_qmv_kq(x, w, kquant_type, indices):
     return y.reshape(T, R, -1)
 
 
-def gather_qmv_mix_ns_kq(x, w, kquant_type, indices, scores):
+def gather_qmv_mix_ns_kq(x, w, kquant_type, indices, scores, *, workspace=None, reuse_grouping=False):
     """The reference's gather_qmv_mix_ns_kq (src/kquant.h:549-558): x [T, S, K], w [E, N, bytes], indices [T, S],
     scores [T, S] -> [T, N] = sum_s scores[t, s] * (x[t, s] . W[e_s]^T), accumulated in float32, one rounding."""
     if x.dim() != 3 or indices.shape != x.shape[:2] or scores.shape != x.shape[:2]:
@@ -159,14 +175,18 @@ def gather_qmv_mix_ns_kq(x, w, kquant_type, indices, scores):
     sc = scores.to(device=x.device, dtype=torch.float32).contiguous()
     y = torch.empty((T, N), dtype=x.dtype, device=x.device)
     with torch.cuda.device(x.device):
+        ws = workspace if workspace is not None else _decode_ws(T * S, E, N, x.device)
         _lib.check(_lib.lib().kq_gather_qmv_mix(xc.data_ptr(), _DT[x.dtype], T, S, K, w.data_ptr(), w.stride(0), rb, N, E,
                                                 kquant_type.encode(), idx.data_ptr(), sc.data_ptr(), y.data_ptr(),
+                                                ws.data_ptr() if ws is not None else None,
+                                                ws.numel() if ws is not None else 0,
+                                                1 if (reuse_grouping and ws is not None) else 0,
                                                 torch.cuda.current_stream(x.device).cuda_stream))
     return y
 
 
 def _fused_decode_ok(x, kquant_type, rows, *stacks) -> bool:
-    if not (x.is_cuda and x.dtype in (torch.float16, torch.bfloat16) and rows <= FUSED_DECODE_MAX_ENTRIES):
+    if not (x.is_cuda and x.dtype in (torch.float16, torch.bfloat16) and _fused_regime(rows, stacks[0].shape[0])):
         return False
     if not codec_has_moe_glu(kquant_type):
         return False
@@ -197,8 +217,11 @@ def moe_glu(x, w_gate, w_up, w_down, kquant_type, expert_ids, expert_probs, *, s
         else:
             wg_v, wu_v = w_gate, w_up
         if _fused_decode_ok(x, kquant_type, rows, wg_v, wu_v, w_down):
-            h = moe_glu_gather_kq(x, wg_v, wu_v, kquant_type, expert_ids)
-            return gather_qmv_mix_ns_kq(h, w_down, kquant_type, expert_ids, expert_probs)
+            # one scratch buffer for both launches: the second reuses the grouping the first made
+            ws = _decode_ws(rows, w_down.shape[0], w_down.shape[1], x.device)
+            h = moe_glu_gather_kq(x, wg_v, wu_v, kquant_type, expert_ids, workspace=ws)
+            return gather_qmv_mix_ns_kq(h, w_down, kquant_type, expert_ids, expert_probs, workspace=ws,
+                                        reuse_grouping=True)
     flat_e = expert_ids.reshape(rows)
     tok = torch.arange(T, device=x.device).repeat_interleave(k)
     # Rows go in routing order: gather_qmm groups them by expert on the device itself, so the explicit
@@ -259,8 +282,11 @@ def moe_glu_expert_parallel(x, w_gate, w_up, w_down, kquant_type, expert_ids, ex
         else:
             wg_v, wu_v = w_gate, w_up
         if _fused_decode_ok(x, kquant_type, rows, wg_v, wu_v, w_down):
-            h = moe_glu_gather_kq(x, wg_v, wu_v, kquant_type, expert_ids)
-            return gather_qmv_mix_ns_kq(h, w_down, kquant_type, expert_ids, expert_probs)
+            # one scratch buffer for both launches: the second reuses the grouping the first made
+            ws = _decode_ws(rows, w_down.shape[0], w_down.shape[1], x.device)
+            h = moe_glu_gather_kq(x, wg_v, wu_v, kquant_type, expert_ids, workspace=ws)
+            return gather_qmv_mix_ns_kq(h, w_down, kquant_type, expert_ids, expert_probs, workspace=ws,
+                                        reuse_grouping=True)
     flat_e = expert_ids.reshape(rows)
     tok = torch.arange(T, device=x.device).repeat_interleave(k)
     owner = expert_owner(flat_e, n_experts, world)

@@ -66,7 +66,7 @@ def test_moe_glu_gather_kq_stacked_views_and_skipped_entries(oracle):
     g_v, u_v = wgu[:, :F], wgu[:, F:]
     _lib.check(L.kq_moe_glu_gather(x.data_ptr(), _lib.KQ_BF16, T, K, g_v.data_ptr(), g_v.stride(0), u_v.data_ptr(),
                                    u_v.stride(0), g_v.shape[2], F, E, b"q4_k", idx.data_ptr(), R, b"silu", 0.0,
-                                   y.data_ptr(), torch.cuda.current_stream().cuda_stream))
+                                   y.data_ptr(), None, 0, torch.cuda.current_stream().cuda_stream))
     torch.cuda.synchronize()
     xs = to_f32(store, "bf16").astype(np.float64)
     Wg = oracle.dequantize(wg, "q4_k", "f32").astype(np.float64)
@@ -147,9 +147,9 @@ def test_indices_written_by_the_preceding_launch(oracle):
                                         idx.data_ptr(), sc.data_ptr(), s.cuda_stream))
         _lib.check(L.kq_moe_glu_gather(x.data_ptr(), _lib.KQ_F16, T, H, wg.data_ptr(), wg.stride(0), wu.data_ptr(),
                                        wu.stride(0), wg.shape[2], F, E, b"q4_k", idx.data_ptr(), k, b"silu", 0.0,
-                                       h.data_ptr(), s.cuda_stream))
+                                       h.data_ptr(), None, 0, s.cuda_stream))
         _lib.check(L.kq_gather_qmv_mix(h.data_ptr(), _lib.KQ_F16, T, k, F, wd.data_ptr(), wd.stride(0), wd.shape[2], H, E,
-                                       b"q4_k", idx.data_ptr(), sc.data_ptr(), y.data_ptr(), s.cuda_stream))
+                                       b"q4_k", idx.data_ptr(), sc.data_ptr(), y.data_ptr(), None, 0, 0, s.cuda_stream))
 
     with torch.cuda.stream(stream):
         block(stream)
@@ -201,3 +201,53 @@ def test_router_kernel_matches_host_statement(case):
             ok = same
             np.testing.assert_allclose(s_d.cpu().numpy()[ok.numpy()], s_h.numpy()[ok.numpy()], rtol=2e-5, atol=1e-6)
             assert int(ok.sum()) >= T - 2
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+def test_grouped_forms_beyond_the_direct_limit(oracle, dt):
+    """More than KQ_MOE_DIRECT_MAX_ENTRIES entries: entries grouped by expert, four per pass over the weights.
+    One expert index is out of range (its rows stay unwritten / count as zero in the mix)."""
+    E, F, K, T, R = 7, 104, 512, 60, 4          # 240 entries; F = 104: last tile of 8 rows, last 128-row block ragged
+    wg, wu, wdn = experts(E, F, K, 71), experts(E, F, K, 72), experts(E, 200, 768, 73)
+    rng = np.random.default_rng(74)
+    x, store = x_to_torch(rng.normal(0, 1, (T, K)).astype(np.float32), dt)
+    ids = rng.integers(0, E, (T, R))
+    ids[5, 2] = E + 2
+    idt = torch.from_numpy(ids).cuda()
+    y = torch.full((T, R, F), 3.0, dtype=x.dtype, device="cuda")
+    L = _lib.lib()
+    code = _lib.KQ_F16 if dt == "f16" else _lib.KQ_BF16
+    wgd, wud = torch.from_numpy(wg).cuda(), torch.from_numpy(wu).cuda()
+    idx = idt.to(torch.int32).contiguous()
+    ws = torch.empty(L.kq_moe_decode_workspace_bytes(T * R, E, 0), dtype=torch.uint8, device="cuda")
+    assert ws.numel() > 0
+    _lib.check(L.kq_moe_glu_gather(x.data_ptr(), code, T, K, wgd.data_ptr(), wgd.stride(0), wud.data_ptr(), wud.stride(0),
+                                   wgd.shape[2], F, E, b"q4_k", idx.data_ptr(), R, b"silu", 0.0, y.data_ptr(),
+                                   ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    xs = to_f32(store, dt).astype(np.float64)
+    Wg = oracle.dequantize(wg, "q4_k", "f32").astype(np.float64)
+    Wu = oracle.dequantize(wu, "q4_k", "f32").astype(np.float64)
+    got = y_to_f32(y)
+    assert (got[5, 2] == 3.0).all()
+    ok = ids < E
+    ref = np.zeros((T, R, F))
+    for t in range(T):
+        for r in range(R):
+            if ok[t, r]:
+                ref[t, r] = act_ref(xs[t] @ Wg[ids[t, r]].T, xs[t] @ Wu[ids[t, r]].T, "silu", 0)
+    assert_close(got[ok], ref[ok], dt, 2e-3)
+    # the same call without a workspace takes the per-entry kernel: same values up to summation order
+    y2 = moe_glu_gather_kq(x[:8], wgd, wud, "q4_k", idt[:8])
+    assert float((y2.float() - y[:8].float())[torch.from_numpy(ok[:8]).cuda()].abs().max()) <= 2e-2 * float(y.float().abs().max())
+
+    # down stage with the weighted sum: x [T, S, 768], N = 200
+    S = R
+    xm, storem = x_to_torch(rng.normal(0, 1, (T, S, 768)).astype(np.float32), dt)
+    sc = rng.uniform(0.05, 0.4, (T, S)).astype(np.float32)
+    ym = gather_qmv_mix_ns_kq(xm, torch.from_numpy(wdn).cuda(), "q4_k", idt, torch.from_numpy(sc).cuda())
+    xms = to_f32(storem, dt).astype(np.float64)
+    Wd = oracle.dequantize(wdn, "q4_k", "f32").astype(np.float64)
+    refm = np.stack([sum(sc[t, s] * (xms[t, s] @ Wd[ids[t, s]].T) for s in range(S) if ok[t, s]) for t in range(T)])
+    err = np.linalg.norm(y_to_f32(ym) - refm) / np.linalg.norm(refm)
+    assert err < 4e-3, err          # every slot's product is rounded once before the weighted sum
