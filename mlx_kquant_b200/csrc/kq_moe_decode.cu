@@ -376,12 +376,15 @@ moe_glu_tasks_kernel(const GluArgs a, const Task4* __restrict__ tasks, const int
   const int rrow[4] = {rA, rA + 2, 16 + rA, 16 + rA + 2};
   for (int m0 = 0; m0 < tk.m; m0 += 4) {   // four activation rows per pass over the tile in shared memory
     for (int sb = warp; sb < nchunks; sb += kMdWarps) {
+      uint4 raw[4];   // the four loads in flight together
 #pragma unroll
       for (int m = 0; m < 4; m++) {
         const XT* x = static_cast<const XT*>(a.x) + (long long)(tk.ent[min(m0 + m, kTaskEntries - 1)] / a.R) * K;
-        st_quantize<XT>(st_ld_cg16(x + sb * 256 + lane * 8), sb, lane, K, planes + m * 2 * K, XS + m * (K / 32),
-                        SX + m * ncp);
+        raw[m] = st_ld_cg16(x + sb * 256 + lane * 8);
       }
+#pragma unroll
+      for (int m = 0; m < 4; m++)
+        st_quantize<XT>(raw[m], sb, lane, K, planes + m * 2 * K, XS + m * (K / 32), SX + m * ncp);
     }
     __syncthreads();  // first pass: the barrier is initialised
     if (m0 == 0 && !md_wait(mbar, 0, error_word)) return;
