@@ -17,9 +17,9 @@
  *    Calls are asynchronous; ordering is stream order.
  *  - dtype codes: KQ_F32 = 0, KQ_F16 = 1, KQ_BF16 = 2.
  *  - Codecs are named as in the reference registry (src/kquant_codec.cpp:12-37);
- *    this library implements q2_k q3_k q4_k q5_k q6_k q4_0 q8_0 iq4_nl iq4_xs
- *    iq2_xxs q4_1 q5_0 q5_1 (registry indices in that order) and reports any other
- *    name as unknown.
+ *    this library implements all 21 of them: q2_k q3_k q4_k q5_k q6_k q4_0 q8_0 iq4_nl iq4_xs
+ *    iq2_xxs q4_1 q5_0 q5_1 iq3_xxs iq3_s iq2_xs iq2_s iq1_s iq1_m mxfp4 nvfp4 (registry indices in that
+ *    order; the ten the benchmark names come first). Any other name is reported as unknown.
  */
 #ifndef KQUANT_B200_H
 #define KQUANT_B200_H
@@ -75,7 +75,9 @@ KQ_API int kq_dequantize(const void* w, size_t w_bytes, const char* kquant_type,
  * kquant_quantize_dispatch, src/kquant_cpu_encode.cpp:824-859 (op: src/kquant_ops.cpp:550-631) ----
  * HOST pointers: the reference's encoder is a CPU-only op as well. w: n_weights values of w_dtype
  * (rows of K), out: n_weights / weights_per_block * bytes_per_block bytes, imatrix: K floats or NULL.
- * Byte-identical with the reference for all thirteen codecs (the IQ ones: src/kquant_iq_encode.cpp:2099-2176);
+ * Byte-identical with the reference for the thirteen codecs that have a host encoder here - q2_k .. q6_k, q4_0, q4_1,
+ * q5_0, q5_1, q8_0, iq4_nl, iq4_xs, iq2_xxs; the other eight of the registry are decode-only in this library and
+ * return KQ_ERR_UNSUPPORTED - (the IQ ones: src/kquant_iq_encode.cpp:2099-2176);
  * iq2_xxs requires an imatrix, as in the reference.
  * threads: 0 = all host threads (blocks are independent: the bytes do not depend on it). */
 KQ_API int kq_quantize_cpu(const void* w, int w_dtype, long long n_weights, long long K, const char* kquant_type,

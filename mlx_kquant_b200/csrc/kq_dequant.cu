@@ -74,7 +74,7 @@ dequant_kernel(const uint8_t* __restrict__ w, T* __restrict__ out, long long n_b
   constexpr int kStage = TB * BPB + 32;       // tile bytes + phase + round-up
   extern __shared__ __align__(16) uint8_t smem[];
   uint8_t* stage = smem;
-  IqTables tabs{};
+  IqTables tabs = global_iq_tables();
   if constexpr (C == IQ4_NL || C == IQ4_XS || C == IQ2_XXS) {
     tabs = stage_iq_tables(smem + ((kStage + 15) & ~15), threadIdx.x, kDqThreads);
   }
@@ -203,6 +203,14 @@ cudaError_t launch_dequantize(int codec, const uint8_t* w, long long n_blocks, i
     case Q4_1: return launch_codec<Q4_1, 4>(w, out, n_blocks, dtype, st);
     case Q5_0: return launch_codec<Q5_0, 2>(w, out, n_blocks, dtype, st);
     case Q5_1: return launch_codec<Q5_1, 8>(w, out, n_blocks, dtype, st);
+    case IQ3_XXS: return launch_codec<IQ3_XXS, 2>(w, out, n_blocks, dtype, st);
+    case IQ3_S: return launch_codec<IQ3_S, 2>(w, out, n_blocks, dtype, st);
+    case IQ2_XS: return launch_codec<IQ2_XS, 2>(w, out, n_blocks, dtype, st);
+    case IQ2_S: return launch_codec<IQ2_S, 2>(w, out, n_blocks, dtype, st);
+    case IQ1_S: return launch_codec<IQ1_S, 2>(w, out, n_blocks, dtype, st);
+    case IQ1_M: return launch_codec<IQ1_M, 8>(w, out, n_blocks, dtype, st);
+    case MXFP4: return launch_codec<MXFP4, 1>(w, out, n_blocks, dtype, st);
+    case NVFP4: return launch_codec<NVFP4, 4>(w, out, n_blocks, dtype, st);
   }
   return cudaErrorInvalidValue;
 }

@@ -100,18 +100,14 @@ struct GemmArgs {
 template <int C, int A>
 __device__ __forceinline__ void produce_w_generic(const uint8_t* row, int kb, int K, uint8_t* dst_row, int r, int hh,
                                                   const IqTables& tabs) {
-  constexpr int WPB = wpb_of(C), BPB = bpb_of(C);
+  constexpr int BPB = bpb_of(C);
 #pragma unroll 2
   for (int c = 4 * hh; c < 4 * hh + 4; c++) {
     const int k = kb * kBK + c * 8;
     uint4 out = make_uint4(0u, 0u, 0u, 0u);
     if (k < K) {
       float v[8];
-      if constexpr (WPB == 256) {
-        decode8<C, A>(row + (long long)(k >> 8) * BPB, (k & 255) >> 3, v, tabs);
-      } else {
-        decode8<C, A>(row + (long long)(k >> 5) * BPB, (k & 31) >> 3, v, tabs);
-      }
+      decode8<C, A>(row + block_of<C>(k) * BPB, octet_of<C>(k), v, tabs);
       out = make_uint4(pack_h2f(v[0], v[1]), pack_h2f(v[2], v[3]), pack_h2f(v[4], v[5]), pack_h2f(v[6], v[7]));
     }
     *reinterpret_cast<uint4*>(dst_row + ((c ^ (r & 7)) << 4)) = out;
@@ -260,7 +256,7 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
   const int mt_live = min(MT, (m_end - m0 + 127) / 128);  // activation tiles of this CTA that hold rows
   constexpr uint32_t kTmemCols = MT * BN;               // 128, 256 or 512: a power of two >= 32
 
-  IqTables tabs{};
+  IqTables tabs = global_iq_tables();
   if constexpr (kIq) tabs = stage_iq_tables(s_tabs, threadIdx.x, kGemmThreads);
   if (threadIdx.x == 0) {
     for (int s = 0; s < kBStages; s++) {
@@ -781,6 +777,14 @@ cudaError_t launch_gemm(int codec, int x_dtype, const void* x, long long x_row_s
     case Q4_1: return launch_codec<Q4_1, 4>(out_half, a, aligned, st);
     case Q5_0: return launch_codec<Q5_0, 2>(out_half, a, aligned, st);
     case Q5_1: return launch_codec<Q5_1, 8>(out_half, a, aligned, st);
+    case IQ3_XXS: return launch_codec<IQ3_XXS, 2>(out_half, a, aligned, st);
+    case IQ3_S: return launch_codec<IQ3_S, 2>(out_half, a, aligned, st);
+    case IQ2_XS: return launch_codec<IQ2_XS, 2>(out_half, a, aligned, st);
+    case IQ2_S: return launch_codec<IQ2_S, 2>(out_half, a, aligned, st);
+    case IQ1_S: return launch_codec<IQ1_S, 2>(out_half, a, aligned, st);
+    case IQ1_M: return launch_codec<IQ1_M, 8>(out_half, a, aligned, st);
+    case MXFP4: return launch_codec<MXFP4, 1>(out_half, a, aligned, st);
+    case NVFP4: return launch_codec<NVFP4, 4>(out_half, a, aligned, st);
   }
   return cudaErrorInvalidValue;
 }
@@ -858,6 +862,14 @@ cudaError_t launch_gemm_tiles(int codec, bool out_half, const void* xh, long lon
     case Q4_1: return launch_grouped_codec<Q4_1, 4>(out_half, a, aligned, max_tiles, st);
     case Q5_0: return launch_grouped_codec<Q5_0, 2>(out_half, a, aligned, max_tiles, st);
     case Q5_1: return launch_grouped_codec<Q5_1, 8>(out_half, a, aligned, max_tiles, st);
+    case IQ3_XXS: return launch_grouped_codec<IQ3_XXS, 2>(out_half, a, aligned, max_tiles, st);
+    case IQ3_S: return launch_grouped_codec<IQ3_S, 2>(out_half, a, aligned, max_tiles, st);
+    case IQ2_XS: return launch_grouped_codec<IQ2_XS, 2>(out_half, a, aligned, max_tiles, st);
+    case IQ2_S: return launch_grouped_codec<IQ2_S, 2>(out_half, a, aligned, max_tiles, st);
+    case IQ1_S: return launch_grouped_codec<IQ1_S, 2>(out_half, a, aligned, max_tiles, st);
+    case IQ1_M: return launch_grouped_codec<IQ1_M, 8>(out_half, a, aligned, max_tiles, st);
+    case MXFP4: return launch_grouped_codec<MXFP4, 1>(out_half, a, aligned, max_tiles, st);
+    case NVFP4: return launch_grouped_codec<NVFP4, 4>(out_half, a, aligned, max_tiles, st);
   }
   return cudaErrorInvalidValue;
 }

@@ -884,7 +884,7 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_kernel(const GemvArgs a) {
   __shared__ __align__(16) __half xsum[FAST ? NT * 8 * (kStageK / 256) * 16 : 8];
 
   cg::cluster_group cluster = cg::this_cluster();
-  IqTables tabs{};
+  IqTables tabs = global_iq_tables();
   if constexpr (kIq) {
     tabs = stage_iq_tables(s_tabs, threadIdx.x, kGemvThreads);
   }
@@ -960,13 +960,8 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_kernel(const GemvArgs a) {
       for (int gi = cs * 8; gi < g_end; gi++) {
         long long boff;
         int oct;
-        if constexpr (WPB == 256) {
-          boff = (long long)(gi >> 3) * BPB;
-          oct = (gi & 7) * 4 + t;
-        } else {
-          boff = (long long)gi * BPB;
-          oct = t;
-        }
+        boff = block_of<C>(32ll * gi) * BPB;   // group gi = weights 32 gi .. 32 gi + 31 of the row
+        oct = octet_of<C>(32ll * gi) + t;
         float va[8], vb[8];
         decode8<C, A>(pA + boff, oct, va, tabs);
         decode8<C, A>(pB + boff, oct, vb, tabs);
@@ -1620,6 +1615,14 @@ cudaError_t launch_gemv(int codec, int x_dtype, const GemvArgs& a, cudaStream_t 
     case Q4_1: return launch_generic<Q4_1, 4>(x_dtype, a, grid, nt2, aligned, st);
     case Q5_0: return launch_generic<Q5_0, 2>(x_dtype, a, grid, nt2, aligned, st);
     case Q5_1: return launch_generic<Q5_1, 8>(x_dtype, a, grid, nt2, aligned, st);
+    case IQ3_XXS: return launch_generic<IQ3_XXS, 2>(x_dtype, a, grid, nt2, aligned, st);
+    case IQ3_S: return launch_generic<IQ3_S, 2>(x_dtype, a, grid, nt2, aligned, st);
+    case IQ2_XS: return launch_generic<IQ2_XS, 2>(x_dtype, a, grid, nt2, aligned, st);
+    case IQ2_S: return launch_generic<IQ2_S, 2>(x_dtype, a, grid, nt2, aligned, st);
+    case IQ1_S: return launch_generic<IQ1_S, 2>(x_dtype, a, grid, nt2, aligned, st);
+    case IQ1_M: return launch_generic<IQ1_M, 8>(x_dtype, a, grid, nt2, aligned, st);
+    case MXFP4: return launch_generic<MXFP4, 1>(x_dtype, a, grid, nt2, aligned, st);
+    case NVFP4: return launch_generic<NVFP4, 4>(x_dtype, a, grid, nt2, aligned, st);
   }
   return cudaErrorInvalidValue;
 }

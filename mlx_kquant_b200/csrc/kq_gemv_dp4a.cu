@@ -652,6 +652,7 @@ cudaError_t launch_codec(int x_dtype, const GemvArgs& a, cudaStream_t st) {
 }  // namespace
 
 bool gemv_dp4a_supported(int codec, int x_dtype, const GemvArgs& a) {
+  if (codec > Q5_1) return false;   // the codecs added after the integer kernels were written use the generic path
   if (!a.w_align16 || (a.K & 255) != 0 || a.K > kMaxK || (a.row_bytes & 15) != 0 || a.row_bytes < 16 * 17) return false;
   if (a.tasks != nullptr) {
     // task lists (gather_qmm): rows in slices of four. q4_k with fp16 rows and the two table codecs keep
@@ -664,6 +665,7 @@ bool gemv_dp4a_supported(int codec, int x_dtype, const GemvArgs& a) {
     return 4 * x_bytes(a.K) <= 96 * 1024;
   }
   if (codec == Q4_K) return false;  // dense q4_k has its own kernels (kq_gemv.cu)
+  if (codec > Q5_1) return false;   // the codecs added after the integer kernels were written use the generic path
   if (a.M < 1 || a.M > 4) return false;
   // measured: with more than one row the table-driven tensor-core kernels of kq_gemv.cu win for these two,
   // and so they do for iq2_xxs matrices too small to hide the lattice lookups

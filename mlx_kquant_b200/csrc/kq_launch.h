@@ -155,7 +155,7 @@ int gather_qmm_entry(const void* x, int x_dtype, long long x_batch, int M, int K
 int set_error(int code, const char* msg);
 
 // Host-side encoder (kq_quantize.cu): float weights -> wire bytes, byte-identical with the
-// reference's CPU encoder for all thirteen codecs of the registry.
+// reference's CPU encoder for the thirteen codecs that have one here (quantize_supported).
 bool quantize_supported(int codec);
 void quantize_host(int codec, const void* w, int dtype, long long n_weights, long long K, const float* imatrix,
                    uint8_t* out, int threads);

@@ -47,7 +47,7 @@ qvm_kernel(const XT* __restrict__ x, long long x_row_stride, void* __restrict__ 
   __shared__ float part[kMT][kCols];
   __shared__ __align__(16) uint8_t s_tabs[(C == IQ4_NL || C == IQ4_XS || C == IQ2_XXS) ? kIqSmemBytes : 16];
   cg::cluster_group cluster = cg::this_cluster();
-  IqTables tabs{};
+  IqTables tabs = global_iq_tables();
   if constexpr (C == IQ4_NL || C == IQ4_XS || C == IQ2_XXS) {
     tabs = stage_iq_tables(s_tabs, threadIdx.x, kThreads);
     __syncthreads();
@@ -76,8 +76,9 @@ qvm_kernel(const XT* __restrict__ x, long long x_row_stride, void* __restrict__ 
   for (int t = 0; t < kMT; t++)
 #pragma unroll
     for (int i = 0; i < 8; i++) acc[t][i] = 0.f;
-  const long long blk_off = WPB == 256 ? (long long)blockIdx.x * BPB : (long long)(blockIdx.x * 8 + (lane >> 2)) * BPB;
-  const int oct = WPB == 256 ? lane : (lane & 3);
+  // this lane's eight columns: 256 blockIdx.x + 8 lane .. + 7
+  const long long blk_off = block_of<C>(256ll * blockIdx.x + 8 * lane) * BPB;
+  const int oct = octet_of<C>(8 * lane);
   if (c0 < N) {
     for (int k = k0 + warp; k < k1; k += kWarps) {
       float v[8];
@@ -183,6 +184,14 @@ cudaError_t launch_qvm(int codec, int x_dtype, const void* x, long long x_row_st
     KQ_CASE(Q4_1, 4);
     KQ_CASE(Q5_0, 2);
     KQ_CASE(Q5_1, 8);
+    KQ_CASE(IQ3_XXS, 2);
+    KQ_CASE(IQ3_S, 2);
+    KQ_CASE(IQ2_XS, 2);
+    KQ_CASE(IQ2_S, 2);
+    KQ_CASE(IQ1_S, 2);
+    KQ_CASE(IQ1_M, 8);
+    KQ_CASE(MXFP4, 1);
+    KQ_CASE(NVFP4, 4);
   }
 #undef KQ_CASE
   return cudaErrorInvalidValue;
@@ -216,6 +225,14 @@ cudaError_t launch_qvm_gather(int codec, int x_dtype, const void* x, long long x
       KQ_CASE(Q4_1, 4);
       KQ_CASE(Q5_0, 2);
       KQ_CASE(Q5_1, 8);
+      KQ_CASE(IQ3_XXS, 2);
+      KQ_CASE(IQ3_S, 2);
+      KQ_CASE(IQ2_XS, 2);
+      KQ_CASE(IQ2_S, 2);
+      KQ_CASE(IQ1_S, 2);
+      KQ_CASE(IQ1_M, 8);
+      KQ_CASE(MXFP4, 1);
+      KQ_CASE(NVFP4, 4);
     }
 #undef KQ_CASE
     if (err != cudaSuccess) return err;

@@ -21,12 +21,15 @@ import torch
 _MAGIC = b"GGUF"
 # ggml tensor type ids of the codecs the ops know, and of the float types
 GGML_TYPES = {0: "f32", 1: "f16", 2: "q4_0", 3: "q4_1", 6: "q5_0", 7: "q5_1", 8: "q8_0", 10: "q2_k", 11: "q3_k", 12: "q4_k", 13: "q5_k", 14: "q6_k",
-              16: "iq2_xxs", 20: "iq4_nl", 23: "iq4_xs", 30: "bf16"}
+              16: "iq2_xxs", 17: "iq2_xs", 18: "iq3_xxs", 19: "iq1_s", 20: "iq4_nl", 21: "iq3_s", 22: "iq2_s", 23: "iq4_xs",
+              29: "iq1_m", 30: "bf16", 39: "mxfp4", 40: "nvfp4"}
 _TYPE_IDS = {v: k for k, v in GGML_TYPES.items()}
 _FLOATS = {"f32": (torch.float32, 4), "f16": (torch.float16, 2), "bf16": (torch.bfloat16, 2)}
 # (weights per block, bytes per block); must agree with the library's registry (checked in the tests)
 BLOCKS = {"q4_0": (32, 18), "q4_1": (32, 20), "q5_0": (32, 22), "q5_1": (32, 24), "q8_0": (32, 34), "q2_k": (256, 84), "q3_k": (256, 110), "q4_k": (256, 144),
-          "q5_k": (256, 176), "q6_k": (256, 210), "iq2_xxs": (256, 66), "iq4_nl": (32, 18), "iq4_xs": (256, 136)}
+          "q5_k": (256, 176), "q6_k": (256, 210), "iq2_xxs": (256, 66), "iq4_nl": (32, 18), "iq4_xs": (256, 136),
+          "iq3_xxs": (256, 98), "iq3_s": (256, 110), "iq2_xs": (256, 74), "iq2_s": (256, 82), "iq1_s": (256, 50),
+          "iq1_m": (256, 56), "mxfp4": (32, 17), "nvfp4": (64, 36)}
 
 _SCALARS = {0: "<B", 1: "<b", 2: "<H", 3: "<h", 4: "<I", 5: "<i", 6: "<f", 7: "<?", 10: "<Q", 11: "<q", 12: "<d"}
 _T_STRING, _T_ARRAY = 8, 9

@@ -81,7 +81,8 @@ def dequantize(w, scales, kquant_type, dtype=None, *, stream=None):
 def quantize(w, kquant_type, imatrix=None, *, stream=None):
     """Float weights [..., K] -> (wire bytes uint8 [..., K / wpb * bpb], scales placeholder uint8 [1]) on the
     HOST, like the reference's CPU-only encoder op (src/kquant_ops.cpp:550-631, bindings.cpp:1439-1446).
-    Byte-identical with the reference for all thirteen codecs; iq2_xxs requires an imatrix."""
+    Byte-identical with the reference for the thirteen codecs with a host encoder here (the ten of the benchmark
+    and q4_1, q5_0, q5_1); iq2_xxs requires an imatrix. The other eight codecs are decode-only in this library."""
     del stream  # host work: there is no stream to order it on
     if w.dtype not in _DT:
         raise ValueError("[mlx_kquant.quantize] w must be a real floating tensor (float32, float16, or bfloat16).")

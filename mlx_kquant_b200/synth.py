@@ -17,7 +17,8 @@ from .ops import codec_geometry
 # byte offsets of the fp16 fields inside one block
 _F16_FIELDS = {"q2_k": (80, 82), "q3_k": (108,), "q4_k": (0, 2), "q5_k": (0, 2), "q6_k": (208,), "q4_0": (0,),
                "q8_0": (0,), "iq4_nl": (0,), "iq4_xs": (0,), "iq2_xxs": (0,), "q4_1": (0, 2), "q5_0": (0,),
-               "q5_1": (0, 2)}
+               "q5_1": (0, 2), "iq3_xxs": (0,), "iq3_s": (0,), "iq2_xs": (0,), "iq2_s": (0,), "iq1_s": (0,),
+               "iq1_m": (), "mxfp4": (), "nvfp4": ()}
 
 
 def random_wire(kquant_type: str, rows: int, K: int, *, seed: int = 0, device="cuda", lead: tuple = ()) -> torch.Tensor:
@@ -34,4 +35,12 @@ def random_wire(kquant_type: str, rows: int, K: int, *, seed: int = 0, device="c
     for off in _F16_FIELDS[kquant_type]:
         w[..., off] = (dbits & 0xFF).to(torch.uint8)
         w[..., off + 1] = (dbits >> 8).to(torch.uint8)
+    if kquant_type == "iq1_m":      # fp16 super-scale = the top nibbles of the four scale words
+        for k in range(4):
+            hi = w[..., 48 + 2 * k + 1]
+            w[..., 48 + 2 * k + 1] = (hi & 0x0F) | (((dbits >> (4 * k)) & 0xF) << 4).to(torch.uint8)
+    elif kquant_type == "mxfp4":    # E8M0 exponent byte
+        w[..., 0] = torch.randint(116, 123, w.shape[:-1], dtype=torch.uint8, device=device, generator=g)
+    elif kquant_type == "nvfp4":    # four unsigned E4M3 scale bytes
+        w[..., 0:4] = torch.randint(0x08, 0x30, w.shape[:-1] + (4,), dtype=torch.uint8, device=device, generator=g)
     return w.reshape(tuple(lead) + (rows, nb * bpb))

@@ -92,7 +92,11 @@ static const kqo_codec KQO_CODECS[] = {
     {"q8_0", 32, 34, 8, 0},    {"iq4_nl", 32, 18, 4, 0},
     {"iq4_xs", 256, 136, 4, 0}, {"iq2_xxs", 256, 66, 2, 1},
     {"q4_1", 32, 20, 4, 0},    {"q5_0", 32, 22, 5, 0},
-    {"q5_1", 32, 24, 5, 0},
+    {"q5_1", 32, 24, 5, 0},    {"iq3_xxs", 256, 98, 3, 0},
+    {"iq3_s", 256, 110, 3, 0}, {"iq2_xs", 256, 74, 2, 1},
+    {"iq2_s", 256, 82, 2, 0},  {"iq1_s", 256, 50, 1, 1},
+    {"iq1_m", 256, 56, 1, 0},  {"mxfp4", 32, 17, 4, 0},
+    {"nvfp4", 64, 36, 4, 0},
 };
 #define KQO_NCODECS ((int)(sizeof(KQO_CODECS) / sizeof(KQO_CODECS[0])))
 
@@ -342,10 +346,155 @@ static void blk_iq2_xxs(const uint8_t* b, float* o) {
   }
 }
 
+
+/* sign of weight j of an eight-weight group whose sign bits are `signs` */
+static float sgn(uint8_t signs, int j) { return (signs & kq_tab_kmask[j]) ? -1.f : 1.f; }
+
+/* src/kquant_cpu_decode.cpp:468-503: [d][qs 64][8 x u32 = 4 x 7-bit sign index + 4-bit scale] */
+static void blk_iq3_xxs(const uint8_t* b, float* o) {
+  float d = rd_f16(b);
+  for (int ib = 0; ib < 8; ib++) {
+    uint32_t aux;
+    memcpy(&aux, b + 66 + 4 * ib, 4);
+    float db = d * (0.5f + (float)(aux >> 28)) * 0.5f;
+    const uint8_t* q = b + 2 + 8 * ib;
+    for (int l = 0; l < 4; l++, o += 8) {
+      uint8_t signs = kq_tab_ksigns[(aux >> (7 * l)) & 127];
+      const uint8_t* g1 = (const uint8_t*)(kq_tab_iq3xxs_grid + q[2 * l]);
+      const uint8_t* g2 = (const uint8_t*)(kq_tab_iq3xxs_grid + q[2 * l + 1]);
+      for (int j = 0; j < 4; j++) {
+        o[j] = db * (float)g1[j] * sgn(signs, j);
+        o[j + 4] = db * (float)g2[j] * sgn(signs, j + 4);
+      }
+    }
+  }
+}
+
+/* src/kquant_cpu_decode.cpp:505-556: [d][qs 64][qh 8][signs 32][scales 4] */
+static void blk_iq3_s(const uint8_t* b, float* o) {
+  float d = rd_f16(b);
+  for (int ib = 0; ib < 8; ib++) {
+    uint8_t sb = b[106 + ib / 2];
+    float db = d * (float)(1 + 2 * ((ib & 1) ? (sb >> 4) : (sb & 15)));
+    const uint8_t* q = b + 2 + 8 * ib;
+    const uint8_t* sg = b + 74 + 4 * ib;
+    uint32_t qh = b[66 + ib];
+    for (int l = 0; l < 4; l++, o += 8) {
+      const uint8_t* g1 = (const uint8_t*)(kq_tab_iq3s_grid + (q[2 * l] | ((qh << (8 - 2 * l)) & 256)));
+      const uint8_t* g2 = (const uint8_t*)(kq_tab_iq3s_grid + (q[2 * l + 1] | ((qh << (7 - 2 * l)) & 256)));
+      for (int j = 0; j < 4; j++) {
+        o[j] = db * (float)g1[j] * sgn(sg[l], j);
+        o[j + 4] = db * (float)g2[j] * sgn(sg[l], j + 4);
+      }
+    }
+  }
+}
+
+/* src/kquant_cpu_decode.cpp:586-616: [d][32 x u16 = 9-bit lattice index | 7-bit sign index][scales 8] */
+static void blk_iq2_xs(const uint8_t* b, float* o) {
+  float d = rd_f16(b);
+  for (int ib = 0; ib < 8; ib++) {
+    uint8_t sb = b[66 + ib];
+    float db[2] = {d * (0.5f + (float)(sb & 15)) * 0.25f, d * (0.5f + (float)(sb >> 4)) * 0.25f};
+    for (int l = 0; l < 4; l++, o += 8) {
+      uint16_t q;
+      memcpy(&q, b + 2 + 2 * (4 * ib + l), 2);
+      const uint8_t* g = (const uint8_t*)(kq_tab_iq2xs_grid + (q & 511));
+      uint8_t signs = kq_tab_ksigns[q >> 9];
+      for (int j = 0; j < 8; j++) o[j] = db[l / 2] * (float)g[j] * sgn(signs, j);
+    }
+  }
+}
+
+/* src/kquant_cpu_decode.cpp:618-649: [d][qs 32][signs 32][qh 8][scales 8] */
+static void blk_iq2_s(const uint8_t* b, float* o) {
+  float d = rd_f16(b);
+  for (int ib = 0; ib < 8; ib++) {
+    uint8_t sb = b[74 + ib];
+    float db[2] = {d * (0.5f + (float)(sb & 15)) * 0.25f, d * (0.5f + (float)(sb >> 4)) * 0.25f};
+    uint32_t qh = b[66 + ib];
+    for (int l = 0; l < 4; l++, o += 8) {
+      const uint8_t* g = (const uint8_t*)(kq_tab_iq2s_grid + (b[2 + 4 * ib + l] | ((qh << (8 - 2 * l)) & 0x300)));
+      uint8_t signs = b[34 + 4 * ib + l];
+      for (int j = 0; j < 8; j++) o[j] = db[l / 2] * (float)g[j] * sgn(signs, j);
+    }
+  }
+}
+
+/* src/kquant_cpu_decode.cpp:658-685: [d][qs 32][8 x u16 qh]; lattice bytes are signed, + or - 1/8 added */
+static void blk_iq1_s(const uint8_t* b, float* o) {
+  float d = rd_f16(b);
+  for (int ib = 0; ib < 8; ib++) {
+    uint16_t qh;
+    memcpy(&qh, b + 34 + 2 * ib, 2);
+    float dl = d * (float)(2 * ((qh >> 12) & 7) + 1);
+    float delta = (qh & 0x8000) ? -0.125f : 0.125f;
+    for (int l = 0; l < 4; l++, o += 8) {
+      const int8_t* g = (const int8_t*)(kq_tab_iq1s_grid + (b[2 + 4 * ib + l] | (((qh >> (3 * l)) & 7) << 8)));
+      for (int j = 0; j < 8; j++) o[j] = dl * ((float)g[j] + delta);
+    }
+  }
+}
+
+/* src/kquant_cpu_decode.cpp:687-735: [qs 32][qh 16][4 x u16 scales]; the fp16 super-scale is the four top nibbles */
+static void blk_iq1_m(const uint8_t* b, float* o) {
+  uint16_t sc[4];
+  memcpy(sc, b + 48, 8);
+  uint16_t dbits = (uint16_t)((sc[0] >> 12) | ((sc[1] >> 8) & 0x00f0) | ((sc[2] >> 4) & 0x0f00) | (sc[3] & 0xf000));
+  float d = rd_f16((const uint8_t*)&dbits);
+  for (int ib = 0; ib < 8; ib++) {
+    float dl[2] = {d * (float)(2 * ((sc[ib / 2] >> (6 * (ib % 2))) & 7) + 1),
+                   d * (float)(2 * ((sc[ib / 2] >> (6 * (ib % 2) + 3)) & 7) + 1)};
+    for (int l = 0; l < 4; l++, o += 8) {
+      uint32_t qh = b[32 + 2 * ib + l / 2];
+      uint32_t idx = b[4 * ib + l] | ((qh << ((l & 1) ? 4 : 8)) & 0x700);
+      float delta = (qh & ((l & 1) ? 0x80 : 0x08)) ? -0.125f : 0.125f;
+      const int8_t* g = (const int8_t*)(kq_tab_iq1s_grid + idx);
+      for (int j = 0; j < 8; j++) o[j] = dl[l / 2] * ((float)g[j] + delta);
+    }
+  }
+}
+
+/* src/kquant_fp_tables.h:24-31: E8M0 byte -> 2^(e - 127) / 2, subnormal results built from the bits */
+static float e8m0_half(uint8_t e) {
+  uint32_t bits = e < 2 ? (0x00200000u << e) : ((uint32_t)(e - 1) << 23);
+  float f;
+  memcpy(&f, &bits, 4);
+  return f;
+}
+/* src/kquant_fp_tables.h:36-45: unsigned E4M3 (bias 7) byte -> value / 2; 0x00 and 0x7f give 0 */
+static float ue4m3_half(uint8_t x) {
+  if (x == 0 || x == 0x7f) return 0.f;
+  int ex = (x >> 3) & 15;
+  float man = (float)(x & 7);
+  float raw = ex == 0 ? man * 0x1p-9f : ldexpf(1.0f + man * 0.125f, ex - 7);
+  return raw * 0.5f;
+}
+/* src/kquant_cpu_decode.cpp:404-419 */
+static void blk_mxfp4(const uint8_t* b, float* o) {
+  float d = e8m0_half(b[0]);
+  for (int j = 0; j < 16; j++) {
+    o[j] = d * (float)kq_tab_mxfp4[b[1 + j] & 15];
+    o[j + 16] = d * (float)kq_tab_mxfp4[b[1 + j] >> 4];
+  }
+}
+/* src/kquant_cpu_decode.cpp:421-438: four groups of sixteen weights, one scale byte each */
+static void blk_nvfp4(const uint8_t* b, float* o) {
+  for (int g = 0; g < 4; g++) {
+    float d = ue4m3_half(b[g]);
+    const uint8_t* q = b + 4 + 8 * g;
+    for (int j = 0; j < 8; j++) {
+      o[16 * g + j] = d * (float)kq_tab_mxfp4[q[j] & 15];
+      o[16 * g + j + 8] = d * (float)kq_tab_mxfp4[q[j] >> 4];
+    }
+  }
+}
+
 typedef void (*blk_fn)(const uint8_t*, float*);
 static const blk_fn BLK_FNS[] = {blk_q2_k, blk_q3_k, blk_q4_k, blk_q5_k,   blk_q6_k,
                                  blk_q4_0, blk_q8_0, blk_iq4_nl, blk_iq4_xs, blk_iq2_xxs,
-                                 blk_q4_1, blk_q5_0, blk_q5_1};
+                                 blk_q4_1, blk_q5_0, blk_q5_1, blk_iq3_xxs, blk_iq3_s,
+                                 blk_iq2_xs, blk_iq2_s, blk_iq1_s, blk_iq1_m, blk_mxfp4, blk_nvfp4};
 
 /* ---- output rounding: one IEEE RNE rounding of the exact f32 value ---- */
 static uint16_t f32_to_bf16(float f) {

@@ -28,15 +28,51 @@ DT = {"f32": 0, "f16": 1, "bf16": 2}
 NP_OF = {"f32": np.float32, "f16": np.float16, "bf16": np.uint16}
 
 # (weights_per_block, bytes_per_block, bits, requires_imatrix): the ten in-scope
-# rows of the reference registry, src/kquant_codec.cpp:12-37, and three further flat codecs.
+# rows of the reference registry, src/kquant_codec.cpp:12-37, then the other eleven in the order of this
+# library's registry.
 GEOMETRY = {
     "q2_k": (256, 84, 2, False), "q3_k": (256, 110, 3, False), "q4_k": (256, 144, 4, False),
     "q5_k": (256, 176, 5, False), "q6_k": (256, 210, 6, False), "q4_0": (32, 18, 4, False),
     "q8_0": (32, 34, 8, False), "iq4_nl": (32, 18, 4, False), "iq4_xs": (256, 136, 4, False),
     "iq2_xxs": (256, 66, 2, True), "q4_1": (32, 20, 4, False), "q5_0": (32, 22, 5, False),
-    "q5_1": (32, 24, 5, False),
+    "q5_1": (32, 24, 5, False), "iq3_xxs": (256, 98, 3, False), "iq3_s": (256, 110, 3, False),
+    "iq2_xs": (256, 74, 2, True), "iq2_s": (256, 82, 2, False), "iq1_s": (256, 50, 1, True),
+    "iq1_m": (256, 56, 1, False), "mxfp4": (32, 17, 4, False), "nvfp4": (64, 36, 4, False),
 }
+# codecs the reference can decode but not encode (src/kquant_codec.cpp:33-34)
+DECODE_ONLY = ("mxfp4", "nvfp4")
 CODECS = list(GEOMETRY)
+
+
+# byte offsets of the fp16 fields inside one block (iq1_m, mxfp4 and nvfp4 carry their scales differently)
+F16_FIELDS = {"q2_k": (80, 82), "q3_k": (108,), "q4_k": (0, 2), "q5_k": (0, 2), "q6_k": (208,), "q4_0": (0,),
+              "q8_0": (0,), "iq4_nl": (0,), "iq4_xs": (0,), "iq2_xxs": (0,), "q4_1": (0, 2), "q5_0": (0,),
+              "q5_1": (0, 2), "iq3_xxs": (0,), "iq3_s": (0,), "iq2_xs": (0,), "iq2_s": (0,), "iq1_s": (0,),
+              "iq1_m": (), "mxfp4": (), "nvfp4": ()}
+
+
+def synthetic_wire(codec: str, rows: int, K: int, seed: int) -> np.ndarray:
+    """Random but valid wire bytes: uniform bytes with every scale field set to a small finite value - the
+    reference's own recipe for codecs without an encoder at hand (tests/test_cpu_decode.py:70-87). iq1_m keeps
+    its fp16 super-scale in the top nibbles of its four scale words; mxfp4 has an E8M0 exponent byte and nvfp4
+    four unsigned E4M3 bytes."""
+    wpb, bpb, _, _ = GEOMETRY[codec]
+    rng = np.random.default_rng(seed)
+    nb = K // wpb
+    w = rng.integers(0, 256, (rows, nb, bpb), dtype=np.uint8)
+    d = rng.uniform(0.001, 0.02, (rows, nb)).astype(np.float16).view(np.uint16)
+    for off in F16_FIELDS[codec]:
+        w[:, :, off] = (d & 0xFF).astype(np.uint8)
+        w[:, :, off + 1] = (d >> 8).astype(np.uint8)
+    if codec == "iq1_m":
+        for k in range(4):   # nibble k of d goes to the top nibble of little-endian scale word k (bytes 48 + 2k + 1)
+            hi = w[:, :, 48 + 2 * k + 1]
+            w[:, :, 48 + 2 * k + 1] = (hi & 0x0F) | ((((d >> (4 * k)) & 0xF) << 4).astype(np.uint8))
+    elif codec == "mxfp4":
+        w[:, :, 0] = rng.integers(116, 123, (rows, nb), dtype=np.uint8)      # 2^-12 .. 2^-6 after the halving
+    elif codec == "nvfp4":
+        w[:, :, 0:4] = rng.integers(0x08, 0x30, (rows, nb, 4), dtype=np.uint8)
+    return w.reshape(rows, nb * bpb)
 
 
 def f32_to_bf16_bits(a: np.ndarray) -> np.ndarray:

@@ -31,7 +31,7 @@ import numpy as np
 ROOT = Path(__file__).resolve().parents[2]
 sys.path.insert(0, str(ROOT))
 
-from oracle.kq_oracle import CODECS, GEOMETRY, Ref, from_f32  # noqa: E402
+from oracle.kq_oracle import CODECS, DECODE_ONLY, GEOMETRY, Ref, from_f32, synthetic_wire  # noqa: E402
 
 
 def main(ref_dir: str) -> None:
@@ -52,7 +52,10 @@ def main(ref_dir: str) -> None:
         out[f"x_m{M}"] = x
     for c in CODECS:
         im = np.ones(512, np.float32) if GEOMETRY[c][3] else None
-        wire = ref.quantize(W, c, im, threads=1)
+        if c in DECODE_ONLY:   # no encoder in the reference: seeded valid bytes
+            wire = synthetic_wire(c, W.shape[0], W.shape[1], seed=77)
+        else:
+            wire = ref.quantize(W, c, im, threads=1)
         out[f"enc_{c}_wire"] = wire
         for dt in ("f32", "f16", "bf16"):
             d = ref.dequantize(wire, c, dt)

@@ -38,28 +38,14 @@ def y_to_f32(y: torch.Tensor) -> np.ndarray:
     return y.detach().float().cpu().numpy()
 
 
-def synthetic_wire(codec: str, rows: int, K: int, seed: int) -> np.ndarray:
-    """Random but valid wire bytes: uniform bytes with every fp16 scale field set
-    to a small finite value - the reference's own recipe for codecs without an
-    encoder at hand (tests/test_cpu_decode.py:70-87)."""
-    wpb, bpb, _, _ = GEOMETRY[codec]
-    rng = np.random.default_rng(seed)
-    nb = K // wpb
-    w = rng.integers(0, 256, (rows, nb, bpb), dtype=np.uint8)
-    d = rng.uniform(0.001, 0.02, (rows, nb)).astype(np.float16).view(np.uint16)
-    f16_at = {"q2_k": (80, 82), "q3_k": (108,), "q4_k": (0, 2), "q5_k": (0, 2), "q6_k": (208,), "q4_0": (0,),
-              "q8_0": (0,), "iq4_nl": (0,), "iq4_xs": (0,), "iq2_xxs": (0,), "q4_1": (0, 2), "q5_0": (0,),
-              "q5_1": (0, 2)}[codec]
-    for off in f16_at:
-        w[:, :, off] = (d & 0xFF).astype(np.uint8)
-        w[:, :, off + 1] = (d >> 8).astype(np.uint8)
-    return w.reshape(rows, nb * bpb)
+synthetic_wire = kq_oracle.synthetic_wire
 
 
 def mint_wire(codec: str, W: np.ndarray, imatrix=None) -> np.ndarray:
     """Really-encoded wire bytes from the reference encoder when its library is
-    present, else synthetic valid bytes of the same shape."""
-    if kq_oracle.Ref.available():
+    present (and the codec has an encoder: mxfp4 / nvfp4 are decode-only in the
+    reference, src/kquant_codec.cpp:33-34), else synthetic valid bytes of the same shape."""
+    if kq_oracle.Ref.available() and codec not in kq_oracle.DECODE_ONLY:
         if imatrix is None and GEOMETRY[codec][3]:
             imatrix = np.ones(W.shape[-1], np.float32)
         return kq_oracle.Ref().quantize(W, codec, imatrix)
