@@ -499,6 +499,10 @@ def parity_n(dev, rank, world, W0, x_dev, y0):
     ep = GatheredExpertParallel(T, H, k, E, wgu, wd, "q4_k")
     y_gat = ep(x, ids, probs).clone()
     del ep
+    from mlx_kquant_b200.moe import PipelinedExpertParallel
+    ep = PipelinedExpertParallel(T, H, k, E, wgu, wd, "q4_k", chunks=2, reduce_dtype=torch.bfloat16)
+    y_pip = ep(x, ids, probs).clone()
+    del ep
 
     def gather(t):
         parts = [torch.empty_like(t) for _ in range(world)]
@@ -509,13 +513,14 @@ def parity_n(dev, rank, world, W0, x_dev, y0):
     if same:
         all_wgu, all_wd = torch.cat(gather(wgu), 0), torch.cat(gather(wd), 0)
         all_x, all_ids, all_p = gather(x), gather(ids), gather(probs)
-        all_a, all_g = gather(y_a2a), gather(y_gat.to(y_a2a.dtype))
+        all_a, all_g, all_pl = gather(y_a2a), gather(y_gat.to(y_a2a.dtype)), gather(y_pip.to(y_a2a.dtype))
         if rank == 0:
             for r in range(world):
                 ref = moe_glu(all_x[r], None, None, all_wd, "q4_k", all_ids[r], all_p[r], w_gate_up=all_wgu).float()
-                for name, got in (("all-to-all", all_a[r]), ("gathered", all_g[r])):
+                for name, got, bar in (("all-to-all", all_a[r], 6e-3), ("gathered", all_g[r], 6e-3),
+                                       ("pipelined, bfloat16 sums", all_pl[r], 8e-3)):
                     err = float((got.float() - ref).norm() / ref.norm())
-                    if not err <= 6e-3:
+                    if not err <= bar:
                         problems.append(f"MoE {name} form, rank {r}: rel error {err:.2e} against the single-GPU block")
     flag = torch.tensor([len(problems)], device=dev)
     dist.broadcast(flag, 0)
@@ -675,16 +680,16 @@ def moe_ep_cell(dev, rank, world):
     ms = float(t.item())
     out = {f"moe_glu_q4k_ep{world}_T4096_per_rank": {"tokens_per_s": world * T / (ms * 1e-3), "ms": ms,
                                                       "experts_per_rank": hi - lo}}
-    # fixed-shape form (all-gather, local experts as a CUDA graph, reduce-scatter): no host read inside a step
-    for Tg in (64, 4096):
-        ep = GatheredExpertParallel(Tg, H, k, E, wgu, wd, "q4_k")
-        xg, idg, prg = x[:Tg].contiguous(), ids[:Tg].contiguous(), probs[:Tg].contiguous()
+    # fixed-shape form (all-gather, local experts as a CUDA graph, reduce-scatter): no host read inside a step;
+    # "pipelined": two token slices, collectives of one overlapping the products of the other, bfloat16 partial sums
+    from mlx_kquant_b200.moe import PipelinedExpertParallel
+
+    def timed_ep(ep, xg, idg, prg, reps):
         ep.capture()
         for _ in range(3):
             ep(xg, idg, prg)
         torch.cuda.synchronize()
         dist.barrier()
-        reps = 20 if Tg <= 64 else 5
         e0.record()
         for _ in range(reps):
             ep(xg, idg, prg)
@@ -692,9 +697,23 @@ def moe_ep_cell(dev, rank, world):
         torch.cuda.synchronize()
         t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+        return float(t.item())
+
+    for Tg in (64, 4096):
+        xg, idg, prg = x[:Tg].contiguous(), ids[:Tg].contiguous(), probs[:Tg].contiguous()
+        ep = GatheredExpertParallel(Tg, H, k, E, wgu, wd, "q4_k")
+        ms = timed_ep(ep, xg, idg, prg, 20 if Tg <= 64 else 5)
         out[f"moe_glu_q4k_ep{world}_gathered_T{Tg}_per_rank"] = {"tokens_per_s": world * Tg / (ms * 1e-3), "ms": ms}
         del ep
+        torch.cuda.empty_cache()
+    for name, kw in (("pipelined2_bf16sum", dict(chunks=2, reduce_dtype=torch.bfloat16)),
+                     ("pipelined4_bf16sum", dict(chunks=4, reduce_dtype=torch.bfloat16)),
+                     ("pipelined2_f32sum", dict(chunks=2))):
+        ep = PipelinedExpertParallel(T, H, k, E, wgu, wd, "q4_k", **kw)
+        ms = timed_ep(ep, x, ids, probs, 5)
+        out[f"moe_glu_q4k_ep{world}_{name}_T{T}_per_rank"] = {"tokens_per_s": world * T / (ms * 1e-3), "ms": ms}
+        del ep
+        torch.cuda.empty_cache()
     return out
 
 

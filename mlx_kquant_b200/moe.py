@@ -58,18 +58,21 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor, row_expert: torch.Tensor | None
 
 
 def combine_partial(d: torch.Tensor, probs: torch.Tensor, k: int, out: torch.Tensor | None = None) -> torch.Tensor:
-    """float32 y[t] = sum_j probs[t, j] * d[t k + j]; rows of d whose weight is exactly 0 are not read. The
-    partial sum of a rank that computed only the rows of its own experts."""
+    """y[t] = sum_j probs[t, j] * d[t k + j]; rows of d whose weight is exactly 0 are not read. The partial sum
+    of a rank that computed only the rows of its own experts: float32 by default, or rounded once to d's dtype
+    when `out` has that dtype (half the bytes for the reduce-scatter that follows)."""
     rows, H = d.shape
     T = rows // k
     if not (d.is_cuda and d.dtype in (torch.float16, torch.bfloat16) and H % 8 == 0 and d.is_contiguous()):
         raise ValueError("[mlx_kquant.moe_combine] needs contiguous float16 / bfloat16 CUDA rows with H % 8 == 0.")
     p = probs.reshape(T * k).float().contiguous()
     y = torch.empty((T, H), dtype=torch.float32, device=d.device) if out is None else out
+    if y.dtype not in (torch.float32, d.dtype):
+        raise ValueError("[mlx_kquant.moe_combine] out must be float32 or of d's dtype.")
+    fn = _lib.lib().kq_moe_combine_f32 if y.dtype == torch.float32 else _lib.lib().kq_moe_combine
     with torch.cuda.device(d.device):
-        _lib.check(_lib.lib().kq_moe_combine_f32(d.data_ptr(), p.data_ptr(), T, k, H,
-                                                 _lib.KQ_F16 if d.dtype == torch.float16 else _lib.KQ_BF16,
-                                                 y.data_ptr(), torch.cuda.current_stream(d.device).cuda_stream))
+        _lib.check(fn(d.data_ptr(), p.data_ptr(), T, k, H, _lib.KQ_F16 if d.dtype == torch.float16 else _lib.KQ_BF16,
+                      y.data_ptr(), torch.cuda.current_stream(d.device).cuda_stream))
     return y
 
 
@@ -273,20 +276,6 @@ def moe_glu_expert_parallel(x, w_gate, w_up, w_down, kquant_type, expert_ids, ex
     T, H = x.shape
     k = expert_ids.shape[1]
     rows = T * k
-    # A few tokens: two launches - gate | up with the activation fused, then down with the weighted sum fused.
-    # One rounding (h) where the composition below has three (gate / up, h, down): not bit-identical to it.
-    if not sort_rows and fused is not False:
-        if w_gate_up is not None:
-            F = w_gate_up.shape[1] // 2
-            wg_v, wu_v = w_gate_up[:, :F], w_gate_up[:, F:]
-        else:
-            wg_v, wu_v = w_gate, w_up
-        if _fused_decode_ok(x, kquant_type, rows, wg_v, wu_v, w_down):
-            # one scratch buffer for both launches: the second reuses the grouping the first made
-            ws = _decode_ws(rows, w_down.shape[0], w_down.shape[1], x.device)
-            h = moe_glu_gather_kq(x, wg_v, wu_v, kquant_type, expert_ids, workspace=ws)
-            return gather_qmv_mix_ns_kq(h, w_down, kquant_type, expert_ids, expert_probs, workspace=ws,
-                                        reuse_grouping=True)
     flat_e = expert_ids.reshape(rows)
     tok = torch.arange(T, device=x.device).repeat_interleave(k)
     owner = expert_owner(flat_e, n_experts, world)
@@ -350,7 +339,7 @@ class GatheredExpertParallel:
     """
 
     def __init__(self, T, H, k, n_experts, w_gate_up, w_down, kquant_type, dtype=torch.bfloat16, group=None,
-                 *, rank=None, world=None):
+                 *, rank=None, world=None, reduce_dtype=torch.float32):
         from .dist import shard_bounds
 
         if world is None:  # rank / world given explicitly: no communicator (pack() and local_stage() only)
@@ -370,8 +359,10 @@ class GatheredExpertParallel:
         R = T + self.pad_rows
         self.send = torch.zeros((R, H), dtype=dtype, device=dev)
         self.recv = torch.empty((self.world * R, H), dtype=dtype, device=dev)
-        self.partial = torch.empty((self.world * T, H), dtype=torch.float32, device=dev)
-        self.y32 = torch.empty((T, H), dtype=torch.float32, device=dev)
+        # reduce_dtype: float32 partial sums (default), or the activation dtype - half the bytes through the
+        # reduce-scatter, at one extra rounding per rank's partial sum and the collective's own sums in that type
+        self.partial = torch.empty((self.world * T, H), dtype=reduce_dtype, device=dev)
+        self.y32 = torch.empty((T, H), dtype=reduce_dtype, device=dev)
         tok = torch.arange(T, device=dev).repeat_interleave(k)
         self.lhs = (torch.arange(self.world, device=dev)[:, None] * R + tok[None, :]).reshape(-1)
         self._graph = None
@@ -429,6 +420,45 @@ class GatheredExpertParallel:
             self.local_stage()
         dist.reduce_scatter_tensor(self.y32, self.partial, group=self.group)
         return self.y32.to(x.dtype)
+
+
+class PipelinedExpertParallel:
+    """GatheredExpertParallel over `chunks` slices of the tokens, so that the collectives of one slice overlap the
+    expert products of another: all slices' all-gathers are issued first (asynchronously, on the communicator's
+    stream), then slice by slice "wait for its gather, replay its local stage, issue its reduce-scatter". Same
+    results as the unsliced form (every token's sum is formed the same way). T must be a multiple of `chunks`."""
+
+    def __init__(self, T, H, k, n_experts, w_gate_up, w_down, kquant_type, dtype=torch.bfloat16, group=None, *,
+                 chunks=2, reduce_dtype=torch.float32):
+        if T % chunks:
+            raise ValueError("[mlx_kquant.moe] T must be a multiple of the number of chunks.")
+        self.T, self.chunks, self.group = T, chunks, group
+        self.parts = [GatheredExpertParallel(T // chunks, H, k, n_experts, w_gate_up, w_down, kquant_type, dtype,
+                                             group, reduce_dtype=reduce_dtype) for _ in range(chunks)]
+
+    def capture(self):
+        for p in self.parts:
+            p.capture()
+
+    def __call__(self, x, expert_ids, expert_probs):
+        import torch.distributed as dist
+
+        n = self.T // self.chunks
+        gathers, sums = [], []
+        for c, p in enumerate(self.parts):
+            sl = slice(c * n, (c + 1) * n)
+            p.pack(x[sl], expert_ids[sl], expert_probs[sl])
+            gathers.append(dist.all_gather_into_tensor(p.recv, p.send, group=self.group, async_op=True))
+        for c, p in enumerate(self.parts):
+            gathers[c].wait()
+            if p._graph is not None:
+                p._graph.replay()
+            else:
+                p.local_stage()
+            sums.append(dist.reduce_scatter_tensor(p.y32, p.partial, group=self.group, async_op=True))
+        for w in sums:
+            w.wait()
+        return torch.cat([p.y32 for p in self.parts]).to(x.dtype)
 
 
 def host_tile_maps(counts, device=None):
