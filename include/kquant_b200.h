@@ -201,6 +201,27 @@ KQ_API int kq_gather_qmv_mix(const void* x, int x_dtype, long long T, int S, int
                              long long w_expert_stride_bytes, size_t w_row_bytes, int N, int n_experts,
                              const char* kquant_type, const uint32_t* indices, const float* scores, void* y,
                              void* workspace, size_t workspace_bytes, int reuse_grouping, void* stream);
+/* One mixture-of-experts SwiGLU block for prefill-sized calls, y[t] = sum_j scores[t, j] * down_e( silu(gate_e x_t) *
+ * up_e x_t ) with e = indices[t, j]: what a reference caller composes from gather_qmm(gate), gather_qmm(up), the
+ * activation, gather_qmm(down) and the weighted sum (mlx_kquant/nn.py SwitchGLU + src/kquant_ops.cpp:292-420), with the
+ * same roundings to x's dtype after each product and after the activation - so the same bits as that composition -
+ * but ONE grouping by expert, no scatter / re-gather between the products and the activation computed inside the
+ * pre-pass of the down product. x [T, H] (row stride x_row_stride elements, float16 / bfloat16, 16-byte aligned rows);
+ * token_rows NULL, or [T] uint32: token t's activation is row token_rows[t] of x (tokens scattered in a larger
+ * buffer); w_gate_up [n_experts, 2 F, gate_up_row_bytes] = every expert's gate rows then its up rows (H weights per
+ * row); w_down [n_experts, H, down_row_bytes] (F weights per row); indices / scores [T, top_k] (uint32 / float32); an
+ * index outside [0, n_experts) contributes nothing (an expert-parallel rank passes the other ranks' experts that
+ * way). y [T, H] of y_dtype = x_dtype or KQ_F32 (partial sums for a later reduction). Any codec. Sizes: at least 512
+ * routed rows and 32 per expert on average, H % 8 == F % 8 == 0; otherwise KQ_ERR_UNSUPPORTED.
+ * kq_moe_block_workspace_bytes(T, top_k, n_experts, H, F): bytes of device scratch the call needs (0 = sizes not
+ * supported); 256-byte aligned, private to the call until it completes. */
+KQ_API size_t kq_moe_block_workspace_bytes(long long T, int top_k, int n_experts, int H, int F);
+KQ_API int kq_moe_swiglu_block(const void* x, int x_dtype, long long T, int H, long long x_row_stride,
+                               const uint32_t* token_rows, const void* w_gate_up, long long gate_up_expert_stride_bytes,
+                               size_t gate_up_row_bytes, int F, const void* w_down, long long down_expert_stride_bytes,
+                               size_t down_row_bytes, int n_experts, const char* kquant_type, const uint32_t* indices,
+                               const float* scores, int top_k, void* y, int y_dtype, void* workspace,
+                               size_t workspace_bytes, void* stream);
 KQ_API int kq_moe_router_topk(const void* logits, int dtype, long long T, int E, int top_k, int norm_topk_prob,
                               int shared_gate, const float* per_expert_scale, const float* bias, const char* scoring,
                               float scale, uint32_t* indices, float* scores, void* stream);

@@ -60,6 +60,11 @@ SIGNATURES = {
                                     C.c_void_p, C.c_size_t, C.c_int, C.c_void_p]),
     "kq_moe_router_topk": (C.c_int, [C.c_void_p, C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                      C.c_void_p, C.c_char_p, C.c_float, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "kq_moe_block_workspace_bytes": (C.c_size_t, [C.c_longlong, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "kq_moe_swiglu_block": (C.c_int, [C.c_void_p, C.c_int, C.c_longlong, C.c_int, C.c_longlong, C.c_void_p, C.c_void_p,
+                                      C.c_longlong, C.c_size_t, C.c_int, C.c_void_p, C.c_longlong, C.c_size_t, C.c_int,
+                                      C.c_char_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p,
+                                      C.c_size_t, C.c_void_p]),
     "kq_gather_qmm_workspace_bytes": (C.c_size_t, [C.c_longlong, C.c_int, C.c_int, C.c_int]),
     "kq_gather_qmm": (C.c_int, [C.c_void_p, C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_void_p, C.c_int,
                                 C.c_longlong, C.c_size_t, C.c_int, C.c_char_p, C.c_void_p, C.c_void_p,

@@ -502,6 +502,57 @@ int kq_gather_qmv_mix(const void* x, int x_dtype, long long T, int S, int K, con
   return KQ_OK;
 }
 
+size_t kq_moe_block_workspace_bytes(long long T, int top_k, int n_experts, int H, int F) {
+  return kq::moe_block_workspace_bytes(T, top_k, n_experts, H, F);
+}
+
+int kq_moe_swiglu_block(const void* x, int x_dtype, long long T, int H, long long x_row_stride,
+                        const uint32_t* token_rows, const void* w_gate_up, long long gate_up_expert_stride_bytes,
+                        size_t gate_up_row_bytes, int F, const void* w_down, long long down_expert_stride_bytes,
+                        size_t down_row_bytes, int n_experts, const char* kquant_type, const uint32_t* indices,
+                        const float* scores, int top_k, void* y, int y_dtype, void* workspace, size_t workspace_bytes,
+                        void* stream) {
+  const int ci = find_codec(kquant_type);
+  if (ci < 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_swiglu_block] Unknown kquant_type: '%s'.",
+                kquant_type ? kquant_type : "(null)");
+  const kq::CodecInfo& c = kq::kCodecs[ci];
+  if (T < 0 || H < 0 || F < 0 || top_k < 0 || n_experts < 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_swiglu_block] negative size.");
+  if (gate_up_row_bytes % (size_t)c.bpb != 0 || (long long)(gate_up_row_bytes / c.bpb) * c.wpb != H)
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.moe_swiglu_block] x last dim (%d) does not match the expanded gate / up row (%lld weights).", H,
+                (long long)(gate_up_row_bytes / c.bpb) * c.wpb);
+  if (down_row_bytes % (size_t)c.bpb != 0 || (long long)(down_row_bytes / c.bpb) * c.wpb != F)
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.moe_swiglu_block] expert FFN width (%d) does not match the expanded down row (%lld weights).", F,
+                (long long)(down_row_bytes / c.bpb) * c.wpb);
+  if (y_dtype != x_dtype && y_dtype != KQ_F32)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_swiglu_block] y must have x's dtype or float32.");
+  if (T == 0 || H == 0) return KQ_OK;
+  if (!x || !w_gate_up || !w_down || !indices || !scores || !y)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_swiglu_block] null pointer.");
+  const size_t xe = 2;
+  if (!kq::moe_block_supported(x_dtype, T, top_k, n_experts, H, F) || (reinterpret_cast<uintptr_t>(x) & 15) != 0 ||
+      ((size_t)x_row_stride * xe) % 16 != 0)
+    return fail(KQ_ERR_UNSUPPORTED,
+                "[mlx_kquant.moe_swiglu_block] the tile-kernel block takes float16 / bfloat16 rows (16-byte aligned), "
+                "H and F multiples of 8 and at least 512 routed rows with 32 or more per expert on average: compose "
+                "smaller calls from kq_moe_glu_gather + kq_gather_qmv_mix or kq_gather_qmm.");
+  const size_t need = kq::moe_block_workspace_bytes(T, top_k, n_experts, H, F);
+  if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.moe_swiglu_block] workspace too small or not 256-byte aligned: %zu bytes given, %zu needed.",
+                workspace_bytes, need);
+  cudaError_t e = kq::launch_moe_block(ci, x_dtype, x, x_row_stride, token_rows, T, H, static_cast<const uint8_t*>(w_gate_up),
+                                       gate_up_expert_stride_bytes, (long long)gate_up_row_bytes, F,
+                                       static_cast<const uint8_t*>(w_down), down_expert_stride_bytes,
+                                       (long long)down_row_bytes, n_experts, indices, scores, top_k, y, y_dtype == KQ_F32,
+                                       workspace, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("moe_swiglu_block", e);
+  return KQ_OK;
+}
+
 int kq_moe_router_topk(const void* logits, int dtype, long long T, int E, int top_k, int norm_topk_prob, int shared_gate,
                        const float* per_expert_scale, const float* bias, const char* scoring, float scale,
                        uint32_t* indices, float* scores, void* stream) {

@@ -15,6 +15,7 @@
 // expert-sorted fp16 copy of the activations (the tile kernel streams it with TMA),
 // and the tcgen05 tile kernel with a row-index scatter in its epilogue.
 // All of it lives in a caller-provided workspace laid out by gather_layout().
+#include <cstdint>
 #include <cstdio>
 #include <mutex>
 
@@ -435,6 +436,104 @@ cudaError_t launch_gather(int codec, int x_dtype, const void* x, long long x_bat
     if ((err = launch_gemv(codec, x_dtype, a, st)) != cudaSuccess) return err;
   }
   return cudaSuccess;
+}
+
+
+// ---------------------------------------------------------------- a whole SwiGLU block on the tile kernel
+// The composition gather_qmm(gate | up) -> silu * up -> gather_qmm(down) -> weighted sum groups the same
+// entries twice, scatters the first product back to entry order only to gather it again, and makes two
+// elementwise passes in between. Here the routed rows are grouped once, the gate | up product stays in
+// expert order, the activation is computed inside the fp16 pre-pass of the down product (with the same
+// roundings as the separate kernels, so the two forms give the same bits), and only the down product is
+// scattered back to entry order for the per-token sum.
+namespace {
+struct MoeBlockLayout {
+  size_t counts, cursor, offsets, tile_base, n_tiles, order, tiles, yrow, scale1, scale2, xh, gu, hh, total;
+  long long max_tiles;
+};
+MoeBlockLayout moe_block_layout(long long T, int k, int E, int H, int F) {
+  MoeBlockLayout L;
+  const size_t rows = (size_t)(T * k);
+  L.max_tiles = (long long)rows / kGroupedTileRows + E;
+  size_t off = 0;
+  L.counts = off;    off = align_up(off + 4 * (size_t)E, 256);
+  L.cursor = off;    off = align_up(off + 4 * (size_t)E, 256);
+  L.offsets = off;   off = align_up(off + 4 * ((size_t)E + 1), 256);
+  L.tile_base = off; off = align_up(off + 4 * ((size_t)E + 1), 256);
+  L.n_tiles = off;   off = align_up(off + 4, 256);
+  L.order = off;     off = align_up(off + 4 * rows, 256);
+  L.tiles = off;     off = align_up(off + 16 * (size_t)L.max_tiles, 256);
+  L.yrow = off;      off = align_up(off + 4 * rows, 256);
+  L.scale1 = off;    off = align_up(off + 4 * rows, 256);
+  L.scale2 = off;    off = align_up(off + 4 * rows, 256);
+  L.xh = off;        off = align_up(off + 2 * rows * (size_t)H, 256);  // later the down product in entry order
+  L.gu = off;        off = align_up(off + 4 * rows * (size_t)F, 256);
+  L.hh = off;        off = align_up(off + 2 * rows * (size_t)F, 256);
+  L.total = off;
+  return L;
+}
+}  // namespace
+
+bool moe_block_supported(int x_dtype, long long T, int k, int n_experts, int H, int F) {
+  if (x_dtype != F16 && x_dtype != BF16) return false;
+  if (T <= 0 || k <= 0 || n_experts <= 0 || H <= 0 || F <= 0 || (H % 8) != 0 || (F % 8) != 0) return false;
+  if (T > (long long)INT32_MAX / k) return false;
+  if (!use_grouped(T * k, 1, n_experts, H)) return false;
+  return T * k / kGroupedTileRows + n_experts <= 65535;
+}
+
+size_t moe_block_workspace_bytes(long long T, int k, int n_experts, int H, int F) {
+  return moe_block_supported(F16, T, k, n_experts, H, F) ? moe_block_layout(T, k, n_experts, H, F).total : 0;
+}
+
+cudaError_t launch_moe_block(int codec, int x_dtype, const void* x, long long x_row_stride, const uint32_t* token_rows,
+                             long long T, int H, const uint8_t* wgu, long long stride_gu, long long rb_h, int F,
+                             const uint8_t* wd, long long stride_d, long long rb_f, int n_experts, const uint32_t* idx,
+                             const float* scores, int k, void* y, bool y_f32, void* workspace, cudaStream_t st) {
+  if (!moe_block_supported(x_dtype, T, k, n_experts, H, F)) return cudaErrorInvalidValue;
+  const MoeBlockLayout L = moe_block_layout(T, k, n_experts, H, F);
+  const long long n = T * k;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  int* counts = reinterpret_cast<int*>(ws + L.counts);
+  int* cursor = reinterpret_cast<int*>(ws + L.cursor);
+  int* offsets = reinterpret_cast<int*>(ws + L.offsets);
+  int* tile_base = reinterpret_cast<int*>(ws + L.tile_base);
+  int* n_tiles = reinterpret_cast<int*>(ws + L.n_tiles);
+  int* order = reinterpret_cast<int*>(ws + L.order);
+  GatherTile* tiles = reinterpret_cast<GatherTile*>(ws + L.tiles);
+  int* yrow = reinterpret_cast<int*>(ws + L.yrow);
+  float* scale1 = reinterpret_cast<float*>(ws + L.scale1);
+  float* scale2 = reinterpret_cast<float*>(ws + L.scale2);
+  __half* xh = reinterpret_cast<__half*>(ws + L.xh);
+  void* gu = ws + L.gu;
+  __half* hh = reinterpret_cast<__half*>(ws + L.hh);
+  void* d = ws + L.xh;  // the sorted copy of x is dead once the gate | up product has run
+
+  cudaError_t err = cudaMemsetAsync(ws + L.counts, 0, L.offsets - L.counts, st);
+  if (err != cudaSuccess) return err;
+  const int th = 256;
+  const unsigned nb = (unsigned)((n + th - 1) / th);
+  gather_hist_kernel<<<nb, th, 0, st>>>(idx, nullptr, 0, n, n_experts, counts);
+  gather_scan_kernel<<<1, 1024, 0, st>>>(counts, n_experts, 1, kGroupedTileRows, offsets, tile_base, n_tiles);
+  gather_scatter_kernel<<<nb, th, 0, st>>>(idx, nullptr, 0, n, n_experts, offsets, cursor, order);
+  gather_tiles_kernel<<<n_experts, 64, 0, st>>>(1, offsets, tile_base, tiles);
+  if ((err = cudaGetLastError()) != cudaSuccess) return err;
+  const int* n_valid = offsets + n_experts;  // entries whose expert is in range: the sorted rows that exist
+  const bool half = x_dtype == F16;
+  // routed rows in expert order (token of entry b = b / k), yrow[r] = entry of sorted row r
+  if ((err = launch_convert(x_dtype, x, x_row_stride, H, n, order, token_rows, k, 1, xh, scale1, yrow, n_valid, false,
+                            st)) != cudaSuccess)
+    return err;
+  if ((err = launch_gemm_tiles(codec, half, xh, n, H, wgu, stride_gu, rb_h, 2 * F, gu, half ? nullptr : scale1, nullptr,
+                               tiles, n_tiles, (int)L.max_tiles, st)) != cudaSuccess)
+    return err;
+  if ((err = launch_convert(x_dtype, gu, 2LL * F, F, n, nullptr, nullptr, 1, 1, hh, scale2, nullptr, n_valid, true, st)) !=
+      cudaSuccess)
+    return err;
+  if ((err = launch_gemm_tiles(codec, half, hh, n, F, wd, stride_d, rb_f, H, d, half ? nullptr : scale2, yrow, tiles,
+                               n_tiles, (int)L.max_tiles, st)) != cudaSuccess)
+    return err;
+  return launch_moe_combine(x_dtype, d, scores, T, k, H, y, y_f32, st, idx, (uint32_t)n_experts);
 }
 
 }  // namespace kq

@@ -527,7 +527,7 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
 // its result goes; this is the expert-sorted copy the grouped kernel streams with TMA.
 template <typename XT>
 __global__ void __launch_bounds__(256)
-convert_x_kernel(const XT* __restrict__ x, long long x_row_stride, int K, __half* __restrict__ xh,
+convert_x_scalar_kernel(const XT* __restrict__ x, long long x_row_stride, int K, __half* __restrict__ xh,
                  float* __restrict__ row_scale, const int* __restrict__ order, const uint32_t* __restrict__ lhs, int M,
                  int* __restrict__ yrow, const int* __restrict__ n_valid) {
   const long long row = blockIdx.x;
@@ -580,20 +580,191 @@ convert_x_kernel(const XT* __restrict__ x, long long x_row_stride, int K, __half
   }
 }
 
+
+// ---- the same pre-pass, eight activations per access: one warp per row, the first 2048 activations of a row
+// stay in registers between the two passes (largest magnitude, then the scaled copy). Rows and K must be whole
+// numbers of 16 bytes (callers fall back to the scalar kernel above otherwise).
+// GLU: the source row holds gate | up (2 K values); the activation is h = silu(gate) * up, rounded to XT first -
+// the value a separate activation kernel would have stored - so the fused form changes no bit of the product.
+// Eight consecutive activations as four bf16 pairs (float input rounded to bf16 as the reference's op does).
+template <typename XT>
+__device__ __forceinline__ uint4 cvt_load8_bf16(const XT* p) {
+  if constexpr (sizeof(XT) == 4) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+    const __nv_bfloat162 q0 = __floats2bfloat162_rn(a.x, a.y), q1 = __floats2bfloat162_rn(a.z, a.w),
+                         q2 = __floats2bfloat162_rn(b.x, b.y), q3 = __floats2bfloat162_rn(b.z, b.w);
+    return make_uint4(*reinterpret_cast<const uint32_t*>(&q0), *reinterpret_cast<const uint32_t*>(&q1),
+                      *reinterpret_cast<const uint32_t*>(&q2), *reinterpret_cast<const uint32_t*>(&q3));
+  } else {
+    return __ldg(reinterpret_cast<const uint4*>(p));
+  }
+}
+// The fused activation over eight gate / up pairs of 16-bit type XT: h = silu(gate) * up rounded to XT, returned
+// as XT pairs.
+template <typename XT>
+__device__ __forceinline__ uint4 cvt_glu8(const XT* xr, int K, int c) {
+  const uint4 g = __ldg(reinterpret_cast<const uint4*>(xr + 8 * c));
+  const uint4 u = __ldg(reinterpret_cast<const uint4*>(xr + K + 8 * c));
+  const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    if constexpr (std::is_same<XT, __half>::value) {
+      const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&gw[i]));
+      const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&uw[i]));
+      o[i] = pack_h2f(silu_f(a.x) * b.x, silu_f(a.y) * b.y);
+    } else {
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gw[i]));
+      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw[i]));
+      const __nv_bfloat162 h = __floats2bfloat162_rn(silu_f(a.x) * b.x, silu_f(a.y) * b.y);
+      o[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+template <typename XT, bool GLU>
+__device__ __forceinline__ uint4 cvt_fetch8(const XT* xr, int K, int c) {
+  if constexpr (GLU) return cvt_glu8<XT>(xr, K, c);
+  else return cvt_load8_bf16<XT>(xr + 8 * c);
+}
+__device__ __forceinline__ __nv_bfloat162 cvt_absmax(__nv_bfloat162 m, const uint4& q) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int i = 0; i < 4; i++) m = __hmax2(m, __habs2(*reinterpret_cast<const __nv_bfloat162*>(&w[i])));  // skips NaNs
+  return m;
+}
+__device__ __forceinline__ float cvt_finite_absmax(float m, const uint4& q) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+    if (fabsf(f.x) < INFINITY) m = fmaxf(m, fabsf(f.x));
+    if (fabsf(f.y) < INFINITY) m = fmaxf(m, fabsf(f.y));
+  }
+  return m;
+}
+// bf16 pairs times s1 * s2 (powers of two: exact) -> fp16 pairs
+__device__ __forceinline__ uint4 cvt_scale8(const uint4& q, float s1, float s2) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+    o[i] = pack_h2f(f.x * s1 * s2, f.y * s1 * s2);
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+constexpr int kCvtChunks = 8;
+template <typename XT, bool GLU>
+__global__ void __launch_bounds__(256, 3)
+convert_x_kernel(const XT* __restrict__ x, long long x_row_stride, int K, __half* __restrict__ xh,
+                 float* __restrict__ row_scale, const int* __restrict__ order, const uint32_t* __restrict__ lhs,
+                 int lhs_div, int M, int* __restrict__ yrow, const int* __restrict__ n_valid, long long rows) {
+  static_assert(!GLU || sizeof(XT) == 2, "the fused activation takes fp16 / bf16 gate | up rows");
+  const int lane = threadIdx.x & 31;
+  const long long row = blockIdx.x * 8LL + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  if (n_valid != nullptr && row >= (long long)(*n_valid) * M) return;  // see the scalar kernel
+  long long src_row = row;
+  if (order != nullptr) {
+    const int entry = order[row / M], i = (int)(row % M);
+    // the activation row of an entry: that of unit u = entry / lhs_div (lhs_div = k routed rows per token when
+    // the entries are a [tokens, k] routing table, else 1), through lhs when there is an index array
+    const int u = entry / lhs_div;
+    src_row = (lhs != nullptr ? (long long)lhs[u] : (long long)u) * M + i;
+    if (lane == 0 && yrow != nullptr) yrow[row] = entry * M + i;
+  } else if (lhs != nullptr) {
+    src_row = (long long)lhs[row / M] * M + row % M;
+  }
+  const XT* xr = x + src_row * x_row_stride;
+  __half* o = xh + row * (long long)K;
+  const int nch = K >> 3;
+  if constexpr (std::is_same<XT, __half>::value) {
+    for (int c = lane; c < nch; c += 32) *reinterpret_cast<uint4*>(o + 8 * c) = cvt_fetch8<XT, GLU>(xr, K, c);
+    if (lane == 0) row_scale[row] = 1.f;
+  } else {
+    uint4 keep[kCvtChunks];  // the row's values as bf16 pairs (they are bf16 values: nothing is lost)
+    __nv_bfloat162 m2 = __floats2bfloat162_rn(0.f, 0.f);
+#pragma unroll
+    for (int j = 0; j < kCvtChunks; j++) {
+      const int c = lane + 32 * j;
+      if (c < nch) {
+        keep[j] = cvt_fetch8<XT, GLU>(xr, K, c);
+        m2 = cvt_absmax(m2, keep[j]);
+      }
+    }
+    for (int c = lane + 32 * kCvtChunks; c < nch; c += 32) m2 = cvt_absmax(m2, cvt_fetch8<XT, GLU>(xr, K, c));
+    float mx = fmaxf(__low2float(m2), __high2float(m2));
+    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    if (!(mx < INFINITY)) {
+      // a row with infinities: they propagate on their own, the factor comes from the finite values
+      mx = 0.f;
+#pragma unroll
+      for (int j = 0; j < kCvtChunks; j++)
+        if (lane + 32 * j < nch) mx = cvt_finite_absmax(mx, keep[j]);
+      for (int c = lane + 32 * kCvtChunks; c < nch; c += 32) mx = cvt_finite_absmax(mx, cvt_fetch8<XT, GLU>(xr, K, c));
+      for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    }
+    // Every row is normalised (see the scalar kernel); 2^-e in two exact halves, since it can overflow float32.
+    int e = 0;
+    if (mx > 0.f) e = ilogbf(mx) - 14;
+    const int eh = (-e) / 2;
+    const float down1 = ldexpf(1.f, eh), down2 = ldexpf(1.f, -e - eh);
+    if (lane == 0) row_scale[row] = ldexpf(1.f, e);
+#pragma unroll
+    for (int j = 0; j < kCvtChunks; j++) {
+      const int c = lane + 32 * j;
+      if (c < nch) *reinterpret_cast<uint4*>(o + 8 * c) = cvt_scale8(keep[j], down1, down2);
+    }
+    for (int c = lane + 32 * kCvtChunks; c < nch; c += 32)
+      *reinterpret_cast<uint4*>(o + 8 * c) = cvt_scale8(cvt_fetch8<XT, GLU>(xr, K, c), down1, down2);
+  }
+}
+
+template <typename XT>
+static void launch_convert_t(const void* x, long long x_row_stride, int K, long long rows, const int* order,
+                             const uint32_t* lhs, int lhs_div, int M, __half* o, float* row_scale, int* yrow,
+                             const int* n_valid, bool glu, bool vec, cudaStream_t st) {
+  const XT* xp = static_cast<const XT*>(x);
+  const unsigned gv = (unsigned)((rows + 7) / 8);
+  if (glu) {
+    if constexpr (sizeof(XT) == 2)
+      convert_x_kernel<XT, true><<<gv, 256, 0, st>>>(xp, x_row_stride, K, o, row_scale, order, lhs, lhs_div, M, yrow,
+                                                     n_valid, rows);
+  } else if (vec) {
+    convert_x_kernel<XT, false><<<gv, 256, 0, st>>>(xp, x_row_stride, K, o, row_scale, order, lhs, lhs_div, M, yrow,
+                                                    n_valid, rows);
+  } else {
+    convert_x_scalar_kernel<XT><<<(unsigned)rows, 256, 0, st>>>(xp, x_row_stride, K, o, row_scale, order, lhs, M, yrow,
+                                                                n_valid);
+  }
+}
+
+// One launch of the pre-pass: rows [rows, K] of x (dtype x_dtype, row stride in elements) -> xh, row_scale.
+// order / lhs / lhs_div / M / yrow / n_valid as in the kernels; glu: x rows hold gate | up (2 K values).
+cudaError_t launch_convert(int x_dtype, const void* x, long long x_row_stride, int K, long long rows, const int* order,
+                           const uint32_t* lhs, int lhs_div, int M, void* xh, float* row_scale, int* yrow,
+                           const int* n_valid, bool glu, cudaStream_t st) {
+  if (rows <= 0 || K <= 0) return cudaSuccess;
+  __half* o = static_cast<__half*>(xh);
+  const size_t es = x_dtype == F32 ? 4 : 2;
+  const bool vec = (K % 8) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && ((size_t)x_row_stride * es) % 16 == 0 &&
+                   (reinterpret_cast<uintptr_t>(xh) & 15) == 0;
+  if (glu && (!vec || x_dtype == F32)) return cudaErrorInvalidValue;
+  if (!vec && order != nullptr && (lhs == nullptr || lhs_div != 1)) return cudaErrorInvalidValue;  // vector kernel only
+  if (x_dtype == F16)
+    launch_convert_t<__half>(x, x_row_stride, K, rows, order, lhs, lhs_div, M, o, row_scale, yrow, n_valid, glu, vec, st);
+  else if (x_dtype == BF16)
+    launch_convert_t<__nv_bfloat16>(x, x_row_stride, K, rows, order, lhs, lhs_div, M, o, row_scale, yrow, n_valid, glu,
+                                    vec, st);
+  else
+    launch_convert_t<float>(x, x_row_stride, K, rows, order, lhs, lhs_div, M, o, row_scale, yrow, n_valid, glu, vec, st);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_convert_rows(int x_dtype, const void* x, long long x_row_stride, int K, long long rows,
                                 const uint32_t* lhs, int M, void* xh, float* row_scale, cudaStream_t st) {
-  if (rows <= 0) return cudaSuccess;
-  __half* o = static_cast<__half*>(xh);
-  if (x_dtype == F16)
-    convert_x_kernel<__half><<<(unsigned)rows, 256, 0, st>>>(static_cast<const __half*>(x), x_row_stride, K, o,
-                                                             row_scale, nullptr, lhs, M, nullptr, nullptr);
-  else if (x_dtype == BF16)
-    convert_x_kernel<__nv_bfloat16><<<(unsigned)rows, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), x_row_stride,
-                                                                    K, o, row_scale, nullptr, lhs, M, nullptr, nullptr);
-  else
-    convert_x_kernel<float><<<(unsigned)rows, 256, 0, st>>>(static_cast<const float*>(x), x_row_stride, K, o, row_scale,
-                                                            nullptr, lhs, M, nullptr, nullptr);
-  return cudaGetLastError();
+  return launch_convert(x_dtype, x, x_row_stride, K, rows, nullptr, lhs, 1, M, xh, row_scale, nullptr, nullptr, false, st);
 }
 
 size_t gemm_workspace_bytes(int x_dtype, long long rows, int K) {
@@ -748,13 +919,7 @@ cudaError_t launch_gemm(int codec, int x_dtype, const void* x, long long x_row_s
   if (x_dtype != F16) {
     __half* xh = static_cast<__half*>(workspace);
     float* rs = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + (((size_t)M * K * 2 + 255) & ~(size_t)255));
-    if (x_dtype == BF16)
-      convert_x_kernel<__nv_bfloat16><<<M, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), x_row_stride, K, xh, rs,
-                                                         nullptr, nullptr, 1, nullptr, nullptr);
-    else
-      convert_x_kernel<float><<<M, 256, 0, st>>>(static_cast<const float*>(x), x_row_stride, K, xh, rs, nullptr,
-                                                 nullptr, 1, nullptr, nullptr);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = launch_convert(x_dtype, x, x_row_stride, K, M, nullptr, nullptr, 1, 1, xh, rs, nullptr, nullptr, false, st);
     if (e != cudaSuccess) return e;
     a.x = xh;
     a.x_row_stride = K;
@@ -805,16 +970,7 @@ cudaError_t launch_gemm_grouped(int codec, int x_dtype, const void* x, int M, in
                                 int* yrow, const void* tiles, const int* n_tiles_dev, int max_tiles,
                                 const int* n_valid_dev, cudaStream_t st) {
   if (rows_total <= 0 || N <= 0 || K <= 0) return cudaSuccess;
-  if (x_dtype == F16)
-    convert_x_kernel<__half><<<(unsigned)rows_total, 256, 0, st>>>(static_cast<const __half*>(x), K, K, xh, row_scale,
-                                                                    order, lhs, M, yrow, n_valid_dev);
-  else if (x_dtype == BF16)
-    convert_x_kernel<__nv_bfloat16><<<(unsigned)rows_total, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), K, K,
-                                                                           xh, row_scale, order, lhs, M, yrow, n_valid_dev);
-  else
-    convert_x_kernel<float><<<(unsigned)rows_total, 256, 0, st>>>(static_cast<const float*>(x), K, K, xh, row_scale,
-                                                                   order, lhs, M, yrow, n_valid_dev);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_convert(x_dtype, x, K, K, rows_total, order, lhs, 1, M, xh, row_scale, yrow, n_valid_dev, false, st);
   if (e != cudaSuccess) return e;
   return launch_gemm_tiles(codec, x_dtype == F16, xh, rows_total, K, w, expert_stride, row_bytes, N, y,
                            x_dtype == F16 ? nullptr : row_scale, yrow, tiles, n_tiles_dev, max_tiles, st);

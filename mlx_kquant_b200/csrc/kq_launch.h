@@ -120,6 +120,22 @@ cudaError_t launch_gemv_stream(int x_dtype, const GemvArgs& a, cudaStream_t st);
 cudaError_t launch_convert_rows(int x_dtype, const void* x, long long x_row_stride, int K, long long rows,
                                 const uint32_t* lhs, int M, void* xh, float* row_scale, cudaStream_t st);
 
+// The general form of that pre-pass: optional expert order (output row r is entry order[r / M]), optional
+// index array over units of lhs_div entries, optional fused h = silu(gate) * up over gate | up rows (glu).
+cudaError_t launch_convert(int x_dtype, const void* x, long long x_row_stride, int K, long long rows, const int* order,
+                           const uint32_t* lhs, int lhs_div, int M, void* xh, float* row_scale, int* yrow,
+                           const int* n_valid, bool glu, cudaStream_t st);
+
+// A whole mixture-of-experts SwiGLU block on the tile kernel (kq_gather.cu): one grouping, an expert-sorted fp16
+// copy of the routed rows, gate | up product left in expert order, activation fused into the pre-pass of the
+// down product, weighted sum per token. wgu: [E, 2F, rb_h] (gate rows then up rows); y: x dtype or float32.
+bool moe_block_supported(int x_dtype, long long T, int k, int n_experts, int H, int F);
+size_t moe_block_workspace_bytes(long long T, int k, int n_experts, int H, int F);
+cudaError_t launch_moe_block(int codec, int x_dtype, const void* x, long long x_row_stride, const uint32_t* token_rows,
+                             long long T, int H, const uint8_t* wgu, long long stride_gu, long long rb_h, int F,
+                             const uint8_t* wd, long long stride_d, long long rb_f, int n_experts, const uint32_t* idx,
+                             const float* scores, int k, void* y, bool y_f32, void* workspace, cudaStream_t st);
+
 // gather_qmm: device-side grouping by expert + the skinny-M kernel per group.
 struct GatherLayout {
   size_t counts, offsets, task_base, cursor, n_tasks, order, tasks, total;
@@ -169,7 +185,7 @@ cudaError_t launch_gemv_imma(int x_dtype, const GemvArgs& a, cudaStream_t st);
 cudaError_t launch_swiglu(int dtype, const void* gate, const void* up, long long in_row_stride, long long rows, int F,
                           void* out, const uint32_t* row_expert, uint32_t n_experts, cudaStream_t st);
 cudaError_t launch_moe_combine(int dtype, const void* d, const float* probs, long long tokens, int k, int H, void* y,
-                               bool y_f32, cudaStream_t st);
+                               bool y_f32, cudaStream_t st, const uint32_t* idx = nullptr, uint32_t n_experts = 0);
 
 cudaError_t launch_qvm_gather(int codec, int x_dtype, const void* x, long long x_batch, void* y, const uint8_t* w,
                               int n_experts, long long expert_stride, long long row_bytes, int M, int N, int K,

@@ -37,7 +37,6 @@ __device__ __forceinline__ uint32_t float_to_pair<__nv_bfloat16>(float a, float 
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-__device__ __forceinline__ float silu(float v) { return v / (1.f + __expf(-v)); }
 
 // eight elements per thread; F % 8 == 0, rows 16-byte aligned
 template <typename T>
@@ -59,7 +58,7 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const T* __restrict__ gate,
 #pragma unroll
     for (int j = 0; j < 4; j++) {
       const float2 a = pair_to_float<T>(gw[j]), b = pair_to_float<T>(uw[j]);
-      o[j] = float_to_pair<T>(silu(a.x) * b.x, silu(a.y) * b.y);
+      o[j] = float_to_pair<T>(silu_f(a.x) * b.x, silu_f(a.y) * b.y);
     }
     *reinterpret_cast<uint4*>(out + r * (long long)F + c) = make_uint4(o[0], o[1], o[2], o[3]);
   }
@@ -87,9 +86,10 @@ __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* o, const fl
 
 // one CTA per token: y[t, :] = sum_j p[t, j] * d[t k + j, :]; H % 8 == 0. A row whose weight is exactly zero
 // is not read (an expert-parallel rank zeroes the weights of the rows other ranks own, and those rows of d
-// were never written).
+// were never written); with idx given, neither is a row whose expert index is outside [0, n_experts).
 template <typename T, typename OT>
-__global__ void __launch_bounds__(256) combine_kernel(const T* __restrict__ d, const float* __restrict__ p, int k, int H,
+__global__ void __launch_bounds__(256) combine_kernel(const T* __restrict__ d, const float* __restrict__ p,
+                                                     const uint32_t* __restrict__ idx, uint32_t n_experts, int k, int H,
                                                      OT* __restrict__ y) {
   const long long t = blockIdx.x;
   for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
@@ -97,6 +97,7 @@ __global__ void __launch_bounds__(256) combine_kernel(const T* __restrict__ d, c
     for (int j = 0; j < k; j++) {
       const float w = p[t * k + j];
       if (w == 0.f) continue;
+      if (idx != nullptr && idx[t * k + j] >= n_experts) continue;
       const uint4 v = *reinterpret_cast<const uint4*>(d + (t * k + j) * (long long)H + c);
       const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -128,17 +129,17 @@ cudaError_t launch_swiglu(int dtype, const void* gate, const void* up, long long
 }
 
 cudaError_t launch_moe_combine(int dtype, const void* d, const float* probs, long long tokens, int k, int H, void* y,
-                               bool y_f32, cudaStream_t st) {
+                               bool y_f32, cudaStream_t st, const uint32_t* idx, uint32_t n_experts) {
   if (tokens <= 0 || H <= 0 || k <= 0) return cudaSuccess;
   const unsigned g = (unsigned)tokens;
   if (dtype == F16) {
     const __half* dp = static_cast<const __half*>(d);
-    if (y_f32) combine_kernel<__half, float><<<g, 256, 0, st>>>(dp, probs, k, H, static_cast<float*>(y));
-    else combine_kernel<__half, __half><<<g, 256, 0, st>>>(dp, probs, k, H, static_cast<__half*>(y));
+    if (y_f32) combine_kernel<__half, float><<<g, 256, 0, st>>>(dp, probs, idx, n_experts, k, H, static_cast<float*>(y));
+    else combine_kernel<__half, __half><<<g, 256, 0, st>>>(dp, probs, idx, n_experts, k, H, static_cast<__half*>(y));
   } else {
     const __nv_bfloat16* dp = static_cast<const __nv_bfloat16*>(d);
-    if (y_f32) combine_kernel<__nv_bfloat16, float><<<g, 256, 0, st>>>(dp, probs, k, H, static_cast<float*>(y));
-    else combine_kernel<__nv_bfloat16, __nv_bfloat16><<<g, 256, 0, st>>>(dp, probs, k, H, static_cast<__nv_bfloat16*>(y));
+    if (y_f32) combine_kernel<__nv_bfloat16, float><<<g, 256, 0, st>>>(dp, probs, idx, n_experts, k, H, static_cast<float*>(y));
+    else combine_kernel<__nv_bfloat16, __nv_bfloat16><<<g, 256, 0, st>>>(dp, probs, idx, n_experts, k, H, static_cast<__nv_bfloat16*>(y));
   }
   return cudaGetLastError();
 }

@@ -188,6 +188,44 @@ def gather_qmv_mix_ns_kq(x, w, kquant_type, indices, scores, *, workspace=None, 
     return y
 
 
+def moe_swiglu_block(x, w_gate_up, w_down, kquant_type, expert_ids, expert_probs, *, token_rows=None, tokens=None,
+                     out=None, workspace=None):
+    """A whole SwiGLU block on the tile kernel (kq_moe_swiglu_block in include/kquant_b200.h): x [T, H] float16 /
+    bfloat16, w_gate_up [E, 2F, bytes(H)] (`fuse_gate_up`), w_down [E, H, bytes(F)], expert_ids / expert_probs [T, k]
+    -> y [T, H]. Same bits as the three-gather composition with its activation and weighted-sum kernels.
+    token_rows [T] (with tokens = T): token t's activation is row token_rows[t] of x. out: a [T, H] tensor of x's
+    dtype or float32 to write into. Returns None when the sizes are outside the block's regime."""
+    T = int(tokens) if tokens is not None else x.shape[0]
+    H = x.shape[1]
+    k = expert_ids.shape[1]
+    E, F2, rb_h = w_gate_up.shape
+    F = F2 // 2
+    if not (x.is_cuda and x.dtype in (torch.float16, torch.bfloat16) and x.stride(1) == 1):
+        return None
+    if w_down.shape[0] != E or w_down.shape[1] != H:
+        raise ValueError("[mlx_kquant.moe_swiglu_block] w_down must be [E, H, bytes] for w_gate_up [E, 2F, bytes].")
+    for w in (w_gate_up, w_down):
+        if w.dtype != torch.uint8 or w.stride(2) != 1 or w.stride(1) != w.shape[2]:
+            raise ValueError("[mlx_kquant.moe_swiglu_block] expert stacks must be uint8, dense in their last two dims.")
+    need = _lib.lib().kq_moe_block_workspace_bytes(T, k, E, H, F)
+    if need == 0 or x.data_ptr() % 16 or (x.stride(0) * 2) % 16:
+        return None
+    idx = _u32(expert_ids, x.device)
+    sc = expert_probs.to(device=x.device, dtype=torch.float32).contiguous()
+    tr = _u32(token_rows, x.device) if token_rows is not None else None
+    y = out if out is not None else torch.empty((T, H), dtype=x.dtype, device=x.device)
+    if y.dtype not in (x.dtype, torch.float32) or not y.is_contiguous() or tuple(y.shape) != (T, H):
+        raise ValueError("[mlx_kquant.moe_swiglu_block] out must be a contiguous [T, H] tensor of x's dtype or float32.")
+    with torch.cuda.device(x.device):
+        ws = workspace if workspace is not None else torch.empty(need, dtype=torch.uint8, device=x.device)
+        _lib.check(_lib.lib().kq_moe_swiglu_block(
+            x.data_ptr(), _DT[x.dtype], T, H, x.stride(0), tr.data_ptr() if tr is not None else None,
+            w_gate_up.data_ptr(), w_gate_up.stride(0), rb_h, F, w_down.data_ptr(), w_down.stride(0), w_down.shape[2], E,
+            kquant_type.encode(), idx.data_ptr(), sc.data_ptr(), k, y.data_ptr(), _DT[y.dtype], ws.data_ptr(), ws.numel(),
+            torch.cuda.current_stream(x.device).cuda_stream))
+    return y
+
+
 def _fused_decode_ok(x, kquant_type, rows, *stacks) -> bool:
     if not (x.is_cuda and x.dtype in (torch.float16, torch.bfloat16) and _fused_regime(rows, stacks[0].shape[0])):
         return False
@@ -225,6 +263,12 @@ def moe_glu(x, w_gate, w_up, w_down, kquant_type, expert_ids, expert_probs, *, s
             h = moe_glu_gather_kq(x, wg_v, wu_v, kquant_type, expert_ids, workspace=ws)
             return gather_qmv_mix_ns_kq(h, w_down, kquant_type, expert_ids, expert_probs, workspace=ws,
                                         reuse_grouping=True)
+        # Prefill sizes with a stacked gate | up: the whole block in one call (one grouping, the first product
+        # kept in expert order, the activation inside the pre-pass of the down product); same bits as below.
+        if w_gate_up is not None:
+            y = moe_swiglu_block(x, w_gate_up, w_down, kquant_type, expert_ids, expert_probs)
+            if y is not None:
+                return y
     flat_e = expert_ids.reshape(rows)
     tok = torch.arange(T, device=x.device).repeat_interleave(k)
     # Rows go in routing order: gather_qmm groups them by expert on the device itself, so the explicit
@@ -365,6 +409,13 @@ class GatheredExpertParallel:
         self.y32 = torch.empty((T, H), dtype=reduce_dtype, device=dev)
         tok = torch.arange(T, device=dev).repeat_interleave(k)
         self.lhs = (torch.arange(self.world, device=dev)[:, None] * R + tok[None, :]).reshape(-1)
+        # row of `recv` that holds token t of rank w, for the one-call block (taken when the sizes allow it)
+        self.tok_rows = (torch.arange(self.world, device=dev)[:, None] * R +
+                         torch.arange(T, device=dev)[None, :]).reshape(-1).to(torch.int32)
+        self.block_ok = bool(dev.type == "cuda" and dtype in (torch.float16, torch.bfloat16) and
+                             reduce_dtype in (dtype, torch.float32) and
+                             _lib.lib().kq_moe_block_workspace_bytes(self.world * T, k, self.e_local, H,
+                                                                     w_gate_up.shape[1] // 2) > 0)
         self._graph = None
 
     def _meta(self, buf, R):
@@ -380,6 +431,10 @@ class GatheredExpertParallel:
         mine = (ids >= 0) & (ids < self.e_local)
         probs = torch.where(mine, probs, torch.zeros_like(probs))
         rows = W * T * k
+        if self.block_ok:
+            moe_swiglu_block(self.recv, self.w_gate_up, self.w_down, self.kquant_type, ids.view(W * T, k),
+                             probs.view(W * T, k), token_rows=self.tok_rows, tokens=W * T, out=self.partial)
+            return
         Fh = self.w_gate_up.shape[1] // 2
         gu = gather_qmm(self.recv.view(W * R, 1, self.H), self.w_gate_up, None, self.kquant_type,
                         lhs_indices=self.lhs, rhs_indices=ids).reshape(rows, 2 * Fh)

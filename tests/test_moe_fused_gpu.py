@@ -251,3 +251,78 @@ def test_grouped_forms_beyond_the_direct_limit(oracle, dt):
     refm = np.stack([sum(sc[t, s] * (xms[t, s] @ Wd[ids[t, s]].T) for s in range(S) if ok[t, s]) for t in range(T)])
     err = np.linalg.norm(y_to_f32(ym) - refm) / np.linalg.norm(refm)
     assert err < 4e-3, err          # every slot's product is rounded once before the weighted sum
+
+
+# ------------------------------------------------------------------------------------------ the one-call block
+def _block_case(codec, E, H, F, seed):
+    rng = np.random.default_rng(seed)
+    mk = lambda n, k: torch.from_numpy(np.stack([mint_wire(codec, rng.normal(0, 0.02, (n, k)).astype(np.float32))
+                                                 for _ in range(E)])).cuda()
+    return mk(2 * F, H), mk(H, F)
+
+
+@pytest.mark.parametrize("codec,dt", [("q4_k", torch.bfloat16), ("q4_k", torch.float16), ("q6_k", torch.bfloat16)])
+def test_block_same_bits_as_the_composition(codec, dt):
+    """kq_moe_swiglu_block against the three-gather composition (gather_qmm x2, the activation kernel, the weighted
+    sum): the same roundings in the same places, so bit-identical outputs - including tokens routed to an expert
+    outside [0, E), which contribute nothing in either form."""
+    from mlx_kquant_b200.moe import moe_swiglu_block
+
+    E, H, F, k, T = 8, 512, 256, 2, 640
+    wgu, wd = _block_case(codec, E, H, F, 71)
+    g = torch.Generator(device="cuda").manual_seed(72)
+    x = torch.randn(T, H, device="cuda", generator=g).to(dt)
+    x[5] *= 1e-6                                  # a row that only survives the fp16 pre-pass through its row factor
+    ids, probs = route_topk(torch.randn(T, E, device="cuda", generator=g), k)
+    y = moe_swiglu_block(x, wgu, wd, codec, ids, probs)
+    assert y is not None and tuple(y.shape) == (T, H) and y.dtype == dt
+    ref = moe_glu(x, None, None, wd, codec, ids, probs, w_gate_up=wgu, fused=False)
+    assert torch.equal(y.view(torch.int16), ref.view(torch.int16))
+    # moe_glu takes the block by itself at this size
+    assert torch.equal(moe_glu(x, None, None, wd, codec, ids, probs, w_gate_up=wgu).view(torch.int16), y.view(torch.int16))
+    if dt == torch.bfloat16:                      # float16 rows take no row factor (nor do they in the composition)
+        assert float(y[5].float().abs().max()) > 0
+
+    # experts of another rank: index E + something, weight irrelevant
+    ids2 = ids.clone()
+    ids2[::3, 0] = E + 3
+    y2 = moe_swiglu_block(x, wgu, wd, codec, ids2, probs)
+    p2 = probs.clone()
+    p2[::3, 0] = 0
+    ids_safe = ids2.clone()
+    ids_safe[::3, 0] = 0
+    ref2 = moe_glu(x, None, None, wd, codec, ids_safe, p2, w_gate_up=wgu, fused=False)
+    assert torch.equal(y2.view(torch.int16), ref2.view(torch.int16))
+
+
+def test_block_token_rows_and_float32_partial_sums():
+    from mlx_kquant_b200.moe import moe_swiglu_block
+
+    E, H, F, k, T = 4, 256, 256, 4, 256
+    wgu, wd = _block_case("q4_k", E, H, F, 81)
+    g = torch.Generator(device="cuda").manual_seed(82)
+    big = torch.randn(2 * T + 7, H, device="cuda", generator=g).to(torch.bfloat16)
+    rows = torch.randperm(2 * T + 7, device="cuda", generator=g)[:T].to(torch.int32)
+    ids, probs = route_topk(torch.randn(T, E, device="cuda", generator=g), k)
+    out = torch.empty(T, H, dtype=torch.float32, device="cuda")
+    y = moe_swiglu_block(big, wgu, wd, "q4_k", ids, probs, token_rows=rows, tokens=T, out=out)
+    assert y is out
+    ref = moe_swiglu_block(big[rows.long()].contiguous(), wgu, wd, "q4_k", ids, probs)
+    # the float32 form is the same sum before its one rounding
+    assert torch.equal(out.to(torch.bfloat16).view(torch.int16), ref.view(torch.int16))
+
+
+def test_block_refuses_small_calls():
+    lib = _lib.lib()
+    assert lib.kq_moe_block_workspace_bytes(8, 2, 8, 512, 256) == 0          # 16 routed rows
+    assert lib.kq_moe_block_workspace_bytes(640, 2, 8, 512, 250) == 0        # F not a multiple of 8
+    assert lib.kq_moe_block_workspace_bytes(640, 2, 8, 512, 256) > 0
+    x = torch.zeros(8, 512, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(8, 512, 288, dtype=torch.uint8, device="cuda")
+    wd = torch.zeros(8, 512, 144, dtype=torch.uint8, device="cuda")
+    idx = torch.zeros(8, 2, dtype=torch.int32, device="cuda")
+    sc = torch.zeros(8, 2, dtype=torch.float32, device="cuda")
+    rc = lib.kq_moe_swiglu_block(x.data_ptr(), 2, 8, 512, 512, None, w.data_ptr(), w.stride(0), 288, 256, wd.data_ptr(),
+                                 wd.stride(0), 144, 8, b"q4_k", idx.data_ptr(), sc.data_ptr(), 2, x.data_ptr(), 2, None, 0,
+                                 None)
+    assert rc == _lib.KQ_ERR_UNSUPPORTED
