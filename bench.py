@@ -699,13 +699,33 @@ def moe_ep_cell(dev, rank, world):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def timed_part(fn, reps=5):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / reps], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     for Tg in (64, 4096):
         xg, idg, prg = x[:Tg].contiguous(), ids[:Tg].contiguous(), probs[:Tg].contiguous()
-        ep = GatheredExpertParallel(Tg, H, k, E, wgu, wd, "q4_k")
-        ms = timed_ep(ep, xg, idg, prg, 20 if Tg <= 64 else 5)
-        out[f"moe_glu_q4k_ep{world}_gathered_T{Tg}_per_rank"] = {"tokens_per_s": world * Tg / (ms * 1e-3), "ms": ms}
-        del ep
-        torch.cuda.empty_cache()
+        for tag, rd in (("", torch.float32), ("_bf16sum", torch.bfloat16)):
+            ep = GatheredExpertParallel(Tg, H, k, E, wgu, wd, "q4_k", reduce_dtype=rd)
+            ms = timed_ep(ep, xg, idg, prg, 20 if Tg <= 64 else 5)
+            cell = {"tokens_per_s": world * Tg / (ms * 1e-3), "ms": ms}
+            if Tg == 4096:  # where the step goes: the two collectives and the local stage, each timed alone
+                cell["all_gather_ms"] = timed_part(lambda: dist.all_gather_into_tensor(ep.recv, ep.send))
+                cell["local_stage_ms"] = timed_part(lambda: ep._graph.replay())
+                cell["reduce_scatter_ms"] = timed_part(lambda: dist.reduce_scatter_tensor(ep.y32, ep.partial))
+            out[f"moe_glu_q4k_ep{world}_gathered{tag}_T{Tg}_per_rank"] = cell
+            del ep
+            torch.cuda.empty_cache()
     for name, kw in (("pipelined2_bf16sum", dict(chunks=2, reduce_dtype=torch.bfloat16)),
                      ("pipelined4_bf16sum", dict(chunks=4, reduce_dtype=torch.bfloat16)),
                      ("pipelined2_f32sum", dict(chunks=2))):

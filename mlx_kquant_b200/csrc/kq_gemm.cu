@@ -48,19 +48,35 @@ namespace kq {
 
 constexpr int kBN = 128;
 constexpr int kBK = 64;
-constexpr int kBStages = 3;            // weight-tile ring
+// weight-tile ring: three stages (two next to a raw-block ring of a 256-column tile, which fills shared memory;
+// that combination was measured slower than per-thread loads and is not dispatched)
+__host__ __device__ constexpr int b_stages(int NB, bool RAW) { return (RAW && NB == 2) ? 2 : 3; }
 // Eight producer warps, then one MMA warp and one TMA warp. A 128-row weight tile has two producer
 // threads per row (32 weights each per K-step), a 256-row tile one (sixteen warps measured slower:
 // the kernel is bound by the L2 traffic of its activation tiles, not by the producers).
 __host__ __device__ constexpr int producer_threads(int) { return 256; }
-__host__ __device__ constexpr int gemm_threads(int NB) { return producer_threads(NB) + 64; }
+// One thread issues the MMAs of an accumulator row block; a tcgen05.mma costs its issuing thread ~75 cycles
+// (measured) against 128 cycles of tensor-pipe time, and every K-step adds barrier waits and commits, so ONE
+// issuer for two or four row blocks leaves the pipe idle half of the time: tiles with two or more row blocks
+// have two issuer warps (row blocks h = 0, 2 and h = 1, 3).
+__host__ __device__ constexpr int mma_warps(int MT) { return MT >= 2 ? 2 : 1; }
+__host__ __device__ constexpr int gemm_threads(int MT, int NB) { return producer_threads(NB) + 32 * (mma_warps(MT) + 1); }
 // activation-tile ring; the raw-block ring of the small-M kernels takes the room of four slots
 __host__ __device__ constexpr int a_slots(int MT, int NB, bool RAW = false) {
-  return NB == 2 ? 6 : (MT == 1 || RAW ? 4 : 8);
+  return NB == 2 ? (RAW ? 5 : 6) : (MT == 1 || RAW ? 4 : 8);
 }
 constexpr int kTileBytes = 128 * 128;  // 128 rows x 64 16-bit elements
 
 __device__ int g_kq_device_error = 0;
+#ifdef KQ_GEMM_TRACE
+// cycles summed over CTAs: [0] MMA warp waiting for weight tiles, [1] for activation tiles, [2] MMA loop,
+// [3] loader waiting for free slots, [4] producer (thread 0) waiting for free stages, [5] producing, [6] CTAs,
+// [7] epilogue
+__device__ unsigned long long g_gemm_trace[8];
+#define KQ_TR(...) __VA_ARGS__
+#else
+#define KQ_TR(...)
+#endif
 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
   return mbar_wait_err(bar, parity, abort_flag, code, &g_kq_device_error);
@@ -216,14 +232,18 @@ __device__ __forceinline__ void produce_w_q4k(const Q4kTileLoad& l, int kb, uint
 // RAW (q4_k fast producer, NB = 1, K-steps a multiple of 4): the wire blocks of the tile's 128 rows
 // stream through a four-superblock cp.async ring in shared memory instead of per-thread register
 // loads - at small M a CTA is alone on its SM and needs ~70 KB in flight to hide HBM latency.
-constexpr int kRawDepth = 4;
-constexpr int kRawSlot = 128 * 144;
+// The ring holds whole superblocks of the tile's rows: four of 128 rows (18 KB each), or two of 256 rows (36 KB
+// each) - the next superblock is then requested one superblock (four K-steps) before its first use.
+__host__ __device__ constexpr int raw_depth(int NB) { return NB == 2 ? 2 : 4; }
+__host__ __device__ constexpr int raw_slot(int NB) { return 128 * NB * 144; }
 template <int C, int A, typename OT, int MT, int NB, bool FASTQ4, bool RAW = false>
-__global__ void __launch_bounds__(gemm_threads(NB), 1)
+__global__ void __launch_bounds__(gemm_threads(MT, NB), 1)
 gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
-  constexpr int kProducerThreads = producer_threads(NB), kGemmThreads = gemm_threads(NB);
-  constexpr int kMmaWarp = kProducerThreads / 32;
-  static_assert(!RAW || (FASTQ4 && NB == 1), "raw ring: q4_k fast producer, 128-row weight tiles");
+  constexpr int kProducerThreads = producer_threads(NB), kGemmThreads = gemm_threads(MT, NB);
+  constexpr int kMmaWarp = kProducerThreads / 32, kMmaWarps = mma_warps(MT);
+  static_assert(!RAW || FASTQ4, "raw ring: q4_k fast producer");
+  constexpr int kBStages = b_stages(NB, RAW), kRawDepth = raw_depth(NB), kRawSlot = raw_slot(NB);
+  constexpr int kRawPieces = 128 * NB * 9;  // 16-byte pieces of one superblock of the tile's rows
   constexpr bool kHalf = std::is_same<OT, __half>::value;
   constexpr int NA = a_slots(MT, NB, RAW);
   constexpr int BN = kBN * NB;
@@ -261,13 +281,13 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < kBStages; s++) {
       mbar_init(&b_full[s], kProducerThreads / 32);
-      mbar_init(&b_empty[s], 1);
+      mbar_init(&b_empty[s], kMmaWarps);
     }
     for (int s = 0; s < NA; s++) {
       mbar_init(&a_full[s], 1);
       mbar_init(&a_empty[s], 1);
     }
-    mbar_init(&accum_bar, 1);
+    mbar_init(&accum_bar, kMmaWarps);
     abort_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -293,9 +313,9 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
       if (sbl < nsb) {
         uint8_t* slot = raw + (sbl % kRawDepth) * kRawSlot;
 #pragma unroll
-        for (int i = 0; i < 5; i++) {
-          const int piece = tid + kProducerThreads * i;  // 1152 16-byte pieces, contiguous in the slot
-          if (piece < 1152) {
+        for (int i = 0; i < (kRawPieces + kProducerThreads - 1) / kProducerThreads; i++) {
+          const int piece = tid + kProducerThreads * i;  // contiguous in the slot
+          if (piece < kRawPieces) {
             const int row = piece / 9, pc = piece % 9;
             const uint8_t* src = wbase + (long long)min(n0 + row, a.N - 1) * a.row_bytes +
                                  (long long)((kb0 >> 2) + sbl) * 144 + pc * 16;
@@ -311,6 +331,7 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
     }
     Q4kTileLoad cur{};
     if constexpr (FASTQ4 && !RAW) cur = q4k_tile_load(wrow, kb0);
+    KQ_TR(long long tr_wait = 0; long long tr_prod = 0;)
     {
     for (int it = 0; it < KB && (ok || RAW); it++) {
       const int kb = kb0 + it;
@@ -325,9 +346,12 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
         if (ok && it >= kBStages) ok = mbar_wait(&b_empty[s], ((it / kBStages) & 1) ^ 1, abort_flag, 1);
         if (!ok) continue;
       } else {
+        KQ_TR(const long long c0 = clock64();)
         if (it >= kBStages) ok = mbar_wait(&b_empty[s], ((it / kBStages) & 1) ^ 1, abort_flag, 1);
+        KQ_TR(tr_wait += clock64() - c0;)
         if (!ok) break;
       }
+      KQ_TR(const long long c1 = clock64();)
       uint8_t* wdst = b_ring + s * kBTile + wr * 128;
       if constexpr (RAW) {
         const uint8_t* blk = raw + ((it >> 2) % kRawDepth) * kRawSlot + wr * 144;
@@ -335,7 +359,8 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
         l.hdr = *reinterpret_cast<const uint4*>(blk);
         l.q0 = *reinterpret_cast<const uint4*>(blk + 16 + 32 * (it & 3));
         l.q1 = *reinterpret_cast<const uint4*>(blk + 32 + 32 * (it & 3));
-        produce_w_q4k(l, kb, wdst, wr, hh0);
+#pragma unroll
+        for (int hh = hh0; hh < hh0 + kHalves; hh++) produce_w_q4k(l, kb, wdst, wr, hh);
       } else if constexpr (FASTQ4) {
         Q4kTileLoad nxt = cur;
         if (it + 1 < KB) nxt = q4k_tile_load(wrow, kb + 1);  // next K-step's bytes are requested first
@@ -353,45 +378,63 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
       fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(&b_full[s]);
+      KQ_TR(tr_prod += clock64() - c1;)
     }
     }
+    KQ_TR(if (tid == 0) { atomicAdd(&g_gemm_trace[4], (unsigned long long)tr_wait); atomicAdd(&g_gemm_trace[5], (unsigned long long)tr_prod); atomicAdd(&g_gemm_trace[6], 1ull); })
     // ================= epilogue =================
+    KQ_TR(const long long ce = clock64();)
     if (ok) ok = mbar_wait(&accum_bar, 0, abort_flag, 4);
     if (ok) {
       tc_fence_after();
       const int lq = warp & 3;                   // TMEM lane quarter this warp may read
       constexpr int kColSpan = BN / (kProducerThreads / 128);  // four warps (one per lane quarter) per column span
       const int cbeg = (warp >> 2) * kColSpan;
+      if (gridDim.z > 1) {
+        // split K: this CTA's partial tile goes to shared memory (the rings are idle now) as fp32
+        // [rows][128], 16-byte chunks XOR-swizzled by the row so that a warp's stores spread over the banks
+        if constexpr (NB == 1) {
 #pragma unroll 1
-      for (int h = 0; h < mt_live; h++) {
-        const int row = m0 + h * 128 + lq * 32 + lane;
-        const bool live = row < m_end;
-        const long long orow = (live && a.yrow) ? a.yrow[row] : row;
-        OT* yrow = static_cast<OT*>(a.y) + orow * a.y_row_stride + n0;
-        const bool vec_ok = ((reinterpret_cast<uintptr_t>(yrow) & 15) == 0);
-        const float rs = (a.row_scale && live) ? a.row_scale[row] : 1.f;
+          for (int h = 0; h < mt_live; h++) {
+            const int rl = h * 128 + lq * 32 + lane;
+            const float rs = (a.row_scale && m0 + rl < m_end) ? a.row_scale[m0 + rl] : 1.f;
+            float* srow = reinterpret_cast<float*>(tiles) + rl * 128;
 #pragma unroll 1
-        for (int c0 = cbeg; c0 < cbeg + kColSpan; c0 += 16) {
-          uint32_t v[16];
-          tmem_ld16(tmem_base + ((uint32_t)(lq * 32) << 16) + (uint32_t)(h * BN + c0), v);
-          tmem_ld_wait();
-          if (gridDim.z > 1) {
-            // split K: this CTA's partial tile goes to shared memory (the rings are idle now) as fp32
-            // [rows][128], 16-byte chunks XOR-swizzled by the row so that a warp's stores spread over the banks
-            if constexpr (NB == 1) {
-              const int rl = h * 128 + lq * 32 + lane;
-              float* srow = reinterpret_cast<float*>(tiles) + rl * 128;
+            for (int c0 = cbeg; c0 < cbeg + kColSpan; c0 += 16) {
+              uint32_t v[16];
+              tmem_ld16(tmem_base + ((uint32_t)(lq * 32) << 16) + (uint32_t)(h * BN + c0), v);
+              tmem_ld_wait();
 #pragma unroll
               for (int i = 0; i < 4; i++)
                 *reinterpret_cast<float4*>(srow + 4 * (((c0 >> 2) + i) ^ (rl & 31))) =
                     make_float4(__uint_as_float(v[4 * i]) * rs, __uint_as_float(v[4 * i + 1]) * rs,
                                 __uint_as_float(v[4 * i + 2]) * rs, __uint_as_float(v[4 * i + 3]) * rs);
             }
-          } else if (live) {
-            uint32_t o[8];
+          }
+        }
+      } else {
+        // A thread owns one accumulator row (a TMEM lane): storing from here would write 32 rows x 32 bytes per
+        // instruction, one memory transaction per lane. The rounded tile goes through shared memory instead (the
+        // rings are idle: every MMA has completed), rows of BN outputs with their 16-byte chunks XOR-swizzled by
+        // the row, and leaves as whole rows, 16 bytes per lane.
+        constexpr int kRowBytes = BN * 2, kChunks = BN / 8;
+        uint8_t* stage = tiles;
+#pragma unroll 1
+        for (int h = 0; h < mt_live; h++) {
+          const int rl = h * 128 + lq * 32 + lane;
+          const float rs = (a.row_scale && m0 + rl < m_end) ? a.row_scale[m0 + rl] : 1.f;
+          uint8_t* srow = stage + rl * kRowBytes;
+#pragma unroll 1
+          for (int c0 = cbeg; c0 < cbeg + kColSpan; c0 += 32) {
+            uint32_t va[16], vb[16];
+            tmem_ld16(tmem_base + ((uint32_t)(lq * 32) << 16) + (uint32_t)(h * BN + c0), va);
+            tmem_ld16(tmem_base + ((uint32_t)(lq * 32) << 16) + (uint32_t)(h * BN + c0 + 16), vb);
+            tmem_ld_wait();
+            uint32_t o[16];
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-              const float f0 = __uint_as_float(v[2 * i]) * rs, f1 = __uint_as_float(v[2 * i + 1]) * rs;
+            for (int i = 0; i < 16; i++) {
+              const uint32_t u0 = i < 8 ? va[2 * i] : vb[2 * i - 16], u1 = i < 8 ? va[2 * i + 1] : vb[2 * i - 15];
+              const float f0 = __uint_as_float(u0) * rs, f1 = __uint_as_float(u1) * rs;
               if constexpr (kHalf) {
                 o[i] = pack_h2f(f0, f1);
               } else {
@@ -399,31 +442,55 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
                 o[i] = *reinterpret_cast<uint32_t*>(&bb);
               }
             }
-            if (vec_ok && n0 + c0 + 16 <= a.N) {
-              reinterpret_cast<uint4*>(yrow + c0)[0] = make_uint4(o[0], o[1], o[2], o[3]);
-              reinterpret_cast<uint4*>(yrow + c0)[1] = make_uint4(o[4], o[5], o[6], o[7]);
-            } else {
-              const OT* oe = reinterpret_cast<const OT*>(o);
-              for (int i = 0; i < 16; i++)
-                if (n0 + c0 + i < a.N) yrow[c0 + i] = oe[i];
-            }
+#pragma unroll
+            for (int q = 0; q < 4; q++)
+              *reinterpret_cast<uint4*>(srow + ((((c0 >> 3) + q) ^ (rl & (kChunks - 1))) << 4)) =
+                  make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+          }
+        }
+        asm volatile("bar.sync 2, %0;\n" ::"n"(kProducerThreads) : "memory");
+        const int rows_live = min(m_end - m0, mt_live * 128);
+        constexpr int kRowsPerPass = 32 / kChunks;  // 1 (256 columns) or 2 (128 columns) rows per warp instruction
+        const int chunk = lane % kChunks;
+        const int col = n0 + chunk * 8;
+        OT* ybase = static_cast<OT*>(a.y);
+        for (int r = warp * kRowsPerPass + lane / kChunks; r < rows_live; r += (kProducerThreads / 32) * kRowsPerPass) {
+          const long long orow = a.yrow ? a.yrow[m0 + r] : (long long)(m0 + r);
+          const uint4 q = *reinterpret_cast<const uint4*>(stage + r * kRowBytes + ((chunk ^ (r & (kChunks - 1))) << 4));
+          OT* yp = ybase + orow * a.y_row_stride + col;
+          if (col + 8 <= a.N && (reinterpret_cast<uintptr_t>(yp) & 15) == 0) {
+            *reinterpret_cast<uint4*>(yp) = q;
+          } else {
+            const OT* qe = reinterpret_cast<const OT*>(&q);
+            for (int i = 0; i < 8; i++)
+              if (col + i < a.N) yp[i] = qe[i];
           }
         }
       }
     }
-  } else if (warp == kMmaWarp) {
-    // ================= MMA issuer =================
+    KQ_TR(if (tid == 0) atomicAdd(&g_gemm_trace[7], (unsigned long long)(clock64() - ce));)
+  } else if (warp < kMmaWarp + kMmaWarps) {
+    // ================= MMA issuers =================
+    // Issuer w takes the row blocks h = w, w + kMmaWarps, ...; the activation tile of (K-step kb, row block h)
+    // is tile number kb * mt_live + h of the loader's sequence. Every issuer arrives on every stage barrier
+    // (a commit with no MMA of its own completes at once), so the counts do not depend on mt_live.
     constexpr uint32_t idesc = umma_idesc(0u, BN);
+    const int w = warp - kMmaWarp;
     bool ok = true;
-    int t = 0;  // running activation-tile number
+    KQ_TR(long long tr_b = 0; long long tr_a = 0; const long long cm = clock64();)
     for (int kb = 0; kb < KB && ok; kb++) {  // kb counts this CTA's own K-steps
       const int s = kb % kBStages;
+      KQ_TR(const long long c0 = clock64();)
       ok = mbar_wait(&b_full[s], (kb / kBStages) & 1, abort_flag, 2);
+      KQ_TR(tr_b += clock64() - c0;)
       if (!ok) break;
       const uint32_t bt = smem_u32(b_ring + s * kBTile);
-      for (int h = 0; h < mt_live && ok; h++, t++) {
+      for (int h = w; h < mt_live && ok; h += kMmaWarps) {
+        const int t = kb * mt_live + h;
         const int slot = t % NA;
+        KQ_TR(const long long c2 = clock64();)
         ok = mbar_wait(&a_full[slot], (t / NA) & 1, abort_flag, 16);
+        KQ_TR(tr_a += clock64() - c2;)
         if (!ok) break;
         tc_fence_after();
         if (lane == 0) {
@@ -439,6 +506,7 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
       if (ok && lane == 0) umma_commit(&b_empty[s]);
       __syncwarp();
     }
+    KQ_TR(if (lane == 0 && w == 0) { atomicAdd(&g_gemm_trace[0], (unsigned long long)tr_b); atomicAdd(&g_gemm_trace[1], (unsigned long long)tr_a); atomicAdd(&g_gemm_trace[2], (unsigned long long)(clock64() - cm)); })
     if (lane == 0) umma_commit(&accum_bar);  // also on the abort path: lets the wait below see the MMAs drain
     __syncwarp();
     if (!ok) mbar_wait(&accum_bar, 0, abort_flag, 8);
@@ -446,10 +514,13 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
     // ================= activation loader (TMA) =================
     bool ok = true;
     int t = 0;
+    KQ_TR(long long tr_e = 0;)
     for (int kb = 0; kb < KB && ok; kb++) {
       for (int h = 0; h < mt_live && ok; h++, t++) {
         const int slot = t % NA;
+        KQ_TR(const long long c0 = clock64();)
         if (t >= NA) ok = mbar_wait(&a_empty[slot], ((t / NA) & 1) ^ 1, abort_flag, 32);
+        KQ_TR(tr_e += clock64() - c0;)
         if (!ok) break;
         if (lane == 0) {
           mbar_expect_tx(&a_full[slot], kTileBytes);
@@ -458,6 +529,7 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
         __syncwarp();
       }
     }
+    KQ_TR(if (lane == 0) atomicAdd(&g_gemm_trace[3], (unsigned long long)tr_e);)
     // In-flight loads must have landed before the CTA may exit: wait (bounded) for the last ones.
     if (ok && t > 0) {
       const int first = t > NA ? t - NA : 0;
@@ -808,7 +880,8 @@ static cudaError_t make_x_map(CUtensorMap* map, const void* x, long long x_row_s
 template <int C, int A, typename OT, int MT, int NB, bool FASTQ4, bool RAW = false>
 static cudaError_t launch_g(const GemmArgs& a, cudaStream_t st, int grid_y = 0, int ksplit = 1) {
   auto kern = gemm_kernel<C, A, OT, MT, NB, FASTQ4, RAW>;
-  const size_t dyn = (size_t)(kBStages * NB + a_slots(MT, NB, RAW)) * kTileBytes + 1024 + (RAW ? kRawDepth * kRawSlot : 0);
+  const size_t dyn = (size_t)(b_stages(NB, RAW) * NB + a_slots(MT, NB, RAW)) * kTileBytes + 1024 +
+                     (RAW ? raw_depth(NB) * raw_slot(NB) : 0);
   static bool attr_set[16] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -823,13 +896,13 @@ static cudaError_t launch_g(const GemmArgs& a, cudaStream_t st, int grid_y = 0, 
   if (NB != 1) ksplit = 1;
   const dim3 grid((a.N + kBN * NB - 1) / (kBN * NB), grid_y > 0 ? grid_y : (a.M + 128 * MT - 1) / (128 * MT), ksplit);
   if (ksplit == 1) {
-    kern<<<grid, gemm_threads(NB), dyn, st>>>(a, map);
+    kern<<<grid, gemm_threads(MT, NB), dyn, st>>>(a, map);
     return cudaGetLastError();
   }
   // split K: the ksplit CTAs of one output tile form a cluster
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
-  cfg.blockDim = dim3(gemm_threads(NB));
+  cfg.blockDim = dim3(gemm_threads(MT, NB));
   cfg.dynamicSmemBytes = dyn;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -1042,6 +1115,17 @@ int* device_error_word() {
   }
   return addr[dev];
 }
+
+#ifdef KQ_GEMM_TRACE
+extern "C" __attribute__((visibility("default"))) int kq_debug_gemm_trace(unsigned long long* out, int clear) {
+  cudaMemcpyFromSymbol(out, g_gemm_trace, sizeof(g_gemm_trace));
+  if (clear) {
+    const unsigned long long z[8] = {};
+    cudaMemcpyToSymbol(g_gemm_trace, z, sizeof(z));
+  }
+  return 0;
+}
+#endif
 
 // Flags raised by kernels that gave up on a bounded wait (0 = none). Synchronises the device.
 cudaError_t read_device_error(int* out, bool clear) {

@@ -161,6 +161,7 @@ def write_gguf(path: str | Path, metadata: dict, tensors: dict[str, tuple[str, t
     the wire bytes (uint8, any shape with the right byte count) or the float tensor itself."""
     meta = dict(metadata)
     meta.setdefault("general.alignment", alignment)
+    alignment = int(meta["general.alignment"])  # what readers pad with: a value in `metadata` wins over the argument
     head = _MAGIC + struct.pack("<IQQ", 3, len(tensors), len(meta))
     for k, v in meta.items():
         head += _pack_string(k) + _pack_value(v)

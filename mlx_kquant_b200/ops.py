@@ -50,6 +50,18 @@ def _stream_ptr(stream, device) -> int:
     return stream.cuda_stream
 
 
+def _order_on(stream, device, *tensors) -> None:
+    """A caller-given stream runs the kernel: it first waits for what the current stream has queued (the
+    operands may have been produced or copied there), and every tensor the kernel touches is recorded on it so
+    that the caching allocator does not hand its memory out while the kernel may still run."""
+    if stream is None:
+        return
+    stream.wait_stream(torch.cuda.current_stream(device))
+    for t in tensors:
+        if t is not None and t.is_cuda:
+            t.record_stream(stream)
+
+
 def _require_cuda(w: torch.Tensor, op: str) -> None:
     if not w.is_cuda:
         raise RuntimeError(f"[mlx_kquant.{op}] w must live on a CUDA device; there is no CPU path.")
@@ -72,6 +84,7 @@ def dequantize(w, scales, kquant_type, dtype=None, *, stream=None):
     _require_cuda(w, "dequantize")
     w_c = w.contiguous()
     out = torch.empty(w.shape[:-1] + (w.shape[-1] // bpb * wpb,), dtype=out_dtype, device=w.device)
+    _order_on(stream, w.device, w_c, out)
     with torch.cuda.device(w.device):
         check(_lib.lib().kq_dequantize(w_c.data_ptr(), w_c.numel(), kquant_type.encode(), _DT[out_dtype],
                                        out.data_ptr(), _stream_ptr(stream, w.device)))
@@ -158,8 +171,7 @@ def quantized_matmul(x, w, scales, kquant_type, transpose=True, *, stream=None):
     L = _lib.lib()
     ws_bytes = L.kq_quantized_matmul_workspace_bytes(_DT[x.dtype], rows, K)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=w.device) if ws_bytes else None
-    if ws is not None and stream is not None:
-        ws.record_stream(stream)
+    _order_on(stream, w.device, ws, x2, w2, y)
     with torch.cuda.device(w.device):
         check(L.kq_quantized_matmul(x2.data_ptr(), _DT[x.dtype], rows, K, x2.stride(0), w2.data_ptr(),
                                     w2.shape[-1], outer, kquant_type.encode(), int(bool(transpose)),
@@ -226,9 +238,7 @@ def gather_qmm(x, w, scales, kquant_type, lhs_indices=None, rhs_indices=None, tr
     ws_bytes = L.kq_gather_qmm_workspace_bytes(n_entries, M, E, K)
     ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
     right_sorted = bool(sorted_indices) and lhs_indices is None
-    if stream is not None:
-        for t in (ws, y, x3, lhs32, rhs32):
-            t.record_stream(stream)
+    _order_on(stream, dev, ws, y, x3, w3, lhs32, rhs32)
     with torch.cuda.device(dev):
         check(L.kq_gather_qmm(x3.data_ptr(), _DT[x.dtype], x3.shape[0], M, K, w3.data_ptr(), E,
                               w3.stride(0) if E > 1 else w3.shape[1] * w3.shape[2], w3.shape[2], outer,
@@ -260,9 +270,7 @@ def expert_tile_map(indices, n_experts, *, stream=None):
     tile_map = torch.zeros((cap, 3), dtype=torch.int32, device=dev)
     count = torch.zeros(1, dtype=torch.int32, device=dev)
     ws = torch.empty(max(L.kq_expert_tile_map_workspace_bytes(n_experts), 256), dtype=torch.uint8, device=dev)
-    if stream is not None:
-        for t in (idx, tile_map, count, ws):
-            t.record_stream(stream)
+    _order_on(stream, dev, idx, tile_map, count, ws)
     with torch.cuda.device(dev):
         check(L.kq_expert_tile_map(idx.data_ptr(), rows, n_experts, tile_map.data_ptr(), count.data_ptr(),
                                    ws.data_ptr(), ws.numel(), _stream_ptr(stream, dev)))
@@ -311,9 +319,7 @@ def gather_qmm_seg(x, w, scales, kquant_type, map, counts, *, stream=None):  # n
     L = _lib.lib()
     ws = torch.empty(max(L.kq_gather_qmm_seg_workspace_bytes(_DT[x.dtype], rows, K, E, mc.shape[0]), 256),
                      dtype=torch.uint8, device=dev)
-    if stream is not None:
-        for t in (xc, mc, cc, ws, y):
-            t.record_stream(stream)
+    _order_on(stream, dev, xc, wc, mc, cc, ws, y)
     with torch.cuda.device(dev):
         check(L.kq_gather_qmm_seg(xc.data_ptr(), _DT[x.dtype], rows, K, wc.data_ptr(), E, wc.stride(0), wc.shape[2], N,
                                   kquant_type.encode(), mc.data_ptr(), cc.data_ptr(), mc.shape[0], y.data_ptr(),
@@ -357,9 +363,7 @@ def quantized_matmul_qmv_bias(x, w, scales, bias, kquant_type, *, stream=None):
     wc = w.contiguous()
     bc = bias.to(dev).to(out_dtype).contiguous()
     y = torch.empty(x.shape[:-1] + (N,), dtype=out_dtype, device=dev)
-    if stream is not None:
-        for t in (xc, bc, y):
-            t.record_stream(stream)
+    _order_on(stream, dev, xc, wc, bc, y)
     with torch.cuda.device(dev):
         check(_lib.lib().kq_quantized_matmul_qmv_bias(xc.data_ptr(), _DT[x.dtype], K, wc.data_ptr(), wc.shape[1], N,
                                                       kquant_type.encode(), bc.data_ptr(), y.data_ptr(),

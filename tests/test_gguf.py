@@ -53,6 +53,17 @@ def test_round_trip(tmp_path):
     assert tuple(got["blk.0.ffn_up.weight"].data.shape) == (64, 288)
 
 
+def test_alignment_in_metadata_wins_over_the_argument(tmp_path):
+    """Readers pad tensor offsets with general.alignment from the file: the writer must use that value too."""
+    _, tensors = _tensors()
+    path = tmp_path / "aligned64.gguf"
+    gguf.write_gguf(path, {"general.alignment": 64}, tensors, alignment=32)
+    got_meta, got = gguf.read_gguf(path)
+    assert got_meta["general.alignment"] == 64
+    for name, (_, _, data) in tensors.items():
+        assert torch.equal(got[name].data, data.reshape(got[name].data.shape)), name
+
+
 def test_rejects_foreign_files(tmp_path):
     p = tmp_path / "x.bin"
     p.write_bytes(b"NOPE" + b"\0" * 64)

@@ -188,3 +188,20 @@ def test_small_and_large_magnitude_rows(oracle, dt, M, scale):
     ref = fp64_ref(oracle, store, dt, wire, "q4_k")
     for m in range(M):   # row by row: the rows differ by many orders of magnitude
         check(y[m:m + 1], ref[m:m + 1], "bf16")
+
+
+def test_stream_keyword_waits_for_the_current_stream():
+    """stream=: the kernel runs on the caller's stream but only after what the current stream has queued - here
+    the host-to-device copy that produces x - and its operands survive until it has run."""
+    side = torch.cuda.Stream()
+    wire = torch.from_numpy(synthetic_wire("q4_k", 512, 1024, seed=77)).cuda()
+    host = torch.randn(64, 1024).half().pin_memory()
+    for _ in range(5):
+        x = host.to("cuda", non_blocking=True)            # queued on the current stream
+        y = kq.quantized_matmul(x, wire, None, "q4_k", stream=side)
+        d = kq.dequantize(wire, None, "q4_k", torch.float16, stream=side)
+        del x
+        side.synchronize()
+        ref = kq.quantized_matmul(host.cuda(), wire, None, "q4_k")
+        assert torch.equal(y, ref)
+        assert torch.equal(d, kq.dequantize(wire, None, "q4_k", torch.float16))
