@@ -65,7 +65,7 @@ MATRIX_BYTES = N_ROWS * ROW_BYTES  # 9 437 184
 # the kernel that runs this workload, and its DRAM bytes per launch from the ncu capture summarised in
 # profiles/gemv_q4k_stream_decode.md (dram__bytes_read.sum + dram__bytes_write.sum)
 ROOFLINE_KERNEL = "gemv_q4k_stream_kernel<__half>"
-ROOFLINE_TRAFFIC = 9486848
+ROOFLINE_TRAFFIC = 9491000
 TEN_CODECS = ("q2_k", "q3_k", "q4_k", "q5_k", "q6_k", "q4_0", "q8_0", "iq4_nl", "iq4_xs", "iq2_xxs")
 
 

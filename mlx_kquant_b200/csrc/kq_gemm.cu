@@ -343,7 +343,9 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
           asm volatile("bar.sync 1, %0;\n" ::"n"(kProducerThreads) : "memory");  // data landed, previous slot read
           if (it > 0) issue_sb((it >> 2) - 1 + kRawDepth);
         }
+        KQ_TR(const long long c0 = clock64();)
         if (ok && it >= kBStages) ok = mbar_wait(&b_empty[s], ((it / kBStages) & 1) ^ 1, abort_flag, 1);
+        KQ_TR(tr_wait += clock64() - c0;)
         if (!ok) continue;
       } else {
         KQ_TR(const long long c0 = clock64();)
