@@ -168,6 +168,77 @@ __device__ __forceinline__ void produce_w_q6k(const uint8_t* row, int kb, uint8_
   }
 }
 
+// The same producer with its bytes requested one K-step ahead (as the q4_k producer does): rows that start on
+// 8-byte boundaries (base pointer and row bytes multiples of 8, i.e. K a multiple of 1024) read the 32 ql bytes
+// and the 32 qh bytes of a thread's quarter as five aligned 8-byte loads each - the quarter starts 0, 2, 4 or 6
+// bytes into its window, the same for every row of the tile - and funnel-shift them into place. The version
+// above issues 35 two-byte loads per K-step and uses each at once, so every K-step waits out a load latency.
+struct Q6kTileLoad {
+  uint2 ql[5], qh[5];
+  uint32_t sc2, dbits;
+};
+__device__ __forceinline__ Q6kTileLoad q6k_tile_load(const uint8_t* row, int kb, int hh) {
+  const uint8_t* blk = row + (long long)(kb >> 2) * 210;
+  const int p = kb & 3, hf = p >> 1, qd = 2 * (p & 1) + hh;
+  const uint8_t* ql = blk + 64 * hf + 32 * hh;
+  const uint8_t* qh = blk + 128 + 32 * hf;
+  const uint2* al = reinterpret_cast<const uint2*>(reinterpret_cast<uintptr_t>(ql) & ~(uintptr_t)7);
+  const uint2* ah = reinterpret_cast<const uint2*>(reinterpret_cast<uintptr_t>(qh) & ~(uintptr_t)7);
+  Q6kTileLoad l;
+#pragma unroll
+  for (int i = 0; i < 5; i++) {
+    l.ql[i] = __ldg(al + i);
+    l.qh[i] = __ldg(ah + i);
+  }
+  l.sc2 = __ldg(reinterpret_cast<const unsigned short*>(blk + 192 + 8 * hf + 2 * qd));
+  l.dbits = __ldg(reinterpret_cast<const unsigned short*>(blk + 208));
+  return l;
+}
+// eight consecutive 32-bit words starting `phase` bytes (0, 2, 4, 6) into a 40-byte window
+__device__ __forceinline__ void q6k_window(const uint2 (&win)[5], int phase, uint32_t (&out)[8]) {
+  const uint32_t w[10] = {win[0].x, win[0].y, win[1].x, win[1].y, win[2].x, win[2].y, win[3].x, win[3].y, win[4].x, win[4].y};
+  const bool up = (phase & 4) != 0;
+  const uint32_t sh = (phase & 2) * 8;
+  uint32_t v[9];
+#pragma unroll
+  for (int i = 0; i < 9; i++) v[i] = up ? w[i + 1] : w[i];
+#pragma unroll
+  for (int i = 0; i < 8; i++) out[i] = __funnelshift_r(v[i], v[i + 1], sh);
+}
+__device__ __forceinline__ void produce_w_q6k_pre(const Q6kTileLoad& l, const uint8_t* row, int kb, uint8_t* dst_row,
+                                                  int r, int hh) {
+  const int p = kb & 3, hf = p >> 1, qd = 2 * (p & 1) + hh;
+  // phases of the two windows: the row base is 8-byte aligned, so they follow from the offsets alone
+  const int off = (kb >> 2) * 210;
+  const int phl = (int)((reinterpret_cast<uintptr_t>(row) + off + 64 * hf + 32 * hh) & 7);
+  const int phh = (int)((reinterpret_cast<uintptr_t>(row) + off + 128 + 32 * hf) & 7);
+  uint32_t L[8], H[8];
+  q6k_window(l.ql, phl, L);
+  q6k_window(l.qh, phh, H);
+  const float d = __half2float(__ushort_as_half((unsigned short)l.dbits));
+  const __half2 sA = __float2half2_rn(d * (float)(int)(int8_t)(l.sc2 & 0xffu));
+  const __half2 sB = __float2half2_rn(d * (float)(int)(int8_t)((l.sc2 >> 8) & 0xffu));
+  const __half2 k1056 = __float2half2_rn(1056.f);
+  const int nsh = (qd & 2) ? 4 : 0;
+#pragma unroll
+  for (int c = 0; c < 4; c++) {
+    uint32_t o[4];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      const uint32_t Lw = L[2 * c + h], Hw = H[2 * c + h];
+      const uint32_t hb = (qd < 2) ? (Hw << (4 - 2 * (qd & 1))) : (Hw >> (2 * (qd & 1)));
+      const uint32_t q4 = ((Lw >> nsh) & 0x0f0f0f0fu) | (hb & 0x30303030u);
+      const __half2 s = c < 2 ? sA : sB;
+      const uint32_t m0 = __byte_perm(q4, 0x64646464u, 0x4140), m1 = __byte_perm(q4, 0x64646464u, 0x4342);
+      const __half2 w0 = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&m0), k1056), s);
+      const __half2 w1 = __hmul2(__hsub2(*reinterpret_cast<const __half2*>(&m1), k1056), s);
+      o[2 * h] = *reinterpret_cast<const uint32_t*>(&w0);
+      o[2 * h + 1] = *reinterpret_cast<const uint32_t*>(&w1);
+    }
+    *reinterpret_cast<uint4*>(dst_row + (((c + 4 * hh) ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 __device__ __forceinline__ uint32_t two_bytes_to_h2(uint32_t two_bytes) {
   const uint32_t m = (two_bytes & 0xffu) | ((two_bytes & 0xff00u) << 8) | 0x64006400u;
   const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&m), __float2half2_rn(1024.f));
@@ -331,6 +402,9 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
     }
     Q4kTileLoad cur{};
     if constexpr (FASTQ4 && !RAW) cur = q4k_tile_load(wrow, kb0);
+    constexpr bool kQ6Pre = (C == Q6_K && A == 8 && NB == 1);  // 8-byte aligned rows, two threads per row
+    Q6kTileLoad cur6{};
+    if constexpr (kQ6Pre) cur6 = q6k_tile_load(wrow, kb0, hh0);
     KQ_TR(long long tr_wait = 0; long long tr_prod = 0;)
     {
     for (int it = 0; it < KB && (ok || RAW); it++) {
@@ -370,10 +444,15 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
         for (int hh = hh0; hh < hh0 + kHalves; hh++)
           produce_w_q4k(cur, kb, wdst, wr, hh);
         cur = nxt;
+      } else if constexpr (kQ6Pre) {
+        Q6kTileLoad nxt6 = cur6;
+        if (it + 1 < KB) nxt6 = q6k_tile_load(wrow, kb + 1, hh0);  // next K-step's bytes are requested first
+        produce_w_q6k_pre(cur6, wrow, kb, wdst, wr, hh0);
+        cur6 = nxt6;
       } else {
 #pragma unroll
         for (int hh = hh0; hh < hh0 + kHalves; hh++) {
-          if constexpr (C == Q6_K && A >= 2) produce_w_q6k<A>(wrow, kb, wdst, wr, hh);
+          if constexpr (C == Q6_K && A >= 2) produce_w_q6k<2>(wrow, kb, wdst, wr, hh);  // blocks are 2-byte aligned
           else produce_w_generic<C, A>(wrow, kb, a.K, wdst, wr, hh, tabs);
         }
       }
@@ -1003,6 +1082,8 @@ cudaError_t launch_gemm(int codec, int x_dtype, const void* x, long long x_row_s
   const bool out_half = x_dtype == F16;
   const bool aligned = (reinterpret_cast<uintptr_t>(w) & 15) == 0;
   if (codec == Q4_K && aligned) return launch_shape<Q4_K, 16, true>(out_half, a, st);
+  // q6_k rows on 8-byte boundaries (K a multiple of 1024): the producer that requests its bytes a K-step ahead
+  if (codec == Q6_K && aligned && (row_bytes % 8) == 0) return launch_shape<Q6_K, 8, false>(out_half, a, st);
   switch (codec) {
     case Q2_K: return launch_codec<Q2_K, 4>(out_half, a, aligned, st);
     case Q3_K: return launch_codec<Q3_K, 2>(out_half, a, aligned, st);
@@ -1078,6 +1159,10 @@ cudaError_t launch_gemm_tiles(int codec, bool out_half, const void* xh, long lon
   if (codec == Q4_K && aligned) {
     if (out_half) return launch_g<Q4_K, 16, __half, 2, 2, true>(a, st, max_tiles);
     return launch_g<Q4_K, 16, __nv_bfloat16, 2, 2, true>(a, st, max_tiles);
+  }
+  if (codec == Q6_K && aligned && (row_bytes % 8) == 0 && (expert_stride % 8) == 0) {
+    if (out_half) return launch_g<Q6_K, 8, __half, 2, 1, false>(a, st, max_tiles);
+    return launch_g<Q6_K, 8, __nv_bfloat16, 2, 1, false>(a, st, max_tiles);
   }
   switch (codec) {
     case Q2_K: return launch_grouped_codec<Q2_K, 4>(out_half, a, aligned, max_tiles, st);
