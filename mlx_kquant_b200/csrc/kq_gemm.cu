@@ -91,6 +91,7 @@ __device__ __forceinline__ uint32_t hfma2_bits(uint32_t a, __half2 b, __half2 c)
   return *reinterpret_cast<uint32_t*>(&r);
 }
 
+constexpr int kTileGridCap = 256;  // grid.y of the grouped kernel, see launch_gemm_tiles
 struct GemmTile {
   int expert, row_start, rows, pad;
 };
@@ -332,335 +333,352 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BN;
-  int m0 = blockIdx.y * (128 * MT), m_end = a.M;
-  const uint8_t* wbase = a.w;
-  if (a.tiles != nullptr) {
-    if ((int)blockIdx.y >= *a.n_tiles_dev) return;  // whole CTA, before any barrier or allocation
-    const GemmTile t = a.tiles[blockIdx.y];
-    m0 = t.row_start;
-    m_end = t.row_start + t.rows;
-    wbase += (long long)t.expert * a.w_expert_stride;
-  }
+  // Grouped mode: the CTA takes tile blockIdx.y of the device-built list, then every gridDim.y-th after it (the
+  // grid is sized on the host for the largest list the call could produce, capped; the list is usually far
+  // shorter, and a CTA with no tile leaves before it allocates anything).
+  const int n_list = a.tiles != nullptr ? *a.n_tiles_dev : 0;
+  if (a.tiles != nullptr && (int)blockIdx.y >= n_list) return;
   // K-steps of this CTA: all of them, or slice blockIdx.z of gridDim.z equal slices (split K, below)
   const int KB = (a.K + kBK - 1) / kBK / (int)gridDim.z;
   const int kb0 = (int)blockIdx.z * KB;
-  const int mt_live = min(MT, (m_end - m0 + 127) / 128);  // activation tiles of this CTA that hold rows
   constexpr uint32_t kTmemCols = MT * BN;               // 128, 256 or 512: a power of two >= 32
 
   IqTables tabs = global_iq_tables();
   if constexpr (kIq) tabs = stage_iq_tables(s_tabs, threadIdx.x, kGemmThreads);
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kBStages; s++) {
-      mbar_init(&b_full[s], kProducerThreads / 32);
-      mbar_init(&b_empty[s], kMmaWarps);
-    }
-    for (int s = 0; s < NA; s++) {
-      mbar_init(&a_full[s], 1);
-      mbar_init(&a_empty[s], 1);
-    }
-    mbar_init(&accum_bar, kMmaWarps);
-    abort_s = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-  }
+  if (threadIdx.x == 0) abort_s = 0;
   if (warp == kMmaWarp) tmem_alloc(&tmem_base_s, kTmemCols);
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = tmem_base_s;
   volatile int* abort_flag = &abort_s;
+  uint32_t tmem_base = 0;
 
-  if (warp < kMmaWarp) {
-    // ================= weight producers =================
-    const int tid = threadIdx.x;
-    // NB = 1: two threads per weight row (hh = which 32 of its 64 weights); NB = 2: one thread per row
-    const int wr = tid % (128 * NB);   // weight row of the tile
-    const int hh0 = tid / (128 * NB);  // first 32-weight half of its 64 weights per K-step this thread makes
-    constexpr int kHalves = 256 * NB / kProducerThreads;  // and how many of them
-    const uint8_t* wrow = wbase + (long long)min(n0 + wr, a.N - 1) * a.row_bytes;
-    bool ok = true;
-    uint8_t* raw = a_ring + NA * kTileBytes;
-    const int nsb = KB >> 2;
-    auto issue_sb = [&](int sbl) {  // one copy group per superblock, an empty one past the end
-      if (sbl < nsb) {
-        uint8_t* slot = raw + (sbl % kRawDepth) * kRawSlot;
-#pragma unroll
-        for (int i = 0; i < (kRawPieces + kProducerThreads - 1) / kProducerThreads; i++) {
-          const int piece = tid + kProducerThreads * i;  // contiguous in the slot
-          if (piece < kRawPieces) {
-            const int row = piece / 9, pc = piece % 9;
-            const uint8_t* src = wbase + (long long)min(n0 + row, a.N - 1) * a.row_bytes +
-                                 (long long)((kb0 >> 2) + sbl) * 144 + pc * 16;
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(slot + piece * 16)), "l"(src)
-                         : "memory");
+  for (int tile = (int)blockIdx.y;; tile += (int)gridDim.y) {
+    int m0 = tile * (128 * MT), m_end = a.M;
+    const uint8_t* wbase = a.w;
+    if (a.tiles != nullptr) {
+      const GemmTile t = a.tiles[tile];
+      m0 = t.row_start;
+      m_end = t.row_start + t.rows;
+      wbase += (long long)t.expert * a.w_expert_stride;
+    }
+    const int mt_live = min(MT, (m_end - m0 + 127) / 128);  // activation tiles of this CTA that hold rows
+    // Every tile starts from freshly initialised barriers (phase 0): nothing is in flight between tiles - the
+    // loader has waited for its last loads, the issuers' MMAs have completed, the epilogue has stored.
+    if (threadIdx.x == 0) {
+      const bool again = tile != (int)blockIdx.y;
+      for (int s = 0; s < kBStages; s++) {
+        if (again) mbar_inval(&b_full[s]), mbar_inval(&b_empty[s]);
+        mbar_init(&b_full[s], kProducerThreads / 32);
+        mbar_init(&b_empty[s], kMmaWarps);
+      }
+      for (int s = 0; s < NA; s++) {
+        if (again) mbar_inval(&a_full[s]), mbar_inval(&a_empty[s]);
+        mbar_init(&a_full[s], 1);
+        mbar_init(&a_empty[s], 1);
+      }
+      if (again) mbar_inval(&accum_bar);
+      mbar_init(&accum_bar, kMmaWarps);
+      asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    tmem_base = tmem_base_s;
+
+    if (warp < kMmaWarp) {
+      // ================= weight producers =================
+      const int tid = threadIdx.x;
+      // NB = 1: two threads per weight row (hh = which 32 of its 64 weights); NB = 2: one thread per row
+      const int wr = tid % (128 * NB);   // weight row of the tile
+      const int hh0 = tid / (128 * NB);  // first 32-weight half of its 64 weights per K-step this thread makes
+      constexpr int kHalves = 256 * NB / kProducerThreads;  // and how many of them
+      const uint8_t* wrow = wbase + (long long)min(n0 + wr, a.N - 1) * a.row_bytes;
+      bool ok = true;
+      uint8_t* raw = a_ring + NA * kTileBytes;
+      const int nsb = KB >> 2;
+      auto issue_sb = [&](int sbl) {  // one copy group per superblock, an empty one past the end
+        if (sbl < nsb) {
+          uint8_t* slot = raw + (sbl % kRawDepth) * kRawSlot;
+  #pragma unroll
+          for (int i = 0; i < (kRawPieces + kProducerThreads - 1) / kProducerThreads; i++) {
+            const int piece = tid + kProducerThreads * i;  // contiguous in the slot
+            if (piece < kRawPieces) {
+              const int row = piece / 9, pc = piece % 9;
+              const uint8_t* src = wbase + (long long)min(n0 + row, a.N - 1) * a.row_bytes +
+                                   (long long)((kb0 >> 2) + sbl) * 144 + pc * 16;
+              asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_u32(slot + piece * 16)), "l"(src)
+                           : "memory");
+            }
           }
         }
-      }
-      asm volatile("cp.async.commit_group;\n" ::: "memory");
-    };
-    if constexpr (RAW) {
-      for (int d = 0; d < kRawDepth; d++) issue_sb(d);
-    }
-    Q4kTileLoad cur{};
-    if constexpr (FASTQ4 && !RAW) cur = q4k_tile_load(wrow, kb0);
-    constexpr bool kQ6Pre = (C == Q6_K && A == 8 && NB == 1);  // 8-byte aligned rows, two threads per row
-    Q6kTileLoad cur6{};
-    if constexpr (kQ6Pre) cur6 = q6k_tile_load(wrow, kb0, hh0);
-    KQ_TR(long long tr_wait = 0; long long tr_prod = 0;)
-    {
-    for (int it = 0; it < KB && (ok || RAW); it++) {
-      const int kb = kb0 + it;
-      const int s = it % kBStages;
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+      };
       if constexpr (RAW) {
-        // Every producer passes every superblock barrier, also after a failed wait: nobody is left behind.
-        if ((it & 3) == 0) {
-          asm volatile("cp.async.wait_group %0;\n" ::"n"(kRawDepth - 2) : "memory");
-          asm volatile("bar.sync 1, %0;\n" ::"n"(kProducerThreads) : "memory");  // data landed, previous slot read
-          if (it > 0) issue_sb((it >> 2) - 1 + kRawDepth);
-        }
-        KQ_TR(const long long c0 = clock64();)
-        if (ok && it >= kBStages) ok = mbar_wait(&b_empty[s], ((it / kBStages) & 1) ^ 1, abort_flag, 1);
-        KQ_TR(tr_wait += clock64() - c0;)
-        if (!ok) continue;
-      } else {
-        KQ_TR(const long long c0 = clock64();)
-        if (it >= kBStages) ok = mbar_wait(&b_empty[s], ((it / kBStages) & 1) ^ 1, abort_flag, 1);
-        KQ_TR(tr_wait += clock64() - c0;)
-        if (!ok) break;
+        for (int d = 0; d < kRawDepth; d++) issue_sb(d);
       }
-      KQ_TR(const long long c1 = clock64();)
-      uint8_t* wdst = b_ring + s * kBTile + wr * 128;
-      if constexpr (RAW) {
-        const uint8_t* blk = raw + ((it >> 2) % kRawDepth) * kRawSlot + wr * 144;
-        Q4kTileLoad l;
-        l.hdr = *reinterpret_cast<const uint4*>(blk);
-        l.q0 = *reinterpret_cast<const uint4*>(blk + 16 + 32 * (it & 3));
-        l.q1 = *reinterpret_cast<const uint4*>(blk + 32 + 32 * (it & 3));
-#pragma unroll
-        for (int hh = hh0; hh < hh0 + kHalves; hh++) produce_w_q4k(l, kb, wdst, wr, hh);
-      } else if constexpr (FASTQ4) {
-        Q4kTileLoad nxt = cur;
-        if (it + 1 < KB) nxt = q4k_tile_load(wrow, kb + 1);  // next K-step's bytes are requested first
-#pragma unroll
-        for (int hh = hh0; hh < hh0 + kHalves; hh++)
-          produce_w_q4k(cur, kb, wdst, wr, hh);
-        cur = nxt;
-      } else if constexpr (kQ6Pre) {
-        Q6kTileLoad nxt6 = cur6;
-        if (it + 1 < KB) nxt6 = q6k_tile_load(wrow, kb + 1, hh0);  // next K-step's bytes are requested first
-        produce_w_q6k_pre(cur6, wrow, kb, wdst, wr, hh0);
-        cur6 = nxt6;
-      } else {
-#pragma unroll
-        for (int hh = hh0; hh < hh0 + kHalves; hh++) {
-          if constexpr (C == Q6_K && A >= 2) produce_w_q6k<2>(wrow, kb, wdst, wr, hh);  // blocks are 2-byte aligned
-          else produce_w_generic<C, A>(wrow, kb, a.K, wdst, wr, hh, tabs);
+      Q4kTileLoad cur{};
+      if constexpr (FASTQ4 && !RAW) cur = q4k_tile_load(wrow, kb0);
+      constexpr bool kQ6Pre = (C == Q6_K && A == 8 && NB == 1);  // 8-byte aligned rows, two threads per row
+      Q6kTileLoad cur6{};
+      if constexpr (kQ6Pre) cur6 = q6k_tile_load(wrow, kb0, hh0);
+      KQ_TR(long long tr_wait = 0; long long tr_prod = 0;)
+      {
+      for (int it = 0; it < KB && (ok || RAW); it++) {
+        const int kb = kb0 + it;
+        const int s = it % kBStages;
+        if constexpr (RAW) {
+          // Every producer passes every superblock barrier, also after a failed wait: nobody is left behind.
+          if ((it & 3) == 0) {
+            asm volatile("cp.async.wait_group %0;\n" ::"n"(kRawDepth - 2) : "memory");
+            asm volatile("bar.sync 1, %0;\n" ::"n"(kProducerThreads) : "memory");  // data landed, previous slot read
+            if (it > 0) issue_sb((it >> 2) - 1 + kRawDepth);
+          }
+          KQ_TR(const long long c0 = clock64();)
+          if (ok && it >= kBStages) ok = mbar_wait(&b_empty[s], ((it / kBStages) & 1) ^ 1, abort_flag, 1);
+          KQ_TR(tr_wait += clock64() - c0;)
+          if (!ok) continue;
+        } else {
+          KQ_TR(const long long c0 = clock64();)
+          if (it >= kBStages) ok = mbar_wait(&b_empty[s], ((it / kBStages) & 1) ^ 1, abort_flag, 1);
+          KQ_TR(tr_wait += clock64() - c0;)
+          if (!ok) break;
         }
+        KQ_TR(const long long c1 = clock64();)
+        uint8_t* wdst = b_ring + s * kBTile + wr * 128;
+        if constexpr (RAW) {
+          const uint8_t* blk = raw + ((it >> 2) % kRawDepth) * kRawSlot + wr * 144;
+          Q4kTileLoad l;
+          l.hdr = *reinterpret_cast<const uint4*>(blk);
+          l.q0 = *reinterpret_cast<const uint4*>(blk + 16 + 32 * (it & 3));
+          l.q1 = *reinterpret_cast<const uint4*>(blk + 32 + 32 * (it & 3));
+  #pragma unroll
+          for (int hh = hh0; hh < hh0 + kHalves; hh++) produce_w_q4k(l, kb, wdst, wr, hh);
+        } else if constexpr (FASTQ4) {
+          Q4kTileLoad nxt = cur;
+          if (it + 1 < KB) nxt = q4k_tile_load(wrow, kb + 1);  // next K-step's bytes are requested first
+  #pragma unroll
+          for (int hh = hh0; hh < hh0 + kHalves; hh++)
+            produce_w_q4k(cur, kb, wdst, wr, hh);
+          cur = nxt;
+        } else if constexpr (kQ6Pre) {
+          Q6kTileLoad nxt6 = cur6;
+          if (it + 1 < KB) nxt6 = q6k_tile_load(wrow, kb + 1, hh0);  // next K-step's bytes are requested first
+          produce_w_q6k_pre(cur6, wrow, kb, wdst, wr, hh0);
+          cur6 = nxt6;
+        } else {
+  #pragma unroll
+          for (int hh = hh0; hh < hh0 + kHalves; hh++) {
+            if constexpr (C == Q6_K && A >= 2) produce_w_q6k<2>(wrow, kb, wdst, wr, hh);  // blocks are 2-byte aligned
+            else produce_w_generic<C, A>(wrow, kb, a.K, wdst, wr, hh, tabs);
+          }
+        }
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&b_full[s]);
+        KQ_TR(tr_prod += clock64() - c1;)
       }
-      fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&b_full[s]);
-      KQ_TR(tr_prod += clock64() - c1;)
-    }
-    }
-    KQ_TR(if (tid == 0) { atomicAdd(&g_gemm_trace[4], (unsigned long long)tr_wait); atomicAdd(&g_gemm_trace[5], (unsigned long long)tr_prod); atomicAdd(&g_gemm_trace[6], 1ull); })
-    // ================= epilogue =================
-    KQ_TR(const long long ce = clock64();)
-    if (ok) ok = mbar_wait(&accum_bar, 0, abort_flag, 4);
-    if (ok) {
-      tc_fence_after();
-      const int lq = warp & 3;                   // TMEM lane quarter this warp may read
-      constexpr int kColSpan = BN / (kProducerThreads / 128);  // four warps (one per lane quarter) per column span
-      const int cbeg = (warp >> 2) * kColSpan;
-      if (gridDim.z > 1) {
-        // split K: this CTA's partial tile goes to shared memory (the rings are idle now) as fp32
-        // [rows][128], 16-byte chunks XOR-swizzled by the row so that a warp's stores spread over the banks
-        if constexpr (NB == 1) {
-#pragma unroll 1
+      }
+      KQ_TR(if (tid == 0) { atomicAdd(&g_gemm_trace[4], (unsigned long long)tr_wait); atomicAdd(&g_gemm_trace[5], (unsigned long long)tr_prod); atomicAdd(&g_gemm_trace[6], 1ull); })
+      // ================= epilogue =================
+      KQ_TR(const long long ce = clock64();)
+      if (ok) ok = mbar_wait(&accum_bar, 0, abort_flag, 4);
+      if (ok) {
+        tc_fence_after();
+        const int lq = warp & 3;                   // TMEM lane quarter this warp may read
+        constexpr int kColSpan = BN / (kProducerThreads / 128);  // four warps (one per lane quarter) per column span
+        const int cbeg = (warp >> 2) * kColSpan;
+        if (gridDim.z > 1) {
+          // split K: this CTA's partial tile goes to shared memory (the rings are idle now) as fp32
+          // [rows][128], 16-byte chunks XOR-swizzled by the row so that a warp's stores spread over the banks
+          if constexpr (NB == 1) {
+  #pragma unroll 1
+            for (int h = 0; h < mt_live; h++) {
+              const int rl = h * 128 + lq * 32 + lane;
+              const float rs = (a.row_scale && m0 + rl < m_end) ? a.row_scale[m0 + rl] : 1.f;
+              float* srow = reinterpret_cast<float*>(tiles) + rl * 128;
+  #pragma unroll 1
+              for (int c0 = cbeg; c0 < cbeg + kColSpan; c0 += 16) {
+                uint32_t v[16];
+                tmem_ld16(tmem_base + ((uint32_t)(lq * 32) << 16) + (uint32_t)(h * BN + c0), v);
+                tmem_ld_wait();
+  #pragma unroll
+                for (int i = 0; i < 4; i++)
+                  *reinterpret_cast<float4*>(srow + 4 * (((c0 >> 2) + i) ^ (rl & 31))) =
+                      make_float4(__uint_as_float(v[4 * i]) * rs, __uint_as_float(v[4 * i + 1]) * rs,
+                                  __uint_as_float(v[4 * i + 2]) * rs, __uint_as_float(v[4 * i + 3]) * rs);
+              }
+            }
+          }
+        } else {
+          // A thread owns one accumulator row (a TMEM lane): storing from here would write 32 rows x 32 bytes per
+          // instruction, one memory transaction per lane. The rounded tile goes through shared memory instead (the
+          // rings are idle: every MMA has completed), rows of BN outputs with their 16-byte chunks XOR-swizzled by
+          // the row, and leaves as whole rows, 16 bytes per lane.
+          constexpr int kRowBytes = BN * 2, kChunks = BN / 8;
+          uint8_t* stage = tiles;
+  #pragma unroll 1
           for (int h = 0; h < mt_live; h++) {
             const int rl = h * 128 + lq * 32 + lane;
             const float rs = (a.row_scale && m0 + rl < m_end) ? a.row_scale[m0 + rl] : 1.f;
-            float* srow = reinterpret_cast<float*>(tiles) + rl * 128;
-#pragma unroll 1
-            for (int c0 = cbeg; c0 < cbeg + kColSpan; c0 += 16) {
-              uint32_t v[16];
-              tmem_ld16(tmem_base + ((uint32_t)(lq * 32) << 16) + (uint32_t)(h * BN + c0), v);
+            uint8_t* srow = stage + rl * kRowBytes;
+  #pragma unroll 1
+            for (int c0 = cbeg; c0 < cbeg + kColSpan; c0 += 32) {
+              uint32_t va[16], vb[16];
+              tmem_ld16(tmem_base + ((uint32_t)(lq * 32) << 16) + (uint32_t)(h * BN + c0), va);
+              tmem_ld16(tmem_base + ((uint32_t)(lq * 32) << 16) + (uint32_t)(h * BN + c0 + 16), vb);
               tmem_ld_wait();
-#pragma unroll
-              for (int i = 0; i < 4; i++)
-                *reinterpret_cast<float4*>(srow + 4 * (((c0 >> 2) + i) ^ (rl & 31))) =
-                    make_float4(__uint_as_float(v[4 * i]) * rs, __uint_as_float(v[4 * i + 1]) * rs,
-                                __uint_as_float(v[4 * i + 2]) * rs, __uint_as_float(v[4 * i + 3]) * rs);
+              uint32_t o[16];
+  #pragma unroll
+              for (int i = 0; i < 16; i++) {
+                const uint32_t u0 = i < 8 ? va[2 * i] : vb[2 * i - 16], u1 = i < 8 ? va[2 * i + 1] : vb[2 * i - 15];
+                const float f0 = __uint_as_float(u0) * rs, f1 = __uint_as_float(u1) * rs;
+                if constexpr (kHalf) {
+                  o[i] = pack_h2f(f0, f1);
+                } else {
+                  __nv_bfloat162 bb = __floats2bfloat162_rn(f0, f1);
+                  o[i] = *reinterpret_cast<uint32_t*>(&bb);
+                }
+              }
+  #pragma unroll
+              for (int q = 0; q < 4; q++)
+                *reinterpret_cast<uint4*>(srow + ((((c0 >> 3) + q) ^ (rl & (kChunks - 1))) << 4)) =
+                    make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+            }
+          }
+          asm volatile("bar.sync 2, %0;\n" ::"n"(kProducerThreads) : "memory");
+          const int rows_live = min(m_end - m0, mt_live * 128);
+          constexpr int kRowsPerPass = 32 / kChunks;  // 1 (256 columns) or 2 (128 columns) rows per warp instruction
+          const int chunk = lane % kChunks;
+          const int col = n0 + chunk * 8;
+          OT* ybase = static_cast<OT*>(a.y);
+          for (int r = warp * kRowsPerPass + lane / kChunks; r < rows_live; r += (kProducerThreads / 32) * kRowsPerPass) {
+            const long long orow = a.yrow ? a.yrow[m0 + r] : (long long)(m0 + r);
+            const uint4 q = *reinterpret_cast<const uint4*>(stage + r * kRowBytes + ((chunk ^ (r & (kChunks - 1))) << 4));
+            OT* yp = ybase + orow * a.y_row_stride + col;
+            if (col + 8 <= a.N && (reinterpret_cast<uintptr_t>(yp) & 15) == 0) {
+              *reinterpret_cast<uint4*>(yp) = q;
+            } else {
+              const OT* qe = reinterpret_cast<const OT*>(&q);
+              for (int i = 0; i < 8; i++)
+                if (col + i < a.N) yp[i] = qe[i];
             }
           }
         }
-      } else {
-        // A thread owns one accumulator row (a TMEM lane): storing from here would write 32 rows x 32 bytes per
-        // instruction, one memory transaction per lane. The rounded tile goes through shared memory instead (the
-        // rings are idle: every MMA has completed), rows of BN outputs with their 16-byte chunks XOR-swizzled by
-        // the row, and leaves as whole rows, 16 bytes per lane.
-        constexpr int kRowBytes = BN * 2, kChunks = BN / 8;
-        uint8_t* stage = tiles;
-#pragma unroll 1
-        for (int h = 0; h < mt_live; h++) {
-          const int rl = h * 128 + lq * 32 + lane;
-          const float rs = (a.row_scale && m0 + rl < m_end) ? a.row_scale[m0 + rl] : 1.f;
-          uint8_t* srow = stage + rl * kRowBytes;
-#pragma unroll 1
-          for (int c0 = cbeg; c0 < cbeg + kColSpan; c0 += 32) {
-            uint32_t va[16], vb[16];
-            tmem_ld16(tmem_base + ((uint32_t)(lq * 32) << 16) + (uint32_t)(h * BN + c0), va);
-            tmem_ld16(tmem_base + ((uint32_t)(lq * 32) << 16) + (uint32_t)(h * BN + c0 + 16), vb);
-            tmem_ld_wait();
-            uint32_t o[16];
-#pragma unroll
-            for (int i = 0; i < 16; i++) {
-              const uint32_t u0 = i < 8 ? va[2 * i] : vb[2 * i - 16], u1 = i < 8 ? va[2 * i + 1] : vb[2 * i - 15];
-              const float f0 = __uint_as_float(u0) * rs, f1 = __uint_as_float(u1) * rs;
-              if constexpr (kHalf) {
-                o[i] = pack_h2f(f0, f1);
-              } else {
-                __nv_bfloat162 bb = __floats2bfloat162_rn(f0, f1);
-                o[i] = *reinterpret_cast<uint32_t*>(&bb);
+      }
+      KQ_TR(if (tid == 0) atomicAdd(&g_gemm_trace[7], (unsigned long long)(clock64() - ce));)
+    } else if (warp < kMmaWarp + kMmaWarps) {
+      // ================= MMA issuers =================
+      // Issuer w takes the row blocks h = w, w + kMmaWarps, ...; the activation tile of (K-step kb, row block h)
+      // is tile number kb * mt_live + h of the loader's sequence. Every issuer arrives on every stage barrier
+      // (a commit with no MMA of its own completes at once), so the counts do not depend on mt_live.
+      constexpr uint32_t idesc = umma_idesc(0u, BN);
+      const int w = warp - kMmaWarp;
+      bool ok = true;
+      KQ_TR(long long tr_b = 0; long long tr_a = 0; const long long cm = clock64();)
+      for (int kb = 0; kb < KB && ok; kb++) {  // kb counts this CTA's own K-steps
+        const int s = kb % kBStages;
+        KQ_TR(const long long c0 = clock64();)
+        ok = mbar_wait(&b_full[s], (kb / kBStages) & 1, abort_flag, 2);
+        KQ_TR(tr_b += clock64() - c0;)
+        if (!ok) break;
+        const uint32_t bt = smem_u32(b_ring + s * kBTile);
+        for (int h = w; h < mt_live && ok; h += kMmaWarps) {
+          const int t = kb * mt_live + h;
+          const int slot = t % NA;
+          KQ_TR(const long long c2 = clock64();)
+          ok = mbar_wait(&a_full[slot], (t / NA) & 1, abort_flag, 16);
+          KQ_TR(tr_a += clock64() - c2;)
+          if (!ok) break;
+          tc_fence_after();
+          if (lane == 0) {
+            const uint32_t at = smem_u32(a_ring + slot * kTileBytes);
+  #pragma unroll
+            for (int j = 0; j < kBK / 16; j++)
+              umma_f16(tmem_base + h * BN, umma_desc_sw128(at + j * 32), umma_desc_sw128(bt + j * 32), idesc,
+                       (kb > 0 || j > 0) ? 1u : 0u);
+            umma_commit(&a_empty[slot]);  // the slot is free once these MMAs have read it
+          }
+          __syncwarp();
+        }
+        if (ok && lane == 0) umma_commit(&b_empty[s]);
+        __syncwarp();
+      }
+      KQ_TR(if (lane == 0 && w == 0) { atomicAdd(&g_gemm_trace[0], (unsigned long long)tr_b); atomicAdd(&g_gemm_trace[1], (unsigned long long)tr_a); atomicAdd(&g_gemm_trace[2], (unsigned long long)(clock64() - cm)); })
+      if (lane == 0) umma_commit(&accum_bar);  // also on the abort path: lets the wait below see the MMAs drain
+      __syncwarp();
+      if (!ok) mbar_wait(&accum_bar, 0, abort_flag, 8);
+    } else {
+      // ================= activation loader (TMA) =================
+      bool ok = true;
+      int t = 0;
+      KQ_TR(long long tr_e = 0;)
+      for (int kb = 0; kb < KB && ok; kb++) {
+        for (int h = 0; h < mt_live && ok; h++, t++) {
+          const int slot = t % NA;
+          KQ_TR(const long long c0 = clock64();)
+          if (t >= NA) ok = mbar_wait(&a_empty[slot], ((t / NA) & 1) ^ 1, abort_flag, 32);
+          KQ_TR(tr_e += clock64() - c0;)
+          if (!ok) break;
+          if (lane == 0) {
+            mbar_expect_tx(&a_full[slot], kTileBytes);
+            tma_load_2d(a_ring + slot * kTileBytes, &tmap_x, (kb0 + kb) * kBK, m0 + h * 128, &a_full[slot]);
+          }
+          __syncwarp();
+        }
+      }
+      KQ_TR(if (lane == 0) atomicAdd(&g_gemm_trace[3], (unsigned long long)tr_e);)
+      // In-flight loads must have landed before the CTA may exit: wait (bounded) for the last ones.
+      if (ok && t > 0) {
+        const int first = t > NA ? t - NA : 0;
+        for (int u = first; u < t; u++)
+          if (!mbar_wait(&a_full[u % NA], (u / NA) & 1, abort_flag, 64)) break;
+      }
+    }
+
+    // ================= split K: the slices of a cluster meet through distributed shared memory =================
+    if (gridDim.z > 1) {
+      if constexpr (NB == 1) {
+        cg::cluster_group cluster = cg::this_cluster();
+        tc_fence_before();
+        cluster.sync();  // every slice's partial tile is in its shared memory
+        const int S = (int)gridDim.z, z = (int)blockIdx.z;
+        if (warp < kMmaWarp) {
+          const float* peer[8];
+  #pragma unroll
+          for (int q = 0; q < 8; q++)
+            peer[q] = q < S ? cluster.map_shared_rank(reinterpret_cast<float*>(tiles), q) : nullptr;
+          const int c = threadIdx.x & 31;  // 16-byte chunk = four columns
+          for (int rl = z + S * (threadIdx.x >> 5); rl < mt_live * 128; rl += S * (kProducerThreads / 32)) {
+            const int row = m0 + rl;
+            if (row >= m_end) continue;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  #pragma unroll
+            for (int q = 0; q < 8; q++) {
+              if (q < S) {
+                const float4 v = *reinterpret_cast<const float4*>(peer[q] + rl * 128 + 4 * (c ^ (rl & 31)));
+                acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
               }
             }
-#pragma unroll
-            for (int q = 0; q < 4; q++)
-              *reinterpret_cast<uint4*>(srow + ((((c0 >> 3) + q) ^ (rl & (kChunks - 1))) << 4)) =
-                  make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+            OT* yp = static_cast<OT*>(a.y) + (long long)row * a.y_row_stride + n0 + 4 * c;
+            const float f[4] = {acc.x, acc.y, acc.z, acc.w};
+  #pragma unroll
+            for (int i = 0; i < 4; i++) {
+              if (n0 + 4 * c + i < a.N) {
+                if constexpr (kHalf) yp[i] = __float2half_rn(f[i]);
+                else yp[i] = __float2bfloat16_rn(f[i]);
+              }
+            }
           }
         }
-        asm volatile("bar.sync 2, %0;\n" ::"n"(kProducerThreads) : "memory");
-        const int rows_live = min(m_end - m0, mt_live * 128);
-        constexpr int kRowsPerPass = 32 / kChunks;  // 1 (256 columns) or 2 (128 columns) rows per warp instruction
-        const int chunk = lane % kChunks;
-        const int col = n0 + chunk * 8;
-        OT* ybase = static_cast<OT*>(a.y);
-        for (int r = warp * kRowsPerPass + lane / kChunks; r < rows_live; r += (kProducerThreads / 32) * kRowsPerPass) {
-          const long long orow = a.yrow ? a.yrow[m0 + r] : (long long)(m0 + r);
-          const uint4 q = *reinterpret_cast<const uint4*>(stage + r * kRowBytes + ((chunk ^ (r & (kChunks - 1))) << 4));
-          OT* yp = ybase + orow * a.y_row_stride + col;
-          if (col + 8 <= a.N && (reinterpret_cast<uintptr_t>(yp) & 15) == 0) {
-            *reinterpret_cast<uint4*>(yp) = q;
-          } else {
-            const OT* qe = reinterpret_cast<const OT*>(&q);
-            for (int i = 0; i < 8; i++)
-              if (col + i < a.N) yp[i] = qe[i];
-          }
-        }
+        cluster.sync();  // peers may still be reading this CTA's partial tile
       }
     }
-    KQ_TR(if (tid == 0) atomicAdd(&g_gemm_trace[7], (unsigned long long)(clock64() - ce));)
-  } else if (warp < kMmaWarp + kMmaWarps) {
-    // ================= MMA issuers =================
-    // Issuer w takes the row blocks h = w, w + kMmaWarps, ...; the activation tile of (K-step kb, row block h)
-    // is tile number kb * mt_live + h of the loader's sequence. Every issuer arrives on every stage barrier
-    // (a commit with no MMA of its own completes at once), so the counts do not depend on mt_live.
-    constexpr uint32_t idesc = umma_idesc(0u, BN);
-    const int w = warp - kMmaWarp;
-    bool ok = true;
-    KQ_TR(long long tr_b = 0; long long tr_a = 0; const long long cm = clock64();)
-    for (int kb = 0; kb < KB && ok; kb++) {  // kb counts this CTA's own K-steps
-      const int s = kb % kBStages;
-      KQ_TR(const long long c0 = clock64();)
-      ok = mbar_wait(&b_full[s], (kb / kBStages) & 1, abort_flag, 2);
-      KQ_TR(tr_b += clock64() - c0;)
-      if (!ok) break;
-      const uint32_t bt = smem_u32(b_ring + s * kBTile);
-      for (int h = w; h < mt_live && ok; h += kMmaWarps) {
-        const int t = kb * mt_live + h;
-        const int slot = t % NA;
-        KQ_TR(const long long c2 = clock64();)
-        ok = mbar_wait(&a_full[slot], (t / NA) & 1, abort_flag, 16);
-        KQ_TR(tr_a += clock64() - c2;)
-        if (!ok) break;
-        tc_fence_after();
-        if (lane == 0) {
-          const uint32_t at = smem_u32(a_ring + slot * kTileBytes);
-#pragma unroll
-          for (int j = 0; j < kBK / 16; j++)
-            umma_f16(tmem_base + h * BN, umma_desc_sw128(at + j * 32), umma_desc_sw128(bt + j * 32), idesc,
-                     (kb > 0 || j > 0) ? 1u : 0u);
-          umma_commit(&a_empty[slot]);  // the slot is free once these MMAs have read it
-        }
-        __syncwarp();
-      }
-      if (ok && lane == 0) umma_commit(&b_empty[s]);
-      __syncwarp();
-    }
-    KQ_TR(if (lane == 0 && w == 0) { atomicAdd(&g_gemm_trace[0], (unsigned long long)tr_b); atomicAdd(&g_gemm_trace[1], (unsigned long long)tr_a); atomicAdd(&g_gemm_trace[2], (unsigned long long)(clock64() - cm)); })
-    if (lane == 0) umma_commit(&accum_bar);  // also on the abort path: lets the wait below see the MMAs drain
-    __syncwarp();
-    if (!ok) mbar_wait(&accum_bar, 0, abort_flag, 8);
-  } else {
-    // ================= activation loader (TMA) =================
-    bool ok = true;
-    int t = 0;
-    KQ_TR(long long tr_e = 0;)
-    for (int kb = 0; kb < KB && ok; kb++) {
-      for (int h = 0; h < mt_live && ok; h++, t++) {
-        const int slot = t % NA;
-        KQ_TR(const long long c0 = clock64();)
-        if (t >= NA) ok = mbar_wait(&a_empty[slot], ((t / NA) & 1) ^ 1, abort_flag, 32);
-        KQ_TR(tr_e += clock64() - c0;)
-        if (!ok) break;
-        if (lane == 0) {
-          mbar_expect_tx(&a_full[slot], kTileBytes);
-          tma_load_2d(a_ring + slot * kTileBytes, &tmap_x, (kb0 + kb) * kBK, m0 + h * 128, &a_full[slot]);
-        }
-        __syncwarp();
-      }
-    }
-    KQ_TR(if (lane == 0) atomicAdd(&g_gemm_trace[3], (unsigned long long)tr_e);)
-    // In-flight loads must have landed before the CTA may exit: wait (bounded) for the last ones.
-    if (ok && t > 0) {
-      const int first = t > NA ? t - NA : 0;
-      for (int u = first; u < t; u++)
-        if (!mbar_wait(&a_full[u % NA], (u / NA) & 1, abort_flag, 64)) break;
-    }
-  }
 
-  // ================= split K: the slices of a cluster meet through distributed shared memory =================
-  if (gridDim.z > 1) {
-    if constexpr (NB == 1) {
-      cg::cluster_group cluster = cg::this_cluster();
-      tc_fence_before();
-      cluster.sync();  // every slice's partial tile is in its shared memory
-      const int S = (int)gridDim.z, z = (int)blockIdx.z;
-      if (warp < kMmaWarp) {
-        const float* peer[8];
-#pragma unroll
-        for (int q = 0; q < 8; q++)
-          peer[q] = q < S ? cluster.map_shared_rank(reinterpret_cast<float*>(tiles), q) : nullptr;
-        const int c = threadIdx.x & 31;  // 16-byte chunk = four columns
-        for (int rl = z + S * (threadIdx.x >> 5); rl < mt_live * 128; rl += S * (kProducerThreads / 32)) {
-          const int row = m0 + rl;
-          if (row >= m_end) continue;
-          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-          for (int q = 0; q < 8; q++) {
-            if (q < S) {
-              const float4 v = *reinterpret_cast<const float4*>(peer[q] + rl * 128 + 4 * (c ^ (rl & 31)));
-              acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
-            }
-          }
-          OT* yp = static_cast<OT*>(a.y) + (long long)row * a.y_row_stride + n0 + 4 * c;
-          const float f[4] = {acc.x, acc.y, acc.z, acc.w};
-#pragma unroll
-          for (int i = 0; i < 4; i++) {
-            if (n0 + 4 * c + i < a.N) {
-              if constexpr (kHalf) yp[i] = __float2half_rn(f[i]);
-              else yp[i] = __float2bfloat16_rn(f[i]);
-            }
-          }
-        }
-      }
-      cluster.sync();  // peers may still be reading this CTA's partial tile
-    }
-  }
+    // ================= end of the tile =================
+    tc_fence_before();
+    __syncthreads();
+    if (a.tiles == nullptr || tile + (int)gridDim.y >= n_list || abort_s != 0) break;
+  }  // tile loop
 
   // ================= teardown =================
-  tc_fence_before();
-  __syncthreads();
   if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
@@ -1140,6 +1158,10 @@ cudaError_t launch_gemm_tiles(int codec, bool out_half, const void* xh, long lon
                               cudaStream_t st) {
   if (rows_total <= 0 || N <= 0 || K <= 0 || max_tiles <= 0) return cudaSuccess;
   if (max_tiles > 65535) return cudaErrorInvalidConfiguration;
+  // The list may hold up to max_tiles tiles but usually holds far fewer (an expert-parallel rank sizes it for all
+  // ranks' rows and owns an eighth of them): a CTA without a tile still costs about 2 us of an SM (one CTA per
+  // SM by shared memory), so the grid is capped and CTAs loop over the list when it is longer.
+  if (max_tiles > kTileGridCap) max_tiles = kTileGridCap;
   GemmArgs a;
   a.x = xh;
   a.x_row_stride = K;

@@ -31,6 +31,10 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
   asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t));
   return t;
 }
+// Before a barrier that has been used is initialised again (nothing may be pending on it).
+__device__ __forceinline__ void mbar_inval(uint64_t* bar) {
+  asm volatile("mbarrier.inval.shared::cta.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
 // Bounded wait. Returns false (after raising the abort flag) when the barrier did
 // not flip within 2 s or another thread of the CTA already gave up.
 __device__ __forceinline__ bool mbar_wait_err(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code,

@@ -326,3 +326,29 @@ def test_block_refuses_small_calls():
                                  wd.stride(0), 144, 8, b"q4_k", idx.data_ptr(), sc.data_ptr(), 2, x.data_ptr(), 2, None, 0,
                                  None)
     assert rc == _lib.KQ_ERR_UNSUPPORTED
+
+
+def test_block_with_more_tiles_than_the_grid_cap():
+    """The grouped tile kernel launches at most 256 tile rows and loops over longer lists: 300 experts with rows
+    make 300 tiles or more. Against the composition per expert on the plain matmul."""
+    import mlx_kquant_b200 as kq
+    from mlx_kquant_b200.moe import moe_swiglu_block, swiglu
+
+    E, H, F, k, T = 300, 256, 256, 1, 300 * 40
+    rng = np.random.default_rng(91)
+    wgu = torch.from_numpy(mint_wire("q4_k", rng.normal(0, 0.02, (E * 2 * F, H)).astype(np.float32))).cuda().reshape(E, 2 * F, -1)
+    wd = torch.from_numpy(mint_wire("q4_k", rng.normal(0, 0.02, (E * H, F)).astype(np.float32))).cuda().reshape(E, H, -1)
+    g = torch.Generator(device="cuda").manual_seed(92)
+    x = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+    ids = (torch.arange(T, device="cuda") % E).to(torch.int32).reshape(T, 1)
+    probs = torch.rand(T, 1, device="cuda", generator=g) + 0.5
+    y = moe_swiglu_block(x, wgu, wd, "q4_k", ids, probs)
+    assert y is not None
+    for e in (0, 1, 149, 255, 256, 299):                       # experts on both sides of the cap
+        rows = torch.nonzero(ids[:, 0] == e)[:, 0]
+        gu = kq.quantized_matmul(x[rows], wgu[e], None, "q4_k")
+        h = swiglu(gu[:, :F], gu[:, F:])
+        d = kq.quantized_matmul(h, wd[e], None, "q4_k")
+        ref = (d.float() * probs[rows]).to(torch.bfloat16)
+        err = float((y[rows].float() - ref.float()).norm() / ref.float().norm())
+        assert err < 4e-3, (e, err)
