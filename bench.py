@@ -726,10 +726,27 @@ def moe_ep_cell(dev, rank, world):
             out[f"moe_glu_q4k_ep{world}_gathered{tag}_T{Tg}_per_rank"] = cell
             del ep
             torch.cuda.empty_cache()
-    for name, kw in (("pipelined2_bf16sum", dict(chunks=2, reduce_dtype=torch.bfloat16)),
-                     ("pipelined4_bf16sum", dict(chunks=4, reduce_dtype=torch.bfloat16)),
-                     ("pipelined2_f32sum", dict(chunks=2))):
-        ep = PipelinedExpertParallel(T, H, k, E, wgu, wd, "q4_k", **kw)
+    # The collectives of the pipelined form run beside the tile kernel, which wants whole SMs: communicators limited
+    # to a few CTAs leave it more of the machine (ncclConfig max_ctas through torch's process-group options).
+    def narrow_group(ctas):
+        try:
+            opts = dist.ProcessGroupNCCL.Options()
+            opts.config.max_ctas = ctas
+            opts.config.min_ctas = 1
+            return dist.new_group(pg_options=opts)
+        except Exception:  # noqa: BLE001 - an older torch without these options: the cell is left out
+            return None
+
+    cells = [("pipelined2_bf16sum", dict(chunks=2, reduce_dtype=torch.bfloat16), None),
+             ("pipelined4_bf16sum", dict(chunks=4, reduce_dtype=torch.bfloat16), None),
+             ("pipelined2_f32sum", dict(chunks=2), None)]
+    if world > 2:
+        cells += [(f"pipelined2_bf16sum_{c}ctas", dict(chunks=2, reduce_dtype=torch.bfloat16), c) for c in (4, 8, 16)]
+    for name, kw, ctas in cells:
+        grp = narrow_group(ctas) if ctas else None
+        if ctas and grp is None:
+            continue
+        ep = PipelinedExpertParallel(T, H, k, E, wgu, wd, "q4_k", group=grp, **kw)
         ms = timed_ep(ep, x, ids, probs, 5)
         out[f"moe_glu_q4k_ep{world}_{name}_T{T}_per_rank"] = {"tokens_per_s": world * T / (ms * 1e-3), "ms": ms}
         del ep
@@ -781,6 +798,36 @@ def run_case(argv):
         ids, probs = route_topk(torch.randn(T, E, device="cuda"), k)
         for _ in range(3):
             y = moe_glu(x, None, None, wd, "q4_k", ids, probs, w_gate_up=wgu)
+    elif what == "ep_local":
+        # the local stage of one expert-parallel rank of eight, on one GPU (no communicator): all ranks' tokens and
+        # routing in the gathered buffer, this rank's sixteen experts
+        from mlx_kquant_b200.moe import GatheredExpertParallel, fuse_gate_up, route_topk
+
+        T = int(argv[1]) if len(argv) > 1 else 4096
+        rd = torch.float32 if (len(argv) > 2 and argv[2] == "f32") else torch.bfloat16
+        E, H, F, k, world = 128, 2048, 768, 8, 8
+        el = E // world
+        wgu = fuse_gate_up(random_wire("q4_k", F, H, seed=5, lead=(el,)), random_wire("q4_k", F, H, seed=6, lead=(el,)))
+        wd = random_wire("q4_k", H, F, seed=7, lead=(el,))
+        ep = GatheredExpertParallel(T, H, k, E, wgu, wd, "q4_k", rank=3, world=world, reduce_dtype=rd)
+        g = torch.Generator(device="cpu").manual_seed(1)
+        rows = T + ep.pad_rows
+        for r in range(world):
+            xr = torch.randn(T, H, generator=g).to(torch.bfloat16).cuda()
+            ids, probs = route_topk(torch.randn(T, E, generator=g).cuda(), k)
+            ep.pack(xr, ids, probs)
+            ep.recv[r * rows:(r + 1) * rows].copy_(ep.send)
+        ep.capture()
+        e0, e1 = _events(torch)
+        for _ in range(3):
+            ep._graph.replay()
+        e0.record()
+        for _ in range(10):
+            ep._graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        print(f"local stage of rank 3 of 8, T = {T} per rank: {e0.elapsed_time(e1) / 10:.4f} ms")
+        y = ep.partial
     else:
         print(__doc__)
         return 2

@@ -833,62 +833,64 @@ convert_x_kernel(const XT* __restrict__ x, long long x_row_stride, int K, __half
                  int lhs_div, int M, int* __restrict__ yrow, const int* __restrict__ n_valid, long long rows) {
   static_assert(!GLU || sizeof(XT) == 2, "the fused activation takes fp16 / bf16 gate | up rows");
   const int lane = threadIdx.x & 31;
-  const long long row = blockIdx.x * 8LL + (threadIdx.x >> 5);
-  if (row >= rows) return;
-  if (n_valid != nullptr && row >= (long long)(*n_valid) * M) return;  // see the scalar kernel
-  long long src_row = row;
-  if (order != nullptr) {
-    const int entry = order[row / M], i = (int)(row % M);
-    // the activation row of an entry: that of unit u = entry / lhs_div (lhs_div = k routed rows per token when
-    // the entries are a [tokens, k] routing table, else 1), through lhs when there is an index array
-    const int u = entry / lhs_div;
-    src_row = (lhs != nullptr ? (long long)lhs[u] : (long long)u) * M + i;
-    if (lane == 0 && yrow != nullptr) yrow[row] = entry * M + i;
-  } else if (lhs != nullptr) {
-    src_row = (long long)lhs[row / M] * M + row % M;
-  }
-  const XT* xr = x + src_row * x_row_stride;
-  __half* o = xh + row * (long long)K;
-  const int nch = K >> 3;
-  if constexpr (std::is_same<XT, __half>::value) {
-    for (int c = lane; c < nch; c += 32) *reinterpret_cast<uint4*>(o + 8 * c) = cvt_fetch8<XT, GLU>(xr, K, c);
-    if (lane == 0) row_scale[row] = 1.f;
-  } else {
-    uint4 keep[kCvtChunks];  // the row's values as bf16 pairs (they are bf16 values: nothing is lost)
-    __nv_bfloat162 m2 = __floats2bfloat162_rn(0.f, 0.f);
-#pragma unroll
-    for (int j = 0; j < kCvtChunks; j++) {
-      const int c = lane + 32 * j;
-      if (c < nch) {
-        keep[j] = cvt_fetch8<XT, GLU>(xr, K, c);
-        m2 = cvt_absmax(m2, keep[j]);
+  // rows that exist: all, or the first *n_valid * M in gather mode (see the scalar kernel). The grid is capped on
+  // the host and the warps stride over the rows, so a list sized for many more rows than it holds costs nothing.
+  const long long limit = n_valid != nullptr ? min(rows, (long long)(*n_valid) * M) : rows;
+  for (long long row = blockIdx.x * 8LL + (threadIdx.x >> 5); row < limit; row += gridDim.x * 8LL) {
+    long long src_row = row;
+    if (order != nullptr) {
+      const int entry = order[row / M], i = (int)(row % M);
+      // the activation row of an entry: that of unit u = entry / lhs_div (lhs_div = k routed rows per token when
+      // the entries are a [tokens, k] routing table, else 1), through lhs when there is an index array
+      const int u = entry / lhs_div;
+      src_row = (lhs != nullptr ? (long long)lhs[u] : (long long)u) * M + i;
+      if (lane == 0 && yrow != nullptr) yrow[row] = entry * M + i;
+    } else if (lhs != nullptr) {
+      src_row = (long long)lhs[row / M] * M + row % M;
+    }
+    const XT* xr = x + src_row * x_row_stride;
+    __half* o = xh + row * (long long)K;
+    const int nch = K >> 3;
+    if constexpr (std::is_same<XT, __half>::value) {
+      for (int c = lane; c < nch; c += 32) *reinterpret_cast<uint4*>(o + 8 * c) = cvt_fetch8<XT, GLU>(xr, K, c);
+      if (lane == 0) row_scale[row] = 1.f;
+    } else {
+      uint4 keep[kCvtChunks];  // the row's values as bf16 pairs (they are bf16 values: nothing is lost)
+      __nv_bfloat162 m2 = __floats2bfloat162_rn(0.f, 0.f);
+  #pragma unroll
+      for (int j = 0; j < kCvtChunks; j++) {
+        const int c = lane + 32 * j;
+        if (c < nch) {
+          keep[j] = cvt_fetch8<XT, GLU>(xr, K, c);
+          m2 = cvt_absmax(m2, keep[j]);
+        }
       }
-    }
-    for (int c = lane + 32 * kCvtChunks; c < nch; c += 32) m2 = cvt_absmax(m2, cvt_fetch8<XT, GLU>(xr, K, c));
-    float mx = fmaxf(__low2float(m2), __high2float(m2));
-    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-    if (!(mx < INFINITY)) {
-      // a row with infinities: they propagate on their own, the factor comes from the finite values
-      mx = 0.f;
-#pragma unroll
-      for (int j = 0; j < kCvtChunks; j++)
-        if (lane + 32 * j < nch) mx = cvt_finite_absmax(mx, keep[j]);
-      for (int c = lane + 32 * kCvtChunks; c < nch; c += 32) mx = cvt_finite_absmax(mx, cvt_fetch8<XT, GLU>(xr, K, c));
+      for (int c = lane + 32 * kCvtChunks; c < nch; c += 32) m2 = cvt_absmax(m2, cvt_fetch8<XT, GLU>(xr, K, c));
+      float mx = fmaxf(__low2float(m2), __high2float(m2));
       for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      if (!(mx < INFINITY)) {
+        // a row with infinities: they propagate on their own, the factor comes from the finite values
+        mx = 0.f;
+  #pragma unroll
+        for (int j = 0; j < kCvtChunks; j++)
+          if (lane + 32 * j < nch) mx = cvt_finite_absmax(mx, keep[j]);
+        for (int c = lane + 32 * kCvtChunks; c < nch; c += 32) mx = cvt_finite_absmax(mx, cvt_fetch8<XT, GLU>(xr, K, c));
+        for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+      }
+      // Every row is normalised (see the scalar kernel); 2^-e in two exact halves, since it can overflow float32.
+      int e = 0;
+      if (mx > 0.f) e = ilogbf(mx) - 14;
+      const int eh = (-e) / 2;
+      const float down1 = ldexpf(1.f, eh), down2 = ldexpf(1.f, -e - eh);
+      if (lane == 0) row_scale[row] = ldexpf(1.f, e);
+  #pragma unroll
+      for (int j = 0; j < kCvtChunks; j++) {
+        const int c = lane + 32 * j;
+        if (c < nch) *reinterpret_cast<uint4*>(o + 8 * c) = cvt_scale8(keep[j], down1, down2);
+      }
+      for (int c = lane + 32 * kCvtChunks; c < nch; c += 32)
+        *reinterpret_cast<uint4*>(o + 8 * c) = cvt_scale8(cvt_fetch8<XT, GLU>(xr, K, c), down1, down2);
     }
-    // Every row is normalised (see the scalar kernel); 2^-e in two exact halves, since it can overflow float32.
-    int e = 0;
-    if (mx > 0.f) e = ilogbf(mx) - 14;
-    const int eh = (-e) / 2;
-    const float down1 = ldexpf(1.f, eh), down2 = ldexpf(1.f, -e - eh);
-    if (lane == 0) row_scale[row] = ldexpf(1.f, e);
-#pragma unroll
-    for (int j = 0; j < kCvtChunks; j++) {
-      const int c = lane + 32 * j;
-      if (c < nch) *reinterpret_cast<uint4*>(o + 8 * c) = cvt_scale8(keep[j], down1, down2);
-    }
-    for (int c = lane + 32 * kCvtChunks; c < nch; c += 32)
-      *reinterpret_cast<uint4*>(o + 8 * c) = cvt_scale8(cvt_fetch8<XT, GLU>(xr, K, c), down1, down2);
   }
 }
 
@@ -897,7 +899,7 @@ static void launch_convert_t(const void* x, long long x_row_stride, int K, long 
                              const uint32_t* lhs, int lhs_div, int M, __half* o, float* row_scale, int* yrow,
                              const int* n_valid, bool glu, bool vec, cudaStream_t st) {
   const XT* xp = static_cast<const XT*>(x);
-  const unsigned gv = (unsigned)((rows + 7) / 8);
+  const unsigned gv = (unsigned)std::min<long long>((rows + 7) / 8, 148 * 24);
   if (glu) {
     if constexpr (sizeof(XT) == 2)
       convert_x_kernel<XT, true><<<gv, 256, 0, st>>>(xp, x_row_stride, K, o, row_scale, order, lhs, lhs_div, M, yrow,

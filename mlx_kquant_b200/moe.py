@@ -428,13 +428,15 @@ class GatheredExpertParallel:
         meta = self._meta(self.recv, R)
         ids = meta[:, :T * k].reshape(W * T * k) - self.lo
         probs = meta[:, T * k:2 * T * k].reshape(W * T * k).view(torch.float32)
-        mine = (ids >= 0) & (ids < self.e_local)
-        probs = torch.where(mine, probs, torch.zeros_like(probs))
         rows = W * T * k
         if self.block_ok:
+            # the block skips every entry whose index is outside [0, e_local) by itself (a negative difference
+            # reads as a huge unsigned index)
             moe_swiglu_block(self.recv, self.w_gate_up, self.w_down, self.kquant_type, ids.view(W * T, k),
                              probs.view(W * T, k), token_rows=self.tok_rows, tokens=W * T, out=self.partial)
             return
+        mine = (ids >= 0) & (ids < self.e_local)
+        probs = torch.where(mine, probs, torch.zeros_like(probs))
         Fh = self.w_gate_up.shape[1] // 2
         gu = gather_qmm(self.recv.view(W * R, 1, self.H), self.w_gate_up, None, self.kquant_type,
                         lhs_indices=self.lhs, rhs_indices=ids).reshape(rows, 2 * Fh)
