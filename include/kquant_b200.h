@@ -126,7 +126,7 @@ KQ_API int kq_device_error_flags(int* flags, int clear);
  * workspace: at least kq_gather_qmm_workspace_bytes(n_entries, M, n_experts, K)
  * bytes of device memory, 256-byte aligned, private to this call until it
  * completes on the stream. Decode-sized calls need a few hundred KB; prefill-sized
- * ones (32 or more rows per expert on average) also hold an expert-sorted fp16 copy
+ * ones (16 or more rows per expert on average) also hold an expert-sorted fp16 copy
  * of the routed activations (n_entries * M * K * 2 bytes) for the tensor-core kernel.
  * The size depends on K (the fp16 copy): pass the call's own K. K = 0 returns the size of the grouping
  * scratch alone, which is what kq_gather_qmm_noalloc needs; kq_gather_qmm rejects a workspace of that size.
@@ -212,7 +212,7 @@ KQ_API int kq_gather_qmv_mix(const void* x, int x_dtype, long long T, int S, int
  * row); w_down [n_experts, H, down_row_bytes] (F weights per row); indices / scores [T, top_k] (uint32 / float32); an
  * index outside [0, n_experts) contributes nothing (an expert-parallel rank passes the other ranks' experts that
  * way). y [T, H] of y_dtype = x_dtype or KQ_F32 (partial sums for a later reduction). Any codec. Sizes: at least 512
- * routed rows and 32 per expert on average, H % 8 == F % 8 == 0; otherwise KQ_ERR_UNSUPPORTED.
+ * routed rows and 16 per expert on average, H % 8 == F % 8 == 0; otherwise KQ_ERR_UNSUPPORTED.
  * kq_moe_block_workspace_bytes(T, top_k, n_experts, H, F): bytes of device scratch the call needs (0 = sizes not
  * supported); 256-byte aligned, private to the call until it completes. */
 KQ_API size_t kq_moe_block_workspace_bytes(long long T, int top_k, int n_experts, int H, int F);

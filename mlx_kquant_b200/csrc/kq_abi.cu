@@ -537,7 +537,7 @@ int kq_moe_swiglu_block(const void* x, int x_dtype, long long T, int H, long lon
       ((size_t)x_row_stride * xe) % 16 != 0)
     return fail(KQ_ERR_UNSUPPORTED,
                 "[mlx_kquant.moe_swiglu_block] the tile-kernel block takes float16 / bfloat16 rows (16-byte aligned), "
-                "H and F multiples of 8 and at least 512 routed rows with 32 or more per expert on average: compose "
+                "H and F multiples of 8 and at least 512 routed rows with 16 or more per expert on average: compose "
                 "smaller calls from kq_moe_glu_gather + kq_gather_qmv_mix or kq_gather_qmm.");
   const size_t need = kq::moe_block_workspace_bytes(T, top_k, n_experts, H, F);
   if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)

@@ -10,7 +10,7 @@
 //   3. scatter of entry ids into expert order
 //   4. task build: each expert's c*M rows are cut into GemvTask slices of 16
 //   5. the skinny-M kernel runs over (row tile, k-slice, task)
-// Prefill-sized calls (on average 32 or more rows per expert) take the tensor-core
+// Prefill-sized calls (on average 16 or more rows per expert) take the tensor-core
 // route instead: steps 1-3, then a tile list of 256 sorted rows per entry, an
 // expert-sorted fp16 copy of the activations (the tile kernel streams it with TMA),
 // and the tcgen05 tile kernel with a row-index scatter in its epilogue.
@@ -30,7 +30,7 @@ static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 // Which regime a call takes is decided on the host from sizes alone (no device round trip).
 static bool use_grouped(long long n_entries, int M, int n_experts, int K) {
   const long long rows = n_entries * (long long)M;
-  return K > 0 && (K % 8) == 0 && rows >= 512 && rows >= 32LL * n_experts && rows < (1LL << 31);
+  return K > 0 && (K % 8) == 0 && rows >= 512 && rows >= 16LL * n_experts && rows < (1LL << 31);
 }
 
 GatherLayout gather_layout(long long n_entries, int M, int n_experts, int K) {

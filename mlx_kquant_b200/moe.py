@@ -103,8 +103,8 @@ FUSED_MAX_ENTRIES = 512   # beyond (measured on the 128-expert block): the three
 
 def _fused_regime(rows: int, n_experts: int) -> bool:
     """The fused decode kernels serve calls below the prefill regime of gather_qmm (512 or more routed entries
-    with 32 or more per expert on average go to the tensor-core tile kernel)."""
-    return not (rows >= 512 and rows >= 32 * n_experts) and rows <= FUSED_MAX_ENTRIES
+    with 16 or more per expert on average go to the tensor-core tile kernel)."""
+    return not (rows >= 512 and rows >= 16 * n_experts) and rows <= FUSED_MAX_ENTRIES
 
 
 def _decode_ws(n_entries: int, n_experts: int, n_mix: int, device):
