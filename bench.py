@@ -499,9 +499,13 @@ def parity_n(dev, rank, world, W0, x_dev, y0):
     ep = GatheredExpertParallel(T, H, k, E, wgu, wd, "q4_k")
     y_gat = ep(x, ids, probs).clone()
     del ep
-    from mlx_kquant_b200.moe import PipelinedExpertParallel
+    from mlx_kquant_b200.moe import PeerExpertParallel, PipelinedExpertParallel
     ep = PipelinedExpertParallel(T, H, k, E, wgu, wd, "q4_k", chunks=2, reduce_dtype=torch.bfloat16)
     y_pip = ep(x, ids, probs).clone()
+    del ep
+    ep = PeerExpertParallel(T, H, k, E, wgu, wd, "q4_k")
+    y_peer = ep(x, ids, probs).clone()
+    ep.close()
     del ep
 
     def gather(t):
@@ -514,11 +518,13 @@ def parity_n(dev, rank, world, W0, x_dev, y0):
         all_wgu, all_wd = torch.cat(gather(wgu), 0), torch.cat(gather(wd), 0)
         all_x, all_ids, all_p = gather(x), gather(ids), gather(probs)
         all_a, all_g, all_pl = gather(y_a2a), gather(y_gat.to(y_a2a.dtype)), gather(y_pip.to(y_a2a.dtype))
+        all_pe = gather(y_peer.to(y_a2a.dtype))
         if rank == 0:
             for r in range(world):
                 ref = moe_glu(all_x[r], None, None, all_wd, "q4_k", all_ids[r], all_p[r], w_gate_up=all_wgu).float()
                 for name, got, bar in (("all-to-all", all_a[r], 6e-3), ("gathered", all_g[r], 6e-3),
-                                       ("pipelined, bfloat16 sums", all_pl[r], 8e-3)):
+                                       ("pipelined, bfloat16 sums", all_pl[r], 8e-3),
+                                       ("peer-memory, bfloat16 slots", all_pe[r], 8e-3)):
                     err = float((got.float() - ref).norm() / ref.norm())
                     if not err <= bar:
                         problems.append(f"MoE {name} form, rank {r}: rel error {err:.2e} against the single-GPU block")
@@ -726,6 +732,24 @@ def moe_ep_cell(dev, rank, world):
             out[f"moe_glu_q4k_ep{world}_gathered{tag}_T{Tg}_per_rank"] = cell
             del ep
             torch.cuda.empty_cache()
+    # the weighted sum written into the owners' memory through peer mappings instead of a reduce-scatter
+    from mlx_kquant_b200.moe import PeerExpertParallel
+
+    for Tg in (64, 4096):
+        try:
+            ep = PeerExpertParallel(Tg, H, k, E, wgu, wd, "q4_k")
+        except ValueError:  # sizes the one-call block does not take (few routed rows per local expert)
+            continue
+        xg, idg, prg = x[:Tg].contiguous(), ids[:Tg].contiguous(), probs[:Tg].contiguous()
+        ms = timed_ep(ep, xg, idg, prg, 20 if Tg <= 64 else 5)
+        cell = {"tokens_per_s": world * Tg / (ms * 1e-3), "ms": ms}
+        if Tg == 4096:
+            cell["local_stage_with_peer_stores_ms"] = timed_part(lambda: ep._graph.replay())
+        out[f"moe_glu_q4k_ep{world}_peer_T{Tg}_per_rank"] = cell
+        ep.close()
+        del ep
+        torch.cuda.empty_cache()
+
     # The collectives of the pipelined form run beside the tile kernel, which wants whole SMs: communicators limited
     # to a few CTAs leave it more of the machine (ncclConfig max_ctas through torch's process-group options).
     def narrow_group(ctas):

@@ -222,6 +222,36 @@ KQ_API int kq_moe_swiglu_block(const void* x, int x_dtype, long long T, int H, l
                                size_t down_row_bytes, int n_experts, const char* kquant_type, const uint32_t* indices,
                                const float* scores, int top_k, void* y, int y_dtype, void* workspace,
                                size_t workspace_bytes, void* stream);
+/* Expert parallelism over peer memory (one process per GPU; the buffers are mapped into each other's address space
+ * by the host, e.g. with CUDA IPC handles; plain stores, no multicast). kq_moe_swiglu_block_scatter is
+ * kq_moe_swiglu_block for a rank that owns n_experts of the experts and sees the tokens of ALL ranks (T = world *
+ * tokens_per_rank, token g = w * tokens_per_rank + t belongs to rank w): instead of a [T, H] output it writes the
+ * partial row of token g to slot_ptrs[w] + (my_rank * tokens_per_rank + t) * H elements - slot_ptrs being a DEVICE
+ * array of `world` pointers to the ranks' [world, tokens_per_rank, H] slot buffers of slot_dtype (x_dtype or
+ * KQ_F32) - and writes nothing for a token none of whose experts it owns. After every rank's call has completed
+ * (the host orders that, e.g. with a collective on the same streams), the owner adds its tokens' slots with
+ * kq_moe_sum_slots: slots [world, T, H] (T tokens of this rank), ids [T, top_k] GLOBAL expert indices, rank_lo
+ * [world + 1] (device) the first expert of each rank's contiguous share: y[t] = sum, in rank order, of slots[r][t]
+ * over the ranks r that own at least one of token t's experts (float32 accumulation, one rounding to y_dtype).
+ * Together they replace "partial sums + reduce-scatter": only non-empty partial rows cross the link, once. */
+KQ_API int kq_moe_swiglu_block_scatter(const void* x, int x_dtype, long long T, int H, long long x_row_stride,
+                                       const uint32_t* token_rows, const void* w_gate_up,
+                                       long long gate_up_expert_stride_bytes, size_t gate_up_row_bytes, int F,
+                                       const void* w_down, long long down_expert_stride_bytes, size_t down_row_bytes,
+                                       int n_experts, const char* kquant_type, const uint32_t* indices,
+                                       const float* scores, int top_k, void* const* slot_ptrs, int slot_dtype,
+                                       int my_rank, long long tokens_per_rank, void* workspace, size_t workspace_bytes,
+                                       void* stream);
+KQ_API int kq_moe_sum_slots(const void* slots, int slot_dtype, const uint32_t* ids, const int* rank_lo, int world,
+                            long long T, int top_k, int H, void* y, int y_dtype, void* stream);
+/* Device buffers shared between the processes of one node, for the peer-memory forms above: the owner creates
+ * (cudaMalloc + CUDA IPC; handle64 receives the 64-byte handle, to be sent to the peers over any host channel), a
+ * peer opens the handle on ITS current device (lazy peer access) and gets a pointer its kernels may store to, closes
+ * it when done; the owner destroys the buffer after every peer has closed it. */
+KQ_API int kq_peer_buffer_create(size_t bytes, void** ptr, unsigned char* handle64);
+KQ_API int kq_peer_buffer_open(const unsigned char* handle64, void** ptr);
+KQ_API int kq_peer_buffer_close(void* ptr);
+KQ_API int kq_peer_buffer_destroy(void* ptr);
 KQ_API int kq_moe_router_topk(const void* logits, int dtype, long long T, int E, int top_k, int norm_topk_prob,
                               int shared_gate, const float* per_expert_scale, const float* bias, const char* scoring,
                               float scale, uint32_t* indices, float* scores, void* stream);

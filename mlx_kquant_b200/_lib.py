@@ -65,6 +65,17 @@ SIGNATURES = {
                                       C.c_longlong, C.c_size_t, C.c_int, C.c_void_p, C.c_longlong, C.c_size_t, C.c_int,
                                       C.c_char_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p,
                                       C.c_size_t, C.c_void_p]),
+    "kq_moe_swiglu_block_scatter": (C.c_int, [C.c_void_p, C.c_int, C.c_longlong, C.c_int, C.c_longlong, C.c_void_p,
+                                              C.c_void_p, C.c_longlong, C.c_size_t, C.c_int, C.c_void_p, C.c_longlong,
+                                              C.c_size_t, C.c_int, C.c_char_p, C.c_void_p, C.c_void_p, C.c_int,
+                                              C.c_void_p, C.c_int, C.c_int, C.c_longlong, C.c_void_p, C.c_size_t,
+                                              C.c_void_p]),
+    "kq_moe_sum_slots": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_longlong, C.c_int, C.c_int,
+                                   C.c_void_p, C.c_int, C.c_void_p]),
+    "kq_peer_buffer_create": (C.c_int, [C.c_size_t, C.c_void_p, C.c_void_p]),
+    "kq_peer_buffer_open": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "kq_peer_buffer_close": (C.c_int, [C.c_void_p]),
+    "kq_peer_buffer_destroy": (C.c_int, [C.c_void_p]),
     "kq_gather_qmm_workspace_bytes": (C.c_size_t, [C.c_longlong, C.c_int, C.c_int, C.c_int]),
     "kq_gather_qmm": (C.c_int, [C.c_void_p, C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_void_p, C.c_int,
                                 C.c_longlong, C.c_size_t, C.c_int, C.c_char_p, C.c_void_p, C.c_void_p,

@@ -506,12 +506,12 @@ size_t kq_moe_block_workspace_bytes(long long T, int top_k, int n_experts, int H
   return kq::moe_block_workspace_bytes(T, top_k, n_experts, H, F);
 }
 
-int kq_moe_swiglu_block(const void* x, int x_dtype, long long T, int H, long long x_row_stride,
-                        const uint32_t* token_rows, const void* w_gate_up, long long gate_up_expert_stride_bytes,
-                        size_t gate_up_row_bytes, int F, const void* w_down, long long down_expert_stride_bytes,
-                        size_t down_row_bytes, int n_experts, const char* kquant_type, const uint32_t* indices,
-                        const float* scores, int top_k, void* y, int y_dtype, void* workspace, size_t workspace_bytes,
-                        void* stream) {
+static int moe_block_entry(const void* x, int x_dtype, long long T, int H, long long x_row_stride,
+                           const uint32_t* token_rows, const void* w_gate_up, long long gate_up_expert_stride_bytes,
+                           size_t gate_up_row_bytes, int F, const void* w_down, long long down_expert_stride_bytes,
+                           size_t down_row_bytes, int n_experts, const char* kquant_type, const uint32_t* indices,
+                           const float* scores, int top_k, void* y, int y_dtype, void* workspace,
+                           size_t workspace_bytes, void* stream, const kq::MoeScatter* scatter) {
   const int ci = find_codec(kquant_type);
   if (ci < 0)
     return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_swiglu_block] Unknown kquant_type: '%s'.",
@@ -530,7 +530,7 @@ int kq_moe_swiglu_block(const void* x, int x_dtype, long long T, int H, long lon
   if (y_dtype != x_dtype && y_dtype != KQ_F32)
     return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_swiglu_block] y must have x's dtype or float32.");
   if (T == 0 || H == 0) return KQ_OK;
-  if (!x || !w_gate_up || !w_down || !indices || !scores || !y)
+  if (!x || !w_gate_up || !w_down || !indices || !scores || (!y && !scatter))
     return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_swiglu_block] null pointer.");
   const size_t xe = 2;
   if (!kq::moe_block_supported(x_dtype, T, top_k, n_experts, H, F) || (reinterpret_cast<uintptr_t>(x) & 15) != 0 ||
@@ -548,8 +548,99 @@ int kq_moe_swiglu_block(const void* x, int x_dtype, long long T, int H, long lon
                                        gate_up_expert_stride_bytes, (long long)gate_up_row_bytes, F,
                                        static_cast<const uint8_t*>(w_down), down_expert_stride_bytes,
                                        (long long)down_row_bytes, n_experts, indices, scores, top_k, y, y_dtype == KQ_F32,
-                                       workspace, static_cast<cudaStream_t>(stream));
+                                       workspace, static_cast<cudaStream_t>(stream), scatter);
   if (e != cudaSuccess) return cuda_fail("moe_swiglu_block", e);
+  return KQ_OK;
+}
+
+int kq_moe_swiglu_block(const void* x, int x_dtype, long long T, int H, long long x_row_stride,
+                        const uint32_t* token_rows, const void* w_gate_up, long long gate_up_expert_stride_bytes,
+                        size_t gate_up_row_bytes, int F, const void* w_down, long long down_expert_stride_bytes,
+                        size_t down_row_bytes, int n_experts, const char* kquant_type, const uint32_t* indices,
+                        const float* scores, int top_k, void* y, int y_dtype, void* workspace, size_t workspace_bytes,
+                        void* stream) {
+  return moe_block_entry(x, x_dtype, T, H, x_row_stride, token_rows, w_gate_up, gate_up_expert_stride_bytes,
+                         gate_up_row_bytes, F, w_down, down_expert_stride_bytes, down_row_bytes, n_experts, kquant_type,
+                         indices, scores, top_k, y, y_dtype, workspace, workspace_bytes, stream, nullptr);
+}
+
+int kq_moe_swiglu_block_scatter(const void* x, int x_dtype, long long T, int H, long long x_row_stride,
+                                const uint32_t* token_rows, const void* w_gate_up, long long gate_up_expert_stride_bytes,
+                                size_t gate_up_row_bytes, int F, const void* w_down, long long down_expert_stride_bytes,
+                                size_t down_row_bytes, int n_experts, const char* kquant_type, const uint32_t* indices,
+                                const float* scores, int top_k, void* const* slot_ptrs, int slot_dtype, int my_rank,
+                                long long tokens_per_rank, void* workspace, size_t workspace_bytes, void* stream) {
+  if (slot_ptrs == nullptr || tokens_per_rank <= 0 || my_rank < 0 || T % (tokens_per_rank > 0 ? tokens_per_rank : 1) != 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT,
+                "[mlx_kquant.moe_swiglu_block_scatter] slot_ptrs must be a device array of one buffer per rank and T a "
+                "whole number of tokens_per_rank.");
+  if (slot_dtype != x_dtype && slot_dtype != KQ_F32)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_swiglu_block_scatter] slots must have x's dtype or float32.");
+  const kq::MoeScatter sc{slot_ptrs, my_rank, tokens_per_rank, slot_dtype == KQ_F32};
+  return moe_block_entry(x, x_dtype, T, H, x_row_stride, token_rows, w_gate_up, gate_up_expert_stride_bytes,
+                         gate_up_row_bytes, F, w_down, down_expert_stride_bytes, down_row_bytes, n_experts, kquant_type,
+                         indices, scores, top_k, nullptr, slot_dtype, workspace, workspace_bytes, stream, &sc);
+}
+
+int kq_moe_sum_slots(const void* slots, int slot_dtype, const uint32_t* ids, const int* rank_lo, int world, long long T,
+                     int top_k, int H, void* y, int y_dtype, void* stream) {
+  if (!dtype_ok(slot_dtype) || !dtype_ok(y_dtype))
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_sum_slots] Only real floating dtypes are supported.");
+  if (T < 0 || top_k < 0 || H < 0 || world <= 0 || world > 32 || top_k > 256 || (H % 8) != 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_sum_slots] sizes: world 1..32, top_k <= 256, H a multiple of 8.");
+  if (T == 0 || H == 0 || top_k == 0) return KQ_OK;
+  if (!slots || !ids || !rank_lo || !y) return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_sum_slots] null pointer.");
+  cudaError_t e = kq::launch_moe_slot_sum(slot_dtype, slots, ids, rank_lo, world, T, top_k, H, y_dtype, y,
+                                          static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("moe_sum_slots", e);
+  return KQ_OK;
+}
+
+// ---- buffers shared between the processes of one node (one process per GPU) ---------------------------------
+// Plain cudaMalloc + CUDA IPC: the owner creates the buffer and hands the 64-byte handle to its peers (any host
+// channel); a peer opens it ON ITS OWN DEVICE with lazy peer access, so its kernels can store into the owner's
+// memory over NVLink without a context on the owner's GPU.
+int kq_peer_buffer_create(size_t bytes, void** ptr, unsigned char* handle64) {
+  if (ptr == nullptr || handle64 == nullptr || bytes == 0)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.peer_buffer_create] null pointer or zero size.");
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e != cudaSuccess) return cuda_fail("peer_buffer_create", e);
+  cudaIpcMemHandle_t h;
+  e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return cuda_fail("peer_buffer_create", e);
+  }
+  static_assert(sizeof(h) == 64, "CUDA IPC handles are 64 bytes");
+  std::memcpy(handle64, &h, 64);
+  *ptr = p;
+  return KQ_OK;
+}
+
+int kq_peer_buffer_open(const unsigned char* handle64, void** ptr) {
+  if (ptr == nullptr || handle64 == nullptr)
+    return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.peer_buffer_open] null pointer.");
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle64, 64);
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return cuda_fail("peer_buffer_open", e);
+  *ptr = p;
+  return KQ_OK;
+}
+
+int kq_peer_buffer_close(void* ptr) {
+  if (ptr == nullptr) return KQ_OK;
+  cudaError_t e = cudaIpcCloseMemHandle(ptr);
+  if (e != cudaSuccess) return cuda_fail("peer_buffer_close", e);
+  return KQ_OK;
+}
+
+int kq_peer_buffer_destroy(void* ptr) {
+  if (ptr == nullptr) return KQ_OK;
+  cudaError_t e = cudaFree(ptr);
+  if (e != cudaSuccess) return cuda_fail("peer_buffer_destroy", e);
   return KQ_OK;
 }
 

@@ -489,7 +489,8 @@ size_t moe_block_workspace_bytes(long long T, int k, int n_experts, int H, int F
 cudaError_t launch_moe_block(int codec, int x_dtype, const void* x, long long x_row_stride, const uint32_t* token_rows,
                              long long T, int H, const uint8_t* wgu, long long stride_gu, long long rb_h, int F,
                              const uint8_t* wd, long long stride_d, long long rb_f, int n_experts, const uint32_t* idx,
-                             const float* scores, int k, void* y, bool y_f32, void* workspace, cudaStream_t st) {
+                             const float* scores, int k, void* y, bool y_f32, void* workspace, cudaStream_t st,
+                             const MoeScatter* scatter) {
   if (!moe_block_supported(x_dtype, T, k, n_experts, H, F)) return cudaErrorInvalidValue;
   const MoeBlockLayout L = moe_block_layout(T, k, n_experts, H, F);
   const long long n = T * k;
@@ -533,6 +534,9 @@ cudaError_t launch_moe_block(int codec, int x_dtype, const void* x, long long x_
   if ((err = launch_gemm_tiles(codec, half, hh, n, F, wd, stride_d, rb_f, H, d, half ? nullptr : scale2, yrow, tiles,
                                n_tiles, (int)L.max_tiles, st)) != cudaSuccess)
     return err;
+  if (scatter != nullptr)
+    return launch_moe_combine_scatter(x_dtype, d, scores, idx, (uint32_t)n_experts, T, k, H, scatter->tokens_per_rank,
+                                      scatter->my_rank, scatter->slots, scatter->slot_f32, st);
   return launch_moe_combine(x_dtype, d, scores, T, k, H, y, y_f32, st, idx, (uint32_t)n_experts);
 }
 

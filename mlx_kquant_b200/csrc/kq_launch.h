@@ -131,10 +131,25 @@ cudaError_t launch_convert(int x_dtype, const void* x, long long x_row_stride, i
 // down product, weighted sum per token. wgu: [E, 2F, rb_h] (gate rows then up rows); y: x dtype or float32.
 bool moe_block_supported(int x_dtype, long long T, int k, int n_experts, int H, int F);
 size_t moe_block_workspace_bytes(long long T, int k, int n_experts, int H, int F);
+// scatter != nullptr (expert parallel over peer memory): instead of y, token g = w * tokens_per_rank + t leaves its
+// partial row in slots[w][my_rank][t] - slots: device array of `world` pointers to the ranks' [world,
+// tokens_per_rank, H] buffers (peer mappings) - unless none of its experts is local.
+struct MoeScatter {
+  void* const* slots;
+  int my_rank;
+  long long tokens_per_rank;
+  bool slot_f32;
+};
 cudaError_t launch_moe_block(int codec, int x_dtype, const void* x, long long x_row_stride, const uint32_t* token_rows,
                              long long T, int H, const uint8_t* wgu, long long stride_gu, long long rb_h, int F,
                              const uint8_t* wd, long long stride_d, long long rb_f, int n_experts, const uint32_t* idx,
-                             const float* scores, int k, void* y, bool y_f32, void* workspace, cudaStream_t st);
+                             const float* scores, int k, void* y, bool y_f32, void* workspace, cudaStream_t st,
+                             const MoeScatter* scatter = nullptr);
+cudaError_t launch_moe_combine_scatter(int dtype, const void* d, const float* probs, const uint32_t* idx,
+                                       uint32_t n_experts, long long tokens, int k, int H, long long tokens_per_rank,
+                                       int my_rank, void* const* slots, bool slot_f32, cudaStream_t st);
+cudaError_t launch_moe_slot_sum(int slot_dtype, const void* slots, const uint32_t* ids, const int* rank_lo, int world,
+                                long long T, int k, int H, int y_dtype, void* y, cudaStream_t st);
 
 // gather_qmm: device-side grouping by expert + the skinny-M kernel per group.
 struct GatherLayout {

@@ -111,6 +111,86 @@ __global__ void __launch_bounds__(256) combine_kernel(const T* __restrict__ d, c
   }
 }
 
+
+// ---- expert-parallel combine over peer memory -------------------------------------------------
+// The weighted sum of an expert-parallel rank, written straight into the memory of the rank that owns the
+// token instead of into a local buffer that a reduce-scatter then moves: token g = w * tokens_per_rank + t
+// belongs to rank w, and this rank's partial row goes to slots[w][my_rank][t] (slots[w] = that rank's
+// [world, tokens_per_rank, H] buffer, reached through a peer mapping; plain 16-byte stores, no multicast).
+// A token none of whose experts lives here writes nothing: the owner knows from its own routing table
+// which ranks contribute to each of its tokens (slot_sum_kernel below) and never reads the other slots.
+template <typename T, typename OT>
+__global__ void __launch_bounds__(256)
+combine_scatter_kernel(const T* __restrict__ d, const float* __restrict__ p, const uint32_t* __restrict__ idx,
+                       uint32_t n_experts, int k, int H, long long tokens_per_rank, int my_rank,
+                       OT* const* __restrict__ slots) {
+  const long long g = blockIdx.x;
+  int mine = 0;
+  if ((int)threadIdx.x < k) mine = (idx[g * k + threadIdx.x] < n_experts && p[g * k + threadIdx.x] != 0.f) ? 1 : 0;
+  if (!__syncthreads_or(mine)) return;
+  const long long w = g / tokens_per_rank, t = g % tokens_per_rank;
+  OT* out = slots[w] + ((long long)my_rank * tokens_per_rank + t) * (long long)H;
+  for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < k; j++) {
+      const float wj = p[g * k + j];
+      if (wj == 0.f || idx[g * k + j] >= n_experts) continue;
+      const uint4 v = *reinterpret_cast<const uint4*>(d + (g * k + j) * (long long)H + c);
+      const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int q = 0; q < 4; q++) {
+        const float2 f = pair_to_float<T>(vw[q]);
+        acc[2 * q] = fmaf(wj, f.x, acc[2 * q]);
+        acc[2 * q + 1] = fmaf(wj, f.y, acc[2 * q + 1]);
+      }
+    }
+    store8<OT>(out + c, acc);
+  }
+  // No fence here: the stores are complete when the grid is, and the host orders "every rank's grid has finished"
+  // before anyone reads its slots (a collective queued behind this kernel on every rank's stream).
+}
+
+// y[t, :] = sum over the ranks r that own at least one of token t's experts, in rank order, of slots[r][t, :]
+// (float32 accumulation, one rounding). rank_lo [world + 1]: first expert of each rank's contiguous share.
+template <typename ST, typename OT>
+__global__ void __launch_bounds__(256)
+slot_sum_kernel(const ST* __restrict__ slots, const uint32_t* __restrict__ ids, const int* __restrict__ rank_lo, int world,
+                long long T, int k, int H, OT* __restrict__ y) {
+  const long long t = blockIdx.x;
+  __shared__ unsigned s_mask;
+  if (threadIdx.x == 0) s_mask = 0u;
+  __syncthreads();
+  if ((int)threadIdx.x < k) {
+    const int e = (int)ids[t * k + threadIdx.x];
+    for (int r = 0; r < world; r++)
+      if (e >= rank_lo[r] && e < rank_lo[r + 1]) atomicOr(&s_mask, 1u << r);
+  }
+  __syncthreads();
+  const unsigned mask = s_mask;
+  for (int c = threadIdx.x * 8; c < H; c += blockDim.x * 8) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < world; r++) {
+      if (!((mask >> r) & 1u)) continue;
+      const ST* src = slots + ((long long)r * T + t) * (long long)H + c;
+      if constexpr (sizeof(ST) == 4) {
+        const float4 a = *reinterpret_cast<const float4*>(src), b = *reinterpret_cast<const float4*>(src + 4);
+        acc[0] += a.x, acc[1] += a.y, acc[2] += a.z, acc[3] += a.w;
+        acc[4] += b.x, acc[5] += b.y, acc[6] += b.z, acc[7] += b.w;
+      } else {
+        const uint4 v = *reinterpret_cast<const uint4*>(src);
+        const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          const float2 f = pair_to_float<ST>(vw[q]);
+          acc[2 * q] += f.x;
+          acc[2 * q + 1] += f.y;
+        }
+      }
+    }
+    store8<OT>(y + t * (long long)H + c, acc);
+  }
+}
+
 }  // namespace
 
 cudaError_t launch_swiglu(int dtype, const void* gate, const void* up, long long in_row_stride, long long rows, int F,
@@ -141,6 +221,49 @@ cudaError_t launch_moe_combine(int dtype, const void* d, const float* probs, lon
     if (y_f32) combine_kernel<__nv_bfloat16, float><<<g, 256, 0, st>>>(dp, probs, idx, n_experts, k, H, static_cast<float*>(y));
     else combine_kernel<__nv_bfloat16, __nv_bfloat16><<<g, 256, 0, st>>>(dp, probs, idx, n_experts, k, H, static_cast<__nv_bfloat16*>(y));
   }
+  return cudaGetLastError();
+}
+
+// d [tokens * k, H] of dtype -> partial rows in the owners' slot buffers (slot_f32: float32 slots, else dtype).
+cudaError_t launch_moe_combine_scatter(int dtype, const void* d, const float* probs, const uint32_t* idx,
+                                       uint32_t n_experts, long long tokens, int k, int H, long long tokens_per_rank,
+                                       int my_rank, void* const* slots, bool slot_f32, cudaStream_t st) {
+  if (tokens <= 0 || H <= 0 || k <= 0) return cudaSuccess;
+  if (k > 256 || tokens_per_rank <= 0) return cudaErrorInvalidValue;
+  const unsigned g = (unsigned)tokens;
+#define KQ_CS(T, OT)                                                                                          \
+  combine_scatter_kernel<T, OT><<<g, 256, 0, st>>>(static_cast<const T*>(d), probs, idx, n_experts, k, H,      \
+                                                   tokens_per_rank, my_rank, reinterpret_cast<OT* const*>(slots))
+  if (dtype == F16) {
+    if (slot_f32) KQ_CS(__half, float);
+    else KQ_CS(__half, __half);
+  } else {
+    if (slot_f32) KQ_CS(__nv_bfloat16, float);
+    else KQ_CS(__nv_bfloat16, __nv_bfloat16);
+  }
+#undef KQ_CS
+  return cudaGetLastError();
+}
+
+// slots [world, T, H] (slot_dtype F32 / F16 / BF16), ids [T, k] global expert indices -> y [T, H] (F16 / BF16 / F32)
+cudaError_t launch_moe_slot_sum(int slot_dtype, const void* slots, const uint32_t* ids, const int* rank_lo, int world,
+                                long long T, int k, int H, int y_dtype, void* y, cudaStream_t st) {
+  if (T <= 0 || H <= 0 || k <= 0) return cudaSuccess;
+  if (k > 256 || world <= 0 || world > 32) return cudaErrorInvalidValue;
+  const unsigned g = (unsigned)T;
+#define KQ_SS(ST, OT) \
+  slot_sum_kernel<ST, OT><<<g, 256, 0, st>>>(static_cast<const ST*>(slots), ids, rank_lo, world, T, k, H, static_cast<OT*>(y))
+#define KQ_SS_OUT(ST)                        \
+  do {                                       \
+    if (y_dtype == F32) KQ_SS(ST, float);    \
+    else if (y_dtype == F16) KQ_SS(ST, __half); \
+    else KQ_SS(ST, __nv_bfloat16);           \
+  } while (0)
+  if (slot_dtype == F32) KQ_SS_OUT(float);
+  else if (slot_dtype == F16) KQ_SS_OUT(__half);
+  else KQ_SS_OUT(__nv_bfloat16);
+#undef KQ_SS_OUT
+#undef KQ_SS
   return cudaGetLastError();
 }
 

@@ -189,12 +189,14 @@ def gather_qmv_mix_ns_kq(x, w, kquant_type, indices, scores, *, workspace=None, 
 
 
 def moe_swiglu_block(x, w_gate_up, w_down, kquant_type, expert_ids, expert_probs, *, token_rows=None, tokens=None,
-                     out=None, workspace=None):
+                     out=None, workspace=None, scatter=None):
     """A whole SwiGLU block on the tile kernel (kq_moe_swiglu_block in include/kquant_b200.h): x [T, H] float16 /
     bfloat16, w_gate_up [E, 2F, bytes(H)] (`fuse_gate_up`), w_down [E, H, bytes(F)], expert_ids / expert_probs [T, k]
     -> y [T, H]. Same bits as the three-gather composition with its activation and weighted-sum kernels.
     token_rows [T] (with tokens = T): token t's activation is row token_rows[t] of x. out: a [T, H] tensor of x's
-    dtype or float32 to write into. Returns None when the sizes are outside the block's regime."""
+    dtype or float32 to write into. Returns None when the sizes are outside the block's regime.
+    scatter = (slot_ptrs int64 [world] on the device, slot dtype, my_rank, tokens_per_rank): the expert-parallel
+    form over peer memory (kq_moe_swiglu_block_scatter); nothing is returned but True."""
     T = int(tokens) if tokens is not None else x.shape[0]
     H = x.shape[1]
     k = expert_ids.shape[1]
@@ -213,6 +215,16 @@ def moe_swiglu_block(x, w_gate_up, w_down, kquant_type, expert_ids, expert_probs
     idx = _u32(expert_ids, x.device)
     sc = expert_probs.to(device=x.device, dtype=torch.float32).contiguous()
     tr = _u32(token_rows, x.device) if token_rows is not None else None
+    if scatter is not None:
+        ptrs, slot_dtype, my_rank, per_rank = scatter
+        with torch.cuda.device(x.device):
+            ws = workspace if workspace is not None else torch.empty(need, dtype=torch.uint8, device=x.device)
+            _lib.check(_lib.lib().kq_moe_swiglu_block_scatter(
+                x.data_ptr(), _DT[x.dtype], T, H, x.stride(0), tr.data_ptr() if tr is not None else None,
+                w_gate_up.data_ptr(), w_gate_up.stride(0), rb_h, F, w_down.data_ptr(), w_down.stride(0), w_down.shape[2],
+                E, kquant_type.encode(), idx.data_ptr(), sc.data_ptr(), k, ptrs.data_ptr(), _DT[slot_dtype], int(my_rank),
+                int(per_rank), ws.data_ptr(), ws.numel(), torch.cuda.current_stream(x.device).cuda_stream))
+        return True
     y = out if out is not None else torch.empty((T, H), dtype=x.dtype, device=x.device)
     if y.dtype not in (x.dtype, torch.float32) or not y.is_contiguous() or tuple(y.shape) != (T, H):
         raise ValueError("[mlx_kquant.moe_swiglu_block] out must be a contiguous [T, H] tensor of x's dtype or float32.")
@@ -477,6 +489,127 @@ class GatheredExpertParallel:
             self.local_stage()
         dist.reduce_scatter_tensor(self.y32, self.partial, group=self.group)
         return self.y32.to(x.dtype)
+
+
+def moe_sum_slots(slots, expert_ids, rank_lo, out_dtype, *, shape=None, dtype=None):
+    """kq_moe_sum_slots: slots [world, T, H] (a tensor, or a raw device pointer with shape= and dtype=), expert_ids
+    [T, k] (global indices), rank_lo int32 [world + 1] on the device -> y [T, H] = the sum of the slots of the ranks
+    that own one of the token's experts."""
+    if isinstance(slots, torch.Tensor):
+        ptr, (W, T, H), dtype, dev = slots.data_ptr(), slots.shape, slots.dtype, slots.device
+    else:
+        ptr, (W, T, H), dev = int(slots), shape, rank_lo.device
+    ids = _u32(expert_ids, dev)
+    y = torch.empty((T, H), dtype=out_dtype, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().kq_moe_sum_slots(ptr, _DT[dtype], ids.data_ptr(), rank_lo.data_ptr(), W, T, ids.shape[1], H,
+                                               y.data_ptr(), _DT[out_dtype], torch.cuda.current_stream(dev).cuda_stream))
+    return y
+
+
+class PeerBuffers:
+    """One device buffer per rank, each mapped into every other rank's process (one process per GPU, one node):
+    the kq_peer_buffer_* entry points (cudaMalloc + CUDA IPC, opened on the opener's own device with lazy peer
+    access); the 64-byte handles travel through the process group's object all-gather. `ptrs[r]` is rank r's
+    buffer as seen from this process. close() is collective."""
+
+    def __init__(self, nbytes: int, device, group=None):
+        import ctypes as C
+
+        import torch.distributed as dist
+
+        self.group, self.device = group, device
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        L = _lib.lib()
+        with torch.cuda.device(device):
+            own, handle = C.c_void_p(), (C.c_ubyte * 64)()
+            _lib.check(L.kq_peer_buffer_create(nbytes, C.byref(own), handle))
+            self.own = own.value
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle), group=group)
+            self.ptrs = []
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    self.ptrs.append(self.own)
+                    continue
+                p = C.c_void_p()
+                _lib.check(L.kq_peer_buffer_open((C.c_ubyte * 64).from_buffer_copy(h), C.byref(p)))
+                self.ptrs.append(p.value)
+        dist.barrier(group=group)   # every rank has opened every buffer before anyone stores
+
+    def close(self):
+        import torch.distributed as dist
+
+        if self.ptrs is None:
+            return
+        L = _lib.lib()
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            for r, p in enumerate(self.ptrs):
+                if r != self.rank:
+                    _lib.check(L.kq_peer_buffer_close(p))
+            dist.barrier(group=self.group)   # nobody still maps this rank's buffer
+            _lib.check(L.kq_peer_buffer_destroy(self.own))
+        self.ptrs = None
+
+
+class PeerExpertParallel(GatheredExpertParallel):
+    """GatheredExpertParallel whose weighted sum goes straight into the owners' memory: the local stage ends with
+    the combine kernel writing each token's partial row into slot [my_rank] of the token's home rank through a
+    peer mapping (only tokens with an expert here write), one small collective tells every rank that all writes
+    have landed, and a local kernel adds the slots of the ranks that contribute to each token. Against the
+    reduce-scatter form: the partial rows cross NVLink once and only the non-empty ones (two thirds at 8 ranks
+    and top-8), and no [world * T, H] buffer is written and read again. Needs the one-call block
+    (`moe_swiglu_block`) sizes; slots of `reduce_dtype` (default: the activation dtype). close() is collective."""
+
+    def __init__(self, T, H, k, n_experts, w_gate_up, w_down, kquant_type, dtype=torch.bfloat16, group=None, *,
+                 reduce_dtype=None):
+        from .dist import shard_bounds
+
+        reduce_dtype = reduce_dtype or dtype
+        super().__init__(T, H, k, n_experts, w_gate_up, w_down, kquant_type, dtype, group, reduce_dtype=reduce_dtype)
+        if not self.block_ok:
+            raise ValueError("[mlx_kquant.moe] PeerExpertParallel needs sizes the one-call block takes "
+                             "(512 or more routed rows over all ranks, 16 per local expert).")
+        dev = w_down.device
+        self.partial = None   # no local [world * T, H] buffer in this form
+        self.slot_dtype = reduce_dtype
+        item = torch.empty((), dtype=reduce_dtype).element_size()
+        self.buffers = PeerBuffers(self.world * T * H * item, dev, group)
+        self.slot_ptrs = torch.tensor(self.buffers.ptrs, dtype=torch.int64, device=dev)
+        self.rank_lo = torch.tensor([shard_bounds(n_experts, r, self.world)[0] for r in range(self.world)] + [n_experts],
+                                    dtype=torch.int32, device=dev)
+        self.flag = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.out_dtype = dtype
+
+    def close(self):
+        self._graph = None
+        self.buffers.close()
+
+    def local_stage(self):
+        T, k, W = self.T, self.k, self.world
+        R = T + self.pad_rows
+        meta = self._meta(self.recv, R)
+        ids = meta[:, :T * k].reshape(W * T * k) - self.lo
+        probs = meta[:, T * k:2 * T * k].reshape(W * T * k).view(torch.float32)
+        moe_swiglu_block(self.recv, self.w_gate_up, self.w_down, self.kquant_type, ids.view(W * T, k),
+                         probs.view(W * T, k), token_rows=self.tok_rows, tokens=W * T,
+                         scatter=(self.slot_ptrs, self.slot_dtype, self.rank, T))
+
+    def __call__(self, x, expert_ids, expert_probs):
+        import torch.distributed as dist
+
+        self.pack(x, expert_ids, expert_probs)
+        dist.all_gather_into_tensor(self.recv, self.send, group=self.group)
+        if self._graph is not None:
+            self._graph.replay()
+        else:
+            self.local_stage()
+        # every rank's stores into this rank's slots are complete once every rank has joined this collective
+        # (it is queued behind the local stage on each rank's stream)
+        dist.all_reduce(self.flag, group=self.group)
+        return moe_sum_slots(self.buffers.own, expert_ids, self.rank_lo, self.out_dtype,
+                             shape=(self.world, self.T, self.H), dtype=self.slot_dtype)
 
 
 class PipelinedExpertParallel:

@@ -27,7 +27,8 @@ def _worker(rank, world, port, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    import datetime
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=datetime.timedelta(seconds=90))
     try:
         E, H, F, k, T = 16, 512, 256, 4, 96
         wg = random_wire("q4_k", F, H, seed=1, device=dev, lead=(E,))
@@ -46,8 +47,24 @@ def _worker(rank, world, port, q):
         err = max(err, float((ep(x, ids, probs).float() - want).norm() / want.norm()))
         ep.capture()
         err = max(err, float((ep(x, ids, probs).float() - want).norm() / want.norm()))
-        torch.cuda.synchronize()
-        q.put((rank, err))
+        # the same with the weighted sum written into the owners' memory through peer mappings: float32 slots
+        # (the same sum as the reduce-scatter form), then slots of the activation dtype (one more rounding per rank)
+        from mlx_kquant_b200.moe import PeerExpertParallel
+        err_slots = 0.0
+        for slot_dtype in (torch.float32, torch.bfloat16):
+            pe = PeerExpertParallel(T, H, k, E, fuse_gate_up(wg[lo:hi], wu[lo:hi]), wd[lo:hi].contiguous(), "q4_k",
+                                    reduce_dtype=slot_dtype)
+            e1 = float((pe(x, ids, probs).float() - want).norm() / want.norm())
+            pe.capture()
+            for _ in range(3):   # the slots are reused step after step
+                e1 = max(e1, float((pe(x, ids, probs).float() - want).norm() / want.norm()))
+            torch.cuda.synchronize()
+            pe.close()
+            if slot_dtype == torch.float32:
+                err = max(err, e1)
+            else:
+                err_slots = e1
+        q.put((rank, err, err_slots))
     finally:
         dist.destroy_process_group()
 
@@ -68,4 +85,4 @@ def test_expert_parallel_matches_single_gpu():
         p.join(timeout=60)
         assert p.exitcode == 0
     # same kernels on both sides; rows only meet different partners inside a tile
-    assert all(err < 2e-3 for _, err in results), results
+    assert all(err < 2e-3 and err_slots < 4e-3 for _, err, err_slots in results), results

@@ -127,3 +127,47 @@ def test_gathered_expert_parallel_two_virtual_ranks(T, E):
         want = moe_glu(xs[r], wg, wu, wd, "q4_k", *routes[r], fused=False).float()   # the same composition
         got = total[r * T:(r + 1) * T].to(torch.bfloat16).float()
         assert float((got - want).norm() / want.norm()) < 2e-3
+
+
+def test_peer_scatter_combine_two_virtual_ranks():
+    """kq_moe_swiglu_block_scatter + kq_moe_sum_slots with both "ranks" on one GPU (the slot buffers are ordinary
+    local tensors here; on two GPUs they are peer mappings, tests/test_moe_ep_gpu.py): every token's output is the
+    single-GPU block's, and slots nobody owns a share of are never read (they hold NaNs)."""
+    from mlx_kquant_b200.dist import shard_bounds
+    from mlx_kquant_b200.moe import GatheredExpertParallel, fuse_gate_up, moe_sum_slots, moe_swiglu_block
+    from mlx_kquant_b200.synth import random_wire
+    dev = torch.device("cuda")
+    T, E, H, F, k, W = 160, 16, 512, 256, 2, 2
+    wg = random_wire("q4_k", F, H, seed=1, device=dev, lead=(E,))
+    wu = random_wire("q4_k", F, H, seed=2, device=dev, lead=(E,))
+    wd = random_wire("q4_k", H, F, seed=3, device=dev, lead=(E,))
+    xs, routes, ranks = [], [], []
+    for r in range(W):
+        g = torch.Generator(device="cpu").manual_seed(300 + r)
+        xs.append(torch.randn(T, H, generator=g).to(torch.bfloat16).to(dev))
+        routes.append(route_topk(torch.randn(T, E, generator=g).to(dev), k))
+        lo, hi = shard_bounds(E, r, W)
+        ranks.append(GatheredExpertParallel(T, H, k, E, fuse_gate_up(wg[lo:hi], wu[lo:hi]), wd[lo:hi].contiguous(),
+                                            "q4_k", rank=r, world=W, reduce_dtype=torch.bfloat16))
+        assert ranks[r].block_ok
+    gathered = torch.cat([ranks[r].pack(xs[r], *routes[r]) for r in range(W)])
+    slots = [torch.full((W, T, H), float("nan"), dtype=torch.bfloat16, device=dev) for _ in range(W)]
+    ptrs = torch.tensor([t.data_ptr() for t in slots], dtype=torch.int64, device=dev)
+    rank_lo = torch.tensor([shard_bounds(E, r, W)[0] for r in range(W)] + [E], dtype=torch.int32, device=dev)
+    for r in range(W):
+        ep = ranks[r]
+        ep.recv.copy_(gathered)
+        R = T + ep.pad_rows
+        meta = ep._meta(ep.recv, R)
+        ids = meta[:, :T * k].reshape(W * T * k) - ep.lo
+        probs = meta[:, T * k:2 * T * k].reshape(W * T * k).view(torch.float32)
+        assert moe_swiglu_block(ep.recv, ep.w_gate_up, ep.w_down, "q4_k", ids.view(W * T, k), probs.view(W * T, k),
+                                token_rows=ep.tok_rows, tokens=W * T, scatter=(ptrs, torch.bfloat16, r, T)) is True
+    some_nan = False
+    for r in range(W):
+        some_nan |= bool(torch.isnan(slots[r]).any())
+        y = moe_sum_slots(slots[r], routes[r][0], rank_lo, torch.bfloat16)
+        assert torch.isfinite(y.float()).all()
+        want = moe_glu(xs[r], wg, wu, wd, "q4_k", *routes[r], fused=False).float()
+        assert float((y.float() - want).norm() / want.norm()) < 4e-3   # two bf16 partial sums instead of one float32 sum
+    assert some_nan   # with top-2 of 16 experts some tokens have no expert on one of the ranks
