@@ -50,7 +50,9 @@ constexpr int kBN = 128;
 constexpr int kBK = 64;
 // weight-tile ring: three stages (two next to a raw-block ring of a 256-column tile, which fills shared memory;
 // that combination was measured slower than per-thread loads and is not dispatched)
-__host__ __device__ constexpr int b_stages(int NB, bool RAW) { return (RAW && NB == 2) ? 2 : 3; }
+// KS: 64-deep K-steps per stage. KS = 2 (the 128 x 128 tile of small M): a stage is 128 deep, so every wait, fence,
+// arrive and commit is paid once per two K-steps - at small M those handshakes, not the tensor pipe, set the pace.
+__host__ __device__ constexpr int b_stages(int NB, bool RAW, int KS = 1) { return ((RAW && NB == 2) || KS == 2) ? 2 : 3; }
 // Eight producer warps, then the MMA issuer warp(s) and one TMA warp. A 128-row weight tile has two producer
 // threads per row (32 weights each per K-step), a 256-row tile one (sixteen producer warps were measured
 // slower: 0.55 against 0.71 of the tensor peak at M = 8192).
@@ -62,8 +64,8 @@ __host__ __device__ constexpr int producer_threads(int) { return 256; }
 __host__ __device__ constexpr int mma_warps(int MT) { return MT >= 2 ? 2 : 1; }
 __host__ __device__ constexpr int gemm_threads(int MT, int NB) { return producer_threads(NB) + 32 * (mma_warps(MT) + 1); }
 // activation-tile ring; the raw-block ring of the small-M kernels takes the room of four slots
-__host__ __device__ constexpr int a_slots(int MT, int NB, bool RAW = false) {
-  return NB == 2 ? (RAW ? 5 : 6) : (MT == 1 || RAW ? 4 : 8);
+__host__ __device__ constexpr int a_slots(int MT, int NB, bool RAW = false, int KS = 1) {
+  return KS == 2 ? 2 : (NB == 2 ? (RAW ? 5 : 6) : (MT == 1 || RAW ? 4 : 8));
 }
 constexpr int kTileBytes = 128 * 128;  // 128 rows x 64 16-bit elements
 
@@ -308,24 +310,26 @@ __device__ __forceinline__ void produce_w_q4k(const Q4kTileLoad& l, int kb, uint
 // each) - the next superblock is then requested one superblock (four K-steps) before its first use.
 __host__ __device__ constexpr int raw_depth(int NB) { return NB == 2 ? 2 : 4; }
 __host__ __device__ constexpr int raw_slot(int NB) { return 128 * NB * 144; }
-template <int C, int A, typename OT, int MT, int NB, bool FASTQ4, bool RAW = false>
+template <int C, int A, typename OT, int MT, int NB, bool FASTQ4, bool RAW = false, int KS = 1>
 __global__ void __launch_bounds__(gemm_threads(MT, NB), 1)
 gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
   constexpr int kProducerThreads = producer_threads(NB), kGemmThreads = gemm_threads(MT, NB);
   constexpr int kMmaWarp = kProducerThreads / 32, kMmaWarps = mma_warps(MT);
   static_assert(!RAW || FASTQ4, "raw ring: q4_k fast producer");
-  constexpr int kBStages = b_stages(NB, RAW), kRawDepth = raw_depth(NB), kRawSlot = raw_slot(NB);
+  static_assert(KS == 1 || (KS == 2 && MT == 1 && NB == 1), "128-deep stages: the 128 x 128 tile only");
+  constexpr int kBStages = b_stages(NB, RAW, KS), kRawDepth = raw_depth(NB), kRawSlot = raw_slot(NB);
   constexpr int kRawPieces = 128 * NB * 9;  // 16-byte pieces of one superblock of the tile's rows
   constexpr bool kHalf = std::is_same<OT, __half>::value;
-  constexpr int NA = a_slots(MT, NB, RAW);
+  constexpr int NA = a_slots(MT, NB, RAW, KS);
   constexpr int BN = kBN * NB;
-  constexpr int kBTile = NB * kTileBytes;
+  constexpr int kBTile = NB * kTileBytes;       // one 64-deep weight tile; a stage holds KS of them
+  constexpr int kBStage = KS * kBTile, kASlot = KS * kTileBytes;
   constexpr bool kIq = (C == IQ4_NL || C == IQ4_XS || C == IQ2_XXS);
   extern __shared__ __align__(1024) uint8_t gemm_smem[];
   // 1024-byte alignment of the tiles is what the 128B swizzle pattern assumes
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gemm_smem) + 1023) & ~(uintptr_t)1023);
   uint8_t* b_ring = tiles;                          // kBStages weight tiles
-  uint8_t* a_ring = tiles + kBStages * kBTile;      // NA activation tiles
+  uint8_t* a_ring = tiles + kBStages * kBStage;     // NA activation slots
   __shared__ uint64_t b_full[kBStages], b_empty[kBStages], a_full[NA], a_empty[NA], accum_bar;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
@@ -392,7 +396,7 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
       constexpr int kHalves = 256 * NB / kProducerThreads;  // and how many of them
       const uint8_t* wrow = wbase + (long long)min(n0 + wr, a.N - 1) * a.row_bytes;
       bool ok = true;
-      uint8_t* raw = a_ring + NA * kTileBytes;
+      uint8_t* raw = a_ring + NA * kASlot;
       const int nsb = KB >> 2;
       auto issue_sb = [&](int sbl) {  // one copy group per superblock, an empty one past the end
         if (sbl < nsb) {
@@ -423,7 +427,8 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
       {
       for (int it = 0; it < KB && (ok || RAW); it++) {
         const int kb = kb0 + it;
-        const int s = it % kBStages;
+        const int sti = it / KS, sub = it % KS;  // stage number and 64-deep part of it
+        const int s = sti % kBStages;
         if constexpr (RAW) {
           // Every producer passes every superblock barrier, also after a failed wait: nobody is left behind.
           if ((it & 3) == 0) {
@@ -432,17 +437,17 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
             if (it > 0) issue_sb((it >> 2) - 1 + kRawDepth);
           }
           KQ_TR(const long long c0 = clock64();)
-          if (ok && it >= kBStages) ok = mbar_wait(&b_empty[s], ((it / kBStages) & 1) ^ 1, abort_flag, 1);
+          if (ok && sub == 0 && sti >= kBStages) ok = mbar_wait(&b_empty[s], ((sti / kBStages) & 1) ^ 1, abort_flag, 1);
           KQ_TR(tr_wait += clock64() - c0;)
           if (!ok) continue;
         } else {
           KQ_TR(const long long c0 = clock64();)
-          if (it >= kBStages) ok = mbar_wait(&b_empty[s], ((it / kBStages) & 1) ^ 1, abort_flag, 1);
+          if (sub == 0 && sti >= kBStages) ok = mbar_wait(&b_empty[s], ((sti / kBStages) & 1) ^ 1, abort_flag, 1);
           KQ_TR(tr_wait += clock64() - c0;)
           if (!ok) break;
         }
         KQ_TR(const long long c1 = clock64();)
-        uint8_t* wdst = b_ring + s * kBTile + wr * 128;
+        uint8_t* wdst = b_ring + s * kBStage + sub * kBTile + wr * 128;
         if constexpr (RAW) {
           const uint8_t* blk = raw + ((it >> 2) % kRawDepth) * kRawSlot + wr * 144;
           Q4kTileLoad l;
@@ -470,9 +475,11 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
             else produce_w_generic<C, A>(wrow, kb, a.K, wdst, wr, hh, tabs);
           }
         }
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&b_full[s]);
+        if (sub == KS - 1) {
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&b_full[s]);
+        }
         KQ_TR(tr_prod += clock64() - c1;)
       }
       }
@@ -574,31 +581,32 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
       bool ok = true;
       KQ_TR(long long tr_b = 0; long long tr_a = 0; const long long cm = clock64();)
       for (int kb = 0; kb < KB && ok; kb++) {  // kb counts this CTA's own K-steps
-        const int s = kb % kBStages;
+        const int sti = kb / KS, sub = kb % KS;
+        const int s = sti % kBStages;
         KQ_TR(const long long c0 = clock64();)
-        ok = mbar_wait(&b_full[s], (kb / kBStages) & 1, abort_flag, 2);
+        if (sub == 0) ok = mbar_wait(&b_full[s], (sti / kBStages) & 1, abort_flag, 2);
         KQ_TR(tr_b += clock64() - c0;)
         if (!ok) break;
-        const uint32_t bt = smem_u32(b_ring + s * kBTile);
+        const uint32_t bt = smem_u32(b_ring + s * kBStage + sub * kBTile);
         for (int h = w; h < mt_live && ok; h += kMmaWarps) {
-          const int t = kb * mt_live + h;
+          const int t = sti * mt_live + h;
           const int slot = t % NA;
           KQ_TR(const long long c2 = clock64();)
-          ok = mbar_wait(&a_full[slot], (t / NA) & 1, abort_flag, 16);
+          if (sub == 0) ok = mbar_wait(&a_full[slot], (t / NA) & 1, abort_flag, 16);
           KQ_TR(tr_a += clock64() - c2;)
           if (!ok) break;
           tc_fence_after();
           if (lane == 0) {
-            const uint32_t at = smem_u32(a_ring + slot * kTileBytes);
+            const uint32_t at = smem_u32(a_ring + slot * kASlot + sub * kTileBytes);
   #pragma unroll
             for (int j = 0; j < kBK / 16; j++)
               umma_f16(tmem_base + h * BN, umma_desc_sw128(at + j * 32), umma_desc_sw128(bt + j * 32), idesc,
                        (kb > 0 || j > 0) ? 1u : 0u);
-            umma_commit(&a_empty[slot]);  // the slot is free once these MMAs have read it
+            if (sub == KS - 1) umma_commit(&a_empty[slot]);  // the slot is free once these MMAs have read it
           }
           __syncwarp();
         }
-        if (ok && lane == 0) umma_commit(&b_empty[s]);
+        if (ok && sub == KS - 1 && lane == 0) umma_commit(&b_empty[s]);
         __syncwarp();
       }
       KQ_TR(if (lane == 0 && w == 0) { atomicAdd(&g_gemm_trace[0], (unsigned long long)tr_b); atomicAdd(&g_gemm_trace[1], (unsigned long long)tr_a); atomicAdd(&g_gemm_trace[2], (unsigned long long)(clock64() - cm)); })
@@ -610,7 +618,7 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
       bool ok = true;
       int t = 0;
       KQ_TR(long long tr_e = 0;)
-      for (int kb = 0; kb < KB && ok; kb++) {
+      for (int sti = 0; sti < KB / KS && ok; sti++) {  // one slot = the KS 64-deep boxes of a stage
         for (int h = 0; h < mt_live && ok; h++, t++) {
           const int slot = t % NA;
           KQ_TR(const long long c0 = clock64();)
@@ -618,8 +626,11 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
           KQ_TR(tr_e += clock64() - c0;)
           if (!ok) break;
           if (lane == 0) {
-            mbar_expect_tx(&a_full[slot], kTileBytes);
-            tma_load_2d(a_ring + slot * kTileBytes, &tmap_x, (kb0 + kb) * kBK, m0 + h * 128, &a_full[slot]);
+            mbar_expect_tx(&a_full[slot], kASlot);
+  #pragma unroll
+            for (int sub = 0; sub < KS; sub++)
+              tma_load_2d(a_ring + slot * kASlot + sub * kTileBytes, &tmap_x, (kb0 + sti * KS + sub) * kBK, m0 + h * 128,
+                          &a_full[slot]);
           }
           __syncwarp();
         }
@@ -978,10 +989,10 @@ static cudaError_t make_x_map(CUtensorMap* map, const void* x, long long x_row_s
   return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
-template <int C, int A, typename OT, int MT, int NB, bool FASTQ4, bool RAW = false>
+template <int C, int A, typename OT, int MT, int NB, bool FASTQ4, bool RAW = false, int KS = 1>
 static cudaError_t launch_g(const GemmArgs& a, cudaStream_t st, int grid_y = 0, int ksplit = 1) {
-  auto kern = gemm_kernel<C, A, OT, MT, NB, FASTQ4, RAW>;
-  const size_t dyn = (size_t)(b_stages(NB, RAW) * NB + a_slots(MT, NB, RAW)) * kTileBytes + 1024 +
+  auto kern = gemm_kernel<C, A, OT, MT, NB, FASTQ4, RAW, KS>;
+  const size_t dyn = (size_t)(b_stages(NB, RAW, KS) * NB + a_slots(MT, NB, RAW, KS)) * KS * kTileBytes + 1024 +
                      (RAW ? raw_depth(NB) * raw_slot(NB) : 0);
   static bool attr_set[16] = {};
   int dev = 0;
@@ -1051,12 +1062,16 @@ static cudaError_t launch_shape(bool out_half, const GemmArgs& a, cudaStream_t s
   // raw-block ring: whole superblocks per slice and rows that are whole numbers of 16 bytes
   static const bool no_raw = std::getenv("KQ_GEMM_NO_RAW") != nullptr;  // A/B lever
   const bool raw_ok = FASTQ4 && !no_raw && (a.K % 256) == 0 && ((a.K / 256) % ksplit) == 0 && (a.row_bytes % 16) == 0;
+  // 128-deep stages for the 128 x 128 tile: every CTA's K-steps must pair up
+  static const bool no_deep = std::getenv("KQ_GEMM_NO_DEEP") != nullptr;  // A/B lever
+  const bool deep_ok = !no_deep && (((a.K + kBK - 1) / kBK / ksplit) % 2) == 0;
 #define KQ_TILE(OT)                                                          \
   do {                                                                       \
     if (mt == 22) return launch_g<C, A, OT, 2, 2, FASTQ4>(a, st);             \
     if (mt == 4) return launch_g<C, A, OT, 4, 1, FASTQ4>(a, st);              \
     if constexpr (FASTQ4) {                                                  \
       if (raw_ok && mt == 2) return launch_g<C, A, OT, 2, 1, true, true>(a, st, 0, ksplit); \
+      if (raw_ok && deep_ok) return launch_g<C, A, OT, 1, 1, true, true, 2>(a, st, 0, ksplit); \
       if (raw_ok) return launch_g<C, A, OT, 1, 1, true, true>(a, st, 0, ksplit);            \
     }                                                                        \
     if (mt == 2) return launch_g<C, A, OT, 2, 1, FASTQ4>(a, st, 0, ksplit);   \
