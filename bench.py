@@ -507,6 +507,16 @@ def parity_n(dev, rank, world, W0, x_dev, y0):
     y_peer = ep(x, ids, probs).clone()
     ep.close()
     del ep
+    y_pp = None
+    from mlx_kquant_b200.moe import PeerPipelinedExpertParallel
+    try:   # each of the two slices must reach the one-call block's sizes (the same answer on every rank)
+        ep = PeerPipelinedExpertParallel(T, H, k, E, wgu, wd, "q4_k", chunks=2)
+    except ValueError:
+        ep = None
+    if ep is not None:
+        y_pp = ep(x, ids, probs).clone()
+        ep.close()
+        del ep
 
     def gather(t):
         parts = [torch.empty_like(t) for _ in range(world)]
@@ -519,12 +529,15 @@ def parity_n(dev, rank, world, W0, x_dev, y0):
         all_x, all_ids, all_p = gather(x), gather(ids), gather(probs)
         all_a, all_g, all_pl = gather(y_a2a), gather(y_gat.to(y_a2a.dtype)), gather(y_pip.to(y_a2a.dtype))
         all_pe = gather(y_peer.to(y_a2a.dtype))
+        all_pp = gather(y_pp.to(y_a2a.dtype)) if y_pp is not None else None
         if rank == 0:
             for r in range(world):
                 ref = moe_glu(all_x[r], None, None, all_wd, "q4_k", all_ids[r], all_p[r], w_gate_up=all_wgu).float()
                 for name, got, bar in (("all-to-all", all_a[r], 6e-3), ("gathered", all_g[r], 6e-3),
                                        ("pipelined, bfloat16 sums", all_pl[r], 8e-3),
-                                       ("peer-memory, bfloat16 slots", all_pe[r], 8e-3)):
+                                       ("peer-memory, bfloat16 slots", all_pe[r], 8e-3),
+                                       ("peer-memory, copy-engine gather over two slices",
+                                        all_pp[r] if all_pp is not None else all_pe[r], 8e-3)):
                     err = float((got.float() - ref).norm() / ref.norm())
                     if not err <= bar:
                         problems.append(f"MoE {name} form, rank {r}: rel error {err:.2e} against the single-GPU block")
@@ -746,6 +759,21 @@ def moe_ep_cell(dev, rank, world):
         if Tg == 4096:
             cell["local_stage_with_peer_stores_ms"] = timed_part(lambda: ep._graph.replay())
         out[f"moe_glu_q4k_ep{world}_peer_T{Tg}_per_rank"] = cell
+        ep.close()
+        del ep
+        torch.cuda.empty_cache()
+
+    # ... and with the gather moved by the copy engines beside the products of the other token slice
+    from mlx_kquant_b200.moe import PeerPipelinedExpertParallel
+
+    for chunks in (2, 4):
+        try:
+            ep = PeerPipelinedExpertParallel(T, H, k, E, wgu, wd, "q4_k", chunks=chunks)
+        except ValueError:
+            continue
+        ms = timed_ep(ep, x, ids, probs, 5)
+        out[f"moe_glu_q4k_ep{world}_peer_pipelined{chunks}_T{T}_per_rank"] = {"tokens_per_s": world * T / (ms * 1e-3),
+                                                                              "ms": ms}
         ep.close()
         del ep
         torch.cuda.empty_cache()

@@ -252,6 +252,8 @@ KQ_API int kq_peer_buffer_create(size_t bytes, void** ptr, unsigned char* handle
 KQ_API int kq_peer_buffer_open(const unsigned char* handle64, void** ptr);
 KQ_API int kq_peer_buffer_close(void* ptr);
 KQ_API int kq_peer_buffer_destroy(void* ptr);
+/* One asynchronous device-to-device copy on `stream` (copy engines, no SM); dst may be a peer's buffer. */
+KQ_API int kq_peer_copy_async(void* dst, const void* src, size_t bytes, void* stream);
 KQ_API int kq_moe_router_topk(const void* logits, int dtype, long long T, int E, int top_k, int norm_topk_prob,
                               int shared_gate, const float* per_expert_scale, const float* bias, const char* scoring,
                               float scale, uint32_t* indices, float* scores, void* stream);

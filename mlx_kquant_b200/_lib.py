@@ -76,6 +76,7 @@ SIGNATURES = {
     "kq_peer_buffer_open": (C.c_int, [C.c_void_p, C.c_void_p]),
     "kq_peer_buffer_close": (C.c_int, [C.c_void_p]),
     "kq_peer_buffer_destroy": (C.c_int, [C.c_void_p]),
+    "kq_peer_copy_async": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "kq_gather_qmm_workspace_bytes": (C.c_size_t, [C.c_longlong, C.c_int, C.c_int, C.c_int]),
     "kq_gather_qmm": (C.c_int, [C.c_void_p, C.c_int, C.c_longlong, C.c_int, C.c_int, C.c_void_p, C.c_int,
                                 C.c_longlong, C.c_size_t, C.c_int, C.c_char_p, C.c_void_p, C.c_void_p,

@@ -644,6 +644,16 @@ int kq_peer_buffer_destroy(void* ptr) {
   return KQ_OK;
 }
 
+int kq_peer_copy_async(void* dst, const void* src, size_t bytes, void* stream) {
+  if (bytes == 0) return KQ_OK;
+  if (dst == nullptr || src == nullptr) return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.peer_copy_async] null pointer.");
+  // one copy per call, device to device (the destination may be another GPU's memory opened with
+  // kq_peer_buffer_open): the copy engines move it, no SM is involved
+  cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return cuda_fail("peer_copy_async", e);
+  return KQ_OK;
+}
+
 int kq_moe_router_topk(const void* logits, int dtype, long long T, int E, int top_k, int norm_topk_prob, int shared_gate,
                        const float* per_expert_scale, const float* bias, const char* scoring, float scale,
                        uint32_t* indices, float* scores, void* stream) {

@@ -537,6 +537,18 @@ class PeerBuffers:
                 self.ptrs.append(p.value)
         dist.barrier(group=group)   # every rank has opened every buffer before anyone stores
 
+    def own_tensor(self, shape, dtype):
+        """This rank's buffer as a torch tensor (no copy; the buffer stays owned by this object)."""
+        n = 1
+        for d in shape:
+            n *= int(d)
+        n *= torch.empty((), dtype=dtype).element_size()
+
+        class _Raw:   # the CUDA array interface over the raw pointer
+            __cuda_array_interface__ = {"shape": (n,), "typestr": "|u1", "data": (self.own, False), "version": 2}
+
+        return torch.as_tensor(_Raw(), device=self.device).view(dtype).view(*shape)
+
     def close(self):
         import torch.distributed as dist
 
@@ -563,7 +575,7 @@ class PeerExpertParallel(GatheredExpertParallel):
     (`moe_swiglu_block`) sizes; slots of `reduce_dtype` (default: the activation dtype). close() is collective."""
 
     def __init__(self, T, H, k, n_experts, w_gate_up, w_down, kquant_type, dtype=torch.bfloat16, group=None, *,
-                 reduce_dtype=None):
+                 reduce_dtype=None, copy_engine_gather=False):
         from .dist import shard_bounds
 
         reduce_dtype = reduce_dtype or dtype
@@ -581,10 +593,38 @@ class PeerExpertParallel(GatheredExpertParallel):
                                     dtype=torch.int32, device=dev)
         self.flag = torch.zeros(1, dtype=torch.int32, device=dev)
         self.out_dtype = dtype
+        # copy_engine_gather: the gathered buffer is peer memory too, and every rank pushes its packed rows into
+        # all ranks' buffers with asynchronous copies (copy engines over NVLink: no SM) instead of an all-gather
+        self.recv_buffers = None
+        if copy_engine_gather:
+            rows = T + self.pad_rows
+            self.recv_buffers = PeerBuffers(self.world * rows * H * self.send.element_size(), dev, group)
+            self.recv = self.recv_buffers.own_tensor((self.world * rows, H), dtype)
+            self.recv.zero_()
+            self.flag_in = torch.zeros(1, dtype=torch.int32, device=dev)
 
     def close(self):
         self._graph = None
         self.buffers.close()
+        if self.recv_buffers is not None:
+            self.recv = None
+            self.recv_buffers.close()
+
+    def push(self):
+        """Copy-engine form of the all-gather: this rank's packed rows into every rank's gathered buffer, then a
+        one-element collective - once it completes here, every rank's rows have landed here."""
+        import torch.distributed as dist
+
+        nbytes = self.send.numel() * self.send.element_size()
+        st = torch.cuda.current_stream(self.send.device).cuda_stream
+        L = _lib.lib()
+        for r in range(self.world):
+            _lib.check(L.kq_peer_copy_async(self.recv_buffers.ptrs[r] + self.rank * nbytes, self.send.data_ptr(), nbytes, st))
+        dist.all_reduce(self.flag_in, group=self.group)
+
+    def finish(self, expert_ids):
+        return moe_sum_slots(self.buffers.own, expert_ids, self.rank_lo, self.out_dtype,
+                             shape=(self.world, self.T, self.H), dtype=self.slot_dtype)
 
     def local_stage(self):
         T, k, W = self.T, self.k, self.world
@@ -608,8 +648,59 @@ class PeerExpertParallel(GatheredExpertParallel):
         # every rank's stores into this rank's slots are complete once every rank has joined this collective
         # (it is queued behind the local stage on each rank's stream)
         dist.all_reduce(self.flag, group=self.group)
-        return moe_sum_slots(self.buffers.own, expert_ids, self.rank_lo, self.out_dtype,
-                             shape=(self.world, self.T, self.H), dtype=self.slot_dtype)
+        return self.finish(expert_ids)
+
+
+class PeerPipelinedExpertParallel:
+    """PeerExpertParallel over `chunks` token slices with the gather moved by the copy engines: while the expert
+    products of slice c run, the rows of slice c + 1 travel over NVLink without taking an SM from the tile
+    kernel (NCCL's all-gather beside it costs more than it hides). Per step: pack all slices; on a side
+    stream push slice after slice (peer copies + a one-element collective that says "everybody's rows are
+    here"); on the main stream, per slice, wait for its rows and replay its local stage (whose weighted sum
+    stores into the owners' slots); one collective after the last slice says "all stores have landed"; the
+    slot sums. close() is collective."""
+
+    def __init__(self, T, H, k, n_experts, w_gate_up, w_down, kquant_type, dtype=torch.bfloat16, group=None, *,
+                 chunks=2, reduce_dtype=None):
+        if T % chunks:
+            raise ValueError("[mlx_kquant.moe] T must be a multiple of the number of chunks.")
+        self.T, self.chunks, self.group = T, chunks, group
+        self.parts = [PeerExpertParallel(T // chunks, H, k, n_experts, w_gate_up, w_down, kquant_type, dtype, group,
+                                         reduce_dtype=reduce_dtype, copy_engine_gather=True) for _ in range(chunks)]
+        dev = w_down.device
+        self.side = torch.cuda.Stream(device=dev)
+        self.events = [torch.cuda.Event() for _ in range(chunks)]
+        self.flag = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def capture(self):
+        for p in self.parts:
+            p.capture()
+
+    def close(self):
+        for p in self.parts:
+            p.close()
+
+    def __call__(self, x, expert_ids, expert_probs):
+        import torch.distributed as dist
+
+        n = self.T // self.chunks
+        main = torch.cuda.current_stream(x.device)
+        for c, p in enumerate(self.parts):
+            sl = slice(c * n, (c + 1) * n)
+            p.pack(x[sl], expert_ids[sl], expert_probs[sl])
+        self.side.wait_stream(main)
+        with torch.cuda.stream(self.side):
+            for c, p in enumerate(self.parts):
+                p.push()
+                self.events[c].record(self.side)
+        for c, p in enumerate(self.parts):
+            main.wait_event(self.events[c])
+            if p._graph is not None:
+                p._graph.replay()
+            else:
+                p.local_stage()
+        dist.all_reduce(self.flag, group=self.group)   # every rank's stores into the slots have landed
+        return torch.cat([p.finish(expert_ids[c * n:(c + 1) * n]) for c, p in enumerate(self.parts)])
 
 
 class PipelinedExpertParallel:

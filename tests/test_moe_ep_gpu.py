@@ -64,6 +64,21 @@ def _worker(rank, world, port, q):
                 err = max(err, e1)
             else:
                 err_slots = e1
+        # two token slices, rows pushed by the copy engines while the other slice multiplies
+        from mlx_kquant_b200.moe import PeerPipelinedExpertParallel
+        T2 = 2 * T
+        x2 = torch.randn(T2, H, generator=g).to(torch.bfloat16).to(dev)
+        ids2, probs2 = route_topk(torch.randn(T2, E, generator=g).to(dev), k)
+        want2 = moe_glu(x2, wg, wu, wd, "q4_k", ids2, probs2, fused=False).float()
+        pp = PeerPipelinedExpertParallel(T2, H, k, E, fuse_gate_up(wg[lo:hi], wu[lo:hi]), wd[lo:hi].contiguous(), "q4_k",
+                                         chunks=2)
+        e2 = float((pp(x2, ids2, probs2).float() - want2).norm() / want2.norm())
+        pp.capture()
+        for _ in range(3):
+            e2 = max(e2, float((pp(x2, ids2, probs2).float() - want2).norm() / want2.norm()))
+        torch.cuda.synchronize()
+        pp.close()
+        err_slots = max(err_slots, e2)
         q.put((rank, err, err_slots))
     finally:
         dist.destroy_process_group()
