@@ -74,7 +74,7 @@ __device__ int g_kq_device_error = 0;
 // cycles summed over CTAs: [0] MMA warp waiting for weight tiles, [1] for activation tiles, [2] MMA loop,
 // [3] loader waiting for free slots, [4] producer (thread 0) waiting for free stages, [5] producing, [6] CTAs,
 // [7] epilogue
-__device__ unsigned long long g_gemm_trace[8];
+__device__ unsigned long long g_gemm_trace[12];  // [8] CTA lifetime per tile, [9] start of the tile to the first K-step
 #define KQ_TR(...) __VA_ARGS__
 #else
 #define KQ_TR(...)
@@ -364,6 +364,7 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
       wbase += (long long)t.expert * a.w_expert_stride;
     }
     const int mt_live = min(MT, (m_end - m0 + 127) / 128);  // activation tiles of this CTA that hold rows
+    KQ_TR(const long long c_tile = clock64();)
     // Every tile starts from freshly initialised barriers (phase 0): nothing is in flight between tiles - the
     // loader has waited for its last loads, the issuers' MMAs have completed, the epilogue has stored.
     if (threadIdx.x == 0) {
@@ -423,7 +424,7 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
       constexpr bool kQ6Pre = (C == Q6_K && A == 8 && NB == 1);  // 8-byte aligned rows, two threads per row
       Q6kTileLoad cur6{};
       if constexpr (kQ6Pre) cur6 = q6k_tile_load(wrow, kb0, hh0);
-      KQ_TR(long long tr_wait = 0; long long tr_prod = 0;)
+      KQ_TR(long long tr_wait = 0; long long tr_prod = 0; const long long c_loop = clock64();)
       {
       for (int it = 0; it < KB && (ok || RAW); it++) {
         const int kb = kb0 + it;
@@ -483,10 +484,11 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
         KQ_TR(tr_prod += clock64() - c1;)
       }
       }
-      KQ_TR(if (tid == 0) { atomicAdd(&g_gemm_trace[4], (unsigned long long)tr_wait); atomicAdd(&g_gemm_trace[5], (unsigned long long)tr_prod); atomicAdd(&g_gemm_trace[6], 1ull); })
+      KQ_TR(if (tid == 0) { atomicAdd(&g_gemm_trace[4], (unsigned long long)tr_wait); atomicAdd(&g_gemm_trace[5], (unsigned long long)tr_prod); atomicAdd(&g_gemm_trace[6], 1ull); atomicAdd(&g_gemm_trace[9], (unsigned long long)(c_loop - c_tile)); })
       // ================= epilogue =================
       KQ_TR(const long long ce = clock64();)
       if (ok) ok = mbar_wait(&accum_bar, 0, abort_flag, 4);
+      KQ_TR(if (tid == 0) atomicAdd(&g_gemm_trace[10], (unsigned long long)(clock64() - ce));)
       if (ok) {
         tc_fence_after();
         const int lq = warp & 3;                   // TMEM lane quarter this warp may read
@@ -551,21 +553,37 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
             }
           }
           asm volatile("bar.sync 2, %0;\n" ::"n"(kProducerThreads) : "memory");
+          KQ_TR(if (tid == 0) atomicAdd(&g_gemm_trace[11], (unsigned long long)(clock64() - ce));)
           const int rows_live = min(m_end - m0, mt_live * 128);
           constexpr int kRowsPerPass = 32 / kChunks;  // 1 (256 columns) or 2 (128 columns) rows per warp instruction
           const int chunk = lane % kChunks;
           const int col = n0 + chunk * 8;
           OT* ybase = static_cast<OT*>(a.y);
-          for (int r = warp * kRowsPerPass + lane / kChunks; r < rows_live; r += (kProducerThreads / 32) * kRowsPerPass) {
-            const long long orow = a.yrow ? a.yrow[m0 + r] : (long long)(m0 + r);
+          // Output rows come from a table in grouped mode. A load per row inside the loop would put a global-memory
+          // round trip before every store (measured: 12 k of a tile's 18 k epilogue cycles), so lane i fetches the
+          // rows of pass i up front (at most 32 passes for every tile shape) and the passes read them by shuffle.
+          constexpr int kPassRows = (kProducerThreads / 32) * kRowsPerPass;
+          const int passes = (rows_live + kPassRows - 1) / kPassRows;
+          const int sub = lane / kChunks;  // which of the pass's rows of this warp (kRowsPerPass = 2) the lane stores
+          long long mine0 = 0, mine1 = 0;
+          {
+            const int r0 = warp * kRowsPerPass + lane * kPassRows;
+            if (r0 < rows_live) mine0 = a.yrow ? (long long)a.yrow[m0 + r0] : (long long)(m0 + r0);
+            if (kRowsPerPass == 2 && r0 + 1 < rows_live) mine1 = a.yrow ? (long long)a.yrow[m0 + r0 + 1] : (long long)(m0 + r0 + 1);
+          }
+          for (int i = 0; i < passes; i++) {
+            const long long o0 = __shfl_sync(0xffffffffu, mine0, i), o1 = __shfl_sync(0xffffffffu, mine1, i);
+            const int r = warp * kRowsPerPass + sub + i * kPassRows;
+            if (r >= rows_live) continue;
+            const long long orow = sub ? o1 : o0;
             const uint4 q = *reinterpret_cast<const uint4*>(stage + r * kRowBytes + ((chunk ^ (r & (kChunks - 1))) << 4));
             OT* yp = ybase + orow * a.y_row_stride + col;
             if (col + 8 <= a.N && (reinterpret_cast<uintptr_t>(yp) & 15) == 0) {
               *reinterpret_cast<uint4*>(yp) = q;
             } else {
               const OT* qe = reinterpret_cast<const OT*>(&q);
-              for (int i = 0; i < 8; i++)
-                if (col + i < a.N) yp[i] = qe[i];
+              for (int e = 0; e < 8; e++)
+                if (col + e < a.N) yp[e] = qe[e];
             }
           }
         }
@@ -686,6 +704,7 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
     // ================= end of the tile =================
     tc_fence_before();
     __syncthreads();
+    KQ_TR(if (threadIdx.x == 0) atomicAdd(&g_gemm_trace[8], (unsigned long long)(clock64() - c_tile));)
     if (a.tiles == nullptr || tile + (int)gridDim.y >= n_list || abort_s != 0) break;
   }  // tile loop
 
@@ -1246,7 +1265,7 @@ int* device_error_word() {
 extern "C" __attribute__((visibility("default"))) int kq_debug_gemm_trace(unsigned long long* out, int clear) {
   cudaMemcpyFromSymbol(out, g_gemm_trace, sizeof(g_gemm_trace));
   if (clear) {
-    const unsigned long long z[8] = {};
+    const unsigned long long z[12] = {};
     cudaMemcpyToSymbol(g_gemm_trace, z, sizeof(z));
   }
   return 0;
