@@ -205,3 +205,23 @@ def test_stream_keyword_waits_for_the_current_stream():
         ref = kq.quantized_matmul(host.cuda(), wire, None, "q4_k")
         assert torch.equal(y, ref)
         assert torch.equal(d, kq.dequantize(wire, None, "q4_k", torch.float16))
+
+
+@pytest.mark.parametrize("M,dt", [(17, "f16"), (100, "bf16"), (300, "bf16"), (700, "f16")])
+def test_q6k_rows_on_8_byte_boundaries(oracle, M, dt):
+    """K a multiple of 1024: q6_k rows start on 8-byte boundaries and the tile kernel's producer fetches its bytes
+    a K-step ahead through aligned windows (every tile shape, ragged N, and a weight pointer that is only 8-byte
+    aligned, which must fall back to the byte-wise path)."""
+    rng = np.random.default_rng(61)
+    N, K = 300, 2048
+    wire = mint_wire("q6_k", rng.normal(0, 0.02, (N, K)).astype(np.float32))
+    x, store = x_to_torch(rng.normal(0, 1, (M, K)).astype(np.float32), dt)
+    wd = torch.from_numpy(wire).cuda()
+    y = kq.quantized_matmul(x, wd, None, "q6_k")
+    ref = fp64_ref(oracle, store, dt, wire, "q6_k")
+    check(y_to_f32(y), ref, dt)
+    if M == 100:
+        off = torch.empty(wire.size + 8, dtype=torch.uint8, device="cuda")
+        shifted = off[8:].view(N, -1)
+        shifted.copy_(wd)
+        check(y_to_f32(kq.quantized_matmul(x, shifted, None, "q6_k")), ref, dt)

@@ -352,3 +352,27 @@ def test_block_with_more_tiles_than_the_grid_cap():
         ref = (d.float() * probs[rows]).to(torch.bfloat16)
         err = float((y[rows].float() - ref.float()).norm() / ref.float().norm())
         assert err < 4e-3, (e, err)
+
+
+def test_block_q6k_rows_on_8_byte_boundaries():
+    """The grouped tile kernel with the q6_k producer that needs 8-byte aligned rows (H and F multiples of 1024)."""
+    from mlx_kquant_b200.moe import moe_swiglu_block
+
+    E, H, F, k, T = 4, 1024, 1024, 2, 320
+    wgu, wd = _block_case("q6_k", E, H, F, 93)
+    g = torch.Generator(device="cuda").manual_seed(94)
+    x = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+    ids, probs = route_topk(torch.randn(T, E, device="cuda", generator=g), k)
+    y = moe_swiglu_block(x, wgu, wd, "q6_k", ids, probs)
+    assert y is not None
+    ref = torch.zeros(T, H, dtype=torch.float64, device="cuda")
+    bf = lambda t: t.float().to(torch.bfloat16).double()
+    import mlx_kquant_b200 as kq
+    for e in range(E):
+        tok, slot = torch.nonzero(ids == e, as_tuple=True)
+        Wgu = kq.dequantize(wgu[e], None, "q6_k", torch.float32).double()      # bit-exact against the oracle elsewhere
+        Wd = kq.dequantize(wd[e], None, "q6_k", torch.float32).double()
+        gu = bf(x[tok].double() @ Wgu.T)
+        h = bf(torch.nn.functional.silu(gu[:, :F].float()).double() * gu[:, F:])
+        ref.index_add_(0, tok, bf(h @ Wd.T) * probs[tok, slot].double()[:, None])
+    assert float((y.double() - ref).norm() / ref.norm()) < 6e-3
