@@ -570,10 +570,11 @@ int kq_moe_swiglu_block_scatter(const void* x, int x_dtype, long long T, int H, 
                                 size_t down_row_bytes, int n_experts, const char* kquant_type, const uint32_t* indices,
                                 const float* scores, int top_k, void* const* slot_ptrs, int slot_dtype, int my_rank,
                                 long long tokens_per_rank, void* workspace, size_t workspace_bytes, void* stream) {
-  if (slot_ptrs == nullptr || tokens_per_rank <= 0 || my_rank < 0 || T % (tokens_per_rank > 0 ? tokens_per_rank : 1) != 0)
+  if (slot_ptrs == nullptr || tokens_per_rank <= 0 || my_rank < 0 || T % (tokens_per_rank > 0 ? tokens_per_rank : 1) != 0 ||
+      (long long)my_rank >= T / (tokens_per_rank > 0 ? tokens_per_rank : 1))
     return fail(KQ_ERR_INVALID_ARGUMENT,
-                "[mlx_kquant.moe_swiglu_block_scatter] slot_ptrs must be a device array of one buffer per rank and T a "
-                "whole number of tokens_per_rank.");
+                "[mlx_kquant.moe_swiglu_block_scatter] slot_ptrs must be a device array of one buffer per rank, T a "
+                "whole number of tokens_per_rank and my_rank one of the T / tokens_per_rank ranks.");
   if (slot_dtype != x_dtype && slot_dtype != KQ_F32)
     return fail(KQ_ERR_INVALID_ARGUMENT, "[mlx_kquant.moe_swiglu_block_scatter] slots must have x's dtype or float32.");
   const kq::MoeScatter sc{slot_ptrs, my_rank, tokens_per_rank, slot_dtype == KQ_F32};

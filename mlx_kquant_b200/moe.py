@@ -528,13 +528,22 @@ class PeerBuffers:
             handles = [None] * self.world
             dist.all_gather_object(handles, bytes(handle), group=group)
             self.ptrs = []
-            for r, h in enumerate(handles):
-                if r == self.rank:
-                    self.ptrs.append(self.own)
-                    continue
-                p = C.c_void_p()
-                _lib.check(L.kq_peer_buffer_open((C.c_ubyte * 64).from_buffer_copy(h), C.byref(p)))
-                self.ptrs.append(p.value)
+            try:
+                for r, h in enumerate(handles):
+                    if r == self.rank:
+                        self.ptrs.append(self.own)
+                        continue
+                    p = C.c_void_p()
+                    _lib.check(L.kq_peer_buffer_open((C.c_ubyte * 64).from_buffer_copy(h), C.byref(p)))
+                    self.ptrs.append(p.value)
+            except Exception:
+                # give back what this rank holds; the other ranks will time out in the barrier below
+                for r, p in enumerate(self.ptrs):
+                    if r != self.rank:
+                        L.kq_peer_buffer_close(p)
+                L.kq_peer_buffer_destroy(self.own)
+                self.ptrs = None
+                raise
         dist.barrier(group=group)   # every rank has opened every buffer before anyone stores
 
     def own_tensor(self, shape, dtype):
