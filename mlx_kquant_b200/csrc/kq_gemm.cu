@@ -496,13 +496,13 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
         const int cbeg = (warp >> 2) * kColSpan;
         if (gridDim.z > 1) {
           // split K: this CTA's partial tile goes to shared memory (the rings are idle now) as fp32
-          // [rows][128], 16-byte chunks XOR-swizzled by the row so that a warp's stores spread over the banks
-          if constexpr (NB == 1) {
+          // [rows][BN], 16-byte chunks XOR-swizzled by the row so that a warp's stores spread over the banks
+          if constexpr (MT * NB <= 2) {  // 128 x 128, 256 x 128 and 128 x 256 tiles: the partial tile fits the rings
   #pragma unroll 1
             for (int h = 0; h < mt_live; h++) {
               const int rl = h * 128 + lq * 32 + lane;
               const float rs = (a.row_scale && m0 + rl < m_end) ? a.row_scale[m0 + rl] : 1.f;
-              float* srow = reinterpret_cast<float*>(tiles) + rl * 128;
+              float* srow = reinterpret_cast<float*>(tiles) + rl * BN;
   #pragma unroll 1
               for (int c0 = cbeg; c0 < cbeg + kColSpan; c0 += 16) {
                 uint32_t v[16];
@@ -664,7 +664,7 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
 
     // ================= split K: the slices of a cluster meet through distributed shared memory =================
     if (gridDim.z > 1) {
-      if constexpr (NB == 1) {
+      if constexpr (MT * NB <= 2) {
         cg::cluster_group cluster = cg::this_cluster();
         tc_fence_before();
         cluster.sync();  // every slice's partial tile is in its shared memory
@@ -674,25 +674,28 @@ gemm_kernel(const GemmArgs a, const __grid_constant__ CUtensorMap tmap_x) {
   #pragma unroll
           for (int q = 0; q < 8; q++)
             peer[q] = q < S ? cluster.map_shared_rank(reinterpret_cast<float*>(tiles), q) : nullptr;
-          const int c = threadIdx.x & 31;  // 16-byte chunk = four columns
           for (int rl = z + S * (threadIdx.x >> 5); rl < mt_live * 128; rl += S * (kProducerThreads / 32)) {
             const int row = m0 + rl;
             if (row >= m_end) continue;
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   #pragma unroll
-            for (int q = 0; q < 8; q++) {
-              if (q < S) {
-                const float4 v = *reinterpret_cast<const float4*>(peer[q] + rl * 128 + 4 * (c ^ (rl & 31)));
-                acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
+            for (int part = 0; part < NB; part++) {
+              const int c = 32 * part + (threadIdx.x & 31);  // 16-byte chunk = four columns
+              float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  #pragma unroll
+              for (int q = 0; q < 8; q++) {
+                if (q < S) {
+                  const float4 v = *reinterpret_cast<const float4*>(peer[q] + rl * BN + 4 * (c ^ (rl & 31)));
+                  acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
+                }
               }
-            }
-            OT* yp = static_cast<OT*>(a.y) + (long long)row * a.y_row_stride + n0 + 4 * c;
-            const float f[4] = {acc.x, acc.y, acc.z, acc.w};
+              OT* yp = static_cast<OT*>(a.y) + (long long)row * a.y_row_stride + n0 + 4 * c;
+              const float f[4] = {acc.x, acc.y, acc.z, acc.w};
   #pragma unroll
-            for (int i = 0; i < 4; i++) {
-              if (n0 + 4 * c + i < a.N) {
-                if constexpr (kHalf) yp[i] = __float2half_rn(f[i]);
-                else yp[i] = __float2bfloat16_rn(f[i]);
+              for (int i = 0; i < 4; i++) {
+                if (n0 + 4 * c + i < a.N) {
+                  if constexpr (kHalf) yp[i] = __float2half_rn(f[i]);
+                  else yp[i] = __float2bfloat16_rn(f[i]);
+                }
               }
             }
           }
@@ -1024,7 +1027,7 @@ static cudaError_t launch_g(const GemmArgs& a, cudaStream_t st, int grid_y = 0, 
   alignas(64) CUtensorMap map;
   cudaError_t e = make_x_map(&map, a.x, a.x_row_stride, a.M, a.K);
   if (e != cudaSuccess) return e;
-  if (NB != 1) ksplit = 1;
+  if (MT * NB > 2) ksplit = 1;  // split K needs the fp32 partial tile in shared memory
   const dim3 grid((a.N + kBN * NB - 1) / (kBN * NB), grid_y > 0 ? grid_y : (a.M + 128 * MT - 1) / (128 * MT), ksplit);
   if (ksplit == 1) {
     kern<<<grid, gemm_threads(MT, NB), dyn, st>>>(a, map);
@@ -1050,32 +1053,49 @@ template <int C, int A, bool FASTQ4>
 static cudaError_t launch_shape(bool out_half, const GemmArgs& a, cudaStream_t st) {
   // Tile shapes (rows x columns): 512 x 128 amortises the weight dequantization best,
   // 256 x 256 halves the activation traffic out of L2; smaller ones fill the GPU at small M.
-  // KQ_GEMM_TILE=1|2|4|22 forces 128x128 / 256x128 / 512x128 / 256x256 (an A/B lever).
+  // KQ_GEMM_TILE=1|2|4|22|12 forces 128x128 / 256x128 / 512x128 / 256x256 / 128x256 (an A/B lever).
   const long long n_tiles = (a.N + kBN - 1) / kBN;
   int mt = a.M > 256 ? 4 : (a.M > 128 ? 2 : 1);
   if (mt == 4 && n_tiles * ((a.M + 511) / 512) < 148) mt = 2;
   // the q4_k producer is cheap enough to feed a 256-column tile; decode8-based producers are not
   if (FASTQ4 && a.M > 256) mt = 22;
   static const char* const tile_env = std::getenv("KQ_GEMM_TILE");  // A/B lever, read once per process
+  bool forced = false;
   if (const char* env = tile_env) {
     const int v = std::atoi(env);
-    if (v == 1 || v == 2 || v == 4 || v == 22) mt = v;
+    if (v == 1 || v == 2 || v == 4 || v == 22 || (v == 12 && FASTQ4 && a.M <= 128)) mt = v, forced = true;
   }
   // Few output tiles (small M on a matrix with few 128-row groups): split K over a cluster so that
   // the weights stream through more SMs. The slices must be equal: K-steps % ksplit == 0.
+  const int kb_total = (a.K + kBK - 1) / kBK;
+  auto pick_ksplit = [&](long long ctas) {
+    int ks = 1;
+    while (ks < 8 && ctas * ks * 2 <= 160 && kb_total % (ks * 2) == 0 && kb_total / (ks * 2) >= 4) ks *= 2;
+    if (FASTQ4)
+      while (ks > 1 && ((a.K / 256) % ks) != 0) ks >>= 1;  // q4_k producers work in whole superblocks
+    return ks;
+  };
   int ksplit = 1;
-  if (mt == 1 || mt == 2) {
-    const long long ctas = n_tiles * ((a.M + 128 * mt - 1) / (128 * mt));
-    const int kb_total = (a.K + kBK - 1) / kBK;
-    while (ksplit < 8 && ctas * ksplit * 2 <= 160 && kb_total % (ksplit * 2) == 0 && kb_total / (ksplit * 2) >= 4)
-      ksplit *= 2;
+  if (mt == 1 || mt == 2) ksplit = pick_ksplit(n_tiles * ((a.M + 128 * mt - 1) / (128 * mt)));
+  // Up to 128 rows, q4_k: a 128 x 256 tile makes a K-step's weights with one thread per weight row (64 weights,
+  // one scale decode) where the 128 x 128 tile uses two (32 each): measured ~1450 cycles per K-step against
+  // ~1250 for half the weights, plus ~12 k cycles per CTA and ~3 k per extra K slice. It is taken when the waves
+  // it needs, times that, come out shorter - and only with at most two K slices: clusters of four or eight
+  // 256-column CTAs were measured slower than the model says ([4096, 4096]: 24 us against 17 us).
+  if (FASTQ4 && a.M <= 128 && ((mt == 1 && !forced) || mt == 12)) {
+    const long long ctas12 = (a.N + 2 * kBN - 1) / (2 * kBN);
+    const int ks12 = pick_ksplit(ctas12);
+    auto cost = [&](long long ctas, int ks, double per_step) {
+      return (double)((ctas * ks + 147) / 148) * ((kb_total / ks) * per_step + 12000.0 + 3000.0 * (ks - 1));
+    };
+    if (mt == 12 || (ks12 <= 2 && cost(ctas12, ks12, 1450.0) < cost(n_tiles, ksplit, 1250.0))) {
+      mt = 12;
+      ksplit = ks12;
+    }
   }
-  if (FASTQ4)
-    while (ksplit > 1 && ((a.K / 256) % ksplit) != 0) ksplit >>= 1;  // q4_k producers work in whole superblocks
   static const char* const ksplit_env = std::getenv("KQ_GEMM_KSPLIT");  // A/B lever, read once per process
   if (const char* env = ksplit_env) {
     const int v = std::atoi(env);
-    const int kb_total = (a.K + kBK - 1) / kBK;
     if ((v == 1 || v == 2 || v == 4 || v == 8) && kb_total % v == 0 && (!FASTQ4 || (a.K / 256) % v == 0)) ksplit = v;
   }
   // raw-block ring: whole superblocks per slice and rows that are whole numbers of 16 bytes
@@ -1089,6 +1109,7 @@ static cudaError_t launch_shape(bool out_half, const GemmArgs& a, cudaStream_t s
     if (mt == 22) return launch_g<C, A, OT, 2, 2, FASTQ4>(a, st);             \
     if (mt == 4) return launch_g<C, A, OT, 4, 1, FASTQ4>(a, st);              \
     if constexpr (FASTQ4) {                                                  \
+      if (mt == 12) return launch_g<C, A, OT, 1, 2, true>(a, st, 0, ksplit);  \
       if (raw_ok && mt == 2) return launch_g<C, A, OT, 2, 1, true, true>(a, st, 0, ksplit); \
       if (raw_ok && deep_ok) return launch_g<C, A, OT, 1, 1, true, true, 2>(a, st, 0, ksplit); \
       if (raw_ok) return launch_g<C, A, OT, 1, 1, true, true>(a, st, 0, ksplit);            \
