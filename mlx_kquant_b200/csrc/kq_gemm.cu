@@ -932,7 +932,7 @@ static void launch_convert_t(const void* x, long long x_row_stride, int K, long 
                              const uint32_t* lhs, int lhs_div, int M, __half* o, float* row_scale, int* yrow,
                              const int* n_valid, bool glu, bool vec, cudaStream_t st) {
   const XT* xp = static_cast<const XT*>(x);
-  const unsigned gv = (unsigned)std::min<long long>((rows + 7) / 8, 148 * 24);
+  const unsigned gv = (unsigned)std::min<long long>((rows + 7) / 8, 148 * 64);  // strided beyond; a lower cap left a thin second pass
   if (glu) {
     if constexpr (sizeof(XT) == 2)
       convert_x_kernel<XT, true><<<gv, 256, 0, st>>>(xp, x_row_stride, K, o, row_scale, order, lhs, lhs_div, M, yrow,
