@@ -225,3 +225,15 @@ def test_q6k_rows_on_8_byte_boundaries(oracle, M, dt):
         shifted = off[8:].view(N, -1)
         shifted.copy_(wd)
         check(y_to_f32(kq.quantized_matmul(x, shifted, None, "q6_k")), ref, dt)
+
+
+@pytest.mark.parametrize("M,dt", [(20, "f16"), (128, "bf16")])
+def test_small_m_wide_tile_with_split_k_and_ragged_n(oracle, M, dt):
+    """Up to 128 rows on a matrix whose 128-column tiles would need a second wave: the 128 x 256 tile with K split
+    over a cluster of two (partial tiles reduced through distributed shared memory), N not a multiple of 256."""
+    rng = np.random.default_rng(71)
+    N, K = 20000, 1024
+    wire = mint_wire("q4_k", rng.normal(0, 0.02, (N, K)).astype(np.float32))
+    x, store = x_to_torch(rng.normal(0, 1, (M, K)).astype(np.float32), dt)
+    y = kq.quantized_matmul(x, torch.from_numpy(wire).cuda(), None, "q4_k")
+    check(y_to_f32(y), fp64_ref(oracle, store, dt, wire, "q4_k"), dt)
