@@ -1093,6 +1093,18 @@ static cudaError_t launch_shape(bool out_half, const GemmArgs& a, cudaStream_t s
       ksplit = ks12;
     }
   }
+  // 129 to 256 rows, q4_k: the same trade between the 256 x 128 tile (two producer threads per weight row, K may
+  // be split; ~1300 cycles per K-step) and the 256 x 256 tile (one thread per row, ~1620 cycles for twice the
+  // weights, no split): [28672, 8192] 184 -> 115 us.
+  if (FASTQ4 && a.M > 128 && a.M <= 256 && mt == 2 && !forced) {
+    auto cost = [&](long long ctas, int ks, double per_step) {
+      return (double)((ctas * ks + 147) / 148) * ((kb_total / ks) * per_step + 12000.0 + 3000.0 * (ks - 1));
+    };
+    if (cost((a.N + 2 * kBN - 1) / (2 * kBN), 1, 1620.0) < cost(n_tiles, ksplit, 1300.0)) {
+      mt = 22;
+      ksplit = 1;
+    }
+  }
   static const char* const ksplit_env = std::getenv("KQ_GEMM_KSPLIT");  // A/B lever, read once per process
   if (const char* env = ksplit_env) {
     const int v = std::atoi(env);
