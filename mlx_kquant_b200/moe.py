@@ -17,15 +17,15 @@ from .ops import gather_qmm
 
 
 def route_topk(router_logits: torch.Tensor, top_k: int) -> tuple[torch.Tensor, torch.Tensor]:
-    """(expert ids [T, k] int64, renormalised probabilities [T, k] float32)."""
+    """(expert ids [T, k] int32 - the index type every kernel here takes, so no conversion sits between the router
+    and the block - and renormalised probabilities [T, k] float32)."""
     if router_logits.is_cuda and router_logits.shape[1] <= 1024 and top_k <= 16:
-        idx, p = moe_router_topk(router_logits, top_k, True, shared_gate=False)
-        return idx.to(torch.int64), p
+        return moe_router_topk(router_logits, top_k, True, shared_gate=False)
     probs = torch.softmax(router_logits.float(), dim=-1)
     # a stable descending sort puts the lowest index first among equal probabilities
     order = torch.sort(probs, dim=-1, descending=True, stable=True)
     p, idx = order.values[:, :top_k], order.indices[:, :top_k]
-    return idx, p / p.sum(dim=-1, keepdim=True)
+    return idx.to(torch.int32), p / p.sum(dim=-1, keepdim=True)
 
 
 def swiglu(gate: torch.Tensor, up: torch.Tensor, row_expert: torch.Tensor | None = None,

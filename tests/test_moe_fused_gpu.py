@@ -162,7 +162,7 @@ def test_indices_written_by_the_preceding_launch(oracle):
             g.replay()
         stream.synchronize()
     ids, probs = route_topk(logits, k)
-    assert torch.equal(idx.long(), ids)
+    assert torch.equal(idx.long(), ids.long())
     want = moe_glu(x, wg, wu, wd, "q4_k", ids, probs)
     assert torch.equal(y, y_eager)
     assert torch.equal(y, want)
