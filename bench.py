@@ -18,7 +18,9 @@ value   device-resident: inputs already in HBM, the step is one CUDA-graph
         replay of the `layers` launches; CUDA events on the launching stream.
 e2e     the same step through the public op with HOST buffers: pinned-host x
         -> device copy, the launches, device -> pinned-host copy of the outputs,
-        all inside the timed region.
+        all inside the timed region. The read of step i's outputs runs on a second
+        stream beside the launches of step i + 1 (two output buffers), the last
+        step's read closes the region.
 extra   (N = 1) the other cells of the metric, each with its roofline fraction
         and a bounded CPU sample of the reference's own code: the headline
         shape at M = 8 and as a dependent chain (every launch consumes the
@@ -917,7 +919,8 @@ def run_b200(args):
     y_devs = [torch.empty(layers, M, N_ROWS, dtype=torch.float16, device=dev) for _ in range(2)]
     y_alls = [torch.empty(world, layers, M, N_ROWS, dtype=torch.float16, device=dev) for _ in range(2)] if world > 1 else None
     y_dev = y_devs[0]
-    y_host = torch.empty(layers, M, N_ROWS, dtype=torch.float16).pin_memory()
+    y_hosts = [torch.empty(layers, M, N_ROWS, dtype=torch.float16).pin_memory() for _ in range(2)]
+    y_host = y_hosts[0]
 
     from mlx_kquant_b200 import _lib
     L = _lib.lib()
@@ -940,20 +943,33 @@ def run_b200(args):
         parity = parity_n(dev, rank, world, W[0], x_dev, y_dev[0])
 
     # ---- device-resident arm: one CUDA graph of `layers` launches (one graph per output buffer)
-    def capture(yb, with_copies):
+    copy_stream = torch.cuda.Stream(dev)
+
+    def capture(b, with_copies):
+        """The step into output buffer b. End to end: the step's x comes from pinned host memory first; the
+        device-to-host read of the PRECEDING step's outputs (the other buffer) runs on a second stream beside this
+        step's launches, as a serving loop would overlap it - every step's result is still read inside the timed
+        region (the last one by finish_e2e below)."""
         gr = torch.cuda.CUDAGraph()
         with torch.cuda.stream(stream):
             with torch.cuda.graph(gr, stream=stream):
                 if with_copies:
+                    copy_stream.wait_stream(stream)
+                    with torch.cuda.stream(copy_stream):
+                        y_hosts[1 - b].copy_(y_devs[1 - b], non_blocking=True)
                     x_dev.copy_(x_host, non_blocking=True)
-                launch_all(stream, yb)
+                launch_all(stream, y_devs[b])
                 if with_copies:
-                    y_host.copy_(yb, non_blocking=True)
+                    stream.wait_stream(copy_stream)
         return gr
 
-    graphs = [capture(yb, False) for yb in y_devs]
+    graphs = [capture(b, False) for b in range(2)]
     # ---- end-to-end arm: H2D of x, the launches, D2H of y, captured as one graph of the public path
-    graphs_e2e = [capture(yb, True) for yb in y_devs]
+    graphs_e2e = [capture(b, True) for b in range(2)]
+
+    def finish_e2e():
+        b = (state["i"] - 1) & 1     # the last step's buffer: its read has not been issued yet
+        y_hosts[b].copy_(y_devs[b], non_blocking=True)
 
     # At N > 1 every step ends with the all-gather of its output shards. It is issued asynchronously and
     # the buffer it reads is not written again before it has finished, so it overlaps the next step.
@@ -980,7 +996,7 @@ def run_b200(args):
     def step_e2e():
         run_step(graphs_e2e)
 
-    def timed(fn, steps, warmup):
+    def timed(fn, steps, warmup, finish=None):
         with torch.cuda.stream(stream):
             for _ in range(warmup):
                 fn()
@@ -993,6 +1009,8 @@ def run_b200(args):
             e0.record(stream)
             for _ in range(steps):
                 fn()
+            if finish is not None:
+                finish()
             drain()                      # the timed region ends when the last all-gather has landed
             e1.record(stream)
             stream.synchronize()
@@ -1010,7 +1028,10 @@ def run_b200(args):
     if rank == 0:
         sampler.start()
     ms_dev = timed(step_device, args.steps, max(3, args.warmup))
-    ms_e2e = timed(step_e2e, args.steps, max(3, args.warmup))
+    ms_e2e = timed(step_e2e, args.steps, max(3, args.warmup), finish_e2e)
+    # the read of a step's outputs arrives intact: the last two steps' host copies equal the device buffers
+    for b in range(2):
+        assert torch.equal(y_hosts[b], y_devs[b].cpu()), "end-to-end arm: host copy differs from the device result"
     clocks = sampler.stop() if rank == 0 else None
 
     step_bytes = layers * MATRIX_BYTES * world
@@ -1053,6 +1074,7 @@ def run_b200(args):
                        "cold_cache": f"{layers} distinct weight matrices per step = {layers * MATRIX_BYTES / 1e6:.0f} MB > 126 MB L2",
                        "parallelism": "single GPU" if world == 1 else f"column shard x{world} + NCCL all-gather of outputs, overlapped with the next step"},
             "e2e": {"value": e2e, "unit": "GB/s", "ms_per_step": ms_e2e / args.steps,
+                    "overlap": "device-to-host read of step i beside the launches of step i + 1; all reads inside the timed region",
                     "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2},
             "gpu_launches": args.steps * layers,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
