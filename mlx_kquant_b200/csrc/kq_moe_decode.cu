@@ -92,6 +92,7 @@ struct GluArgs {
   void* y;                  // [T * R, F]
   int act;
   float limit;
+  int tiles_per_cta;        // grouped kernel only: consecutive 16-feature tiles a CTA walks
 };
 
 // shared memory: gate tile | up tile (4 groups each) | planes 2 K | XS K / 32 | SX K / 256 (padded) | red 8 x 32 | mbar
@@ -337,12 +338,17 @@ __device__ __forceinline__ float md_pick4(const float (&v)[4], int t) {
 }
 
 // shared memory: gate tile | up tile | planes 4 x 2 K | XS 4 x K / 32 | SX 4 x padded K / 256 | red 8 x 32 x 4 | mbar
+// Feature tiles per CTA of the grouped gate | up kernel: a CTA keeps its task's quantized activations and walks
+// kGluTiles consecutive 16-feature tiles through a two-deep ring of weight buffers, the copy of tile i + 2 issued
+// as soon as tile i has been used. (One tile per CTA left the CTA's ~10 us of serial latencies - task load, copy
+// issue, activation fetch and quantization, first weight bytes, reduction - in front of every 36 KB of weights.)
+constexpr int kGluTiles = 4;
 inline int glu4_smem_bytes(int K, int row_bytes) {
-  return 8 * md_group_stride(row_bytes) + 8 * K + (K / 32) * 16 + (((K / 256) + 3) & ~3) * 16 + kMdWarps * 32 * 16 + 16;
+  return 16 * md_group_stride(row_bytes) + 8 * K + (K / 32) * 16 + (((K / 256) + 3) & ~3) * 16 + kMdWarps * 32 * 16 + 32;
 }
 
 template <typename XT>
-__global__ void __launch_bounds__(kMdThreads, 3)
+__global__ void __launch_bounds__(kMdThreads, 2)
 moe_glu_tasks_kernel(const GluArgs a, const Task4* __restrict__ tasks, const int* __restrict__ n_tasks,
                      int* __restrict__ error_word) {
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
@@ -353,28 +359,35 @@ moe_glu_tasks_kernel(const GluArgs a, const Task4* __restrict__ tasks, const int
   const int g = lane >> 2, t = lane & 3;
   const int K = a.K, nchunks = K >> 8, ncp = (nchunks + 3) & ~3, RB = a.row_bytes;
   const int gb = 4 * RB, GS = gb + ((32 - (gb & 127)) & 127);
-  uint8_t* wbuf = md_dyn;
-  uint8_t* planes = wbuf + 8 * GS;
+  uint8_t* wbuf = md_dyn;                       // two buffers of (gate tile | up tile), 4 groups each
+  uint8_t* planes = wbuf + 16 * GS;
   float* XS = reinterpret_cast<float*>(planes + 8 * K);
   float* SX = XS + 4 * (K / 32);
   float* red = SX + 4 * ncp;
-  uint64_t* mbar = reinterpret_cast<uint64_t*>(red + kMdWarps * 32 * 4);
+  uint64_t* mbar = reinterpret_cast<uint64_t*>(red + kMdWarps * 32 * 4);   // [2]
   const Task4 tk = tasks[blockIdx.y];
-  const int f0 = blockIdx.x * 16, rows = min(16, a.F - f0);
+  const int all_tiles = (a.F + 15) >> 4;
+  const int tile0 = blockIdx.x * a.tiles_per_cta, ntile = min(a.tiles_per_cta, all_tiles - tile0);
+  const int npass = (tk.m + 3) >> 2, total = npass * ntile;   // weight copies: tiles of a pass, pass after pass
+  auto issue = [&](int seq) {
+    const int f0 = (tile0 + seq % ntile) * 16, rows = min(16, a.F - f0);
+    uint8_t* wb = wbuf + (seq & 1) * 8 * GS;
+    st_mbar_expect_tx(&mbar[seq & 1], (uint32_t)(2 * rows * RB));
+    md_copy_tile(wb, a.wg + (long long)tk.expert * a.stride_g + (long long)f0 * RB, rows, RB, GS, &mbar[seq & 1]);
+    md_copy_tile(wb + 4 * GS, a.wu + (long long)tk.expert * a.stride_u + (long long)f0 * RB, rows, RB, GS, &mbar[seq & 1]);
+  };
   if (threadIdx.x == 0) {
-    st_mbar_init(mbar, 1);
+    st_mbar_init(&mbar[0], 1);
+    st_mbar_init(&mbar[1], 1);
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    st_mbar_expect_tx(mbar, (uint32_t)(2 * rows * RB));
-    md_copy_tile(wbuf, a.wg + (long long)tk.expert * a.stride_g + (long long)f0 * RB, rows, RB, GS, mbar);
-    md_copy_tile(wbuf + 4 * GS, a.wu + (long long)tk.expert * a.stride_u + (long long)f0 * RB, rows, RB, GS, mbar);
+    issue(0);
+    if (total > 1) issue(1);
   }
   const uint8_t* bcol = planes + min(g >> 1, 3) * 2 * K + (g & 1) * K + 8 * t;
-  const int lrA = min(4 * (g & 3) + (g >> 2), rows - 1), lrB = min(4 * (g & 3) + (g >> 2) + 2, rows - 1);
-  const uint8_t* base[4] = {wbuf + (lrA >> 2) * GS + (lrA & 3) * RB, wbuf + (lrB >> 2) * GS + (lrB & 3) * RB,
-                            wbuf + (4 + (lrA >> 2)) * GS + (lrA & 3) * RB, wbuf + (4 + (lrB >> 2)) * GS + (lrB & 3) * RB};
   const int rA = 4 * (g & 3) + (g >> 2);
   const int rrow[4] = {rA, rA + 2, 16 + rA, 16 + rA + 2};
-  for (int m0 = 0; m0 < tk.m; m0 += 4) {   // four activation rows per pass over the tile in shared memory
+  int seq = 0;
+  for (int m0 = 0; m0 < tk.m; m0 += 4) {   // four activation rows per pass over the CTA's tiles
     for (int sb = warp; sb < nchunks; sb += kMdWarps) {
       uint4 raw[4];   // the four loads in flight together
 #pragma unroll
@@ -386,36 +399,44 @@ moe_glu_tasks_kernel(const GluArgs a, const Task4* __restrict__ tasks, const int
       for (int m = 0; m < 4; m++)
         st_quantize<XT>(raw[m], sb, lane, K, planes + m * 2 * K, XS + m * (K / 32), SX + m * ncp);
     }
-    __syncthreads();  // first pass: the barrier is initialised
-    if (m0 == 0 && !md_wait(mbar, 0, error_word)) return;
-    float ydot[4] = {0.f, 0.f, 0.f, 0.f}, ymin[4][4] = {};
-    for (int sb = warp; sb < nchunks; sb += kMdWarps) {
-      const uint8_t* const blk[4] = {base[0] + sb * 144, base[1] + sb * 144, base[2] + sb * 144, base[3] + sb * 144};
-      st_unit_mx<2, 4>(blk, bcol + sb * 256, XS + sb * 8, K / 32, SX + sb, ncp, t, ydot, ymin);
-    }
-#pragma unroll
-    for (int r = 0; r < 4; r++) {
-#pragma unroll
-      for (int m = 0; m < 4; m++) {
-        ymin[r][m] += __shfl_xor_sync(0xffffffffu, ymin[r][m], 1);
-        ymin[r][m] += __shfl_xor_sync(0xffffffffu, ymin[r][m], 2);
+    __syncthreads();  // first pass: the barriers are initialised
+    for (int ti = 0; ti < ntile; ti++, seq++) {
+      const int f0 = (tile0 + ti) * 16, rows = min(16, a.F - f0);
+      const uint8_t* wb = wbuf + (seq & 1) * 8 * GS;
+      if (!md_wait(&mbar[seq & 1], (uint32_t)((seq >> 1) & 1), error_word)) return;
+      const int lrA = min(rA, rows - 1), lrB = min(rA + 2, rows - 1);
+      const uint8_t* base[4] = {wb + (lrA >> 2) * GS + (lrA & 3) * RB, wb + (lrB >> 2) * GS + (lrB & 3) * RB,
+                                wb + (4 + (lrA >> 2)) * GS + (lrA & 3) * RB, wb + (4 + (lrB >> 2)) * GS + (lrB & 3) * RB};
+      float ydot[4] = {0.f, 0.f, 0.f, 0.f}, ymin[4][4] = {};
+      for (int sb = warp; sb < nchunks; sb += kMdWarps) {
+        const uint8_t* const blk[4] = {base[0] + sb * 144, base[1] + sb * 144, base[2] + sb * 144, base[3] + sb * 144};
+        st_unit_mx<2, 4>(blk, bcol + sb * 256, XS + sb * 8, K / 32, SX + sb, ncp, t, ydot, ymin);
       }
-      red[(warp * 32 + rrow[r]) * 4 + t] = ydot[r] - md_pick4(ymin[r], t);   // activation row m0 + t of this lane
-    }
-    __syncthreads();
-    if (threadIdx.x < 64) {
-      const int r = threadIdx.x & 15, m = threadIdx.x >> 4;
-      if (r < rows && m0 + m < tk.m) {
-        float gs = 0.f, us = 0.f;
 #pragma unroll
-        for (int w = 0; w < kMdWarps; w++) {
-          gs += red[(w * 32 + r) * 4 + m];
-          us += red[(w * 32 + 16 + r) * 4 + m];
+      for (int r = 0; r < 4; r++) {
+#pragma unroll
+        for (int m = 0; m < 4; m++) {
+          ymin[r][m] += __shfl_xor_sync(0xffffffffu, ymin[r][m], 1);
+          ymin[r][m] += __shfl_xor_sync(0xffffffffu, ymin[r][m], 2);
         }
-        md_store(static_cast<XT*>(a.y) + (long long)tk.ent[m0 + m] * a.F + f0 + r, md_act(gs, us, a.act, a.limit));
+        red[(warp * 32 + rrow[r]) * 4 + t] = ydot[r] - md_pick4(ymin[r], t);   // activation row m0 + t of this lane
       }
+      __syncthreads();   // every warp has read this tile's weights and left its partial sums
+      if (threadIdx.x == 0 && seq + 2 < total) issue(seq + 2);   // the buffer is free: the copy after next goes in
+      if (threadIdx.x < 64) {
+        const int r = threadIdx.x & 15, m = threadIdx.x >> 4;
+        if (r < rows && m0 + m < tk.m) {
+          float gs = 0.f, us = 0.f;
+#pragma unroll
+          for (int w = 0; w < kMdWarps; w++) {
+            gs += red[(w * 32 + r) * 4 + m];
+            us += red[(w * 32 + 16 + r) * 4 + m];
+          }
+          md_store(static_cast<XT*>(a.y) + (long long)tk.ent[m0 + m] * a.F + f0 + r, md_act(gs, us, a.act, a.limit));
+        }
+      }
+      __syncthreads();   // red (and, after the last tile, the planes) are free again
     }
-    __syncthreads();   // red and the planes are free for the next pass
   }
 }
 
@@ -727,9 +748,15 @@ cudaError_t launch_moe_glu_grouped(int x_dtype, const void* x, int K, const uint
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   cudaError_t e = moe_build_tasks(idx, n_entries, n_experts, ws, L, st);
   if (e != cudaSuccess) return e;
-  GluArgs a{x, wg, wu, stride_g, stride_u, (int)row_bytes, K, F, R, (int)n_entries, n_experts, idx, y, act, limit};
+  static const int tiles_env = [] {
+    const char* e = std::getenv("KQ_MOE_GLU_TILES");   // A/B lever
+    const int v = e ? std::atoi(e) : 0;
+    return v >= 1 && v <= 64 ? v : kGluTiles;
+  }();
+  GluArgs a{x, wg, wu, stride_g, stride_u, (int)row_bytes, K, F, R, (int)n_entries, n_experts, idx, y, act, limit,
+            tiles_env};
   const int smem = glu4_smem_bytes(K, (int)row_bytes);
-  const dim3 grid((F + 15) / 16, (unsigned)L.max_tasks, 1);
+  const dim3 grid(((F + 15) / 16 + tiles_env - 1) / tiles_env, (unsigned)L.max_tasks, 1);
   const Task4* tasks = reinterpret_cast<const Task4*>(ws + L.tasks);
   const int* nt = reinterpret_cast<const int*>(ws + L.n_tasks);
   static bool done_h[16] = {}, done_b[16] = {};
