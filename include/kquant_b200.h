@@ -189,7 +189,7 @@ KQ_API int kq_moe_combine_f32(const void* d, const float* probs, long long token
  *   scores (sqrtsoftplus with a 1e-20 guard), multiplies by per_expert_scale [E] (if given) and by `scale`; with
  *   shared_gate the sigmoid of column E lands in scores[:, top_k]. indices uint32 [T, top_k], scores float32
  *   [T, top_k (+ 1)]. E <= 1024, top_k <= 16. */
-#define KQ_MOE_DIRECT_MAX_ENTRIES 192
+#define KQ_MOE_DIRECT_MAX_ENTRIES 152
 KQ_API int kq_codec_has_moe_glu(const char* kquant_type);
 KQ_API size_t kq_moe_decode_workspace_bytes(long long n_entries, int n_experts, int N_mix);
 KQ_API int kq_moe_glu_gather(const void* x, int x_dtype, long long T, int K, const void* gate_w,
