@@ -369,17 +369,29 @@ moe_glu_tasks_kernel(const GluArgs a, const Task4* __restrict__ tasks, const int
   const int all_tiles = (a.F + 15) >> 4;
   const int tile0 = blockIdx.x * a.tiles_per_cta, ntile = min(a.tiles_per_cta, all_tiles - tile0);
   const int npass = (tk.m + 3) >> 2, total = npass * ntile;   // weight copies: tiles of a pass, pass after pass
+  // Warp 0 issues a tile's eight bulk copies (four-row groups of the gate and of the up rows), one per lane: a
+  // single thread issuing all eight kept the other warps waiting at the tile's barrier for its issue time.
   auto issue = [&](int seq) {
     const int f0 = (tile0 + seq % ntile) * 16, rows = min(16, a.F - f0);
     uint8_t* wb = wbuf + (seq & 1) * 8 * GS;
-    st_mbar_expect_tx(&mbar[seq & 1], (uint32_t)(2 * rows * RB));
-    md_copy_tile(wb, a.wg + (long long)tk.expert * a.stride_g + (long long)f0 * RB, rows, RB, GS, &mbar[seq & 1]);
-    md_copy_tile(wb + 4 * GS, a.wu + (long long)tk.expert * a.stride_u + (long long)f0 * RB, rows, RB, GS, &mbar[seq & 1]);
+    if (lane == 0) st_mbar_expect_tx(&mbar[seq & 1], (uint32_t)(2 * rows * RB));
+    __syncwarp();
+    if (lane < 8) {
+      const int grp = lane & 3, r = 4 * grp;
+      if (r < rows) {
+        const uint8_t* src = (lane < 4 ? a.wg + (long long)tk.expert * a.stride_g : a.wu + (long long)tk.expert * a.stride_u) +
+                             (long long)(f0 + r) * RB;
+        st_bulk_g2s(wb + (lane < 4 ? 0 : 4 * GS) + grp * GS, src, (uint32_t)(min(4, rows - r) * RB), &mbar[seq & 1]);
+      }
+    }
   };
-  if (threadIdx.x == 0) {
-    st_mbar_init(&mbar[0], 1);
-    st_mbar_init(&mbar[1], 1);
-    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  if (warp == 0) {
+    if (lane == 0) {
+      st_mbar_init(&mbar[0], 1);
+      st_mbar_init(&mbar[1], 1);
+      asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    __syncwarp();
     issue(0);
     if (total > 1) issue(1);
   }
@@ -422,7 +434,7 @@ moe_glu_tasks_kernel(const GluArgs a, const Task4* __restrict__ tasks, const int
         red[(warp * 32 + rrow[r]) * 4 + t] = ydot[r] - md_pick4(ymin[r], t);   // activation row m0 + t of this lane
       }
       __syncthreads();   // every warp has read this tile's weights and left its partial sums
-      if (threadIdx.x == 0 && seq + 2 < total) issue(seq + 2);   // the buffer is free: the copy after next goes in
+      if (warp == 0 && seq + 2 < total) issue(seq + 2);   // the buffer is free: the copy after next goes in
       if (threadIdx.x < 64) {
         const int r = threadIdx.x & 15, m = threadIdx.x >> 4;
         if (r < rows && m0 + m < tk.m) {
